@@ -1,0 +1,334 @@
+"""Synthetic models and audio for the mynah-asr hot path.
+
+The reference's published numbers were taken on real NeMo checkpoints and real
+speech; neither is available offline, so tests and the benchmark use seeded
+synthetic stand-ins with the same shapes and value distributions:
+
+* weights: every tensor the reference loaders require, HF-verbatim names
+  (src/encoder.c:62-143, src/subsampling.c:14-58, src/decoder.c:14-62,
+  src/decoder_ctc.c:11-22), matrices ~ N(0, 0.02), norms gamma=1 beta=0,
+  BatchNorm running_mean=0 running_var=1; the linears on the reference's
+  quantisation allow-list (cli/main.c:268-282) stored as ggml blocks.
+* audio: 16 kHz mono int16, Gaussian noise (sigma 3000) with a 4 Hz amplitude
+  envelope 0.5*(1+sin(2*pi*4*t)), converted to float by /32768 as the
+  reference CLI does (cli/main.c:248).
+
+The block quantisers write valid ggml blocks (layouts as decoded by
+third_party/ingot/src/dequant.c); they are simple absmax quantisers, not
+ggml's search-based K-quant encoders — any valid block stream is a legitimate
+weight file, and both sides of a parity test see the same effective weights.
+"""
+from __future__ import annotations
+
+import json
+import struct
+from dataclasses import dataclass, field
+
+import numpy as np
+
+GGML_F32, GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 8, 12, 14
+GGML_NAMES = {"f32": GGML_F32, "q4_0": GGML_Q4_0, "q8_0": GGML_Q8_0, "q4_k": GGML_Q4_K, "q6_k": GGML_Q6_K}
+
+
+# ----------------------------------------------------------------- quantisers
+def quantize_q8_0(w: np.ndarray) -> np.ndarray:
+    g = np.ascontiguousarray(w, np.float32).reshape(-1, 32)
+    amax = np.abs(g).max(axis=1)
+    d = (amax / 127.0).astype(np.float16)
+    df = d.astype(np.float32)
+    inv = np.where(df > 0, 1.0 / np.where(df > 0, df, 1), 0).astype(np.float32)
+    q = np.clip(np.rint(g * inv[:, None]), -127, 127).astype(np.int8)
+    out = np.empty((g.shape[0], 34), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:] = q.view(np.uint8)
+    return out.reshape(-1)
+
+
+def quantize_q4_0(w: np.ndarray) -> np.ndarray:
+    g = np.ascontiguousarray(w, np.float32).reshape(-1, 32)
+    idx = np.abs(g).argmax(axis=1)
+    mx = g[np.arange(g.shape[0]), idx]
+    d = (mx / -8.0).astype(np.float16)
+    df = d.astype(np.float32)
+    inv = np.where(df != 0, 1.0 / np.where(df != 0, df, 1), 0).astype(np.float32)
+    q = np.clip((g * inv[:, None] + 8.5).astype(np.int32), 0, 15).astype(np.uint8)
+    out = np.empty((g.shape[0], 18), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:] = q[:, :16] | (q[:, 16:] << 4)
+    return out.reshape(-1)
+
+
+def quantize_q4_k(w: np.ndarray) -> np.ndarray:
+    """256-element super-blocks: per 32-sub-block affine (scale, min) with 6-bit
+    codes relative to f16 d / dmin."""
+    g = np.ascontiguousarray(w, np.float32).reshape(-1, 8, 32)
+    nb = g.shape[0]
+    mn = np.minimum(g.min(axis=2), 0.0)
+    mxv = g.max(axis=2)
+    sc = np.maximum(mxv - mn, 0) / 15.0
+    d = (sc.max(axis=1) / 63.0).astype(np.float16)
+    dmin = ((-mn).max(axis=1) / 63.0).astype(np.float16)
+    df, dmf = d.astype(np.float32), dmin.astype(np.float32)
+    ls = np.clip(np.rint(sc / np.where(df > 0, df, 1)[:, None]), 0, 63).astype(np.uint8)
+    lm = np.clip(np.rint(-mn / np.where(dmf > 0, dmf, 1)[:, None]), 0, 63).astype(np.uint8)
+    eff_d = df[:, None] * ls
+    eff_m = dmf[:, None] * lm
+    q = np.clip(np.rint((g + eff_m[:, :, None]) / np.where(eff_d > 0, eff_d, 1)[:, :, None]), 0, 15).astype(np.uint8)
+    out = np.zeros((nb, 144), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:4] = dmin.view(np.uint8).reshape(-1, 2)
+    s = out[:, 4:16]
+    s[:, 0:4] = (ls[:, 0:4] & 63) | ((ls[:, 4:8] >> 4) << 6)
+    s[:, 4:8] = (lm[:, 0:4] & 63) | ((lm[:, 4:8] >> 4) << 6)
+    s[:, 8:12] = (ls[:, 4:8] & 0x0F) | ((lm[:, 4:8] & 0x0F) << 4)
+    qq = q.reshape(nb, 4, 2, 32)
+    out[:, 16:] = (qq[:, :, 0, :] | (qq[:, :, 1, :] << 4)).reshape(nb, 128)
+    return out.reshape(-1)
+
+
+def quantize_q6_k(w: np.ndarray) -> np.ndarray:
+    """256-element super-blocks: 16 sub-blocks of 16 with int8 scales, 6-bit
+    quants stored as ql nibbles + qh bit pairs."""
+    g = np.ascontiguousarray(w, np.float32).reshape(-1, 16, 16)
+    nb = g.shape[0]
+    amax = np.abs(g).max(axis=2)
+    sub = amax / 31.0
+    d = (sub.max(axis=1) / 127.0).astype(np.float16)
+    df = d.astype(np.float32)
+    sc = np.clip(np.rint(sub / np.where(df > 0, df, 1)[:, None]), 0, 127).astype(np.int8)
+    eff = df[:, None] * sc.astype(np.float32)
+    q = (np.clip(np.rint(g / np.where(eff > 0, eff, 1)[:, :, None]), -32, 31) + 32).astype(np.uint8)
+    q = q.reshape(nb, 2, 4, 32)                 # half, quarter j, position i
+    out = np.zeros((nb, 210), np.uint8)
+    ql = out[:, 0:128].reshape(nb, 2, 64)
+    qh = out[:, 128:192].reshape(nb, 2, 32)
+    ql[:, :, 0:32] = (q[:, :, 0] & 0x0F) | ((q[:, :, 2] & 0x0F) << 4)
+    ql[:, :, 32:64] = (q[:, :, 1] & 0x0F) | ((q[:, :, 3] & 0x0F) << 4)
+    qh[:] = (q[:, :, 0] >> 4) | ((q[:, :, 1] >> 4) << 2) | ((q[:, :, 2] >> 4) << 4) | ((q[:, :, 3] >> 4) << 6)
+    out[:, 192:208] = sc.view(np.uint8)
+    out[:, 208:210] = d.view(np.uint8).reshape(-1, 2)
+    return out.reshape(-1)
+
+
+QUANTIZERS = {GGML_Q8_0: quantize_q8_0, GGML_Q4_0: quantize_q4_0, GGML_Q4_K: quantize_q4_k, GGML_Q6_K: quantize_q6_k}
+
+
+# ------------------------------------------------------------- mel filterbank
+def _hz_to_mel(f):
+    f = np.asarray(f, np.float64)
+    return np.where(f >= 1000.0, 15.0 + 27.0 * np.log(np.maximum(f, 1e-10) / 1000.0) / np.log(6.4), 3.0 * f / 200.0)
+
+
+def _mel_to_hz(m):
+    m = np.asarray(m, np.float64)
+    return np.where(m >= 15.0, 1000.0 * np.exp(np.log(6.4) * (m - 15.0) / 27.0), 200.0 * m / 3.0)
+
+
+def mel_filterbank(n_mels: int, n_fft: int = 512, sample_rate: int = 16000) -> np.ndarray:
+    """Slaney-scale, slaney-normalised triangular filters [n_fft/2+1, n_mels]
+    (the construction tools/convert_nemo.py:59-74 writes to mel_filters)."""
+    n_freqs = n_fft // 2 + 1
+    freqs = np.linspace(0.0, sample_rate // 2, n_freqs)
+    pts = _mel_to_hz(np.linspace(_hz_to_mel(0.0), _hz_to_mel(sample_rate / 2), n_mels + 2))
+    diff = pts[1:] - pts[:-1]
+    slopes = pts[None, :] - freqs[:, None]
+    fb = np.maximum(0.0, np.minimum(-slopes[:, :-2] / diff[:-1], slopes[:, 2:] / diff[1:]))
+    fb *= 2.0 / (pts[2:] - pts[:-2])
+    return fb.astype(np.float32)
+
+
+def hann_window(win_length: int = 400) -> np.ndarray:
+    return np.hanning(win_length).astype(np.float32)
+
+
+# -------------------------------------------------------------------- configs
+@dataclass
+class ModelConfig:
+    name: str = "tiny"
+    d_model: int = 128
+    n_layers: int = 2
+    n_heads: int = 4
+    ffn_dim: int = 512
+    conv_k: int = 9
+    n_mels: int = 80
+    channels: int = 256
+    causal: bool = False          # Nemotron-style causal convs + LayerNorm conv norm
+    decoder: str = "ctc"          # "ctc" | "rnnt" | "tdt"
+    vocab: int = 129              # includes blank (last index for CTC; blank_id = vocab-1)
+    pred_hidden: int = 640
+    pred_layers: int = 1
+    durations: tuple = ()
+    max_symbols: int = 10
+    wtype: str = "q8_0"           # ggml type of the allow-listed linears
+    wtype_out: str = ""           # optional second type for the output projections (mixed K-quant)
+    use_bias: bool = False
+    normalize: bool = True        # per_feature mel normalisation (Parakeet); NA for Nemotron
+    left: int = -1
+    right: int = -1
+    d_out: int = field(init=False, default=0)
+
+    def __post_init__(self):
+        self.d_out = self.d_model if self.decoder == "ctc" else self.pred_hidden
+
+
+CONFIGS = {
+    # Parakeet-TDT_CTC-110M-shaped, CTC head, Q8_0
+    "cfg0": dict(name="cfg0", d_model=512, n_layers=17, n_heads=8, ffn_dim=2048, n_mels=80,
+                 decoder="ctc", vocab=1025, wtype="q8_0"),
+    # Parakeet-TDT-0.6B-shaped, Q4_0
+    "cfg1": dict(name="cfg1", d_model=1024, n_layers=24, n_heads=8, ffn_dim=4096, n_mels=128,
+                 decoder="tdt", vocab=8193, pred_hidden=640, pred_layers=2,
+                 durations=(0, 1, 2, 3, 4), wtype="q4_0"),
+    # Parakeet-RNNT-1.1B-shaped, Q4_K + Q6_K
+    "cfg2": dict(name="cfg2", d_model=1024, n_layers=42, n_heads=8, ffn_dim=4096, n_mels=128,
+                 decoder="rnnt", vocab=1025, pred_hidden=640, pred_layers=1, wtype="q4_k",
+                 wtype_out="q6_k"),
+    # Nemotron-streaming-0.6B-shaped, Q8_0
+    "cfg3": dict(name="cfg3", d_model=1024, n_layers=24, n_heads=8, ffn_dim=4096, n_mels=128,
+                 causal=True, decoder="rnnt", vocab=1025, pred_hidden=640, pred_layers=1,
+                 wtype="q8_0", normalize=False, left=70, right=0),
+}
+
+
+def config(name: str, **over) -> ModelConfig:
+    kw = dict(CONFIGS[name]) if name in CONFIGS else dict(name=name)
+    kw.update(over)
+    return ModelConfig(**kw)
+
+
+# --------------------------------------------------------------------- models
+class Tensor:
+    """One named tensor: ggml type, logical shape, raw bytes."""
+    __slots__ = ("name", "ggml_type", "shape", "raw")
+
+    def __init__(self, name, ggml_type, shape, raw):
+        self.name, self.ggml_type, self.shape = name, int(ggml_type), tuple(int(s) for s in shape)
+        self.raw = np.ascontiguousarray(raw).view(np.uint8).reshape(-1)
+
+
+def _freq_dims(n_mels: int, causal: bool):
+    f = n_mels
+    for _ in range(3):
+        f = (f + (3 if causal else 2) - 3) // 2 + 1
+    return f
+
+
+def make_model(cfg: ModelConfig, seed: int = 0, weight_std: float = 0.02):
+    """Returns an ordered dict name -> Tensor with every tensor the loaders need."""
+    rng = np.random.default_rng(seed)
+    T = {}
+
+    def f32t(name, arr):
+        T[name] = Tensor(name, GGML_F32, arr.shape, np.asarray(arr, np.float32))
+
+    def normal(*shape):
+        return rng.standard_normal(shape, dtype=np.float32) * np.float32(weight_std)
+
+    def qlin(name, n, k, out_proj=False):
+        w = normal(n, k)
+        tname = cfg.wtype_out if (out_proj and cfg.wtype_out) else cfg.wtype
+        gt = GGML_NAMES[tname]
+        if gt in (GGML_Q4_K, GGML_Q6_K) and k % 256 != 0:
+            gt = GGML_Q8_0                      # K-quant fallback, as tools/export_gguf.py:106-107
+        if gt == GGML_F32:
+            f32t(name, w)
+        else:
+            T[name] = Tensor(name, gt, (n, k), QUANTIZERS[gt](w))
+
+    d, F, C, k = cfg.d_model, cfg.ffn_dim, cfg.channels, cfg.conv_k
+    ss = "encoder.subsampling."
+    if cfg.causal:
+        names = dict(cin=ss + "conv_in", dw=[ss + "layers.0.depthwise_conv", ss + "layers.1.depthwise_conv"],
+                     pw=[ss + "layers.0.pointwise_conv", ss + "layers.1.pointwise_conv"])
+    else:
+        names = dict(cin=ss + "layers.0", dw=[ss + "layers.2", ss + "layers.5"], pw=[ss + "layers.3", ss + "layers.6"])
+    # fan-in-scaled conv weights keep the subsampling output O(1) (the reference
+    # recipe's 0.02 would vanish through three stages; shapes are what matter)
+    f32t(names["cin"] + ".weight", rng.standard_normal((C, 1, 3, 3), dtype=np.float32) / 3.0)
+    f32t(names["cin"] + ".bias", np.zeros(C))
+    for i in range(2):
+        f32t(names["dw"][i] + ".weight", rng.standard_normal((C, 1, 3, 3), dtype=np.float32) / 3.0)
+        f32t(names["dw"][i] + ".bias", np.zeros(C))
+        f32t(names["pw"][i] + ".weight", rng.standard_normal((C, C, 1, 1), dtype=np.float32) / np.sqrt(C))
+        f32t(names["pw"][i] + ".bias", np.zeros(C))
+    CF = C * _freq_dims(cfg.n_mels, cfg.causal)
+    f32t(ss + "linear.weight", rng.standard_normal((d, CF), dtype=np.float32) / np.sqrt(CF))
+    f32t(ss + "linear.bias", np.zeros(d))
+
+    for li in range(cfg.n_layers):
+        p = f"encoder.layers.{li}."
+        for nm in ("norm_feed_forward1", "norm_self_att", "norm_conv", "norm_feed_forward2", "norm_out"):
+            f32t(p + nm + ".weight", np.ones(d)); f32t(p + nm + ".bias", np.zeros(d))
+        qlin(p + "feed_forward1.linear1.weight", F, d)
+        qlin(p + "feed_forward1.linear2.weight", d, F, True)
+        qlin(p + "feed_forward2.linear1.weight", F, d)
+        qlin(p + "feed_forward2.linear2.weight", d, F, True)
+        for nm in ("q_proj", "k_proj", "v_proj"):
+            qlin(p + f"self_attn.{nm}.weight", d, d)
+        qlin(p + "self_attn.o_proj.weight", d, d, True)
+        f32t(p + "self_attn.relative_k_proj.weight", normal(d, d))
+        f32t(p + "self_attn.bias_u", normal(cfg.n_heads, d // cfg.n_heads))
+        f32t(p + "self_attn.bias_v", normal(cfg.n_heads, d // cfg.n_heads))
+        qlin(p + "conv.pointwise_conv1.weight", 2 * d, d)
+        f32t(p + "conv.depthwise_conv.weight", rng.standard_normal((d, 1, k), dtype=np.float32) / np.sqrt(k))
+        qlin(p + "conv.pointwise_conv2.weight", d, d, True)
+        f32t(p + "conv.norm.weight", np.ones(d)); f32t(p + "conv.norm.bias", np.zeros(d))
+        if not cfg.causal:                      # Parakeet: BatchNorm with running stats
+            f32t(p + "conv.norm.running_mean", np.zeros(d)); f32t(p + "conv.norm.running_var", np.ones(d))
+        if cfg.use_bias:
+            for nm, n in (("feed_forward1.linear1", F), ("feed_forward1.linear2", d), ("feed_forward2.linear1", F),
+                          ("feed_forward2.linear2", d), ("self_attn.q_proj", d), ("self_attn.k_proj", d),
+                          ("self_attn.v_proj", d), ("self_attn.o_proj", d), ("conv.pointwise_conv1", 2 * d),
+                          ("conv.depthwise_conv", d), ("conv.pointwise_conv2", d)):
+                f32t(p + nm + ".bias", normal(n))
+
+    if cfg.decoder == "ctc":
+        f32t("ctc_head.weight", normal(cfg.vocab, d, 1)); f32t("ctc_head.bias", np.zeros(cfg.vocab))
+    else:
+        H, V, ND = cfg.pred_hidden, cfg.vocab, len(cfg.durations)
+        f32t("encoder_projector.weight", rng.standard_normal((H, d), dtype=np.float32) / np.sqrt(d))
+        f32t("encoder_projector.bias", np.zeros(H))
+        f32t("decoder.embedding.weight", rng.standard_normal((V, H), dtype=np.float32))
+        for l in range(cfg.pred_layers):
+            f32t(f"decoder.lstm.weight_ih_l{l}", rng.standard_normal((4 * H, H), dtype=np.float32) / np.sqrt(H))
+            f32t(f"decoder.lstm.weight_hh_l{l}", rng.standard_normal((4 * H, H), dtype=np.float32) / np.sqrt(H))
+            f32t(f"decoder.lstm.bias_ih_l{l}", np.zeros(4 * H)); f32t(f"decoder.lstm.bias_hh_l{l}", np.zeros(4 * H))
+        f32t("decoder.decoder_projector.weight", rng.standard_normal((H, H), dtype=np.float32) / np.sqrt(H))
+        f32t("decoder.decoder_projector.bias", np.zeros(H))
+        # the joint head is on the allow-list; its scale is fan-in based so the
+        # greedy stream is not a single repeated argmax
+        w = rng.standard_normal((V + ND, H), dtype=np.float32) / np.sqrt(H)
+        gt = GGML_NAMES[cfg.wtype]
+        if gt in (GGML_Q4_K, GGML_Q6_K) and H % 256 != 0:
+            gt = GGML_Q8_0
+        T["joint.head.weight"] = Tensor("joint.head.weight", gt, (V + ND, H), QUANTIZERS[gt](w)) if gt != GGML_F32 \
+            else Tensor("joint.head.weight", GGML_F32, (V + ND, H), w)
+        f32t("joint.head.bias", np.zeros(V + ND))
+    return T
+
+
+def synth_audio(seconds: float, seed: int = 0, sample_rate: int = 16000) -> np.ndarray:
+    """int16-quantised Gaussian noise with a 4 Hz envelope, as float32 in [-1,1]."""
+    n = int(round(seconds * sample_rate))
+    rng = np.random.default_rng(1000003 * (seed + 1))
+    t = np.arange(n, dtype=np.float64) / sample_rate
+    env = 0.5 * (1.0 + np.sin(2.0 * np.pi * 4.0 * t))
+    x = np.clip(np.rint(3000.0 * rng.standard_normal(n) * env), -32768, 32767).astype(np.int16)
+    return (x.astype(np.float32) / np.float32(32768.0)).astype(np.float32)
+
+
+def write_safetensors(path: str, tensors: dict) -> None:
+    """name -> float32 ndarray, in the safetensors container the reference's
+    loader opens (8-byte little-endian header length, JSON header, raw data)."""
+    hdr, off = {}, 0
+    for name, a in tensors.items():
+        a = np.ascontiguousarray(a, np.float32)
+        hdr[name] = {"dtype": "F32", "shape": list(a.shape), "data_offsets": [off, off + a.nbytes]}
+        off += a.nbytes
+    js = json.dumps(hdr, separators=(",", ":")).encode()
+    js += b" " * ((8 - len(js) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(js)))
+        f.write(js)
+        for a in tensors.values():
+            f.write(np.ascontiguousarray(a, np.float32).tobytes())

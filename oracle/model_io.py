@@ -1,0 +1,91 @@
+"""Glue between a synthetic tensor dictionary and the two CPU checkers —
+TEST INFRASTRUCTURE ONLY.
+
+* effective_f32(): what the reference holds after its eager GGUF block decode
+  (src/weights.c:90-115): every tensor as float32.
+* oracle_model(): the nested dict oracle/mynah_oracle.py works on.
+* write_reference_files(): model.safetensors (+ mel_filters.safetensors) the
+  compiled reference opens through its own loader.
+"""
+from __future__ import annotations
+
+import os
+
+import numpy as np
+
+from . import mynah_oracle as O
+
+
+def effective_f32(tensors) -> dict:
+    out = {}
+    for name, t in tensors.items():
+        a = O.ggml_dequant(t.ggml_type, t.raw)
+        out[name] = a.reshape(t.shape).astype(np.float32)
+    return out
+
+
+def oracle_model(cfg, tensors) -> dict:
+    W = effective_f32(tensors)
+    ss = "encoder.subsampling."
+    if cfg.causal:
+        cin, dw, pw = ss + "conv_in", [ss + f"layers.{i}.depthwise_conv" for i in range(2)], \
+            [ss + f"layers.{i}.pointwise_conv" for i in range(2)]
+    else:
+        cin, dw, pw = ss + "layers.0", [ss + "layers.2", ss + "layers.5"], [ss + "layers.3", ss + "layers.6"]
+    M = {"causal": bool(cfg.causal), "n_heads": cfg.n_heads, "xscale": 1.0,
+         "ss": {"conv_in_w": W[cin + ".weight"], "conv_in_b": W[cin + ".bias"],
+                "dw_w": [W[n + ".weight"] for n in dw], "dw_b": [W[n + ".bias"] for n in dw],
+                "pw_w": [W[n + ".weight"] for n in pw], "pw_b": [W[n + ".bias"] for n in pw],
+                "lin_w": W[ss + "linear.weight"], "lin_b": W[ss + "linear.bias"]},
+         "layers": []}
+    lin = {"ff1_w1": "feed_forward1.linear1", "ff1_w2": "feed_forward1.linear2",
+           "ff2_w1": "feed_forward2.linear1", "ff2_w2": "feed_forward2.linear2",
+           "q_w": "self_attn.q_proj", "k_w": "self_attn.k_proj", "v_w": "self_attn.v_proj",
+           "o_w": "self_attn.o_proj", "pw1_w": "conv.pointwise_conv1", "pw2_w": "conv.pointwise_conv2"}
+    for li in range(cfg.n_layers):
+        p = f"encoder.layers.{li}."
+        L = {}
+        for short, nm in (("ln_ff1", "norm_feed_forward1"), ("ln_att", "norm_self_att"), ("ln_conv", "norm_conv"),
+                          ("ln_ff2", "norm_feed_forward2"), ("ln_out", "norm_out")):
+            L[short + "_w"], L[short + "_b"] = W[p + nm + ".weight"], W[p + nm + ".bias"]
+        for short, nm in lin.items():
+            L[short] = W[p + nm + ".weight"].reshape(W[p + nm + ".weight"].shape[0], -1)
+            if p + nm + ".bias" in W:
+                L[short + "_b"] = W[p + nm + ".bias"]
+        L["relk_w"] = W[p + "self_attn.relative_k_proj.weight"]
+        L["bias_u"], L["bias_v"] = W[p + "self_attn.bias_u"], W[p + "self_attn.bias_v"]
+        L["dw_w"] = W[p + "conv.depthwise_conv.weight"]
+        L["dw_b"] = W.get(p + "conv.depthwise_conv.bias")
+        L["cnorm_w"], L["cnorm_b"] = W[p + "conv.norm.weight"], W[p + "conv.norm.bias"]
+        if p + "conv.norm.running_mean" in W:   # BatchNorm fold (src/encoder.c:149-170)
+            mu, var = W[p + "conv.norm.running_mean"], W[p + "conv.norm.running_var"]
+            scale = (L["cnorm_w"].astype(np.float64) / np.sqrt(var.astype(np.float64) + 1e-5)).astype(np.float32)
+            L["cnorm_scale"], L["cnorm_shift"] = scale, (L["cnorm_b"] - mu * scale).astype(np.float32)
+        M["layers"].append(L)
+    if "encoder_projector.weight" in W:
+        M["encproj_w"], M["encproj_b"] = W["encoder_projector.weight"], W["encoder_projector.bias"]
+    if "ctc_head.weight" in W:
+        M["ctc_w"] = W["ctc_head.weight"].reshape(W["ctc_head.weight"].shape[0], -1)
+        M["ctc_b"] = W["ctc_head.bias"]
+    if "decoder.embedding.weight" in W:
+        nl = cfg.pred_layers
+        M["dec"] = {"embedding": W["decoder.embedding.weight"], "hidden": cfg.pred_hidden, "n_layers": nl,
+                    "w_ih": [W[f"decoder.lstm.weight_ih_l{l}"] for l in range(nl)],
+                    "w_hh": [W[f"decoder.lstm.weight_hh_l{l}"] for l in range(nl)],
+                    "b_ih": [W[f"decoder.lstm.bias_ih_l{l}"] for l in range(nl)],
+                    "b_hh": [W[f"decoder.lstm.bias_hh_l{l}"] for l in range(nl)],
+                    "proj_w": W["decoder.decoder_projector.weight"], "proj_b": W["decoder.decoder_projector.bias"],
+                    "head_w": W["joint.head.weight"], "head_b": W["joint.head.bias"],
+                    "vocab": cfg.vocab, "blank": cfg.vocab - 1, "max_symbols": cfg.max_symbols,
+                    "durations": list(cfg.durations)}
+    return M
+
+
+def write_reference_files(dirpath: str, cfg, tensors, synth) -> tuple:
+    """Writes model.safetensors (effective f32) and mel_filters.safetensors."""
+    os.makedirs(dirpath, exist_ok=True)
+    wpath = os.path.join(dirpath, "model.safetensors")
+    mpath = os.path.join(dirpath, "mel_filters.safetensors")
+    synth.write_safetensors(wpath, effective_f32(tensors))
+    synth.write_safetensors(mpath, {"mel_fb": synth.mel_filterbank(cfg.n_mels), "window": synth.hann_window()})
+    return wpath, mpath

@@ -1,0 +1,508 @@
+"""CPU oracle for the mynah-asr hot path — TEST INFRASTRUCTURE ONLY.
+
+A numpy restatement of the reference's algorithms for the quantised matmul,
+the FastConformer encoder, the dw-striding subsampling, the log-mel front end
+and the greedy CTC / RNNT / TDT decoders. Nothing in the product imports this
+module: it exists so that the CUDA path can be checked against the reference's
+arithmetic on machines where the reference sources are absent.
+
+Parity pin: every function here is checked (tests/test_oracle_pin.py) against
+  * the ggml block-decode known-answer vectors the reference ships
+    (third_party/ingot/tests/fixtures/{Q8_0,Q4_0,Q4_K,Q6_K}.{bin,ref}), and
+  * outputs of the reference itself, compiled unmodified into
+    oracle/_ref/libmynah_ref.so, committed as fixtures under tests/golden/.
+
+Each function cites the reference file:line it follows (paths relative to the
+reference project root). Float work is done in float32 with float64 where the
+reference uses double; integer work is exact.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+f32 = np.float32
+
+# --------------------------------------------------------------------------
+# ggml block formats (third_party/ingot/src/dequant.c)
+# --------------------------------------------------------------------------
+GGML_F32, GGML_F16, GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 1, 2, 8, 12, 14
+BLOCK_GEOM = {GGML_Q4_0: (32, 18), GGML_Q8_0: (32, 34), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210)}
+
+
+def _f16(b: np.ndarray) -> np.ndarray:
+    """little-endian byte pairs [..., 2] -> float32"""
+    return np.ascontiguousarray(b).view("<f2").astype(f32)[..., 0]
+
+
+def dequant_q8_0(raw: np.ndarray) -> np.ndarray:
+    """34-byte blocks: f16 d + 32 int8; w = d*q (dequant.c:131-156)."""
+    blk = raw.reshape(-1, 34)
+    d = _f16(blk[:, 0:2])
+    q = blk[:, 2:].view(np.int8).astype(f32)
+    return (d[:, None] * q).reshape(-1)
+
+
+def dequant_q4_0(raw: np.ndarray) -> np.ndarray:
+    """18-byte blocks: f16 d + 16 bytes; byte i holds element i (low nibble) and
+    element i+16 (high nibble); w = d*(nib-8) (dequant.c:72-83)."""
+    blk = raw.reshape(-1, 18)
+    d = _f16(blk[:, 0:2])
+    q = blk[:, 2:]
+    lo = (q & 0x0F).astype(np.int32) - 8
+    hi = (q >> 4).astype(np.int32) - 8
+    w = np.concatenate([lo, hi], axis=1).astype(f32)
+    return (d[:, None] * w).reshape(-1)
+
+
+def _k4_scale_min(sc: np.ndarray):
+    """6-bit packed scales/mins of Q4_K (dequant.c:55-68). sc [nb,12] uint8 ->
+    (scale [nb,8], min [nb,8])."""
+    s = np.zeros(sc.shape[:-1] + (8,), np.uint8)
+    m = np.zeros_like(s)
+    s[:, 0:4] = sc[:, 0:4] & 63
+    m[:, 0:4] = sc[:, 4:8] & 63
+    s[:, 4:8] = (sc[:, 8:12] & 0x0F) | ((sc[:, 0:4] >> 6) << 4)
+    m[:, 4:8] = (sc[:, 8:12] >> 4) | ((sc[:, 4:8] >> 6) << 4)
+    return s, m
+
+
+def dequant_q4_k(raw: np.ndarray) -> np.ndarray:
+    """144-byte super-blocks of 256: f16 d, f16 dmin, 12 bytes of 6-bit
+    scales/mins, 128 bytes of nibbles; eight sub-blocks of 32,
+    w = (d*sc)*q - (dmin*m) (dequant.c:222-273)."""
+    blk = raw.reshape(-1, 144)
+    d = _f16(blk[:, 0:2])
+    dmin = _f16(blk[:, 2:4])
+    sc, mn = _k4_scale_min(blk[:, 4:16])
+    q = blk[:, 16:].reshape(-1, 4, 32)          # four groups of 64 elements
+    lo = (q & 0x0F).astype(f32)                  # sub-block 2g
+    hi = (q >> 4).astype(f32)                    # sub-block 2g+1
+    qq = np.stack([lo, hi], axis=2).reshape(-1, 8, 32)
+    dd = (d[:, None] * sc.astype(f32)).astype(f32)
+    mm = (dmin[:, None] * mn.astype(f32)).astype(f32)
+    return (dd[:, :, None] * qq - mm[:, :, None]).astype(f32).reshape(-1)
+
+
+def dequant_q6_k(raw: np.ndarray) -> np.ndarray:
+    """210-byte super-blocks of 256: ql[128], qh[64], 16 int8 scales, f16 d;
+    w = d*sc*(q-32), two halves of 128 (dequant.c:352-445)."""
+    blk = raw.reshape(-1, 210)
+    nb = blk.shape[0]
+    ql = blk[:, 0:128].reshape(nb, 2, 64)
+    qh = blk[:, 128:192].reshape(nb, 2, 32)
+    sc = blk[:, 192:208].view(np.int8).reshape(nb, 2, 8).astype(f32)
+    d = _f16(blk[:, 208:210])
+    out = np.zeros((nb, 2, 128), f32)
+    l0, l1 = ql[:, :, 0:32], ql[:, :, 32:64]
+    q1 = ((l0 & 0x0F) | (((qh >> 0) & 3) << 4)).astype(np.int32) - 32
+    q2 = ((l1 & 0x0F) | (((qh >> 2) & 3) << 4)).astype(np.int32) - 32
+    q3 = ((l0 >> 4) | (((qh >> 4) & 3) << 4)).astype(np.int32) - 32
+    q4 = ((l1 >> 4) | (((qh >> 6) & 3) << 4)).astype(np.int32) - 32
+    isx = np.arange(32) // 16
+    for j, q in enumerate((q1, q2, q3, q4)):
+        s = sc[:, :, isx + 2 * j]               # [nb,2,32]
+        out[:, :, 32 * j:32 * j + 32] = ((d[:, None, None] * s).astype(f32) * q.astype(f32))
+    return out.reshape(-1)
+
+
+def ggml_dequant(ggml_type: int, raw: np.ndarray) -> np.ndarray:
+    raw = np.ascontiguousarray(raw, dtype=np.uint8).reshape(-1)
+    if ggml_type == GGML_F32:
+        return raw.view(f32).copy()
+    return {GGML_Q8_0: dequant_q8_0, GGML_Q4_0: dequant_q4_0,
+            GGML_Q4_K: dequant_q4_k, GGML_Q6_K: dequant_q6_k}[ggml_type](raw)
+
+
+# --------------------------------------------------------------------------
+# mynah-native int8 / int4 (src/qmat.c)
+# --------------------------------------------------------------------------
+def _round_half_away(v: np.ndarray) -> np.ndarray:
+    """(int)(v >= 0 ? v + 0.5f : v - 0.5f) in float32 (qmat.c:33,57,196)."""
+    v = v.astype(f32)
+    return np.where(v >= 0, (v + f32(0.5)).astype(f32), (v - f32(0.5)).astype(f32)).astype(np.int32)
+
+
+def quantize_int8(w: np.ndarray):
+    """Per-row symmetric int8, scale = amax/127 (qmat.c:19-36)."""
+    w = w.astype(f32)
+    amax = np.abs(w).max(axis=1)
+    scale = np.where(amax > 0, amax / f32(127.0), f32(1.0)).astype(f32)
+    inv = (f32(1.0) / scale).astype(f32)
+    q = _round_half_away(w * inv[:, None]).astype(np.int8)
+    return q, scale
+
+
+def quantize_int4(w: np.ndarray):
+    """Per-group-of-32 symmetric int4: byte j of a group = element 2j | (2j+1)<<4,
+    stored value = q+8, scale = amax/7 (qmat.c:38-67)."""
+    w = w.astype(f32)
+    n, k = w.shape
+    g = w.reshape(n, k // 32, 32)
+    amax = np.abs(g).max(axis=2)
+    scale = np.where(amax > 0, amax / f32(7.0), f32(1.0)).astype(f32)
+    inv = (f32(1.0) / scale).astype(f32)
+    q = np.clip(_round_half_away(g * inv[:, :, None]), -8, 7)
+    packed = ((q[:, :, 0::2] + 8) | ((q[:, :, 1::2] + 8) << 4)).astype(np.uint8)
+    return packed.reshape(n, k // 2), scale
+
+
+def dequant_int8(q: np.ndarray, scale: np.ndarray) -> np.ndarray:
+    return q.astype(f32) * scale[:, None].astype(f32)          # qmat.c:153-156
+
+
+def unpack_int4(q4: np.ndarray) -> np.ndarray:
+    """[n,k/2] packed -> [n,k] signed ints in [-8,7] (qmat.c:160-166)."""
+    n = q4.shape[0]
+    lo = (q4 & 0x0F).astype(np.int32) - 8
+    hi = (q4 >> 4).astype(np.int32) - 8
+    return np.stack([lo, hi], axis=2).reshape(n, -1)
+
+
+def dequant_int4(q4: np.ndarray, scale: np.ndarray) -> np.ndarray:
+    w = unpack_int4(q4).astype(f32)
+    n, k = w.shape
+    return (w.reshape(n, k // 32, 32) * scale[:, :, None].astype(f32)).reshape(n, k)
+
+
+def quantize_act_int8(x: np.ndarray):
+    """Per-row absmax activation quantisation: inv = 127/amax, round half away,
+    clamp to +-127, returns (qx int8 [T,k], sx = amax/127) (qmat.c:186-202)."""
+    x = x.astype(f32)
+    amax = np.abs(x).max(axis=1)
+    inv = np.where(amax > 0, f32(127.0) / np.where(amax > 0, amax, 1).astype(f32), f32(0)).astype(f32)
+    q = np.clip(_round_half_away(x * inv[:, None]), -127, 127).astype(np.int8)
+    sx = np.where(amax > 0, amax / f32(127.0), f32(0)).astype(f32)
+    return q, sx
+
+
+def int_dots_q8(qx: np.ndarray, qw: np.ndarray) -> np.ndarray:
+    """Exact int32 row dots [T,n] (qmat.c:285-300: one int32 per (t, row))."""
+    return qx.astype(np.int32) @ qw.astype(np.int32).T
+
+
+def int_dots_q4(qx: np.ndarray, qw_signed: np.ndarray) -> np.ndarray:
+    """Exact per-group int32 dots [T,n,k/32] (qmat.c:347-362)."""
+    T, k = qx.shape
+    n = qw_signed.shape[0]
+    a = qx.astype(np.int32).reshape(T, 1, k // 32, 32)
+    b = qw_signed.astype(np.int32).reshape(1, n, k // 32, 32)
+    return (a * b).sum(axis=3)
+
+
+def qmat_mul_a8_q8(x, q, scale):
+    """int8 activations x int8 weights: (float)int32 * ws * sx (qmat.c:299)."""
+    qx, sx = quantize_act_int8(x)
+    dots = int_dots_q8(qx, q).astype(f32)
+    return ((dots * scale[None, :].astype(f32)).astype(f32) * sx[:, None]).astype(f32)
+
+
+def qmat_mul_a8_q4(x, q4, scale):
+    """Per group: acc += (float)int32_g * scale_g, groups in ascending order,
+    then * sx (qmat.c:347-363)."""
+    qx, sx = quantize_act_int8(x)
+    dots = int_dots_q4(qx, unpack_int4(q4)).astype(f32)         # [T,n,G]
+    acc = np.zeros(dots.shape[:2], f32)
+    for g in range(dots.shape[2]):
+        acc = (acc + (dots[:, :, g] * scale[None, :, g].astype(f32)).astype(f32)).astype(f32)
+    return (acc * sx[:, None]).astype(f32)
+
+
+def gemm_wt(x, w):
+    """out[T,n] = x[T,k] @ W[n,k]^T in float32 (backend.c:68-81)."""
+    return (x.astype(f32) @ w.astype(f32).T).astype(f32)
+
+
+# --------------------------------------------------------------------------
+# activations (src/qmat.h:31-35, src/backend.c:88-108)
+# --------------------------------------------------------------------------
+def sigmoid(x):
+    x = x.astype(f32)
+    e = np.exp(-np.abs(x)).astype(f32)
+    return np.where(x >= 0, f32(1) / (f32(1) + e), e / (f32(1) + e)).astype(f32)
+
+
+def silu(x):
+    return (x.astype(f32) * sigmoid(x)).astype(f32)
+
+
+# --------------------------------------------------------------------------
+# log-mel front end (src/features.c:106-167)
+# --------------------------------------------------------------------------
+def log_mel(audio, mel_fb, window, n_fft=512, hop=160, preemph=0.97, guard=2.0 ** -24,
+            normalize_per_feature=False):
+    """audio float32 [S] -> (feats [T, n_mels] float32, valid). T = 1 + S//hop,
+    rows >= valid = S//hop stay zero. Double precision inside, like the reference."""
+    audio = np.asarray(audio, f32)
+    S = audio.shape[0]
+    n_mels = mel_fb.shape[1]
+    pad = n_fft // 2
+    T, valid = 1 + S // hop, S // hop
+    y = np.zeros(S + 2 * pad, np.float64)
+    if S > 0:
+        y[pad] = audio[0]
+        y[pad + 1:pad + S] = audio[1:].astype(np.float64) - preemph * audio[:-1].astype(np.float64)
+    win = np.zeros(n_fft, np.float64)
+    off = (n_fft - window.shape[0]) // 2
+    win[off:off + window.shape[0]] = window.astype(np.float64)
+    feats = np.zeros((T, n_mels), f32)
+    if valid > 0:
+        idx = np.arange(valid)[:, None] * hop + np.arange(n_fft)[None, :]
+        spec = np.fft.rfft(y[idx] * win[None, :], axis=1)
+        power = spec.real ** 2 + spec.imag ** 2
+        acc = power @ mel_fb.astype(np.float64)
+        feats[:valid] = np.log(acc + guard).astype(f32)
+    if normalize_per_feature and valid > 1:
+        v = feats[:valid].astype(np.float64)
+        mu = v.mean(axis=0)
+        var = ((v - mu) ** 2).sum(axis=0) / (valid - 1)
+        feats[:valid] = ((v - mu) / (np.sqrt(var) + 1e-5)).astype(f32)
+    return feats, valid
+
+
+# --------------------------------------------------------------------------
+# dw-striding subsampling (src/subsampling.c:107-269)
+# --------------------------------------------------------------------------
+def _conv3x3_s2(x, w, b, pl_t, pr_t, pl_f, pr_f, depthwise):
+    """x [C_in,T,F] -> [C_out,To,Fo]; kernel 3, stride 2, zero padding."""
+    C_in, T, F = x.shape
+    xp = np.zeros((C_in, T + pl_t + pr_t, F + pl_f + pr_f), f32)
+    xp[:, pl_t:pl_t + T, pl_f:pl_f + F] = x
+    To = (xp.shape[1] - 3) // 2 + 1
+    Fo = (xp.shape[2] - 3) // 2 + 1
+    C_out = w.shape[0]
+    out = np.zeros((C_out, To, Fo), f32)
+    for dt in range(3):
+        for df in range(3):
+            patch = xp[:, dt:dt + 2 * To:2, df:df + 2 * Fo:2][:, :To, :Fo]
+            if depthwise:
+                out += w[:, 0, dt, df][:, None, None] * patch
+            else:
+                out += np.einsum("oc,ctf->otf", w[:, :, dt, df], patch).astype(f32)
+    return (out + b[:, None, None]).astype(f32)
+
+
+def subsampling_forward(W, feats, causal=False):
+    """feats [T,n_mels] -> [T', d_model]. W: dict with conv_in_w/b, dw_w/b[2],
+    pw_w/b[2], lin_w/b (names as src/subsampling.h:13-17)."""
+    pl, pr = (2, 1) if causal else (1, 1)
+    a = _conv3x3_s2(feats[None].astype(f32), W["conv_in_w"], W["conv_in_b"], pl, pr, pl, pr, False)
+    a = np.maximum(a, 0)
+    for i in range(2):
+        bq = _conv3x3_s2(a, W["dw_w"][i], W["dw_b"][i], pl, pr, pl, pr, True)
+        C, To, Fo = bq.shape
+        pw = W["pw_w"][i].reshape(C, C)
+        a = (pw @ bq.reshape(C, -1)).astype(f32).reshape(C, To, Fo) + W["pw_b"][i][:, None, None]
+        a = np.maximum(a, 0).astype(f32)
+    C, To, Fo = a.shape
+    flat = a.transpose(1, 0, 2).reshape(To, C * Fo)            # channel-major flatten
+    return (gemm_wt(flat, W["lin_w"]) + W["lin_b"][None, :]).astype(f32)
+
+
+# --------------------------------------------------------------------------
+# encoder (src/encoder.c)
+# --------------------------------------------------------------------------
+def layer_norm(x, w, b, eps=1e-5):
+    """Mean/var in double, ((x-mu)*inv)*w + b in float (encoder.c:25-37)."""
+    xd = x.astype(np.float64)
+    mu = xd.mean(axis=1, keepdims=True)
+    var = ((xd - mu) ** 2).mean(axis=1, keepdims=True)
+    inv = (1.0 / np.sqrt(var + eps)).astype(f32)
+    return (((x.astype(f32) - mu.astype(f32)) * inv).astype(f32) * w + b).astype(f32)
+
+
+def pos_emb(T, d):
+    """[2T-1, d], positions T-1 .. -(T-1), sin/cos interleaved (encoder.c:201-211)."""
+    pos = (T - 1 - np.arange(2 * T - 1, dtype=np.float64))[:, None]
+    j = np.arange(d // 2, dtype=np.float64)[None, :]
+    freq = pos * np.power(10000.0, -2.0 * j / d)
+    pe = np.zeros((2 * T - 1, d), f32)
+    pe[:, 0::2] = np.sin(freq).astype(f32)
+    pe[:, 1::2] = np.cos(freq).astype(f32)
+    return pe
+
+
+def _lin(L, name, x):
+    """A quantisable linear; L[name] is the EFFECTIVE f32 weight (what the
+    reference holds after its eager block decode, src/weights.c:90-115)."""
+    y = gemm_wt(x, L[name])
+    b = L.get(name + "_b")
+    return y if b is None else (y + b[None, :]).astype(f32)
+
+
+def attention(L, x, pe, H, left=-1, right=-1):
+    """Rel-pos MHSA with bias_u/bias_v and the closed-form rel-shift
+    bd[t, T-1+j-t]; softmax over the chunked-limited window when left >= 0
+    (encoder.c:315-410, windows :371-381)."""
+    T, d = x.shape
+    dk = d // H
+    scaling = f32(1.0) / np.sqrt(f32(dk))
+    q, k, v = _lin(L, "q_w", x), _lin(L, "k_w", x), _lin(L, "v_w", x)
+    rk = gemm_wt(pe, L["relk_w"])                               # [2T-1, d]
+    chunk = right + 1 if left >= 0 else 1
+    lc = left // chunk if left >= 0 else 0
+    t_idx = np.arange(T)
+    ctx = np.zeros((T, d), f32)
+    rel = (T - 1) + t_idx[None, :] - t_idx[:, None]             # [t, j] -> p
+    for h in range(H):
+        sl = slice(h * dk, (h + 1) * dk)
+        ac = ((q[:, sl] + L["bias_u"][h]) @ k[:, sl].T).astype(f32)
+        bd = ((q[:, sl] + L["bias_v"][h]) @ rk[:, sl].T).astype(f32)
+        s = ((ac + np.take_along_axis(bd, rel, axis=1)) * scaling).astype(f32)
+        if left >= 0:
+            tc = t_idx // chunk
+            j0 = np.maximum((tc - lc) * chunk, 0)
+            j1 = np.minimum((tc + 1) * chunk, T)
+            mask = (t_idx[None, :] >= j0[:, None]) & (t_idx[None, :] < j1[:, None])
+            s = np.where(mask, s, f32(-3.0e38))
+        else:
+            mask = None
+        m = s.max(axis=1, keepdims=True)
+        e = np.exp((s - m).astype(f32)).astype(f32)
+        if mask is not None:
+            e = np.where(mask, e, f32(0))
+        p = (e * (f32(1.0) / e.sum(axis=1, keepdims=True, dtype=f32))).astype(f32)
+        ctx[:, sl] = (p @ v[:, sl]).astype(f32)
+    return _lin(L, "o_w", ctx)
+
+
+def conv_module(L, x, causal):
+    """pw1 -> GLU -> depthwise k -> folded BN affine or LN -> SiLU -> pw2
+    (encoder.c:413-460)."""
+    T, d = x.shape
+    h2 = _lin(L, "pw1_w", x)
+    g = (h2[:, :d] * sigmoid(h2[:, d:])).astype(f32)
+    dw = L["dw_w"].reshape(d, -1)
+    k = dw.shape[1]
+    pc = k - 1 if causal else (k - 1) // 2
+    gp = np.zeros((T + k - 1, d), f32)
+    gp[pc:pc + T] = g
+    c = np.zeros((T, d), f32)
+    if L.get("dw_b") is not None:
+        c += L["dw_b"][None, :]
+    for j in range(k):
+        c = (c + dw[None, :, j] * gp[j:j + T]).astype(f32)
+    if L.get("cnorm_scale") is not None:
+        g2 = (c * L["cnorm_scale"][None, :] + L["cnorm_shift"][None, :]).astype(f32)
+    else:
+        g2 = layer_norm(c, L["cnorm_w"], L["cnorm_b"])
+    return _lin(L, "pw2_w", silu(g2))
+
+
+def half_ffn(L, x, which):
+    """LN -> linear1 (+b) -> SiLU -> linear2 (+b) (encoder.c:464-482)."""
+    p = "ff2" if which else "ff1"
+    h = layer_norm(x, L["ln_" + p + "_w"], L["ln_" + p + "_b"])
+    return _lin(L, p + "_w2", silu(_lin(L, p + "_w1", h)))
+
+
+def encoder_layer(L, x, pe, H, causal, left=-1, right=-1):
+    """Macaron block, residual weights 0.5/1/1/0.5, output LN (encoder.c:485-519)."""
+    x = (x + f32(0.5) * half_ffn(L, x, 0)).astype(f32)
+    x = (x + attention(L, layer_norm(x, L["ln_att_w"], L["ln_att_b"]), pe, H, left, right)).astype(f32)
+    x = (x + conv_module(L, layer_norm(x, L["ln_conv_w"], L["ln_conv_b"]), causal)).astype(f32)
+    x = (x + f32(0.5) * half_ffn(L, x, 1)).astype(f32)
+    return layer_norm(x, L["ln_out_w"], L["ln_out_b"])
+
+
+def encoder_post(M, x):
+    """encoder_projector when present, else identity (encoder.c:573-590).
+    The prompt MLP (Nemotron) is not restated: no config here carries one."""
+    if M.get("encproj_w") is None:
+        return x.copy()
+    return (gemm_wt(x, M["encproj_w"]) + M["encproj_b"][None, :]).astype(f32)
+
+
+def encoder_forward(M, feats, left=-1, right=-1, raw=False, n_layers=None):
+    """feats [T_mel, n_mels] (valid frames) -> [T, d_out] (encoder.c:1013-1039)."""
+    x = subsampling_forward(M["ss"], feats, M["causal"])
+    if M.get("xscale", 1.0) != 1.0:
+        x = (x * f32(M["xscale"])).astype(f32)
+    T, d = x.shape
+    pe = pos_emb(T, d)
+    for L in M["layers"][:n_layers]:
+        x = encoder_layer(L, x, pe, M["n_heads"], M["causal"], left, right)
+    return x if raw else encoder_post(M, x)
+
+
+# --------------------------------------------------------------------------
+# decoders (src/decoder_ctc.c, src/decoder.c)
+# --------------------------------------------------------------------------
+def _argmax_bias(lg, bias):
+    """First index of the maximum of logits+bias (decoder.c:113-121)."""
+    return int(np.argmax((lg + bias).astype(f32)))
+
+
+def ctc_decode(enc, w, b):
+    """argmax(logit+b), collapse repeats, drop blank = V-1, first frame per token
+    (decoder_ctc.c:36-61)."""
+    logits = gemm_wt(enc, w)
+    best = np.argmax((logits + b[None, :]).astype(f32), axis=1)
+    blank = w.shape[0] - 1
+    toks, frames, prev = [], [], -1
+    for t, k in enumerate(best):
+        if k != prev and k != blank:
+            toks.append(int(k)); frames.append(t)
+        prev = k
+    return toks, frames
+
+
+def _lstm_pred_step(D, state, token):
+    """Stacked LSTM step + decoder_projector, gates i,f,g,o (decoder.c:73-99)."""
+    H = D["hidden"]
+    x = D["embedding"][token]
+    for l in range(D["n_layers"]):
+        z = (D["b_ih"][l] + D["b_hh"][l]).astype(f32)
+        z = (z + D["w_ih"][l] @ x).astype(f32)
+        z = (z + D["w_hh"][l] @ state["h"][l]).astype(f32)
+        ig, fg = sigmoid(z[:H]), sigmoid(z[H:2 * H])
+        gg, og = np.tanh(z[2 * H:3 * H]).astype(f32), sigmoid(z[3 * H:])
+        state["c"][l] = (fg * state["c"][l] + ig * gg).astype(f32)
+        state["h"][l] = (og * np.tanh(state["c"][l]).astype(f32)).astype(f32)
+        x = state["h"][l]
+    state["g"] = (D["proj_b"] + D["proj_w"] @ state["h"][D["n_layers"] - 1]).astype(f32)
+
+
+def greedy_decode(D, enc):
+    """RNNT (durations empty) or TDT greedy from a fresh state; SOS = blank.
+    RNNT: per frame emit until blank or max_symbols (decoder.c:183-265; the
+    blocked blank-run batching there is an optimisation with identical
+    semantics). TDT: t += duration with the blank/max_symbols rules
+    (decoder.c:129-181). Returns (tokens, frames)."""
+    H = D["hidden"]
+    st = {"h": [np.zeros(H, f32) for _ in range(D["n_layers"])],
+          "c": [np.zeros(H, f32) for _ in range(D["n_layers"])], "g": None}
+    _lstm_pred_step(D, st, D["blank"])
+    T = enc.shape[0]
+    V = D["vocab"]
+    durs = D.get("durations") or []
+    toks, frames = [], []
+    t = 0
+    if durs:
+        emitted_here = 0
+        while t < T:
+            joint = np.maximum(enc[t] + st["g"], 0).astype(f32)
+            logits = (D["head_w"] @ joint).astype(f32)
+            k = _argmax_bias(logits[:V], D["head_b"][:V])
+            dur = durs[_argmax_bias(logits[V:], D["head_b"][V:])]
+            if k != D["blank"]:
+                toks.append(k); frames.append(t)
+                _lstm_pred_step(D, st, k)
+                emitted_here += 1
+                if dur == 0 and emitted_here >= D["max_symbols"]:
+                    dur = 1
+            elif dur == 0:
+                dur = 1
+            if dur > 0:
+                emitted_here = 0
+            t += dur
+        return toks, frames
+    while t < T:
+        for _ in range(D["max_symbols"]):
+            joint = np.maximum(enc[t] + st["g"], 0).astype(f32)
+            k = _argmax_bias((D["head_w"] @ joint).astype(f32), D["head_b"])
+            if k == D["blank"]:
+                break
+            toks.append(k); frames.append(t)
+            _lstm_pred_step(D, st, k)
+        t += 1
+    return toks, frames
