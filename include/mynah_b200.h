@@ -1,0 +1,166 @@
+/* mynah_b200 — B200 (sm_100a) compute backend for the mynah-asr hot path.
+ *
+ * A plain C ABI (pointers and sizes only) meant to sit behind the reference's
+ * backend dispatch (src/backend.h, src/backend.c) and beside its qmat / encoder /
+ * features / decoder entry points. Every function names the reference interface it
+ * replaces. Conventions follow the reference: 0 = ok, -1 / NULL = error (the text is
+ * available from mynah_b200_last_error()), never abort; host buffers returned to the
+ * caller are malloc()'d and freed by the caller with free(); inputs are borrowed.
+ * There is no CPU fallback inside: if the device path cannot run, the call fails.
+ *
+ * Threading: a model is immutable after mynah_b200_model_finalize() and may be
+ * shared; calls that run the encoder or a decoder on the same model serialise on
+ * the model's stream and workspace. One process drives one GPU (cudaSetDevice by
+ * the caller, or MYNAH_B200_DEVICE / LOCAL_RANK through mynah_b200_select_device).
+ */
+#ifndef MYNAH_B200_H
+#define MYNAH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- weight formats ---------------------------------------------------------- */
+enum {
+    MYNAH_B200_F32 = 0,
+    MYNAH_B200_MYNAH_Q8 = 1,   /* reference-native per-row int8 + f32 scales [n]      (src/qmat.h:6-9)  */
+    MYNAH_B200_MYNAH_Q4 = 2,   /* reference-native 32-group nibbles + f32 scales [n,k/32]               */
+    MYNAH_B200_GGML_Q4_0 = 102,/* ggml blocks, 100 + ggml type id (third_party/ingot/src/dequant.c)     */
+    MYNAH_B200_GGML_Q8_0 = 108,
+    MYNAH_B200_GGML_Q4_K = 112,
+    MYNAH_B200_GGML_Q6_K = 114
+};
+
+/* qmat_mul flags */
+enum {
+    MYNAH_B200_A16 = 0,        /* float activations x exactly decoded weights (the reference's f32 path) */
+    MYNAH_B200_A8 = 1,         /* int8 activations, integer block dots (src/qmat.c:186-202,285-364)      */
+    MYNAH_B200_FAST = 2        /* large T: single fp16 tensor-core pass instead of the 3-term split      */
+};
+
+/* ---- backend presence and errors --------------------------------------------- */
+/* replaces mynah_asr_cuda_available (src/backend.c:24): 1 when an sm_100 device is usable */
+int mynah_b200_available(void);
+/* picks the GPU for this process: explicit index, else env MYNAH_B200_DEVICE, else LOCAL_RANK, else 0 */
+int mynah_b200_select_device(int index);
+const char *mynah_b200_last_error(void);
+
+/* ---- f32 GEMM hook ------------------------------------------------------------ */
+/* replaces mynah_asr_cuda_gemm_wt (src/backend.c:25, src/cuda_gemm.cu:144-190):
+ * out[T,n] = x[T,k] W[n,k]^T, host pointers, synchronous. W is uploaded on every call
+ * (no address-keyed cache; use a qmat handle for resident weights). */
+int mynah_b200_gemm_wt(const float *x, const float *w, float *out, int T, int n, int k);
+
+/* ---- quantised weight matrix --------------------------------------------------- */
+/* replaces mynah_asr_qmat + mynah_asr_qmat_init (src/qmat.h:39-47, src/qmat.c:80-143): the
+ * stored blocks are copied to HBM once and stay resident. scales: native formats only. */
+typedef struct mynah_b200_qmat mynah_b200_qmat;
+mynah_b200_qmat *mynah_b200_qmat_create(int fmt, const void *data, const float *scales, int n, int k);
+void mynah_b200_qmat_free(mynah_b200_qmat *m);
+/* replaces mynah_asr_qmat_mul (src/qmat.c:503-651): out[T,n] = x[T,k] W^T, host x/out.
+ * T <= 16 streams the stored blocks (bandwidth-bound); larger T runs on the tensor cores. */
+int mynah_b200_qmat_mul(const mynah_b200_qmat *m, const float *x, float *out, int T, int flags);
+/* A8 diagnostics: the exact int32 dot of every 32-block, dots[T][n][k/32], and the activation
+ * scales sx[T] (the quantities the reference forms in dot_q8_* / dot_q4_*, src/qmat.c:285-364). */
+int mynah_b200_qmat_block_dots(const mynah_b200_qmat *m, const float *x, int T, int32_t *dots, float *sx, float *out);
+/* replaces mynah_asr_qmat_dequant (src/qmat.c:171-177): wd[n,k] f32 on the host */
+int mynah_b200_qmat_dequant(const mynah_b200_qmat *m, float *wd);
+/* same product with x, out already on the device (for callers that keep activations resident) */
+int mynah_b200_qmat_mul_device(const mynah_b200_qmat *m, const float *x_dev, float *out_dev, int T, int flags);
+
+/* ---- model --------------------------------------------------------------------- */
+typedef struct {
+    int n_mels;                 /* mynah.json features.n_mels */
+    int n_fft, win_length, hop_length;      /* 512, 400, 160 */
+    double preemphasis, log_zero_guard;     /* 0.97, 2^-24 */
+    int normalize_per_feature;  /* features.normalize == "per_feature" */
+    int causal;                 /* -1: infer from tensor naming (src/subsampling.c:16-35); 0/1: config wins */
+    int xscaling;               /* encoder.xscaling */
+    int left_ctx, right_ctx;    /* default attention context; left < 0 = full attention */
+    int blank_id, max_symbols;  /* decoder.blank_id, decoder.max_symbols_per_step */
+    int n_durations;            /* TDT durations; 0 = RNNT */
+    int durations[16];
+    int strict;                 /* 1: 3-term fp16 split (f32-grade, default); 0: single fp16 pass */
+    int attn_impl;              /* 0 tiled tensor-core kernel (default), 1 plain kernel (cross-check) */
+} mynah_b200_config;
+
+void mynah_b200_config_default(mynah_b200_config *cfg);
+
+typedef struct mynah_b200_model mynah_b200_model;
+/* replaces the weight side of mynah_asr_load_quant (src/mynah_asr.c:167-350) and what the survey
+ * calls model_attach: tensors are handed over by their HF-verbatim names exactly as
+ * src/weights.c exposes them (name, shape, data), but block-quantised tensors keep their ggml
+ * type instead of being decoded to f32. fmt is one of the MYNAH_B200_* formats; data is
+ * borrowed until mynah_b200_model_finalize returns. */
+mynah_b200_model *mynah_b200_model_new(const mynah_b200_config *cfg);
+int mynah_b200_model_add_tensor(mynah_b200_model *m, const char *name, int fmt, const int64_t *shape, int rank,
+                                const void *data);
+/* mel filterbank [n_fft/2+1, n_mels] and window [win_length] (mel_filters.safetensors) */
+int mynah_b200_model_set_mel(mynah_b200_model *m, const float *mel_fb, const float *window);
+/* resolves tensors like mynah_asr_encoder_init / subsampling_init / decoder_init / ctc_init
+ * (src/encoder.c:56-183, src/subsampling.c:14-58, src/decoder.c:14-62, src/decoder_ctc.c:11-22),
+ * uploads and decodes them; replaces the lazy per-pointer upload of src/cuda_gemm.cu:96-130 */
+int mynah_b200_model_finalize(mynah_b200_model *m);
+/* replaces mynah_asr_metal_weights_evict / mynah_asr_encoder_free */
+void mynah_b200_model_free(mynah_b200_model *m);
+/* dims[0..7] = d_model, n_layers, n_heads, ffn_dim, conv_k, d_out, causal, channels */
+void mynah_b200_model_dims(const mynah_b200_model *m, int *dims);
+
+/* ---- stages (host in, host out; everything in between stays on the device) ----- */
+/* replaces mynah_asr_log_mel (src/features.h:28-29): returns feats [*n_frames, n_mels] */
+float *mynah_b200_log_mel(mynah_b200_model *m, const float *audio, size_t n_samples, int *n_frames,
+                          int *valid_frames);
+/* replaces mynah_asr_subsampling_forward (src/subsampling.h:31-32) */
+float *mynah_b200_subsampling_forward(mynah_b200_model *m, const float *feats, int T, int n_mels, int *t_out);
+/* replaces mynah_asr_encoder_layer (src/encoder.h:57-58): one block in place on host x [T,d];
+ * the positional embedding is computed inside (the reference's pe argument is a pure function of T) */
+int mynah_b200_encoder_layer(mynah_b200_model *m, int li, float *x, int T, int left_ctx, int right_ctx);
+/* replace mynah_asr_encoder_forward / _forward_raw (src/encoder.h:67-76) */
+float *mynah_b200_encoder_forward(mynah_b200_model *m, const float *feats, int t_mel, int n_mels, int prompt_id,
+                                  int left_ctx, int right_ctx, int *t_out);
+float *mynah_b200_encoder_forward_raw(mynah_b200_model *m, const float *feats, int t_mel, int n_mels, int left_ctx,
+                                      int right_ctx, int *t_out);
+/* replaces mynah_asr_encoder_forward_batch (src/encoder.h:82-85): padding-free packed batch */
+int mynah_b200_encoder_forward_batch(mynah_b200_model *m, const float *const *feats, const int *t_mel, int batch,
+                                     int n_mels, const int *prompt_ids, int left_ctx, int right_ctx, float **outs,
+                                     int *t_outs);
+/* replaces mynah_asr_ctc_decode (src/decoder_ctc.h:28-29) */
+int mynah_b200_ctc_decode(mynah_b200_model *m, const float *enc_out, int T, int *tokens, int *frames, int cap);
+/* replaces mynah_asr_greedy_decode from a fresh state (src/decoder.h:51-52, as called by
+ * eng_decode_rnnt, src/mynah_asr.c:124-137) */
+int mynah_b200_greedy_decode(mynah_b200_model *m, const float *enc, int T, int *tokens, int *frames, int cap);
+
+/* ---- whole path, resident ------------------------------------------------------- */
+/* audio in, token ids out: log-mel -> encoder (packed batch) -> greedy decoder, with only the
+ * audio and the token ids crossing PCIe. The device-resident counterpart of one wave of
+ * mynah_asr_transcribe_batch_ts (src/mynah_asr.c:624-679) up to detokenisation.
+ * tokens[b] / frames[b] are malloc()'d (caller frees; frames may be NULL), n_tokens[b] set.
+ * decoder: 0 = the model's transducer head (RNNT/TDT), 1 = CTC head. */
+int mynah_b200_transcribe_batch(mynah_b200_model *m, const float *const *audio, const size_t *n_samples, int batch,
+                                int decoder, int **tokens, int **frames, int *n_tokens);
+
+/* Same, split for measurement: inputs already resident on the device. h = handle returned by
+ * mynah_b200_batch_upload; run may be called repeatedly; results fetched once. */
+typedef struct mynah_b200_batch mynah_b200_batch;
+mynah_b200_batch *mynah_b200_batch_upload(mynah_b200_model *m, const float *const *audio, const size_t *n_samples,
+                                          int batch);
+int mynah_b200_batch_run(mynah_b200_model *m, mynah_b200_batch *h, int decoder);
+int mynah_b200_batch_fetch(mynah_b200_model *m, mynah_b200_batch *h, int **tokens, int **frames, int *n_tokens);
+void mynah_b200_batch_free(mynah_b200_batch *h);
+
+/* ---- introspection for tests and benchmarks ------------------------------------- */
+/* number of kernels this library launched since the last reset (its own launches only) */
+long long mynah_b200_launch_count(int reset);
+/* CUDA stream the model runs on (a cudaStream_t), for event timing by the caller */
+void *mynah_b200_model_stream(mynah_b200_model *m);
+/* Times one large-T contraction with device-resident operands: returns the average milliseconds
+ * of `iters` launches of out[T,n] = x[T,k] W^T (CUDA events on the launching stream). */
+double mynah_b200_qmat_time(const mynah_b200_qmat *m, int T, int flags, int iters);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

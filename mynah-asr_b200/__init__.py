@@ -1,0 +1,335 @@
+"""mynah-asr_b200 — host-side mirror of the reference's hot-path interface over the
+B200 CUDA library (include/mynah_b200.h).
+
+The product is the C-ABI shared library built from csrc/; this module is the thin
+ctypes binding tests and the benchmark use — the same kind of binding the
+reference ships for its own library (bindings/python/mynah_asr.py). Function and
+argument names follow the reference: qmat_mul, log_mel, subsampling_forward,
+encoder_layer, encoder_forward(_raw/_batch), ctc_decode, greedy_decode.
+
+There is no CPU path here: if the CUDA library is missing or no sm_100 device is
+present, loading fails loudly.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmynah_b200.so")
+
+F32, MYNAH_Q8, MYNAH_Q4 = 0, 1, 2
+GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 102, 108, 112, 114
+A16, A8, FAST = 0, 1, 2
+
+c_fp = C.POINTER(C.c_float)
+c_ip = C.POINTER(C.c_int)
+
+
+class Config(C.Structure):
+    _fields_ = [("n_mels", C.c_int), ("n_fft", C.c_int), ("win_length", C.c_int), ("hop_length", C.c_int),
+                ("preemphasis", C.c_double), ("log_zero_guard", C.c_double), ("normalize_per_feature", C.c_int),
+                ("causal", C.c_int), ("xscaling", C.c_int), ("left_ctx", C.c_int), ("right_ctx", C.c_int),
+                ("blank_id", C.c_int), ("max_symbols", C.c_int), ("n_durations", C.c_int),
+                ("durations", C.c_int * 16), ("strict", C.c_int), ("attn_impl", C.c_int)]
+
+
+class BackendError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def lib():
+    """Loads the CUDA library. Raises if it has not been built — never falls back."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise BackendError(f"{LIB_PATH} is missing: build it with `python __graft_entry__.py` "
+                           "(or mynah-asr_b200/build.py); there is no CPU fallback")
+    L = C.CDLL(LIB_PATH)
+    vp, ci, cf = C.c_void_p, C.c_int, C.c_float
+    L.mynah_b200_last_error.restype = C.c_char_p
+    L.mynah_b200_available.restype = ci
+    L.mynah_b200_select_device.argtypes = [ci]
+    L.mynah_b200_launch_count.restype = C.c_longlong
+    L.mynah_b200_launch_count.argtypes = [ci]
+    L.mynah_b200_config_default.argtypes = [C.POINTER(Config)]
+    L.mynah_b200_gemm_wt.argtypes = [c_fp, c_fp, c_fp, ci, ci, ci]
+    L.mynah_b200_qmat_create.restype = vp
+    L.mynah_b200_qmat_create.argtypes = [ci, vp, c_fp, ci, ci]
+    L.mynah_b200_qmat_free.argtypes = [vp]
+    L.mynah_b200_qmat_mul.argtypes = [vp, c_fp, c_fp, ci, ci]
+    L.mynah_b200_qmat_block_dots.argtypes = [vp, c_fp, ci, C.POINTER(C.c_int32), c_fp, c_fp]
+    L.mynah_b200_qmat_dequant.argtypes = [vp, c_fp]
+    L.mynah_b200_qmat_time.restype = C.c_double
+    L.mynah_b200_qmat_time.argtypes = [vp, ci, ci, ci]
+    L.mynah_b200_model_new.restype = vp
+    L.mynah_b200_model_new.argtypes = [C.POINTER(Config)]
+    L.mynah_b200_model_add_tensor.argtypes = [vp, C.c_char_p, ci, C.POINTER(C.c_int64), ci, vp]
+    L.mynah_b200_model_set_mel.argtypes = [vp, c_fp, c_fp]
+    L.mynah_b200_model_finalize.argtypes = [vp]
+    L.mynah_b200_model_free.argtypes = [vp]
+    L.mynah_b200_model_dims.argtypes = [vp, c_ip]
+    L.mynah_b200_model_stream.restype = vp
+    L.mynah_b200_model_stream.argtypes = [vp]
+    L.mynah_b200_log_mel.restype = vp
+    L.mynah_b200_log_mel.argtypes = [vp, c_fp, C.c_size_t, c_ip, c_ip]
+    L.mynah_b200_subsampling_forward.restype = vp
+    L.mynah_b200_subsampling_forward.argtypes = [vp, c_fp, ci, ci, c_ip]
+    L.mynah_b200_encoder_layer.argtypes = [vp, ci, c_fp, ci, ci, ci]
+    L.mynah_b200_encoder_forward.restype = vp
+    L.mynah_b200_encoder_forward.argtypes = [vp, c_fp, ci, ci, ci, ci, ci, c_ip]
+    L.mynah_b200_encoder_forward_raw.restype = vp
+    L.mynah_b200_encoder_forward_raw.argtypes = [vp, c_fp, ci, ci, ci, ci, c_ip]
+    L.mynah_b200_encoder_forward_batch.argtypes = [vp, C.POINTER(c_fp), c_ip, ci, ci, c_ip, ci, ci,
+                                                   C.POINTER(vp), c_ip]
+    L.mynah_b200_ctc_decode.argtypes = [vp, c_fp, ci, c_ip, c_ip, ci]
+    L.mynah_b200_greedy_decode.argtypes = [vp, c_fp, ci, c_ip, c_ip, ci]
+    L.mynah_b200_transcribe_batch.argtypes = [vp, C.POINTER(c_fp), C.POINTER(C.c_size_t), ci, ci, C.POINTER(vp),
+                                              C.POINTER(vp), c_ip]
+    L.mynah_b200_batch_upload.restype = vp
+    L.mynah_b200_batch_upload.argtypes = [vp, C.POINTER(c_fp), C.POINTER(C.c_size_t), ci]
+    L.mynah_b200_batch_run.argtypes = [vp, vp, ci]
+    L.mynah_b200_batch_fetch.argtypes = [vp, vp, C.POINTER(vp), C.POINTER(vp), c_ip]
+    L.mynah_b200_batch_free.argtypes = [vp]
+    _lib = L
+    return L
+
+
+_libc = C.CDLL(None)
+_libc.free.argtypes = [C.c_void_p]
+
+
+def _err() -> str:
+    return lib().mynah_b200_last_error().decode(errors="replace")
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise BackendError(f"{what}: {_err()}")
+
+
+def _fp(a):
+    return a.ctypes.data_as(c_fp)
+
+
+def _take_f32(ptr, shape):
+    if not ptr:
+        raise BackendError(_err())
+    n = int(np.prod(shape))
+    out = np.ctypeslib.as_array(C.cast(ptr, c_fp), shape=(max(n, 1),))[:n].copy().reshape(shape)
+    _libc.free(ptr)
+    return out
+
+
+def _take_i32(ptr, n):
+    out = np.ctypeslib.as_array(C.cast(ptr, c_ip), shape=(max(n, 1),))[:n].copy()
+    _libc.free(ptr)
+    return out.tolist()
+
+
+def available() -> bool:
+    return bool(lib().mynah_b200_available())
+
+
+def launch_count(reset: bool = False) -> int:
+    return int(lib().mynah_b200_launch_count(int(reset)))
+
+
+def gemm_wt(x, w):
+    """out[T,n] = x[T,k] @ W[n,k]^T (mynah_asr_gemm_wt, src/backend.c:68-81)."""
+    x = np.ascontiguousarray(x, np.float32); w = np.ascontiguousarray(w, np.float32)
+    out = np.empty((x.shape[0], w.shape[0]), np.float32)
+    _check(lib().mynah_b200_gemm_wt(_fp(x), _fp(w), _fp(out), x.shape[0], w.shape[0], w.shape[1]), "gemm_wt")
+    return out
+
+
+class QMat:
+    """Resident quantised weight matrix [n,k] (mynah_asr_qmat, src/qmat.h:39-47)."""
+
+    def __init__(self, fmt, data, n, k, scales=None):
+        self._raw = np.ascontiguousarray(data).view(np.uint8).reshape(-1)
+        self._scales = None if scales is None else np.ascontiguousarray(scales, np.float32)
+        self.n, self.k, self.fmt = n, k, fmt
+        self.h = lib().mynah_b200_qmat_create(fmt, self._raw.ctypes.data,
+                                              None if self._scales is None else _fp(self._scales), n, k)
+        if not self.h:
+            raise BackendError("qmat_create: " + _err())
+
+    def close(self):
+        if self.h:
+            lib().mynah_b200_qmat_free(self.h)
+            self.h = None
+
+    __del__ = close
+
+    def mul(self, x, flags=A16):
+        """out[T,n] = x[T,k] @ W^T (mynah_asr_qmat_mul, src/qmat.c:503-651)."""
+        x = np.ascontiguousarray(x, np.float32)
+        out = np.empty((x.shape[0], self.n), np.float32)
+        _check(lib().mynah_b200_qmat_mul(self.h, _fp(x), _fp(out), x.shape[0], flags), "qmat_mul")
+        return out
+
+    def block_dots(self, x):
+        x = np.ascontiguousarray(x, np.float32)
+        T = x.shape[0]
+        dots = np.empty((T, self.n, self.k // 32), np.int32)
+        sx = np.empty(T, np.float32)
+        out = np.empty((T, self.n), np.float32)
+        _check(lib().mynah_b200_qmat_block_dots(self.h, _fp(x), T, dots.ctypes.data_as(C.POINTER(C.c_int32)),
+                                                _fp(sx), _fp(out)), "qmat_block_dots")
+        return dots, sx, out
+
+    def dequant(self):
+        wd = np.empty((self.n, self.k), np.float32)
+        _check(lib().mynah_b200_qmat_dequant(self.h, _fp(wd)), "qmat_dequant")
+        return wd
+
+    def time_ms(self, T, flags=A16, iters=20):
+        ms = lib().mynah_b200_qmat_time(self.h, T, flags, iters)
+        if ms < 0:
+            raise BackendError("qmat_time: " + _err())
+        return ms
+
+
+class Model:
+    """Device-resident encoder + decoders built from named tensors
+    (the weight side of mynah_asr_load_quant, src/mynah_asr.c:167-350)."""
+
+    def __init__(self, tensors, *, n_mels, mel_fb=None, window=None, causal=-1, xscaling=False, normalize=True,
+                 left=-1, right=-1, blank=0, max_symbols=10, durations=(), strict=True, attn_impl=0):
+        L = lib()
+        cfg = Config()
+        L.mynah_b200_config_default(C.byref(cfg))
+        cfg.n_mels, cfg.causal, cfg.xscaling = n_mels, causal, int(xscaling)
+        cfg.normalize_per_feature, cfg.left_ctx, cfg.right_ctx = int(normalize), left, right
+        cfg.blank_id, cfg.max_symbols, cfg.n_durations = blank, max_symbols, len(durations)
+        for i, d in enumerate(durations):
+            cfg.durations[i] = d
+        cfg.strict, cfg.attn_impl = int(strict), attn_impl
+        self.cfg = cfg
+        self.h = L.mynah_b200_model_new(C.byref(cfg))
+        if not self.h:
+            raise BackendError("model_new: " + _err())
+        keep = []
+        for name, t in tensors.items():
+            fmt = {0: F32, 2: GGML_Q4_0, 8: GGML_Q8_0, 12: GGML_Q4_K, 14: GGML_Q6_K}[t.ggml_type]
+            shape = (C.c_int64 * len(t.shape))(*t.shape)
+            raw = np.ascontiguousarray(t.raw)
+            keep.append(raw)
+            _check(L.mynah_b200_model_add_tensor(self.h, name.encode(), fmt, shape, len(t.shape), raw.ctypes.data),
+                   "add_tensor " + name)
+        if mel_fb is not None:
+            fb = np.ascontiguousarray(mel_fb, np.float32); win = np.ascontiguousarray(window, np.float32)
+            _check(L.mynah_b200_model_set_mel(self.h, _fp(fb), _fp(win)), "set_mel")
+        _check(L.mynah_b200_model_finalize(self.h), "finalize")
+        dims = (C.c_int * 8)()
+        L.mynah_b200_model_dims(self.h, dims)
+        (self.d_model, self.n_layers, self.n_heads, self.ffn_dim, self.conv_k, self.d_out, self.causal,
+         self.channels) = list(dims)
+        self.n_mels = n_mels
+        self.max_symbols = max_symbols
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().mynah_b200_model_free(self.h)
+            self.h = None
+
+    __del__ = close
+
+    def stream(self):
+        return lib().mynah_b200_model_stream(self.h)
+
+    def log_mel(self, audio):
+        audio = np.ascontiguousarray(audio, np.float32)
+        T, v = C.c_int(), C.c_int()
+        p = lib().mynah_b200_log_mel(self.h, _fp(audio), audio.size, C.byref(T), C.byref(v))
+        return _take_f32(p, (T.value, self.n_mels)), v.value
+
+    def subsampling_forward(self, feats):
+        feats = np.ascontiguousarray(feats, np.float32)
+        t = C.c_int()
+        p = lib().mynah_b200_subsampling_forward(self.h, _fp(feats), feats.shape[0], feats.shape[1], C.byref(t))
+        return _take_f32(p, (t.value, self.d_model))
+
+    def encoder_layer(self, li, x, left=-1, right=-1):
+        x = np.ascontiguousarray(x, np.float32).copy()
+        _check(lib().mynah_b200_encoder_layer(self.h, li, _fp(x), x.shape[0], left, right), "encoder_layer")
+        return x
+
+    def encoder_forward(self, feats, left=-1, right=-1, raw=False):
+        feats = np.ascontiguousarray(feats, np.float32)
+        t = C.c_int()
+        if raw:
+            p = lib().mynah_b200_encoder_forward_raw(self.h, _fp(feats), feats.shape[0], feats.shape[1], left, right,
+                                                     C.byref(t))
+        else:
+            p = lib().mynah_b200_encoder_forward(self.h, _fp(feats), feats.shape[0], feats.shape[1], 0, left, right,
+                                                 C.byref(t))
+        return _take_f32(p, (t.value, self.d_model if raw else self.d_out))
+
+    def encoder_forward_batch(self, feats_list, left=-1, right=-1):
+        B = len(feats_list)
+        fl = [np.ascontiguousarray(f, np.float32) for f in feats_list]
+        ptrs = (c_fp * B)(*[_fp(f) for f in fl])
+        tm = (C.c_int * B)(*[f.shape[0] for f in fl])
+        pid = (C.c_int * B)()
+        outs = (C.c_void_p * B)()
+        touts = (C.c_int * B)()
+        _check(lib().mynah_b200_encoder_forward_batch(self.h, ptrs, tm, B, self.n_mels, pid, left, right, outs, touts),
+               "encoder_forward_batch")
+        return [_take_f32(outs[b], (touts[b], self.d_out)) for b in range(B)]
+
+    def _decode(self, fn, enc, cap, what):
+        enc = np.ascontiguousarray(enc, np.float32)
+        toks = np.zeros(max(cap, 1), np.int32)
+        frames = np.zeros(max(cap, 1), np.int32)
+        n = fn(self.h, _fp(enc), enc.shape[0], toks.ctypes.data_as(c_ip), frames.ctypes.data_as(c_ip), cap)
+        if n < 0:
+            raise BackendError(what + ": " + _err())
+        return toks[:n].tolist(), frames[:n].tolist()
+
+    def ctc_decode(self, enc):
+        return self._decode(lib().mynah_b200_ctc_decode, enc, enc.shape[0], "ctc_decode")
+
+    def greedy_decode(self, enc):
+        return self._decode(lib().mynah_b200_greedy_decode, enc, enc.shape[0] * self.max_symbols, "greedy_decode")
+
+    # ---- audio in, tokens out
+    @staticmethod
+    def _audio_args(audio_list):
+        B = len(audio_list)
+        al = [np.ascontiguousarray(a, np.float32) for a in audio_list]
+        ptrs = (c_fp * B)(*[_fp(a) for a in al])
+        ns = (C.c_size_t * B)(*[a.size for a in al])
+        return al, ptrs, ns
+
+    def transcribe_batch(self, audio_list, decoder=0):
+        B = len(audio_list)
+        al, ptrs, ns = self._audio_args(audio_list)
+        tk, fr, nt = (C.c_void_p * B)(), (C.c_void_p * B)(), (C.c_int * B)()
+        _check(lib().mynah_b200_transcribe_batch(self.h, ptrs, ns, B, decoder, tk, fr, nt), "transcribe_batch")
+        return [(_take_i32(tk[b], nt[b]), _take_i32(fr[b], nt[b])) for b in range(B)]
+
+    def batch_upload(self, audio_list):
+        al, ptrs, ns = self._audio_args(audio_list)
+        h = lib().mynah_b200_batch_upload(self.h, ptrs, ns, len(audio_list))
+        if not h:
+            raise BackendError("batch_upload: " + _err())
+        return h
+
+    def batch_run(self, bh, decoder=0):
+        _check(lib().mynah_b200_batch_run(self.h, bh, decoder), "batch_run")
+
+    def batch_fetch(self, bh, B):
+        tk, fr, nt = (C.c_void_p * B)(), (C.c_void_p * B)(), (C.c_int * B)()
+        _check(lib().mynah_b200_batch_fetch(self.h, bh, tk, fr, nt), "batch_fetch")
+        return [(_take_i32(tk[b], nt[b]), _take_i32(fr[b], nt[b])) for b in range(B)]
+
+    def batch_free(self, bh):
+        lib().mynah_b200_batch_free(bh)

@@ -1,0 +1,749 @@
+// extern "C" boundary (include/mynah_b200.h): plain pointers and sizes in, host
+// buffers out; resolves the reference's tensor names and drives the device path.
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "model.h"
+
+using namespace mb;
+
+namespace mb { long long launch_count(bool reset); }
+
+struct mynah_b200_model { Model m; };
+struct mynah_b200_qmat {
+    QWeight w;
+    std::vector<void *> owned;
+    cudaStream_t stream = nullptr;
+    int *status = nullptr;
+};
+struct mynah_b200_batch {
+    int batch = 0;
+    std::vector<float *> audio;          // device
+    std::vector<size_t> n_samples;
+    std::vector<std::vector<int>> tokens, frames;
+};
+
+static int internal_fmt(int fmt) {
+    switch (fmt) {
+    case MYNAH_B200_F32: return FMT_F32;
+    case MYNAH_B200_MYNAH_Q8: return FMT_MYNAH_Q8;
+    case MYNAH_B200_MYNAH_Q4: return FMT_MYNAH_Q4;
+    case MYNAH_B200_GGML_Q4_0: return FMT_GGML_Q4_0;
+    case MYNAH_B200_GGML_Q8_0: return FMT_GGML_Q8_0;
+    case MYNAH_B200_GGML_Q4_K: return FMT_GGML_Q4_K;
+    case MYNAH_B200_GGML_Q6_K: return FMT_GGML_Q6_K;
+    default: return -1;
+    }
+}
+
+extern "C" {
+
+const char *mynah_b200_last_error(void) { return mb::last_error(); }
+
+int mynah_b200_available(void) {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) { cudaGetLastError(); return 0; }
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceProp p;
+    if (cudaGetDeviceProperties(&p, dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return p.major == 10 ? 1 : 0;
+}
+
+int mynah_b200_select_device(int index) {
+    if (index < 0) {
+        const char *e = getenv("MYNAH_B200_DEVICE");
+        if (!e) e = getenv("LOCAL_RANK");
+        index = e ? atoi(e) : 0;
+    }
+    int n = 0;
+    MB_CUDA(cudaGetDeviceCount(&n));
+    if (index >= n) { set_error("device %d requested, %d present", index, n); return -1; }
+    MB_CUDA(cudaSetDevice(index));
+    return index;
+}
+
+long long mynah_b200_launch_count(int reset) { return mb::launch_count(reset != 0); }
+
+void mynah_b200_config_default(mynah_b200_config *c) {
+    memset(c, 0, sizeof(*c));
+    c->n_mels = 128; c->n_fft = 512; c->win_length = 400; c->hop_length = 160;
+    c->preemphasis = 0.97; c->log_zero_guard = 5.9604644775390625e-8;
+    c->normalize_per_feature = 1; c->causal = -1; c->xscaling = 0;
+    c->left_ctx = -1; c->right_ctx = -1; c->blank_id = 0; c->max_symbols = 10;
+    c->n_durations = 0; c->strict = 1; c->attn_impl = 0;
+}
+
+// ------------------------------------------------------------------- model
+mynah_b200_model *mynah_b200_model_new(const mynah_b200_config *cfg) {
+    if (!mynah_b200_available()) { set_error("no sm_100 CUDA device available"); return nullptr; }
+    mynah_b200_model *h = new mynah_b200_model();
+    if (cfg) h->m.cfg = *cfg; else mynah_b200_config_default(&h->m.cfg);
+    if (cudaStreamCreateWithFlags(&h->m.stream, cudaStreamNonBlocking) != cudaSuccess) {
+        set_error("cudaStreamCreate failed"); delete h; return nullptr;
+    }
+    h->m.status = (int *)h->m.dev_alloc(sizeof(int));
+    if (!h->m.status) { delete h; return nullptr; }
+    cudaMemset(h->m.status, 0, sizeof(int));
+    return h;
+}
+
+int mynah_b200_model_add_tensor(mynah_b200_model *h, const char *name, int fmt, const int64_t *shape, int rank,
+                                const void *data) {
+    if (!h || !name || !data || rank <= 0 || rank > 8) { set_error("add_tensor: bad argument"); return -1; }
+    if (h->m.finalized) { set_error("add_tensor after finalize"); return -1; }
+    const int f = internal_fmt(fmt);
+    if (f < 0) { set_error("add_tensor '%s': unknown format %d", name, fmt); return -1; }
+    HostTensor t;
+    t.fmt = f; t.data = data; t.shape.assign(shape, shape + rank);
+    h->m.host[name] = t;
+    return 0;
+}
+
+int mynah_b200_model_set_mel(mynah_b200_model *h, const float *mel_fb, const float *window) {
+    if (!h || !mel_fb || !window) { set_error("set_mel: bad argument"); return -1; }
+    Model &m = h->m;
+    const int nb = m.cfg.n_fft / 2 + 1, nm = m.cfg.n_mels, nf = m.cfg.n_fft;
+    m.mel_fb = m.upload_f32(mel_fb, (size_t)nb * nm);
+    // non-zero bin range per filter, as mel_ranges does (src/features.c:50-61)
+    std::vector<int> lo(nm), hi(nm);
+    for (int k = 0; k < nm; k++) {
+        int a = nb, z = 0;
+        for (int b = 0; b < nb; b++) if (mel_fb[(size_t)b * nm + k] != 0.0f) { if (b < a) a = b; z = b + 1; }
+        lo[k] = a; hi[k] = z;
+    }
+    std::vector<double> win(nf, 0.0), tw(nf);
+    const int off = (nf - m.cfg.win_length) / 2;
+    for (int i = 0; i < m.cfg.win_length; i++) win[off + i] = (double)window[i];
+    for (int j = 0; j < nf / 2; j++) { const double a = -2.0 * M_PI * j / nf; tw[2 * j] = cos(a); tw[2 * j + 1] = sin(a); }
+    m.mel_lo = (int *)m.dev_alloc(nm * sizeof(int));
+    m.mel_hi = (int *)m.dev_alloc(nm * sizeof(int));
+    m.mel_win = (double *)m.dev_alloc(nf * sizeof(double));
+    m.mel_tw = (double *)m.dev_alloc(nf * sizeof(double));
+    if (!m.mel_fb || !m.mel_lo || !m.mel_hi || !m.mel_win || !m.mel_tw) return -1;
+    MB_CUDA(cudaMemcpy(m.mel_lo, lo.data(), nm * sizeof(int), cudaMemcpyHostToDevice));
+    MB_CUDA(cudaMemcpy(m.mel_hi, hi.data(), nm * sizeof(int), cudaMemcpyHostToDevice));
+    MB_CUDA(cudaMemcpy(m.mel_win, win.data(), nf * sizeof(double), cudaMemcpyHostToDevice));
+    MB_CUDA(cudaMemcpy(m.mel_tw, tw.data(), nf * sizeof(double), cudaMemcpyHostToDevice));
+    m.has_mel = true;
+    return 0;
+}
+
+}  // extern "C"
+
+// ---- name resolution helpers
+static const HostTensor *find(Model &m, const std::string &name) {
+    auto it = m.host.find(name);
+    return it == m.host.end() ? nullptr : &it->second;
+}
+static const float *f32dev(Model &m, const std::string &name, bool required, int *err) {
+    const HostTensor *t = find(m, name);
+    if (!t) { if (required) { set_error("missing tensor '%s'", name.c_str()); *err = 1; } return nullptr; }
+    if (t->fmt != FMT_F32) { set_error("tensor '%s' must be f32", name.c_str()); *err = 1; return nullptr; }
+    float *d = m.upload_f32((const float *)t->data, t->nelem());
+    if (!d) *err = 1;
+    return d;
+}
+// a linear [n, k] or [n, k, 1]; bias looked up beside it
+static int lin(Model &m, QWeight &w, const std::string &wname, bool planes, bool want_f32, const int *perm = nullptr) {
+    const HostTensor *t = find(m, wname);
+    if (!t || t->shape.empty() || t->shape[0] <= 0) { set_error("missing tensor '%s'", wname.c_str()); return -1; }
+    const int n = (int)t->shape[0], k = (int)(t->nelem() / (size_t)t->shape[0]);
+    const HostTensor *ts = find(m, wname + ".scales");     // native quantised checkpoints
+    if (m.upload_weight(w, t->fmt, t->data, ts ? (const float *)ts->data : nullptr, n, k, planes, want_f32, perm)) return -1;
+    std::string bname = wname;
+    const size_t p = bname.rfind(".weight");
+    if (p != std::string::npos) bname.replace(p, 7, ".bias");
+    int err = 0;
+    w.bias = const_cast<float *>(f32dev(m, bname, false, &err));
+    return err ? -1 : 0;
+}
+
+extern "C" {
+
+int mynah_b200_model_finalize(mynah_b200_model *h) {
+    if (!h) { set_error("finalize: null model"); return -1; }
+    Model &m = h->m;
+    if (m.finalized) return 0;
+    int err = 0;
+    const std::string ss = "encoder.subsampling.";
+    std::string cin, dwn[2], pwn[2];
+    int causal_naming;
+    if (find(m, ss + "conv_in.weight")) {           // Nemotron naming (src/subsampling.c:16-35)
+        causal_naming = 1; cin = ss + "conv_in";
+        for (int i = 0; i < 2; i++) { dwn[i] = ss + "layers." + std::to_string(i) + ".depthwise_conv"; pwn[i] = ss + "layers." + std::to_string(i) + ".pointwise_conv"; }
+    } else {                                        // Parakeet naming (src/subsampling.c:36-52)
+        causal_naming = 0; cin = ss + "layers.0";
+        dwn[0] = ss + "layers.2"; dwn[1] = ss + "layers.5"; pwn[0] = ss + "layers.3"; pwn[1] = ss + "layers.6";
+    }
+    m.causal = m.cfg.causal >= 0 ? m.cfg.causal : causal_naming;
+    const HostTensor *tc = find(m, cin + ".weight"), *tl = find(m, ss + "linear.weight");
+    if (!tc || !tl) { set_error("missing subsampling tensors"); return -1; }
+    m.channels = (int)tc->shape[0];
+    m.d_model = (int)tl->shape[0];
+    m.conv_in_w = f32dev(m, cin + ".weight", true, &err);
+    m.conv_in_b = f32dev(m, cin + ".bias", true, &err);
+    for (int i = 0; i < 2 && !err; i++) {
+        m.dw_w[i] = f32dev(m, dwn[i] + ".weight", true, &err);
+        m.dw_b[i] = f32dev(m, dwn[i] + ".bias", true, &err);
+        if (lin(m, m.pw[i], pwn[i] + ".weight", true, false)) return -1;
+        if (!m.pw[i].bias) { set_error("missing '%s.bias'", pwn[i].c_str()); return -1; }
+    }
+    if (err) return -1;
+    {   // channel-major flatten c*F'+f  ->  f*C+c (see subsampling.cu)
+        const int CF = (int)tl->shape[1], C = m.channels, F3 = CF / C;
+        int f = m.cfg.n_mels;
+        for (int i = 0; i < 3; i++) f = Model::sub_len(f, m.causal);
+        if (f != F3) { set_error("subsampling linear expects %d freq bins, n_mels=%d gives %d", F3, m.cfg.n_mels, f); return -1; }
+        std::vector<int> perm(CF);
+        for (int ff = 0; ff < F3; ff++) for (int c = 0; c < C; c++) perm[ff * C + c] = c * F3 + ff;
+        if (lin(m, m.ss_lin, ss + "linear.weight", true, false, perm.data())) return -1;
+        if (!m.ss_lin.bias) { set_error("missing subsampling linear bias"); return -1; }
+    }
+    const HostTensor *bu = find(m, "encoder.layers.0.self_attn.bias_u");
+    const HostTensor *dw = find(m, "encoder.layers.0.conv.depthwise_conv.weight");
+    if (!bu || !dw) { set_error("missing encoder.layers.0 tensors"); return -1; }
+    m.n_heads = (int)bu->shape[0]; m.d_head = (int)bu->shape[1]; m.conv_k = (int)dw->shape[2];
+    if (m.cfg.xscaling) m.xscale = sqrtf((float)m.d_model);
+    if (find(m, "prompt_projector.linear_1.weight")) { set_error("prompt projector models are not supported"); return -1; }
+    int nl = 0;
+    while (find(m, "encoder.layers." + std::to_string(nl) + ".norm_out.weight")) nl++;
+    if (nl == 0) { set_error("no encoder layers found"); return -1; }
+    m.n_layers = nl;
+    m.layers.resize(nl);
+    const bool bn = find(m, "encoder.layers.0.conv.norm.running_mean") != nullptr;
+    for (int li = 0; li < nl; li++) {
+        EncLayer &L = m.layers[li];
+        const std::string p = "encoder.layers." + std::to_string(li) + ".";
+        L.ln_ff1_w = f32dev(m, p + "norm_feed_forward1.weight", true, &err); L.ln_ff1_b = f32dev(m, p + "norm_feed_forward1.bias", true, &err);
+        L.ln_att_w = f32dev(m, p + "norm_self_att.weight", true, &err); L.ln_att_b = f32dev(m, p + "norm_self_att.bias", true, &err);
+        L.ln_conv_w = f32dev(m, p + "norm_conv.weight", true, &err); L.ln_conv_b = f32dev(m, p + "norm_conv.bias", true, &err);
+        L.ln_ff2_w = f32dev(m, p + "norm_feed_forward2.weight", true, &err); L.ln_ff2_b = f32dev(m, p + "norm_feed_forward2.bias", true, &err);
+        L.ln_out_w = f32dev(m, p + "norm_out.weight", true, &err); L.ln_out_b = f32dev(m, p + "norm_out.bias", true, &err);
+        L.bias_u = f32dev(m, p + "self_attn.bias_u", true, &err); L.bias_v = f32dev(m, p + "self_attn.bias_v", true, &err);
+        L.dw_w = f32dev(m, p + "conv.depthwise_conv.weight", true, &err);
+        L.dw_b = f32dev(m, p + "conv.depthwise_conv.bias", false, &err);
+        L.cnorm_w = f32dev(m, p + "conv.norm.weight", true, &err); L.cnorm_b = f32dev(m, p + "conv.norm.bias", true, &err);
+        L.cnorm_scale = L.cnorm_shift = nullptr;
+        if (err) return -1;
+        if (bn) {   // fold BatchNorm running stats (src/encoder.c:149-170)
+            const HostTensor *mu = find(m, p + "conv.norm.running_mean"), *var = find(m, p + "conv.norm.running_var");
+            const HostTensor *gw = find(m, p + "conv.norm.weight"), *gb = find(m, p + "conv.norm.bias");
+            if (!mu || !var) { set_error("missing BatchNorm running stats at layer %d", li); return -1; }
+            std::vector<float> sc(m.d_model), sh(m.d_model);
+            for (int i = 0; i < m.d_model; i++) {
+                sc[i] = (float)((double)((const float *)gw->data)[i] / sqrt((double)((const float *)var->data)[i] + 1e-5));
+                sh[i] = ((const float *)gb->data)[i] - ((const float *)mu->data)[i] * sc[i];
+            }
+            L.cnorm_scale = m.upload_f32(sc.data(), m.d_model);
+            L.cnorm_shift = m.upload_f32(sh.data(), m.d_model);
+            if (!L.cnorm_scale || !L.cnorm_shift) return -1;
+        }
+        if (lin(m, L.ff1_w1, p + "feed_forward1.linear1.weight", true, false) || lin(m, L.ff1_w2, p + "feed_forward1.linear2.weight", true, false) ||
+            lin(m, L.ff2_w1, p + "feed_forward2.linear1.weight", true, false) || lin(m, L.ff2_w2, p + "feed_forward2.linear2.weight", true, false) ||
+            lin(m, L.q_w, p + "self_attn.q_proj.weight", true, false) || lin(m, L.k_w, p + "self_attn.k_proj.weight", true, false) ||
+            lin(m, L.v_w, p + "self_attn.v_proj.weight", true, false) || lin(m, L.o_w, p + "self_attn.o_proj.weight", true, false) ||
+            lin(m, L.relk, p + "self_attn.relative_k_proj.weight", true, false) ||
+            lin(m, L.pw1_w, p + "conv.pointwise_conv1.weight", true, false) || lin(m, L.pw2_w, p + "conv.pointwise_conv2.weight", true, false))
+            return -1;
+    }
+    m.ffn_dim = m.layers[0].ff1_w1.n;
+    m.d_out = m.d_model;
+    if (find(m, "encoder_projector.weight")) {
+        if (lin(m, m.encproj, "encoder_projector.weight", true, false)) return -1;
+        m.has_encproj = true;
+        m.d_out = m.encproj.n;
+    }
+    if (find(m, "ctc_head.weight")) {
+        if (lin(m, m.ctc_head, "ctc_head.weight", true, false)) return -1;
+        if (!m.ctc_head.bias) { set_error("missing ctc_head.bias"); return -1; }
+        m.has_ctc = true;
+        m.ctc_vocab = m.ctc_head.n;
+    }
+    if (const HostTensor *e = find(m, "decoder.embedding.weight")) {
+        m.vocab = (int)e->shape[0]; m.pred_hidden = (int)e->shape[1];
+        m.emb = f32dev(m, "decoder.embedding.weight", true, &err);
+        m.proj_w = f32dev(m, "decoder.decoder_projector.weight", true, &err);
+        m.proj_b = f32dev(m, "decoder.decoder_projector.bias", true, &err);
+        m.head_b = f32dev(m, "joint.head.bias", true, &err);
+        int n = 0;
+        for (; n < DEC_MAX_LAYERS; n++) {
+            const std::string s = std::to_string(n);
+            if (!find(m, "decoder.lstm.weight_ih_l" + s)) break;
+            m.w_ih[n] = f32dev(m, "decoder.lstm.weight_ih_l" + s, true, &err);
+            m.w_hh[n] = f32dev(m, "decoder.lstm.weight_hh_l" + s, true, &err);
+            m.b_ih[n] = f32dev(m, "decoder.lstm.bias_ih_l" + s, true, &err);
+            m.b_hh[n] = f32dev(m, "decoder.lstm.bias_hh_l" + s, true, &err);
+        }
+        if (err) return -1;
+        if (n == 0 || m.pred_hidden > 1024 || m.pred_hidden % 4) { set_error("unsupported prediction network (layers %d, hidden %d)", n, m.pred_hidden); return -1; }
+        m.pred_layers = n;
+        if (lin(m, m.head, "joint.head.weight", false, true)) return -1;
+        if (m.head.n != m.vocab + m.cfg.n_durations) { set_error("joint head has %d rows, expected vocab %d + %d durations", m.head.n, m.vocab, m.cfg.n_durations); return -1; }
+        if (m.d_out != m.pred_hidden) { set_error("encoder output width %d != prediction hidden %d", m.d_out, m.pred_hidden); return -1; }
+        m.has_dec = true;
+    }
+    m.host.clear();
+    m.finalized = true;
+    MB_CUDA(cudaDeviceSynchronize());
+    return 0;
+}
+
+void mynah_b200_model_free(mynah_b200_model *h) { delete h; }
+
+void mynah_b200_model_dims(const mynah_b200_model *h, int *dims) {
+    const Model &m = h->m;
+    dims[0] = m.d_model; dims[1] = m.n_layers; dims[2] = m.n_heads; dims[3] = m.ffn_dim;
+    dims[4] = m.conv_k; dims[5] = m.d_out; dims[6] = m.causal; dims[7] = m.channels;
+}
+
+void *mynah_b200_model_stream(mynah_b200_model *h) { return h ? (void *)h->m.stream : nullptr; }
+
+}  // extern "C"
+
+// -------------------------------------------------------------- workspace sizes
+static size_t ss_bytes(const Model &m, int t_mel) {
+    const int C = m.channels;
+    const size_t T1 = Model::sub_len(t_mel, m.causal), F1 = Model::sub_len(m.cfg.n_mels, m.causal);
+    const size_t T2 = Model::sub_len((int)T1, m.causal), F2 = Model::sub_len((int)F1, m.causal);
+    const size_t T3 = Model::sub_len((int)T2, m.causal), F3 = Model::sub_len((int)F2, m.causal);
+    return T1 * F1 * C * 4 + T2 * F2 * C * 8 + T3 * F3 * C * 8 + (1 << 16);
+}
+static size_t enc_bytes(const Model &m, size_t M, size_t rk_rows) {
+    return M * ((size_t)m.d_model * 44 + (size_t)m.ffn_dim * 4) + rk_rows * m.d_model * 6 + (1 << 20);
+}
+static size_t dec_bytes(const Model &m, int max_len) {
+    const size_t B = DEC_MAX_B;
+    return (size_t)max_len * m.cfg.max_symbols * B * 8 + B * 148 * 8 * 16 + 4 * (size_t)DEC_MAX_LAYERS * B * 1024 * 4 + (1 << 20);
+}
+
+// Full device pipeline for a packed batch whose mel features are already on the
+// device: subsampling per item, layer stack on the packed rows, projector.
+// x_out receives [sum T, d_model]; returns lens.
+static int encode_batch_dev(Model &m, const std::vector<const float *> &feats_dev, const std::vector<int> &t_mel, int left,
+                            int right, float *x, std::vector<int> &lens) {
+    const int B = (int)t_mel.size();
+    lens.resize(B);
+    int off = 0;
+    for (int b = 0; b < B; b++) {
+        int t = 0;
+        if (t_mel[b] > 0 && m.subsample_item(feats_dev[b], t_mel[b], x + (size_t)off * m.d_model, &t)) return -1;
+        lens[b] = t;
+        off += t;
+    }
+    return m.encoder_layers(x, lens, left, right, 0, m.n_layers);
+}
+
+extern "C" {
+
+float *mynah_b200_log_mel(mynah_b200_model *h, const float *audio, size_t n, int *n_frames, int *valid_frames) {
+    if (!h || !h->m.finalized || (!audio && n)) { set_error("log_mel: bad argument"); return nullptr; }
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    const int hop = m.cfg.hop_length, T = 1 + (int)(n / hop), valid = (int)(n / hop), nm = m.cfg.n_mels;
+    if (m.ws.reserve(n * 4 + (size_t)T * nm * 4 + (1 << 20))) return nullptr;
+    m.ws.reset();
+    float *a = m.ws.get<float>(n ? n : 1), *f = m.ws.get<float>((size_t)T * nm);
+    if (!a || !f) return nullptr;
+    MB_CUDA_NULL(cudaMemcpyAsync(a, audio, n * 4, cudaMemcpyHostToDevice, m.stream));
+    if (m.log_mel(a, n, f, T, valid)) return nullptr;
+    float *out = (float *)malloc((size_t)T * nm * sizeof(float));
+    if (!out) { set_error("out of host memory"); return nullptr; }
+    MB_CUDA_NULL(cudaMemcpyAsync(out, f, (size_t)T * nm * 4, cudaMemcpyDeviceToHost, m.stream));
+    MB_CUDA_NULL(cudaStreamSynchronize(m.stream));
+    *n_frames = T; *valid_frames = valid;
+    return out;
+}
+
+float *mynah_b200_subsampling_forward(mynah_b200_model *h, const float *feats, int T, int n_mels, int *t_out) {
+    if (!h || !h->m.finalized || !feats || T <= 0 || n_mels != h->m.cfg.n_mels) { set_error("subsampling_forward: bad argument"); return nullptr; }
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    const int T3 = m.enc_len(T);
+    if (m.ws.reserve(ss_bytes(m, T) + (size_t)T * n_mels * 4 + (size_t)T3 * m.d_model * 4 + (1 << 20))) return nullptr;
+    m.ws.reset();
+    float *f = m.ws.get<float>((size_t)T * n_mels), *x = m.ws.get<float>((size_t)T3 * m.d_model);
+    MB_CUDA_NULL(cudaMemcpyAsync(f, feats, (size_t)T * n_mels * 4, cudaMemcpyHostToDevice, m.stream));
+    int t = 0;
+    if (m.subsample_item(f, T, x, &t) || m.check_status("subsampling")) return nullptr;
+    float *out = (float *)malloc((size_t)t * m.d_model * sizeof(float));
+    if (!out) { set_error("out of host memory"); return nullptr; }
+    MB_CUDA_NULL(cudaMemcpyAsync(out, x, (size_t)t * m.d_model * 4, cudaMemcpyDeviceToHost, m.stream));
+    MB_CUDA_NULL(cudaStreamSynchronize(m.stream));
+    *t_out = t;
+    return out;
+}
+
+int mynah_b200_encoder_layer(mynah_b200_model *h, int li, float *x, int T, int left, int right) {
+    if (!h || !h->m.finalized || !x || T <= 0 || li < 0 || li >= h->m.n_layers) { set_error("encoder_layer: bad argument"); return -1; }
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    if (m.ws.reserve(enc_bytes(m, T, 2 * T - 1) + (size_t)T * m.d_model * 4)) return -1;
+    m.ws.reset();
+    float *xd = m.ws.get<float>((size_t)T * m.d_model);
+    MB_CUDA(cudaMemcpyAsync(xd, x, (size_t)T * m.d_model * 4, cudaMemcpyHostToDevice, m.stream));
+    std::vector<int> lens{T};
+    if (m.encoder_layers(xd, lens, left, right, li, 1) || m.check_status("encoder_layer")) return -1;
+    MB_CUDA(cudaMemcpyAsync(x, xd, (size_t)T * m.d_model * 4, cudaMemcpyDeviceToHost, m.stream));
+    MB_CUDA(cudaStreamSynchronize(m.stream));
+    return 0;
+}
+
+int mynah_b200_encoder_forward_batch(mynah_b200_model *h, const float *const *feats, const int *t_mel, int batch,
+                                     int n_mels, const int *prompt_ids, int left, int right, float **outs, int *t_outs) {
+    (void)prompt_ids;
+    if (!h || !h->m.finalized || batch <= 0 || n_mels != h->m.cfg.n_mels) { set_error("encoder_forward_batch: bad argument"); return -1; }
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    size_t M = 0, rk = 0, fbytes = 0, ssmax = 0;
+    for (int b = 0; b < batch; b++) {
+        const size_t t = t_mel[b] > 0 ? m.enc_len(t_mel[b]) : 0;
+        M += t; rk += 2 * t; fbytes += align_up((size_t)t_mel[b] * n_mels * 4, 256) + 256;
+        if (t_mel[b] > 0 && ss_bytes(m, t_mel[b]) > ssmax) ssmax = ss_bytes(m, t_mel[b]);
+    }
+    if (m.ws.reserve(fbytes + ssmax + enc_bytes(m, M, rk) + M * ((size_t)m.d_model + m.d_out) * 4 + (1 << 20))) return -1;
+    m.ws.reset();
+    std::vector<const float *> fd(batch);
+    std::vector<int> tm(t_mel, t_mel + batch), lens;
+    for (int b = 0; b < batch; b++) {
+        float *f = m.ws.get<float>((size_t)(t_mel[b] > 0 ? t_mel[b] : 1) * n_mels);
+        if (!f) return -1;
+        if (t_mel[b] > 0) MB_CUDA(cudaMemcpyAsync(f, feats[b], (size_t)t_mel[b] * n_mels * 4, cudaMemcpyHostToDevice, m.stream));
+        fd[b] = f;
+    }
+    float *x = m.ws.get<float>((M ? M : 1) * m.d_model), *y = m.ws.get<float>((M ? M : 1) * m.d_out);
+    if (!x || !y) return -1;
+    if (encode_batch_dev(m, fd, tm, left, right, x, lens)) return -1;
+    if (m.encoder_post(x, (int)M, y) || m.check_status("encoder_forward_batch")) return -1;
+    size_t off = 0;
+    for (int b = 0; b < batch; b++) {
+        t_outs[b] = lens[b];
+        outs[b] = (float *)malloc((size_t)(lens[b] ? lens[b] : 1) * m.d_out * sizeof(float));
+        if (!outs[b]) { set_error("out of host memory"); return -1; }
+        MB_CUDA(cudaMemcpyAsync(outs[b], y + off * m.d_out, (size_t)lens[b] * m.d_out * 4, cudaMemcpyDeviceToHost, m.stream));
+        off += lens[b];
+    }
+    MB_CUDA(cudaStreamSynchronize(m.stream));
+    return 0;
+}
+
+static float *forward_one(mynah_b200_model *h, const float *feats, int t_mel, int n_mels, int left, int right, int raw,
+                          int *t_out) {
+    if (!h || !h->m.finalized || !feats || t_mel <= 0 || n_mels != h->m.cfg.n_mels) { set_error("encoder_forward: bad argument"); return nullptr; }
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    const size_t M = m.enc_len(t_mel);
+    if (m.ws.reserve((size_t)t_mel * n_mels * 4 + ss_bytes(m, t_mel) + enc_bytes(m, M, 2 * M) + M * ((size_t)m.d_model + m.d_out) * 4 + (1 << 20))) return nullptr;
+    m.ws.reset();
+    float *f = m.ws.get<float>((size_t)t_mel * n_mels), *x = m.ws.get<float>(M * m.d_model), *y = m.ws.get<float>(M * m.d_out);
+    if (!f || !x || !y) return nullptr;
+    MB_CUDA_NULL(cudaMemcpyAsync(f, feats, (size_t)t_mel * n_mels * 4, cudaMemcpyHostToDevice, m.stream));
+    std::vector<const float *> fd{f};
+    std::vector<int> tm{t_mel}, lens;
+    if (encode_batch_dev(m, fd, tm, left, right, x, lens)) return nullptr;
+    const int wout = raw ? m.d_model : m.d_out;
+    if (!raw && m.encoder_post(x, (int)M, y)) return nullptr;
+    if (m.check_status("encoder_forward")) return nullptr;
+    float *out = (float *)malloc(M * wout * sizeof(float));
+    if (!out) { set_error("out of host memory"); return nullptr; }
+    MB_CUDA_NULL(cudaMemcpyAsync(out, raw ? x : y, M * wout * 4, cudaMemcpyDeviceToHost, m.stream));
+    MB_CUDA_NULL(cudaStreamSynchronize(m.stream));
+    *t_out = (int)M;
+    return out;
+}
+
+float *mynah_b200_encoder_forward(mynah_b200_model *h, const float *feats, int t_mel, int n_mels, int prompt_id,
+                                  int left, int right, int *t_out) {
+    (void)prompt_id;
+    return forward_one(h, feats, t_mel, n_mels, left, right, 0, t_out);
+}
+float *mynah_b200_encoder_forward_raw(mynah_b200_model *h, const float *feats, int t_mel, int n_mels, int left,
+                                      int right, int *t_out) {
+    return forward_one(h, feats, t_mel, n_mels, left, right, 1, t_out);
+}
+
+int mynah_b200_ctc_decode(mynah_b200_model *h, const float *enc_out, int T, int *tokens, int *frames, int cap) {
+    if (!h || !h->m.finalized || !enc_out || T < 0) { set_error("ctc_decode: bad argument"); return -1; }
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    if (T == 0) return 0;
+    if (m.ws.reserve((size_t)T * (m.d_model * 8 + m.ctc_vocab * 4 + 8) + (1 << 20))) return -1;
+    m.ws.reset();
+    float *e = m.ws.get<float>((size_t)T * m.d_model);
+    MB_CUDA(cudaMemcpyAsync(e, enc_out, (size_t)T * m.d_model * 4, cudaMemcpyHostToDevice, m.stream));
+    std::vector<int> tk, fr;
+    if (m.decode_ctc(e, T, tk, fr) || m.check_status("ctc_decode")) return -1;
+    int n = 0;
+    for (size_t i = 0; i < tk.size() && n < cap; i++, n++) { tokens[n] = tk[i]; if (frames) frames[n] = fr[i]; }
+    return n;
+}
+
+int mynah_b200_greedy_decode(mynah_b200_model *h, const float *enc, int T, int *tokens, int *frames, int cap) {
+    if (!h || !h->m.finalized || !enc || T < 0) { set_error("greedy_decode: bad argument"); return -1; }
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    if (T == 0) return 0;
+    if (m.ws.reserve((size_t)T * m.d_out * 4 + dec_bytes(m, T))) return -1;
+    m.ws.reset();
+    float *e = m.ws.get<float>((size_t)T * m.d_out);
+    MB_CUDA(cudaMemcpyAsync(e, enc, (size_t)T * m.d_out * 4, cudaMemcpyHostToDevice, m.stream));
+    std::vector<int> lens{T};
+    std::vector<std::vector<int>> tk, fr;
+    if (m.decode_greedy(e, lens, tk, fr)) return -1;
+    int n = 0;
+    for (size_t i = 0; i < tk[0].size() && n < cap; i++, n++) { tokens[n] = tk[0][i]; if (frames) frames[n] = fr[0][i]; }
+    return n;
+}
+
+// ------------------------------------------------------------ resident pipeline
+mynah_b200_batch *mynah_b200_batch_upload(mynah_b200_model *h, const float *const *audio, const size_t *n_samples, int batch) {
+    if (!h || !h->m.finalized || batch <= 0) { set_error("batch_upload: bad argument"); return nullptr; }
+    mynah_b200_batch *bt = new mynah_b200_batch();
+    bt->batch = batch;
+    bt->audio.assign(batch, nullptr);
+    bt->n_samples.assign(n_samples, n_samples + batch);
+    for (int b = 0; b < batch; b++) {
+        if (cudaMalloc(&bt->audio[b], (n_samples[b] ? n_samples[b] : 1) * sizeof(float)) != cudaSuccess) {
+            set_error("batch_upload: cudaMalloc failed"); mynah_b200_batch_free(bt); return nullptr;
+        }
+        cudaMemcpyAsync(bt->audio[b], audio[b], n_samples[b] * sizeof(float), cudaMemcpyHostToDevice, h->m.stream);
+    }
+    cudaStreamSynchronize(h->m.stream);
+    return bt;
+}
+
+void mynah_b200_batch_free(mynah_b200_batch *bt) {
+    if (!bt) return;
+    for (float *p : bt->audio) if (p) cudaFree(p);
+    delete bt;
+}
+
+int mynah_b200_batch_run(mynah_b200_model *h, mynah_b200_batch *bt, int decoder) {
+    if (!h || !bt) { set_error("batch_run: bad argument"); return -1; }
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    const int B = bt->batch, nm = m.cfg.n_mels, hop = m.cfg.hop_length;
+    size_t M = 0, rk = 0, fbytes = 0, ssmax = 0;
+    int max_len = 0;
+    std::vector<int> tmel(B), valid(B);
+    for (int b = 0; b < B; b++) {
+        tmel[b] = 1 + (int)(bt->n_samples[b] / hop); valid[b] = (int)(bt->n_samples[b] / hop);
+        const int t = valid[b] > 0 ? m.enc_len(valid[b]) : 0;
+        M += t; rk += 2 * (size_t)t; if (t > max_len) max_len = t;
+        fbytes += align_up((size_t)tmel[b] * nm * 4, 256) + 256;
+        if (valid[b] > 0 && ss_bytes(m, valid[b]) > ssmax) ssmax = ss_bytes(m, valid[b]);
+    }
+    const size_t decb = decoder == 1 ? M * ((size_t)m.d_model * 4 + (size_t)m.ctc_vocab * 4 + 8) : dec_bytes(m, max_len);
+    if (m.ws.reserve(fbytes + ssmax + enc_bytes(m, M, rk) + M * ((size_t)m.d_model + m.d_out) * 4 + decb + (4 << 20))) return -1;
+    m.ws.reset();
+    std::vector<const float *> fd(B);
+    for (int b = 0; b < B; b++) {
+        float *f = m.ws.get<float>((size_t)tmel[b] * nm);
+        if (!f) return -1;
+        if (m.log_mel(bt->audio[b], bt->n_samples[b], f, tmel[b], valid[b])) return -1;
+        fd[b] = f;
+    }
+    float *x = m.ws.get<float>((M ? M : 1) * m.d_model), *y = m.ws.get<float>((M ? M : 1) * m.d_out);
+    if (!x || !y) return -1;
+    std::vector<int> lens;
+    if (encode_batch_dev(m, fd, valid, m.cfg.left_ctx, m.cfg.right_ctx, x, lens)) return -1;
+    bt->tokens.assign(B, {}); bt->frames.assign(B, {});
+    if (decoder == 1) {
+        size_t off = 0;
+        for (int b = 0; b < B; b++) {      // CTC works on the raw encoder output (engine raw_encoder = 1)
+            if (m.decode_ctc(x + off * m.d_model, lens[b], bt->tokens[b], bt->frames[b])) return -1;
+            off += lens[b];
+        }
+    } else {
+        if (m.encoder_post(x, (int)M, y)) return -1;
+        if (m.decode_greedy(y, lens, bt->tokens, bt->frames)) return -1;
+    }
+    return m.check_status("batch_run");
+}
+
+int mynah_b200_batch_fetch(mynah_b200_model *h, mynah_b200_batch *bt, int **tokens, int **frames, int *n_tokens) {
+    (void)h;
+    if (!bt || (int)bt->tokens.size() != bt->batch) { set_error("batch_fetch: nothing to fetch"); return -1; }
+    for (int b = 0; b < bt->batch; b++) {
+        const size_t n = bt->tokens[b].size();
+        n_tokens[b] = (int)n;
+        tokens[b] = (int *)malloc((n ? n : 1) * sizeof(int));
+        if (!tokens[b]) { set_error("out of host memory"); return -1; }
+        memcpy(tokens[b], bt->tokens[b].data(), n * sizeof(int));
+        if (frames) {
+            frames[b] = (int *)malloc((n ? n : 1) * sizeof(int));
+            if (!frames[b]) { set_error("out of host memory"); return -1; }
+            memcpy(frames[b], bt->frames[b].data(), n * sizeof(int));
+        }
+    }
+    return 0;
+}
+
+int mynah_b200_transcribe_batch(mynah_b200_model *h, const float *const *audio, const size_t *n_samples, int batch,
+                                int decoder, int **tokens, int **frames, int *n_tokens) {
+    mynah_b200_batch *bt = mynah_b200_batch_upload(h, audio, n_samples, batch);
+    if (!bt) return -1;
+    int rc = mynah_b200_batch_run(h, bt, decoder);
+    if (rc == 0) rc = mynah_b200_batch_fetch(h, bt, tokens, frames, n_tokens);
+    mynah_b200_batch_free(bt);
+    return rc;
+}
+
+// ------------------------------------------------------------------- qmat API
+mynah_b200_qmat *mynah_b200_qmat_create(int fmt, const void *data, const float *scales, int n, int k) {
+    if (!mynah_b200_available()) { set_error("no sm_100 CUDA device available"); return nullptr; }
+    const int f = internal_fmt(fmt);
+    if (f < 0 || !data || n <= 0 || k <= 0) { set_error("qmat_create: bad argument"); return nullptr; }
+    // a throw-away Model supplies the upload/dequant plumbing; ownership moves to the handle
+    Model tmp;
+    if (cudaStreamCreateWithFlags(&tmp.stream, cudaStreamNonBlocking) != cudaSuccess) { set_error("cudaStreamCreate failed"); return nullptr; }
+    mynah_b200_qmat *q = new mynah_b200_qmat();
+    const bool planes = (k % 64) == 0;
+    if (tmp.upload_weight(q->w, f, data, scales, n, k, planes, false)) { delete q; return nullptr; }
+    q->status = (int *)tmp.dev_alloc(sizeof(int));
+    cudaMemset(q->status, 0, sizeof(int));
+    q->owned.swap(tmp.owned);
+    q->stream = tmp.stream;
+    tmp.stream = nullptr;
+    return q;
+}
+
+void mynah_b200_qmat_free(mynah_b200_qmat *q) {
+    if (!q) return;
+    for (void *p : q->owned) cudaFree(p);
+    if (q->stream) cudaStreamDestroy(q->stream);
+    delete q;
+}
+
+int mynah_b200_qmat_mul_device(const mynah_b200_qmat *q, const float *x, float *out, int T, int flags) {
+    if (!q || !x || !out || T < 0) { set_error("qmat_mul: bad argument"); return -1; }
+    if (T == 0) return 0;
+    const QWeight &w = q->w;
+    if (flags & MYNAH_B200_A8) {
+        const int rc = qgemv_a8(w, x, out, T, nullptr, nullptr, q->stream);
+        if (rc == 0) note_launch(2);
+        return rc;
+    }
+    if (T <= 16 && w.k <= 8192) {     // QMAT_SMALL_T / QMAT_K_MAX of the reference (src/qmat.c:180-181)
+        const int rc = qgemv(w, x, w.k, out, w.n, nullptr, T, q->stream);
+        if (rc == 0) note_launch((T + 3) / 4);
+        return rc;
+    }
+    if (!w.hi) { set_error("qmat_mul: large-T path needs k %% 64 == 0 (k=%d)", w.k); return -1; }
+    __half *hi = nullptr, *lo = nullptr;
+    MB_CUDA(cudaMallocAsync(&hi, (size_t)T * w.k * 2, q->stream));
+    MB_CUDA(cudaMallocAsync(&lo, (size_t)T * w.k * 2, q->stream));
+    int rc = split_to_h16(x, hi, lo, (size_t)T * w.k, q->stream);
+    GemmEpilogue e;
+    memset(&e, 0, sizeof(e));
+    e.mode = OUT_F32; e.act = ACT_NONE; e.alpha = 1.f; e.out = out; e.ldo = w.n;
+    GemmOperand A{hi, lo, w.k}, B{w.hi, w.lo, w.k};
+    if (rc == 0) rc = gemm_tc(A, B, e, T, w.n, w.k, (flags & MYNAH_B200_FAST) ? 1 : 3, q->status, q->stream);
+    if (rc == 0) note_launch(2);
+    cudaFreeAsync(hi, q->stream);
+    cudaFreeAsync(lo, q->stream);
+    return rc;
+}
+
+int mynah_b200_qmat_mul(const mynah_b200_qmat *q, const float *x, float *out, int T, int flags) {
+    if (!q || !x || !out || T < 0) { set_error("qmat_mul: bad argument"); return -1; }
+    if (T == 0) return 0;
+    float *xd = nullptr, *od = nullptr;
+    MB_CUDA(cudaMallocAsync(&xd, (size_t)T * q->w.k * 4, q->stream));
+    MB_CUDA(cudaMallocAsync(&od, (size_t)T * q->w.n * 4, q->stream));
+    MB_CUDA(cudaMemcpyAsync(xd, x, (size_t)T * q->w.k * 4, cudaMemcpyHostToDevice, q->stream));
+    int rc = mynah_b200_qmat_mul_device(q, xd, od, T, flags);
+    if (rc == 0) MB_CUDA(cudaMemcpyAsync(out, od, (size_t)T * q->w.n * 4, cudaMemcpyDeviceToHost, q->stream));
+    int st = 0;
+    cudaMemcpyAsync(&st, q->status, sizeof(int), cudaMemcpyDeviceToHost, q->stream);
+    cudaFreeAsync(xd, q->stream);
+    cudaFreeAsync(od, q->stream);
+    MB_CUDA(cudaStreamSynchronize(q->stream));
+    if (st != 0) { set_error("qmat_mul: a bounded wait inside the contraction kernel ran out (code %d)", st); cudaMemset(q->status, 0, sizeof(int)); return -1; }
+    return rc;
+}
+
+int mynah_b200_qmat_block_dots(const mynah_b200_qmat *q, const float *x, int T, int32_t *dots, float *sx, float *out) {
+    if (!q || !x || T <= 0) { set_error("qmat_block_dots: bad argument"); return -1; }
+    const QWeight &w = q->w;
+    const size_t nd = (size_t)T * w.n * (w.k / 32);
+    float *xd = nullptr, *od = nullptr, *sd = nullptr;
+    int32_t *dd = nullptr;
+    MB_CUDA(cudaMalloc(&xd, (size_t)T * w.k * 4));
+    MB_CUDA(cudaMalloc(&od, (size_t)T * w.n * 4));
+    MB_CUDA(cudaMalloc(&sd, (size_t)T * 4));
+    MB_CUDA(cudaMalloc(&dd, nd * 4));
+    MB_CUDA(cudaMemcpy(xd, x, (size_t)T * w.k * 4, cudaMemcpyHostToDevice));
+    int rc = qgemv_a8(w, xd, od, T, dd, sd, q->stream);
+    if (rc == 0) note_launch(2);
+    cudaStreamSynchronize(q->stream);
+    if (rc == 0 && dots) cudaMemcpy(dots, dd, nd * 4, cudaMemcpyDeviceToHost);
+    if (rc == 0 && sx) cudaMemcpy(sx, sd, (size_t)T * 4, cudaMemcpyDeviceToHost);
+    if (rc == 0 && out) cudaMemcpy(out, od, (size_t)T * w.n * 4, cudaMemcpyDeviceToHost);
+    cudaFree(xd); cudaFree(od); cudaFree(sd); cudaFree(dd);
+    if (rc == 0 && cudaGetLastError() != cudaSuccess) { set_error("qmat_block_dots: device error"); rc = -1; }
+    return rc;
+}
+
+int mynah_b200_qmat_dequant(const mynah_b200_qmat *q, float *wd) {
+    if (!q || !wd) { set_error("qmat_dequant: bad argument"); return -1; }
+    const QWeight &w = q->w;
+    float *d = nullptr;
+    MB_CUDA(cudaMalloc(&d, (size_t)w.n * w.k * 4));
+    int rc = dequant_to_f32(w.fmt, w.raw, w.scales, d, w.n, w.k, q->stream);
+    if (rc == 0) note_launch();
+    cudaStreamSynchronize(q->stream);
+    if (rc == 0) cudaMemcpy(wd, d, (size_t)w.n * w.k * 4, cudaMemcpyDeviceToHost);
+    cudaFree(d);
+    return rc;
+}
+
+int mynah_b200_gemm_wt(const float *x, const float *w, float *out, int T, int n, int k) {
+    if (!x || !w || !out || T <= 0 || n <= 0 || k <= 0) { set_error("gemm_wt: bad argument"); return -1; }
+    mynah_b200_qmat *q = mynah_b200_qmat_create(MYNAH_B200_F32, w, nullptr, n, k);
+    if (!q) return -1;
+    const int rc = mynah_b200_qmat_mul(q, x, out, T, MYNAH_B200_A16);
+    mynah_b200_qmat_free(q);
+    return rc;
+}
+
+double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iters) {
+    if (!q || T <= 0 || iters <= 0) { set_error("qmat_time: bad argument"); return -1.0; }
+    const QWeight &w = q->w;
+    float *x = nullptr, *out = nullptr;
+    __half *hi = nullptr, *lo = nullptr;
+    if (cudaMalloc(&x, (size_t)T * w.k * 4) != cudaSuccess || cudaMalloc(&out, (size_t)T * w.n * 4) != cudaSuccess) { set_error("qmat_time: cudaMalloc failed"); return -1.0; }
+    cudaMemset(x, 0, (size_t)T * w.k * 4);
+    const bool small = (T <= 16 && w.k <= 8192) || (flags & MYNAH_B200_A8);
+    if (!small) {
+        if (!w.hi) { set_error("qmat_time: no operand planes"); cudaFree(x); cudaFree(out); return -1.0; }
+        cudaMalloc(&hi, (size_t)T * w.k * 2); cudaMalloc(&lo, (size_t)T * w.k * 2);
+        split_to_h16(x, hi, lo, (size_t)T * w.k, q->stream);
+    }
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    int rc = 0;
+    for (int it = -2; it < iters && rc == 0; it++) {
+        if (it == 0) cudaEventRecord(e0, q->stream);
+        if (small) rc = (flags & MYNAH_B200_A8) ? qgemv_a8(w, x, out, T, nullptr, nullptr, q->stream) : qgemv(w, x, w.k, out, w.n, nullptr, T, q->stream);
+        else {
+            GemmEpilogue e;
+            memset(&e, 0, sizeof(e));
+            e.mode = OUT_F32; e.alpha = 1.f; e.out = out; e.ldo = w.n;
+            GemmOperand A{hi, lo, w.k}, B{w.hi, w.lo, w.k};
+            rc = gemm_tc(A, B, e, T, w.n, w.k, (flags & MYNAH_B200_FAST) ? 1 : 3, q->status, q->stream);
+        }
+        if (it >= 0) note_launch();
+    }
+    cudaEventRecord(e1, q->stream);
+    cudaEventSynchronize(e1);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaFree(x); cudaFree(out); if (hi) cudaFree(hi); if (lo) cudaFree(lo);
+    if (rc != 0 || cudaGetLastError() != cudaSuccess) { if (rc == 0) set_error("qmat_time: device error"); return -1.0; }
+    return (double)ms / iters;
+}
+
+}  // extern "C"

@@ -1,0 +1,164 @@
+// Row-wise and channel-wise pieces of the FastConformer block that are bound by
+// HBM bandwidth: LayerNorm, the conv-module middle (GLU -> depthwise conv ->
+// folded BatchNorm -> SiLU), positional embedding. Each one reads its input once,
+// coalesced and vectorised, and writes the operand form the next contraction wants.
+#include "kernels.h"
+
+namespace mb {
+
+// ---------------------------------------------------------------- LayerNorm
+// One warp per row. Mean and variance are accumulated in double like the
+// reference's layer_norm_f (src/encoder.c:25-37): y = ((x - mu) * inv) * w + b.
+__global__ void __launch_bounds__(256)
+ln_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b,
+          float *__restrict__ out, __half *__restrict__ hi, __half *__restrict__ lo, int T, int d, int act) {
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= T) return;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * d);
+    const int n4 = d >> 2;
+    double s = 0.0;
+    for (int i = lane; i < n4; i += 32) { const float4 v = xr[i]; s += (double)v.x + (double)v.y + (double)v.z + (double)v.w; }
+    const double mu = warp_sum_d(s) / d;
+    double q = 0.0;
+    for (int i = lane; i < n4; i += 32) {
+        const float4 v = xr[i];
+        const double a = v.x - mu, c = v.y - mu, e = v.z - mu, f = v.w - mu;
+        q += a * a + c * c + e * e + f * f;
+    }
+    const double var = warp_sum_d(q) / d;
+    const float inv = (float)(1.0 / sqrt(var + 1e-5));
+    const float muf = (float)mu;
+    for (int i = lane; i < n4; i += 32) {
+        const float4 v = xr[i];
+        const float4 ww = reinterpret_cast<const float4 *>(w)[i];
+        const float4 bb = reinterpret_cast<const float4 *>(b)[i];
+        float y[4] = {((v.x - muf) * inv) * ww.x + bb.x, ((v.y - muf) * inv) * ww.y + bb.y,
+                      ((v.z - muf) * inv) * ww.z + bb.z, ((v.w - muf) * inv) * ww.w + bb.w};
+        if (act == ACT_SILU) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) y[j] = silu_f(y[j]);
+        }
+        if (out) reinterpret_cast<float4 *>(out + (size_t)row * d)[i] = make_float4(y[0], y[1], y[2], y[3]);
+        if (hi) {
+            __align__(8) __half h[4], l[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) split_h16(y[j], h[j], l[j]);
+            reinterpret_cast<uint2 *>(hi + (size_t)row * d)[i] = *reinterpret_cast<uint2 *>(h);
+            if (lo) reinterpret_cast<uint2 *>(lo + (size_t)row * d)[i] = *reinterpret_cast<uint2 *>(l);
+        }
+    }
+}
+
+int layer_norm(const float *x, const float *w, const float *b, float *out_f32, H16 out_h, int T, int d, int act,
+               cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (d % 4) { set_error("layer_norm: d=%d must be a multiple of 4", d); return -1; }
+    ln_kernel<<<cdiv(T, 8), 256, 0, st>>>(x, w, b, out_f32, out_h.hi, out_h.lo, T, d, act);
+    MB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// -------------------------------------------------- GLU + depthwise conv (+BN+SiLU)
+// h2 [rows, 2d]: a = h2[:, :d], b = h2[:, d:], g = a * sigmoid(b). Depthwise conv of
+// width k along time with zero padding at the segment edges (causal: k-1 on the
+// left; symmetric: (k-1)/2 each side) — src/encoder.c:421-444. One thread per
+// channel, a time tile of TT rows plus the k-1 halo staged in shared memory so every
+// GLU value is computed once.
+static constexpr int DW_TT = 32;
+static constexpr int DW_CH = 128;
+static constexpr int DW_KMAX = 32;
+
+__global__ void __launch_bounds__(DW_CH)
+glu_dw_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, const float *__restrict__ dw_b,
+              const float *__restrict__ scale, const float *__restrict__ shift, float *__restrict__ out,
+              __half *__restrict__ hi, __half *__restrict__ lo, const int *__restrict__ seg_off,
+              const int *__restrict__ seg_len, int d, int k, int pad_left) {
+    __shared__ float g[(DW_TT + DW_KMAX - 1) * DW_CH];
+    const int b = blockIdx.z;
+    const int len = seg_len[b], off = seg_off[b];
+    const int t0 = blockIdx.y * DW_TT;
+    if (t0 >= len) return;
+    const int c = blockIdx.x * DW_CH + threadIdx.x;
+    const bool cok = c < d;
+    const int rows = DW_TT + k - 1;
+    for (int r = 0; r < rows; r++) {
+        const int t = t0 - pad_left + r;
+        float v = 0.0f;
+        if (cok && t >= 0 && t < len) {
+            const float *p = h2 + (size_t)(off + t) * (2 * d);
+            v = p[c] * sigmoid_stable(p[d + c]);
+        }
+        g[r * DW_CH + threadIdx.x] = v;
+    }
+    if (!cok) return;
+    float w[DW_KMAX];
+#pragma unroll
+    for (int j = 0; j < DW_KMAX; j++) w[j] = j < k ? dw_w[(size_t)c * k + j] : 0.0f;
+    const float bias = dw_b ? dw_b[c] : 0.0f;
+    const float sc = scale ? scale[c] : 1.0f, sh = scale ? shift[c] : 0.0f;
+    const int tend = len - t0 < DW_TT ? len - t0 : DW_TT;
+    for (int tt = 0; tt < tend; tt++) {
+        float acc = bias;
+#pragma unroll
+        for (int j = 0; j < DW_KMAX; j++)
+            if (j < k) acc += w[j] * g[(tt + j) * DW_CH + threadIdx.x];
+        const size_t o = (size_t)(off + t0 + tt) * d + c;
+        if (scale) {
+            const float y = silu_f(acc * sc + sh);
+            __half h, l;
+            split_h16(y, h, l);
+            hi[o] = h;
+            if (lo) lo[o] = l;
+        } else {
+            out[o] = acc;
+        }
+    }
+}
+
+int glu_dwconv(const float *h2, const float *dw_w, const float *dw_b, const float *scale, const float *shift,
+               float *out_f32, H16 out_h, const int *seg_off, const int *seg_len, int batch, int max_len, int d,
+               int k, int pad_left, cudaStream_t st) {
+    if (batch <= 0 || max_len <= 0) return 0;
+    if (k > DW_KMAX) { set_error("glu_dwconv: kernel width %d > %d", k, DW_KMAX); return -1; }
+    dim3 grid(cdiv(d, DW_CH), cdiv(max_len, DW_TT), batch);
+    glu_dw_kernel<<<grid, DW_CH, 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
+                                          seg_len, d, k, pad_left);
+    MB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// ------------------------------------------------------------------- misc
+__global__ void scale_kernel(float *x, size_t n, float s) {
+    size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= s;
+}
+int scale_inplace(float *x, size_t n, float s, cudaStream_t st) {
+    if (n == 0 || s == 1.0f) return 0;
+    scale_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(x, n, s);
+    MB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+// Relative positional embedding [2T-1, d]: row p is position T-1-p, interleaved
+// sin/cos of pos * 10000^(-2j/d), evaluated in double (src/encoder.c:201-211).
+__global__ void pos_emb_kernel(__half *hi, __half *lo, int T, int d) {
+    const int p = blockIdx.x;
+    const double pos = (double)(T - 1 - p);
+    for (int j = threadIdx.x; j < d / 2; j += blockDim.x) {
+        const double f = pos * pow(10000.0, -2.0 * j / (double)d);
+        const float s = (float)sin(f), c = (float)cos(f);
+        __half h, l;
+        split_h16(s, h, l);
+        hi[(size_t)p * d + 2 * j] = h; lo[(size_t)p * d + 2 * j] = l;
+        split_h16(c, h, l);
+        hi[(size_t)p * d + 2 * j + 1] = h; lo[(size_t)p * d + 2 * j + 1] = l;
+    }
+}
+int pos_emb(H16 pe, int T, int d, cudaStream_t st) {
+    if (T <= 0) return 0;
+    pos_emb_kernel<<<2 * T - 1, 128, 0, st>>>(pe.hi, pe.lo, T, d);
+    MB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace mb

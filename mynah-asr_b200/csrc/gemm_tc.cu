@@ -1,0 +1,223 @@
+// Dense contraction C[M,N] = A[M,K] * B[N,K]^T on the 5th-generation tensor cores.
+//
+// This is the large-M half of the quantised matmul (the reference's
+// mynah_asr_qmat_mul, src/qmat.c:503-651, and mynah_asr_gemm_wt, src/backend.c:68-81):
+// weights arrive already decoded to fp16 (hi, lo) planes resident in HBM, activations
+// as fp16 (hi, lo) planes written by the producing kernel's epilogue.
+//
+//   * TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) stages 128 x 64
+//     A tiles and BN x 64 B tiles into a shared-memory ring guarded by mbarriers;
+//   * one elected thread issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) into a
+//     TMEM accumulator; with NTERMS=3 every k-step issues hi*hi + lo*hi + hi*lo so
+//     the product carries ~22 significant bits per operand (f32-grade parity with
+//     the reference's sgemm), with NTERMS=1 only hi*hi (fast mode);
+//   * four epilogue warps read the accumulator with tcgen05.ld and apply the fused
+//     tail: + bias, SiLU / ReLU, then either store f32, accumulate into the residual
+//     stream (x += alpha * y), or store the result as fp16 (hi, lo) planes for the
+//     next contraction.
+//
+// Row stability: an output row depends only on its own A row and on B; the k order
+// and the instruction sequence are the same for every tile position and every M, so
+// a row's bits do not depend on what else is in the batch.
+#include "gemm.h"
+
+namespace mb {
+
+static constexpr int BM = 128;
+static constexpr int BK = 64;
+static constexpr int GEMM_THREADS = 192;
+static constexpr int SMEM_LIMIT = 232448;  // 227 KB
+
+template <int BN, int NTERMS>
+struct GemmCfg {
+    static constexpr int NPLANES = NTERMS == 1 ? 1 : 2;
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = NPLANES * (A_BYTES + B_BYTES);
+    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2048;
+    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+template <int BN, int NTERMS>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant__ CUtensorMap tmA_lo,
+               const __grid_constant__ CUtensorMap tmB_hi, const __grid_constant__ CUtensorMap tmB_lo,
+               const GemmEpilogue ep, const int M, const int N, const int K, int *status) {
+    using Cfg = GemmCfg<BN, NTERMS>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *tiles = smem;
+    uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t *empty_bar = full_bar + Cfg::STAGES;
+    uint64_t *acc_bar = empty_bar + Cfg::STAGES;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_bar + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+    const int num_k = K / BK;
+
+    if (threadIdx.x == 0) {
+        tma_prefetch_desc(&tmA_hi);
+        tma_prefetch_desc(&tmB_hi);
+        if (NTERMS > 1) { tma_prefetch_desc(&tmA_lo); tma_prefetch_desc(&tmB_lo); }
+        for (int s = 0; s < Cfg::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(acc_bar, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) { tc_alloc(tmem_slot, Cfg::TMEM_COLS); tc_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0 && lane == 0) {
+        // ---------------------------------------------------------- TMA producer
+        int issued = 0;
+        bool ok = true;
+        for (int kb = 0; kb < num_k && ok; kb++) {
+            const int s = kb % Cfg::STAGES;
+            const uint32_t ph = (kb / Cfg::STAGES) & 1;
+            if (!mbar_wait(&empty_bar[s], ph ^ 1)) { ok = false; break; }
+            uint8_t *st = tiles + s * Cfg::STAGE_BYTES;
+            mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+            tma_load_2d(st, &tmA_hi, kb * BK, m0, &full_bar[s]);
+            if (NTERMS > 1) tma_load_2d(st + Cfg::A_BYTES, &tmA_lo, kb * BK, m0, &full_bar[s]);
+            uint8_t *bt = st + Cfg::NPLANES * Cfg::A_BYTES;
+            tma_load_2d(bt, &tmB_hi, kb * BK, n0, &full_bar[s]);
+            if (NTERMS > 1) tma_load_2d(bt + Cfg::B_BYTES, &tmB_lo, kb * BK, n0, &full_bar[s]);
+            issued++;
+        }
+        if (!ok) {
+            atomicExch(status, ST_TIMEOUT_PRODUCER);
+            // let copies already in flight land before the CTA's shared memory goes away
+            for (int kb = issued > Cfg::STAGES ? issued - Cfg::STAGES : 0; kb < issued; kb++)
+                mbar_wait(&full_bar[kb % Cfg::STAGES], (kb / Cfg::STAGES) & 1);
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc = umma_idesc_f16(BM, BN);
+        bool ok = true;
+        for (int kb = 0; kb < num_k; kb++) {
+            const int s = kb % Cfg::STAGES;
+            const uint32_t ph = (kb / Cfg::STAGES) & 1;
+            if (!mbar_wait(&full_bar[s], ph)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t a_hi = smem_u32(tiles + s * Cfg::STAGE_BYTES);
+            const uint32_t a_lo = a_hi + Cfg::A_BYTES;
+            const uint32_t b_hi = a_hi + Cfg::NPLANES * Cfg::A_BYTES;
+            const uint32_t b_lo = b_hi + Cfg::B_BYTES;
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; kk++) {
+                const uint32_t off = kk * 32;   // 16 fp16 = 32 bytes inside the swizzle atom
+                tc_mma_f16(tmem_base, umma_desc_sw128(a_hi + off), umma_desc_sw128(b_hi + off), idesc,
+                           (kb | kk) != 0);
+                if (NTERMS > 1) {
+                    tc_mma_f16(tmem_base, umma_desc_sw128(a_lo + off), umma_desc_sw128(b_hi + off), idesc, 1);
+                    tc_mma_f16(tmem_base, umma_desc_sw128(a_hi + off), umma_desc_sw128(b_lo + off), idesc, 1);
+                }
+            }
+            tc_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
+        }
+        if (!ok) atomicExch(status, ST_TIMEOUT_MMA);
+        tc_commit(acc_bar);             // accumulator complete (or abandoned)
+    } else if (warp >= 2) {
+        // -------------------------------------------------------------- epilogue
+        const int lg = warp & 3;                       // TMEM lane group this warp may read
+        const int row = lg * 32 + lane;
+        const int m = m0 + row;
+        bool ok = mbar_wait(acc_bar, 0);
+        if (!ok) { if (lane == 0) atomicExch(status, ST_TIMEOUT_EPILOGUE); }
+        tc_fence_after();
+        if (ok && num_k > 0) {
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                float v[32];
+                tc_ld32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(c * 32), v);
+                tc_wait_ld();
+                const int nb = n0 + c * 32;
+                if (m < M && nb < N) gemm_epilogue_row(ep, v, m, nb, N);
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tc_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// fp16 [rows, K] row-major with row stride ld (halves): box = 64 (K) x box_rows, 128B swizzle.
+static int make_map(CUtensorMap *m, const __half *base, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) { set_error("cuTensorMapEncodeTiled entry point unavailable"); return -1; }
+    if ((reinterpret_cast<uintptr_t>(base) & 15) || (ld % 8) != 0) {
+        set_error("gemm_tc: operand base/stride not 16-byte aligned");
+        return -1;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<__half *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return -1; }
+    return 0;
+}
+
+template <int BN, int NTERMS>
+static int launch(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, int M, int N, int K,
+                  int *status, cudaStream_t stream) {
+    using Cfg = GemmCfg<BN, NTERMS>;
+    CUtensorMap ta_hi, ta_lo, tb_hi, tb_lo;
+    if (make_map(&ta_hi, A.hi, M, K, A.ld, BM)) return -1;
+    if (make_map(&tb_hi, B.hi, N, K, B.ld, BN)) return -1;
+    if (NTERMS > 1) {
+        if (make_map(&ta_lo, A.lo, M, K, A.ld, BM)) return -1;
+        if (make_map(&tb_lo, B.lo, N, K, B.ld, BN)) return -1;
+    } else {
+        ta_lo = ta_hi; tb_lo = tb_hi;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        MB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, NTERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    dim3 grid(cdiv(N, BN), cdiv(M, BM));
+    gemm_tc_kernel<BN, NTERMS><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, ep, M,
+                                                                               N, K, status);
+    MB_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int gemm_tc(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, int M, int N, int K, int nterms,
+            int *status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % BK != 0) { set_error("gemm_tc: K=%d must be a positive multiple of %d", K, BK); return -1; }
+    if (nterms == 1) {
+        if (N >= 256) return launch<256, 1>(A, B, ep, M, N, K, status, stream);
+        return launch<128, 1>(A, B, ep, M, N, K, status, stream);
+    }
+    if (!A.lo || !B.lo) { set_error("gemm_tc: 3-term mode needs lo planes"); return -1; }
+    return launch<128, 3>(A, B, ep, M, N, K, status, stream);
+}
+
+}  // namespace mb

@@ -1,0 +1,78 @@
+// Host-callable launchers for the non-GEMM kernels of the hot path.
+#pragma once
+#include "common.cuh"
+#include "gemm.h"
+
+namespace mb {
+
+// Weight formats accepted at the boundary (values are part of the C ABI).
+enum {
+    FMT_F32 = 0,
+    FMT_MYNAH_Q8 = 1,    // per-row int8, f32 scales [n]            (src/qmat.h:6-9)
+    FMT_MYNAH_Q4 = 2,    // per-32 nibbles, f32 scales [n,k/32]
+    FMT_GGML_Q4_0 = 102, // 100 + ggml type id: 18-byte blocks of 32
+    FMT_GGML_Q8_0 = 108, // 34-byte blocks of 32
+    FMT_GGML_Q4_K = 112, // 144-byte super-blocks of 256
+    FMT_GGML_Q6_K = 114, // 210-byte super-blocks of 256
+};
+
+// ---- dequant.cu
+int dequant_to_f32(int fmt, const void *src, const float *scales, float *dst, int n, int k, cudaStream_t st);
+size_t format_bytes(int fmt, int n, int k);
+int format_block(int fmt);
+int split_to_h16(const float *x, __half *hi, __half *lo, size_t n, cudaStream_t st);
+
+// ---- elementwise.cu
+// Row LayerNorm (mean/var accumulated in double, eps 1e-5) with optional SiLU;
+// writes f32 and/or fp16 (hi,lo) planes. out_f32 may alias x.
+int layer_norm(const float *x, const float *w, const float *b, float *out_f32, H16 out_h, int T, int d, int act,
+               cudaStream_t st);
+// Conv-module middle: GLU over h2 [T,2d], depthwise conv k along time inside each
+// segment, then either a per-channel affine (folded BatchNorm) + SiLU -> planes, or
+// (affine null) the raw depthwise output as f32 for a following LayerNorm.
+int glu_dwconv(const float *h2, const float *dw_w, const float *dw_b, const float *scale, const float *shift,
+               float *out_f32, H16 out_h, const int *seg_off, const int *seg_len, int batch, int max_len, int d,
+               int k, int pad_left, cudaStream_t st);
+int scale_inplace(float *x, size_t n, float s, cudaStream_t st);
+int pos_emb(H16 pe, int T, int d, cudaStream_t st);            // [2T-1, d] planes
+
+// ---- attention.cu
+struct AttnArgs {
+    const float *q;             // [rows, ldq] f32 (packed batch), bias_u / bias_v added inside
+    int ldq;
+    const __half *k, *v;        // [rows, d] fp16
+    const __half *rk;           // [sum(2T-1), d] fp16: pos-emb projected by relative_k_proj
+    const float *bias_u, *bias_v;   // [H, dk]
+    float *ctx_f32;             // optional [rows, d]
+    H16 ctx_h;                  // [rows, d] planes (operand of the output projection)
+    const int *seg_off, *seg_len, *rk_off;   // device arrays [batch]
+    int batch, max_len, d, H;
+    int left, right;            // left < 0: full attention
+};
+int attention_forward(const AttnArgs &a, int impl, cudaStream_t st);   // impl 0 = tiled tensor-core, 1 = plain
+
+// ---- subsampling.cu
+int conv_in_relu(const float *feats, const float *w, const float *b, float *out, int T, int F, int C, int To, int Fo,
+                 int pl, cudaStream_t st);                         // [T,F] -> [To,Fo,C]
+int dwconv3x3_s2(const float *x, const float *w, const float *b, H16 out, int T, int F, int C, int To, int Fo, int pl,
+                 cudaStream_t st);                                 // [T,F,C] -> planes [To*Fo, C]
+
+// ---- mel.cu
+struct MelCfg {
+    int n_mels, n_fft, win_length, hop;
+    double preemph, guard;
+    int normalize;
+};
+int log_mel_device(const MelCfg &c, const float *audio, size_t n_samples, const float *mel_fb, const int *mel_lo,
+                   const int *mel_hi, const double *win, const double *twiddle, float *feats, int T, int valid,
+                   cudaStream_t st);
+
+// ---- qgemv.cu : out[T,n] = x[T,k] W^T for T <= 16 straight from the stored blocks
+struct QWeight;
+int qgemv(const QWeight &w, const float *x, int ldx, float *out, int ldo, const float *bias, int T, cudaStream_t st);
+int qgemv_a8(const QWeight &w, const float *x, float *out, int T, int32_t *block_dots, float *sx_out, cudaStream_t st);
+
+// ---- decoder.cu
+int argmax_rows(const float *logits, int ld, const float *bias, int T, int V, int *best, cudaStream_t st);
+
+}  // namespace mb

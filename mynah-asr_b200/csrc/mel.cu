@@ -1,0 +1,99 @@
+// Log-mel front end (the reference's mynah_asr_log_mel, src/features.c:106-167):
+// pre-emphasis -> zero centre pad n_fft/2 -> Hann window centred in n_fft ->
+// radix-2 FFT in double -> |X|^2 -> sparse triangular mel projection in double ->
+// log(x + guard) -> float; optional per-feature normalisation over the valid
+// frames (mean, std with ddof=1, (x-mu)/(std+1e-5)).
+//
+// One CTA per frame: the frame is gathered straight from the f32 audio with the
+// pre-emphasis applied on the fly, the FFT runs in shared memory in double (the
+// reference keeps double for parity with its numpy oracle, src/features.c:13-15;
+// at ~0.14 GFLOP per minute of audio it costs nothing), twiddles come from an exact
+// host table. Frames >= valid stay zero, as in the reference.
+#include "kernels.h"
+
+namespace mb {
+
+static constexpr int MEL_MAX_FFT = 1024;
+
+__global__ void __launch_bounds__(128)
+mel_frame_kernel(const float *__restrict__ audio, long long S, const double *__restrict__ win,
+                 const double *__restrict__ tw, const float *__restrict__ fb, const int *__restrict__ mlo,
+                 const int *__restrict__ mhi, float *__restrict__ feats, int n_fft, int log2n, int hop, int n_mels,
+                 double preemph, double guard) {
+    __shared__ double re[MEL_MAX_FFT], im[MEL_MAX_FFT];
+    const int t = blockIdx.x;
+    const long long start = (long long)t * hop - n_fft / 2;      // index into the unpadded signal
+    for (int i = threadIdx.x; i < n_fft; i += blockDim.x) {
+        const long long s = start + i;
+        double y = 0.0;
+        if (s >= 0 && s < S) y = s == 0 ? (double)audio[0] : (double)audio[s] - preemph * (double)audio[s - 1];
+        const int r = (int)(__brev((unsigned)i) >> (32 - log2n));
+        re[r] = y * win[i];
+        im[r] = 0.0;
+    }
+    __syncthreads();
+    for (int len = 2, sh = log2n - 1; len <= n_fft; len <<= 1, sh--) {
+        const int half = len >> 1;
+        for (int i = threadIdx.x; i < n_fft / 2; i += blockDim.x) {
+            const int grp = i / half, k = i % half;
+            const int a = grp * len + k, bq = a + half;
+            const double wr = tw[2 * (k << sh)], wi = tw[2 * (k << sh) + 1];
+            const double xr = re[bq] * wr - im[bq] * wi, xi = re[bq] * wi + im[bq] * wr;
+            re[bq] = re[a] - xr; im[bq] = im[a] - xi;
+            re[a] += xr;         im[a] += xi;
+        }
+        __syncthreads();
+    }
+    const int nb = n_fft / 2 + 1;
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) re[i] = re[i] * re[i] + im[i] * im[i];   // power, in place
+    __syncthreads();
+    for (int m = threadIdx.x; m < n_mels; m += blockDim.x) {
+        double acc = 0.0;
+        for (int b = mlo[m]; b < mhi[m]; b++) acc += re[b] * (double)fb[(size_t)b * n_mels + m];
+        feats[(size_t)t * n_mels + m] = (float)log(acc + guard);
+    }
+}
+
+// per-feature normalisation: one CTA per mel bin
+__global__ void __launch_bounds__(256)
+mel_norm_kernel(float *feats, int valid, int n_mels) {
+    __shared__ double red[256];
+    const int m = blockIdx.x;
+    double s = 0.0;
+    for (int t = threadIdx.x; t < valid; t += 256) s += (double)feats[(size_t)t * n_mels + m];
+    red[threadIdx.x] = s;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) { if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o]; __syncthreads(); }
+    const double mu = red[0] / valid;
+    __syncthreads();
+    double q = 0.0;
+    for (int t = threadIdx.x; t < valid; t += 256) { const double c = (double)feats[(size_t)t * n_mels + m] - mu; q += c * c; }
+    red[threadIdx.x] = q;
+    __syncthreads();
+    for (int o = 128; o > 0; o >>= 1) { if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o]; __syncthreads(); }
+    const double inv = 1.0 / (sqrt(red[0] / (valid - 1)) + 1e-5);
+    for (int t = threadIdx.x; t < valid; t += 256) {
+        float *v = feats + (size_t)t * n_mels + m;
+        *v = (float)(((double)*v - mu) * inv);
+    }
+}
+
+int log_mel_device(const MelCfg &c, const float *audio, size_t n_samples, const float *mel_fb, const int *mel_lo,
+                   const int *mel_hi, const double *win, const double *twiddle, float *feats, int T, int valid,
+                   cudaStream_t st) {
+    if (c.n_fft > MEL_MAX_FFT || (c.n_fft & (c.n_fft - 1))) { set_error("log_mel: n_fft %d unsupported", c.n_fft); return -1; }
+    MB_CUDA(cudaMemsetAsync(feats, 0, (size_t)T * c.n_mels * sizeof(float), st));
+    if (valid <= 0) return 0;
+    int log2n = 0;
+    while ((1 << log2n) < c.n_fft) log2n++;
+    mel_frame_kernel<<<valid, 128, 0, st>>>(audio, (long long)n_samples, win, twiddle, mel_fb, mel_lo, mel_hi, feats,
+                                            c.n_fft, log2n, c.hop, c.n_mels, c.preemph, c.guard);
+    MB_CUDA(cudaGetLastError());
+    if (c.normalize && valid > 1) {
+        mel_norm_kernel<<<c.n_mels, 256, 0, st>>>(feats, valid, c.n_mels);
+        MB_CUDA(cudaGetLastError());
+    }
+    return 0;
+}
+
+}  // namespace mb

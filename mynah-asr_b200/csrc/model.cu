@@ -1,0 +1,354 @@
+// Model container and the device-resident drivers of the hot path: weights are
+// uploaded and decoded once (replacing the reference's lazy per-pointer upload,
+// src/cuda_gemm.cu:96-130), activations never leave HBM between the mel input and
+// the token ids (replacing its per-GEMM H2D/D2H round trip, src/cuda_gemm.cu:170-188).
+#include "model.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
+
+namespace mb {
+
+static std::atomic<long long> g_launches{0};
+void note_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launch_count(bool reset) { return reset ? g_launches.exchange(0) : g_launches.load(); }
+
+// -------------------------------------------------------------------- arena
+int Arena::reserve(size_t bytes) {
+    bytes = align_up(bytes, 1 << 20);
+    if (bytes <= cap) return 0;
+    if (base) MB_CUDA(cudaFree(base));
+    base = nullptr; cap = 0;
+    MB_CUDA(cudaMalloc(&base, bytes));
+    cap = bytes;
+    return 0;
+}
+void *Arena::take(size_t bytes) {
+    const size_t o = align_up(off, 256);
+    if (o + bytes > cap) { set_error("workspace arena exhausted (%zu + %zu > %zu)", o, bytes, cap); return nullptr; }
+    off = o + bytes;
+    return base + o;
+}
+void Arena::release() { if (base) cudaFree(base); base = nullptr; cap = off = 0; }
+
+// -------------------------------------------------------------------- model
+Model::~Model() {
+    for (void *p : owned) cudaFree(p);
+    ws.release();
+    if (stream) cudaStreamDestroy(stream);
+}
+void *Model::dev_alloc(size_t bytes) {
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess) { set_error("cudaMalloc(%zu) failed", bytes); cudaGetLastError(); return nullptr; }
+    owned.push_back(p);
+    return p;
+}
+float *Model::upload_f32(const float *src, size_t n) {
+    float *d = (float *)dev_alloc(n * sizeof(float));
+    if (!d) return nullptr;
+    if (cudaMemcpy(d, src, n * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) { set_error("H2D copy failed"); return nullptr; }
+    return d;
+}
+
+int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *scales, int n, int k, bool want_planes,
+                         bool want_f32, const int *col_perm) {
+    w.fmt = fmt; w.n = n; w.k = k;
+    const int blk = format_block(fmt);
+    if (k % blk) { set_error("weight [%d,%d]: k not a multiple of the %d-element block", n, k, blk); return -1; }
+    w.raw_bytes = format_bytes(fmt, n, k);
+    if (!w.raw_bytes) { set_error("unknown weight format %d", fmt); return -1; }
+    w.raw = (uint8_t *)dev_alloc(w.raw_bytes + 64);          // slack for aligned over-reads
+    if (!w.raw) return -1;
+    MB_CUDA(cudaMemcpy(w.raw, data, w.raw_bytes, cudaMemcpyHostToDevice));
+    MB_CUDA(cudaMemset(w.raw + w.raw_bytes, 0, 64));
+    if (fmt == FMT_MYNAH_Q8 || fmt == FMT_MYNAH_Q4) {
+        if (!scales) { set_error("native quantised weight without scales"); return -1; }
+        const size_t ns = fmt == FMT_MYNAH_Q8 ? (size_t)n : (size_t)n * (k / 32);
+        w.scales = upload_f32(scales, ns);
+        if (!w.scales) return -1;
+    }
+    if (!want_planes && !want_f32) return 0;
+    float *tmp = nullptr;
+    MB_CUDA(cudaMalloc(&tmp, (size_t)n * k * sizeof(float)));
+    int rc = dequant_to_f32(fmt, w.raw, w.scales, tmp, n, k, stream);
+    note_launch();
+    if (rc == 0 && col_perm) {
+        // column permutation on the host (only the subsampling linear, once at load)
+        std::vector<float> a((size_t)n * k), b((size_t)n * k);
+        cudaStreamSynchronize(stream);
+        cudaMemcpy(a.data(), tmp, a.size() * 4, cudaMemcpyDeviceToHost);
+        for (int r = 0; r < n; r++)
+            for (int c = 0; c < k; c++) b[(size_t)r * k + c] = a[(size_t)r * k + col_perm[c]];
+        cudaMemcpy(tmp, b.data(), b.size() * 4, cudaMemcpyHostToDevice);
+    }
+    if (rc == 0 && want_planes) {
+        w.hi = (__half *)dev_alloc((size_t)n * k * 2);
+        w.lo = (__half *)dev_alloc((size_t)n * k * 2);
+        if (!w.hi || !w.lo) rc = -1;
+        else { rc = split_to_h16(tmp, w.hi, w.lo, (size_t)n * k, stream); note_launch(); }
+    }
+    cudaStreamSynchronize(stream);
+    if (rc == 0 && want_f32) { w.f32 = tmp; owned.push_back(tmp); }
+    else cudaFree(tmp);
+    return rc;
+}
+
+int Model::check_status(const char *where) {
+    int st = 0;
+    MB_CUDA(cudaMemcpyAsync(&st, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    MB_CUDA(cudaStreamSynchronize(stream));
+    if (st != 0) {
+        set_error("%s: a bounded wait inside the contraction kernel ran out (code %d)", where, st);
+        cudaMemsetAsync(status, 0, sizeof(int), stream);
+        return -1;
+    }
+    return 0;
+}
+
+int Model::gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep, int M) {
+    if (!w.hi) { set_error("contraction on a weight without operand planes"); return -1; }
+    GemmOperand A{a.hi, a.lo, lda}, B{w.hi, w.lo, w.k};
+    const int rc = gemm_tc(A, B, ep, M, w.n, w.k, cfg.strict ? 3 : 1, status, stream);
+    if (rc == 0) note_launch();
+    return rc;
+}
+
+static GemmEpilogue epi(int mode, int act, float alpha, const float *bias, float *out, int ldo, H16 h = H16{nullptr, nullptr},
+                        int ldh = 0) {
+    GemmEpilogue e;
+    e.mode = mode; e.act = act; e.alpha = alpha; e.bias = bias; e.out = out; e.ldo = ldo;
+    e.out_hi = h.hi; e.out_lo = h.lo; e.ldh = ldh;
+    return e;
+}
+
+// ---------------------------------------------------------------- subsampling
+// feats [t_mel, n_mels] on the device -> x_out [T3, d_model]; scratch from the arena
+// (released on return: later kernels are ordered behind these on the same stream).
+int Model::subsample_item(const float *feats, int t_mel, float *x_out, int *t_out) {
+    const int C = channels, pl = causal ? 2 : 1, F0 = cfg.n_mels;
+    const int T1 = sub_len(t_mel, causal), F1 = sub_len(F0, causal);
+    const int T2 = sub_len(T1, causal), F2 = sub_len(F1, causal);
+    const int T3 = sub_len(T2, causal), F3 = sub_len(F2, causal);
+    const size_t mark = ws.off;
+    float *a0 = ws.get<float>((size_t)T1 * F1 * C);
+    H16 p1 = ws.planes((size_t)T2 * F2 * C);
+    float *a1 = ws.get<float>((size_t)T2 * F2 * C);
+    H16 p2 = ws.planes((size_t)T3 * F3 * C);
+    H16 flat = ws.planes((size_t)T3 * F3 * C);
+    if (!a0 || !p1.hi || !p1.lo || !a1 || !p2.hi || !p2.lo || !flat.hi || !flat.lo) return -1;
+    if (conv_in_relu(feats, conv_in_w, conv_in_b, a0, t_mel, F0, C, T1, F1, pl, stream)) return -1;
+    if (dwconv3x3_s2(a0, dw_w[0], dw_b[0], p1, T1, F1, C, T2, F2, pl, stream)) return -1;
+    if (gemm(p1, C, pw[0], epi(OUT_F32, ACT_RELU, 1.f, pw[0].bias, a1, C), T2 * F2)) return -1;
+    if (dwconv3x3_s2(a1, dw_w[1], dw_b[1], p2, T2, F2, C, T3, F3, pl, stream)) return -1;
+    if (gemm(p2, C, pw[1], epi(OUT_H16, ACT_RELU, 1.f, pw[1].bias, nullptr, 0, flat, C), T3 * F3)) return -1;
+    // flat is [T3, F3*C]: the linear's columns were permuted to this order at load
+    if (gemm(flat, F3 * C, ss_lin, epi(OUT_F32, ACT_NONE, 1.f, ss_lin.bias, x_out, d_model), T3)) return -1;
+    note_launch(3);
+    if (xscale != 1.0f) { if (scale_inplace(x_out, (size_t)T3 * d_model, xscale, stream)) return -1; note_launch(); }
+    ws.off = mark;
+    *t_out = T3;
+    return 0;
+}
+
+// ---------------------------------------------------------------- encoder stack
+// x [sum(lens), d] in place. Runs layers [first_layer, first_layer + n_run).
+int Model::encoder_layers(float *x, const std::vector<int> &lens, int left, int right, int first_layer, int n_run) {
+    const int d = d_model, F = ffn_dim, B = (int)lens.size();
+    int M = 0, max_len = 0;
+    std::vector<int> seg_off(B), rk_off(B);
+    std::vector<int> distinct, rk_base;        // distinct lengths and the row offset of their rk block
+    int rk_rows = 0;
+    for (int b = 0; b < B; b++) {
+        seg_off[b] = M; M += lens[b];
+        if (lens[b] > max_len) max_len = lens[b];
+        int j = -1;
+        for (size_t i = 0; i < distinct.size(); i++) if (distinct[i] == lens[b]) j = (int)i;
+        if (j < 0) { distinct.push_back(lens[b]); rk_base.push_back(rk_rows); j = (int)distinct.size() - 1; rk_rows += 2 * lens[b] - 1; }
+        rk_off[b] = rk_base[j];
+    }
+    if (M == 0) return 0;
+    const size_t mark = ws.off;
+    int *meta = ws.get<int>(3 * (size_t)B);
+    if (!meta) return -1;
+    std::vector<int> hmeta(3 * B);
+    for (int b = 0; b < B; b++) { hmeta[b] = seg_off[b]; hmeta[B + b] = lens[b]; hmeta[2 * B + b] = rk_off[b]; }
+    MB_CUDA(cudaMemcpyAsync(meta, hmeta.data(), hmeta.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
+    MB_CUDA(cudaStreamSynchronize(stream));      // hmeta is a stack-lifetime buffer
+    const int *d_off = meta, *d_len = meta + B, *d_rk = meta + 2 * B;
+
+    H16 hA = ws.planes((size_t)M * d), hC = ws.planes((size_t)M * d), hF = ws.planes((size_t)M * F);
+    float *qbuf = ws.get<float>((size_t)M * d);
+    H16 kbuf = ws.planes((size_t)M * d, false), vbuf = ws.planes((size_t)M * d, false);
+    float *h2 = ws.get<float>((size_t)M * 2 * d);
+    float *cbuf = ws.get<float>((size_t)M * d);
+    H16 pe = ws.planes((size_t)rk_rows * d);
+    H16 rk = ws.planes((size_t)rk_rows * d, false);
+    if (!hA.lo || !hC.lo || !hF.lo || !qbuf || !kbuf.hi || !vbuf.hi || !h2 || !cbuf || !pe.lo || !rk.hi) return -1;
+
+    for (size_t i = 0; i < distinct.size(); i++) {
+        H16 p{pe.hi + (size_t)rk_base[i] * d, pe.lo + (size_t)rk_base[i] * d};
+        if (pos_emb(p, distinct[i], d, stream)) return -1;
+        note_launch();
+    }
+    const int pad_left = causal ? conv_k - 1 : (conv_k - 1) / 2;
+    const H16 none{nullptr, nullptr};
+    for (int li = first_layer; li < first_layer + n_run; li++) {
+        const EncLayer &L = layers[li];
+        // half FFN 1 (src/encoder.c:464-482,495-496)
+        if (layer_norm(x, L.ln_ff1_w, L.ln_ff1_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.ff1_w1, epi(OUT_H16, ACT_SILU, 1.f, L.ff1_w1.bias, nullptr, 0, hF, F), M)) return -1;
+        if (gemm(hF, F, L.ff1_w2, epi(OUT_RESID, ACT_NONE, 0.5f, L.ff1_w2.bias, x, d), M)) return -1;
+        // rel-pos MHSA (src/encoder.c:315-410,501-503)
+        if (layer_norm(x, L.ln_att_w, L.ln_att_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.q_w, epi(OUT_F32, ACT_NONE, 1.f, L.q_w.bias, qbuf, d), M)) return -1;
+        if (gemm(hA, d, L.k_w, epi(OUT_H16, ACT_NONE, 1.f, L.k_w.bias, nullptr, 0, kbuf, d), M)) return -1;
+        if (gemm(hA, d, L.v_w, epi(OUT_H16, ACT_NONE, 1.f, L.v_w.bias, nullptr, 0, vbuf, d), M)) return -1;
+        if (gemm(pe, d, L.relk, epi(OUT_H16, ACT_NONE, 1.f, nullptr, nullptr, 0, rk, d), rk_rows)) return -1;
+        AttnArgs at;
+        at.q = qbuf; at.ldq = d; at.k = kbuf.hi; at.v = vbuf.hi; at.rk = rk.hi;
+        at.bias_u = L.bias_u; at.bias_v = L.bias_v; at.ctx_f32 = nullptr; at.ctx_h = hC;
+        at.seg_off = d_off; at.seg_len = d_len; at.rk_off = d_rk;
+        at.batch = B; at.max_len = max_len; at.d = d; at.H = n_heads; at.left = left; at.right = right;
+        if (attention_forward(at, cfg.attn_impl, stream)) return -1;
+        if (gemm(hC, d, L.o_w, epi(OUT_RESID, ACT_NONE, 1.f, L.o_w.bias, x, d), M)) return -1;
+        // conv module (src/encoder.c:413-460,506-508)
+        if (layer_norm(x, L.ln_conv_w, L.ln_conv_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.pw1_w, epi(OUT_F32, ACT_NONE, 1.f, L.pw1_w.bias, h2, 2 * d), M)) return -1;
+        if (L.cnorm_scale) {
+            if (glu_dwconv(h2, L.dw_w, L.dw_b, L.cnorm_scale, L.cnorm_shift, nullptr, hC, d_off, d_len, B, max_len, d,
+                           conv_k, pad_left, stream)) return -1;
+        } else {
+            if (glu_dwconv(h2, L.dw_w, L.dw_b, nullptr, nullptr, cbuf, none, d_off, d_len, B, max_len, d, conv_k,
+                           pad_left, stream)) return -1;
+            if (layer_norm(cbuf, L.cnorm_w, L.cnorm_b, nullptr, hC, M, d, ACT_SILU, stream)) return -1;
+            note_launch();
+        }
+        if (gemm(hC, d, L.pw2_w, epi(OUT_RESID, ACT_NONE, 1.f, L.pw2_w.bias, x, d), M)) return -1;
+        // half FFN 2 + output LayerNorm (src/encoder.c:510-516)
+        if (layer_norm(x, L.ln_ff2_w, L.ln_ff2_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.ff2_w1, epi(OUT_H16, ACT_SILU, 1.f, L.ff2_w1.bias, nullptr, 0, hF, F), M)) return -1;
+        if (gemm(hF, F, L.ff2_w2, epi(OUT_RESID, ACT_NONE, 0.5f, L.ff2_w2.bias, x, d), M)) return -1;
+        if (layer_norm(x, L.ln_out_w, L.ln_out_b, x, none, M, d, ACT_NONE, stream)) return -1;
+        note_launch(7);   // 5 LayerNorms + attention + glu_dwconv (the contractions count themselves)
+    }
+    ws.off = mark;
+    return 0;
+}
+
+// encoder_projector when present, else copy (src/encoder.c:573-590)
+int Model::encoder_post(const float *x, int M, float *out) {
+    if (!has_encproj) {
+        MB_CUDA(cudaMemcpyAsync(out, x, (size_t)M * d_model * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+        return 0;
+    }
+    const size_t mark = ws.off;
+    H16 h = ws.planes((size_t)M * d_model);
+    if (!h.lo) return -1;
+    if (split_to_h16(x, h.hi, h.lo, (size_t)M * d_model, stream)) return -1;
+    note_launch();
+    if (gemm(h, d_model, encproj, epi(OUT_F32, ACT_NONE, 1.f, encproj.bias, out, d_out), M)) return -1;
+    ws.off = mark;
+    return 0;
+}
+
+int Model::log_mel(const float *audio_dev, size_t n, float *feats_dev, int T, int valid) {
+    if (!has_mel) { set_error("log_mel: mel filterbank not set"); return -1; }
+    MelCfg c{cfg.n_mels, cfg.n_fft, cfg.win_length, cfg.hop_length, cfg.preemphasis, cfg.log_zero_guard,
+             cfg.normalize_per_feature};
+    const int rc = log_mel_device(c, audio_dev, n, mel_fb, mel_lo, mel_hi, mel_win, mel_tw, feats_dev, T, valid, stream);
+    if (rc == 0) note_launch(valid > 0 ? (c.normalize && valid > 1 ? 2 : 1) : 0);
+    return rc;
+}
+
+// ---------------------------------------------------------------- decoders
+int Model::decode_ctc(const float *enc_dev, int T, std::vector<int> &tokens, std::vector<int> &frames) {
+    tokens.clear(); frames.clear();
+    if (!has_ctc) { set_error("model has no CTC head"); return -1; }
+    if (T <= 0) return 0;
+    const int V = ctc_vocab, d = d_model;
+    const size_t mark = ws.off;
+    H16 h = ws.planes((size_t)T * d);
+    float *logits = ws.get<float>((size_t)T * V);
+    int *best = ws.get<int>(T);
+    if (!h.lo || !logits || !best) return -1;
+    if (split_to_h16(enc_dev, h.hi, h.lo, (size_t)T * d, stream)) return -1;
+    if (gemm(h, d, ctc_head, epi(OUT_F32, ACT_NONE, 1.f, ctc_head.bias, logits, V), T)) return -1;
+    if (argmax_rows(logits, V, nullptr, T, V, best, stream)) return -1;
+    note_launch(2);
+    std::vector<int> hb(T);
+    MB_CUDA(cudaMemcpyAsync(hb.data(), best, T * sizeof(int), cudaMemcpyDeviceToHost, stream));
+    MB_CUDA(cudaStreamSynchronize(stream));
+    ws.off = mark;
+    // collapse repeats, drop blank = V-1, keep the first frame (src/decoder_ctc.c:43-58)
+    int prev = -1;
+    for (int t = 0; t < T; t++) {
+        if (hb[t] != prev && hb[t] != V - 1) { tokens.push_back(hb[t]); frames.push_back(t); }
+        prev = hb[t];
+    }
+    return 0;
+}
+
+int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std::vector<std::vector<int>> &tokens,
+                         std::vector<std::vector<int>> &frames) {
+    const int Ball = (int)lens.size(), H = pred_hidden, L = pred_layers;
+    tokens.assign(Ball, {}); frames.assign(Ball, {});
+    if (!has_dec) { set_error("model has no transducer decoder"); return -1; }
+    std::vector<int> offs(Ball);
+    for (int b = 0, o = 0; b < Ball; o += lens[b], b++) offs[b] = o;
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+    const int nw = sms * 8;
+    for (int g0 = 0; g0 < Ball; g0 += DEC_MAX_B) {
+        const int B = Ball - g0 < DEC_MAX_B ? Ball - g0 : DEC_MAX_B;
+        int max_len = 0;
+        for (int b = 0; b < B; b++) if (lens[g0 + b] > max_len) max_len = lens[g0 + b];
+        if (max_len == 0) continue;
+        const int cap = max_len * cfg.max_symbols;
+        const size_t mark = ws.off;
+        const size_t nstate = (size_t)L * B * H;
+        float *fz = ws.get<float>(3 * nstate + (size_t)B * H + 2 * (size_t)B * nw);
+        int *iz = ws.get<int>(8 * (size_t)B + 2 * (size_t)B * nw + 2 * (size_t)B * cap + 16);
+        if (!fz || !iz) return -1;
+        MB_CUDA(cudaMemsetAsync(fz, 0, (3 * nstate + (size_t)B * H) * sizeof(float), stream));
+        MB_CUDA(cudaMemsetAsync(iz, 0, (8 * (size_t)B + 16) * sizeof(int), stream));
+        GreedyDev p;
+        memset(&p, 0, sizeof(p));
+        p.emb = emb; p.head_w = head.f32; p.head_b = head_b; p.proj_w = proj_w; p.proj_b = proj_b;
+        for (int l = 0; l < L; l++) { p.w_ih[l] = w_ih[l]; p.w_hh[l] = w_hh[l]; p.b_ih[l] = b_ih[l]; p.b_hh[l] = b_hh[l]; }
+        p.V = vocab; p.ND = cfg.n_durations; p.H = H; p.L = L; p.blank = cfg.blank_id; p.max_symbols = cfg.max_symbols;
+        for (int i = 0; i < cfg.n_durations; i++) p.durations[i] = cfg.durations[i];
+        p.B = B; p.enc = enc_dev;
+        p.h[0] = fz; p.h[1] = fz + nstate; p.c = fz + 2 * nstate; p.g = fz + 3 * nstate;
+        p.cand_v = p.g + (size_t)B * H;
+        int *q = iz;
+        p.flags = q; q += 16;
+        p.t = q; q += B; p.emitted_here = q; q += B; p.n_out = q; q += B; p.last_tok = q; q += B; p.emit = q; q += B;
+        int *d_off = q; q += B; int *d_len = q; q += B; q += B;
+        p.cand_i = q; q += 2 * (size_t)B * nw;
+        p.tokens = q; q += (size_t)B * cap; p.frames = q;
+        p.cap = cap; p.enc_off = d_off; p.enc_len = d_len;
+        p.max_steps = max_len * (cfg.max_symbols + 1) + 8; p.init_state = 1;
+        std::vector<int> hm(2 * B);
+        for (int b = 0; b < B; b++) { hm[b] = offs[g0 + b]; hm[B + b] = lens[g0 + b]; }
+        MB_CUDA(cudaMemcpyAsync(d_off, hm.data(), B * sizeof(int), cudaMemcpyHostToDevice, stream));
+        MB_CUDA(cudaMemcpyAsync(d_len, hm.data() + B, B * sizeof(int), cudaMemcpyHostToDevice, stream));
+        if (greedy_launch(p, stream)) return -1;
+        note_launch();
+        std::vector<int> hn(B), ht((size_t)B * cap), hf((size_t)B * cap);
+        MB_CUDA(cudaMemcpyAsync(hn.data(), p.n_out, B * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        MB_CUDA(cudaMemcpyAsync(ht.data(), p.tokens, ht.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        MB_CUDA(cudaMemcpyAsync(hf.data(), p.frames, hf.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        MB_CUDA(cudaStreamSynchronize(stream));
+        for (int b = 0; b < B; b++) {
+            tokens[g0 + b].assign(ht.begin() + (size_t)b * cap, ht.begin() + (size_t)b * cap + hn[b]);
+            frames[g0 + b].assign(hf.begin() + (size_t)b * cap, hf.begin() + (size_t)b * cap + hn[b]);
+        }
+        ws.off = mark;
+    }
+    return 0;
+}
+
+}  // namespace mb

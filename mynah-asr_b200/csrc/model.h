@@ -1,0 +1,125 @@
+// Device-resident model: weights, workspace arena and the encoder / decoder drivers.
+#pragma once
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/mynah_b200.h"
+#include "kernels.h"
+#include "qweight.h"
+
+namespace mb {
+
+static constexpr int DEC_MAX_LAYERS = 4;    // MYNAH_ASR_MAX_PRED_LAYERS (src/decoder.h:15)
+static constexpr int DEC_MAX_DUR = 16;      // MYNAH_ASR_MAX_DURATIONS
+static constexpr int DEC_MAX_B = 16;        // utterances decoded in lock step per launch
+
+struct HostTensor {
+    int fmt;
+    std::vector<int64_t> shape;
+    const void *data;
+    size_t nelem() const { size_t n = 1; for (auto s : shape) n *= (size_t)s; return n; }
+};
+
+// Bump allocator over one cudaMalloc'd slab; reset at the start of every forward.
+struct Arena {
+    uint8_t *base = nullptr;
+    size_t cap = 0, off = 0;
+    int reserve(size_t bytes);
+    void reset() { off = 0; }
+    void *take(size_t bytes);
+    template <typename T> T *get(size_t n) { return reinterpret_cast<T *>(take(n * sizeof(T))); }
+    H16 planes(size_t n, bool with_lo = true) { H16 h; h.hi = get<__half>(n); h.lo = with_lo ? get<__half>(n) : nullptr; return h; }
+    void release();
+};
+
+struct EncLayer {
+    const float *ln_ff1_w, *ln_ff1_b, *ln_att_w, *ln_att_b, *ln_conv_w, *ln_conv_b, *ln_ff2_w, *ln_ff2_b, *ln_out_w, *ln_out_b;
+    QWeight ff1_w1, ff1_w2, ff2_w1, ff2_w2, q_w, k_w, v_w, o_w, pw1_w, pw2_w, relk;
+    const float *bias_u, *bias_v, *dw_w, *dw_b, *cnorm_w, *cnorm_b, *cnorm_scale, *cnorm_shift;
+};
+
+struct Model {
+    mynah_b200_config cfg;
+    std::map<std::string, HostTensor> host;          // until finalize
+    std::map<std::string, float *> f32;              // small f32 tensors on the device
+    std::vector<void *> owned;                       // every device allocation of the model
+    bool finalized = false;
+    cudaStream_t stream = nullptr;
+    std::mutex mu;                                   // serialises forward calls on the workspace
+    Arena ws;
+    int *status = nullptr;                           // device status word (bounded waits)
+
+    // encoder
+    int d_model = 0, n_layers = 0, n_heads = 0, d_head = 0, ffn_dim = 0, conv_k = 0, d_out = 0, channels = 0;
+    int causal = 0, ss_freq[4] = {0, 0, 0, 0};
+    float xscale = 1.0f;
+    std::vector<EncLayer> layers;
+    const float *conv_in_w = nullptr, *conv_in_b = nullptr, *dw_w[2] = {nullptr, nullptr}, *dw_b[2] = {nullptr, nullptr};
+    QWeight pw[2], ss_lin, encproj;
+    bool has_encproj = false;
+
+    // decoders
+    bool has_ctc = false, has_dec = false;
+    QWeight ctc_head;
+    int ctc_vocab = 0;
+    const float *emb = nullptr, *proj_w = nullptr, *proj_b = nullptr, *head_b = nullptr;
+    const float *w_ih[DEC_MAX_LAYERS], *w_hh[DEC_MAX_LAYERS], *b_ih[DEC_MAX_LAYERS], *b_hh[DEC_MAX_LAYERS];
+    QWeight head;
+    int vocab = 0, pred_hidden = 0, pred_layers = 0;
+
+    // mel
+    std::vector<float> mel_fb_host, window_host;
+    float *mel_fb = nullptr;
+    int *mel_lo = nullptr, *mel_hi = nullptr;
+    double *mel_win = nullptr, *mel_tw = nullptr;
+    bool has_mel = false;
+
+    ~Model();
+    void *dev_alloc(size_t bytes);
+    float *upload_f32(const float *src, size_t n);
+    int upload_weight(QWeight &w, int fmt, const void *data, const float *scales, int n, int k, bool want_planes,
+                      bool want_f32, const int *col_perm = nullptr);
+    int check_status(const char *where);
+
+    // drivers (device pointers in / out, all on `stream`)
+    int gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep, int M);
+    int subsample_item(const float *feats_dev, int t_mel, float *x_out, int *t_out);
+    int encoder_layers(float *x, const std::vector<int> &lens, int left, int right, int first_layer, int n_run);
+    int encoder_post(const float *x, int M, float *out);
+    int decode_ctc(const float *enc_dev, int T, std::vector<int> &tokens, std::vector<int> &frames);
+    int decode_greedy(const float *enc_dev, const std::vector<int> &lens, std::vector<std::vector<int>> &tokens,
+                      std::vector<std::vector<int>> &frames);
+    int log_mel(const float *audio_dev, size_t n, float *feats_dev, int T, int valid);
+    static int sub_len(int n, bool causal) { return (n + (causal ? 3 : 2) - 3) / 2 + 1; }
+    int enc_len(int t_mel) const { int t = t_mel; for (int i = 0; i < 3; i++) t = sub_len(t, causal); return t; }
+};
+
+// Everything the lock-step greedy kernel needs (decoder.cu).
+struct GreedyDev {
+    // model
+    const float *emb, *head_w, *head_b, *proj_w, *proj_b;
+    const float *w_ih[DEC_MAX_LAYERS], *w_hh[DEC_MAX_LAYERS], *b_ih[DEC_MAX_LAYERS], *b_hh[DEC_MAX_LAYERS];
+    int V, ND, H, L, blank, max_symbols;
+    int durations[DEC_MAX_DUR];
+    // batch
+    int B;
+    const float *enc;            // packed [sum T, H]
+    const int *enc_off, *enc_len;
+    // state
+    float *h[2], *c;             // h[parity][L][B][H], c[L][B][H]
+    float *g;                    // [B][H]
+    int *t, *emitted_here, *n_out, *last_tok, *emit;
+    int *tokens, *frames, cap;
+    // scratch
+    float *cand_v;               // [B][2][nwarps]  (token / duration candidates)
+    int *cand_i;
+    int *flags;                  // [2][2] {any_emit, all_done} by step parity, [4] final h parity
+    int max_steps, init_state;
+};
+
+int greedy_launch(const GreedyDev &p, cudaStream_t st);
+void note_launch(int n = 1);
+
+}  // namespace mb

@@ -1,0 +1,20 @@
+// A weight matrix [n, k] (PyTorch linear layout) resident in HBM — the device
+// counterpart of the reference's mynah_asr_qmat (src/qmat.h:39-47).
+#pragma once
+#include "common.cuh"
+
+namespace mb {
+
+struct QWeight {
+    int fmt = 0;                // FMT_* (kernels.h)
+    int n = 0, k = 0;
+    uint8_t *raw = nullptr;     // stored blocks exactly as given (padded by 64 bytes); small-M kernels stream these
+    size_t raw_bytes = 0;
+    float *scales = nullptr;    // native formats: [n] or [n, k/32]
+    __half *hi = nullptr;       // decoded operand planes [n, k] for the tensor-core contraction
+    __half *lo = nullptr;
+    float *f32 = nullptr;       // decoded f32 copy (only where a kernel wants f32 weights)
+    float *bias = nullptr;      // optional [n]
+};
+
+}  // namespace mb

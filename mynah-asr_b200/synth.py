@@ -162,6 +162,7 @@ class ModelConfig:
     wtype: str = "q8_0"           # ggml type of the allow-listed linears
     wtype_out: str = ""           # optional second type for the output projections (mixed K-quant)
     use_bias: bool = False
+    blank_bias: float = 0.0       # added to the blank logit so greedy streams mix blanks and tokens
     normalize: bool = True        # per_feature mel normalisation (Parakeet); NA for Nemotron
     left: int = -1
     right: int = -1
@@ -303,7 +304,9 @@ def make_model(cfg: ModelConfig, seed: int = 0, weight_std: float = 0.02):
             gt = GGML_Q8_0
         T["joint.head.weight"] = Tensor("joint.head.weight", gt, (V + ND, H), QUANTIZERS[gt](w)) if gt != GGML_F32 \
             else Tensor("joint.head.weight", GGML_F32, (V + ND, H), w)
-        f32t("joint.head.bias", np.zeros(V + ND))
+        hb = np.zeros(V + ND, np.float32)
+        hb[V - 1] = cfg.blank_bias
+        f32t("joint.head.bias", hb)
     return T
 
 

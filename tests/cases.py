@@ -1,0 +1,30 @@
+"""Small model shapes shared by the parity tests and the golden-fixture generator."""
+
+TINY = {
+    # Parakeet-style offline CTC, Q8_0, dk = 32 (plain attention kernel)
+    "ctc_q8": dict(d_model=128, n_layers=2, n_heads=4, ffn_dim=256, n_mels=80, decoder="ctc", vocab=65,
+                   wtype="q8_0"),
+    # Parakeet-TDT-style, Q4_0, dk = 64 (tiled attention kernel), 2-layer LSTM, durations 0..4
+    "tdt_q4": dict(d_model=256, n_layers=2, n_heads=4, ffn_dim=512, n_mels=128, decoder="tdt", vocab=97,
+                   pred_hidden=64, pred_layers=2, durations=(0, 1, 2, 3, 4), wtype="q4_0", blank_bias=1.0),
+    # Nemotron-style causal RNNT with LayerNorm conv norm, mixed Q4_K / Q6_K, dk = 128
+    "rnnt_kq": dict(d_model=256, n_layers=2, n_heads=2, ffn_dim=512, n_mels=128, decoder="rnnt", vocab=65,
+                    pred_hidden=64, pred_layers=1, wtype="q4_k", wtype_out="q6_k", causal=True, normalize=False,
+                    blank_bias=2.0, max_symbols=3),
+    # biases everywhere (use_bias checkpoints, e.g. parakeet-110m)
+    "ctc_bias": dict(d_model=128, n_layers=1, n_heads=2, ffn_dim=256, n_mels=80, decoder="ctc", vocab=33,
+                     wtype="q8_0", use_bias=True),
+}
+
+
+def build(synth, name, seed=1):
+    cfg = synth.config(name, **TINY[name])
+    return cfg, synth.make_model(cfg, seed=seed)
+
+
+def device_model(pkg, synth, cfg, tensors, **over):
+    kw = dict(n_mels=cfg.n_mels, mel_fb=synth.mel_filterbank(cfg.n_mels), window=synth.hann_window(),
+              causal=int(cfg.causal), normalize=cfg.normalize, left=cfg.left, right=cfg.right, blank=cfg.vocab - 1,
+              max_symbols=cfg.max_symbols, durations=tuple(cfg.durations))
+    kw.update(over)
+    return pkg.Model(tensors, **kw)

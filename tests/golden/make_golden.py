@@ -1,0 +1,85 @@
+"""Generates tests/golden/*.npz by running the UNMODIFIED reference
+(oracle/_ref/libmynah_ref.so, built by oracle/Makefile from the reference sources)
+on seeded synthetic models and audio. Run in a container that has the reference:
+
+    make -C oracle && python tests/golden/make_golden.py
+
+The fixtures pin both the numpy oracle (tests/test_oracle_pin.py) and the CUDA path
+(tests/test_golden_gpu.py) on machines where the reference itself is absent.
+Inputs are regenerated from seeds by the tests; only reference OUTPUTS are stored.
+"""
+import os
+import sys
+import tempfile
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+from conftest import load_package  # noqa: E402
+
+load_package()
+import mynah_asr_b200.synth as synth  # noqa: E402
+
+import cases  # noqa: E402
+from oracle import model_io, ref_binding as R  # noqa: E402
+
+AUDIO_SECONDS = {"ctc_q8": 2.5, "tdt_q4": 3.0, "rnnt_kq": 2.0, "ctc_bias": 1.5}
+
+
+def pipeline(name):
+    cfg, tensors = cases.build(synth, name)
+    d = tempfile.mkdtemp()
+    wp, mp = model_io.write_reference_files(d, cfg, tensors, synth)
+    rm = R.RefModel(wp, mp, n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
+                    max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), causal=int(cfg.causal))
+    audio = synth.synth_audio(AUDIO_SECONDS[name], seed=7)
+    feats, valid = rm.log_mel(audio)
+    out = {"valid": np.int32(valid), "feats": feats}
+    out["subsampling"] = rm.subsampling(feats[:valid])
+    pe = rm.pos_emb(out["subsampling"].shape[0])
+    out["layer0"] = rm.encoder_layer(0, out["subsampling"], pe)
+    out["enc_raw"] = rm.encoder_forward(feats[:valid], raw=True)
+    out["enc"] = rm.encoder_forward(feats[:valid])
+    out["enc_lim"] = rm.encoder_forward(feats[:valid], left=8, right=1, raw=True)
+    # a second, shorter utterance for the packed-batch path
+    audio2 = synth.synth_audio(AUDIO_SECONDS[name] * 0.6, seed=8)
+    f2, v2 = rm.log_mel(audio2)
+    b = rm.encoder_forward_batch([feats[:valid], f2[:v2]])
+    out["batch0"], out["batch1"] = b[0], b[1]
+    if cfg.decoder == "ctc":
+        t, f = rm.ctc_decode(out["enc_raw"])
+    else:
+        t, f = rm.greedy_decode(out["enc"], cfg.max_symbols)
+    out["tokens"], out["frames"] = np.array(t, np.int32), np.array(f, np.int32)
+    rm.close()
+    np.savez_compressed(os.path.join(HERE, f"ref_{name}.npz"), **out)
+    print(name, {k: getattr(v, "shape", v) for k, v in out.items()}, "tokens", len(t), "distinct", len(set(t)))
+
+
+def qmat():
+    """mynah_asr_qmat_mul on weights quantised by the reference's own load-time
+    quantiser, T = 1, 4 (int8-activation dots) and 48 (dequant + sgemm): the cases
+    of the reference's tests/test_qmat.c."""
+    rng = np.random.default_rng(42)
+    out = {}
+    for n, k in ((96, 256), (40, 1024)):
+        w = rng.uniform(-1, 1, (n, k)).astype(np.float32)
+        out[f"w_{n}x{k}"] = w
+        for T in (1, 4, 48):
+            x = rng.uniform(-1, 1, (T, k)).astype(np.float32)
+            out[f"x_{n}x{k}_T{T}"] = x
+            for q, qn in ((0, "f32"), (1, "q8"), (2, "q4")):
+                out[f"y_{n}x{k}_T{T}_{qn}"] = R.qmat_mul(w, q, x)
+    np.savez_compressed(os.path.join(HERE, "ref_qmat.npz"), **out)
+    print("qmat", len(out), "arrays")
+
+
+if __name__ == "__main__":
+    assert R.available(), "build oracle/_ref first: make -C oracle"
+    for name in cases.TINY:
+        pipeline(name)
+    qmat()
