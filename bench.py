@@ -1,0 +1,353 @@
+"""Benchmark of the mynah-asr hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload cfg1] [--batch 16] [--seconds 60] [--mode strict|fast]
+
+A step is one pass of the whole path (log-mel -> subsampling -> FastConformer stack ->
+greedy TDT decode) over one batch of synthetic utterances. The default workload is the
+Parakeet-TDT-0.6B-shaped Q4_0 model on 16 x 60 s of synthetic audio per GPU (weak
+scaling: every rank decodes its own 16 utterances against a full weight replica;
+nothing crosses GPUs but the final timing reduction).
+
+Prints ONE JSON line (rank 0): metric audio-sec/sec, `value` with inputs resident in
+HBM, `e2e` through the public call with host buffers (H2D of the audio and D2H of the
+token ids inside the timed region), `roofline` for the contraction kernel (tensor
+pipe), `cpu_baseline` = the reference's own CPU path timed on this host.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import pickle
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+CACHE = os.path.join(tempfile.gettempdir(), "mynah_b200_bench_cache")
+METRIC, UNIT = "audio-sec/sec (1/RTF)", "audio-s/s"
+
+
+def load_package():
+    if "mynah_asr_b200" in sys.modules:
+        return sys.modules["mynah_asr_b200"]
+    pkg_dir = os.path.join(ROOT, "mynah-asr_b200")
+    spec = importlib.util.spec_from_file_location("mynah_asr_b200", os.path.join(pkg_dir, "__init__.py"),
+                                                  submodule_search_locations=[pkg_dir])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["mynah_asr_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def shard(n_items: int, rank: int, world: int):
+    """Contiguous, balanced split of item indices over ranks (utterances are independent)."""
+    base, extra = divmod(n_items, world)
+    lo = rank * base + min(rank, extra)
+    return list(range(lo, lo + base + (1 if rank < extra else 0)))
+
+
+def workload_config(synth, name: str):
+    # blank_bias keeps the greedy stream a realistic mix of blanks and tokens
+    return synth.config(name, blank_bias=3.0) if name in ("cfg1", "cfg2", "cfg3") else synth.config(name)
+
+
+def cached_model(synth, name: str, rank: int, barrier):
+    """Synthetic weights are generated once per box (rank 0) and shared through a file."""
+    os.makedirs(CACHE, exist_ok=True)
+    path = os.path.join(CACHE, f"{name}_seed0.pkl")
+    cfg = workload_config(synth, name)
+    if rank == 0 and not os.path.exists(path):
+        tensors = synth.make_model(cfg, seed=0)
+        with open(path + ".tmp", "wb") as f:
+            pickle.dump({k: (t.ggml_type, t.shape, t.raw) for k, t in tensors.items()}, f, protocol=4)
+        os.replace(path + ".tmp", path)
+    barrier()
+    with open(path, "rb") as f:
+        raw = pickle.load(f)
+    return cfg, {k: synth.Tensor(k, *v) for k, v in raw.items()}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = os.path.join(tempfile.gettempdir(), f"mynah_b200_clocks_{os.getpid()}.csv")
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.proc.wait()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in open(self.path):
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 8:
+                continue
+            try:
+                sm.append(float(p[0])); mx.append(float(p[1])); power.append(float(p[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, p[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.unlink(self.path)
+        # under load = the upper half of the samples (idle gaps between steps read low)
+        sm_sorted = sorted(sm)
+        load = sm_sorted[len(sm_sorted) // 2:] if sm_sorted else []
+        return {"sm_mhz": statistics.median(load) if load else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_reference(args, rank, world):
+    """--impl reference: the reference's own CPU implementation of the path on this
+    host's cores, on a bounded sample of the same workload (one utterance per step)."""
+    if rank != 0:
+        return
+    pkg = load_package()
+    import mynah_asr_b200.synth as synth
+    from oracle import model_io, mynah_oracle as O, ref_binding as R
+    cfg, tensors = cached_model(synth, args.workload, 0, lambda: None)
+    cores = os.cpu_count() or 1
+    audio = synth.synth_audio(args.seconds, seed=100)
+    fb, win = synth.mel_filterbank(cfg.n_mels), synth.hann_window()
+    if R.available():
+        kind = "reference"
+        d = os.path.join(CACHE, f"{args.workload}_ref")
+        if not os.path.exists(os.path.join(d, "model.safetensors")):
+            model_io.write_reference_files(d, cfg, tensors, synth)
+        rm = R.RefModel(os.path.join(d, "model.safetensors"), os.path.join(d, "mel_filters.safetensors"),
+                        n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
+                        max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), causal=int(cfg.causal))
+
+        def step():
+            feats, valid = rm.log_mel(audio)
+            enc = rm.encoder_forward(feats[:valid], cfg.left, cfg.right)
+            return rm.greedy_decode(enc, cfg.max_symbols)
+    else:
+        kind = "port"
+        M = model_io.oracle_model(cfg, tensors)
+
+        def step():
+            feats, valid = O.log_mel(audio, fb, win, normalize_per_feature=cfg.normalize)
+            enc = O.encoder_forward(M, feats[:valid], cfg.left, cfg.right)
+            return O.greedy_decode(M["dec"], enc)
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = time.perf_counter() - t0
+    value = args.seconds * args.steps / dt
+    sample = f"1 utterance x {args.seconds:g} s per step (of the {args.batch} x {args.seconds:g} s batch)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_desc(args, cfg),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }))
+
+
+def workload_desc(args, cfg):
+    return {"workload": f"{args.workload}: Parakeet-TDT-0.6B-shaped, {cfg.n_layers} layers d={cfg.d_model} "
+                        f"ffn={cfg.ffn_dim}, {cfg.wtype.upper()} weights, TDT greedy, "
+                        f"{args.batch} x {args.seconds:g} s per GPU",
+            "batch_per_gpu": args.batch, "audio_seconds": args.seconds, "numerics": getattr(args, "mode", "strict"),
+            "l2": "per-step working set (activations + weights, >1 GB) exceeds the 126 MB L2"}
+
+
+def cpu_baseline(args, cfg, tensors, synth):
+    """The reference's CPU path on one utterance of the workload (bounded sample)."""
+    from oracle import model_io, ref_binding as R
+    if not R.available():
+        return {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+                "sample": "oracle/_ref not built on this box"}
+    d = os.path.join(CACHE, f"{args.workload}_ref")
+    if not os.path.exists(os.path.join(d, "model.safetensors")):
+        model_io.write_reference_files(d, cfg, tensors, synth)
+    rm = R.RefModel(os.path.join(d, "model.safetensors"), os.path.join(d, "mel_filters.safetensors"),
+                    n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
+                    max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), causal=int(cfg.causal))
+    audio = synth.synth_audio(args.seconds, seed=100)
+    times = []
+    for i in range(2):           # first pass warms the page cache / BLAS threads
+        t0 = time.perf_counter()
+        feats, valid = rm.log_mel(audio)
+        enc = rm.encoder_forward(feats[:valid], cfg.left, cfg.right)
+        toks = rm.greedy_decode(enc, cfg.max_symbols)
+        times.append(time.perf_counter() - t0)
+    rm.close()
+    return {"value": args.seconds / min(times), "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+            "sample": f"1 utterance x {args.seconds:g} s, best of 2 (the GPU step is {args.batch} of these)",
+            "tokens": len(toks[0])}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg1")
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--seconds", type=float, default=60.0)
+    ap.add_argument("--mode", default="strict", choices=["strict", "fast"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if args.steps == 5 and args.warmup == 3:
+            args.steps, args.warmup = 2, 1
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    pkg = load_package()
+    import mynah_asr_b200.synth as synth
+    torch.cuda.set_device(local)
+    if pkg.lib().mynah_b200_select_device(local) < 0:
+        raise SystemExit("device selection failed")
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cfg, tensors = cached_model(synth, args.workload, rank, barrier)
+    model = pkg.Model(tensors, n_mels=cfg.n_mels, mel_fb=synth.mel_filterbank(cfg.n_mels),
+                      window=synth.hann_window(), causal=int(cfg.causal), normalize=cfg.normalize, left=cfg.left,
+                      right=cfg.right, blank=cfg.vocab - 1, max_symbols=cfg.max_symbols,
+                      durations=tuple(cfg.durations), strict=args.mode == "strict")
+    # this rank's utterances: global item ids shard over ranks (weak scaling: batch per GPU fixed)
+    items = shard(args.batch * world, rank, world)
+    n = int(round(args.seconds * 16000))
+    pinned = torch.empty((len(items), n), dtype=torch.float32).pin_memory()
+    for i, it in enumerate(items):
+        pinned[i].copy_(torch.from_numpy(synth.synth_audio(args.seconds, seed=100 + it)))
+    audio = [pinned[i].numpy() for i in range(len(items))]
+    audio_s = args.seconds * len(items)
+    stream = torch.cuda.ExternalStream(model.stream())
+
+    # ---- value: inputs resident in HBM
+    bh = model.batch_upload(audio)
+    for _ in range(args.warmup):
+        model.batch_run(bh)
+    clocks = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        clocks.start()
+    pkg.launch_count(reset=True)
+    model.profile_begin()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        model.batch_run(bh)
+    e1.record(stream)
+    e1.synchronize()
+    barrier()
+    launches = pkg.launch_count()
+    prof = model.profile_end()
+    ms = e0.elapsed_time(e1)
+    clk = clocks.stop() if rank == 0 else None
+    resident_tokens = model.batch_fetch(bh, len(items))
+    model.batch_free(bh)
+
+    # ---- e2e: the public call with host (pinned) buffers, copies inside the timed region
+    for _ in range(min(args.warmup, 2)):
+        model.transcribe_batch(audio)
+    barrier()
+    t0 = time.perf_counter()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(args.steps):
+        res = model.transcribe_batch(audio)
+    f1.record(stream)
+    f1.synchronize()
+    e2e_ms = max(f0.elapsed_time(f1), (time.perf_counter() - t0) * 1e3)
+    barrier()
+    assert [r[0] for r in res] == [r[0] for r in resident_tokens], "resident and e2e paths disagree"
+    h2d = sum(a.nbytes for a in audio)
+    d2h = sum(8 * len(r[0]) for r in res)
+
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max, e2e_max = t.tolist()
+    total_audio = audio_s * world
+
+    if rank == 0:
+        import json as _json
+        peaks = {}
+        try:
+            peaks = _json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak_tf = peaks.get("bf16_tflops_sustained")
+        peak_src = "measured (MEASURED_PEAKS.json bf16_tflops_sustained: kernel timed inside a long step)"
+        if not peak_tf:
+            peak_tf, peak_src = 1590.0, "fallback 1.59 PFLOP/s (MEASURED_PEAKS.json absent)"
+        g = prof["gemm"]
+        achieved = g["flops"] / (g["ms"] * 1e-3) / 1e12 if g["ms"] > 0 else None
+        line = {
+            "metric": METRIC, "value": total_audio * args.steps / (ms_max * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None,
+            "dtype": "f16 x3 split (f32 accumulate)" if args.mode == "strict" else "f16 (f32 accumulate)",
+            "data": "synthetic", "config": workload_desc(args, cfg),
+            "e2e": {"value": total_audio * args.steps / (e2e_max * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": launches,
+            "roofline": {"kernel": "gemm_tc_kernel (tcgen05 contraction)", "bound": "tensor",
+                         "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": achieved / peak_tf if achieved else None, "peak_source": peak_src,
+                         "traffic": None, "launches": g["launches"], "kernel_ms_per_step": g["ms"] / args.steps,
+                         "flops_per_step": g["flops"] / args.steps,
+                         "mma_flops_multiplier": 3 if args.mode == "strict" else 1},
+            "breakdown_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
+            "tokens_per_step": sum(len(r[0]) for r in res),
+            "clocks": clk,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args, cfg, tensors, synth)
+        else:
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+                                    "sample": "timed at N=1 only"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -156,6 +156,12 @@ void mynah_b200_batch_free(mynah_b200_batch *h);
 long long mynah_b200_launch_count(int reset);
 /* CUDA stream the model runs on (a cudaStream_t), for event timing by the caller */
 void *mynah_b200_model_stream(mynah_b200_model *m);
+/* Per-category device timing of a model's launches (CUDA events recorded on the model's stream
+ * around each launch): categories 0 contraction (tcgen05), 1 attention, 2 element-wise,
+ * 3 subsampling convs, 4 log-mel, 5 greedy decoder. profile_end returns, per category, the summed
+ * milliseconds, the algorithmic flops (contractions: 2*M*N*K) and the number of launches. */
+void mynah_b200_profile_begin(mynah_b200_model *m);
+int mynah_b200_profile_end(mynah_b200_model *m, double *ms, double *flops, long long *launches, int ncat);
 /* Times one large-T contraction with device-resident operands: returns the average milliseconds
  * of `iters` launches of out[T,n] = x[T,k] W^T (CUDA events on the launching stream). */
 double mynah_b200_qmat_time(const mynah_b200_qmat *m, int T, int flags, int iters);

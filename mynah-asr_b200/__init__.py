@@ -68,6 +68,8 @@ def lib():
     L.mynah_b200_qmat_dequant.argtypes = [vp, c_fp]
     L.mynah_b200_qmat_time.restype = C.c_double
     L.mynah_b200_qmat_time.argtypes = [vp, ci, ci, ci]
+    L.mynah_b200_profile_begin.argtypes = [vp]
+    L.mynah_b200_profile_end.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_longlong), ci]
     L.mynah_b200_model_new.restype = vp
     L.mynah_b200_model_new.argtypes = [C.POINTER(Config)]
     L.mynah_b200_model_add_tensor.argtypes = [vp, C.c_char_p, ci, C.POINTER(C.c_int64), ci, vp]
@@ -244,6 +246,17 @@ class Model:
 
     def stream(self):
         return lib().mynah_b200_model_stream(self.h)
+
+    PROFILE_CATEGORIES = ("gemm", "attention", "elementwise", "subsampling", "mel", "decode")
+
+    def profile_begin(self):
+        lib().mynah_b200_profile_begin(self.h)
+
+    def profile_end(self):
+        n = len(self.PROFILE_CATEGORIES)
+        ms, fl, ln = (C.c_double * n)(), (C.c_double * n)(), (C.c_longlong * n)()
+        _check(lib().mynah_b200_profile_end(self.h, ms, fl, ln, n), "profile_end")
+        return {c: {"ms": ms[i], "flops": fl[i], "launches": ln[i]} for i, c in enumerate(self.PROFILE_CATEGORIES)}
 
     def log_mel(self, audio):
         audio = np.ascontiguousarray(audio, np.float32)

@@ -708,6 +708,31 @@ int mynah_b200_gemm_wt(const float *x, const float *w, float *out, int T, int n,
     return rc;
 }
 
+void mynah_b200_profile_begin(mynah_b200_model *h) {
+    if (!h) return;
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    m.prof_on = true; m.prof_used = 0;
+    for (int i = 0; i < Model::PROF_NCAT; i++) { m.prof_flops[i] = 0; m.prof_bytes[i] = 0; m.prof_launches[i] = 0; }
+}
+
+int mynah_b200_profile_end(mynah_b200_model *h, double *ms, double *flops, long long *launches, int ncat) {
+    if (!h) { set_error("profile_end: null model"); return -1; }
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    m.prof_on = false;
+    MB_CUDA(cudaStreamSynchronize(m.stream));
+    for (int i = 0; i < ncat; i++) { ms[i] = 0; flops[i] = 0; launches[i] = 0; }
+    for (size_t i = 0; i < m.prof_used; i++) {
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, m.prof_spans[i].a, m.prof_spans[i].b) == cudaSuccess && m.prof_spans[i].cat < ncat)
+            ms[m.prof_spans[i].cat] += t;
+    }
+    for (int i = 0; i < ncat && i < Model::PROF_NCAT; i++) { flops[i] = m.prof_flops[i]; launches[i] = m.prof_launches[i]; }
+    m.prof_used = 0;
+    return 0;
+}
+
 double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iters) {
     if (!q || T <= 0 || iters <= 0) { set_error("qmat_time: bad argument"); return -1.0; }
     const QWeight &w = q->w;

@@ -37,6 +37,7 @@ void Arena::release() { if (base) cudaFree(base); base = nullptr; cap = off = 0;
 // -------------------------------------------------------------------- model
 Model::~Model() {
     for (void *p : owned) cudaFree(p);
+    for (auto &s : prof_spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     ws.release();
     if (stream) cudaStreamDestroy(stream);
 }
@@ -96,6 +97,22 @@ int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *sca
     return rc;
 }
 
+int Model::prof_begin_span(int cat) {
+    if (!prof_on) return -1;
+    if (prof_used == prof_spans.size()) {
+        ProfSpan s;
+        if (cudaEventCreate(&s.a) != cudaSuccess || cudaEventCreate(&s.b) != cudaSuccess) return -1;
+        prof_spans.push_back(s);
+    }
+    ProfSpan &s = prof_spans[prof_used];
+    s.cat = cat;
+    cudaEventRecord(s.a, stream);
+    return (int)prof_used++;
+}
+void Model::prof_end_span(int idx) {
+    if (idx >= 0) cudaEventRecord(prof_spans[idx].b, stream);
+}
+
 int Model::check_status(const char *where) {
     int st = 0;
     MB_CUDA(cudaMemcpyAsync(&st, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
@@ -111,7 +128,10 @@ int Model::check_status(const char *where) {
 int Model::gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep, int M) {
     if (!w.hi) { set_error("contraction on a weight without operand planes"); return -1; }
     GemmOperand A{a.hi, a.lo, lda}, B{w.hi, w.lo, w.k};
+    const int sp = prof_begin_span(PROF_GEMM);
     const int rc = gemm_tc(A, B, ep, M, w.n, w.k, cfg.strict ? 3 : 1, status, stream);
+    prof_end_span(sp);
+    if (sp >= 0) { prof_flops[PROF_GEMM] += 2.0 * M * (double)w.n * w.k; prof_launches[PROF_GEMM]++; }
     if (rc == 0) note_launch();
     return rc;
 }
@@ -212,7 +232,11 @@ int Model::encoder_layers(float *x, const std::vector<int> &lens, int left, int 
         at.bias_u = L.bias_u; at.bias_v = L.bias_v; at.ctx_f32 = nullptr; at.ctx_h = hC;
         at.seg_off = d_off; at.seg_len = d_len; at.rk_off = d_rk;
         at.batch = B; at.max_len = max_len; at.d = d; at.H = n_heads; at.left = left; at.right = right;
-        if (attention_forward(at, cfg.attn_impl, stream)) return -1;
+        { const int sp = prof_begin_span(PROF_ATTN);
+          const int rc = attention_forward(at, cfg.attn_impl, stream);
+          prof_end_span(sp);
+          if (sp >= 0) prof_launches[PROF_ATTN]++;
+          if (rc) return -1; }
         if (gemm(hC, d, L.o_w, epi(OUT_RESID, ACT_NONE, 1.f, L.o_w.bias, x, d), M)) return -1;
         // conv module (src/encoder.c:413-460,506-508)
         if (layer_norm(x, L.ln_conv_w, L.ln_conv_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
@@ -258,7 +282,10 @@ int Model::log_mel(const float *audio_dev, size_t n, float *feats_dev, int T, in
     if (!has_mel) { set_error("log_mel: mel filterbank not set"); return -1; }
     MelCfg c{cfg.n_mels, cfg.n_fft, cfg.win_length, cfg.hop_length, cfg.preemphasis, cfg.log_zero_guard,
              cfg.normalize_per_feature};
+    const int sp = prof_begin_span(PROF_MEL);
     const int rc = log_mel_device(c, audio_dev, n, mel_fb, mel_lo, mel_hi, mel_win, mel_tw, feats_dev, T, valid, stream);
+    prof_end_span(sp);
+    if (sp >= 0) prof_launches[PROF_MEL]++;
     if (rc == 0) note_launch(valid > 0 ? (c.normalize && valid > 1 ? 2 : 1) : 0);
     return rc;
 }
@@ -335,7 +362,11 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
         for (int b = 0; b < B; b++) { hm[b] = offs[g0 + b]; hm[B + b] = lens[g0 + b]; }
         MB_CUDA(cudaMemcpyAsync(d_off, hm.data(), B * sizeof(int), cudaMemcpyHostToDevice, stream));
         MB_CUDA(cudaMemcpyAsync(d_len, hm.data() + B, B * sizeof(int), cudaMemcpyHostToDevice, stream));
-        if (greedy_launch(p, stream)) return -1;
+        { const int sp = prof_begin_span(PROF_DECODE);
+          const int rc = greedy_launch(p, stream);
+          prof_end_span(sp);
+          if (sp >= 0) prof_launches[PROF_DECODE]++;
+          if (rc) return -1; }
         note_launch();
         std::vector<int> hn(B), ht((size_t)B * cap), hf((size_t)B * cap);
         MB_CUDA(cudaMemcpyAsync(hn.data(), p.n_out, B * sizeof(int), cudaMemcpyDeviceToHost, stream));

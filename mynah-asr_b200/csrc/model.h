@@ -51,6 +51,17 @@ struct Model {
     Arena ws;
     int *status = nullptr;                           // device status word (bounded waits)
 
+    // optional per-category device timing (CUDA events on `stream` around launches)
+    enum { PROF_GEMM = 0, PROF_ATTN, PROF_ELEMWISE, PROF_SUBSAMPLING, PROF_MEL, PROF_DECODE, PROF_NCAT };
+    struct ProfSpan { cudaEvent_t a, b; int cat; };
+    bool prof_on = false;
+    std::vector<ProfSpan> prof_spans;
+    size_t prof_used = 0;
+    double prof_flops[PROF_NCAT] = {0}, prof_bytes[PROF_NCAT] = {0};
+    long long prof_launches[PROF_NCAT] = {0};
+    int prof_begin_span(int cat);                    // returns span index or -1
+    void prof_end_span(int idx);
+
     // encoder
     int d_model = 0, n_layers = 0, n_heads = 0, d_head = 0, ffn_dim = 0, conv_k = 0, d_out = 0, channels = 0;
     int causal = 0, ss_freq[4] = {0, 0, 0, 0};
