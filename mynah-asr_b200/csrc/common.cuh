@@ -36,9 +36,12 @@ static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 // Device status word codes written by kernels whose bounded waits ran out.
 enum { ST_OK = 0, ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA = 2, ST_TIMEOUT_EPILOGUE = 3 };
 
-// An activation matrix stored as two fp16 planes: value = hi + lo (22 significant
-// bits). GEMM operands are always read in this form so that the tensor cores can
-// reproduce f32-grade products with three fp16 MMAs (hi*hi + lo*hi + hi*lo).
+// A matrix stored as two fp16 planes: value = hi + lo * 2^-11 (22 significant bits).
+// The residual is kept pre-scaled by 2^11 so that it has the magnitude of hi and never
+// falls into the fp16 subnormal range. GEMM operands are always read in this form so
+// that the tensor cores can reproduce f32-grade products with three fp16 MMAs:
+// hi*hi into one accumulator, lo*hi + hi*lo into a second one that the epilogue adds
+// back scaled by 2^-11.
 struct H16 {
     __half *hi;
     __half *lo;
@@ -50,9 +53,11 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
 }
 
+static constexpr float H16_LO_SCALE = 2048.0f;          // 2^11
+static constexpr float H16_LO_INV = 1.0f / 2048.0f;
 __device__ __forceinline__ void split_h16(float v, __half &hi, __half &lo) {
     hi = __float2half_rn(v);
-    lo = __float2half_rn(v - __half2float(hi));
+    lo = __float2half_rn((v - __half2float(hi)) * H16_LO_SCALE);
 }
 
 // Stable sigmoid: never exponentiates a positive argument (the reference's

@@ -39,7 +39,7 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmEpilogue &ep, float 
     for (int j = 0; j < 32; j++) {
         float x = v[j];
         if (ep.bias && j < nvalid) x += ep.bias[nb + j];
-        if (ep.act == ACT_SILU) x = silu_f(x);
+        if (ep.act == ACT_SILU) x = x * __frcp_rn(1.0f + __expf(-x));   // exp(-x) -> inf gives x * 0
         else if (ep.act == ACT_RELU) x = fmaxf(x, 0.0f);
         v[j] = x;
     }

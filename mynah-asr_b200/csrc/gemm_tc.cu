@@ -7,12 +7,16 @@
 //
 //   * TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) stages 128 x 64
 //     A tiles and BN x 64 B tiles into a shared-memory ring guarded by mbarriers;
-//   * one elected thread issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) into a
-//     TMEM accumulator; with NTERMS=3 every k-step issues hi*hi + lo*hi + hi*lo so
-//     the product carries ~22 significant bits per operand (f32-grade parity with
-//     the reference's sgemm), with NTERMS=1 only hi*hi (fast mode);
-//   * four epilogue warps read the accumulator with tcgen05.ld and apply the fused
-//     tail: + bias, SiLU / ReLU, then either store f32, accumulate into the residual
+//   * one elected thread issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) into TMEM
+//     accumulators; with NTERMS=3 every k-step issues hi*hi into one accumulator and
+//     lo*hi + hi*lo into a second one (the lo planes are pre-scaled by 2^11, the
+//     epilogue adds the second accumulator back times 2^-11), so the product carries
+//     ~22 significant bits per operand (f32-grade parity with the reference's sgemm);
+//     with NTERMS=1 only hi*hi (fast mode);
+//   * the kernel is persistent (one CTA per SM walks the output tiles) and the
+//     accumulators are double-buffered in TMEM, so the epilogue of one tile overlaps
+//     the MMAs of the next; eight epilogue warps read the accumulator with tcgen05.ld
+//     and apply the fused tail: + bias, SiLU / ReLU, then either store f32, accumulate into the residual
 //     stream (x += alpha * y), or store the result as fp16 (hi, lo) planes for the
 //     next contraction.
 //
@@ -25,7 +29,8 @@ namespace mb {
 
 static constexpr int BM = 128;
 static constexpr int BK = 64;
-static constexpr int GEMM_THREADS = 192;
+static constexpr int EPI_WARPS = 8;
+static constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
 static constexpr int SMEM_LIMIT = 232448;  // 227 KB
 
 template <int BN, int NTERMS>
@@ -37,9 +42,15 @@ struct GemmCfg {
     static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2048;
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+    // NTERMS == 3 keeps a second accumulator for the cross terms (lo*hi + hi*lo);
+    // everything is double-buffered so the epilogue of tile i overlaps the MMAs of tile i+1
+    static constexpr int ACC_COLS = NTERMS == 1 ? BN : 2 * BN;
+    static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
+    static_assert(TMEM_COLS <= 512, "TMEM has 512 columns");
 };
 
+// Persistent kernel: one CTA per SM walks the output tiles (n fastest, so the CTAs in
+// flight share a few A row-blocks while B stays L2-resident).
 template <int BN, int NTERMS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant__ CUtensorMap tmA_lo,
@@ -51,19 +62,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     uint8_t *tiles = smem;
     uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
     uint64_t *empty_bar = full_bar + Cfg::STAGES;
-    uint64_t *acc_bar = empty_bar + Cfg::STAGES;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_bar + 1);
+    uint64_t *acc_full = empty_bar + Cfg::STAGES;      // [2] MMA -> epilogue
+    uint64_t *acc_empty = acc_full + 2;                // [2] epilogue -> MMA
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
     const int num_k = K / BK;
+    const int tiles_n = (N + BN - 1) / BN, tiles_m = (M + BM - 1) / BM;
+    const int total = tiles_n * tiles_m;
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmA_hi);
         tma_prefetch_desc(&tmB_hi);
         if (NTERMS > 1) { tma_prefetch_desc(&tmA_lo); tma_prefetch_desc(&tmB_lo); }
         for (int s = 0; s < Cfg::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        mbar_init(acc_bar, 1);
+        for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], EPI_WARPS); }
         mbar_fence_init();
     }
     if (warp == 1) { tc_alloc(tmem_slot, Cfg::TMEM_COLS); tc_relinquish(); }
@@ -74,71 +87,101 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
 
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------- TMA producer
-        int issued = 0;
+        int it = 0;                                    // k-blocks issued so far (ring position)
         bool ok = true;
-        for (int kb = 0; kb < num_k && ok; kb++) {
-            const int s = kb % Cfg::STAGES;
-            const uint32_t ph = (kb / Cfg::STAGES) & 1;
-            if (!mbar_wait(&empty_bar[s], ph ^ 1)) { ok = false; break; }
-            uint8_t *st = tiles + s * Cfg::STAGE_BYTES;
-            mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-            tma_load_2d(st, &tmA_hi, kb * BK, m0, &full_bar[s]);
-            if (NTERMS > 1) tma_load_2d(st + Cfg::A_BYTES, &tmA_lo, kb * BK, m0, &full_bar[s]);
-            uint8_t *bt = st + Cfg::NPLANES * Cfg::A_BYTES;
-            tma_load_2d(bt, &tmB_hi, kb * BK, n0, &full_bar[s]);
-            if (NTERMS > 1) tma_load_2d(bt + Cfg::B_BYTES, &tmB_lo, kb * BK, n0, &full_bar[s]);
-            issued++;
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            for (int kb = 0; kb < num_k; kb++, it++) {
+                const int s = it % Cfg::STAGES;
+                const uint32_t ph = (it / Cfg::STAGES) & 1;
+                if (!mbar_wait(&empty_bar[s], ph ^ 1)) { ok = false; break; }
+                uint8_t *st = tiles + s * Cfg::STAGE_BYTES;
+                mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+                tma_load_2d(st, &tmA_hi, kb * BK, m0, &full_bar[s]);
+                if (NTERMS > 1) tma_load_2d(st + Cfg::A_BYTES, &tmA_lo, kb * BK, m0, &full_bar[s]);
+                uint8_t *bt = st + Cfg::NPLANES * Cfg::A_BYTES;
+                tma_load_2d(bt, &tmB_hi, kb * BK, n0, &full_bar[s]);
+                if (NTERMS > 1) tma_load_2d(bt + Cfg::B_BYTES, &tmB_lo, kb * BK, n0, &full_bar[s]);
+            }
         }
         if (!ok) {
             atomicExch(status, ST_TIMEOUT_PRODUCER);
             // let copies already in flight land before the CTA's shared memory goes away
-            for (int kb = issued > Cfg::STAGES ? issued - Cfg::STAGES : 0; kb < issued; kb++)
-                mbar_wait(&full_bar[kb % Cfg::STAGES], (kb / Cfg::STAGES) & 1);
+            for (int j = it > Cfg::STAGES ? it - Cfg::STAGES : 0; j < it; j++)
+                mbar_wait(&full_bar[j % Cfg::STAGES], (j / Cfg::STAGES) & 1);
         }
     } else if (warp == 1 && lane == 0) {
         // ------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc = umma_idesc_f16(BM, BN);
+        int it = 0, lt = 0;
         bool ok = true;
-        for (int kb = 0; kb < num_k; kb++) {
-            const int s = kb % Cfg::STAGES;
-            const uint32_t ph = (kb / Cfg::STAGES) & 1;
-            if (!mbar_wait(&full_bar[s], ph)) { ok = false; break; }
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, lt++) {
+            const int buf = lt & 1;
+            const uint32_t acc = tmem_base + buf * Cfg::ACC_COLS;
+            // the epilogue must have drained this accumulator (two tiles ago)
+            if (!mbar_wait(&acc_empty[buf], ((lt >> 1) & 1) ^ 1)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t a_hi = smem_u32(tiles + s * Cfg::STAGE_BYTES);
-            const uint32_t a_lo = a_hi + Cfg::A_BYTES;
-            const uint32_t b_hi = a_hi + Cfg::NPLANES * Cfg::A_BYTES;
-            const uint32_t b_lo = b_hi + Cfg::B_BYTES;
+            for (int kb = 0; kb < num_k; kb++, it++) {
+                const int s = it % Cfg::STAGES;
+                const uint32_t ph = (it / Cfg::STAGES) & 1;
+                if (!mbar_wait(&full_bar[s], ph)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t a_hi = smem_u32(tiles + s * Cfg::STAGE_BYTES);
+                const uint32_t a_lo = a_hi + Cfg::A_BYTES;
+                const uint32_t b_hi = a_hi + Cfg::NPLANES * Cfg::A_BYTES;
+                const uint32_t b_lo = b_hi + Cfg::B_BYTES;
 #pragma unroll
-            for (int kk = 0; kk < BK / 16; kk++) {
-                const uint32_t off = kk * 32;   // 16 fp16 = 32 bytes inside the swizzle atom
-                tc_mma_f16(tmem_base, umma_desc_sw128(a_hi + off), umma_desc_sw128(b_hi + off), idesc,
-                           (kb | kk) != 0);
-                if (NTERMS > 1) {
-                    tc_mma_f16(tmem_base, umma_desc_sw128(a_lo + off), umma_desc_sw128(b_hi + off), idesc, 1);
-                    tc_mma_f16(tmem_base, umma_desc_sw128(a_hi + off), umma_desc_sw128(b_lo + off), idesc, 1);
+                for (int kk = 0; kk < BK / 16; kk++) {
+                    const uint32_t off = kk * 32;   // 16 fp16 = 32 bytes inside the swizzle atom
+                    tc_mma_f16(acc, umma_desc_sw128(a_hi + off), umma_desc_sw128(b_hi + off), idesc, (kb | kk) != 0);
+                    if (NTERMS > 1) {
+                        tc_mma_f16(acc + BN, umma_desc_sw128(a_lo + off), umma_desc_sw128(b_hi + off), idesc,
+                                   (kb | kk) != 0);
+                        tc_mma_f16(acc + BN, umma_desc_sw128(a_hi + off), umma_desc_sw128(b_lo + off), idesc, 1);
+                    }
                 }
+                tc_commit(&empty_bar[s]);           // frees the stage once these MMAs have read it
             }
-            tc_commit(&empty_bar[s]);   // frees the stage once these MMAs have read it
+            tc_commit(&acc_full[buf]);              // accumulator complete (or abandoned)
         }
         if (!ok) atomicExch(status, ST_TIMEOUT_MMA);
-        tc_commit(acc_bar);             // accumulator complete (or abandoned)
     } else if (warp >= 2) {
         // -------------------------------------------------------------- epilogue
         const int lg = warp & 3;                       // TMEM lane group this warp may read
+        const int half = (warp - 2) >> 2;              // which half of the tile's columns
         const int row = lg * 32 + lane;
-        const int m = m0 + row;
-        bool ok = mbar_wait(acc_bar, 0);
-        if (!ok) { if (lane == 0) atomicExch(status, ST_TIMEOUT_EPILOGUE); }
-        tc_fence_after();
-        if (ok && num_k > 0) {
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                float v[32];
-                tc_ld32(tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(c * 32), v);
-                tc_wait_ld();
-                const int nb = n0 + c * 32;
-                if (m < M && nb < N) gemm_epilogue_row(ep, v, m, nb, N);
+        int lt = 0;
+        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            const int buf = lt & 1;
+            const uint32_t acc = tmem_base + buf * Cfg::ACC_COLS + ((uint32_t)(lg * 32) << 16);
+            if (!mbar_wait(&acc_full[buf], (lt >> 1) & 1)) {
+                if (lane == 0) atomicExch(status, ST_TIMEOUT_EPILOGUE);
+                break;
             }
+            tc_fence_after();
+            const int m = m0 + row;
+            if (num_k > 0) {
+#pragma unroll 1
+                for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); c++) {
+                    float v[32];
+                    tc_ld32(acc + (uint32_t)(c * 32), v);
+                    if (NTERMS > 1) {
+                        float x[32];
+                        tc_ld32(acc + (uint32_t)(BN + c * 32), x);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; j++) v[j] = fmaf(x[j], H16_LO_INV, v[j]);
+                    } else {
+                        tc_wait_ld();
+                    }
+                    const int nb = n0 + c * 32;
+                    if (m < M && nb < N) gemm_epilogue_row(ep, v, m, nb, N);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
     }
     tc_fence_before();
@@ -201,7 +244,14 @@ static int launch(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue
                                      Cfg::SMEM_BYTES));
         attr_set = true;
     }
-    dim3 grid(cdiv(N, BN), cdiv(M, BM));
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        MB_CUDA(cudaGetDevice(&dev));
+        MB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    const int total = cdiv(N, BN) * cdiv(M, BM);
+    dim3 grid(total < sms ? total : sms);
     gemm_tc_kernel<BN, NTERMS><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, ep, M,
                                                                                N, K, status);
     MB_CUDA(cudaGetLastError());
