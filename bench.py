@@ -341,6 +341,8 @@ def main():
                          "mma_flops_multiplier": 3 if args.mode == "strict" else 1},
             "breakdown_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
             "tokens_per_step": sum(len(r[0]) for r in res),
+            "decoder_clocks": dict(zip(("head_mma", "head_barrier", "select", "lstm", "proj", "steps", "emit_steps", "head_stage"),
+                                       model.decoder_clocks())),
             "clocks": clk,
         }
         if world == 1 and not args.no_cpu_baseline:

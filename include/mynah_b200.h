@@ -162,6 +162,10 @@ void *mynah_b200_model_stream(mynah_b200_model *m);
  * milliseconds, the algorithmic flops (contractions: 2*M*N*K) and the number of launches. */
 void mynah_b200_profile_begin(mynah_b200_model *m);
 int mynah_b200_profile_end(mynah_b200_model *m, double *ms, double *flops, long long *launches, int ncat);
+/* Phase clocks (SM cycles seen by CTA 0) of the last greedy-decoder launch made while profiling was
+ * on: head, head barrier, select + barrier, LSTM layers + barriers, projector + barrier, then the
+ * number of steps and of steps in which some utterance emitted. */
+void mynah_b200_decoder_clocks(mynah_b200_model *m, long long *out8);
 /* Times one large-T contraction with device-resident operands: returns the average milliseconds
  * of `iters` launches of out[T,n] = x[T,k] W^T (CUDA events on the launching stream). */
 double mynah_b200_qmat_time(const mynah_b200_qmat *m, int T, int flags, int iters);

@@ -70,6 +70,7 @@ def lib():
     L.mynah_b200_qmat_time.argtypes = [vp, ci, ci, ci]
     L.mynah_b200_profile_begin.argtypes = [vp]
     L.mynah_b200_profile_end.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_longlong), ci]
+    L.mynah_b200_decoder_clocks.argtypes = [vp, C.POINTER(C.c_longlong)]
     L.mynah_b200_model_new.restype = vp
     L.mynah_b200_model_new.argtypes = [C.POINTER(Config)]
     L.mynah_b200_model_add_tensor.argtypes = [vp, C.c_char_p, ci, C.POINTER(C.c_int64), ci, vp]
@@ -257,6 +258,11 @@ class Model:
         ms, fl, ln = (C.c_double * n)(), (C.c_double * n)(), (C.c_longlong * n)()
         _check(lib().mynah_b200_profile_end(self.h, ms, fl, ln, n), "profile_end")
         return {c: {"ms": ms[i], "flops": fl[i], "launches": ln[i]} for i, c in enumerate(self.PROFILE_CATEGORIES)}
+
+    def decoder_clocks(self):
+        out = (C.c_longlong * 8)()
+        lib().mynah_b200_decoder_clocks(self.h, out)
+        return list(out)
 
     def log_mel(self, audio):
         audio = np.ascontiguousarray(audio, np.float32)

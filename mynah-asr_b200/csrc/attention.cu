@@ -100,6 +100,17 @@ __device__ __forceinline__ uint32_t pack_h2(float x, float y) {
     __half2 h = __floats2half2_rn(x, y);
     return *reinterpret_cast<uint32_t *>(&h);
 }
+__device__ __forceinline__ void ldsm_x4(uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3, const void *p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
+}
+// 16-byte asynchronous global -> shared copy; `valid` false writes zeros without reading.
+__device__ __forceinline__ void cp_async16_zfill(void *dst, const void *src, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(valid ? 16 : 0)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void ldsm_x2_trans(uint32_t &r0, uint32_t &r1, const void *p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_u32(p)));
 }
@@ -165,38 +176,44 @@ attn_tiled_kernel(AttnDev a) {
 
     for (int j0 = (cta_lo / AT_K) * AT_K; j0 < cta_hi; j0 += AT_K) {
         __syncthreads();
-        // ---- stage K, V (64 rows) and the rk window (127 rows) as fp16, 16-byte chunks
+        // ---- stage K and the rk window (group 0), then V (group 1), as asynchronous 16-byte copies:
+        // the score terms start as soon as group 0 has landed, V arrives under them
         constexpr int CPR = DK / 8;                   // 16-byte chunks per row
+        const int pbase = len - 1 + j0 - tq0 - (AT_Q - 1);
         for (int i = threadIdx.x; i < AT_K * CPR; i += 128) {
             const int r = i / CPR, c = (i % CPR) * 8;
-            uint4 kv = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
-            if (j0 + r < len) {
-                kv = *reinterpret_cast<const uint4 *>(a.k + (size_t)(off + j0 + r) * a.d + ho + c);
-                vv = *reinterpret_cast<const uint4 *>(a.v + (size_t)(off + j0 + r) * a.d + ho + c);
-            }
-            *reinterpret_cast<uint4 *>(Ks + r * LD + c) = kv;
-            *reinterpret_cast<uint4 *>(Vs + r * LD + c) = vv;
+            const bool ok = j0 + r < len;
+            cp_async16_zfill(Ks + r * LD + c, a.k + (size_t)(off + (ok ? j0 + r : 0)) * a.d + ho + c, ok);
         }
-        const int pbase = len - 1 + j0 - tq0 - (AT_Q - 1);
         for (int i = threadIdx.x; i < 128 * CPR; i += 128) {
             const int r = i / CPR, c = (i % CPR) * 8, p = pbase + r;
-            uint4 rv = make_uint4(0, 0, 0, 0);
-            if (p >= 0 && p <= 2 * len - 2) rv = *reinterpret_cast<const uint4 *>(rkg + (size_t)p * a.d + ho + c);
-            *reinterpret_cast<uint4 *>(Rs + r * LD + c) = rv;
+            const bool ok = p >= 0 && p <= 2 * len - 2;
+            cp_async16_zfill(Rs + r * LD + c, rkg + (size_t)(ok ? p : 0) * a.d + ho + c, ok);
         }
+        cp_async_commit();
+        for (int i = threadIdx.x; i < AT_K * CPR; i += 128) {
+            const int r = i / CPR, c = (i % CPR) * 8;
+            const bool ok = j0 + r < len;
+            cp_async16_zfill(Vs + r * LD + c, a.v + (size_t)(off + (ok ? j0 + r : 0)) * a.d + ho + c, ok);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
         __syncthreads();
 
         // ---- content term: S = (q+u) K^T, 16 x 64 per warp
         float s[AT_K / 8][4];
 #pragma unroll
         for (int nb = 0; nb < AT_K / 8; nb++) { s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f; }
+        // B fragments by ldmatrix.x4: one load covers two k-steps of an 8-key block
+        const int lrow = lane & 7, lcol = (lane >> 3) * 8;
 #pragma unroll
-        for (int ks = 0; ks < DK / 16; ks++) {
+        for (int ks = 0; ks < DK / 16; ks += 2) {
 #pragma unroll
             for (int nb = 0; nb < AT_K / 8; nb++) {
-                const __half *kp = Ks + (nb * 8 + g) * LD + ks * 16 + 2 * tq;
-                mma16816(s[nb], qu[ks], *reinterpret_cast<const uint32_t *>(kp),
-                         *reinterpret_cast<const uint32_t *>(kp + 8));
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(b0, b1, b2, b3, Ks + (nb * 8 + lrow) * LD + ks * 16 + lcol);
+                mma16816(s[nb], qu[ks], b0, b1);
+                mma16816(s[nb], qu[ks + 1], b2, b3);
             }
         }
         // ---- position term: band of 80 rk rows for this warp, skewed back through BDw
@@ -207,13 +224,14 @@ attn_tiled_kernel(AttnDev a) {
 #pragma unroll
             for (int nb = 0; nb < AT_BDW / 16; nb++) { bd[nb][0] = bd[nb][1] = bd[nb][2] = bd[nb][3] = 0.f; }
 #pragma unroll
-            for (int ks = 0; ks < DK / 16; ks++) {
+            for (int ks = 0; ks < DK / 16; ks += 2) {
 #pragma unroll
                 for (int nb = 0; nb < AT_BDW / 16; nb++) {
-                    const int x = (half * (AT_BDW / 16) + nb) * 8 + g;
-                    const __half *rp = Rs + (rbase + x) * LD + ks * 16 + 2 * tq;
-                    mma16816(bd[nb], qv[ks], *reinterpret_cast<const uint32_t *>(rp),
-                             *reinterpret_cast<const uint32_t *>(rp + 8));
+                    const int x = (half * (AT_BDW / 16) + nb) * 8 + lrow;
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(b0, b1, b2, b3, Rs + (rbase + x) * LD + ks * 16 + lcol);
+                    mma16816(bd[nb], qv[ks], b0, b1);
+                    mma16816(bd[nb], qv[ks + 1], b2, b3);
                 }
             }
 #pragma unroll
@@ -266,6 +284,8 @@ attn_tiled_kernel(AttnDev a) {
 #pragma unroll
         for (int i = 0; i < DK / 8; i++) { o[i][0] *= c0; o[i][1] *= c0; o[i][2] *= c1; o[i][3] *= c1; }
         // ---- O += P V  (B fragments via transposed ldmatrix on row-major V)
+        cp_async_wait<0>();
+        __syncthreads();
 #pragma unroll
         for (int ks = 0; ks < AT_K / 16; ks++) {
 #pragma unroll

@@ -86,6 +86,7 @@ mynah_b200_model *mynah_b200_model_new(const mynah_b200_config *cfg) {
     h->m.status = (int *)h->m.dev_alloc(sizeof(int));
     if (!h->m.status) { delete h; return nullptr; }
     cudaMemset(h->m.status, 0, sizeof(int));
+    cudaDeviceSynchronize();
     return h;
 }
 
@@ -126,6 +127,7 @@ int mynah_b200_model_set_mel(mynah_b200_model *h, const float *mel_fb, const flo
     MB_CUDA(cudaMemcpy(m.mel_hi, hi.data(), nm * sizeof(int), cudaMemcpyHostToDevice));
     MB_CUDA(cudaMemcpy(m.mel_win, win.data(), nf * sizeof(double), cudaMemcpyHostToDevice));
     MB_CUDA(cudaMemcpy(m.mel_tw, tw.data(), nf * sizeof(double), cudaMemcpyHostToDevice));
+    MB_CUDA(cudaDeviceSynchronize());     // these went through the legacy stream; the model's stream does not wait on it
     m.has_mel = true;
     return 0;
 }
@@ -264,22 +266,32 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
     if (const HostTensor *e = find(m, "decoder.embedding.weight")) {
         m.vocab = (int)e->shape[0]; m.pred_hidden = (int)e->shape[1];
         m.emb = f32dev(m, "decoder.embedding.weight", true, &err);
-        m.proj_w = f32dev(m, "decoder.decoder_projector.weight", true, &err);
         m.proj_b = f32dev(m, "decoder.decoder_projector.bias", true, &err);
         m.head_b = f32dev(m, "joint.head.bias", true, &err);
         int n = 0;
+        const int Hh = m.pred_hidden;
         for (; n < DEC_MAX_LAYERS; n++) {
             const std::string s = std::to_string(n);
-            if (!find(m, "decoder.lstm.weight_ih_l" + s)) break;
-            m.w_ih[n] = f32dev(m, "decoder.lstm.weight_ih_l" + s, true, &err);
-            m.w_hh[n] = f32dev(m, "decoder.lstm.weight_hh_l" + s, true, &err);
+            const HostTensor *wi = find(m, "decoder.lstm.weight_ih_l" + s), *wh = find(m, "decoder.lstm.weight_hh_l" + s);
+            if (!wi) break;
+            if (!wh || wi->fmt != FMT_F32 || wh->fmt != FMT_F32 || (int)wi->nelem() != 4 * Hh * Hh || (int)wh->nelem() != 4 * Hh * Hh) {
+                set_error("LSTM layer %d is incomplete or has an unexpected shape", n); return -1;
+            }
             m.b_ih[n] = f32dev(m, "decoder.lstm.bias_ih_l" + s, true, &err);
             m.b_hh[n] = f32dev(m, "decoder.lstm.bias_hh_l" + s, true, &err);
+            // [W_ih | W_hh] side by side so one contraction over [input ; h] gives the gate pre-activations
+            std::vector<float> cat((size_t)4 * Hh * 2 * Hh);
+            for (int r = 0; r < 4 * Hh; r++) {
+                memcpy(&cat[(size_t)r * 2 * Hh], (const float *)wi->data + (size_t)r * Hh, Hh * sizeof(float));
+                memcpy(&cat[(size_t)r * 2 * Hh + Hh], (const float *)wh->data + (size_t)r * Hh, Hh * sizeof(float));
+            }
+            if (m.upload_weight(m.wcat[n], FMT_F32, cat.data(), nullptr, 4 * Hh, 2 * Hh, true, false)) return -1;
         }
         if (err) return -1;
-        if (n == 0 || m.pred_hidden > 1024 || m.pred_hidden % 4) { set_error("unsupported prediction network (layers %d, hidden %d)", n, m.pred_hidden); return -1; }
+        if (n == 0 || m.pred_hidden > 1024 || m.pred_hidden % 32) { set_error("unsupported prediction network (layers %d, hidden %d)", n, m.pred_hidden); return -1; }
         m.pred_layers = n;
-        if (lin(m, m.head, "joint.head.weight", false, true)) return -1;
+        if (lin(m, m.dec_proj, "decoder.decoder_projector.weight", true, false)) return -1;
+        if (lin(m, m.head, "joint.head.weight", true, false)) return -1;
         if (m.head.n != m.vocab + m.cfg.n_durations) { set_error("joint head has %d rows, expected vocab %d + %d durations", m.head.n, m.vocab, m.cfg.n_durations); return -1; }
         if (m.d_out != m.pred_hidden) { set_error("encoder output width %d != prediction hidden %d", m.d_out, m.pred_hidden); return -1; }
         m.has_dec = true;
@@ -519,12 +531,13 @@ void mynah_b200_batch_free(mynah_b200_batch *bt) {
     delete bt;
 }
 
-int mynah_b200_batch_run(mynah_b200_model *h, mynah_b200_batch *bt, int decoder) {
-    if (!h || !bt) { set_error("batch_run: bad argument"); return -1; }
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+// Whole path for one batch. audio_dev: utterances already on the device, or null with
+// audio_host set: then the audio is copied into the workspace arena first (no allocation
+// on the hot path). Caller holds the model lock.
+static int run_batch_locked(Model &m, mynah_b200_batch *bt, const float *const *audio_dev, const float *const *audio_host,
+                            int decoder) {
     const int B = bt->batch, nm = m.cfg.n_mels, hop = m.cfg.hop_length;
-    size_t M = 0, rk = 0, fbytes = 0, ssmax = 0;
+    size_t M = 0, rk = 0, fbytes = 0, ssmax = 0, abytes = 0;
     int max_len = 0;
     std::vector<int> tmel(B), valid(B);
     for (int b = 0; b < B; b++) {
@@ -532,16 +545,28 @@ int mynah_b200_batch_run(mynah_b200_model *h, mynah_b200_batch *bt, int decoder)
         const int t = valid[b] > 0 ? m.enc_len(valid[b]) : 0;
         M += t; rk += 2 * (size_t)t; if (t > max_len) max_len = t;
         fbytes += align_up((size_t)tmel[b] * nm * 4, 256) + 256;
+        abytes += align_up(bt->n_samples[b] * 4, 256) + 256;
         if (valid[b] > 0 && ss_bytes(m, valid[b]) > ssmax) ssmax = ss_bytes(m, valid[b]);
     }
     const size_t decb = decoder == 1 ? M * ((size_t)m.d_model * 4 + (size_t)m.ctc_vocab * 4 + 8) : dec_bytes(m, max_len);
-    if (m.ws.reserve(fbytes + ssmax + enc_bytes(m, M, rk) + M * ((size_t)m.d_model + m.d_out) * 4 + decb + (4 << 20))) return -1;
+    if (m.ws.reserve((audio_host ? abytes : 0) + fbytes + ssmax + enc_bytes(m, M, rk) + M * ((size_t)m.d_model + m.d_out) * 4 +
+                     decb + (4 << 20))) return -1;
     m.ws.reset();
-    std::vector<const float *> fd(B);
+    std::vector<const float *> ad(B), fd(B);
+    for (int b = 0; b < B; b++) {
+        if (audio_host) {
+            float *a = m.ws.get<float>(bt->n_samples[b] ? bt->n_samples[b] : 1);
+            if (!a) return -1;
+            MB_CUDA(cudaMemcpyAsync(a, audio_host[b], bt->n_samples[b] * sizeof(float), cudaMemcpyHostToDevice, m.stream));
+            ad[b] = a;
+        } else {
+            ad[b] = audio_dev[b];
+        }
+    }
     for (int b = 0; b < B; b++) {
         float *f = m.ws.get<float>((size_t)tmel[b] * nm);
         if (!f) return -1;
-        if (m.log_mel(bt->audio[b], bt->n_samples[b], f, tmel[b], valid[b])) return -1;
+        if (m.log_mel(ad[b], bt->n_samples[b], f, tmel[b], valid[b])) return -1;
         fd[b] = f;
     }
     float *x = m.ws.get<float>((M ? M : 1) * m.d_model), *y = m.ws.get<float>((M ? M : 1) * m.d_out);
@@ -560,6 +585,12 @@ int mynah_b200_batch_run(mynah_b200_model *h, mynah_b200_batch *bt, int decoder)
         if (m.decode_greedy(y, lens, bt->tokens, bt->frames)) return -1;
     }
     return m.check_status("batch_run");
+}
+
+int mynah_b200_batch_run(mynah_b200_model *h, mynah_b200_batch *bt, int decoder) {
+    if (!h || !bt) { set_error("batch_run: bad argument"); return -1; }
+    std::lock_guard<std::mutex> lk(h->m.mu);
+    return run_batch_locked(h->m, bt, bt->audio.data(), nullptr, decoder);
 }
 
 int mynah_b200_batch_fetch(mynah_b200_model *h, mynah_b200_batch *bt, int **tokens, int **frames, int *n_tokens) {
@@ -582,11 +613,16 @@ int mynah_b200_batch_fetch(mynah_b200_model *h, mynah_b200_batch *bt, int **toke
 
 int mynah_b200_transcribe_batch(mynah_b200_model *h, const float *const *audio, const size_t *n_samples, int batch,
                                 int decoder, int **tokens, int **frames, int *n_tokens) {
-    mynah_b200_batch *bt = mynah_b200_batch_upload(h, audio, n_samples, batch);
-    if (!bt) return -1;
-    int rc = mynah_b200_batch_run(h, bt, decoder);
-    if (rc == 0) rc = mynah_b200_batch_fetch(h, bt, tokens, frames, n_tokens);
-    mynah_b200_batch_free(bt);
+    if (!h || !h->m.finalized || batch <= 0 || !audio || !n_samples) { set_error("transcribe_batch: bad argument"); return -1; }
+    mynah_b200_batch bt;
+    bt.batch = batch;
+    bt.n_samples.assign(n_samples, n_samples + batch);
+    int rc;
+    {
+        std::lock_guard<std::mutex> lk(h->m.mu);
+        rc = run_batch_locked(h->m, &bt, nullptr, audio, decoder);
+    }
+    if (rc == 0) rc = mynah_b200_batch_fetch(h, &bt, tokens, frames, n_tokens);
     return rc;
 }
 
@@ -603,6 +639,7 @@ mynah_b200_qmat *mynah_b200_qmat_create(int fmt, const void *data, const float *
     if (tmp.upload_weight(q->w, f, data, scales, n, k, planes, false)) { delete q; return nullptr; }
     q->status = (int *)tmp.dev_alloc(sizeof(int));
     cudaMemset(q->status, 0, sizeof(int));
+    cudaDeviceSynchronize();
     q->owned.swap(tmp.owned);
     q->stream = tmp.stream;
     tmp.stream = nullptr;
@@ -674,7 +711,7 @@ int mynah_b200_qmat_block_dots(const mynah_b200_qmat *q, const float *x, int T, 
     MB_CUDA(cudaMalloc(&od, (size_t)T * w.n * 4));
     MB_CUDA(cudaMalloc(&sd, (size_t)T * 4));
     MB_CUDA(cudaMalloc(&dd, nd * 4));
-    MB_CUDA(cudaMemcpy(xd, x, (size_t)T * w.k * 4, cudaMemcpyHostToDevice));
+    MB_CUDA(cudaMemcpyAsync(xd, x, (size_t)T * w.k * 4, cudaMemcpyHostToDevice, q->stream));
     int rc = qgemv_a8(w, xd, od, T, dd, sd, q->stream);
     if (rc == 0) note_launch(2);
     cudaStreamSynchronize(q->stream);
@@ -733,6 +770,10 @@ int mynah_b200_profile_end(mynah_b200_model *h, double *ms, double *flops, long 
     return 0;
 }
 
+void mynah_b200_decoder_clocks(mynah_b200_model *h, long long *out8) {
+    for (int i = 0; i < 8; i++) out8[i] = h ? h->m.dec_dbg[i] : 0;
+}
+
 double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iters) {
     if (!q || T <= 0 || iters <= 0) { set_error("qmat_time: bad argument"); return -1.0; }
     const QWeight &w = q->w;
@@ -740,6 +781,7 @@ double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iter
     __half *hi = nullptr, *lo = nullptr;
     if (cudaMalloc(&x, (size_t)T * w.k * 4) != cudaSuccess || cudaMalloc(&out, (size_t)T * w.n * 4) != cudaSuccess) { set_error("qmat_time: cudaMalloc failed"); return -1.0; }
     cudaMemset(x, 0, (size_t)T * w.k * 4);
+    cudaDeviceSynchronize();
     const bool small = (T <= 16 && w.k <= 8192) || (flags & MYNAH_B200_A8);
     if (!small) {
         if (!w.hi) { set_error("qmat_time: no operand planes"); cudaFree(x); cudaFree(out); return -1.0; }

@@ -9,17 +9,19 @@
 // strictly sequential per utterance, so a batch of up to 16 utterances advances in
 // lock step inside ONE persistent cooperative kernel — no launch or host round trip
 // per step. Every step is a few grid-wide phases separated by grid syncs:
-//   head    logits[b] = head . relu(enc[b][t_b] + g[b]), every warp owning a slice
-//           of the V (+durations) rows and keeping a running first-argmax per b
+//   head    logits[b] = head . relu(enc[b][t_b] + g[b]); a warp owns 16 rows of the
+//           V (+durations) rows for all utterances and emits first-argmax candidates
 //   select  one CTA per utterance merges the candidates and applies the emission
 //           rule: non-blank -> emit, advance by the predicted duration (RNNT: 0),
 //           blank with duration 0 -> 1, max_symbols guard (src/decoder.c:161-176)
-//   lstm    (only if some utterance emitted) one warp per hidden unit computes the
-//           four gate rows of W_ih and W_hh for all emitting utterances and applies
-//           the cell update; layers are separated by a grid sync
+//   lstm    (only if some utterance emitted) a row block is 4 hidden units x 4 gates of
+//           [W_ih | W_hh] against [input ; previous h] of all utterances, then the cell
+//           update; layers are separated by a grid sync
 //   proj    g[b] = decoder_projector(h_last[b])
-// All arithmetic is f32 FMA over the exactly decoded f32 weights, like the
-// reference's sgemv/sgemm path.
+// The matvecs run on the warp-level tensor-core path with the utterances as the N
+// dimension: weights as fp16 (hi, lo) planes (a decoded Q4_0/Q8_0 weight is exact in
+// that form), activations split the same way, three MMAs per k-step, f32 accumulate —
+// f32-grade like the reference's sgemv/sgemm path.
 #include <cooperative_groups.h>
 
 #include "kernels.h"
@@ -63,123 +65,311 @@ int argmax_rows(const float *logits, int ld, const float *bias, int T, int V, in
 
 // ------------------------------------------------------- RNNT / TDT lock-step
 
-__device__ __forceinline__ float dotrow(const float *__restrict__ w, const float *__restrict__ x, int H, int lane) {
-    float s = 0.0f;
-    for (int k = lane * 4; k < H; k += 128) {
-        const float4 a = *reinterpret_cast<const float4 *>(w + k);
-        const float4 b = *reinterpret_cast<const float4 *>(x + k);
-        s += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
-    }
-    return warp_sum(s);
+// ---- tensor-core matvec for a batch of up to 16 utterances ----------------------
+// out[r][b] = sum_k W[r][k] * X[b][k] with W as fp16 (hi, lo) planes streamed from L2 and
+// X as fp16 (hi, lo) planes in shared memory. A warp owns 16 weight rows (the M side
+// of mma.m16n8k16) and the 16 utterances are two N blocks; three MMAs per k-step
+// (hi*hi, lo*hi, hi*lo) give f32-grade products. k is consumed in a permuted order
+// that lets both operands be fetched with 16-byte loads: within a 32-wide chunk lane
+// (g, t) holds k = 8t..8t+7 of its rows, and k-step s uses elements 4s..4s+3 of them —
+// the same assignment on both operands, so the sum is unchanged.
+static constexpr int XPAD = 32;                       // halves of padding per X row (bank spread)
+
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                        uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// One stacked-LSTM layer for the utterances whose emit flag is set (pred_step,
-// src/decoder.c:73-99). Reads h[par], writes h[par^1]; c is updated in place
-// (each (b, unit) has one owner). Non-emitting utterances copy h through.
-__device__ void lstm_layer(const GreedyDev &p, int l, int par, float *xs, int gw, int nw, int lane) {
-    const int H = p.H, B = p.B;
+// Accumulates chunks [c0, c1) of 32 k for rows rowA (fragment rows g) and rowB (g + 8).
+// acc[nb][0..3]: rows g (0,1) and g+8 (2,3) x utterances nb*8 + 2t, +1.
+__device__ __forceinline__ void rowblock_mma(const __half *__restrict__ whi, const __half *__restrict__ wlo, int ldw,
+                                             int rowA, int rowB, int c0, int c1, const __half *xhi,
+                                             const __half *xlo, int xs, int lane, float (&acc)[2][4]) {
+    const int g = lane >> 2, t = lane & 3;
+    float d0[2][4], d1[2][4];
+#pragma unroll
+    for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) { d0[nb][i] = 0.f; d1[nb][i] = 0.f; }
+    const uint4 *pAh = reinterpret_cast<const uint4 *>(whi + (size_t)rowA * ldw + 8 * t);
+    const uint4 *pBh = reinterpret_cast<const uint4 *>(whi + (size_t)rowB * ldw + 8 * t);
+    const uint4 *pAl = reinterpret_cast<const uint4 *>(wlo + (size_t)rowA * ldw + 8 * t);
+    const uint4 *pBl = reinterpret_cast<const uint4 *>(wlo + (size_t)rowB * ldw + 8 * t);
+    const uint4 *x0h = reinterpret_cast<const uint4 *>(xhi + (size_t)g * xs + 8 * t);
+    const uint4 *x1h = reinterpret_cast<const uint4 *>(xhi + (size_t)(g + 8) * xs + 8 * t);
+    const uint4 *x0l = reinterpret_cast<const uint4 *>(xlo + (size_t)g * xs + 8 * t);
+    const uint4 *x1l = reinterpret_cast<const uint4 *>(xlo + (size_t)(g + 8) * xs + 8 * t);
+#pragma unroll 5
+    for (int c = c0; c < c1; c++) {
+        const uint4 ah = __ldg(pAh + c * 4), bh = __ldg(pBh + c * 4);      // 32 halves = 4 uint4 per chunk
+        const uint4 al = __ldg(pAl + c * 4), bl = __ldg(pBl + c * 4);
+        const uint4 u0h = x0h[c * 4], u1h = x1h[c * 4], u0l = x0l[c * 4], u1l = x1l[c * 4];
+        // k-step 0: elements 0..3, k-step 1: elements 4..7
+        mma_f16(d0[0], ah.x, bh.x, ah.y, bh.y, u0h.x, u0h.y);
+        mma_f16(d0[1], ah.x, bh.x, ah.y, bh.y, u1h.x, u1h.y);
+        mma_f16(d1[0], al.x, bl.x, al.y, bl.y, u0h.x, u0h.y);
+        mma_f16(d1[1], al.x, bl.x, al.y, bl.y, u1h.x, u1h.y);
+        mma_f16(d1[0], ah.x, bh.x, ah.y, bh.y, u0l.x, u0l.y);
+        mma_f16(d1[1], ah.x, bh.x, ah.y, bh.y, u1l.x, u1l.y);
+        mma_f16(d0[0], ah.z, bh.z, ah.w, bh.w, u0h.z, u0h.w);
+        mma_f16(d0[1], ah.z, bh.z, ah.w, bh.w, u1h.z, u1h.w);
+        mma_f16(d1[0], al.z, bl.z, al.w, bl.w, u0h.z, u0h.w);
+        mma_f16(d1[1], al.z, bl.z, al.w, bl.w, u1h.z, u1h.w);
+        mma_f16(d1[0], ah.z, bh.z, ah.w, bh.w, u0l.z, u0l.w);
+        mma_f16(d1[1], ah.z, bh.z, ah.w, bh.w, u1l.z, u1l.w);
+    }
+#pragma unroll
+    for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[nb][i] = fmaf(d1[nb][i], H16_LO_INV, d0[nb][i]);
+}
+
+// Writes f32 rows [16][K] (rows >= B zero) as (hi, lo) planes into shared memory.
+// Two passes — every global load of the CTA is issued before the first shared store —
+// so the loads overlap instead of queueing behind stores the compiler cannot prove
+// independent. value4(b, k) returns elements k..k+3 of row b.
+static constexpr int STAGE_NV = 16;                   // float4 per thread: covers K <= 1024
+template <typename F>
+__device__ __forceinline__ void stage_x(__half *xhi, __half *xlo, int xs, int koff, int K, int B, F value4) {
+    const int k4n = K >> 2, n4 = 16 * k4n;
+    float4 v[STAGE_NV];
+#pragma unroll
+    for (int j = 0; j < STAGE_NV; j++) {
+        const int idx = threadIdx.x + j * 256;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < n4) {
+            const int b = idx / k4n, k = (idx - b * k4n) * 4;
+            if (b < B) v[j] = value4(b, k);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < STAGE_NV; j++) {
+        const int idx = threadIdx.x + j * 256;
+        if (idx < n4) {
+            const int b = idx / k4n, k = (idx - b * k4n) * 4;
+            __align__(8) __half h[4], l[4];
+            split_h16(v[j].x, h[0], l[0]); split_h16(v[j].y, h[1], l[1]);
+            split_h16(v[j].z, h[2], l[2]); split_h16(v[j].w, h[3], l[3]);
+            *reinterpret_cast<uint2 *>(xhi + b * xs + koff + k) = *reinterpret_cast<uint2 *>(h);
+            *reinterpret_cast<uint2 *>(xlo + b * xs + koff + k) = *reinterpret_cast<uint2 *>(l);
+        }
+    }
+}
+__device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+
+struct Cand { float v; int i; };
+__device__ __forceinline__ void cand_take(Cand &a, float v, int i) {
+    if (v > a.v || (v == a.v && i < a.i)) { a.v = v; a.i = i; }
+}
+
+// One stacked-LSTM layer (pred_step, src/decoder.c:73-99) for all utterances. A row
+// block is 4 units x 4 gates (i, f, g, o); k = [input ; previous h] is split over
+// NSL warps and reduced through shared memory. Reads h[par], writes h[par^1]; c in
+// place. Utterances that did not emit copy their state through.
+__device__ void lstm_phase(const GreedyDev &p, int l, int par, __half *xhi, __half *xlo, float *red, int lane, int wib) {
+    const int H = p.H, B = p.B, K = 2 * H, xs = K + XPAD;
     const float *hold = p.h[par] + (size_t)l * B * H;
     float *hnew = p.h[par ^ 1] + (size_t)l * B * H;
     float *cc = p.c + (size_t)l * B * H;
-    for (int idx = gw; idx < H * B; idx += nw) {
-        const int b = idx / H, i = idx % H;
-        if (!p.emit[b]) { if (lane == 0) hnew[(size_t)b * H + i] = hold[(size_t)b * H + i]; continue; }
-        const float *x = l == 0 ? p.emb + (size_t)p.last_tok[b] * H : p.h[par ^ 1] + ((size_t)(l - 1) * B + b) * H;
-        const float *hp = hold + (size_t)b * H;
-        float z[4];
+    const float *xin = l == 0 ? nullptr : p.h[par ^ 1] + (size_t)(l - 1) * B * H;
+    stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) { return ld4(l == 0 ? p.emb + (size_t)p.last_tok[b] * H + k : xin + (size_t)b * H + k); });
+    stage_x(xhi, xlo, xs, H, H, B, [&](int b, int k) { return ld4(hold + (size_t)b * H + k); });
+    __syncthreads();
+    constexpr int NSL = 4;
+    const int nrb = H / 4, chunks = K / 32, per = (chunks + NSL - 1) / NSL;
+    const int g = lane >> 2, t = lane & 3;
+    for (int base = blockIdx.x * 8; base < nrb * NSL; base += gridDim.x * 8) {
+        const int task = base + wib, rb = task / NSL, sl = task % NSL;
+        const bool on = task < nrb * NSL;
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        if (on) {
+            // fragment row lr -> gate lr/4, unit rb*4 + lr%4
+            const int rowA = (g >> 2) * H + rb * 4 + (g & 3), rowB = (2 + (g >> 2)) * H + rb * 4 + (g & 3);
+            const int c0 = sl * per, c1 = (sl + 1) * per < chunks ? (sl + 1) * per : chunks;
+            rowblock_mma(p.wcat_hi[l], p.wcat_lo[l], K, rowA, rowB, c0, c1, xhi, xlo, xs, lane, acc);
+        }
 #pragma unroll
-        for (int gte = 0; gte < 4; gte++) {
-            const size_t r = (size_t)(gte * H + i);
-            z[gte] = p.b_ih[l][r] + p.b_hh[l][r] + dotrow(p.w_ih[l] + r * H, x, H, lane) +
-                     dotrow(p.w_hh[l] + r * H, hp, H, lane);
+        for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) red[(wib * 32 + lane) * 8 + nb * 4 + i] = acc[nb][i];
+        __syncthreads();
+        if (on && sl == 0) {
+            float z[2][4];
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float s = 0.f;
+                    for (int q = 0; q < NSL; q++) s += red[((wib + q) * 32 + lane) * 8 + nb * 4 + i];
+                    z[nb][i] = s;
+                }
+            // lane g<4 holds gates i (rows g) and g (rows g+8) of unit g; lane g+4 holds f and o
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const float za = z[nb][e], zb = z[nb][2 + e];
+                    const float oa = __shfl_xor_sync(0xffffffffu, za, 16), ob = __shfl_xor_sync(0xffffffffu, zb, 16);
+                    if (g < 4) {
+                        const int unit = rb * 4 + g, b = nb * 8 + 2 * t + e;
+                        if (b < B) {
+                            const size_t o = (size_t)b * H + unit;
+                            if (p.emit[b]) {
+                                const float zi = za + p.b_ih[l][unit] + p.b_hh[l][unit];
+                                const float zf = oa + p.b_ih[l][H + unit] + p.b_hh[l][H + unit];
+                                const float zg = zb + p.b_ih[l][2 * H + unit] + p.b_hh[l][2 * H + unit];
+                                const float zo = ob + p.b_ih[l][3 * H + unit] + p.b_hh[l][3 * H + unit];
+                                const float cn = sigmoid_stable(zf) * cc[o] + sigmoid_stable(zi) * tanhf(zg);
+                                cc[o] = cn;
+                                hnew[o] = sigmoid_stable(zo) * tanhf(cn);
+                            } else {
+                                hnew[o] = hold[o];
+                            }
+                        }
+                    }
+                }
         }
-        if (lane == 0) {
-            const float ig = sigmoid_stable(z[0]), fg = sigmoid_stable(z[1]);
-            const float gg = tanhf(z[2]), og = sigmoid_stable(z[3]);
-            const float cn = fg * cc[(size_t)b * H + i] + ig * gg;
-            cc[(size_t)b * H + i] = cn;
-            hnew[(size_t)b * H + i] = og * tanhf(cn);
-        }
+        __syncthreads();
     }
-    (void)xs;
+}
+
+// g[b] = proj_b + proj_w . h_last[b] for the utterances that emitted.
+__device__ void proj_phase(const GreedyDev &p, int par, bool all, __half *xhi, __half *xlo, float *red, int lane, int wib) {
+    const int H = p.H, B = p.B, xs = 2 * H + XPAD;
+    const float *hl = p.h[par] + (size_t)(p.L - 1) * B * H;
+    stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) { return ld4(hl + (size_t)b * H + k); });
+    __syncthreads();
+    constexpr int NSL = 4;
+    const int nrb = (H + 15) / 16, chunks = H / 32, per = (chunks + NSL - 1) / NSL;
+    const int g = lane >> 2, t = lane & 3;
+    for (int base = blockIdx.x * 8; base < nrb * NSL; base += gridDim.x * 8) {
+        const int task = base + wib, rb = task / NSL, sl = task % NSL;
+        const bool on = task < nrb * NSL;
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        if (on) {
+            const int rA = rb * 16 + g, rB = rA + 8;
+            const int c0 = sl * per, c1 = (sl + 1) * per < chunks ? (sl + 1) * per : chunks;
+            rowblock_mma(p.proj_hi, p.proj_lo, H, rA < H ? rA : H - 1, rB < H ? rB : H - 1, c0, c1, xhi, xlo, xs, lane, acc);
+        }
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) red[(wib * 32 + lane) * 8 + nb * 4 + i] = acc[nb][i];
+        __syncthreads();
+        if (on && sl == 0) {
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float s = 0.f;
+                    for (int q = 0; q < NSL; q++) s += red[((wib + q) * 32 + lane) * 8 + nb * 4 + i];
+                    const int r = rb * 16 + g + (i >> 1) * 8, b = nb * 8 + 2 * t + (i & 1);
+                    if (r < H && b < B && (all || p.emit[b])) p.g[(size_t)b * H + r] = s + p.proj_b[r];
+                }
+        }
+        __syncthreads();
+    }
 }
 
 __global__ void __launch_bounds__(256, 1)
 greedy_kernel(GreedyDev p) {
     cg::grid_group grid = cg::this_grid();
-    extern __shared__ float joint[];                 // [B][H]
-    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
-    const int nw = gridDim.x * 8, gw = blockIdx.x * 8 + wib;
+    extern __shared__ __align__(16) uint8_t dsm[];
     const int H = p.H, B = p.B, V = p.V, VL = p.V + p.ND;
+    const int xs = 2 * H + XPAD;
+    __half *xhi = reinterpret_cast<__half *>(dsm);
+    __half *xlo = xhi + 16 * xs;
+    float *red = reinterpret_cast<float *>(xlo + 16 * xs);          // [8 warps][32 lanes][8]
+    const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
+    const int g = lane >> 2, t = lane & 3;
     int par = 0;
 
     if (p.init_state) {
         // SOS = blank on a zero state (src/decoder.c:151): run the prediction net once
         if (blockIdx.x == 0 && threadIdx.x < B) { p.emit[threadIdx.x] = 1; p.last_tok[threadIdx.x] = p.blank; }
         grid.sync();
-        for (int l = 0; l < p.L; l++) { lstm_layer(p, l, par, joint, gw, nw, lane); grid.sync(); }
+        for (int l = 0; l < p.L; l++) { lstm_phase(p, l, par, xhi, xlo, red, lane, wib); grid.sync(); }
         par ^= 1;
-        for (int i = gw; i < B * H; i += nw) {
-            const int b = i / H, u = i % H;
-            const float v = p.proj_b[u] + dotrow(p.proj_w + (size_t)u * H, p.h[par] + ((size_t)(p.L - 1) * B + b) * H, H, lane);
-            if (lane == 0) p.g[i] = v;
-        }
+        proj_phase(p, par, true, xhi, xlo, red, lane, wib);
         grid.sync();
     }
 
+    constexpr int NSL = 2;
+    const int nrb = (VL + 15) / 16, chunks = H / 32, per = (chunks + NSL - 1) / NSL;
+    // optional phase timers (clock64 of CTA 0): head, sync, select+sync, lstm+syncs, proj+sync, steps, emit steps
+    const bool timing = p.dbg != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
+    long long tq = timing ? clock64() : 0;
+#define PHASE_MARK(slot) do { if (timing) { const long long n_ = clock64(); p.dbg[slot] += n_ - tq; tq = n_; } } while (0)
     for (int step = 0; step < p.max_steps; step++) {
-        // ---- head: joint = relu(enc[t] + g), logits, running first-argmax per warp
-        for (int i = threadIdx.x; i < B * H; i += blockDim.x) {
-            const int b = i / H, u = i % H;
+        // ---- head: joint = relu(enc[t] + g) -> logits -> first-argmax candidates per row block
+        stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) {
             const int tb = p.t[b];
-            joint[i] = tb < p.enc_len[b] ? fmaxf(p.enc[(size_t)(p.enc_off[b] + tb) * H + u] + p.g[i], 0.0f) : 0.0f;
-        }
+            if (tb >= p.enc_len[b]) return make_float4(0.f, 0.f, 0.f, 0.f);
+            const float4 e = ld4(p.enc + (size_t)(p.enc_off[b] + tb) * H + k), gg = ld4(p.g + (size_t)b * H + k);
+            return make_float4(fmaxf(e.x + gg.x, 0.f), fmaxf(e.y + gg.y, 0.f), fmaxf(e.z + gg.z, 0.f), fmaxf(e.w + gg.w, 0.f));
+        });
         __syncthreads();
-        float bvt[DEC_MAX_B], bvd[DEC_MAX_B];
-        int bit[DEC_MAX_B], bid[DEC_MAX_B];
-#pragma unroll
-        for (int b = 0; b < DEC_MAX_B; b++) { bvt[b] = bvd[b] = -3.0e38f; bit[b] = bid[b] = 0x7fffffff; }
-        for (int r = gw; r < VL; r += nw) {
-            const float *wr = p.head_w + (size_t)r * H;
-            const float hb = p.head_b[r];
-            const bool is_dur = r >= V;
-#pragma unroll
-            for (int b = 0; b < DEC_MAX_B; b++) {
-                if (b < B) {
-                    const float v = dotrow(wr, joint + b * H, H, lane) + hb;
-                    // rows ascend within a warp, so ">" keeps the first maximum
-                    if (is_dur) { if (v > bvd[b]) { bvd[b] = v; bid[b] = r; } }
-                    else { if (v > bvt[b]) { bvt[b] = v; bit[b] = r; } }
-                }
+        PHASE_MARK(7);
+        for (int base = blockIdx.x * 8; base < nrb * NSL; base += gridDim.x * 8) {
+            const int task = base + wib, rb = task / NSL, sl = task % NSL;
+            const bool on = task < nrb * NSL;
+            float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            const int rA = rb * 16 + g, rB = rA + 8;
+            if (on) {
+                const int c0 = sl * per, c1 = (sl + 1) * per < chunks ? (sl + 1) * per : chunks;
+                rowblock_mma(p.head_hi, p.head_lo, H, rA < VL ? rA : VL - 1, rB < VL ? rB : VL - 1, c0, c1, xhi, xlo, xs, lane, acc);
             }
-        }
-        if (lane == 0) {
 #pragma unroll
-            for (int b = 0; b < DEC_MAX_B; b++) {
-                if (b < B) {
-                    p.cand_v[((size_t)b * 2 + 0) * nw + gw] = bvt[b]; p.cand_i[((size_t)b * 2 + 0) * nw + gw] = bit[b];
-                    p.cand_v[((size_t)b * 2 + 1) * nw + gw] = bvd[b]; p.cand_i[((size_t)b * 2 + 1) * nw + gw] = bid[b];
-                }
+            for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) red[(wib * 32 + lane) * 8 + nb * 4 + i] = acc[nb][i];
+            __syncthreads();
+            if (on && sl == 0) {
+                const float biasA = rA < VL ? p.head_b[rA] : 0.f, biasB = rB < VL ? p.head_b[rB] : 0.f;
+#pragma unroll
+                for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const float va = red[(wib * 32 + lane) * 8 + nb * 4 + e] + red[((wib + 1) * 32 + lane) * 8 + nb * 4 + e] + biasA;
+                        const float vb = red[(wib * 32 + lane) * 8 + nb * 4 + 2 + e] + red[((wib + 1) * 32 + lane) * 8 + nb * 4 + 2 + e] + biasB;
+                        Cand tk{-3.0e38f, 0x7fffffff}, du{-3.0e38f, 0x7fffffff};
+                        if (rA < V) cand_take(tk, va, rA); else if (rA < VL) cand_take(du, va, rA);
+                        if (rB < V) cand_take(tk, vb, rB); else if (rB < VL) cand_take(du, vb, rB);
+                        // reduce over the eight lanes that hold the other rows of this utterance
+#pragma unroll
+                        for (int o = 4; o < 32; o <<= 1) {
+                            cand_take(tk, __shfl_xor_sync(0xffffffffu, tk.v, o), __shfl_xor_sync(0xffffffffu, tk.i, o));
+                            cand_take(du, __shfl_xor_sync(0xffffffffu, du.v, o), __shfl_xor_sync(0xffffffffu, du.i, o));
+                        }
+                        const int b = nb * 8 + 2 * t + e;
+                        if (g == 0 && b < B) {
+                            p.cand_v[((size_t)b * 2 + 0) * nrb + rb] = tk.v; p.cand_i[((size_t)b * 2 + 0) * nrb + rb] = tk.i;
+                            p.cand_v[((size_t)b * 2 + 1) * nrb + rb] = du.v; p.cand_i[((size_t)b * 2 + 1) * nrb + rb] = du.i;
+                        }
+                    }
             }
+            __syncthreads();
         }
         // flags are double-buffered by step parity: a CTA that runs ahead into the next
         // step must not overwrite what a slower CTA is still reading
         int *fl = p.flags + (step & 1) * 2;
         if (blockIdx.x == 0 && threadIdx.x == 0) { fl[0] = 0; fl[1] = 1; }
+        PHASE_MARK(0);
         grid.sync();
+        PHASE_MARK(1);
         // ---- select: CTA b merges candidates and applies the emission rule
         if (blockIdx.x < B) {
             const int b = blockIdx.x;
             __shared__ float sv[2][256];
             __shared__ int si[2][256];
             for (int kind = 0; kind < 2; kind++) {
-                float v = -3.0e38f; int ix = 0x7fffffff;
-                for (int w = threadIdx.x; w < nw; w += blockDim.x) {
-                    const float cv = p.cand_v[((size_t)b * 2 + kind) * nw + w];
-                    const int ci = p.cand_i[((size_t)b * 2 + kind) * nw + w];
-                    if (cv > v || (cv == v && ci < ix)) { v = cv; ix = ci; }
-                }
-                sv[kind][threadIdx.x] = v; si[kind][threadIdx.x] = ix;
+                Cand c{-3.0e38f, 0x7fffffff};
+                for (int w = threadIdx.x; w < nrb; w += blockDim.x)
+                    cand_take(c, p.cand_v[((size_t)b * 2 + kind) * nrb + w], p.cand_i[((size_t)b * 2 + kind) * nrb + w]);
+                sv[kind][threadIdx.x] = c.v; si[kind][threadIdx.x] = c.i;
             }
             __syncthreads();
             for (int o = 128; o > 0; o >>= 1) {
@@ -219,21 +409,21 @@ greedy_kernel(GreedyDev p) {
             }
         }
         grid.sync();
+        PHASE_MARK(2);
         const int any_emit = *reinterpret_cast<volatile int *>(&fl[0]);
         const int all_done = *reinterpret_cast<volatile int *>(&fl[1]);
+        if (timing) { p.dbg[5] += 1; p.dbg[6] += any_emit; }
         if (any_emit) {
-            for (int l = 0; l < p.L; l++) { lstm_layer(p, l, par, joint, gw, nw, lane); grid.sync(); }
+            for (int l = 0; l < p.L; l++) { lstm_phase(p, l, par, xhi, xlo, red, lane, wib); grid.sync(); }
+            PHASE_MARK(3);
             par ^= 1;
-            for (int i = gw; i < B * H; i += nw) {
-                const int b = i / H, u = i % H;
-                if (!p.emit[b]) continue;
-                const float v = p.proj_b[u] + dotrow(p.proj_w + (size_t)u * H, p.h[par] + ((size_t)(p.L - 1) * B + b) * H, H, lane);
-                if (lane == 0) p.g[i] = v;
-            }
+            proj_phase(p, par, false, xhi, xlo, red, lane, wib);
             grid.sync();
+            PHASE_MARK(4);
         }
         if (all_done) break;
     }
+#undef PHASE_MARK
     if (blockIdx.x == 0 && threadIdx.x == 0) p.flags[4] = par;
 }
 
@@ -243,7 +433,7 @@ int greedy_launch(const GreedyDev &p, cudaStream_t st) {
     MB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     MB_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
     if (!coop) { set_error("greedy decode: device lacks cooperative launch"); return -1; }
-    const size_t smem = (size_t)p.B * p.H * sizeof(float);
+    const size_t smem = 2 * 16 * (size_t)(2 * p.H + XPAD) * sizeof(__half) + 8 * 32 * 8 * sizeof(float);
     if (smem > 48 * 1024)
         MB_CUDA(cudaFuncSetAttribute(greedy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int per_sm = 0;

@@ -64,10 +64,11 @@ int layer_norm(const float *x, const float *w, const float *b, float *out_f32, H
 // left; symmetric: (k-1)/2 each side) — src/encoder.c:421-444. One thread per
 // channel, a time tile of TT rows plus the k-1 halo staged in shared memory so every
 // GLU value is computed once.
-static constexpr int DW_TT = 32;
+static constexpr int DW_TT = 64;
 static constexpr int DW_CH = 128;
 static constexpr int DW_KMAX = 32;
 
+template <int KW>      // KW > 0: compile-time kernel width; 0: runtime width up to DW_KMAX
 __global__ void __launch_bounds__(DW_CH)
 glu_dw_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, const float *__restrict__ dw_b,
               const float *__restrict__ scale, const float *__restrict__ shift, float *__restrict__ out,
@@ -91,17 +92,18 @@ glu_dw_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, cons
         g[r * DW_CH + threadIdx.x] = v;
     }
     if (!cok) return;
-    float w[DW_KMAX];
+    constexpr int KU = KW > 0 ? KW : DW_KMAX;
+    float w[KU];
 #pragma unroll
-    for (int j = 0; j < DW_KMAX; j++) w[j] = j < k ? dw_w[(size_t)c * k + j] : 0.0f;
+    for (int j = 0; j < KU; j++) w[j] = j < k ? dw_w[(size_t)c * k + j] : 0.0f;
     const float bias = dw_b ? dw_b[c] : 0.0f;
     const float sc = scale ? scale[c] : 1.0f, sh = scale ? shift[c] : 0.0f;
     const int tend = len - t0 < DW_TT ? len - t0 : DW_TT;
     for (int tt = 0; tt < tend; tt++) {
         float acc = bias;
 #pragma unroll
-        for (int j = 0; j < DW_KMAX; j++)
-            if (j < k) acc += w[j] * g[(tt + j) * DW_CH + threadIdx.x];
+        for (int j = 0; j < KU; j++)
+            if (KW > 0 || j < k) acc += w[j] * g[(tt + j) * DW_CH + threadIdx.x];
         const size_t o = (size_t)(off + t0 + tt) * d + c;
         if (scale) {
             const float y = silu_f(acc * sc + sh);
@@ -121,8 +123,12 @@ int glu_dwconv(const float *h2, const float *dw_w, const float *dw_b, const floa
     if (batch <= 0 || max_len <= 0) return 0;
     if (k > DW_KMAX) { set_error("glu_dwconv: kernel width %d > %d", k, DW_KMAX); return -1; }
     dim3 grid(cdiv(d, DW_CH), cdiv(max_len, DW_TT), batch);
-    glu_dw_kernel<<<grid, DW_CH, 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
-                                          seg_len, d, k, pad_left);
+    if (k == 9)
+        glu_dw_kernel<9><<<grid, DW_CH, 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
+                                                 seg_len, d, k, pad_left);
+    else
+        glu_dw_kernel<0><<<grid, DW_CH, 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
+                                                 seg_len, d, k, pad_left);
     MB_CUDA(cudaGetLastError());
     return 0;
 }

@@ -54,6 +54,8 @@ int attention_forward(const AttnArgs &a, int impl, cudaStream_t st);   // impl 0
 // ---- subsampling.cu
 int conv_in_relu(const float *feats, const float *w, const float *b, float *out, int T, int F, int C, int To, int Fo,
                  int pl, cudaStream_t st);                         // [T,F] -> [To,Fo,C]
+int conv_in_dw_fused(const float *feats, const float *w0, const float *b0, const float *w1, const float *b1, H16 out,
+                     int T, int F, int C, int T1, int F1, int T2, int F2, int pl, cudaStream_t st);   // [T,F] -> planes [T2*F2, C]
 int dwconv3x3_s2(const float *x, const float *w, const float *b, H16 out, int T, int F, int C, int To, int Fo, int pl,
                  cudaStream_t st);                                 // [T,F,C] -> planes [To*Fo, C]
 

@@ -50,7 +50,10 @@ void *Model::dev_alloc(size_t bytes) {
 float *Model::upload_f32(const float *src, size_t n) {
     float *d = (float *)dev_alloc(n * sizeof(float));
     if (!d) return nullptr;
-    if (cudaMemcpy(d, src, n * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) { set_error("H2D copy failed"); return nullptr; }
+    // on the model's stream: it does not synchronise with the legacy default stream, so every
+    // upload is ordered on the stream the kernels that consume it run on
+    if (cudaMemcpyAsync(d, src, n * sizeof(float), cudaMemcpyHostToDevice, stream) != cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess) { set_error("H2D copy failed"); return nullptr; }
     return d;
 }
 
@@ -63,8 +66,9 @@ int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *sca
     if (!w.raw_bytes) { set_error("unknown weight format %d", fmt); return -1; }
     w.raw = (uint8_t *)dev_alloc(w.raw_bytes + 64);          // slack for aligned over-reads
     if (!w.raw) return -1;
-    MB_CUDA(cudaMemcpy(w.raw, data, w.raw_bytes, cudaMemcpyHostToDevice));
-    MB_CUDA(cudaMemset(w.raw + w.raw_bytes, 0, 64));
+    MB_CUDA(cudaMemcpyAsync(w.raw, data, w.raw_bytes, cudaMemcpyHostToDevice, stream));
+    MB_CUDA(cudaMemsetAsync(w.raw + w.raw_bytes, 0, 64, stream));
+    MB_CUDA(cudaStreamSynchronize(stream));
     if (fmt == FMT_MYNAH_Q8 || fmt == FMT_MYNAH_Q4) {
         if (!scales) { set_error("native quantised weight without scales"); return -1; }
         const size_t ns = fmt == FMT_MYNAH_Q8 ? (size_t)n : (size_t)n * (k / 32);
@@ -79,11 +83,12 @@ int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *sca
     if (rc == 0 && col_perm) {
         // column permutation on the host (only the subsampling linear, once at load)
         std::vector<float> a((size_t)n * k), b((size_t)n * k);
-        cudaStreamSynchronize(stream);
-        cudaMemcpy(a.data(), tmp, a.size() * 4, cudaMemcpyDeviceToHost);
+        MB_CUDA(cudaMemcpyAsync(a.data(), tmp, a.size() * 4, cudaMemcpyDeviceToHost, stream));
+        MB_CUDA(cudaStreamSynchronize(stream));
         for (int r = 0; r < n; r++)
             for (int c = 0; c < k; c++) b[(size_t)r * k + c] = a[(size_t)r * k + col_perm[c]];
-        cudaMemcpy(tmp, b.data(), b.size() * 4, cudaMemcpyHostToDevice);
+        MB_CUDA(cudaMemcpyAsync(tmp, b.data(), b.size() * 4, cudaMemcpyHostToDevice, stream));
+        MB_CUDA(cudaStreamSynchronize(stream));
     }
     if (rc == 0 && want_planes) {
         w.hi = (__half *)dev_alloc((size_t)n * k * 2);
@@ -153,20 +158,18 @@ int Model::subsample_item(const float *feats, int t_mel, float *x_out, int *t_ou
     const int T2 = sub_len(T1, causal), F2 = sub_len(F1, causal);
     const int T3 = sub_len(T2, causal), F3 = sub_len(F2, causal);
     const size_t mark = ws.off;
-    float *a0 = ws.get<float>((size_t)T1 * F1 * C);
     H16 p1 = ws.planes((size_t)T2 * F2 * C);
     float *a1 = ws.get<float>((size_t)T2 * F2 * C);
     H16 p2 = ws.planes((size_t)T3 * F3 * C);
     H16 flat = ws.planes((size_t)T3 * F3 * C);
-    if (!a0 || !p1.hi || !p1.lo || !a1 || !p2.hi || !p2.lo || !flat.hi || !flat.lo) return -1;
-    if (conv_in_relu(feats, conv_in_w, conv_in_b, a0, t_mel, F0, C, T1, F1, pl, stream)) return -1;
-    if (dwconv3x3_s2(a0, dw_w[0], dw_b[0], p1, T1, F1, C, T2, F2, pl, stream)) return -1;
+    if (!p1.hi || !p1.lo || !a1 || !p2.hi || !p2.lo || !flat.hi || !flat.lo) return -1;
+    if (conv_in_dw_fused(feats, conv_in_w, conv_in_b, dw_w[0], dw_b[0], p1, t_mel, F0, C, T1, F1, T2, F2, pl, stream)) return -1;
     if (gemm(p1, C, pw[0], epi(OUT_F32, ACT_RELU, 1.f, pw[0].bias, a1, C), T2 * F2)) return -1;
     if (dwconv3x3_s2(a1, dw_w[1], dw_b[1], p2, T2, F2, C, T3, F3, pl, stream)) return -1;
     if (gemm(p2, C, pw[1], epi(OUT_H16, ACT_RELU, 1.f, pw[1].bias, nullptr, 0, flat, C), T3 * F3)) return -1;
     // flat is [T3, F3*C]: the linear's columns were permuted to this order at load
     if (gemm(flat, F3 * C, ss_lin, epi(OUT_F32, ACT_NONE, 1.f, ss_lin.bias, x_out, d_model), T3)) return -1;
-    note_launch(3);
+    note_launch(2);
     if (xscale != 1.0f) { if (scale_inplace(x_out, (size_t)T3 * d_model, xscale, stream)) return -1; note_launch(); }
     ws.off = mark;
     *t_out = T3;
@@ -327,7 +330,8 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
     for (int b = 0, o = 0; b < Ball; o += lens[b], b++) offs[b] = o;
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
-    const int nw = sms * 8;
+    const int nw = (vocab + cfg.n_durations + 15) / 16;     // candidate slots: one per 16-row block of the head
+    (void)sms;
     for (int g0 = 0; g0 < Ball; g0 += DEC_MAX_B) {
         const int B = Ball - g0 < DEC_MAX_B ? Ball - g0 : DEC_MAX_B;
         int max_len = 0;
@@ -343,8 +347,9 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
         MB_CUDA(cudaMemsetAsync(iz, 0, (8 * (size_t)B + 16) * sizeof(int), stream));
         GreedyDev p;
         memset(&p, 0, sizeof(p));
-        p.emb = emb; p.head_w = head.f32; p.head_b = head_b; p.proj_w = proj_w; p.proj_b = proj_b;
-        for (int l = 0; l < L; l++) { p.w_ih[l] = w_ih[l]; p.w_hh[l] = w_hh[l]; p.b_ih[l] = b_ih[l]; p.b_hh[l] = b_hh[l]; }
+        p.emb = emb; p.head_b = head_b; p.proj_b = proj_b;
+        p.head_hi = head.hi; p.head_lo = head.lo; p.proj_hi = dec_proj.hi; p.proj_lo = dec_proj.lo;
+        for (int l = 0; l < L; l++) { p.wcat_hi[l] = wcat[l].hi; p.wcat_lo[l] = wcat[l].lo; p.b_ih[l] = b_ih[l]; p.b_hh[l] = b_hh[l]; }
         p.V = vocab; p.ND = cfg.n_durations; p.H = H; p.L = L; p.blank = cfg.blank_id; p.max_symbols = cfg.max_symbols;
         for (int i = 0; i < cfg.n_durations; i++) p.durations[i] = cfg.durations[i];
         p.B = B; p.enc = enc_dev;
@@ -358,6 +363,9 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
         p.tokens = q; q += (size_t)B * cap; p.frames = q;
         p.cap = cap; p.enc_off = d_off; p.enc_len = d_len;
         p.max_steps = max_len * (cfg.max_symbols + 1) + 8; p.init_state = 1;
+        long long *dbg_dev = nullptr;
+        if (prof_on) { dbg_dev = reinterpret_cast<long long *>(ws.get<long long>(8)); if (dbg_dev) MB_CUDA(cudaMemsetAsync(dbg_dev, 0, 64, stream)); }
+        p.dbg = dbg_dev;
         std::vector<int> hm(2 * B);
         for (int b = 0; b < B; b++) { hm[b] = offs[g0 + b]; hm[B + b] = lens[g0 + b]; }
         MB_CUDA(cudaMemcpyAsync(d_off, hm.data(), B * sizeof(int), cudaMemcpyHostToDevice, stream));
@@ -372,6 +380,7 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
         MB_CUDA(cudaMemcpyAsync(hn.data(), p.n_out, B * sizeof(int), cudaMemcpyDeviceToHost, stream));
         MB_CUDA(cudaMemcpyAsync(ht.data(), p.tokens, ht.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
         MB_CUDA(cudaMemcpyAsync(hf.data(), p.frames, hf.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        if (dbg_dev) MB_CUDA(cudaMemcpyAsync(dec_dbg, dbg_dev, 64, cudaMemcpyDeviceToHost, stream));
         MB_CUDA(cudaStreamSynchronize(stream));
         for (int b = 0; b < B; b++) {
             tokens[g0 + b].assign(ht.begin() + (size_t)b * cap, ht.begin() + (size_t)b * cap + hn[b]);

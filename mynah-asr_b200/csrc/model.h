@@ -55,6 +55,7 @@ struct Model {
     enum { PROF_GEMM = 0, PROF_ATTN, PROF_ELEMWISE, PROF_SUBSAMPLING, PROF_MEL, PROF_DECODE, PROF_NCAT };
     struct ProfSpan { cudaEvent_t a, b; int cat; };
     bool prof_on = false;
+    long long dec_dbg[8] = {0};                      // greedy-decoder phase clocks of the last profiled run
     std::vector<ProfSpan> prof_spans;
     size_t prof_used = 0;
     double prof_flops[PROF_NCAT] = {0}, prof_bytes[PROF_NCAT] = {0};
@@ -75,9 +76,9 @@ struct Model {
     bool has_ctc = false, has_dec = false;
     QWeight ctc_head;
     int ctc_vocab = 0;
-    const float *emb = nullptr, *proj_w = nullptr, *proj_b = nullptr, *head_b = nullptr;
-    const float *w_ih[DEC_MAX_LAYERS], *w_hh[DEC_MAX_LAYERS], *b_ih[DEC_MAX_LAYERS], *b_hh[DEC_MAX_LAYERS];
-    QWeight head;
+    const float *emb = nullptr, *proj_b = nullptr, *head_b = nullptr;
+    const float *b_ih[DEC_MAX_LAYERS], *b_hh[DEC_MAX_LAYERS];
+    QWeight head, dec_proj, wcat[DEC_MAX_LAYERS];    // wcat[l] = [W_ih | W_hh] of LSTM layer l
     int vocab = 0, pred_hidden = 0, pred_layers = 0;
 
     // mel
@@ -110,8 +111,10 @@ struct Model {
 // Everything the lock-step greedy kernel needs (decoder.cu).
 struct GreedyDev {
     // model
-    const float *emb, *head_w, *head_b, *proj_w, *proj_b;
-    const float *w_ih[DEC_MAX_LAYERS], *w_hh[DEC_MAX_LAYERS], *b_ih[DEC_MAX_LAYERS], *b_hh[DEC_MAX_LAYERS];
+    const float *emb, *head_b, *proj_b;
+    const __half *head_hi, *head_lo, *proj_hi, *proj_lo;           // [V+ND, H], [H, H] operand planes
+    const __half *wcat_hi[DEC_MAX_LAYERS], *wcat_lo[DEC_MAX_LAYERS];   // [4H, 2H] = [W_ih | W_hh]
+    const float *b_ih[DEC_MAX_LAYERS], *b_hh[DEC_MAX_LAYERS];
     int V, ND, H, L, blank, max_symbols;
     int durations[DEC_MAX_DUR];
     // batch
@@ -124,10 +127,11 @@ struct GreedyDev {
     int *t, *emitted_here, *n_out, *last_tok, *emit;
     int *tokens, *frames, cap;
     // scratch
-    float *cand_v;               // [B][2][nwarps]  (token / duration candidates)
+    float *cand_v;               // [B][2][row blocks]  (token / duration candidates)
     int *cand_i;
     int *flags;                  // [2][2] {any_emit, all_done} by step parity, [4] final h parity
     int max_steps, init_state;
+    long long *dbg;              // optional [8] phase timers (clock64 ticks of CTA 0), null = off
 };
 
 int greedy_launch(const GreedyDev &p, cudaStream_t st);

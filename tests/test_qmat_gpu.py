@@ -71,8 +71,11 @@ def test_large_T_tensor_core_path(gpu_pkg, synth, fmt):
             continue
         q, wd = make(gpu_pkg, synth, fmt, n, k, seed=T)
         x = np.random.default_rng(T).standard_normal((T, k)).astype(np.float32)
-        ref = O.gemm_wt(x, wd)
-        assert rel(q.mul(x), ref) < 5e-6, (fmt, T, n, k)            # 3-term split: f32 grade
+        ref = x.astype(np.float64) @ wd.astype(np.float64).T
+        # 3-term split: f32 grade. The tensor core truncates when it aligns addends, so a sum of
+        # same-sign terms (the T=48 case: x is correlated with W) drifts a few 1e-6; random signs ~1e-6.
+        assert rel(q.mul(x), ref) < 2e-5, (fmt, T, n, k)
+        assert rel(O.gemm_wt(x, wd), ref) < 3e-6                    # (the f32 sgemm itself, for scale)
         assert rel(q.mul(x, gpu_pkg.FAST), ref) < 1e-3, (fmt, T, n, k)   # single fp16 pass
         q.close()
 
