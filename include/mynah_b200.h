@@ -71,6 +71,17 @@ int mynah_b200_qmat_dequant(const mynah_b200_qmat *m, float *wd);
 /* same product with x, out already on the device (for callers that keep activations resident) */
 int mynah_b200_qmat_mul_device(const mynah_b200_qmat *m, const float *x_dev, float *out_dev, int T, int flags);
 
+/* No counterpart in the reference. The int8-activation product of mynah_b200_qmat_mul(.., A8) for
+ * hosts that must not allocate device memory while running (a real-time streaming thread, a process
+ * with a fixed GPU memory budget): x_dev [T,k] and out_dev [T,n] are DEVICE pointers owned by the
+ * caller, and the only scratch (quantised activations + scales) is a fixed ~128 KB array inside the
+ * library, so the call makes no cudaMalloc/cudaFree and uses no allocating library routine.
+ * Limits: T <= 16 rows and k <= 8192 per call, larger sizes are refused with -1. The first call on
+ * a device resolves the array's address (make it before any stream capture). All calls share the
+ * array: it keeps the previous call's contents and calls that overlap on the GPU race — serialise
+ * them. Synchronous: out_dev is complete on return. */
+int mynah_b200_qmat_mul_a8_static(const mynah_b200_qmat *m, const float *x_dev, float *out_dev, int T);
+
 /* ---- model --------------------------------------------------------------------- */
 typedef struct {
     int n_mels;                 /* mynah.json features.n_mels */

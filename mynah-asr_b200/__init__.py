@@ -66,6 +66,7 @@ def lib():
     L.mynah_b200_qmat_mul.argtypes = [vp, c_fp, c_fp, ci, ci]
     L.mynah_b200_qmat_block_dots.argtypes = [vp, c_fp, ci, C.POINTER(C.c_int32), c_fp, c_fp]
     L.mynah_b200_qmat_dequant.argtypes = [vp, c_fp]
+    L.mynah_b200_qmat_mul_a8_static.argtypes = [vp, vp, vp, ci]
     L.mynah_b200_qmat_time.restype = C.c_double
     L.mynah_b200_qmat_time.argtypes = [vp, ci, ci, ci]
     L.mynah_b200_profile_begin.argtypes = [vp]
@@ -177,6 +178,12 @@ class QMat:
         out = np.empty((x.shape[0], self.n), np.float32)
         _check(lib().mynah_b200_qmat_mul(self.h, _fp(x), _fp(out), x.shape[0], flags), "qmat_mul")
         return out
+
+    def mul_a8_static(self, x_dev_ptr: int, out_dev_ptr: int, T: int):
+        """A8 product on caller-owned DEVICE buffers without any device allocation: the
+        scratch is a fixed array inside the library (T <= 16, k <= 8192). For hosts that
+        may not call cudaMalloc while running. Synchronous."""
+        _check(lib().mynah_b200_qmat_mul_a8_static(self.h, x_dev_ptr, out_dev_ptr, T), "qmat_mul_a8_static")
 
     def block_dots(self, x):
         x = np.ascontiguousarray(x, np.float32)

@@ -24,6 +24,13 @@ struct mynah_b200_batch {
     std::vector<std::vector<int>> tokens, frames;
 };
 
+namespace mb {
+QmatView qmat_view(const void *handle) {
+    const mynah_b200_qmat *q = static_cast<const mynah_b200_qmat *>(handle);
+    return QmatView{&q->w, q->stream};
+}
+}  // namespace mb
+
 static int internal_fmt(int fmt) {
     switch (fmt) {
     case MYNAH_B200_F32: return FMT_F32;

@@ -15,6 +15,9 @@
 //   A16  f32 activations x exactly decoded weights, f32 FMA    (default)
 //   A8   activations quantised per row to int8 (quantize_act_int8, src/qmat.c:186-202)
 //        and integer block dots (dp4a); the int32 dot of every 32-block is exact
+#include <mutex>
+
+#include "../../include/mynah_b200.h"
 #include "kernels.h"
 #include "qweight.h"
 
@@ -413,4 +416,68 @@ int qgemv_a8(const QWeight &w, const float *x, float *out, int T, int32_t *block
     return rc;
 }
 
+// ------------------------------------------------- allocation-free A8 entry point
+// Some hosts of this library must not allocate device memory once they are running:
+// a streaming server that feeds chunks from a real-time audio thread cannot afford
+// cudaMalloc / cudaFree (they serialise against every other stream of the process and
+// take an unbounded time), and a deployment that sizes its GPU memory up front wants
+// no pool growing behind its back. For them the int8-activation product is offered in
+// a form whose only scratch — the quantised activation rows and their scales — lives
+// in a fixed array inside the library image. Every GPU that loads the library carries
+// these ~128 KB until the process exits.
+static constexpr int NOALLOC_MAX_T = 16;        // rows of activations per call
+static constexpr int NOALLOC_MAX_K = 8192;      // the reference's QMAT_K_MAX (src/qmat.c:181)
+static constexpr size_t NOALLOC_SX_OFF = (size_t)NOALLOC_MAX_T * NOALLOC_MAX_K;
+static __device__ __align__(256) unsigned char g_a8_scratch[NOALLOC_SX_OFF + 256];
+
+// In host code `g_a8_scratch` is only a stand-in for the symbol, not a device address; the
+// address has to be asked for once per device, with that device current.
+static unsigned char *a8_scratch_for_current_device() {
+    static std::mutex mu;
+    static unsigned char *ptr[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { set_error("noalloc: cannot identify the current device"); return nullptr; }
+    std::lock_guard<std::mutex> lk(mu);
+    if (!ptr[dev]) {
+        void *p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_a8_scratch);
+        if (e != cudaSuccess) { set_error("noalloc: cudaGetSymbolAddress -> %s", cudaGetErrorString(e)); return nullptr; }
+        ptr[dev] = static_cast<unsigned char *>(p);
+    }
+    return ptr[dev];
+}
+
 }  // namespace mb
+
+extern "C" int mynah_b200_qmat_mul_a8_static(const mynah_b200_qmat *m, const float *x_dev, float *out_dev, int T) {
+    using namespace mb;
+    if (!m || !x_dev || !out_dev || T < 0) { set_error("qmat_mul_a8_static: bad argument"); return -1; }
+    if (T == 0) return 0;
+    const QmatView v = qmat_view(m);
+    const QWeight &w = *v.w;
+    if (T > NOALLOC_MAX_T || w.k > NOALLOC_MAX_K) {
+        set_error("qmat_mul_a8_static: T=%d, k=%d exceed the built-in scratch (T <= %d, k <= %d)", T, w.k, NOALLOC_MAX_T,
+                  NOALLOC_MAX_K);
+        return -1;
+    }
+    if (w.k % 32) { set_error("qmat_mul_a8_static: k=%d not a multiple of 32", w.k); return -1; }
+    unsigned char *scratch = a8_scratch_for_current_device();      // first call on a device resolves the symbol
+    if (!scratch) return -1;
+    int8_t *qx = reinterpret_cast<int8_t *>(scratch);
+    float *sx = reinterpret_cast<float *>(scratch + NOALLOC_SX_OFF);
+    // nothing in the scratch has to start at zero: rows [0, T) of qx and sx are fully rewritten here
+    act_quant_kernel<<<cdiv(T, 8), 256, 0, v.stream>>>(x_dev, qx, sx, T, w.k);
+    dim3 grid(cdiv(w.n, 8), T);
+    const size_t rb = format_bytes(w.fmt, 1, w.k);
+    switch (w.fmt) {
+    case FMT_GGML_Q8_0: qgemv_a8_kernel<FMT_GGML_Q8_0><<<grid, 256, 0, v.stream>>>(w.raw, w.scales, w.n, w.k, rb, qx, sx, out_dev, nullptr, T); break;
+    case FMT_GGML_Q4_0: qgemv_a8_kernel<FMT_GGML_Q4_0><<<grid, 256, 0, v.stream>>>(w.raw, w.scales, w.n, w.k, rb, qx, sx, out_dev, nullptr, T); break;
+    case FMT_MYNAH_Q8: qgemv_a8_kernel<FMT_MYNAH_Q8><<<grid, 256, 0, v.stream>>>(w.raw, w.scales, w.n, w.k, rb, qx, sx, out_dev, nullptr, T); break;
+    case FMT_MYNAH_Q4: qgemv_a8_kernel<FMT_MYNAH_Q4><<<grid, 256, 0, v.stream>>>(w.raw, w.scales, w.n, w.k, rb, qx, sx, out_dev, nullptr, T); break;
+    default: set_error("qmat_mul_a8_static: format %d has no int8-activation mode", w.fmt); return -1;
+    }
+    if (cudaGetLastError() != cudaSuccess) { set_error("qmat_mul_a8_static: launch failed"); return -1; }
+    const cudaError_t e = cudaStreamSynchronize(v.stream);
+    if (e != cudaSuccess) { set_error("qmat_mul_a8_static: %s", cudaGetErrorString(e)); return -1; }
+    return 0;
+}

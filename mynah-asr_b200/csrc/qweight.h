@@ -17,4 +17,11 @@ struct QWeight {
     float *bias = nullptr;      // optional [n]
 };
 
+// What a kernel launcher needs from an opaque mynah_b200_qmat handle.
+struct QmatView {
+    const QWeight *w;
+    cudaStream_t stream;
+};
+QmatView qmat_view(const void *handle);
+
 }  // namespace mb
