@@ -101,8 +101,7 @@ typedef struct {
 void mynah_b200_config_default(mynah_b200_config *cfg);
 
 typedef struct mynah_b200_model mynah_b200_model;
-/* replaces the weight side of mynah_asr_load_quant (src/mynah_asr.c:167-350) and what the survey
- * calls model_attach: tensors are handed over by their HF-verbatim names exactly as
+/* replaces the weight side of mynah_asr_load_quant (src/mynah_asr.c:167-350): tensors are handed over by their HF-verbatim names exactly as
  * src/weights.c exposes them (name, shape, data), but block-quantised tensors keep their ggml
  * type instead of being decoded to f32. fmt is one of the MYNAH_B200_* formats; data is
  * borrowed until mynah_b200_model_finalize returns. */

@@ -1,0 +1,82 @@
+"""One kernel on one synthetic case, for timing and for profiler captures.
+
+    python mynah-asr_b200/kernel_case.py gemm  --T 16384 --n 4096 --k 1024 [--fast] [--iters 3]
+    python mynah-asr_b200/kernel_case.py qgemv --T 1 --n 65536 --k 4096 --fmt q4_0 [--iters 3]
+
+gemm : the tcgen05 contraction on resident fp16 planes (large T).
+qgemv: the weight-streaming small-T kernel on the stored blocks; sizes above the 126 MB L2
+       make the figure an HBM figure. Prints the CUDA-event time per launch, the algorithmic
+       bytes / flops and the achieved rate.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def _pkg():
+    spec = importlib.util.spec_from_file_location("mynah_asr_b200", os.path.join(HERE, "__init__.py"),
+                                                  submodule_search_locations=[HERE])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["mynah_asr_b200"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+BPP = {"f32": 4.0, "q8_0": 34 / 32, "q4_0": 18 / 32, "q4_k": 144 / 256, "q6_k": 210 / 256}
+
+
+def random_blocks(fmt: str, n: int, k: int, rng) -> np.ndarray:
+    """Random but well-formed stored blocks (f16 scales around 0.005, random quants)."""
+    ne = n * k
+    if fmt == "f32":
+        return (rng.standard_normal(ne, dtype=np.float32) * 0.02).view(np.uint8)
+    geom = {"q8_0": (32, 34, [0]), "q4_0": (32, 18, [0]), "q4_k": (256, 144, [0, 2]), "q6_k": (256, 210, [208])}[fmt]
+    nb = ne // geom[0]
+    raw = rng.integers(0, 256, (nb, geom[1]), dtype=np.uint8)
+    d = (rng.uniform(0.002, 0.008, nb)).astype(np.float16).view(np.uint8).reshape(nb, 2)
+    for off in geom[2]:
+        raw[:, off:off + 2] = d
+    return raw.reshape(-1)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "qgemv"])
+    ap.add_argument("--T", type=int, default=0)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=1024)
+    ap.add_argument("--fmt", default="q4_0", choices=list(BPP))
+    ap.add_argument("--fast", action="store_true")
+    ap.add_argument("--a8", action="store_true")
+    ap.add_argument("--iters", type=int, default=3)
+    a = ap.parse_args()
+    pkg = _pkg()
+    assert pkg.available(), "no sm_100 device"
+    rng = np.random.default_rng(0)
+    T = a.T or (16384 if a.kernel == "gemm" else 1)
+    fmt = {"f32": pkg.F32, "q8_0": pkg.GGML_Q8_0, "q4_0": pkg.GGML_Q4_0, "q4_k": pkg.GGML_Q4_K, "q6_k": pkg.GGML_Q6_K}[a.fmt]
+    q = pkg.QMat(fmt, random_blocks(a.fmt, a.n, a.k, rng), a.n, a.k)
+    flags = (pkg.FAST if a.fast else pkg.A16) | (pkg.A8 if a.a8 else 0)
+    ms = q.time_ms(T, flags, a.iters)
+    out = {"kernel": a.kernel, "T": T, "n": a.n, "k": a.k, "fmt": a.fmt, "ms": ms}
+    if a.kernel == "gemm":
+        assert T > 16
+        out["flops"] = 2.0 * T * a.n * a.k
+        out["tflops"] = out["flops"] / (ms * 1e-3) / 1e12
+    else:
+        assert T <= 16
+        out["bytes"] = a.n * a.k * BPP[a.fmt] + T * a.k * 4 + T * a.n * 4
+        out["gbs"] = out["bytes"] / (ms * 1e-3) / 1e9
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
