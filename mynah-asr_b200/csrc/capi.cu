@@ -670,6 +670,11 @@ int mynah_b200_qmat_mul_device(const mynah_b200_qmat *q, const float *x, float *
         return rc;
     }
     if (T <= 16 && w.k <= 8192) {     // QMAT_SMALL_T / QMAT_K_MAX of the reference (src/qmat.c:180-181)
+        if (w.mma_q && !(flags & MYNAH_B200_SCALAR)) {
+            const int rc = qgemv_mma(w, x, w.k, out, w.n, nullptr, T, q->stream);
+            if (rc == 0) note_launch((T + 3) / 4);
+            return rc;
+        }
         const int rc = qgemv(w, x, w.k, out, w.n, nullptr, T, q->stream);
         if (rc == 0) note_launch((T + 3) / 4);
         return rc;
@@ -800,7 +805,9 @@ double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iter
     int rc = 0;
     for (int it = -2; it < iters && rc == 0; it++) {
         if (it == 0) cudaEventRecord(e0, q->stream);
-        if (small) rc = (flags & MYNAH_B200_A8) ? qgemv_a8(w, x, out, T, nullptr, nullptr, q->stream) : qgemv(w, x, w.k, out, w.n, nullptr, T, q->stream);
+        if (small) rc = (flags & MYNAH_B200_A8) ? qgemv_a8(w, x, out, T, nullptr, nullptr, q->stream)
+                   : (w.mma_q && !(flags & MYNAH_B200_SCALAR)) ? qgemv_mma(w, x, w.k, out, w.n, nullptr, T, q->stream)
+                   : qgemv(w, x, w.k, out, w.n, nullptr, T, q->stream);
         else {
             GemmEpilogue e;
             memset(&e, 0, sizeof(e));

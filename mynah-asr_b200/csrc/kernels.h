@@ -72,6 +72,9 @@ int log_mel_device(const MelCfg &c, const float *audio, size_t n_samples, const 
 // ---- qgemv.cu : out[T,n] = x[T,k] W^T for T <= 16 straight from the stored blocks
 struct QWeight;
 int qgemv(const QWeight &w, const float *x, int ldx, float *out, int ldo, const float *bias, int T, cudaStream_t st);
+// ---- qgemv_mma.cu : the same product for Q4_0 / Q8_0 on mma.sync, from re-tiled blocks
+int qgemv_mma_retile(const QWeight &w, uint8_t *qs, __half *ds, cudaStream_t st);
+int qgemv_mma(const QWeight &w, const float *x, int ldx, float *out, int ldo, const float *bias, int T, cudaStream_t st);
 int qgemv_a8(const QWeight &w, const float *x, float *out, int T, int32_t *block_dots, float *sx_out, cudaStream_t st);
 
 // ---- decoder.cu

@@ -75,6 +75,15 @@ int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *sca
         w.scales = upload_f32(scales, ns);
         if (!w.scales) return -1;
     }
+    if ((fmt == FMT_GGML_Q4_0 || fmt == FMT_GGML_Q8_0) && k % 128 == 0) {
+        // re-tiled copy for the tensor-core small-T kernel (same bytes per parameter)
+        w.mma_q = (uint8_t *)dev_alloc(fmt == FMT_GGML_Q4_0 ? (size_t)n * k / 2 : (size_t)n * k);
+        w.mma_d = (__half *)dev_alloc((size_t)n * (k / 32) * sizeof(__half));
+        if (!w.mma_q || !w.mma_d) return -1;
+        if (qgemv_mma_retile(w, w.mma_q, w.mma_d, stream)) return -1;
+        note_launch();
+        MB_CUDA(cudaStreamSynchronize(stream));
+    }
     if (!want_planes && !want_f32) return 0;
     float *tmp = nullptr;
     MB_CUDA(cudaMalloc(&tmp, (size_t)n * k * sizeof(float)));

@@ -15,6 +15,8 @@ struct QWeight {
     __half *lo = nullptr;
     float *f32 = nullptr;       // decoded f32 copy (only where a kernel wants f32 weights)
     float *bias = nullptr;      // optional [n]
+    uint8_t *mma_q = nullptr;   // Q4_0 / Q8_0 quants re-tiled for the tensor-core small-T kernel (qgemv_mma.cu)
+    __half *mma_d = nullptr;    // their block scales [n, k/32]
 };
 
 // What a kernel launcher needs from an opaque mynah_b200_qmat handle.
