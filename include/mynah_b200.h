@@ -39,8 +39,9 @@ enum {
     MYNAH_B200_A16 = 0,        /* float activations x exactly decoded weights (the reference's f32 path) */
     MYNAH_B200_A8 = 1,         /* int8 activations, integer block dots (src/qmat.c:186-202,285-364)      */
     MYNAH_B200_FAST = 2,       /* large T: single fp16 tensor-core pass instead of the 3-term split      */
-    MYNAH_B200_SCALAR = 4      /* small T: force the scalar-FMA streaming kernel (Q4_0/Q8_0 default to the
-                                  tensor-core streaming kernel); for cross-checks                        */
+    MYNAH_B200_SCALAR = 4,     /* small T: force the scalar-FMA streaming kernel; for cross-checks        */
+    MYNAH_B200_MMA_SYNC = 8    /* small T: force the warp-level (mma.sync) streaming kernel; Q4_0/Q8_0 with
+                                  T <= 8 default to the tcgen05 streaming kernel                          */
 };
 
 /* ---- backend presence and errors --------------------------------------------- */

@@ -670,6 +670,14 @@ int mynah_b200_qmat_mul_device(const mynah_b200_qmat *q, const float *x, float *
         return rc;
     }
     if (T <= 16 && w.k <= 8192) {     // QMAT_SMALL_T / QMAT_K_MAX of the reference (src/qmat.c:180-181)
+        if (w.tc_q && !(flags & (MYNAH_B200_SCALAR | MYNAH_B200_MMA_SYNC))) {
+            int rc = 0;
+            for (int t0 = 0; t0 < T && rc == 0; t0 += 8)
+                rc = qstream_tc(w, x + (size_t)t0 * w.k, w.k, out + (size_t)t0 * w.n, w.n, nullptr, T - t0 < 8 ? T - t0 : 8,
+                                q->status, q->stream);
+            if (rc == 0) note_launch(((T + 7) / 8) * (w.tc_scratch ? 2 : 1));
+            return rc;
+        }
         if (w.mma_q && !(flags & MYNAH_B200_SCALAR)) {
             const int rc = qgemv_mma(w, x, w.k, out, w.n, nullptr, T, q->stream);
             if (rc == 0) note_launch((T + 3) / 4);
@@ -806,6 +814,7 @@ double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iter
     for (int it = -2; it < iters && rc == 0; it++) {
         if (it == 0) cudaEventRecord(e0, q->stream);
         if (small) rc = (flags & MYNAH_B200_A8) ? qgemv_a8(w, x, out, T, nullptr, nullptr, q->stream)
+                   : (w.tc_q && T <= 8 && !(flags & (MYNAH_B200_SCALAR | MYNAH_B200_MMA_SYNC))) ? qstream_tc(w, x, w.k, out, w.n, nullptr, T, q->status, q->stream)
                    : (w.mma_q && !(flags & MYNAH_B200_SCALAR)) ? qgemv_mma(w, x, w.k, out, w.n, nullptr, T, q->stream)
                    : qgemv(w, x, w.k, out, w.n, nullptr, T, q->stream);
         else {

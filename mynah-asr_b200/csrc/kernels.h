@@ -75,6 +75,12 @@ int qgemv(const QWeight &w, const float *x, int ldx, float *out, int ldo, const 
 // ---- qgemv_mma.cu : the same product for Q4_0 / Q8_0 on mma.sync, from re-tiled blocks
 int qgemv_mma_retile(const QWeight &w, uint8_t *qs, __half *ds, cudaStream_t st);
 int qgemv_mma(const QWeight &w, const float *x, int ldx, float *out, int ldo, const float *bias, int T, cudaStream_t st);
+// ---- qstream_tc.cu : the same product with the decode fused into the tcgen05 operand pipeline (T <= 8)
+size_t qstream_tc_bytes(int fmt, int n, int k);
+int qstream_tc_retile(const QWeight &w, uint8_t *dst, cudaStream_t st);
+size_t qstream_tc_scratch_bytes(int n, int k);
+int qstream_tc(const QWeight &w, const float *x, int ldx, float *out, int ldo, const float *bias, int T, int *status,
+               cudaStream_t st);
 int qgemv_a8(const QWeight &w, const float *x, float *out, int T, int32_t *block_dots, float *sx_out, cudaStream_t st);
 
 // ---- decoder.cu

@@ -84,6 +84,17 @@ int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *sca
         note_launch();
         MB_CUDA(cudaStreamSynchronize(stream));
     }
+    if ((fmt == FMT_GGML_Q4_0 || fmt == FMT_GGML_Q8_0) && k % 128 == 0) {
+        w.tc_q = (uint8_t *)dev_alloc(qstream_tc_bytes(fmt, n, k));
+        if (!w.tc_q) return -1;
+        if (const size_t sb = qstream_tc_scratch_bytes(n, k)) {
+            w.tc_scratch = (float *)dev_alloc(sb);
+            if (!w.tc_scratch) return -1;
+        }
+        if (qstream_tc_retile(w, w.tc_q, stream)) return -1;
+        note_launch();
+        MB_CUDA(cudaStreamSynchronize(stream));
+    }
     if (!want_planes && !want_f32) return 0;
     float *tmp = nullptr;
     MB_CUDA(cudaMalloc(&tmp, (size_t)n * k * sizeof(float)));

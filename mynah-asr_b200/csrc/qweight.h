@@ -17,6 +17,8 @@ struct QWeight {
     float *bias = nullptr;      // optional [n]
     uint8_t *mma_q = nullptr;   // Q4_0 / Q8_0 quants re-tiled for the tensor-core small-T kernel (qgemv_mma.cu)
     __half *mma_d = nullptr;    // their block scales [n, k/32]
+    uint8_t *tc_q = nullptr;    // Q4_0 / Q8_0 stages re-tiled for the tcgen05 streaming kernel (qstream_tc.cu)
+    float *tc_scratch = nullptr;  // its K-slice partial sums, when the shape is split over K
 };
 
 // What a kernel launcher needs from an opaque mynah_b200_qmat handle.
