@@ -1,29 +1,35 @@
-// Weight-streaming quantised matmul with the block decode fused into the tcgen05 operand
-// pipeline: out[T,n] = x[T,k] W^T for T <= 8, W stored as ggml Q4_0 / Q8_0 blocks.
+// Weight-streaming quantised matmul on the tcgen05 integer tensor path:
+// out[T,n] = x[T,k] W^T for T <= 8, W stored as ggml Q4_0 / Q8_0 blocks.
 // The bandwidth-bound half of the reference's mynah_asr_qmat_mul (src/qmat.c:508-597).
+//
+// Arithmetic. A stored block is 32 integers q and an f16 scale d (w = d*q, ingot dequant.c:72-83).
+// Each 32-element block of an activation row is written as 2^e * (p0 + p1/2^7 + p2/2^14 + p3/2^21)
+// with four int8 planes p and a power-of-two block scale, so every step of the split is exact and
+// the row is reproduced to 2^-28 of the block's largest element. The tensor core then forms the
+// exact int32 dots q.p0 .. q.p3 of every (weight row, block), and a thread folds them in f32:
+// out += d * 2^e * (v0 + v1/2^7 + v2/2^14 + v3/2^21). No product is ever rounded before that fold.
 //
 // Per CTA (persistent, one per SM), 32 warps with fixed roles:
 //   * warp 0, one thread: streams the stored bytes of a stage (128 weight rows x 128 k: the
 //     quants and the four f16 block scales per row, laid out contiguously at load) from HBM
-//     into a shared-memory ring with bulk asynchronous copies (cp.async.bulk, no multicast)
-//     tracked by mbarriers — 70-90 KB in flight per SM to cover HBM latency;
-//   * warps 8-23, four groups of four: group g decodes block g of every stage. A thread owns
-//     one weight row, turns its 32 integers into fp16 (`q | 0x6400` is the fp16 number 1024 + q,
-//     so two weights cost one LOP3/PRMT and half an HSUB2) and writes them with tcgen05.st into
-//     tensor memory, where they are the A operand — the decoded weights never touch shared memory;
-//   * warps 1-4, one thread each: issuer g issues the tcgen05.mma (kind::f16, M = 128 weight rows,
-//     N = 16, K = 16) of block g — one thread gets an MMA out every ~45 cycles whatever its size, so
-//     the small ones here need several issuers — with A from tensor memory and B from shared memory: B is the fp16 (hi, lo) planes of up to 8
-//     activation rows, resident in shared memory for the CTA's K slice. Each 32-element block
-//     gets its own 16 accumulator columns, because the block scale d has to multiply the block's
-//     dot afterwards (w = d*q, ingot dequant.c:72-83);
+//     into an 8-deep shared-memory ring with bulk asynchronous copies (cp.async.bulk, no multicast)
+//     tracked by mbarriers — 70-140 KB in flight per SM to cover HBM latency;
+//   * warps 8-23, four groups of four: group g handles block g of every stage. A thread owns one
+//     weight row and moves its 32 integers into tensor memory with tcgen05.st, where they are the
+//     A operand: Q8_0 bytes go as they are, a Q4_0 word becomes two words of (q-8)*16 with three
+//     logic instructions. The weights never pass through shared memory a second time;
+//   * warps 1-4, one thread each: issuer g issues the tcgen05.mma (kind::i8, M = 128 weight rows,
+//     N = 16 or 32 plane rows, K = 32) of block g — one thread gets an MMA out every ~45 cycles
+//     whatever its size, so the small ones here need several issuers. B is the int8 planes of the
+//     activations, resident in shared memory for the CTA's K slice. Each block has its own
+//     accumulator columns, because d and 2^e multiply the block's dots afterwards;
 //   * warps 24-31, two groups of four: read the block dots back (tcgen05.ld; thread = weight row)
-//     and fold them into f32 accumulators: out += d * (q.x_hi + 2^-11 q.x_lo);
-//   * every warp but the streamer's first stages its share of the activations (warps 5-7 do only that).
+//     and fold them into f32 accumulators;
+//   * every warp but the streamer's first splits its share of the activations into planes.
 // Large K, or few rows, are split over CTAs (fixed K slice per CTA, so its activations are staged
 // once); the slices are then summed in a fixed order by a second small kernel, so results are
-// reproducible. Every mbarrier wait is bounded; a wait that runs out sets a status word and the
-// kernel unwinds.
+// reproducible and a row's result does not depend on T. Every mbarrier wait is bounded; a wait
+// that runs out sets a status word and the kernel unwinds.
 #include "kernels.h"
 #include "qweight.h"
 
@@ -32,21 +38,20 @@ namespace mb {
 static constexpr int QS_ROWS = 128;           // weight rows per tile (UMMA M)
 static constexpr int QS_SK = 128;             // k per stage
 static constexpr int QS_NB = 4;               // 32-element blocks per stage
-static constexpr int QS_N = 16;               // UMMA N: (hi, lo) x 8 activation rows
+static constexpr int QS_PLANES = 4;           // int8 planes per activation row
 static constexpr int QS_MAX_SLICE_ST = 32;    // stages of K per CTA slice (4096 k)
 static constexpr int QS_FIRST_ISSUER = 1;     // warps 1-4: one MMA issuer per block of the stage
 static constexpr int QS_FIRST_DECODE = 8, QS_DECODE_WARPS = 16;
 static constexpr int QS_FIRST_SCALE = 24, QS_SCALE_WARPS = 8;
 static constexpr int QS_THREADS = (QS_FIRST_SCALE + QS_SCALE_WARPS) * 32;     // 1024
-static constexpr int QS_X_CHUNK = QS_N * 128;                 // 2 KB: 16 rows x 64 k of fp16
-static constexpr int QS_X_STAGE = 2 * QS_X_CHUNK;             // 4 KB per stage of K
-static constexpr int QS_TMEM_COLS = 256;                      // A: 2 stages x 64 columns, D: 2 stages x 64
-static constexpr int QS_D_COL0 = 128;
+static constexpr int QS_A_COLS = 8;                           // tensor-memory columns of one decoded block (32 int8)
+static constexpr int QS_TMEM_COLS = 512;
 static constexpr int QS_SCALE_BYTES = QS_NB * QS_ROWS * 2;    // 1 KB of f16 block scales per stage
 
 __host__ __device__ constexpr int qs_quant_bytes(int fmt) { return fmt == FMT_GGML_Q4_0 ? QS_ROWS * QS_SK / 2 : QS_ROWS * QS_SK; }
 __host__ __device__ constexpr int qs_stage_bytes(int fmt) { return qs_quant_bytes(fmt) + QS_SCALE_BYTES; }
-__host__ __device__ constexpr int qs_raw_depth(int fmt) { return fmt == FMT_GGML_Q4_0 ? 8 : 5; }
+// stored-byte stages in flight (a power of two); 8 rows of Q8_0 planes leave room for 4
+__host__ __device__ constexpr int qs_raw_depth(int fmt, int nt) { return (fmt == FMT_GGML_Q8_0 && nt == 8) ? 4 : 8; }
 
 // -------------------------------------------------------------------- re-tiling at load
 // [tile][stage][ quants: [16-byte chunk c][row 0..127][16 B] | scales: [block 0..3][row 0..127] f16 ]
@@ -110,71 +115,64 @@ __device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t b
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ uint32_t hsub2u(uint32_t a, uint32_t b) {
-    uint32_t d;
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-    return d;
-}
-// eight Q4_0 weights of one 32-bit word -> eight fp16 (q-8): bytes i = 0..3 hold element i in the
-// low nibble and element i+16 in the high one; the result order is (e0,e2) (e1,e3) (e16,e18) (e17,e19)
-__device__ __forceinline__ void q4_word(uint32_t w, uint32_t *r) {
-    constexpr uint32_t M = 0x000F000Fu, E = 0x64006400u, OFF = 0x64086408u;
-    r[0] = hsub2u((w & M) | E, OFF);
-    r[1] = hsub2u(((w >> 8) & M) | E, OFF);
-    r[2] = hsub2u(((w >> 4) & M) | E, OFF);
-    r[3] = hsub2u(((w >> 12) & M) | E, OFF);
-}
-// four int8 -> four fp16, natural order
-__device__ __forceinline__ void q8_word(uint32_t w, uint32_t *r) {
-    constexpr uint32_t E = 0x64646464u, OFF = 0x64806480u;
-    const uint32_t u = w ^ 0x80808080u;
-    r[0] = hsub2u(__byte_perm(u, E, 0x4140), OFF);
-    r[1] = hsub2u(__byte_perm(u, E, 0x4342), OFF);
-}
-// position (0..31) of element e of a block along the K axis of the decoded operand
-__device__ __forceinline__ int qs_slot(int fmt, int e) {
-    if (fmt != FMT_GGML_Q4_0) return e;
-    const int c = (e & 15) >> 2, i = e & 3;
-    return 8 * c + 4 * (e >> 4) + ((i & 1) * 2 + (i >> 1));
-}
-// D[tmem] (+)= A[tmem] * B[smem]; fp16 inputs, f32 accumulators. A: lane = row, one 32-bit
-// column per two consecutive k.
-__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]; int8 inputs, int32 accumulators. A: lane = row, one 32-bit
+// column per four consecutive k.
+__device__ __forceinline__ void tc_mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// 16 registers per thread -> 32 lanes x 16 consecutive columns of tensor memory
-__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t *r) {
+// instruction descriptor: D s32, A/B s8 K-major, M x N
+__host__ __device__ constexpr uint32_t qs_idesc_i8(int M, int N) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+// 8 registers per thread -> 32 lanes x 8 consecutive columns of tensor memory
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t *r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+// 32 registers per thread -> 32 lanes x 32 consecutive columns of tensor memory
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t *r) {
     asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// 32 lanes x (2 | 4 | 8 | 16) consecutive f32 columns -> registers
+// 32 lanes x (4 | 8 | 16 | 32) consecutive 32-bit columns -> registers
 template <int NC>
-__device__ __forceinline__ void tc_ldn(uint32_t taddr, float *v) {
-    uint32_t *r = reinterpret_cast<uint32_t *>(v);
-    if constexpr (NC == 2) {
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(taddr) : "memory");
-    } else if constexpr (NC == 4) {
+__device__ __forceinline__ void tc_ldn(uint32_t taddr, int *r) {
+    if constexpr (NC == 4) {
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
     } else if constexpr (NC == 8) {
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
                      : "r"(taddr) : "memory");
-    } else {
+    } else if constexpr (NC == 16) {
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
             : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
               "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(taddr) : "memory");
+    } else {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
             : "r"(taddr) : "memory");
     }
 }
@@ -193,24 +191,38 @@ struct QsArgs {
     int *status;
 };
 
-// NT: activation rows read back from the accumulators (1, 2, 4 or 8; T <= NT)
+// NT: activation rows the accumulators are read back for (1, 2, 4 or 8; T <= NT). The MMA's N is
+// the 4 NT plane rows, padded to 16.
 template <int FMT, int NT>
 __global__ void __launch_bounds__(QS_THREADS, 1)
 qstream_tc_kernel(const QsArgs a) {
     constexpr int SB = qs_stage_bytes(FMT);
     constexpr int QBYTES = qs_quant_bytes(FMT);
-    constexpr int DEPTH = qs_raw_depth(FMT);
+    constexpr int DEPTH = qs_raw_depth(FMT, NT);
+    constexpr int N = NT <= 4 ? 16 : 32;                    // plane rows of the B operand (row 4j+p: plane p of activation row j)
+    constexpr int NCOL = QS_PLANES * NT;                    // accumulator columns that carry data
+    constexpr int XT = N * 128;                             // bytes of planes per stage: N rows x 128 k of int8, 128-byte swizzle
+    constexpr int DST = QS_NB * N;                          // accumulator columns per stage
+    // Stages in tensor memory: AP of decoded weights, one per decode group, and DP of accumulators.
+    // Every barrier below is waited on by threads that lag it by at most one phase: a decode group
+    // comes back to its own A slot, a read-back group to its own accumulator slots.
+    constexpr int AP = QS_DECODE_WARPS / 4;                 // 4
+    constexpr int DP = NT <= 4 ? 4 : 2;
+    constexpr int AST = QS_NB * QS_A_COLS;                  // A columns per stage
+    constexpr int D_COL0 = AP * AST;                        // accumulators start after the A stages (AP * AST + DP * DST <= 512)
     extern __shared__ uint8_t qs_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(qs_smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *x_tile = smem;                                                // max_slice_st x 4 KB, 128-byte swizzle
-    uint8_t *raw = x_tile + (size_t)a.max_slice_st * QS_X_STAGE;           // DEPTH x SB
+    uint8_t *x_tile = smem;                                                // max_slice_st x XT
+    uint8_t *raw = x_tile + (size_t)a.max_slice_st * XT;                   // DEPTH x SB
     float *xch = reinterpret_cast<float *>(raw + DEPTH * SB);              // 2 x 8 x 128: sums of read-back group 1
-    uint64_t *raw_full = reinterpret_cast<uint64_t *>(xch + 2 * 8 * QS_ROWS);
+    float *sxs = xch + 2 * 8 * QS_ROWS;                                    // [stage][block][NT] activation block scales 2^e
+    uint64_t *raw_full = reinterpret_cast<uint64_t *>(sxs + (size_t)a.max_slice_st * QS_NB * NT);
     uint64_t *raw_empty = raw_full + DEPTH;
-    uint64_t *a_full = raw_empty + DEPTH;                                  // [parity][block]
-    uint64_t *d_full = a_full + 2 * QS_NB;
-    uint64_t *d_free = d_full + 2;
-    uint64_t *x_full = d_free + 2;
+    uint64_t *a_full = raw_empty + DEPTH;
+    uint64_t *a_free = a_full + AP;                                        // used when DP != AP; else d_full says the same
+    uint64_t *d_full = a_free + AP;
+    uint64_t *d_free = d_full + DP;
+    uint64_t *x_full = d_free + DP;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(x_full + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -224,9 +236,9 @@ qstream_tc_kernel(const QsArgs a) {
     const int total = my_tiles * nst;                                      // stages this CTA works through
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < DEPTH; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QS_DECODE_WARPS + QS_SCALE_WARPS); }
-        for (int i = 0; i < 2 * QS_NB; i++) mbar_init(&a_full[i], QS_DECODE_WARPS / QS_NB);
-        for (int i = 0; i < 2; i++) { mbar_init(&d_full[i], QS_NB); mbar_init(&d_free[i], QS_SCALE_WARPS); }
+        for (int i = 0; i < DEPTH; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4 + 4); }   // one decode, one read-back group
+        for (int i = 0; i < AP; i++) { mbar_init(&a_full[i], 4); mbar_init(&a_free[i], QS_NB); }
+        for (int i = 0; i < DP; i++) { mbar_init(&d_full[i], QS_NB); mbar_init(&d_free[i], 4); }
         mbar_init(x_full, QS_THREADS / 32 - 1);
         mbar_fence_init();
     }
@@ -236,175 +248,206 @@ qstream_tc_kernel(const QsArgs a) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    // ---- activations of this slice: fp16 (hi, lo) rows 2j, 2j+1, K-major, 128-byte swizzle, each
-    // block's k in the order the decode produces. Rows past 2T stay as they are: their accumulator
-    // columns are never written out. Every warp but the streamer's takes (row, stage) units of 128 k,
-    // two units = eight loads per lane in flight at a time.
-    if (warp != 0) {
-        const int units = a.T * nst, slot = qs_slot(FMT, lane);
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------------------------------------------------- byte streamer
+            int it = 0;
+            bool ok = true;
+            for (int ti = 0; ti < my_tiles && ok; ti++) {
+                const uint8_t *src = a.wt + ((size_t)(cta_in_slice + ti * ctas_per_slice) * nst_total + s0) * SB;
+                for (int st = 0; st < nst; st++, it++) {
+                    const int rs = it & (DEPTH - 1);
+                    if (it >= DEPTH && !mbar_wait(&raw_empty[rs], (uint32_t)(((it / DEPTH) & 1) ^ 1))) { ok = false; break; }
+                    mbar_expect_tx(&raw_full[rs], SB);
+                    bulk_load(raw + rs * SB, src + (size_t)st * SB, SB, &raw_full[rs]);
+                }
+            }
+            if (!ok) atomicExch(a.status, ST_TIMEOUT_PRODUCER);
+            // every copy this thread started has to land before the CTA may exit
+            for (int j = it > DEPTH ? it - DEPTH : 0; j < it; j++) mbar_wait(&raw_full[j & (DEPTH - 1)], (uint32_t)((j / DEPTH) & 1));
+        }
+    } else {
+        // ---- every other warp first splits its share of this slice's activations into int8 planes
+        // (units of one row x one stage; eight loads per lane in flight). Block b of a row:
+        // 2^e with |x| * 2^-e < 64 for the block's largest |x|, then four exact rounding steps.
+        // Plane rows past 4T stay as they are: their accumulator columns are never written out.
+        const int units = a.T * nst;
         const float *xs = a.x + (size_t)s0 * QS_SK;
-        for (int u0 = warp - 1; u0 < units; u0 += 2 * (QS_THREADS / 32 - 1)) {
+        constexpr int NW = QS_THREADS / 32 - 1;
+        for (int u0 = warp - 1; u0 < units; u0 += 2 * NW) {
             float v[2][4];
 #pragma unroll
             for (int uu = 0; uu < 2; uu++) {
-                const int u = u0 + uu * (QS_THREADS / 32 - 1);
+                const int u = u0 + uu * NW;
                 const int j = u / nst, st = u - j * nst;
 #pragma unroll
-                for (int i = 0; i < 4; i++) v[uu][i] = u < units ? __ldg(xs + (size_t)j * a.ldx + st * QS_SK + lane + 32 * i) : 0.f;
+                for (int b = 0; b < 4; b++) v[uu][b] = u < units ? __ldg(xs + (size_t)j * a.ldx + st * QS_SK + 32 * b + lane) : 0.f;
             }
 #pragma unroll
             for (int uu = 0; uu < 2; uu++) {
-                const int u = u0 + uu * (QS_THREADS / 32 - 1);
+                const int u = u0 + uu * NW;
                 if (u >= units) break;
                 const int j = u / nst, st = u - j * nst;
-                const int r0 = 2 * j, r1 = 2 * j + 1;
 #pragma unroll
-                for (int i = 0; i < 4; i++) {            // k = 128 st + 32 i + lane: 64-k chunk 2 st + (i >> 1), block i & 1 of it
-                    __half h, l;
-                    split_h16(v[uu][i], h, l);
-                    const int pos = (i & 1) * 32 + slot, c16 = pos >> 3;
-                    uint8_t *base = x_tile + (2 * st + (i >> 1)) * QS_X_CHUNK + (pos & 7) * 2;
-                    *reinterpret_cast<__half *>(base + r0 * 128 + ((c16 ^ (r0 & 7)) << 4)) = h;
-                    *reinterpret_cast<__half *>(base + r1 * 128 + ((c16 ^ (r1 & 7)) << 4)) = l;
+                for (int b = 0; b < 4; b++) {
+                    const float m = warp_max(fabsf(v[uu][b]));
+                    int eb = (__float_as_int(m) >> 23) - 132;                // floor(log2 m) - 5
+                    eb = eb < -100 ? -100 : eb;
+                    const float sinv = m > 0.f ? __int_as_float((127 - eb) << 23) : 0.f;
+                    float r = v[uu][b] * sinv;
+                    const int kpos = 32 * b + lane;
+#pragma unroll
+                    for (int p = 0; p < QS_PLANES; p++) {
+                        const float pl = rintf(r);
+                        r = (r - pl) * 128.f;
+                        const int row = QS_PLANES * j + p;
+                        *reinterpret_cast<int8_t *>(x_tile + st * XT + row * 128 + (((kpos >> 4) ^ (row & 7)) << 4) + (kpos & 15)) = (int8_t)(int)pl;
+                    }
+                    if (lane == 0) sxs[(st * QS_NB + b) * NT + j] = m > 0.f ? __int_as_float((127 + eb) << 23) : 0.f;
                 }
             }
         }
         fence_async_smem();                              // generic-proxy stores -> visible to the tensor core
         __syncwarp();
         if (lane == 0) mbar_arrive(x_full);
-    }
 
-    if (warp == 0) {
-        if (lane == 0) {
-            // ---------------------------------------------------------- byte streamer
-            int rs = 0, it = 0;
-            uint32_t rph = 0;
-            bool ok = true;
-            for (int ti = 0; ti < my_tiles && ok; ti++) {
-                const uint8_t *src = a.wt + ((size_t)(cta_in_slice + ti * ctas_per_slice) * nst_total + s0) * SB;
-                for (int st = 0; st < nst; st++) {
-                    if (it >= DEPTH && !mbar_wait(&raw_empty[rs], rph ^ 1)) { ok = false; break; }
-                    mbar_expect_tx(&raw_full[rs], SB);
-                    bulk_load(raw + rs * SB, src + (size_t)st * SB, SB, &raw_full[rs]);
-                    it++;
-                    if (++rs == DEPTH) { rs = 0; rph ^= 1; }
-                }
-            }
-            if (!ok) atomicExch(a.status, ST_TIMEOUT_PRODUCER);
-            // every copy this thread started has to land before the CTA may exit
-            for (int j = it > DEPTH ? it - DEPTH : 0; j < it; j++) mbar_wait(&raw_full[j % DEPTH], (uint32_t)((j / DEPTH) & 1));
-        }
-    } else if (warp >= QS_FIRST_ISSUER && warp < QS_FIRST_ISSUER + QS_NB) {
-        if (lane == 0 && total > 0) {
-            // ---------------------------------------------------------- MMA issuer of block b
-            const int b = warp - QS_FIRST_ISSUER;
-            bool ok = mbar_wait(x_full, 0);
-            const uint64_t bdesc0 = umma_desc_sw128(smem_u32(x_tile));
-            constexpr uint32_t idesc = umma_idesc_f16(QS_ROWS, QS_N);
-            int st = 0;
-            for (int it = 0; it < total && ok; it++) {
-                const int par = it & 1;
-                const uint32_t uph = (uint32_t)((it >> 1) & 1);
-                if (!mbar_wait(&a_full[par * QS_NB + b], uph)) { ok = false; break; }
-                if (it >= 2 && !mbar_wait(&d_free[par], uph ^ 1)) { ok = false; break; }
-                tc_fence_after();
-                const uint64_t bd = bdesc0 + (uint64_t)((st * QS_X_STAGE + (b >> 1) * QS_X_CHUNK + (b & 1) * 64) >> 4);
-                const uint32_t acol = tmem_base + par * 64 + b * 16, dcol = tmem_base + QS_D_COL0 + par * 64 + b * 16;
-                tc_mma_f16_ts(dcol, acol, bd, idesc, 0);
-                tc_mma_f16_ts(dcol, acol + 8, bd + 2, idesc, 1);
-                tc_commit(&d_full[par]);
-                if (++st == nst) st = 0;
-            }
-            if (!ok) atomicExch(a.status, ST_TIMEOUT_MMA);
-        }
-    } else if (warp >= QS_FIRST_DECODE && warp < QS_FIRST_DECODE + QS_DECODE_WARPS) {
-        // ---------------------------------------------------------------- decode warps
-        const int g = (warp - QS_FIRST_DECODE) >> 2;         // block of the stage this group decodes
-        const int row = (warp & 3) * 32 + lane;              // weight row = TMEM lane (quarter warp % 4)
-        const uint32_t tdst = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + g * 16;
-        int rs = 0;
-        uint32_t rph = 0;
-        for (int it = 0; it < total; it++) {
-            const int par = it & 1;
-            const uint32_t uph = (uint32_t)((it >> 1) & 1);
-            bool ok = mbar_wait(&raw_full[rs], rph);
-            if (ok && it >= 2) ok = mbar_wait(&d_full[par], uph ^ 1);      // MMAs of stage it-2 are done with this A region
-            if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) atomicExch(a.status, ST_TIMEOUT_PRODUCER); break; }
-            tc_fence_after();
-            const uint8_t *src = raw + rs * SB;
-            uint32_t r[16];
-            if (FMT == FMT_GGML_Q4_0) {
-                const uint4 q = *reinterpret_cast<const uint4 *>(src + (g * QS_ROWS + row) * 16);
-                q4_word(q.x, r); q4_word(q.y, r + 4); q4_word(q.z, r + 8); q4_word(q.w, r + 12);
-            } else {
-                const uint4 q0 = *reinterpret_cast<const uint4 *>(src + ((2 * g) * QS_ROWS + row) * 16);
-                const uint4 q1 = *reinterpret_cast<const uint4 *>(src + ((2 * g + 1) * QS_ROWS + row) * 16);
-                q8_word(q0.x, r); q8_word(q0.y, r + 2); q8_word(q0.z, r + 4); q8_word(q0.w, r + 6);
-                q8_word(q1.x, r + 8); q8_word(q1.y, r + 10); q8_word(q1.z, r + 12); q8_word(q1.w, r + 14);
-            }
-            tc_st16(tdst + par * 64, r);
-            tc_wait_st();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) { mbar_arrive(&a_full[par * QS_NB + g]); mbar_arrive(&raw_empty[rs]); }
-            if (++rs == DEPTH) { rs = 0; rph ^= 1; }
-        }
-    } else if (warp >= QS_FIRST_SCALE) {
-        // ---------------------------------------------------------------- read-back warps
-        const int h = (warp - QS_FIRST_SCALE) >> 2;          // this group folds blocks 2h, 2h+1 of every stage
-        const int row = (warp & 3) * 32 + lane;
-        const uint32_t tsrc = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + QS_D_COL0 + (2 * h) * 16;
-        int rs = 0, it = 0;
-        uint32_t rph = 0;
-        bool ok = true;
-        for (int ti = 0; ti < my_tiles; ti++) {
-            float ah[NT], al[NT];
-#pragma unroll
-            for (int j = 0; j < NT; j++) ah[j] = al[j] = 0.f;
-            for (int st = 0; st < nst; st++, it++) {
-                const int par = it & 1;
-                const uint32_t uph = (uint32_t)((it >> 1) & 1);
-                if (ok) {
-                    bool w = mbar_wait(&d_full[par], uph);
-                    if (w) w = mbar_wait(&raw_full[rs], rph);              // completed long ago; orders the scale reads
-                    if (!__all_sync(0xffffffffu, w)) { ok = false; if (lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE); }
-                }
-                if (ok) {
+        if (warp >= QS_FIRST_ISSUER && warp < QS_FIRST_ISSUER + QS_NB) {
+            if (lane == 0 && total > 0) {
+                // ------------------------------------------------------ MMA issuer of block b
+                const int b = warp - QS_FIRST_ISSUER;
+                bool ok = mbar_wait(x_full, 0);
+                const uint64_t bdesc0 = umma_desc_sw128(smem_u32(x_tile)) + (uint64_t)((b * 32) >> 4);
+                constexpr uint32_t idesc = qs_idesc_i8(QS_ROWS, N);
+                int st = 0;
+                for (int it = 0; it < total && ok; it++) {
+                    const int as = it & (AP - 1), par = it & (DP - 1);
+                    if (!mbar_wait(&a_full[as], (uint32_t)((it / AP) & 1))) { ok = false; break; }
+                    if (it >= DP && !mbar_wait(&d_free[par], (uint32_t)(((it / DP) & 1) ^ 1))) { ok = false; break; }
                     tc_fence_after();
-                    float v0[2 * NT], v1[2 * NT];
-                    tc_ldn<2 * NT>(tsrc + par * 64, v0);
-                    tc_ldn<2 * NT>(tsrc + par * 64 + 16, v1);
-                    const __half *dp = reinterpret_cast<const __half *>(raw + rs * SB + QBYTES) + (2 * h) * QS_ROWS + row;
-                    const float d0 = __half2float(dp[0]), d1 = __half2float(dp[QS_ROWS]);
-                    tc_wait_ld();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) { mbar_arrive(&d_free[par]); mbar_arrive(&raw_empty[rs]); }
+                    tc_mma_i8_ts(tmem_base + D_COL0 + par * DST + b * N, tmem_base + (as * QS_NB + b) * QS_A_COLS,
+                                 bdesc0 + (uint64_t)((st * XT) >> 4), idesc, 0);
+                    if (DP != AP) tc_commit(&a_free[as]);
+                    tc_commit(&d_full[par]);
+                    if (++st == nst) st = 0;
+                }
+                if (!ok) atomicExch(a.status, ST_TIMEOUT_MMA);
+            }
+        } else if (warp >= QS_FIRST_DECODE && warp < QS_FIRST_DECODE + QS_DECODE_WARPS) {
+            // ------------------------------------------------------------ decode warps
+            // Group g takes the stages it = g, g+4, ...: the wait - load - store - wait::st chain of
+            // one stage is several hundred cycles long, so four stages are in flight in four groups.
+            const int g = (warp - QS_FIRST_DECODE) >> 2;
+            const int row = (warp & 3) * 32 + lane;              // weight row = TMEM lane (quarter warp % 4)
+            const uint32_t tdst = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+            for (int it = g; it < total; it += AP) {
+                const int rs = it & (DEPTH - 1);
+                bool ok = mbar_wait(&raw_full[rs], (uint32_t)((it / DEPTH) & 1));
+                // the MMAs of stage it-AP, the last user of A slot g, must be done
+                if (ok && it >= AP) ok = mbar_wait(DP == AP ? &d_full[g] : &a_free[g], (uint32_t)(((it / AP) & 1) ^ 1));
+                if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) atomicExch(a.status, ST_TIMEOUT_PRODUCER); break; }
+                tc_fence_after();
+                const uint8_t *src = raw + rs * SB + row * 16;
+                uint32_t r[QS_NB * QS_A_COLS];
+                if (FMT == FMT_GGML_Q4_0) {
+                    // byte i of a block holds element i (low nibble) and element i+16 (high nibble):
+                    // (q-8)*16 as a signed byte is the nibble in the high half with its top bit flipped
+                    constexpr uint32_t HM = 0xF0F0F0F0u, FL = 0x80808080u;
 #pragma unroll
-                    for (int j = 0; j < NT; j++) {
-                        ah[j] = fmaf(d0, v0[2 * j], ah[j]);
-                        al[j] = fmaf(d0, v0[2 * j + 1], al[j]);
-                        ah[j] = fmaf(d1, v1[2 * j], ah[j]);
-                        al[j] = fmaf(d1, v1[2 * j + 1], al[j]);
+                    for (int b = 0; b < QS_NB; b++) {
+                        const uint4 q = *reinterpret_cast<const uint4 *>(src + b * QS_ROWS * 16);
+                        uint32_t *rb = r + b * QS_A_COLS;
+                        rb[0] = ((q.x << 4) & HM) ^ FL; rb[1] = ((q.y << 4) & HM) ^ FL; rb[2] = ((q.z << 4) & HM) ^ FL; rb[3] = ((q.w << 4) & HM) ^ FL;
+                        rb[4] = (q.x & HM) ^ FL; rb[5] = (q.y & HM) ^ FL; rb[6] = (q.z & HM) ^ FL; rb[7] = (q.w & HM) ^ FL;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 2 * QS_NB; c++) {
+                        const uint4 q = *reinterpret_cast<const uint4 *>(src + c * QS_ROWS * 16);
+                        r[4 * c] = q.x; r[4 * c + 1] = q.y; r[4 * c + 2] = q.z; r[4 * c + 3] = q.w;
                     }
                 }
-                if (++rs == DEPTH) { rs = 0; rph ^= 1; }
+                tc_st32(tdst + g * AST, r);
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(&a_full[g]); mbar_arrive(&raw_empty[rs]); }
             }
-            // group 1 hands its sums to group 0 (fixed order: blocks 0,1 of every stage, then blocks 2,3)
-            float *xb = xch + (ti & 1) * (8 * QS_ROWS);
-            if (h == 1) {
+        } else if (warp >= QS_FIRST_SCALE) {
+            // ------------------------------------------------------------ read-back warps
+            // Group h folds the stages with it % 2 == h (two stages in flight); at the end of a row
+            // tile group 1 hands its sums to group 0.
+            const int h = (warp - QS_FIRST_SCALE) >> 2;
+            const int row = (warp & 3) * 32 + lane;
+            const uint32_t tsrc = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + D_COL0;
+            constexpr float DQ = FMT == FMT_GGML_Q4_0 ? 0.0625f : 1.f;     // Q4_0 weights sit in tensor memory as (q-8)*16
+            constexpr float P7 = 0.0078125f;                              // 2^-7 between planes
+            constexpr int BPL = NCOL <= 8 ? 4 : NCOL == 16 ? 2 : 1;        // blocks read back per tcgen05.wait::ld
+            int it = 0;
+            bool ok = __all_sync(0xffffffffu, mbar_wait(x_full, 0));   // the block scales 2^e are in place
+            if (!ok && lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE);
+            for (int ti = 0; ti < my_tiles; ti++) {
+                float acc[NT];
 #pragma unroll
-                for (int j = 0; j < NT; j++) xb[j * QS_ROWS + row] = fmaf(al[j], H16_LO_INV, ah[j]);
-            }
-            named_bar_sync(1, QS_SCALE_WARPS * 32);
-            const int r = (cta_in_slice + ti * ctas_per_slice) * QS_ROWS + row;
-            if (h == 0 && ok && r < a.n) {
+                for (int j = 0; j < NT; j++) acc[j] = 0.f;
+                for (int st = 0; st < nst; st++, it++) {
+                    if ((it & 1) != h) continue;
+                    const int par = it & (DP - 1), rs = it & (DEPTH - 1);
+                    const uint32_t uph = (uint32_t)((it / DP) & 1);
+                    if (ok) {
+                        bool w = mbar_wait(&d_full[par], uph);
+                        if (w) w = mbar_wait(&raw_full[rs], (uint32_t)((it / DEPTH) & 1));   // completed long ago; orders the scale reads
+                        if (!__all_sync(0xffffffffu, w)) { ok = false; if (lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE); }
+                    }
+                    if (!ok) continue;
+                    tc_fence_after();
+                    const __half *dp = reinterpret_cast<const __half *>(raw + rs * SB + QBYTES) + row;
+                    float d[QS_NB];
 #pragma unroll
-                for (int j = 0; j < NT; j++) {
-                    if (j < a.T) {
-                        const float v = fmaf(al[j], H16_LO_INV, ah[j]) + xb[j * QS_ROWS + row];
-                        if (a.nslice == 1) a.dst[(size_t)j * a.ldo + r] = v + (a.bias ? a.bias[r] : 0.f);
-                        else a.dst[((size_t)slice * a.T + j) * a.n + r] = v;
+                    for (int b = 0; b < QS_NB; b++) d[b] = __half2float(dp[b * QS_ROWS]) * DQ;
+#pragma unroll
+                    for (int b0 = 0; b0 < QS_NB; b0 += BPL) {
+                        int v[BPL][NCOL];
+#pragma unroll
+                        for (int bb = 0; bb < BPL; bb++) tc_ldn<NCOL>(tsrc + par * DST + (b0 + bb) * N, v[bb]);
+                        float ds[BPL][NT];
+#pragma unroll
+                        for (int bb = 0; bb < BPL; bb++) {
+                            const float *sp = sxs + (st * QS_NB + b0 + bb) * NT;
+#pragma unroll
+                            for (int j = 0; j < NT; j++) ds[bb][j] = d[b0 + bb] * sp[j];
+                        }
+                        tc_wait_ld();
+                        if (b0 + BPL == QS_NB) {             // the whole stage is in registers: accumulators and bytes may be reused
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) { mbar_arrive(&d_free[par]); mbar_arrive(&raw_empty[rs]); }
+                        }
+#pragma unroll
+                        for (int bb = 0; bb < BPL; bb++)
+#pragma unroll
+                            for (int j = 0; j < NT; j++) {
+                                const float f = fmaf(fmaf(fmaf((float)v[bb][4 * j + 3], P7, (float)v[bb][4 * j + 2]), P7, (float)v[bb][4 * j + 1]), P7,
+                                                     (float)v[bb][4 * j]);
+                                acc[j] = fmaf(ds[bb][j], f, acc[j]);
+                            }
+                    }
+                }
+                // group 1 hands its sums to group 0
+                float *xb = xch + (ti & 1) * (8 * QS_ROWS);
+                if (h == 1) {
+#pragma unroll
+                    for (int j = 0; j < NT; j++) xb[j * QS_ROWS + row] = acc[j];
+                }
+                named_bar_sync(1, QS_SCALE_WARPS * 32);
+                const int r = (cta_in_slice + ti * ctas_per_slice) * QS_ROWS + row;
+                if (h == 0 && ok && r < a.n) {
+#pragma unroll
+                    for (int j = 0; j < NT; j++) {
+                        if (j < a.T) {
+                            const float v = acc[j] + xb[j * QS_ROWS + row];
+                            if (a.nslice == 1) a.dst[(size_t)j * a.ldo + r] = v + (a.bias ? a.bias[r] : 0.f);
+                            else a.dst[((size_t)slice * a.T + j) * a.n + r] = v;
+                        }
                     }
                 }
             }
@@ -425,14 +468,16 @@ __global__ void qs_reduce_kernel(const float *__restrict__ partial, float *__res
     out[(size_t)j * ldo + r] = v + (bias ? bias[r] : 0.f);
 }
 
-static size_t qs_smem_bytes(int fmt, int max_slice_st) {
-    return 1024 + (size_t)max_slice_st * QS_X_STAGE + (size_t)qs_raw_depth(fmt) * qs_stage_bytes(fmt) + 2 * 8 * QS_ROWS * sizeof(float) +
-           (2 * qs_raw_depth(fmt) + 2 * QS_NB + 5) * 8 + 16;
+static size_t qs_smem_bytes(int fmt, int nt, int max_slice_st) {
+    const int nrows = nt <= 4 ? 16 : 32;
+    return 1024 + (size_t)max_slice_st * nrows * 128 + (size_t)qs_raw_depth(fmt, nt) * qs_stage_bytes(fmt) + 2 * 8 * QS_ROWS * sizeof(float) +
+           (size_t)max_slice_st * QS_NB * nt * sizeof(float) + (2 * qs_raw_depth(fmt, nt) + 4 * 4 + 1) * 8 + 16;
 }
 
 template <int FMT, int NT>
-static int qs_launch(const QsArgs &a, int grid, size_t smem, cudaStream_t st) {
+static int qs_launch(const QsArgs &a, int grid, cudaStream_t st) {
     static size_t configured = 0;                // largest dynamic shared memory size requested so far
+    const size_t smem = qs_smem_bytes(FMT, NT, a.max_slice_st);
     if (smem > configured) {
         MB_CUDA(cudaFuncSetAttribute(qstream_tc_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
@@ -443,7 +488,7 @@ static int qs_launch(const QsArgs &a, int grid, size_t smem, cudaStream_t st) {
 }
 
 // Partial sums of the K slices go through w.tc_scratch (qstream_tc_scratch_bytes(n, k) bytes, allocated
-// with the weight): calls on one weight must not overlap in time.
+// with the weight): calls on one weight must not overlap in time. Activations must be finite.
 int qstream_tc(const QWeight &w, const float *x, int ldx, float *out, int ldo, const float *bias, int T, int *status,
                cudaStream_t st) {
     float *scratch = w.tc_scratch;
@@ -461,15 +506,14 @@ int qstream_tc(const QWeight &w, const float *x, int ldx, float *out, int ldo, c
     a.wt = w.tc_q; a.n = w.n; a.k = w.k; a.T = T; a.x = x; a.ldx = ldx; a.ldo = ldo; a.bias = bias;
     a.nslice = nslice; a.max_slice_st = cdiv(nst_total, nslice); a.status = status;
     a.dst = nslice == 1 ? out : scratch;
-    const size_t smem = qs_smem_bytes(w.fmt, a.max_slice_st);
     const int nt = T <= 1 ? 1 : T <= 2 ? 2 : T <= 4 ? 4 : 8;
     int rc;
     if (w.fmt == FMT_GGML_Q4_0)
-        rc = nt == 1 ? qs_launch<FMT_GGML_Q4_0, 1>(a, grid, smem, st) : nt == 2 ? qs_launch<FMT_GGML_Q4_0, 2>(a, grid, smem, st)
-           : nt == 4 ? qs_launch<FMT_GGML_Q4_0, 4>(a, grid, smem, st) : qs_launch<FMT_GGML_Q4_0, 8>(a, grid, smem, st);
+        rc = nt == 1 ? qs_launch<FMT_GGML_Q4_0, 1>(a, grid, st) : nt == 2 ? qs_launch<FMT_GGML_Q4_0, 2>(a, grid, st)
+           : nt == 4 ? qs_launch<FMT_GGML_Q4_0, 4>(a, grid, st) : qs_launch<FMT_GGML_Q4_0, 8>(a, grid, st);
     else
-        rc = nt == 1 ? qs_launch<FMT_GGML_Q8_0, 1>(a, grid, smem, st) : nt == 2 ? qs_launch<FMT_GGML_Q8_0, 2>(a, grid, smem, st)
-           : nt == 4 ? qs_launch<FMT_GGML_Q8_0, 4>(a, grid, smem, st) : qs_launch<FMT_GGML_Q8_0, 8>(a, grid, smem, st);
+        rc = nt == 1 ? qs_launch<FMT_GGML_Q8_0, 1>(a, grid, st) : nt == 2 ? qs_launch<FMT_GGML_Q8_0, 2>(a, grid, st)
+           : nt == 4 ? qs_launch<FMT_GGML_Q8_0, 4>(a, grid, st) : qs_launch<FMT_GGML_Q8_0, 8>(a, grid, st);
     if (rc) return rc;
     if (nslice > 1) {
         qs_reduce_kernel<<<dim3(cdiv(w.n, 256), T), 256, 0, st>>>(scratch, out, ldo, bias, w.n, T, nslice);

@@ -72,9 +72,9 @@ def test_small_T_streams_stored_blocks(gpu_pkg, synth, fmt, T):
 @pytest.mark.parametrize("fmt", ["q4_0", "q8_0"])
 def test_streaming_kernel_work_splits(gpu_pkg, synth, fmt):
     """Shapes that drive the tcgen05 streaming kernel through each of its work splits: several row
-    tiles per CTA (more tiles than multiprocessors), one K slice, many K slices, and K beyond what one
-    CTA holds (8192) with many tiles; ragged last tile everywhere."""
-    for n, k, Ts in ((20001, 256, (1, 5)), (19001, 128, (2,)), (300, 8192, (1, 8)), (9700, 8192, (1,)), (129, 1024, (3,))):
+    tiles per CTA (more tiles than multiprocessors), one K slice, many K slices, K beyond what one
+    CTA holds (8192) with many tiles, and long runs of stages per CTA at every read-back width; ragged last tile everywhere."""
+    for n, k, Ts in ((20001, 256, (1, 5)), (19001, 128, (2,)), (300, 8192, (1, 8)), (9700, 8192, (1,)), (19000, 4096, (4, 8)), (129, 1024, (3,))):
         q, wd = make(gpu_pkg, synth, fmt, n, k, seed=n)
         for T in Ts:
             x = np.random.default_rng(T).standard_normal((T, k)).astype(np.float32)
