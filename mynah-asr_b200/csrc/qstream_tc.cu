@@ -14,17 +14,19 @@
 //     quants and the four f16 block scales per row, laid out contiguously at load) from HBM
 //     into an 8-deep shared-memory ring with bulk asynchronous copies (cp.async.bulk, no multicast)
 //     tracked by mbarriers — 70-140 KB in flight per SM to cover HBM latency;
-//   * warps 8-23, four groups of four: group g handles block g of every stage. A thread owns one
+//   * warps 8-23, four groups of four: group g handles the stages g, g+4, ... A thread owns one
 //     weight row and moves its 32 integers into tensor memory with tcgen05.st, where they are the
 //     A operand: Q8_0 bytes go as they are, a Q4_0 word becomes two words of (q-8)*16 with three
-//     logic instructions. The weights never pass through shared memory a second time;
-//   * warps 1-4, one thread each: issuer g issues the tcgen05.mma (kind::i8, M = 128 weight rows,
-//     N = 16 or 32 plane rows, K = 32) of block g — one thread gets an MMA out every ~45 cycles
-//     whatever its size, so the small ones here need several issuers. B is the int8 planes of the
-//     activations, resident in shared memory for the CTA's K slice. Each block has its own
-//     accumulator columns, because d and 2^e multiply the block's dots afterwards;
-//   * warps 24-31, two groups of four: read the block dots back (tcgen05.ld; thread = weight row)
-//     and fold them into f32 accumulators;
+//     logic instructions; the row's four block scales follow into two more columns. The weights
+//     never pass through shared memory a second time and the ring slot is free again at once;
+//   * warps 1-4, one thread each: an issuer takes every fourth stage and issues its four
+//     tcgen05.mma (kind::i8, M = 128 weight rows, N = 16 or 32 plane rows, K = 32, one per block) —
+//     one thread gets an MMA out every ~45 cycles whatever its size, so the small ones here need
+//     several issuers. B is the int8 planes of the activations, resident in shared memory for the
+//     CTA's K slice. Each block has its own accumulator columns, because d and 2^e multiply the
+//     block's dots afterwards;
+//   * warps 24-31, two groups of four: read the block dots and scales back (tcgen05.ld; thread =
+//     weight row) and fold them into f32 accumulators;
 //   * every warp but the streamer's first splits its share of the activations into planes.
 // Large K, or few rows, are split over CTAs (fixed K slice per CTA, so its activations are staged
 // once); the slices are then summed in a fixed order by a second small kernel, so results are
@@ -40,12 +42,14 @@ static constexpr int QS_SK = 128;             // k per stage
 static constexpr int QS_NB = 4;               // 32-element blocks per stage
 static constexpr int QS_PLANES = 4;           // int8 planes per activation row
 static constexpr int QS_MAX_SLICE_ST = 32;    // stages of K per CTA slice (4096 k)
-static constexpr int QS_FIRST_ISSUER = 1;     // warps 1-4: one MMA issuer per block of the stage
+static constexpr int QS_FIRST_ISSUER = 1;     // warps 1-4: MMA issuers
 static constexpr int QS_FIRST_DECODE = 8, QS_DECODE_WARPS = 16;
 static constexpr int QS_FIRST_SCALE = 24, QS_SCALE_WARPS = 8;
 static constexpr int QS_THREADS = (QS_FIRST_SCALE + QS_SCALE_WARPS) * 32;     // 1024
 static constexpr int QS_A_COLS = 8;                           // tensor-memory columns of one decoded block (32 int8)
 static constexpr int QS_TMEM_COLS = 512;
+static constexpr int QS_SC_COL0 = 384;                        // eight 2-column slots: the four f16 block scales of a row
+static constexpr int QS_SC_SLOTS = 8;
 static constexpr int QS_SCALE_BYTES = QS_NB * QS_ROWS * 2;    // 1 KB of f16 block scales per stage
 
 __host__ __device__ constexpr int qs_quant_bytes(int fmt) { return fmt == FMT_GGML_Q4_0 ? QS_ROWS * QS_SK / 2 : QS_ROWS * QS_SK; }
@@ -54,7 +58,7 @@ __host__ __device__ constexpr int qs_stage_bytes(int fmt) { return qs_quant_byte
 __host__ __device__ constexpr int qs_raw_depth(int fmt, int nt) { return (fmt == FMT_GGML_Q8_0 && nt == 8) ? 4 : 8; }
 
 // -------------------------------------------------------------------- re-tiling at load
-// [tile][stage][ quants: [16-byte chunk c][row 0..127][16 B] | scales: [block 0..3][row 0..127] f16 ]
+// [tile][stage][ quants: [16-byte chunk c][row 0..127][16 B] | scales: [row 0..127][block 0..3] f16 ]
 // Q4_0: chunk c is block c (32 nibbles); Q8_0: chunks 2b, 2b+1 are the halves of block b.
 // A decode warp reads consecutive 16-byte pieces: conflict-free 128-bit shared loads.
 __global__ void qs_retile_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ dst, int n, int k, int fmt) {
@@ -67,7 +71,7 @@ __global__ void qs_retile_kernel(const uint8_t *__restrict__ raw, uint8_t *__res
     uint8_t *stage = dst + ((size_t)tile * (k / QS_SK) + st) * qs_stage_bytes(fmt);
     const uint8_t *p = raw + b * (qb + 2);
     for (int i = 0; i < qb; i++) stage[((bs * (qb / 16) + i / 16) * QS_ROWS + rl) * 16 + (i & 15)] = p[2 + i];
-    uint8_t *sc = stage + qs_quant_bytes(fmt) + (bs * QS_ROWS + rl) * 2;
+    uint8_t *sc = stage + qs_quant_bytes(fmt) + (rl * QS_NB + bs) * 2;
     sc[0] = p[0];
     sc[1] = p[1];
 }
@@ -134,6 +138,12 @@ __device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t *r) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                  : "memory");
+}
+__device__ __forceinline__ void tc_st2(uint32_t taddr, uint32_t r0, uint32_t r1) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(r0), "r"(r1) : "memory");
+}
+__device__ __forceinline__ void tc_ld2(uint32_t taddr, uint32_t &r0, uint32_t &r1) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(taddr) : "memory");
 }
 // 32 registers per thread -> 32 lanes x 32 consecutive columns of tensor memory
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t *r) {
@@ -236,9 +246,9 @@ qstream_tc_kernel(const QsArgs a) {
     const int total = my_tiles * nst;                                      // stages this CTA works through
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < DEPTH; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4 + 4); }   // one decode, one read-back group
-        for (int i = 0; i < AP; i++) { mbar_init(&a_full[i], 4); mbar_init(&a_free[i], QS_NB); }
-        for (int i = 0; i < DP; i++) { mbar_init(&d_full[i], QS_NB); mbar_init(&d_free[i], 4); }
+        for (int i = 0; i < DEPTH; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4); }   // the four warps of one decode group
+        for (int i = 0; i < AP; i++) { mbar_init(&a_full[i], 4); mbar_init(&a_free[i], 1); }
+        for (int i = 0; i < DP; i++) { mbar_init(&d_full[i], 1); mbar_init(&d_free[i], 4); }
         mbar_init(x_full, QS_THREADS / 32 - 1);
         mbar_fence_init();
     }
@@ -311,24 +321,29 @@ qstream_tc_kernel(const QsArgs a) {
         __syncwarp();
         if (lane == 0) mbar_arrive(x_full);
 
-        if (warp >= QS_FIRST_ISSUER && warp < QS_FIRST_ISSUER + QS_NB) {
+        if (warp >= QS_FIRST_ISSUER && warp < QS_FIRST_ISSUER + DP) {
             if (lane == 0 && total > 0) {
-                // ------------------------------------------------------ MMA issuer of block b
-                const int b = warp - QS_FIRST_ISSUER;
+                // ------------------------------------------------------ MMA issuer of the stages i, i+DP, ...
+                // (an issuer returns to its own accumulator slot, and to an A slot only after the decode
+                // group that fills it has been there, so no barrier is ever more than a phase ahead)
+                const int i = warp - QS_FIRST_ISSUER;
                 bool ok = mbar_wait(x_full, 0);
-                const uint64_t bdesc0 = umma_desc_sw128(smem_u32(x_tile)) + (uint64_t)((b * 32) >> 4);
+                const uint64_t bdesc0 = umma_desc_sw128(smem_u32(x_tile));
                 constexpr uint32_t idesc = qs_idesc_i8(QS_ROWS, N);
-                int st = 0;
-                for (int it = 0; it < total && ok; it++) {
-                    const int as = it & (AP - 1), par = it & (DP - 1);
+                int st = i % nst;
+                for (int it = i; it < total && ok; it += DP) {
+                    const int as = it & (AP - 1);
                     if (!mbar_wait(&a_full[as], (uint32_t)((it / AP) & 1))) { ok = false; break; }
-                    if (it >= DP && !mbar_wait(&d_free[par], (uint32_t)(((it / DP) & 1) ^ 1))) { ok = false; break; }
+                    if (it >= DP && !mbar_wait(&d_free[i], (uint32_t)(((it / DP) & 1) ^ 1))) { ok = false; break; }
                     tc_fence_after();
-                    tc_mma_i8_ts(tmem_base + D_COL0 + par * DST + b * N, tmem_base + (as * QS_NB + b) * QS_A_COLS,
-                                 bdesc0 + (uint64_t)((st * XT) >> 4), idesc, 0);
+                    const uint64_t bd = bdesc0 + (uint64_t)((st * XT) >> 4);
+#pragma unroll
+                    for (int b = 0; b < QS_NB; b++)
+                        tc_mma_i8_ts(tmem_base + D_COL0 + i * DST + b * N, tmem_base + (as * QS_NB + b) * QS_A_COLS, bd + (uint64_t)(2 * b), idesc, 0);
                     if (DP != AP) tc_commit(&a_free[as]);
-                    tc_commit(&d_full[par]);
-                    if (++st == nst) st = 0;
+                    tc_commit(&d_full[i]);
+                    st += DP;
+                    while (st >= nst) st -= nst;
                 }
                 if (!ok) atomicExch(a.status, ST_TIMEOUT_MMA);
             }
@@ -367,6 +382,8 @@ qstream_tc_kernel(const QsArgs a) {
                     }
                 }
                 tc_st32(tdst + g * AST, r);
+                const uint2 sc = *reinterpret_cast<const uint2 *>(raw + rs * SB + QBYTES + row * (QS_NB * 2));
+                tc_st2(tdst + QS_SC_COL0 + (it & (QS_SC_SLOTS - 1)) * 2, sc.x, sc.y);   // slot it-8 was read before the MMAs of it-4 could start
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -391,36 +408,35 @@ qstream_tc_kernel(const QsArgs a) {
                 for (int j = 0; j < NT; j++) acc[j] = 0.f;
                 for (int st = 0; st < nst; st++, it++) {
                     if ((it & 1) != h) continue;
-                    const int par = it & (DP - 1), rs = it & (DEPTH - 1);
+                    const int par = it & (DP - 1);
                     const uint32_t uph = (uint32_t)((it / DP) & 1);
-                    if (ok) {
-                        bool w = mbar_wait(&d_full[par], uph);
-                        if (w) w = mbar_wait(&raw_full[rs], (uint32_t)((it / DEPTH) & 1));   // completed long ago; orders the scale reads
-                        if (!__all_sync(0xffffffffu, w)) { ok = false; if (lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE); }
-                    }
+                    if (ok && !__all_sync(0xffffffffu, mbar_wait(&d_full[par], uph))) { ok = false; if (lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE); }
                     if (!ok) continue;
                     tc_fence_after();
-                    const __half *dp = reinterpret_cast<const __half *>(raw + rs * SB + QBYTES) + row;
+                    uint32_t sc0, sc1;                       // the row's four f16 block scales, left by the decode warps
+                    tc_ld2(tsrc - D_COL0 + QS_SC_COL0 + (it & (QS_SC_SLOTS - 1)) * 2, sc0, sc1);
                     float d[QS_NB];
-#pragma unroll
-                    for (int b = 0; b < QS_NB; b++) d[b] = __half2float(dp[b * QS_ROWS]) * DQ;
 #pragma unroll
                     for (int b0 = 0; b0 < QS_NB; b0 += BPL) {
                         int v[BPL][NCOL];
 #pragma unroll
                         for (int bb = 0; bb < BPL; bb++) tc_ldn<NCOL>(tsrc + par * DST + (b0 + bb) * N, v[bb]);
+                        tc_wait_ld();
+                        if (b0 == 0) {
+                            const __half2 h01 = *reinterpret_cast<const __half2 *>(&sc0), h23 = *reinterpret_cast<const __half2 *>(&sc1);
+                            d[0] = __low2float(h01) * DQ; d[1] = __high2float(h01) * DQ; d[2] = __low2float(h23) * DQ; d[3] = __high2float(h23) * DQ;
+                        }
+                        if (b0 + BPL == QS_NB) {             // the whole stage is in registers: its accumulators may be reused
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&d_free[par]);
+                        }
                         float ds[BPL][NT];
 #pragma unroll
                         for (int bb = 0; bb < BPL; bb++) {
                             const float *sp = sxs + (st * QS_NB + b0 + bb) * NT;
 #pragma unroll
                             for (int j = 0; j < NT; j++) ds[bb][j] = d[b0 + bb] * sp[j];
-                        }
-                        tc_wait_ld();
-                        if (b0 + BPL == QS_NB) {             // the whole stage is in registers: accumulators and bytes may be reused
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) { mbar_arrive(&d_free[par]); mbar_arrive(&raw_empty[rs]); }
                         }
 #pragma unroll
                         for (int bb = 0; bb < BPL; bb++)
