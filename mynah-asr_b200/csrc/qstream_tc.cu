@@ -10,10 +10,11 @@
 // out += d * 2^e * (v0 + v1/2^7 + v2/2^14 + v3/2^21). No product is ever rounded before that fold.
 //
 // Per CTA (persistent, one per SM), 32 warps with fixed roles:
-//   * warp 0, one thread: streams the stored bytes of a stage (128 weight rows x 128 k: the
-//     quants and the four f16 block scales per row, laid out contiguously at load) from HBM
-//     into an 8-deep shared-memory ring with bulk asynchronous copies (cp.async.bulk, no multicast)
-//     tracked by mbarriers — 70-140 KB in flight per SM to cover HBM latency;
+//   * warps 0 and 5-7, one thread each: stream the stored bytes of every fourth stage (128 weight
+//     rows x 128 k: the quants and the four f16 block scales per row, laid out contiguously at
+//     load) from HBM into a shared-memory ring (4 to 16 stages deep) with bulk asynchronous copies
+//     (cp.async.bulk, no multicast) tracked by mbarriers — 70-140 KB in flight per SM to cover HBM
+//     latency. One thread needs ~400 cycles per copy it starts, more than a stage may take;
 //   * warps 8-23, four groups of four: group g handles the stages g, g+4, ... A thread owns one
 //     weight row and moves its 32 integers into tensor memory with tcgen05.st, where they are the
 //     A operand: Q8_0 bytes go as they are, a Q4_0 word becomes two words of (q-8)*16 with three
@@ -27,7 +28,7 @@
 //     block's dots afterwards;
 //   * warps 24-31, two groups of four: read the block dots and scales back (tcgen05.ld; thread =
 //     weight row) and fold them into f32 accumulators;
-//   * every warp but the streamer's first splits its share of the activations into planes.
+//   * every warp but the streamers' first splits its share of the activations into planes.
 // Large K, or few rows, are split over CTAs (fixed K slice per CTA, so its activations are staged
 // once); the slices are then summed in a fixed order by a second small kernel, so results are
 // reproducible and a row's result does not depend on T. Every mbarrier wait is bounded; a wait
@@ -42,6 +43,7 @@ static constexpr int QS_SK = 128;             // k per stage
 static constexpr int QS_NB = 4;               // 32-element blocks per stage
 static constexpr int QS_PLANES = 4;           // int8 planes per activation row
 static constexpr int QS_MAX_SLICE_ST = 32;    // stages of K per CTA slice (4096 k)
+static constexpr int QS_STREAMERS = 4;        // warps 0, 5, 6, 7
 static constexpr int QS_FIRST_ISSUER = 1;     // warps 1-4: MMA issuers
 static constexpr int QS_FIRST_DECODE = 8, QS_DECODE_WARPS = 16;
 static constexpr int QS_FIRST_SCALE = 24, QS_SCALE_WARPS = 8;
@@ -54,8 +56,9 @@ static constexpr int QS_SCALE_BYTES = QS_NB * QS_ROWS * 2;    // 1 KB of f16 blo
 
 __host__ __device__ constexpr int qs_quant_bytes(int fmt) { return fmt == FMT_GGML_Q4_0 ? QS_ROWS * QS_SK / 2 : QS_ROWS * QS_SK; }
 __host__ __device__ constexpr int qs_stage_bytes(int fmt) { return qs_quant_bytes(fmt) + QS_SCALE_BYTES; }
-// stored-byte stages in flight (a power of two); 8 rows of Q8_0 planes leave room for 4
-__host__ __device__ constexpr int qs_raw_depth(int fmt, int nt) { return (fmt == FMT_GGML_Q8_0 && nt == 8) ? 4 : 8; }
+// stored-byte stages in flight (a power of two): what fits beside 4096 k of activation planes
+// (64 KB for up to 4 rows, 128 KB for 8) — 144 / 72 KB of Q4_0, 136 / 68 KB of Q8_0
+__host__ __device__ constexpr int qs_raw_depth(int fmt, int nt) { return (fmt == FMT_GGML_Q4_0 ? 16 : 8) / (nt == 8 ? 2 : 1); }
 
 // -------------------------------------------------------------------- re-tiling at load
 // [tile][stage][ quants: [16-byte chunk c][row 0..127][16 B] | scales: [row 0..127][block 0..3] f16 ]
@@ -249,7 +252,7 @@ qstream_tc_kernel(const QsArgs a) {
         for (int i = 0; i < DEPTH; i++) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], 4); }   // the four warps of one decode group
         for (int i = 0; i < AP; i++) { mbar_init(&a_full[i], 4); mbar_init(&a_free[i], 1); }
         for (int i = 0; i < DP; i++) { mbar_init(&d_full[i], 1); mbar_init(&d_free[i], 4); }
-        mbar_init(x_full, QS_THREADS / 32 - 1);
+        mbar_init(x_full, QS_THREADS / 32 - QS_STREAMERS);
         mbar_fence_init();
     }
     if (warp == QS_FIRST_ISSUER) { tc_alloc(tmem_slot, QS_TMEM_COLS); tc_relinquish(); }
@@ -258,23 +261,24 @@ qstream_tc_kernel(const QsArgs a) {
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
+    if (warp == 0 || (warp > QS_FIRST_ISSUER + 3 && warp < QS_FIRST_DECODE)) {
         if (lane == 0) {
-            // ---------------------------------------------------------- byte streamer
-            int it = 0;
+            // ---------------------------------------------------------- byte streamer of the stages s, s+4, ...
+            // (DEPTH is a multiple of 4, so a streamer keeps to its own ring slots)
+            const int s = warp == 0 ? 0 : warp - QS_FIRST_ISSUER - 3;
+            int ti = s / nst, st = s - ti * nst, it = s;
             bool ok = true;
-            for (int ti = 0; ti < my_tiles && ok; ti++) {
-                const uint8_t *src = a.wt + ((size_t)(cta_in_slice + ti * ctas_per_slice) * nst_total + s0) * SB;
-                for (int st = 0; st < nst; st++, it++) {
-                    const int rs = it & (DEPTH - 1);
-                    if (it >= DEPTH && !mbar_wait(&raw_empty[rs], (uint32_t)(((it / DEPTH) & 1) ^ 1))) { ok = false; break; }
-                    mbar_expect_tx(&raw_full[rs], SB);
-                    bulk_load(raw + rs * SB, src + (size_t)st * SB, SB, &raw_full[rs]);
-                }
+            for (; it < total; it += QS_STREAMERS) {
+                const int rs = it & (DEPTH - 1);
+                if (it >= DEPTH && !mbar_wait(&raw_empty[rs], (uint32_t)(((it / DEPTH) & 1) ^ 1))) { ok = false; break; }
+                mbar_expect_tx(&raw_full[rs], SB);
+                bulk_load(raw + rs * SB, a.wt + ((size_t)(cta_in_slice + ti * ctas_per_slice) * nst_total + s0 + st) * SB, SB, &raw_full[rs]);
+                st += QS_STREAMERS;
+                while (st >= nst) { st -= nst; ti++; }
             }
             if (!ok) atomicExch(a.status, ST_TIMEOUT_PRODUCER);
             // every copy this thread started has to land before the CTA may exit
-            for (int j = it > DEPTH ? it - DEPTH : 0; j < it; j++) mbar_wait(&raw_full[j & (DEPTH - 1)], (uint32_t)((j / DEPTH) & 1));
+            for (int j = it - QS_STREAMERS; j >= s && j >= it - DEPTH; j -= QS_STREAMERS) mbar_wait(&raw_full[j & (DEPTH - 1)], (uint32_t)((j / DEPTH) & 1));
         }
     } else {
         // ---- every other warp first splits its share of this slice's activations into int8 planes
@@ -283,8 +287,8 @@ qstream_tc_kernel(const QsArgs a) {
         // Plane rows past 4T stay as they are: their accumulator columns are never written out.
         const int units = a.T * nst;
         const float *xs = a.x + (size_t)s0 * QS_SK;
-        constexpr int NW = QS_THREADS / 32 - 1;
-        for (int u0 = warp - 1; u0 < units; u0 += 2 * NW) {
+        constexpr int NW = QS_THREADS / 32 - QS_STREAMERS;
+        for (int u0 = warp < QS_FIRST_DECODE ? warp - 1 : warp - QS_STREAMERS; u0 < units; u0 += 2 * NW) {
             float v[2][4];
 #pragma unroll
             for (int uu = 0; uu < 2; uu++) {
@@ -356,11 +360,7 @@ qstream_tc_kernel(const QsArgs a) {
             const uint32_t tdst = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
             for (int it = g; it < total; it += AP) {
                 const int rs = it & (DEPTH - 1);
-                bool ok = mbar_wait(&raw_full[rs], (uint32_t)((it / DEPTH) & 1));
-                // the MMAs of stage it-AP, the last user of A slot g, must be done
-                if (ok && it >= AP) ok = mbar_wait(DP == AP ? &d_full[g] : &a_free[g], (uint32_t)(((it / AP) & 1) ^ 1));
-                if (!__all_sync(0xffffffffu, ok)) { if (lane == 0) atomicExch(a.status, ST_TIMEOUT_PRODUCER); break; }
-                tc_fence_after();
+                if (!__all_sync(0xffffffffu, mbar_wait(&raw_full[rs], (uint32_t)((it / DEPTH) & 1)))) { if (lane == 0) atomicExch(a.status, ST_TIMEOUT_PRODUCER); break; }
                 const uint8_t *src = raw + rs * SB + row * 16;
                 uint32_t r[QS_NB * QS_A_COLS];
                 if (FMT == FMT_GGML_Q4_0) {
@@ -381,8 +381,15 @@ qstream_tc_kernel(const QsArgs a) {
                         r[4 * c] = q.x; r[4 * c + 1] = q.y; r[4 * c + 2] = q.z; r[4 * c + 3] = q.w;
                     }
                 }
-                tc_st32(tdst + g * AST, r);
                 const uint2 sc = *reinterpret_cast<const uint2 *>(raw + rs * SB + QBYTES + row * (QS_NB * 2));
+                // only now is A slot g needed: the MMAs of stage it-AP, its last user, must be done
+                // (the loads and the unpacking above are off the slot's critical path)
+                if (it >= AP && !__all_sync(0xffffffffu, mbar_wait(DP == AP ? &d_full[g] : &a_free[g], (uint32_t)(((it / AP) & 1) ^ 1)))) {
+                    if (lane == 0) atomicExch(a.status, ST_TIMEOUT_PRODUCER);
+                    break;
+                }
+                tc_fence_after();
+                tc_st32(tdst + g * AST, r);
                 tc_st2(tdst + QS_SC_COL0 + (it & (QS_SC_SLOTS - 1)) * 2, sc.x, sc.y);   // slot it-8 was read before the MMAs of it-4 could start
                 tc_wait_st();
                 tc_fence_before();
@@ -406,8 +413,9 @@ qstream_tc_kernel(const QsArgs a) {
                 float acc[NT];
 #pragma unroll
                 for (int j = 0; j < NT; j++) acc[j] = 0.f;
-                for (int st = 0; st < nst; st++, it++) {
-                    if ((it & 1) != h) continue;
+                const int it_end = it + nst;
+                int st = (it & 1) != h;                      // this group's first stage of the tile
+                for (it += st; it < it_end; it += 2, st += 2) {
                     const int par = it & (DP - 1);
                     const uint32_t uph = (uint32_t)((it / DP) & 1);
                     if (ok && !__all_sync(0xffffffffu, mbar_wait(&d_full[par], uph))) { ok = false; if (lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE); }
@@ -448,6 +456,7 @@ qstream_tc_kernel(const QsArgs a) {
                             }
                     }
                 }
+                it = it_end;
                 // group 1 hands its sums to group 0
                 float *xb = xch + (ti & 1) * (8 * QS_ROWS);
                 if (h == 1) {
