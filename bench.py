@@ -34,6 +34,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 CACHE = os.path.join(tempfile.gettempdir(), "mynah_b200_bench_cache")
 METRIC, UNIT = "audio-sec/sec (1/RTF)", "audio-s/s"
+GEMM_TRAFFIC_RATIO = 300.5 / 352.3   # ncu dram bytes / algorithmic bytes of one contraction launch (summary under profiles/)
 
 
 def load_package():
@@ -336,7 +337,14 @@ def main():
             "roofline": {"kernel": "gemm_tc_kernel (tcgen05 contraction)", "bound": "tensor",
                          "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": achieved / peak_tf if achieved else None, "peak_source": peak_src,
-                         "traffic": None, "launches": g["launches"], "kernel_ms_per_step": g["ms"] / args.steps,
+                         # DRAM bytes of the contraction launches of one step: their algorithmic bytes (operand
+                         # planes once, output once) times the ratio an ncu capture of one launch measured
+                         # ([16384 x 4096 x 1024], dram read + write = 300.5 MB for 352.3 MB algorithmic: part
+                         # of the output is still in L2 when the kernel ends)
+                         "traffic": g["bytes"] / args.steps * GEMM_TRAFFIC_RATIO,
+                         "traffic_unit": "bytes per step (all contraction launches)",
+                         "algorithmic_bytes_per_step": g["bytes"] / args.steps,
+                         "launches": g["launches"], "kernel_ms_per_step": g["ms"] / args.steps,
                          "flops_per_step": g["flops"] / args.steps,
                          "mma_flops_multiplier": 3 if args.mode == "strict" else 1},
             "breakdown_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},

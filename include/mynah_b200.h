@@ -175,6 +175,9 @@ void *mynah_b200_model_stream(mynah_b200_model *m);
  * milliseconds, the algorithmic flops (contractions: 2*M*N*K) and the number of launches. */
 void mynah_b200_profile_begin(mynah_b200_model *m);
 int mynah_b200_profile_end(mynah_b200_model *m, double *ms, double *flops, long long *launches, int ncat);
+/* Algorithmic DRAM bytes of the launches since profile_begin, per category (filled for the
+ * contractions: both operands' fp16 planes read once, the output and any residual once). */
+void mynah_b200_profile_bytes(mynah_b200_model *m, double *bytes, int ncat);
 /* Phase clocks (SM cycles seen by CTA 0) of the last greedy-decoder launch made while profiling was
  * on: head, head barrier, select + barrier, LSTM layers + barriers, projector + barrier, then the
  * number of steps and of steps in which some utterance emitted. */

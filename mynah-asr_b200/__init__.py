@@ -71,6 +71,7 @@ def lib():
     L.mynah_b200_qmat_time.argtypes = [vp, ci, ci, ci]
     L.mynah_b200_profile_begin.argtypes = [vp]
     L.mynah_b200_profile_end.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_longlong), ci]
+    L.mynah_b200_profile_bytes.argtypes = [vp, C.POINTER(C.c_double), ci]
     L.mynah_b200_decoder_clocks.argtypes = [vp, C.POINTER(C.c_longlong)]
     L.mynah_b200_model_new.restype = vp
     L.mynah_b200_model_new.argtypes = [C.POINTER(Config)]
@@ -264,7 +265,9 @@ class Model:
         n = len(self.PROFILE_CATEGORIES)
         ms, fl, ln = (C.c_double * n)(), (C.c_double * n)(), (C.c_longlong * n)()
         _check(lib().mynah_b200_profile_end(self.h, ms, fl, ln, n), "profile_end")
-        return {c: {"ms": ms[i], "flops": fl[i], "launches": ln[i]} for i, c in enumerate(self.PROFILE_CATEGORIES)}
+        by = (C.c_double * n)()
+        lib().mynah_b200_profile_bytes(self.h, by, n)
+        return {c: {"ms": ms[i], "flops": fl[i], "launches": ln[i], "bytes": by[i]} for i, c in enumerate(self.PROFILE_CATEGORIES)}
 
     def decoder_clocks(self):
         out = (C.c_longlong * 8)()

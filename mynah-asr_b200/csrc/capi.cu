@@ -790,6 +790,10 @@ int mynah_b200_profile_end(mynah_b200_model *h, double *ms, double *flops, long 
     return 0;
 }
 
+void mynah_b200_profile_bytes(mynah_b200_model *h, double *bytes, int ncat) {
+    for (int i = 0; i < ncat; i++) bytes[i] = (h && i < Model::PROF_NCAT) ? h->m.prof_bytes[i] : 0.0;
+}
+
 void mynah_b200_decoder_clocks(mynah_b200_model *h, long long *out8) {
     for (int i = 0; i < 8; i++) out8[i] = h ? h->m.dec_dbg[i] : 0;
 }

@@ -156,7 +156,14 @@ int Model::gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep,
     const int sp = prof_begin_span(PROF_GEMM);
     const int rc = gemm_tc(A, B, ep, M, w.n, w.k, cfg.strict ? 3 : 1, status, stream);
     prof_end_span(sp);
-    if (sp >= 0) { prof_flops[PROF_GEMM] += 2.0 * M * (double)w.n * w.k; prof_launches[PROF_GEMM]++; }
+    if (sp >= 0) {
+        prof_flops[PROF_GEMM] += 2.0 * M * (double)w.n * w.k;
+        // operand planes read once (fp16 hi, and lo in strict mode) + what the epilogue reads and writes
+        const double planes = cfg.strict ? 4.0 : 2.0;
+        const double out_b = ep.mode == OUT_H16 ? (cfg.strict ? 4.0 : 2.0) : ep.mode == OUT_F32_H16 ? 8.0 : ep.mode == OUT_RESID ? 8.0 : 4.0;
+        prof_bytes[PROF_GEMM] += planes * ((double)M * w.k + (double)w.n * w.k) + out_b * M * (double)w.n;
+        prof_launches[PROF_GEMM]++;
+    }
     if (rc == 0) note_launch();
     return rc;
 }
