@@ -153,7 +153,7 @@ class ModelConfig:
     n_mels: int = 80
     channels: int = 256
     causal: bool = False          # Nemotron-style causal convs + LayerNorm conv norm
-    decoder: str = "ctc"          # "ctc" | "rnnt" | "tdt"
+    decoder: str = "ctc"          # "ctc" | "rnnt" | "tdt" | "aed"
     vocab: int = 129              # includes blank (last index for CTC; blank_id = vocab-1)
     pred_hidden: int = 640
     pred_layers: int = 1
@@ -166,10 +166,20 @@ class ModelConfig:
     normalize: bool = True        # per_feature mel normalisation (Parakeet); NA for Nemotron
     left: int = -1
     right: int = -1
+    # AED (Canary-style transformer decoder, src/decoder_aed.h)
+    aed_d: int = 0                # decoder width; != d_model adds enc_dec_proj
+    aed_layers: int = 4
+    aed_heads: int = 8
+    aed_ffn: int = 0
+    aed_max_seq: int = 1024
+    aed_max_gen_delta: int = 50
     d_out: int = field(init=False, default=0)
 
     def __post_init__(self):
-        self.d_out = self.d_model if self.decoder == "ctc" else self.pred_hidden
+        self.d_out = self.d_model if self.decoder in ("ctc", "aed") else self.pred_hidden
+        if self.decoder == "aed":
+            self.aed_d = self.aed_d or self.d_model
+            self.aed_ffn = self.aed_ffn or 4 * self.aed_d
 
 
 CONFIGS = {
@@ -188,6 +198,9 @@ CONFIGS = {
     "cfg3": dict(name="cfg3", d_model=1024, n_layers=24, n_heads=8, ffn_dim=4096, n_mels=128,
                  causal=True, decoder="rnnt", vocab=1025, pred_hidden=640, pred_layers=1,
                  wtype="q8_0", normalize=False, left=70, right=0),
+    # Canary-1B-shaped AED, Q8_0
+    "cfg4": dict(name="cfg4", d_model=1024, n_layers=32, n_heads=8, ffn_dim=4096, n_mels=128,
+                 decoder="aed", vocab=16384, aed_layers=4, aed_heads=8, aed_ffn=4096, wtype="q8_0"),
 }
 
 
@@ -285,6 +298,34 @@ def make_model(cfg: ModelConfig, seed: int = 0, weight_std: float = 0.02):
 
     if cfg.decoder == "ctc":
         f32t("ctc_head.weight", normal(cfg.vocab, d, 1)); f32t("ctc_head.bias", np.zeros(cfg.vocab))
+    elif cfg.decoder == "aed":
+        # tensor names as mynah_asr_aed_init resolves them (src/decoder_aed.c:50-113)
+        D, V, FA = cfg.aed_d, cfg.vocab, cfg.aed_ffn
+        f32t("aed.embedding.weight", rng.standard_normal((V, D), dtype=np.float32))
+        pos = np.arange(cfg.aed_max_seq, dtype=np.float64)[:, None] / (10000.0 ** (2 * (np.arange(D) // 2) / D))[None, :]
+        pe = np.where(np.arange(D)[None, :] % 2 == 0, np.sin(pos), np.cos(pos)) / np.sqrt(D)
+        f32t("aed.pos_enc", pe.astype(np.float32))
+        for nm in ("aed.emb_norm", "aed.final_norm"):
+            f32t(nm + ".weight", 1.0 + 0.1 * rng.standard_normal(D, dtype=np.float32)); f32t(nm + ".bias", normal(D))
+        qlin("aed.head.weight", V, D)
+        f32t("aed.head.bias", normal(V))
+        if D != d:
+            qlin("enc_dec_proj.weight", D, d)
+            f32t("enc_dec_proj.bias", normal(D))
+        for li in range(cfg.aed_layers):
+            p = f"aed.layers.{li}."
+            for nm in ("ln_self", "ln_cross", "ln_ffn"):
+                f32t(p + nm + ".weight", 1.0 + 0.1 * rng.standard_normal(D, dtype=np.float32)); f32t(p + nm + ".bias", normal(D))
+            for att in ("self_attn", "cross_attn"):
+                for nm in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                    # attention logits of a random model are tiny; a larger scale makes the softmax selective
+                    w = rng.standard_normal((D, D), dtype=np.float32) * np.float32(4.0 / np.sqrt(D) if nm in ("q_proj", "k_proj") else 1.0 / np.sqrt(D))
+                    gt = GGML_NAMES[cfg.wtype]
+                    T[p + f"{att}.{nm}.weight"] = Tensor(p + f"{att}.{nm}.weight", gt, (D, D), QUANTIZERS[gt](w)) if gt != GGML_F32 \
+                        else Tensor(p + f"{att}.{nm}.weight", GGML_F32, (D, D), w)
+                    f32t(p + f"{att}.{nm}.bias", normal(D))
+            qlin(p + "ffn.linear1.weight", FA, D); f32t(p + "ffn.linear1.bias", normal(FA))
+            qlin(p + "ffn.linear2.weight", D, FA, True); f32t(p + "ffn.linear2.bias", normal(D))
     else:
         H, V, ND = cfg.pred_hidden, cfg.vocab, len(cfg.durations)
         f32t("encoder_projector.weight", rng.standard_normal((H, d), dtype=np.float32) / np.sqrt(d))

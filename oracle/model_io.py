@@ -78,6 +78,24 @@ def oracle_model(cfg, tensors) -> dict:
                     "head_w": W["joint.head.weight"], "head_b": W["joint.head.bias"],
                     "vocab": cfg.vocab, "blank": cfg.vocab - 1, "max_symbols": cfg.max_symbols,
                     "durations": list(cfg.durations)}
+    if "aed.embedding.weight" in W:
+        A = {"emb": W["aed.embedding.weight"], "pos": W["aed.pos_enc"], "embln_w": W["aed.emb_norm.weight"],
+             "embln_b": W["aed.emb_norm.bias"], "fin_w": W["aed.final_norm.weight"], "fin_b": W["aed.final_norm.bias"],
+             "head_w": W["aed.head.weight"], "head_b": W["aed.head.bias"], "n_heads": cfg.aed_heads,
+             "max_seq": cfg.aed_max_seq, "proj_w": W.get("enc_dec_proj.weight"), "proj_b": W.get("enc_dec_proj.bias"),
+             "layers": []}
+        for li in range(cfg.aed_layers):
+            p = f"aed.layers.{li}."
+            L = {}
+            for nm in ("ln_self", "ln_cross", "ln_ffn"):
+                L[nm + "_w"], L[nm + "_b"] = W[p + nm + ".weight"], W[p + nm + ".bias"]
+            for pre, att in (("s", "self_attn"), ("c", "cross_attn")):
+                for c in "qkvo":
+                    L[pre + c + "_w"], L[pre + c + "_b"] = W[p + f"{att}.{c}_proj.weight"], W[p + f"{att}.{c}_proj.bias"]
+            for i in (1, 2):
+                L[f"ff{i}_w"], L[f"ff{i}_b"] = W[p + f"ffn.linear{i}.weight"], W[p + f"ffn.linear{i}.bias"]
+            A["layers"].append(L)
+        M["aed"] = A
     return M
 
 

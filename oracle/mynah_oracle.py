@@ -506,3 +506,73 @@ def greedy_decode(D, enc):
             _lstm_pred_step(D, st, k)
         t += 1
     return toks, frames
+
+
+# ------------------------------------------------------------------ AED decoder
+def _aed_ln(x, w, b):
+    """ln of src/decoder_aed.c:24-31: mean / variance in double, eps 1e-5."""
+    x64 = x.astype(np.float64)
+    mu = x64.mean()
+    var = ((x64 - mu) ** 2).mean()
+    inv = np.float32(1.0 / np.sqrt(var + 1e-5))
+    return ((x64 - mu) * inv).astype(np.float32) * w + b
+
+
+def _aed_attend(q, K, V, H):
+    """attend of src/decoder_aed.c:117-131: one query over n_kv keys, per head,
+    scores scaled by 1/sqrt(dk), f32 softmax."""
+    d = q.shape[0]
+    dk = d // H
+    out = np.empty(d, np.float32)
+    scale = np.float32(1.0 / np.sqrt(np.float32(dk)))
+    for h in range(H):
+        sl = slice(h * dk, (h + 1) * dk)
+        sc = (K[:, sl] @ q[sl]).astype(np.float32) * scale
+        e = np.exp(sc - sc.max(), dtype=np.float32)
+        pr = e * np.float32(1.0 / e.sum(dtype=np.float32))
+        out[sl] = pr @ V[:, sl]
+    return out
+
+
+def aed_decode(A, enc, prompt, eos, cap):
+    """mynah_asr_aed_decode (src/decoder_aed.c:139-232): greedy autoregressive decode of the
+    pre-LN transformer decoder; returns the generated tokens (prompt and EOS excluded).
+    A: dict with emb, pos, embln_w/b, fin_w/b, head_w/b, optional proj_w/b, n_heads, max_seq and
+    layers[...] of ln_{self,cross,ffn}_w/b, s{q,k,v,o}_w/b, c{q,k,v,o}_w/b, ff1_w/b, ff2_w/b."""
+    H = A["n_heads"]
+    prompt = list(prompt)
+    if not prompt:
+        return None
+    max_len = min(len(prompt) + cap, A["max_seq"])                      # :144-146
+    encp = gemm_wt(enc, A["proj_w"]) + A["proj_b"] if A.get("proj_w") is not None else enc     # :149-157
+    cross = [(gemm_wt(encp, L["ck_w"]) + L["ck_b"], gemm_wt(encp, L["cv_w"]) + L["cv_b"]) for L in A["layers"]]   # :171-178
+    d = A["emb"].shape[1]
+    SK = [np.zeros((max_len, d), np.float32) for _ in A["layers"]]
+    SV = [np.zeros((max_len, d), np.float32) for _ in A["layers"]]
+    out, cur = [], prompt[0]
+    for p in range(max_len):
+        x = _aed_ln(A["emb"][cur] + A["pos"][p], A["embln_w"], A["embln_b"])      # :183-185
+        for li, L in enumerate(A["layers"]):
+            xn = _aed_ln(x, L["ln_self_w"], L["ln_self_b"])
+            q = gemm_wt(xn[None], L["sq_w"])[0] + L["sq_b"]
+            SK[li][p] = gemm_wt(xn[None], L["sk_w"])[0] + L["sk_b"]
+            SV[li][p] = gemm_wt(xn[None], L["sv_w"])[0] + L["sv_b"]
+            att = _aed_attend(q, SK[li][:p + 1], SV[li][:p + 1], H)             # causal: keys 0..p
+            x = x + (gemm_wt(att[None], L["so_w"])[0] + L["so_b"])
+            xn = _aed_ln(x, L["ln_cross_w"], L["ln_cross_b"])
+            q = gemm_wt(xn[None], L["cq_w"])[0] + L["cq_b"]
+            att = _aed_attend(q, cross[li][0], cross[li][1], H)
+            x = x + (gemm_wt(att[None], L["co_w"])[0] + L["co_b"])
+            xn = _aed_ln(x, L["ln_ffn_w"], L["ln_ffn_b"])
+            ff = np.maximum(gemm_wt(xn[None], L["ff1_w"])[0] + L["ff1_b"], np.float32(0.0))
+            x = x + (gemm_wt(ff[None], L["ff2_w"])[0] + L["ff2_b"])
+        if p + 1 < len(prompt):                                                  # :211-214
+            cur = prompt[p + 1]
+            continue
+        logits = gemm_wt(_aed_ln(x, A["fin_w"], A["fin_b"])[None], A["head_w"])[0] + A["head_b"]
+        best = int(np.argmax(logits))                                            # first maximum, as :217-218
+        if best == eos or len(out) >= cap:
+            break
+        out.append(best)
+        cur = best
+    return np.asarray(out, np.int32)

@@ -48,6 +48,8 @@ def lib():
                                                 C.c_int, C.POINTER(C.c_void_p), c_ip]
         L.ref_ctc_decode.argtypes = [C.c_void_p, c_fp, C.c_int, c_ip, c_ip, C.c_int]
         L.ref_greedy_decode.argtypes = [C.c_void_p, c_fp, C.c_int, c_ip, c_ip, C.c_int]
+        L.ref_aed_open.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.ref_aed_decode.argtypes = [C.c_void_p, c_fp, C.c_int, c_ip, C.c_int, C.c_int, c_ip, C.c_int]
         L.ref_stream_open.restype = C.c_void_p
         L.ref_stream_open.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int]
         L.ref_stream_need.argtypes = [C.c_void_p]
@@ -184,6 +186,20 @@ class RefModel:
 
     def greedy_decode(self, enc, max_symbols=10):
         return self._decode(lib().ref_greedy_decode, enc, enc.shape[0] * max_symbols)
+
+    def aed_open(self, n_layers, n_heads, max_seq, max_gen_delta, quant=0):
+        if lib().ref_aed_open(self.h, n_layers, n_heads, max_seq, max_gen_delta, quant) != 0:
+            raise RuntimeError("reference: AED weights missing or incomplete")
+
+    def aed_decode(self, enc, prompt, eos, cap):
+        """mynah_asr_aed_decode (src/decoder_aed.c:139-232): generated tokens, prompt and EOS excluded."""
+        enc = np.ascontiguousarray(enc, np.float32)
+        pr = np.ascontiguousarray(prompt, np.int32)
+        out = np.zeros(max(cap, 1), np.int32)
+        n = lib().ref_aed_decode(self.h, _fp(enc), enc.shape[0], pr.ctypes.data_as(C.POINTER(C.c_int)), pr.size, eos,
+                                 out.ctypes.data_as(C.POINTER(C.c_int)), cap)
+        assert n >= 0
+        return out[:n].copy()
 
     def stream_encode(self, mel, left, right):
         """Feed valid mel frames through the cache-aware streaming encoder in the

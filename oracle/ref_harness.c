@@ -12,6 +12,7 @@
  *                    mynah_asr_pos_emb, mynah_asr_enc_stream_*
  *   src/decoder.c    mynah_asr_greedy_decode (RNNT + TDT)
  *   src/decoder_ctc.c mynah_asr_ctc_decode
+ *   src/decoder_aed.c mynah_asr_aed_{init,decode}
  *   src/qmat.c       mynah_asr_qmat_{init,mul}
  *
  * Every function below only forwards to the reference; no arithmetic lives
@@ -22,6 +23,7 @@
 #include <string.h>
 
 #include "decoder.h"
+#include "decoder_aed.h"
 #include "decoder_ctc.h"
 #include "encoder.h"
 #include "features.h"
@@ -36,12 +38,14 @@ typedef struct {
     mynah_asr_decoder dec;
     mynah_asr_ctc ctc;
     mynah_asr_feat_cfg feat;
-    int has_dec, has_ctc, has_feat;
+    mynah_asr_aed aed;
+    int has_dec, has_ctc, has_feat, has_aed;
 } ref_model;
 
 void ref_close(ref_model *m) {
     if (!m) return;
     if (m->has_dec) mynah_asr_qmat_free(&m->dec.head);
+    if (m->has_aed) mynah_asr_aed_free(&m->aed);
     mynah_asr_encoder_free(&m->enc);
     if (m->st) mynah_asr_st_close(m->st);
     if (m->mel) mynah_asr_st_close(m->mel);
@@ -81,6 +85,23 @@ ref_model *ref_open(const char *weights, const char *mel_filters, int quant, int
         m->has_feat = 1;
     }
     return m;
+}
+
+/* AED decoder of the same safetensors file (mynah_asr_aed_init, src/decoder_aed.c:50-113). */
+int ref_aed_open(ref_model *m, int n_layers, int n_heads, int max_seq, int max_gen_delta, int quant) {
+    if (m->has_aed) return 0;
+    if (mynah_asr_aed_init(&m->aed, m->st, n_layers, n_heads, max_seq, max_gen_delta, quant) != 0) {
+        mynah_asr_aed_free(&m->aed);
+        return -1;
+    }
+    m->has_aed = 1;
+    return 0;
+}
+
+int ref_aed_decode(const ref_model *m, const float *enc, int T, const int *prompt, int n_prompt, int eos,
+                   int *tokens, int cap) {
+    if (!m->has_aed) return -1;
+    return mynah_asr_aed_decode(&m->aed, enc, T, prompt, n_prompt, eos, tokens, cap);
 }
 
 /* dims[0..7] = d_model, n_layers, n_heads, ffn_dim, conv_k, d_out, causal, channels */

@@ -16,9 +16,22 @@ TINY = {
                      wtype="q8_0", use_bias=True),
 }
 
+# Canary-style AED models (transformer decoder with cross-attention): decoder as wide as the
+# encoder, and a narrower one behind enc_dec_proj
+AED = {
+    "aed_same": dict(d_model=128, n_layers=1, n_heads=4, ffn_dim=256, n_mels=80, decoder="aed", vocab=300,
+                     aed_layers=2, aed_heads=4, aed_max_seq=64, wtype="q8_0"),
+    "aed_proj": dict(d_model=128, n_layers=1, n_heads=4, ffn_dim=256, n_mels=80, decoder="aed", vocab=211,
+                     aed_d=64, aed_layers=3, aed_heads=2, aed_ffn=192, aed_max_seq=48, wtype="q4_0"),
+}
+AED_PROMPT = (7, 9, 200, 11)
+AED_CAP = 24
+SEEDS = {"aed_same": 4}       # weight seeds whose greedy streams do not fall into a one-token fixed point
 
-def build(synth, name, seed=1):
-    cfg = synth.config(name, **TINY[name])
+
+def build(synth, name, seed=None):
+    seed = SEEDS.get(name, 1) if seed is None else seed
+    cfg = synth.config(name, **(TINY[name] if name in TINY else AED[name]))
     return cfg, synth.make_model(cfg, seed=seed)
 
 

@@ -60,6 +60,28 @@ def pipeline(name):
     print(name, {k: getattr(v, "shape", v) for k, v in out.items()}, "tokens", len(t), "distinct", len(set(t)))
 
 
+def aed(name):
+    """mynah_asr_aed_decode on the reference's own encoder output: the whole stream with an EOS
+    that never fires, and the stream cut by an EOS id taken from it."""
+    cfg, tensors = cases.build(synth, name)
+    d = tempfile.mkdtemp()
+    wp, mp = model_io.write_reference_files(d, cfg, tensors, synth)
+    rm = R.RefModel(wp, mp, n_mels=cfg.n_mels, normalize=int(cfg.normalize))
+    rm.aed_open(cfg.aed_layers, cfg.aed_heads, cfg.aed_max_seq, cfg.aed_max_gen_delta)
+    out = {}
+    for i, secs in enumerate((2.0, 1.2)):
+        feats, valid = rm.log_mel(synth.synth_audio(secs, seed=11 + i))
+        enc = rm.encoder_forward(feats[:valid])
+        toks = rm.aed_decode(enc, cases.AED_PROMPT, -1, cases.AED_CAP)
+        eos = int(toks[7])
+        out[f"enc{i}"], out[f"tokens{i}"], out[f"eos{i}"] = enc, toks, np.int32(eos)
+        out[f"tokens_eos{i}"] = rm.aed_decode(enc, cases.AED_PROMPT, eos, cases.AED_CAP)
+        out[f"tokens_start{i}"] = rm.aed_decode(enc, cases.AED_PROMPT[:1], -1, cases.AED_CAP)
+        print(name, i, "T", enc.shape[0], "tokens", len(toks), "distinct", len(set(toks.tolist())), "cut at", len(out[f"tokens_eos{i}"]))
+    rm.close()
+    np.savez_compressed(os.path.join(HERE, f"ref_{name}.npz"), **out)
+
+
 def qmat():
     """mynah_asr_qmat_mul on weights quantised by the reference's own load-time
     quantiser, T = 1, 4 (int8-activation dots) and 48 (dequant + sgemm): the cases
@@ -82,4 +104,6 @@ if __name__ == "__main__":
     assert R.available(), "build oracle/_ref first: make -C oracle"
     for name in cases.TINY:
         pipeline(name)
+    for name in cases.AED:
+        aed(name)
     qmat()
