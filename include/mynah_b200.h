@@ -99,6 +99,8 @@ typedef struct {
     int durations[16];
     int strict;                 /* 1: 3-term fp16 split (f32-grade, default); 0: single fp16 pass */
     int attn_impl;              /* 0 tiled tensor-core kernel (default), 1 plain kernel (cross-check) */
+    int aed_heads;              /* decoder.n_heads of an AED model (mynah_asr_aed_init's n_heads); layers, width,
+                                 * vocabulary and max_seq are read off the tensors */
 } mynah_b200_config;
 
 void mynah_b200_config_default(mynah_b200_config *cfg);
@@ -146,20 +148,39 @@ int mynah_b200_ctc_decode(mynah_b200_model *m, const float *enc_out, int T, int 
  * eng_decode_rnnt, src/mynah_asr.c:124-137) */
 int mynah_b200_greedy_decode(mynah_b200_model *m, const float *enc, int T, int *tokens, int *frames, int cap);
 
+/* replaces mynah_asr_aed_decode (src/decoder_aed.h:44-48): greedy decode of the transformer decoder over
+ * enc [T, d_out]; generated tokens (prompt and EOS excluded) in tokens[cap]; returns the count, -1 on error */
+int mynah_b200_aed_decode(mynah_b200_model *m, const float *enc, int T, const int *prompt, int n_prompt, int eos,
+                          int *tokens, int cap);
+/* the same for several utterances decoded in lock step (the batched counterpart of batch_decode_worker,
+ * src/mynah_asr.c:473-502, for the AED engine): utterance b has encs[b] [Ts[b], d_out], its own prompt and
+ * budget caps[b]; tokens[b] is malloc()'d (caller frees). A batch gives the same tokens as each utterance alone. */
+int mynah_b200_aed_decode_batch(mynah_b200_model *m, const float *const *encs, const int *Ts, int batch,
+                                const int *const *prompts, const int *n_prompts, int eos, const int *caps, int **tokens,
+                                int *n_tokens);
+
 /* ---- whole path, resident ------------------------------------------------------- */
 /* audio in, token ids out: log-mel -> encoder (packed batch) -> greedy decoder, with only the
  * audio and the token ids crossing PCIe. The device-resident counterpart of one wave of
  * mynah_asr_transcribe_batch_ts (src/mynah_asr.c:624-679) up to detokenisation.
  * tokens[b] / frames[b] are malloc()'d (caller frees; frames may be NULL), n_tokens[b] set.
- * decoder: 0 = the model's transducer head (RNNT/TDT), 1 = CTC head. */
+ * decoder: 0 = the model's transducer head (RNNT/TDT), 1 = CTC head (2 = AED: see mynah_b200_transcribe_batch_aed). */
 int mynah_b200_transcribe_batch(mynah_b200_model *m, const float *const *audio, const size_t *n_samples, int batch,
                                 int decoder, int **tokens, int **frames, int *n_tokens);
+
+/* The AED engine's wave (eng_decode_aed, src/mynah_asr.c:147-160): every utterance starts from the same prompt
+ * and may generate T + max_gen_delta tokens (T = its encoder frames). */
+int mynah_b200_transcribe_batch_aed(mynah_b200_model *m, const float *const *audio, const size_t *n_samples, int batch,
+                                    const int *prompt, int n_prompt, int eos, int max_gen_delta, int **tokens,
+                                    int *n_tokens);
 
 /* Same, split for measurement: inputs already resident on the device. h = handle returned by
  * mynah_b200_batch_upload; run may be called repeatedly; results fetched once. */
 typedef struct mynah_b200_batch mynah_b200_batch;
 mynah_b200_batch *mynah_b200_batch_upload(mynah_b200_model *m, const float *const *audio, const size_t *n_samples,
                                           int batch);
+/* decoder 2 (AED) needs its prompt, EOS id and generation allowance set on the handle first */
+void mynah_b200_batch_set_aed(mynah_b200_batch *h, const int *prompt, int n_prompt, int eos, int max_gen_delta);
 int mynah_b200_batch_run(mynah_b200_model *m, mynah_b200_batch *h, int decoder);
 int mynah_b200_batch_fetch(mynah_b200_model *m, mynah_b200_batch *h, int **tokens, int **frames, int *n_tokens);
 void mynah_b200_batch_free(mynah_b200_batch *h);

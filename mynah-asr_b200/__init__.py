@@ -33,7 +33,7 @@ class Config(C.Structure):
                 ("preemphasis", C.c_double), ("log_zero_guard", C.c_double), ("normalize_per_feature", C.c_int),
                 ("causal", C.c_int), ("xscaling", C.c_int), ("left_ctx", C.c_int), ("right_ctx", C.c_int),
                 ("blank_id", C.c_int), ("max_symbols", C.c_int), ("n_durations", C.c_int),
-                ("durations", C.c_int * 16), ("strict", C.c_int), ("attn_impl", C.c_int)]
+                ("durations", C.c_int * 16), ("strict", C.c_int), ("attn_impl", C.c_int), ("aed_heads", C.c_int)]
 
 
 class BackendError(RuntimeError):
@@ -71,6 +71,13 @@ def lib():
     L.mynah_b200_qmat_time.argtypes = [vp, ci, ci, ci]
     L.mynah_b200_profile_begin.argtypes = [vp]
     L.mynah_b200_profile_end.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_longlong), ci]
+    L.mynah_b200_aed_decode.argtypes = [vp, c_fp, ci, c_ip, ci, ci, c_ip, ci]
+    L.mynah_b200_aed_decode_batch.argtypes = [vp, C.POINTER(c_fp), c_ip, ci, C.POINTER(C.POINTER(C.c_int)), c_ip, ci, c_ip,
+                                              C.POINTER(C.c_void_p), c_ip]
+    L.mynah_b200_transcribe_batch_aed.argtypes = [vp, C.POINTER(c_fp), C.POINTER(C.c_size_t), ci, c_ip, ci, ci, ci,
+                                                  C.POINTER(C.c_void_p), c_ip]
+    L.mynah_b200_batch_set_aed.argtypes = [vp, c_ip, ci, ci, ci]
+    L.mynah_b200_batch_set_aed.restype = None
     L.mynah_b200_profile_bytes.argtypes = [vp, C.POINTER(C.c_double), ci]
     L.mynah_b200_decoder_clocks.argtypes = [vp, C.POINTER(C.c_longlong)]
     L.mynah_b200_model_new.restype = vp
@@ -213,7 +220,7 @@ class Model:
     (the weight side of mynah_asr_load_quant, src/mynah_asr.c:167-350)."""
 
     def __init__(self, tensors, *, n_mels, mel_fb=None, window=None, causal=-1, xscaling=False, normalize=True,
-                 left=-1, right=-1, blank=0, max_symbols=10, durations=(), strict=True, attn_impl=0):
+                 left=-1, right=-1, blank=0, max_symbols=10, durations=(), strict=True, attn_impl=0, aed_heads=8):
         L = lib()
         cfg = Config()
         L.mynah_b200_config_default(C.byref(cfg))
@@ -222,7 +229,7 @@ class Model:
         cfg.blank_id, cfg.max_symbols, cfg.n_durations = blank, max_symbols, len(durations)
         for i, d in enumerate(durations):
             cfg.durations[i] = d
-        cfg.strict, cfg.attn_impl = int(strict), attn_impl
+        cfg.strict, cfg.attn_impl, cfg.aed_heads = int(strict), attn_impl, aed_heads
         self.cfg = cfg
         self.h = L.mynah_b200_model_new(C.byref(cfg))
         if not self.h:
@@ -328,6 +335,38 @@ class Model:
 
     def greedy_decode(self, enc):
         return self._decode(lib().mynah_b200_greedy_decode, enc, enc.shape[0] * self.max_symbols, "greedy_decode")
+
+    def aed_decode(self, enc, prompt, eos, cap):
+        """mynah_asr_aed_decode: generated tokens, prompt and EOS excluded."""
+        enc = np.ascontiguousarray(enc, np.float32)
+        pr = (C.c_int * len(prompt))(*prompt)
+        out = (C.c_int * max(cap, 1))()
+        n = lib().mynah_b200_aed_decode(self.h, _fp(enc), enc.shape[0], pr, len(prompt), eos, out, cap)
+        if n < 0:
+            raise BackendError("aed_decode: " + _err())
+        return np.array(out[:n], np.int32)
+
+    def aed_decode_batch(self, encs, prompts, eos, caps):
+        B = len(encs)
+        el = [np.ascontiguousarray(e, np.float32) for e in encs]
+        ep = (c_fp * B)(*[_fp(e) for e in el])
+        Ts = (C.c_int * B)(*[e.shape[0] for e in el])
+        pl = [(C.c_int * len(p))(*p) for p in prompts]
+        pp = (C.POINTER(C.c_int) * B)(*[C.cast(p, C.POINTER(C.c_int)) for p in pl])
+        npr = (C.c_int * B)(*[len(p) for p in prompts])
+        cp = (C.c_int * B)(*caps)
+        tk, nt = (C.c_void_p * B)(), (C.c_int * B)()
+        _check(lib().mynah_b200_aed_decode_batch(self.h, ep, Ts, B, pp, npr, eos, cp, tk, nt), "aed_decode_batch")
+        return [_take_i32(tk[b], nt[b]) for b in range(B)]
+
+    def transcribe_batch_aed(self, audio_list, prompt, eos, max_gen_delta):
+        B = len(audio_list)
+        al, ptrs, ns = self._audio_args(audio_list)
+        pr = (C.c_int * len(prompt))(*prompt)
+        tk, nt = (C.c_void_p * B)(), (C.c_int * B)()
+        _check(lib().mynah_b200_transcribe_batch_aed(self.h, ptrs, ns, B, pr, len(prompt), eos, max_gen_delta, tk, nt),
+               "transcribe_batch_aed")
+        return [_take_i32(tk[b], nt[b]) for b in range(B)]
 
     # ---- audio in, tokens out
     @staticmethod

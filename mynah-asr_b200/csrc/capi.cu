@@ -22,6 +22,8 @@ struct mynah_b200_batch {
     std::vector<float *> audio;          // device
     std::vector<size_t> n_samples;
     std::vector<std::vector<int>> tokens, frames;
+    std::vector<int> aed_prompt;         // decoder 2 (AED): the prompt every utterance starts from,
+    int aed_eos = -1, aed_delta = 0;     // the end-of-sequence id and the generation allowance beyond T
 };
 
 namespace mb {
@@ -79,7 +81,7 @@ void mynah_b200_config_default(mynah_b200_config *c) {
     c->preemphasis = 0.97; c->log_zero_guard = 5.9604644775390625e-8;
     c->normalize_per_feature = 1; c->causal = -1; c->xscaling = 0;
     c->left_ctx = -1; c->right_ctx = -1; c->blank_id = 0; c->max_symbols = 10;
-    c->n_durations = 0; c->strict = 1; c->attn_impl = 0;
+    c->n_durations = 0; c->strict = 1; c->attn_impl = 0; c->aed_heads = 8;
 }
 
 // ------------------------------------------------------------------- model
@@ -167,6 +169,28 @@ static int lin(Model &m, QWeight &w, const std::string &wname, bool planes, bool
     int err = 0;
     w.bias = const_cast<float *>(f32dev(m, bname, false, &err));
     return err ? -1 : 0;
+}
+
+// several linears over the same input, stored one below the other: [sum n, k] with the biases concatenated
+// (block formats keep whole rows of blocks, so the stored bytes concatenate as they are)
+static int lin_cat(Model &m, QWeight &w, const float **bias, const std::vector<std::string> &prefixes) {
+    std::vector<uint8_t> bytes;
+    std::vector<float> b;
+    int fmt = -1, k = 0, n = 0;
+    for (const std::string &pre : prefixes) {
+        const HostTensor *t = find(m, pre + ".weight"), *tb = find(m, pre + ".bias");
+        if (!t || t->shape.size() != 2 || !tb || tb->fmt != FMT_F32) { set_error("missing tensor '%s.weight' or its bias", pre.c_str()); return -1; }
+        if (t->fmt == FMT_MYNAH_Q8 || t->fmt == FMT_MYNAH_Q4) { set_error("'%s': natively quantised AED weights are not supported", pre.c_str()); return -1; }
+        if (fmt < 0) { fmt = t->fmt; k = (int)t->shape[1]; }
+        if (t->fmt != fmt || (int)t->shape[1] != k) { set_error("'%s': projections of one attention differ in format or width", pre.c_str()); return -1; }
+        const size_t nb = format_bytes(fmt, (int)t->shape[0], k);
+        bytes.insert(bytes.end(), (const uint8_t *)t->data, (const uint8_t *)t->data + nb);
+        b.insert(b.end(), (const float *)tb->data, (const float *)tb->data + t->shape[0]);
+        n += (int)t->shape[0];
+    }
+    if (m.upload_weight(w, fmt, bytes.data(), nullptr, n, k, true, false)) return -1;
+    *bias = m.upload_f32(b.data(), b.size());
+    return *bias ? 0 : -1;
 }
 
 extern "C" {
@@ -302,6 +326,53 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
         if (m.head.n != m.vocab + m.cfg.n_durations) { set_error("joint head has %d rows, expected vocab %d + %d durations", m.head.n, m.vocab, m.cfg.n_durations); return -1; }
         if (m.d_out != m.pred_hidden) { set_error("encoder output width %d != prediction hidden %d", m.d_out, m.pred_hidden); return -1; }
         m.has_dec = true;
+    }
+    if (const HostTensor *e = find(m, "aed.embedding.weight")) {
+        // mynah_asr_aed_init (src/decoder_aed.c:50-113)
+        if (e->fmt != FMT_F32 || e->shape.size() != 2) { set_error("aed.embedding.weight must be f32 [vocab, d]"); return -1; }
+        m.aed_vocab = (int)e->shape[0]; m.aed_d = (int)e->shape[1];
+        m.aed_heads = m.cfg.aed_heads > 0 ? m.cfg.aed_heads : 8;
+        if (m.aed_d % m.aed_heads || m.aed_d % 64) { set_error("AED width %d must be a multiple of 64 and of its %d heads", m.aed_d, m.aed_heads); return -1; }
+        const HostTensor *pe = find(m, "aed.pos_enc");
+        if (!pe || pe->shape.size() != 2 || (int)pe->shape[1] != m.aed_d) { set_error("missing or misshapen aed.pos_enc"); return -1; }
+        m.aed_max_seq = (int)pe->shape[0];
+        m.aed_emb = f32dev(m, "aed.embedding.weight", true, &err);
+        m.aed_pos = f32dev(m, "aed.pos_enc", true, &err);
+        m.aed_embln_w = f32dev(m, "aed.emb_norm.weight", true, &err); m.aed_embln_b = f32dev(m, "aed.emb_norm.bias", true, &err);
+        m.aed_fin_w = f32dev(m, "aed.final_norm.weight", true, &err); m.aed_fin_b = f32dev(m, "aed.final_norm.bias", true, &err);
+        if (err) return -1;
+        if (lin(m, m.aed_head, "aed.head.weight", true, false)) return -1;
+        m.aed_head_b = m.aed_head.bias;
+        if (!m.aed_head_b) { set_error("missing aed.head.bias"); return -1; }
+        if (find(m, "enc_dec_proj.weight")) {
+            if (lin(m, m.aed_proj, "enc_dec_proj.weight", true, false)) return -1;
+            m.aed_proj_b = m.aed_proj.bias;
+            m.has_aed_proj = true;
+            if (m.aed_proj.n != m.aed_d || m.aed_proj.k != m.d_out) { set_error("enc_dec_proj is [%d,%d], expected [%d,%d]", m.aed_proj.n, m.aed_proj.k, m.aed_d, m.d_out); return -1; }
+        } else if (m.d_out != m.aed_d) { set_error("encoder output width %d != AED width %d and no enc_dec_proj", m.d_out, m.aed_d); return -1; }
+        int nl = 0;
+        while (find(m, "aed.layers." + std::to_string(nl) + ".ln_self.weight")) nl++;
+        if (nl == 0) { set_error("AED decoder without layers"); return -1; }
+        m.aed_layers.resize(nl);
+        for (int li = 0; li < nl; li++) {
+            AedLayer &A = m.aed_layers[li];
+            const std::string p = "aed.layers." + std::to_string(li) + ".";
+            A.ln_self_w = f32dev(m, p + "ln_self.weight", true, &err); A.ln_self_b = f32dev(m, p + "ln_self.bias", true, &err);
+            A.ln_cross_w = f32dev(m, p + "ln_cross.weight", true, &err); A.ln_cross_b = f32dev(m, p + "ln_cross.bias", true, &err);
+            A.ln_ffn_w = f32dev(m, p + "ln_ffn.weight", true, &err); A.ln_ffn_b = f32dev(m, p + "ln_ffn.bias", true, &err);
+            if (err) return -1;
+            if (lin_cat(m, A.sqkv, &A.sqkv_b, {p + "self_attn.q_proj", p + "self_attn.k_proj", p + "self_attn.v_proj"}) ||
+                lin_cat(m, A.ckv, &A.ckv_b, {p + "cross_attn.k_proj", p + "cross_attn.v_proj"}) ||
+                lin_cat(m, A.so, &A.so_b, {p + "self_attn.o_proj"}) || lin_cat(m, A.cq, &A.cq_b, {p + "cross_attn.q_proj"}) ||
+                lin_cat(m, A.co, &A.co_b, {p + "cross_attn.o_proj"}) || lin_cat(m, A.ff1, &A.ff1_b, {p + "ffn.linear1"}) ||
+                lin_cat(m, A.ff2, &A.ff2_b, {p + "ffn.linear2"}))
+                return -1;
+            if (A.sqkv.n != 3 * m.aed_d || A.ckv.n != 2 * m.aed_d || A.sqkv.k != m.aed_d || A.ff2.n != m.aed_d || A.ff1.n % 64) {
+                set_error("AED layer %d has unexpected shapes", li); return -1;
+            }
+        }
+        m.aed_ffn = m.aed_layers[0].ff1.n;
+        m.has_aed = true;
     }
     m.host.clear();
     m.finalized = true;
@@ -515,6 +586,61 @@ int mynah_b200_greedy_decode(mynah_b200_model *h, const float *enc, int T, int *
     return n;
 }
 
+int mynah_b200_aed_decode_batch(mynah_b200_model *h, const float *const *encs, const int *Ts, int batch, const int *const *prompts,
+                                const int *n_prompts, int eos, const int *caps, int **tokens, int *n_tokens) {
+    if (!h || !h->m.finalized || !encs || !Ts || batch <= 0 || !prompts || !n_prompts || !caps || !tokens || !n_tokens) {
+        set_error("aed_decode_batch: bad argument"); return -1;
+    }
+    Model &m = h->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    if (!m.has_aed) { set_error("model has no AED decoder"); return -1; }
+    size_t total = 0;
+    int max_len = 0;
+    std::vector<int> lens(Ts, Ts + batch), cp(caps, caps + batch);
+    std::vector<std::vector<int>> pr(batch);
+    for (int b = 0; b < batch; b++) {
+        if (Ts[b] <= 0 || n_prompts[b] <= 0 || !prompts[b] || !encs[b]) { set_error("aed_decode_batch: utterance %d is empty or has no start token", b); return -1; }
+        total += (size_t)Ts[b];
+        pr[b].assign(prompts[b], prompts[b] + n_prompts[b]);
+        const int ml = n_prompts[b] + (caps[b] > 0 ? caps[b] : 0);
+        max_len = ml > max_len ? ml : max_len;
+    }
+    if (max_len > m.aed_max_seq) max_len = m.aed_max_seq;
+    if (m.ws.reserve(total * m.d_out * 4 + m.aed_bytes((int)total, batch, max_len))) return -1;
+    m.ws.reset();
+    float *e = m.ws.get<float>(total * m.d_out);
+    if (!e) return -1;
+    size_t off = 0;
+    for (int b = 0; b < batch; b++) {
+        MB_CUDA(cudaMemcpyAsync(e + off * m.d_out, encs[b], (size_t)Ts[b] * m.d_out * 4, cudaMemcpyHostToDevice, m.stream));
+        off += (size_t)Ts[b];
+    }
+    std::vector<std::vector<int>> tk;
+    if (m.decode_aed(e, lens, pr, eos, cp, tk)) return -1;
+    for (int b = 0; b < batch; b++) {
+        n_tokens[b] = (int)tk[b].size();
+        tokens[b] = (int *)malloc((tk[b].size() ? tk[b].size() : 1) * sizeof(int));
+        if (!tokens[b]) { set_error("out of host memory"); return -1; }
+        memcpy(tokens[b], tk[b].data(), tk[b].size() * sizeof(int));
+    }
+    return 0;
+}
+
+int mynah_b200_aed_decode(mynah_b200_model *h, const float *enc, int T, const int *prompt, int n_prompt, int eos, int *tokens, int cap) {
+    if (!tokens || n_prompt <= 0 || !prompt) { set_error("aed_decode: bad argument (at least one start token is needed)"); return -1; }
+    int *out = nullptr, n = 0;
+    if (mynah_b200_aed_decode_batch(h, &enc, &T, 1, &prompt, &n_prompt, eos, &cap, &out, &n)) return -1;
+    memcpy(tokens, out, (size_t)n * sizeof(int));
+    free(out);
+    return n;
+}
+
+void mynah_b200_batch_set_aed(mynah_b200_batch *bt, const int *prompt, int n_prompt, int eos, int max_gen_delta) {
+    if (!bt) return;
+    bt->aed_prompt.assign(prompt, prompt + (n_prompt > 0 ? n_prompt : 0));
+    bt->aed_eos = eos; bt->aed_delta = max_gen_delta;
+}
+
 // ------------------------------------------------------------ resident pipeline
 mynah_b200_batch *mynah_b200_batch_upload(mynah_b200_model *h, const float *const *audio, const size_t *n_samples, int batch) {
     if (!h || !h->m.finalized || batch <= 0) { set_error("batch_upload: bad argument"); return nullptr; }
@@ -555,7 +681,11 @@ static int run_batch_locked(Model &m, mynah_b200_batch *bt, const float *const *
         abytes += align_up(bt->n_samples[b] * 4, 256) + 256;
         if (valid[b] > 0 && ss_bytes(m, valid[b]) > ssmax) ssmax = ss_bytes(m, valid[b]);
     }
-    const size_t decb = decoder == 1 ? M * ((size_t)m.d_model * 4 + (size_t)m.ctc_vocab * 4 + 8) : dec_bytes(m, max_len);
+    if (decoder == 2 && (!m.has_aed || bt->aed_prompt.empty())) { set_error("batch_run: AED decoding needs an AED model and mynah_b200_batch_set_aed"); return -1; }
+    int aed_len = (int)bt->aed_prompt.size() + max_len + bt->aed_delta;
+    if (decoder == 2 && aed_len > m.aed_max_seq) aed_len = m.aed_max_seq;
+    const size_t decb = decoder == 1 ? M * ((size_t)m.d_model * 4 + (size_t)m.ctc_vocab * 4 + 8)
+                      : decoder == 2 ? m.aed_bytes((int)M, B, aed_len) : dec_bytes(m, max_len);
     if (m.ws.reserve((audio_host ? abytes : 0) + fbytes + ssmax + enc_bytes(m, M, rk) + M * ((size_t)m.d_model + m.d_out) * 4 +
                      decb + (4 << 20))) return -1;
     m.ws.reset();
@@ -587,6 +717,25 @@ static int run_batch_locked(Model &m, mynah_b200_batch *bt, const float *const *
             if (m.decode_ctc(x + off * m.d_model, lens[b], bt->tokens[b], bt->frames[b])) return -1;
             off += lens[b];
         }
+    } else if (decoder == 2) {
+        // AED engine: projected encoder output, generation budget T + max_gen_delta per utterance
+        // (eng_decode_aed, src/mynah_asr.c:147-160, without timestamp tokens)
+        if (m.encoder_post(x, (int)M, y)) return -1;
+        std::vector<std::vector<int>> pr(B, bt->aed_prompt);
+        std::vector<int> caps(B);
+        for (int b = 0; b < B; b++) caps[b] = lens[b] + bt->aed_delta;
+        std::vector<int> idx;
+        for (int b = 0; b < B; b++) if (lens[b] > 0) idx.push_back(b);
+        if ((int)idx.size() == B) {
+            if (m.decode_aed(y, lens, pr, bt->aed_eos, caps, bt->tokens)) return -1;
+        } else {                           // utterances without a single encoder frame produce nothing
+            std::vector<int> l2, c2;
+            std::vector<std::vector<int>> p2, t2;
+            for (int b : idx) { l2.push_back(lens[b]); c2.push_back(caps[b]); p2.push_back(pr[b]); }
+            if (!idx.empty() && m.decode_aed(y, l2, p2, bt->aed_eos, c2, t2)) return -1;
+            for (size_t i = 0; i < idx.size(); i++) bt->tokens[idx[i]] = t2[i];
+        }
+        for (int b = 0; b < B; b++) bt->frames[b].assign(bt->tokens[b].size(), 0);
     } else {
         if (m.encoder_post(x, (int)M, y)) return -1;
         if (m.decode_greedy(y, lens, bt->tokens, bt->frames)) return -1;
@@ -630,6 +779,22 @@ int mynah_b200_transcribe_batch(mynah_b200_model *h, const float *const *audio, 
         rc = run_batch_locked(h->m, &bt, nullptr, audio, decoder);
     }
     if (rc == 0) rc = mynah_b200_batch_fetch(h, &bt, tokens, frames, n_tokens);
+    return rc;
+}
+
+int mynah_b200_transcribe_batch_aed(mynah_b200_model *h, const float *const *audio, const size_t *n_samples, int batch,
+                                    const int *prompt, int n_prompt, int eos, int max_gen_delta, int **tokens, int *n_tokens) {
+    if (!h || !h->m.finalized || batch <= 0 || !audio || !n_samples || !prompt || n_prompt <= 0) { set_error("transcribe_batch_aed: bad argument"); return -1; }
+    mynah_b200_batch bt;
+    bt.batch = batch;
+    bt.n_samples.assign(n_samples, n_samples + batch);
+    mynah_b200_batch_set_aed(&bt, prompt, n_prompt, eos, max_gen_delta);
+    int rc;
+    {
+        std::lock_guard<std::mutex> lk(h->m.mu);
+        rc = run_batch_locked(h->m, &bt, nullptr, audio, 2);
+    }
+    if (rc == 0) rc = mynah_b200_batch_fetch(h, &bt, tokens, nullptr, n_tokens);
     return rc;
 }
 

@@ -1,0 +1,283 @@
+// Greedy AED decode (pre-LN transformer decoder with a self-attention KV cache and
+// cross-attention over the projected encoder output): the device counterpart of
+// mynah_asr_aed_decode (src/decoder_aed.c:139-232) for B utterances in lock step.
+// All utterances sit at the same position p; each row of every kernel depends only on its own
+// utterance, so a batch decodes to the same bits as each utterance alone.
+// The large linears run on the tcgen05 contraction (model.cu); this file holds what sits
+// between them: embedding, the two single-query attentions and the greedy selection.
+#include "model.h"
+
+namespace mb {
+
+// x[b] = emb[cur[b]] + pos[p]   (src/decoder_aed.c:183-184; the LayerNorm follows as its own launch)
+__global__ void aed_embed_kernel(const float *__restrict__ emb, const float *__restrict__ pos, const int *__restrict__ cur, int p,
+                                 float *__restrict__ x, int D) {
+    const int b = blockIdx.x;
+    const float *e = emb + (size_t)cur[b] * D, *pe = pos + (size_t)p * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)b * D + i] = e[i] + pe[i];
+}
+
+// Block-wide max / sum over `n` values held in shared memory (blockDim.x <= 1024).
+__device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = is_max ? warp_max(v) : warp_sum(v);
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = is_max ? -INFINITY : 0.f;
+    for (int i = 0; i < nw; i++) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+    __syncthreads();
+    return r;
+}
+
+// Causal self-attention of one new position (src/decoder_aed.c:191-196 with attend, :117-131):
+// appends this step's k, v to the cache and attends over positions 0..p. Grid (H, B).
+// qkv [B, 3D] = (q | k | v) with biases already added; cache [B, max_len, D] each.
+__global__ void aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, float *__restrict__ cv, int p, int max_len,
+                                     int D, int dk, H16 out) {
+    extern __shared__ float sm[];
+    float *sc = sm, *q = sm + max_len, *red = q + dk;
+    const int h = blockIdx.x, b = blockIdx.y;
+    const float *row = qkv + (size_t)b * 3 * D + h * dk;
+    float *K = ck + (size_t)b * max_len * D + h * dk, *V = cv + (size_t)b * max_len * D + h * dk;
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+        q[i] = row[i];
+        K[(size_t)p * D + i] = row[D + i];
+        V[(size_t)p * D + i] = row[2 * D + i];
+    }
+    __syncthreads();
+    const float scale = 1.0f / sqrtf((float)dk);
+    float m = -INFINITY;
+    for (int j = threadIdx.x; j <= p; j += blockDim.x) {
+        const float *kj = K + (size_t)j * D;
+        float s = 0.f;
+        for (int i = 0; i < dk; i++) s = fmaf(q[i], kj[i], s);
+        s *= scale;
+        sc[j] = s;
+        m = fmaxf(m, s);
+    }
+    m = block_reduce(m, red, true);
+    float sum = 0.f;
+    for (int j = threadIdx.x; j <= p; j += blockDim.x) { const float e = expf(sc[j] - m); sc[j] = e; sum += e; }
+    sum = block_reduce(sum, red, false);
+    const float inv = 1.0f / sum;
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+        float o = 0.f;
+        for (int j = 0; j <= p; j++) o = fmaf(sc[j] * inv, V[(size_t)j * D + i], o);
+        __half hi, lo;
+        split_h16(o, hi, lo);
+        out.hi[(size_t)b * D + h * dk + i] = hi;
+        if (out.lo) out.lo[(size_t)b * D + h * dk + i] = lo;
+    }
+}
+
+// Cross-attention of one query per utterance over its T_b projected encoder frames
+// (src/decoder_aed.c:199-202). Grid (H, B). kv: planes [sum T, 2D] = (K | V) of this layer,
+// fp16 hi (+ lo * 2^-11 when present). q [B, D] f32 with bias.
+__global__ void aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ kv_hi, const __half *__restrict__ kv_lo,
+                                      const int *__restrict__ enc_off, const int *__restrict__ enc_len, int max_T, int D, int dk, H16 out) {
+    extern __shared__ float sm[];
+    float *sc = sm, *q = sm + max_T, *red = q + dk, *part = red + 32;     // part: [blockDim.x] partial outputs
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int T = enc_len[b], lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const size_t r0 = (size_t)enc_off[b];
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) q[i] = qm[(size_t)b * D + h * dk + i];
+    __syncthreads();
+    const float scale = 1.0f / sqrtf((float)dk);
+    // scores: one warp per key row, lanes over dk
+    for (int j = warp; j < T; j += nw) {
+        const size_t o = (r0 + j) * 2 * D + h * dk;
+        float s = 0.f;
+        for (int i = lane; i < dk; i += 32) {
+            float k = __half2float(kv_hi[o + i]);
+            if (kv_lo) k = fmaf(__half2float(kv_lo[o + i]), H16_LO_INV, k);
+            s = fmaf(q[i], k, s);
+        }
+        s = warp_sum(s);
+        if (lane == 0) sc[j] = s * scale;
+    }
+    __syncthreads();
+    float m = -INFINITY;
+    for (int j = threadIdx.x; j < T; j += blockDim.x) m = fmaxf(m, sc[j]);
+    m = block_reduce(m, red, true);
+    float sum = 0.f;
+    for (int j = threadIdx.x; j < T; j += blockDim.x) { const float e = expf(sc[j] - m); sc[j] = e; sum += e; }
+    sum = block_reduce(sum, red, false);
+    const float inv = 1.0f / sum;
+    // out[i] = sum_j pr[j] V[j][i]: thread (g, i) sums the keys j = g, g + G, ... of column i, then the G partials are added in order
+    const int G = blockDim.x / dk > 0 ? blockDim.x / dk : 1;
+    const int i = threadIdx.x % dk, g = threadIdx.x / dk;
+    float o = 0.f;
+    if (g < G) {
+        for (int j = g; j < T; j += G) {
+            const size_t a = (r0 + j) * 2 * D + D + h * dk + i;
+            float v = __half2float(kv_hi[a]);
+            if (kv_lo) v = fmaf(__half2float(kv_lo[a]), H16_LO_INV, v);
+            o = fmaf(sc[j] * inv, v, o);
+        }
+        part[threadIdx.x] = o;
+    }
+    __syncthreads();
+    if (threadIdx.x < dk) {
+        float t = 0.f;
+        for (int gg = 0; gg < G; gg++) t += part[gg * dk + threadIdx.x];
+        __half hi, lo;
+        split_h16(t, hi, lo);
+        out.hi[(size_t)b * D + h * dk + threadIdx.x] = hi;
+        if (out.lo) out.lo[(size_t)b * D + h * dk + threadIdx.x] = lo;
+    }
+}
+
+// Greedy selection at position p (src/decoder_aed.c:211-223). best may be null while every
+// utterance is still inside its prompt. st: [cur | n_out | done | n_prompt | max_len | cap] x B, then n_done.
+__global__ void aed_select_kernel(const int *__restrict__ best, int p, int eos, int cap_stride, int B, int *st, const int *__restrict__ prompts,
+                                  int max_prompt, int *__restrict__ tokens) {
+    const int b = threadIdx.x;
+    if (b >= B) return;
+    int *cur = st, *n_out = st + B, *done = st + 2 * B, *n_prompt = st + 3 * B, *max_len = st + 4 * B, *n_done = st + 6 * B;
+    const int cap = st[5 * B + b];
+    if (done[b]) return;
+    bool fin = false;
+    if (p + 1 < n_prompt[b]) {
+        cur[b] = prompts[b * max_prompt + p + 1];
+    } else {
+        const int t = best[b];
+        if (t == eos || n_out[b] >= cap) fin = true;
+        else { tokens[(size_t)b * cap_stride + n_out[b]] = t; n_out[b]++; cur[b] = t; }
+    }
+    if (p + 1 >= max_len[b]) fin = true;
+    if (fin) { done[b] = 1; atomicAdd(n_done, 1); }
+}
+
+static GemmEpilogue aed_epi(int mode, int act, float alpha, const float *bias, float *out, int ldo, H16 h = {nullptr, nullptr}, int ldh = 0) {
+    GemmEpilogue e;
+    memset(&e, 0, sizeof(e));
+    e.mode = mode; e.act = act; e.alpha = alpha; e.bias = bias; e.out = out; e.ldo = ldo; e.out_hi = h.hi; e.out_lo = h.lo; e.ldh = ldh;
+    return e;
+}
+
+size_t Model::aed_bytes(int total_T, int B, int max_len) const {
+    const size_t D = aed_d, F = aed_ffn, L = aed_layers.size();
+    return (size_t)total_T * (d_out * 4 + D * 4 + L * 2 * D * 4) + L * 2 * (size_t)B * max_len * D * 4 +
+           (size_t)B * (D * 24 + 3 * D * 4 + F * 4 + (size_t)aed_vocab * 4) + (size_t)B * (max_len + 64) * 8 + (1 << 20);
+}
+
+int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const std::vector<std::vector<int>> &prompts, int eos,
+                      const std::vector<int> &caps, std::vector<std::vector<int>> &tokens) {
+    const int B = (int)lens.size(), D = aed_d, H = aed_heads, dk = D / H, L = (int)aed_layers.size(), V = aed_vocab, F = aed_ffn;
+    tokens.assign(B, {});
+    if (!has_aed) { set_error("model has no AED decoder"); return -1; }
+    if (B == 0) return 0;
+    if (dk > 256) { set_error("aed_decode: head width %d above 256", dk); return -1; }
+    if ((int)prompts.size() != B || (int)caps.size() != B) { set_error("aed_decode: one prompt and one cap per utterance"); return -1; }
+    int cap = 0;
+    for (int c : caps) cap = c > cap ? c : cap;
+    std::vector<int> off(B), mlen(B);
+    int total_T = 0, max_T = 0, max_len = 0, max_prompt = 0, min_prompt = 1 << 30;
+    for (int b = 0; b < B; b++) {
+        if (prompts[b].empty()) { set_error("aed_decode: empty prompt (a start token is needed)"); return -1; }   // :143
+        if (lens[b] <= 0) { set_error("aed_decode: utterance %d has no encoder frames", b); return -1; }
+        for (int t : prompts[b]) if (t < 0 || t >= V) { set_error("aed_decode: prompt token %d outside the vocabulary", t); return -1; }
+        off[b] = total_T; total_T += lens[b];
+        max_T = lens[b] > max_T ? lens[b] : max_T;
+        const int np = (int)prompts[b].size();
+        const int cb = caps[b] > 0 ? caps[b] : 0;
+        mlen[b] = np + cb < aed_max_seq ? np + cb : aed_max_seq;                 // :145-146
+        max_len = mlen[b] > max_len ? mlen[b] : max_len;
+        max_prompt = np > max_prompt ? np : max_prompt;
+        min_prompt = np < min_prompt ? np : min_prompt;
+    }
+    const size_t mark = ws.off;
+    const int capn = cap > 0 ? cap : 1;
+    // ---- projected encoder output and the per-layer cross K/V, once (:149-178)
+    H16 enc_h = ws.planes((size_t)total_T * d_out);
+    H16 encp = enc_h;
+    if (!enc_h.hi) return -1;
+    if (split_to_h16(enc_dev, enc_h.hi, enc_h.lo, (size_t)total_T * d_out, stream)) return -1;
+    note_launch();
+    if (has_aed_proj) {
+        encp = ws.planes((size_t)total_T * D);
+        if (!encp.hi) return -1;
+        if (gemm(enc_h, d_out, aed_proj, aed_epi(OUT_H16, ACT_NONE, 1.f, aed_proj_b, nullptr, 0, encp, D), total_T)) return -1;
+    }
+    std::vector<H16> ckv(L);
+    for (int l = 0; l < L; l++) {
+        ckv[l] = ws.planes((size_t)total_T * 2 * D);
+        if (!ckv[l].hi) return -1;
+        if (gemm(encp, D, aed_layers[l].ckv, aed_epi(OUT_H16, ACT_NONE, 1.f, aed_layers[l].ckv_b, nullptr, 0, ckv[l], 2 * D), total_T)) return -1;
+    }
+    // ---- state
+    float *sk = ws.get<float>((size_t)L * 2 * B * max_len * D);
+    float *x = ws.get<float>((size_t)B * D), *qkv = ws.get<float>((size_t)B * 3 * D), *q = ws.get<float>((size_t)B * D);
+    float *logits = ws.get<float>((size_t)B * V);
+    H16 xn = ws.planes((size_t)B * D), att = ws.planes((size_t)B * D), ff = ws.planes((size_t)B * F);
+    int *st = ws.get<int>(6 * (size_t)B + 4), *best = ws.get<int>(B), *d_prompts = ws.get<int>((size_t)B * max_prompt);
+    int *d_tokens = ws.get<int>((size_t)B * capn), *d_off = ws.get<int>(2 * (size_t)B);
+    if (!sk || !x || !qkv || !q || !logits || !xn.hi || !att.hi || !ff.hi || !st || !best || !d_prompts || !d_tokens || !d_off) return -1;
+    std::vector<int> hst(6 * (size_t)B + 4, 0), hp((size_t)B * max_prompt, 0), ho(2 * (size_t)B);
+    for (int b = 0; b < B; b++) {
+        hst[b] = prompts[b][0];                              // cur
+        hst[3 * B + b] = (int)prompts[b].size();
+        hst[4 * B + b] = mlen[b];
+        hst[5 * B + b] = caps[b] > 0 ? caps[b] : 0;
+        for (size_t i = 0; i < prompts[b].size(); i++) hp[(size_t)b * max_prompt + i] = prompts[b][i];
+        ho[b] = off[b]; ho[B + b] = lens[b];
+    }
+    MB_CUDA(cudaMemcpyAsync(st, hst.data(), hst.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
+    MB_CUDA(cudaMemcpyAsync(d_prompts, hp.data(), hp.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
+    MB_CUDA(cudaMemcpyAsync(d_off, ho.data(), ho.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
+    const size_t self_smem = ((size_t)max_len + dk + 32) * sizeof(float);
+    const int cross_threads = dk >= 128 ? 256 : 128;
+    const size_t cross_smem = ((size_t)max_T + dk + 32 + cross_threads) * sizeof(float);
+    if (self_smem > 200 * 1024 || cross_smem > 200 * 1024) { set_error("aed_decode: sequence too long for the attention kernels"); return -1; }
+    MB_CUDA(cudaFuncSetAttribute(aed_self_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)self_smem));
+    MB_CUDA(cudaFuncSetAttribute(aed_cross_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cross_smem));
+    const int sp = prof_begin_span(PROF_DECODE);
+    int n_done = 0;
+    for (int p = 0; p < max_len && n_done < B; p++) {
+        aed_embed_kernel<<<B, 128, 0, stream>>>(aed_emb, aed_pos, st, p, x, D);
+        if (layer_norm(x, aed_embln_w, aed_embln_b, x, H16{nullptr, nullptr}, B, D, 0, stream)) return -1;
+        note_launch(2);
+        for (int l = 0; l < L; l++) {
+            const AedLayer &A = aed_layers[l];
+            float *K = sk + (size_t)(2 * l) * B * max_len * D, *Vc = K + (size_t)B * max_len * D;
+            if (layer_norm(x, A.ln_self_w, A.ln_self_b, nullptr, xn, B, D, 0, stream)) return -1;
+            if (gemm(xn, D, A.sqkv, aed_epi(OUT_F32, ACT_NONE, 1.f, A.sqkv_b, qkv, 3 * D), B)) return -1;
+            aed_self_attn_kernel<<<dim3(H, B), 128, self_smem, stream>>>(qkv, K, Vc, p, max_len, D, dk, att);
+            if (gemm(att, D, A.so, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.so_b, x, D), B)) return -1;
+            if (layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream)) return -1;
+            if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B)) return -1;
+            aed_cross_attn_kernel<<<dim3(H, B), cross_threads, cross_smem, stream>>>(q, ckv[l].hi, ckv[l].lo, d_off, d_off + B, max_T, D, dk, att);
+            if (gemm(att, D, A.co, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.co_b, x, D), B)) return -1;
+            if (layer_norm(x, A.ln_ffn_w, A.ln_ffn_b, nullptr, xn, B, D, 0, stream)) return -1;
+            if (gemm(xn, D, A.ff1, aed_epi(OUT_H16, ACT_RELU, 1.f, A.ff1_b, nullptr, 0, ff, F), B)) return -1;
+            if (gemm(ff, F, A.ff2, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.ff2_b, x, D), B)) return -1;
+            note_launch(5);
+        }
+        const bool sample = p + 1 >= min_prompt;             // someone leaves its prompt at this position
+        if (sample) {
+            if (layer_norm(x, aed_fin_w, aed_fin_b, nullptr, xn, B, D, 0, stream)) return -1;
+            if (gemm(xn, D, aed_head, aed_epi(OUT_F32, ACT_NONE, 1.f, aed_head_b, logits, V), B)) return -1;
+            if (argmax_rows(logits, V, nullptr, B, V, best, stream)) return -1;
+            note_launch(2);
+        }
+        aed_select_kernel<<<1, B <= 32 ? 32 : ((B + 31) / 32) * 32, 0, stream>>>(sample ? best : nullptr, p, eos, capn, B, st, d_prompts, max_prompt, d_tokens);
+        note_launch();
+        MB_CUDA(cudaGetLastError());
+        if ((p & 3) == 3 || p + 1 == max_len) {              // look at the finished count every fourth position
+            MB_CUDA(cudaMemcpyAsync(&n_done, st + 6 * B, sizeof(int), cudaMemcpyDeviceToHost, stream));
+            MB_CUDA(cudaStreamSynchronize(stream));
+        }
+    }
+    prof_end_span(sp);
+    if (sp >= 0) prof_launches[PROF_DECODE]++;
+    std::vector<int> hn(B), ht((size_t)B * capn);
+    MB_CUDA(cudaMemcpyAsync(hn.data(), st + B, B * sizeof(int), cudaMemcpyDeviceToHost, stream));
+    MB_CUDA(cudaMemcpyAsync(ht.data(), d_tokens, ht.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
+    MB_CUDA(cudaStreamSynchronize(stream));
+    if (check_status("aed_decode")) return -1;
+    for (int b = 0; b < B; b++) tokens[b].assign(ht.begin() + (size_t)b * capn, ht.begin() + (size_t)b * capn + hn[b]);
+    ws.off = mark;
+    return 0;
+}
+
+}  // namespace mb

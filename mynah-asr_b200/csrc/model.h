@@ -40,6 +40,14 @@ struct EncLayer {
     const float *bias_u, *bias_v, *dw_w, *dw_b, *cnorm_w, *cnorm_b, *cnorm_scale, *cnorm_shift;
 };
 
+// One layer of the AED transformer decoder (mynah_asr_aed_layer, src/decoder_aed.h:13-24): the self-attention
+// q/k/v projections and the cross-attention k/v projections are stored concatenated by rows.
+struct AedLayer {
+    const float *ln_self_w, *ln_self_b, *ln_cross_w, *ln_cross_b, *ln_ffn_w, *ln_ffn_b;
+    QWeight sqkv, so, cq, ckv, co, ff1, ff2;
+    const float *sqkv_b, *so_b, *cq_b, *ckv_b, *co_b, *ff1_b, *ff2_b;
+};
+
 struct Model {
     mynah_b200_config cfg;
     std::map<std::string, HostTensor> host;          // until finalize
@@ -81,6 +89,14 @@ struct Model {
     QWeight head, dec_proj, wcat[DEC_MAX_LAYERS];    // wcat[l] = [W_ih | W_hh] of LSTM layer l
     int vocab = 0, pred_hidden = 0, pred_layers = 0;
 
+    // AED decoder (mynah_asr_aed, src/decoder_aed.h:26-38)
+    bool has_aed = false, has_aed_proj = false;
+    int aed_d = 0, aed_heads = 0, aed_ffn = 0, aed_vocab = 0, aed_max_seq = 0;
+    const float *aed_emb = nullptr, *aed_pos = nullptr, *aed_embln_w = nullptr, *aed_embln_b = nullptr, *aed_fin_w = nullptr,
+                *aed_fin_b = nullptr, *aed_head_b = nullptr, *aed_proj_b = nullptr;
+    QWeight aed_head, aed_proj;
+    std::vector<AedLayer> aed_layers;
+
     // mel
     std::vector<float> mel_fb_host, window_host;
     float *mel_fb = nullptr;
@@ -103,6 +119,10 @@ struct Model {
     int decode_ctc(const float *enc_dev, int T, std::vector<int> &tokens, std::vector<int> &frames);
     int decode_greedy(const float *enc_dev, const std::vector<int> &lens, std::vector<std::vector<int>> &tokens,
                       std::vector<std::vector<int>> &frames);
+    // packed encoder output [sum T, d_out] -> generated tokens per utterance (prompt and EOS excluded); caps[b] bounds utterance b
+    int decode_aed(const float *enc_dev, const std::vector<int> &lens, const std::vector<std::vector<int>> &prompts, int eos,
+                   const std::vector<int> &caps, std::vector<std::vector<int>> &tokens);
+    size_t aed_bytes(int total_T, int B, int max_len) const;
     int log_mel(const float *audio_dev, size_t n, float *feats_dev, int T, int valid);
     static int sub_len(int n, bool causal) { return (n + (causal ? 3 : 2) - 3) / 2 + 1; }
     int enc_len(int t_mel) const { int t = t_mel; for (int i = 0; i < 3; i++) t = sub_len(t, causal); return t; }
