@@ -143,9 +143,16 @@ def run_reference(args, rank, world):
                         n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
                         max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), causal=int(cfg.causal))
 
+        if cfg.decoder == "aed":
+            rm.aed_open(cfg.aed_layers, cfg.aed_heads, cfg.aed_max_seq, cfg.aed_max_gen_delta)
+
         def step():
             feats, valid = rm.log_mel(audio)
+            if cfg.decoder == "ctc":
+                return rm.ctc_decode(rm.encoder_forward(feats[:valid], cfg.left, cfg.right, raw=True))
             enc = rm.encoder_forward(feats[:valid], cfg.left, cfg.right)
+            if cfg.decoder == "aed":
+                return rm.aed_decode(enc, AED_PROMPT, AED_EOS, enc.shape[0] + cfg.aed_max_gen_delta)
             return rm.greedy_decode(enc, cfg.max_symbols)
     else:
         kind = "port"
@@ -153,7 +160,11 @@ def run_reference(args, rank, world):
 
         def step():
             feats, valid = O.log_mel(audio, fb, win, normalize_per_feature=cfg.normalize)
+            if cfg.decoder == "ctc":
+                return O.ctc_decode(O.encoder_forward(M, feats[:valid], cfg.left, cfg.right, raw=True), M["ctc_w"], M["ctc_b"])
             enc = O.encoder_forward(M, feats[:valid], cfg.left, cfg.right)
+            if cfg.decoder == "aed":
+                return O.aed_decode(M["aed"], enc, AED_PROMPT, AED_EOS, enc.shape[0] + cfg.aed_max_gen_delta)
             return O.greedy_decode(M["dec"], enc)
     for _ in range(args.warmup):
         step()
@@ -174,9 +185,16 @@ def run_reference(args, rank, world):
     }))
 
 
+AED_PROMPT, AED_EOS = (3, 4, 5, 6, 7), 2     # stand-ins for the canary2 prompt and <|endoftext|>
+SHAPES = {"cfg0": "Parakeet-TDT_CTC-110M", "cfg1": "Parakeet-TDT-0.6B", "cfg2": "Parakeet-RNNT-1.1B",
+          "cfg3": "Nemotron-streaming-0.6B (offline path)", "cfg4": "Canary-1B"}
+
+
 def workload_desc(args, cfg):
-    return {"workload": f"{args.workload}: Parakeet-TDT-0.6B-shaped, {cfg.n_layers} layers d={cfg.d_model} "
-                        f"ffn={cfg.ffn_dim}, {cfg.wtype.upper()} weights, TDT greedy, "
+    dec = {"ctc": "CTC greedy", "tdt": "TDT greedy", "rnnt": "RNNT greedy",
+           "aed": f"AED greedy ({cfg.aed_layers}-layer decoder, budget T+{cfg.aed_max_gen_delta})"}[cfg.decoder]
+    return {"workload": f"{args.workload}: {SHAPES.get(args.workload, args.workload)}-shaped, {cfg.n_layers} layers d={cfg.d_model} "
+                        f"ffn={cfg.ffn_dim}, {cfg.wtype.upper()} weights, {dec}, "
                         f"{args.batch} x {args.seconds:g} s per GPU",
             "batch_per_gpu": args.batch, "audio_seconds": args.seconds, "numerics": getattr(args, "mode", "strict"),
             "l2": "per-step working set (activations + weights, >1 GB) exceeds the 126 MB L2"}
@@ -199,8 +217,17 @@ def cpu_baseline(args, cfg, tensors, synth):
     for i in range(2):           # first pass warms the page cache / BLAS threads
         t0 = time.perf_counter()
         feats, valid = rm.log_mel(audio)
-        enc = rm.encoder_forward(feats[:valid], cfg.left, cfg.right)
-        toks = rm.greedy_decode(enc, cfg.max_symbols)
+        if cfg.decoder == "ctc":
+            toks = rm.ctc_decode(rm.encoder_forward(feats[:valid], cfg.left, cfg.right, raw=True))
+        elif cfg.decoder == "aed":
+            if i == 0:
+                rm.aed_open(cfg.aed_layers, cfg.aed_heads, cfg.aed_max_seq, cfg.aed_max_gen_delta)
+            enc = rm.encoder_forward(feats[:valid], cfg.left, cfg.right)
+            t = rm.aed_decode(enc, AED_PROMPT, AED_EOS, enc.shape[0] + cfg.aed_max_gen_delta)
+            toks = (t.tolist(), [0] * len(t))
+        else:
+            enc = rm.encoder_forward(feats[:valid], cfg.left, cfg.right)
+            toks = rm.greedy_decode(enc, cfg.max_symbols)
         times.append(time.perf_counter() - t0)
     rm.close()
     return {"value": args.seconds / min(times), "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
@@ -250,7 +277,8 @@ def main():
     model = pkg.Model(tensors, n_mels=cfg.n_mels, mel_fb=synth.mel_filterbank(cfg.n_mels),
                       window=synth.hann_window(), causal=int(cfg.causal), normalize=cfg.normalize, left=cfg.left,
                       right=cfg.right, blank=cfg.vocab - 1, max_symbols=cfg.max_symbols,
-                      durations=tuple(cfg.durations), strict=args.mode == "strict")
+                      durations=tuple(cfg.durations), strict=args.mode == "strict", aed_heads=cfg.aed_heads)
+    dec_id = {"ctc": 1, "aed": 2}.get(cfg.decoder, 0)
     # this rank's utterances: global item ids shard over ranks (weak scaling: batch per GPU fixed)
     items = shard(args.batch * world, rank, world)
     n = int(round(args.seconds * 16000))
@@ -263,8 +291,16 @@ def main():
 
     # ---- value: inputs resident in HBM
     bh = model.batch_upload(audio)
+    if dec_id == 2:
+        model.batch_set_aed(bh, AED_PROMPT, AED_EOS, cfg.aed_max_gen_delta)
+
+    def public_call():
+        if dec_id == 2:
+            return [(t, [0] * len(t)) for t in model.transcribe_batch_aed(audio, AED_PROMPT, AED_EOS, cfg.aed_max_gen_delta)]
+        return model.transcribe_batch(audio, dec_id)
+
     for _ in range(args.warmup):
-        model.batch_run(bh)
+        model.batch_run(bh, dec_id)
     clocks = ClockSampler(local)
     barrier()
     if rank == 0:
@@ -275,7 +311,7 @@ def main():
     barrier()
     e0.record(stream)
     for _ in range(args.steps):
-        model.batch_run(bh)
+        model.batch_run(bh, dec_id)
     e1.record(stream)
     e1.synchronize()
     barrier()
@@ -291,13 +327,13 @@ def main():
         res, e2e_ms = resident_tokens, float("nan")
     else:
         for _ in range(min(args.warmup, 2)):
-            model.transcribe_batch(audio)
+            public_call()
         barrier()
         t0 = time.perf_counter()
         f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         f0.record(stream)
         for _ in range(args.steps):
-            res = model.transcribe_batch(audio)
+            res = public_call()
         f1.record(stream)
         f1.synchronize()
         e2e_ms = max(f0.elapsed_time(f1), (time.perf_counter() - t0) * 1e3)

@@ -391,6 +391,10 @@ class Model:
             raise BackendError("batch_upload: " + _err())
         return h
 
+    def batch_set_aed(self, bh, prompt, eos, max_gen_delta):
+        pr = (C.c_int * len(prompt))(*prompt)
+        lib().mynah_b200_batch_set_aed(bh, pr, len(prompt), eos, max_gen_delta)
+
     def batch_run(self, bh, decoder=0):
         _check(lib().mynah_b200_batch_run(self.h, bh, decoder), "batch_run")
 

@@ -9,10 +9,11 @@
 
 namespace mb {
 
+// The position p lives in device memory (pd) so that one captured CUDA graph serves every position.
 // x[b] = emb[cur[b]] + pos[p]   (src/decoder_aed.c:183-184; the LayerNorm follows as its own launch)
-__global__ void aed_embed_kernel(const float *__restrict__ emb, const float *__restrict__ pos, const int *__restrict__ cur, int p,
-                                 float *__restrict__ x, int D) {
-    const int b = blockIdx.x;
+__global__ void aed_embed_kernel(const float *__restrict__ emb, const float *__restrict__ pos, const int *__restrict__ cur,
+                                 const int *__restrict__ pd, float *__restrict__ x, int D) {
+    const int b = blockIdx.x, p = *pd;
     const float *e = emb + (size_t)cur[b] * D, *pe = pos + (size_t)p * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)b * D + i] = e[i] + pe[i];
 }
@@ -32,9 +33,10 @@ __device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) 
 // Causal self-attention of one new position (src/decoder_aed.c:191-196 with attend, :117-131):
 // appends this step's k, v to the cache and attends over positions 0..p. Grid (H, B).
 // qkv [B, 3D] = (q | k | v) with biases already added; cache [B, max_len, D] each.
-__global__ void aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, float *__restrict__ cv, int p, int max_len,
-                                     int D, int dk, H16 out) {
+__global__ void aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, float *__restrict__ cv,
+                                     const int *__restrict__ pd, int max_len, int D, int dk, H16 out) {
     extern __shared__ float sm[];
+    const int p = *pd;
     float *sc = sm, *q = sm + max_len, *red = q + dk;
     const int h = blockIdx.x, b = blockIdx.y;
     const float *row = qkv + (size_t)b * 3 * D + h * dk;
@@ -127,13 +129,16 @@ __global__ void aed_cross_attn_kernel(const float *__restrict__ qm, const __half
     }
 }
 
-// Greedy selection at position p (src/decoder_aed.c:211-223). best may be null while every
-// utterance is still inside its prompt. st: [cur | n_out | done | n_prompt | max_len | cap] x B, then n_done.
-__global__ void aed_select_kernel(const int *__restrict__ best, int p, int eos, int cap_stride, int B, int *st, const int *__restrict__ prompts,
+// Greedy selection at position p (src/decoder_aed.c:211-223), then p += 1. One block.
+// st: [cur | n_out | done | n_prompt | max_len | cap] x B, then n_done, p.
+__global__ void aed_select_kernel(const int *__restrict__ best, int eos, int cap_stride, int B, int *st, const int *__restrict__ prompts,
                                   int max_prompt, int *__restrict__ tokens) {
     const int b = threadIdx.x;
-    if (b >= B) return;
     int *cur = st, *n_out = st + B, *done = st + 2 * B, *n_prompt = st + 3 * B, *max_len = st + 4 * B, *n_done = st + 6 * B;
+    const int p = st[6 * B + 1];
+    __syncthreads();
+    if (b == 0) st[6 * B + 1] = p + 1;
+    if (b >= B) return;
     const int cap = st[5 * B + b];
     if (done[b]) return;
     bool fin = false;
@@ -232,17 +237,17 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     MB_CUDA(cudaFuncSetAttribute(aed_self_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)self_smem));
     MB_CUDA(cudaFuncSetAttribute(aed_cross_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cross_smem));
     const int sp = prof_begin_span(PROF_DECODE);
-    int n_done = 0;
-    for (int p = 0; p < max_len && n_done < B; p++) {
-        aed_embed_kernel<<<B, 128, 0, stream>>>(aed_emb, aed_pos, st, p, x, D);
+    const int *pd = st + 6 * B + 1;
+    // everything one position needs, in stream order; no host value changes between positions
+    auto position = [&]() -> int {
+        aed_embed_kernel<<<B, 128, 0, stream>>>(aed_emb, aed_pos, st, pd, x, D);
         if (layer_norm(x, aed_embln_w, aed_embln_b, x, H16{nullptr, nullptr}, B, D, 0, stream)) return -1;
-        note_launch(2);
         for (int l = 0; l < L; l++) {
             const AedLayer &A = aed_layers[l];
             float *K = sk + (size_t)(2 * l) * B * max_len * D, *Vc = K + (size_t)B * max_len * D;
             if (layer_norm(x, A.ln_self_w, A.ln_self_b, nullptr, xn, B, D, 0, stream)) return -1;
             if (gemm(xn, D, A.sqkv, aed_epi(OUT_F32, ACT_NONE, 1.f, A.sqkv_b, qkv, 3 * D), B)) return -1;
-            aed_self_attn_kernel<<<dim3(H, B), 128, self_smem, stream>>>(qkv, K, Vc, p, max_len, D, dk, att);
+            aed_self_attn_kernel<<<dim3(H, B), 128, self_smem, stream>>>(qkv, K, Vc, pd, max_len, D, dk, att);
             if (gemm(att, D, A.so, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.so_b, x, D), B)) return -1;
             if (layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream)) return -1;
             if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B)) return -1;
@@ -251,23 +256,56 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
             if (layer_norm(x, A.ln_ffn_w, A.ln_ffn_b, nullptr, xn, B, D, 0, stream)) return -1;
             if (gemm(xn, D, A.ff1, aed_epi(OUT_H16, ACT_RELU, 1.f, A.ff1_b, nullptr, 0, ff, F), B)) return -1;
             if (gemm(ff, F, A.ff2, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.ff2_b, x, D), B)) return -1;
-            note_launch(5);
         }
-        const bool sample = p + 1 >= min_prompt;             // someone leaves its prompt at this position
-        if (sample) {
-            if (layer_norm(x, aed_fin_w, aed_fin_b, nullptr, xn, B, D, 0, stream)) return -1;
-            if (gemm(xn, D, aed_head, aed_epi(OUT_F32, ACT_NONE, 1.f, aed_head_b, logits, V), B)) return -1;
-            if (argmax_rows(logits, V, nullptr, B, V, best, stream)) return -1;
-            note_launch(2);
-        }
-        aed_select_kernel<<<1, B <= 32 ? 32 : ((B + 31) / 32) * 32, 0, stream>>>(sample ? best : nullptr, p, eos, capn, B, st, d_prompts, max_prompt, d_tokens);
-        note_launch();
+        // the head is evaluated at prompt positions too (its result is ignored there): one graph for all positions
+        if (layer_norm(x, aed_fin_w, aed_fin_b, nullptr, xn, B, D, 0, stream)) return -1;
+        if (gemm(xn, D, aed_head, aed_epi(OUT_F32, ACT_NONE, 1.f, aed_head_b, logits, V), B)) return -1;
+        if (argmax_rows(logits, V, nullptr, B, V, best, stream)) return -1;
+        aed_select_kernel<<<1, ((B + 31) / 32) * 32, 0, stream>>>(best, eos, capn, B, st, d_prompts, max_prompt, d_tokens);
         MB_CUDA(cudaGetLastError());
-        if ((p & 3) == 3 || p + 1 == max_len) {              // look at the finished count every fourth position
+        return 0;
+    };
+    const int launches_per_position = 2 + L * 13 + 4, gemms_per_position = 7 * L + 1;   // (the contraction wrapper counts its own launches)
+    (void)min_prompt;
+    int n_done = 0;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int rc = 0;
+    for (int p = 0; p < max_len && n_done < B && rc == 0; p++) {
+        if (p == 0) {
+            rc = position();                                 // eager: also sets every kernel's launch attributes
+            note_launch(launches_per_position - gemms_per_position);
+        } else {
+            if (p == 1) {
+                // positions 1.. replay one captured graph (57 small launches per position are launch-bound otherwise)
+                const bool was_on = prof_on;
+                prof_on = false;                             // no event records inside the capture
+                if (cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+                    const int prc = position();
+                    note_launch(-gemms_per_position);        // recorded, not launched
+                    cudaGraph_t g = nullptr;
+                    const cudaError_t e = cudaStreamEndCapture(stream, &g);
+                    if (prc == 0 && e == cudaSuccess && g && cudaGraphInstantiate(&exec, g, 0) == cudaSuccess) graph = g;
+                    else { if (g) cudaGraphDestroy(g); exec = nullptr; cudaGetLastError(); }
+                }
+                prof_on = was_on;
+            }
+            if (exec) {
+                if (cudaGraphLaunch(exec, stream) != cudaSuccess) { set_error("aed_decode: graph launch failed"); rc = -1; }
+                note_launch(launches_per_position);
+            } else {
+                rc = position();
+                note_launch(launches_per_position - gemms_per_position);
+            }
+        }
+        if (rc == 0 && ((p & 7) == 7 || p + 1 == max_len)) { // look at the finished count every eighth position
             MB_CUDA(cudaMemcpyAsync(&n_done, st + 6 * B, sizeof(int), cudaMemcpyDeviceToHost, stream));
             MB_CUDA(cudaStreamSynchronize(stream));
         }
     }
+    if (exec) cudaGraphExecDestroy(exec);
+    if (graph) cudaGraphDestroy(graph);
+    if (rc) return -1;
     prof_end_span(sp);
     if (sp >= 0) prof_launches[PROF_DECODE]++;
     std::vector<int> hn(B), ht((size_t)B * capn);
