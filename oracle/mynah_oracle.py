@@ -576,3 +576,128 @@ def aed_decode(A, enc, prompt, eos, cap):
         out.append(best)
         cur = best
     return np.asarray(out, np.int32)
+
+
+# ------------------------------------------------------------------ cache-aware streaming
+class EncStream:
+    """State of mynah_asr_enc_stream (src/encoder.h:93-108): per-layer K/V caches of up to `left`
+    frames, conv caches of k-1 GLU rows, and the subsampling's one-frame caches."""
+
+    def __init__(self, M, left, right, n_mels):
+        self.M, self.left, self.right, self.q = M, left, right, right + 1
+        d, nl = M["layers"][0]["q_w"].shape[1], len(M["layers"])
+        k = M["layers"][0]["dw_w"].reshape(d, -1).shape[1]
+        self.kc = [np.zeros((0, d), f32) for _ in range(nl)]
+        self.vc = [np.zeros((0, d), f32) for _ in range(nl)]
+        self.cc = [np.zeros((k - 1, d), f32) for _ in range(nl)]
+        self.valid = 0
+        C = M["ss"]["conv_in_w"].shape[0]
+        self.ss_first = True
+        F, self.ss_cache = n_mels, []
+        for s in range(3):                                   # ss_stream_init (src/subsampling.c:272-285)
+            self.ss_cache.append(np.zeros((1 if s == 0 else C, F), f32))
+            F = F // 2 + 1
+
+    def need(self):
+        """mynah_asr_enc_stream_need (src/encoder.c:685-689)."""
+        return 1 + 8 * self.right if (self.valid == 0 and self.ss_first) else 8 * (self.right + 1)
+
+
+def _ss_stream_stage(x, first, last, cache, w, b, depthwise):
+    """stream_stage (src/subsampling.c:289-318): time axis = [zero if first][cached frame][chunk][zero if last],
+    valid stride-2 conv in time, (2,1) padding in frequency; the cache becomes the chunk's last frame."""
+    C, T, F = x.shape
+    lp, rp = (2 if first else 1), (1 if last else 0)
+    xp = np.zeros((C, T + lp + rp, F), f32)
+    xp[:, lp - 1] = cache
+    xp[:, lp:lp + T] = x
+    cache[...] = x[:, T - 1]
+    return _conv3x3_s2(xp, w, b, 0, 0, 2, 1, depthwise)
+
+
+def ss_stream_step(W, st, mel, is_last):
+    """mynah_asr_ss_stream_step (src/subsampling.c:320-370): mel chunk [n, n_mels] -> [q, d_model]."""
+    a = np.maximum(_ss_stream_stage(mel[None].astype(f32), st.ss_first, is_last, st.ss_cache[0], W["conv_in_w"], W["conv_in_b"], False), 0)
+    for i in range(2):
+        bq = _ss_stream_stage(a, st.ss_first, is_last, st.ss_cache[i + 1], W["dw_w"][i], W["dw_b"][i], True)
+        C, To, Fo = bq.shape
+        a = (W["pw_w"][i].reshape(C, C) @ bq.reshape(C, -1)).astype(f32).reshape(C, To, Fo) + W["pw_b"][i][:, None, None]
+        a = np.maximum(a, 0).astype(f32)
+    st.ss_first = False
+    C, To, Fo = a.shape
+    flat = a.transpose(1, 0, 2).reshape(To, C * Fo)
+    return (gemm_wt(flat, W["lin_w"]) + W["lin_b"][None, :]).astype(f32)
+
+
+def _stream_attention(L, x, kn, vn, pe, H, kc, vc):
+    """stream_attention (src/encoder.c:695-760): Q query rows over keys [valid cache ; chunk], no mask,
+    rel-shift index p = (K-1) - (valid + t) + j."""
+    Q, d = x.shape
+    valid = kc.shape[0]
+    K = valid + Q
+    dk = d // H
+    scaling = f32(1.0) / np.sqrt(f32(dk))
+    q = _lin(L, "q_w", x)
+    kk, vv = np.concatenate([kc, kn]), np.concatenate([vc, vn])
+    rk = gemm_wt(pe, L["relk_w"])                             # [2K-1, d]
+    ctx = np.zeros((Q, d), f32)
+    for h in range(H):
+        sl = slice(h * dk, (h + 1) * dk)
+        bd = ((q[:, sl] + L["bias_v"][h]) @ rk[:, sl].T).astype(f32)
+        ac = ((q[:, sl] + L["bias_u"][h]) @ kk[:, sl].T).astype(f32)
+        for t in range(Q):
+            base = K - 1 - valid - t
+            s = ((ac[t] + bd[t, base:base + K]) * scaling).astype(f32)
+            e = np.exp((s - s.max()).astype(f32)).astype(f32)
+            pr = (e * (f32(1.0) / e.sum(dtype=f32))).astype(f32)
+            ctx[t, sl] = (pr @ vv[:, sl]).astype(f32)
+    return _lin(L, "o_w", ctx)
+
+
+def _stream_conv_module(L, x, cache):
+    """stream_conv_module (src/encoder.c:779-807): GLU rows appended to the k-1 cached ones, depthwise
+    conv over the k rows ending at each new one, LayerNorm, SiLU, pw2. Returns (out, new cache)."""
+    Q, d = x.shape
+    h2 = _lin(L, "pw1_w", x)
+    g = (h2[:, :d] * sigmoid(h2[:, d:])).astype(f32)
+    gp = np.concatenate([cache, g])
+    dw = L["dw_w"].reshape(d, -1)
+    k = dw.shape[1]
+    c = np.zeros((Q, d), f32)
+    for j in range(k):
+        c = (c + dw[None, :, j] * gp[j:j + Q]).astype(f32)
+    return _lin(L, "pw2_w", silu(layer_norm(c, L["cnorm_w"], L["cnorm_b"]))), gp[Q:].copy()
+
+
+def enc_stream_step(st, mel, is_last=False):
+    """mynah_asr_enc_stream_step (src/encoder.c:809-872): one chunk of mel frames [n, n_mels] (n = st.need())
+    through the subsampling and every layer with the caches; returns [q, d_out]."""
+    M = st.M
+    x = ss_stream_step(M["ss"], st, mel, is_last)
+    Q, d = x.shape
+    pe = pos_emb(st.valid + Q, d)
+    for li, L in enumerate(M["layers"]):
+        x = (x + f32(0.5) * half_ffn(L, x, 0)).astype(f32)
+        xn = layer_norm(x, L["ln_att_w"], L["ln_att_b"])
+        kn, vn = _lin(L, "k_w", xn), _lin(L, "v_w", xn)
+        x = (x + _stream_attention(L, xn, kn, vn, pe, M["n_heads"], st.kc[li], st.vc[li])).astype(f32)
+        st.kc[li] = np.concatenate([st.kc[li], kn])[-st.left:] if st.left > 0 else np.zeros((0, d), f32)   # update_kv_cache :763-776
+        st.vc[li] = np.concatenate([st.vc[li], vn])[-st.left:] if st.left > 0 else np.zeros((0, d), f32)
+        y, st.cc[li] = _stream_conv_module(L, layer_norm(x, L["ln_conv_w"], L["ln_conv_b"]), st.cc[li])
+        x = (x + y).astype(f32)
+        x = (x + f32(0.5) * half_ffn(L, x, 1)).astype(f32)
+        x = layer_norm(x, L["ln_out_w"], L["ln_out_b"])
+    st.valid = min(st.valid + Q, st.left)
+    return encoder_post(M, x)
+
+
+def stream_encode(M, mel, left, right):
+    """Feeds valid mel frames through the streaming encoder in the chunk sizes it asks for
+    (the loop of mynah_asr_stream_feed, src/mynah_asr.c:868-890); returns the concatenated [T, d_out]."""
+    st = EncStream(M, left, right, mel.shape[1])
+    outs, pos, T = [], 0, mel.shape[0]
+    while pos < T:
+        n = st.need()
+        outs.append(enc_stream_step(st, mel[pos:pos + n], pos + n >= T))
+        pos += n
+    return np.concatenate(outs)

@@ -24,6 +24,7 @@ AED = {
     "aed_proj": dict(d_model=128, n_layers=1, n_heads=4, ffn_dim=256, n_mels=80, decoder="aed", vocab=211,
                      aed_d=64, aed_layers=3, aed_heads=2, aed_ffn=192, aed_max_seq=48, wtype="q4_0"),
 }
+STREAM_CONTEXTS = ((6, 0), (8, 1), (70, 0))      # (left, right) attention contexts of the streaming tests
 AED_PROMPT = (7, 9, 200, 11)
 AED_CAP = 24
 SEEDS = {"aed_same": 4}       # weight seeds whose greedy streams do not fall into a one-token fixed point

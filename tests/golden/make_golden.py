@@ -55,6 +55,9 @@ def pipeline(name):
     else:
         t, f = rm.greedy_decode(out["enc"], cfg.max_symbols)
     out["tokens"], out["frames"] = np.array(t, np.int32), np.array(f, np.int32)
+    if cfg.causal:      # cache-aware streaming (mynah_asr_enc_stream_step) fed chunk by chunk, two context shapes
+        for left, right in cases.STREAM_CONTEXTS:
+            out[f"stream_{left}_{right}"] = rm.stream_encode(feats[:valid], left, right)
     rm.close()
     np.savez_compressed(os.path.join(HERE, f"ref_{name}.npz"), **out)
     print(name, {k: getattr(v, "shape", v) for k, v in out.items()}, "tokens", len(t), "distinct", len(set(t)))
