@@ -159,6 +159,25 @@ int mynah_b200_aed_decode_batch(mynah_b200_model *m, const float *const *encs, c
                                 const int *const *prompts, const int *n_prompts, int eos, const int *caps, int **tokens,
                                 int *n_tokens);
 
+/* ---- cache-aware streaming (Nemotron-style causal encoders) ------------------------ */
+/* replaces mynah_asr_enc_stream_init / _need / _step / _free (src/encoder.h:110-120) for n_streams
+ * streams that advance in lock step: every step takes one chunk of mel frames from each stream and
+ * returns q = right_ctx + 1 encoder frames per stream. The K/V caches (left_ctx frames per layer), the
+ * conv caches and the subsampling's one-frame caches of all streams stay on the device; all streams of a
+ * group start together (open one group per start time). */
+typedef struct mynah_b200_stream_group mynah_b200_stream_group;
+mynah_b200_stream_group *mynah_b200_stream_open(mynah_b200_model *m, int n_streams, int left_ctx, int right_ctx);
+void mynah_b200_stream_close(mynah_b200_stream_group *g);
+/* mel frames every stream must supply to the next step: 1 + 8 right_ctx first, then 8 (right_ctx + 1) */
+int mynah_b200_stream_need(const mynah_b200_stream_group *g);
+/* mel [n_streams, n_mel, n_mels] -> out [n_streams, q, d_out] (host buffers, room for right_ctx + 3 frames
+ * per stream as in the reference's callers); n_mel = stream_need() except
+ * for the last, shorter chunk (is_last = 1: causal right padding as offline). Returns q, -1 on error. */
+int mynah_b200_stream_step(mynah_b200_stream_group *g, const float *mel, int n_mel, int is_last, float *out);
+/* the same with device buffers on both sides (asynchronous on the model's stream) */
+int mynah_b200_stream_step_device(mynah_b200_stream_group *g, const float *mel_dev, int n_mel, int is_last,
+                                  float *out_dev);
+
 /* ---- whole path, resident ------------------------------------------------------- */
 /* audio in, token ids out: log-mel -> encoder (packed batch) -> greedy decoder, with only the
  * audio and the token ids crossing PCIe. The device-resident counterpart of one wave of

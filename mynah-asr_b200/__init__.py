@@ -40,6 +40,31 @@ class BackendError(RuntimeError):
     pass
 
 
+class StreamGroup:
+    """n streams advancing in lock step through the cache-aware streaming encoder."""
+
+    def __init__(self, model, handle, n, q):
+        self.model, self.h, self.n, self.q = model, handle, n, q
+
+    def need(self):
+        return lib().mynah_b200_stream_need(self.h)
+
+    def step(self, mel, is_last=False):
+        """mel [n, n_mel, n_mels] -> [n, q, d_out]"""
+        mel = np.ascontiguousarray(mel, np.float32)
+        assert mel.ndim == 3 and mel.shape[0] == self.n
+        out = np.empty((self.n, self.q + 2, self.model.d_out), np.float32)
+        q = lib().mynah_b200_stream_step(self.h, _fp(mel), mel.shape[1], int(is_last), _fp(out))
+        if q < 0:
+            raise BackendError("stream_step: " + _err())
+        return out.reshape(-1)[:self.n * q * self.model.d_out].reshape(self.n, q, self.model.d_out).copy()
+
+    def close(self):
+        if self.h:
+            lib().mynah_b200_stream_close(self.h)
+            self.h = None
+
+
 _lib = None
 
 
@@ -78,6 +103,13 @@ def lib():
                                                   C.POINTER(C.c_void_p), c_ip]
     L.mynah_b200_batch_set_aed.argtypes = [vp, c_ip, ci, ci, ci]
     L.mynah_b200_batch_set_aed.restype = None
+    L.mynah_b200_stream_open.restype = vp
+    L.mynah_b200_stream_open.argtypes = [vp, ci, ci, ci]
+    L.mynah_b200_stream_close.argtypes = [vp]
+    L.mynah_b200_stream_close.restype = None
+    L.mynah_b200_stream_need.argtypes = [vp]
+    L.mynah_b200_stream_step.argtypes = [vp, c_fp, ci, ci, c_fp]
+    L.mynah_b200_stream_step_device.argtypes = [vp, vp, ci, ci, vp]
     L.mynah_b200_profile_bytes.argtypes = [vp, C.POINTER(C.c_double), ci]
     L.mynah_b200_decoder_clocks.argtypes = [vp, C.POINTER(C.c_longlong)]
     L.mynah_b200_model_new.restype = vp
@@ -367,6 +399,13 @@ class Model:
         _check(lib().mynah_b200_transcribe_batch_aed(self.h, ptrs, ns, B, pr, len(prompt), eos, max_gen_delta, tk, nt),
                "transcribe_batch_aed")
         return [_take_i32(tk[b], nt[b]) for b in range(B)]
+
+    # ---- cache-aware streaming
+    def stream_open(self, n_streams, left, right):
+        g = lib().mynah_b200_stream_open(self.h, n_streams, left, right)
+        if not g:
+            raise BackendError("stream_open: " + _err())
+        return StreamGroup(self, g, n_streams, right + 1)
 
     # ---- audio in, tokens out
     @staticmethod

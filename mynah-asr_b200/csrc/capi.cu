@@ -26,6 +26,11 @@ struct mynah_b200_batch {
     int aed_eos = -1, aed_delta = 0;     // the end-of-sequence id and the generation allowance beyond T
 };
 
+struct mynah_b200_stream_group {
+    mynah_b200_model *model = nullptr;
+    mb::StreamState st;
+};
+
 namespace mb {
 QmatView qmat_view(const void *handle) {
     const mynah_b200_qmat *q = static_cast<const mynah_b200_qmat *>(handle);
@@ -639,6 +644,55 @@ void mynah_b200_batch_set_aed(mynah_b200_batch *bt, const int *prompt, int n_pro
     if (!bt) return;
     bt->aed_prompt.assign(prompt, prompt + (n_prompt > 0 ? n_prompt : 0));
     bt->aed_eos = eos; bt->aed_delta = max_gen_delta;
+}
+
+// ------------------------------------------------------------ cache-aware streaming
+mynah_b200_stream_group *mynah_b200_stream_open(mynah_b200_model *h, int n_streams, int left_ctx, int right_ctx) {
+    if (!h || !h->m.finalized) { set_error("stream_open: bad argument"); return nullptr; }
+    std::lock_guard<std::mutex> lk(h->m.mu);
+    mynah_b200_stream_group *g = new mynah_b200_stream_group();
+    g->model = h;
+    if (h->m.stream_open(g->st, n_streams, left_ctx, right_ctx)) { h->m.stream_close(g->st); delete g; return nullptr; }
+    return g;
+}
+
+void mynah_b200_stream_close(mynah_b200_stream_group *g) {
+    if (!g) return;
+    { std::lock_guard<std::mutex> lk(g->model->m.mu); g->model->m.stream_close(g->st); }
+    delete g;
+}
+
+int mynah_b200_stream_need(const mynah_b200_stream_group *g) { return g ? g->model->m.stream_need(g->st) : -1; }
+
+int mynah_b200_stream_step_device(mynah_b200_stream_group *g, const float *mel_dev, int n_mel, int is_last, float *out_dev) {
+    if (!g || !mel_dev || !out_dev) { set_error("stream_step: bad argument"); return -1; }
+    Model &m = g->model->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    if (n_mel != m.stream_need(g->st) && !is_last) { set_error("stream_step: %d mel frames given, %d needed", n_mel, m.stream_need(g->st)); return -1; }
+    if (m.ws.reserve(m.stream_bytes(g->st, n_mel))) return -1;
+    m.ws.reset();
+    const int q = m.stream_step(g->st, mel_dev, n_mel, is_last, out_dev);
+    if (q < 0 || m.check_status("stream_step")) return -1;
+    return q;
+}
+
+int mynah_b200_stream_step(mynah_b200_stream_group *g, const float *mel, int n_mel, int is_last, float *out) {
+    if (!g || !mel || !out || n_mel <= 0) { set_error("stream_step: bad argument"); return -1; }
+    Model &m = g->model->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    if (n_mel != m.stream_need(g->st) && !is_last) { set_error("stream_step: %d mel frames given, %d needed", n_mel, m.stream_need(g->st)); return -1; }
+    const size_t S = g->st.S, nin = S * n_mel * m.cfg.n_mels, nout = S * (g->st.q + 2) * m.d_out;
+    if (m.ws.reserve(m.stream_bytes(g->st, n_mel) + (nin + nout) * 4 + 4096)) return -1;
+    m.ws.reset();
+    float *md = m.ws.get<float>(nin), *od = m.ws.get<float>(nout);
+    if (!md || !od) return -1;
+    MB_CUDA(cudaMemcpyAsync(md, mel, nin * 4, cudaMemcpyHostToDevice, m.stream));
+    const int q = m.stream_step(g->st, md, n_mel, is_last, od);
+    if (q < 0) return -1;
+    MB_CUDA(cudaMemcpyAsync(out, od, S * q * m.d_out * 4, cudaMemcpyDeviceToHost, m.stream));
+    MB_CUDA(cudaStreamSynchronize(m.stream));
+    if (m.check_status("stream_step")) return -1;
+    return q;
 }
 
 // ------------------------------------------------------------ resident pipeline

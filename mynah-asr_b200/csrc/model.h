@@ -48,6 +48,18 @@ struct AedLayer {
     const float *sqkv_b, *so_b, *cq_b, *ckv_b, *co_b, *ff1_b, *ff2_b;
 };
 
+// Cache-aware streaming state of S streams that advance in lock step (the device counterpart of S
+// mynah_asr_enc_stream objects, src/encoder.h:93-108). K/V caches are rings of `left` slots: the j-th
+// oldest valid frame of every stream sits in slot (start + j) % left.
+struct StreamState {
+    int S = 0, left = 0, right = 0, q = 1;
+    int first = 1, valid = 0, start = 0;
+    float *ss_cache[3] = {nullptr, nullptr, nullptr};   // last input frame of each subsampling stage: [S,F0], [S,F1,C], [S,F2,C]
+    __half *k_cache = nullptr, *v_cache = nullptr;      // [L][S][left][d] fp16
+    float *conv_cache = nullptr;                        // [L][S][k-1][d] GLU rows
+    std::vector<void *> owned;
+};
+
 struct Model {
     mynah_b200_config cfg;
     std::map<std::string, HostTensor> host;          // until finalize
@@ -123,6 +135,12 @@ struct Model {
     int decode_aed(const float *enc_dev, const std::vector<int> &lens, const std::vector<std::vector<int>> &prompts, int eos,
                    const std::vector<int> &caps, std::vector<std::vector<int>> &tokens);
     size_t aed_bytes(int total_T, int B, int max_len) const;
+    // one chunk of every stream: mel_dev [S, n_mel, n_mels] -> out_dev [S, q, d_out]; returns q or -1
+    int stream_open(StreamState &st, int S, int left, int right);
+    void stream_close(StreamState &st);
+    int stream_need(const StreamState &st) const { return st.valid == 0 && st.first ? 1 + 8 * st.right : 8 * (st.right + 1); }
+    size_t stream_bytes(const StreamState &st, int n_mel) const;
+    int stream_step(StreamState &st, const float *mel_dev, int n_mel, int is_last, float *out_dev);
     int log_mel(const float *audio_dev, size_t n, float *feats_dev, int T, int valid);
     static int sub_len(int n, bool causal) { return (n + (causal ? 3 : 2) - 3) / 2 + 1; }
     int enc_len(int t_mel) const { int t = t_mel; for (int i = 0; i < 3; i++) t = sub_len(t, causal); return t; }

@@ -1,0 +1,317 @@
+// Cache-aware streaming encoder step for S streams in lock step: the device counterpart of
+// mynah_asr_enc_stream_step (src/encoder.c:809-872) with ss_stream_step (src/subsampling.c:320-370),
+// stream_attention (:695-760), update_kv_cache (:763-776) and stream_conv_module (:779-807).
+// Where the reference runs 240 weight-streaming GEMVs per stream and chunk, the streams of a group are
+// stacked: every linear is one contraction over M = S * q rows, so the weights cross HBM once per
+// chunk for all streams. Only the parts that touch per-stream state are kernels of their own.
+#include "model.h"
+
+namespace mb {
+
+// ---- subsampling stages on a chunk (time axis = [zero if first][cached frame][chunk][zero if last], valid
+// stride-2 conv in time, (2,1) zero padding in frequency: stream_stage, src/subsampling.c:289-318)
+// stage 0: mel [S, T, F] (one channel) -> out [S, To, Fo, C] with ReLU
+__global__ void ss_stream_stage0_kernel(const float *__restrict__ mel, const float *__restrict__ cache, const float *__restrict__ w,
+                                        const float *__restrict__ b, float *__restrict__ out, int S, int T, int F, int C, int To, int Fo,
+                                        int lp) {
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= (size_t)S * To * Fo * C) return;
+    const int c = (int)(idx % C);
+    size_t r = idx / C;
+    const int fo = (int)(r % Fo); r /= Fo;
+    const int to = (int)(r % To);
+    const int s = (int)(r / To);
+    float acc = b[c];
+    for (int dt = 0; dt < 3; dt++) {
+        const int tp = 2 * to + dt - lp;                 // index into the chunk; -1 = cached frame, below = zero, >= T = zero
+        if (tp < -1 || tp >= T) continue;
+        const float *row = tp < 0 ? cache + (size_t)s * F : mel + ((size_t)s * T + tp) * F;
+        for (int df = 0; df < 3; df++) {
+            const int f = 2 * fo + df - 2;
+            if (f >= 0 && f < F) acc = fmaf(w[c * 9 + dt * 3 + df], row[f], acc);
+        }
+    }
+    out[idx] = fmaxf(acc, 0.f);
+}
+
+// depthwise stage: a [S, T, F, C] -> planes [S, To, Fo, C] (operand of the pointwise contraction)
+__global__ void ss_stream_dw_kernel(const float *__restrict__ a, const float *__restrict__ cache, const float *__restrict__ w,
+                                    const float *__restrict__ b, H16 out, int S, int T, int F, int C, int To, int Fo, int lp) {
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= (size_t)S * To * Fo * C) return;
+    const int c = (int)(idx % C);
+    size_t r = idx / C;
+    const int fo = (int)(r % Fo); r /= Fo;
+    const int to = (int)(r % To);
+    const int s = (int)(r / To);
+    float acc = b[c];
+    for (int dt = 0; dt < 3; dt++) {
+        const int tp = 2 * to + dt - lp;
+        if (tp < -1 || tp >= T) continue;
+        const float *row = tp < 0 ? cache + (size_t)s * F * C : a + ((size_t)s * T + tp) * F * C;
+        for (int df = 0; df < 3; df++) {
+            const int f = 2 * fo + df - 2;
+            if (f >= 0 && f < F) acc = fmaf(w[c * 9 + dt * 3 + df], row[(size_t)f * C + c], acc);
+        }
+    }
+    __half hi, lo;
+    split_h16(acc, hi, lo);
+    out.hi[idx] = hi;
+    out.lo[idx] = lo;
+}
+
+// cache[s] = last time row of x [S, T, W]
+__global__ void ss_stream_cache_kernel(const float *__restrict__ x, float *__restrict__ cache, int S, int T, int W) {
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= (size_t)S * W) return;
+    const int s = (int)(idx / W), i = (int)(idx % W);
+    cache[idx] = x[((size_t)s * T + (T - 1)) * W + i];
+}
+
+// ---- attention of the chunk's Q rows over [valid cached frames ; chunk], no mask. Grid (H, S), 128 threads.
+// score[t][j] = ((q_t + u) . k_j + (q_t + v) . rk[K-1-valid-t+j]) / sqrt(dk); ctx planes [S*Q, d].
+__global__ void stream_attn_kernel(const float *__restrict__ q, const __half *__restrict__ kn, const __half *__restrict__ vn,
+                                   const __half *__restrict__ kc, const __half *__restrict__ vc, const __half *__restrict__ rk,
+                                   const float *__restrict__ bias_u, const float *__restrict__ bias_v, H16 ctx, int Q, int valid,
+                                   int start, int left, int d, int dk) {
+    extern __shared__ float sm[];
+    const int K = valid + Q;
+    float *sc = sm;                    // [K]
+    float *qu = sc + K, *qv = qu + dk; // [dk] each
+    float *red = qv + dk;              // [32]
+    const int h = blockIdx.x, s = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float scale = 1.0f / sqrtf((float)dk);
+    const size_t cbase = (size_t)s * left * d;
+    for (int t = 0; t < Q; t++) {
+        const size_t row = (size_t)s * Q + t;
+        for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+            const float v = q[row * d + h * dk + i];
+            qu[i] = v + bias_u[h * dk + i];
+            qv[i] = v + bias_v[h * dk + i];
+        }
+        __syncthreads();
+        const int base = K - 1 - valid - t;
+        for (int j = warp; j < K; j += nw) {
+            const __half *kj = j < valid ? kc + cbase + (size_t)((start + j) % left) * d : kn + ((size_t)s * Q + (j - valid)) * d;
+            const __half *rj = rk + (size_t)(base + j) * d;
+            float a = 0.f;
+            for (int i = lane; i < dk; i += 32) {
+                a = fmaf(qu[i], __half2float(kj[h * dk + i]), a);
+                a = fmaf(qv[i], __half2float(rj[h * dk + i]), a);
+            }
+            a = warp_sum(a);
+            if (lane == 0) sc[j] = a * scale;
+        }
+        __syncthreads();
+        float m = -INFINITY;
+        for (int j = threadIdx.x; j < K; j += blockDim.x) m = fmaxf(m, sc[j]);
+        m = warp_max(m);
+        if (lane == 0) red[warp] = m;
+        __syncthreads();
+        m = red[0];
+        for (int i = 1; i < nw; i++) m = fmaxf(m, red[i]);
+        __syncthreads();
+        float sum = 0.f;
+        for (int j = threadIdx.x; j < K; j += blockDim.x) { const float e = expf(sc[j] - m); sc[j] = e; sum += e; }
+        sum = warp_sum(sum);
+        if (lane == 0) red[warp] = sum;
+        __syncthreads();
+        sum = 0.f;
+        for (int i = 0; i < nw; i++) sum += red[i];
+        const float inv = 1.0f / sum;
+        for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+            float o = 0.f;
+            for (int j = 0; j < K; j++) {
+                const __half *vj = j < valid ? vc + cbase + (size_t)((start + j) % left) * d : vn + ((size_t)s * Q + (j - valid)) * d;
+                o = fmaf(sc[j] * inv, __half2float(vj[h * dk + i]), o);
+            }
+            __half hi, lo;
+            split_h16(o, hi, lo);
+            ctx.hi[row * d + h * dk + i] = hi;
+            ctx.lo[row * d + h * dk + i] = lo;
+        }
+        __syncthreads();
+    }
+}
+
+// new k / v rows of the chunk into their ring slots (update_kv_cache, src/encoder.c:763-776)
+__global__ void stream_kv_update_kernel(const __half *__restrict__ kn, const __half *__restrict__ vn, __half *__restrict__ kc,
+                                        __half *__restrict__ vc, int S, int Q, int valid, int start, int left, int d) {
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= (size_t)S * Q * d) return;
+    const int i = (int)(idx % d);
+    const int t = (int)((idx / d) % Q), s = (int)(idx / ((size_t)d * Q));
+    const int slot = (start + valid + t) % left;
+    kc[((size_t)s * left + slot) * d + i] = kn[idx];
+    vc[((size_t)s * left + slot) * d + i] = vn[idx];
+}
+
+// GLU rows appended to the k-1 cached ones, depthwise conv over the k rows ending at each new row, cache
+// refreshed with the last k-1 rows (stream_conv_module, src/encoder.c:779-800). One thread per (stream, channel).
+template <int KMAX>
+__global__ void stream_conv_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, float *__restrict__ cache,
+                                   float *__restrict__ out, int S, int Q, int d, int k) {
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= (size_t)S * d) return;
+    const int s = (int)(idx / d), i = (int)(idx % d);
+    float seq[KMAX];                                     // k-1 cached rows then the Q new ones (k - 1 + Q <= KMAX)
+    float *cc = cache + (size_t)s * (k - 1) * d + i;
+    for (int j = 0; j < k - 1; j++) seq[j] = cc[(size_t)j * d];
+    for (int t = 0; t < Q; t++) {
+        const float *r = h2 + ((size_t)s * Q + t) * 2 * d;
+        seq[k - 1 + t] = r[i] * sigmoid_stable(r[d + i]);
+    }
+    for (int t = 0; t < Q; t++) {
+        float o = 0.f;
+        for (int j = 0; j < k; j++) o = fmaf(dw_w[(size_t)i * k + j], seq[t + j], o);
+        out[((size_t)s * Q + t) * d + i] = o;
+    }
+    for (int j = 0; j < k - 1; j++) cc[(size_t)j * d] = seq[Q + j];
+}
+
+static GemmEpilogue st_epi(int mode, int act, float alpha, const float *bias, float *out, int ldo, H16 h = H16{nullptr, nullptr}, int ldh = 0) {
+    GemmEpilogue e;
+    memset(&e, 0, sizeof(e));
+    e.mode = mode; e.act = act; e.alpha = alpha; e.bias = bias; e.out = out; e.ldo = ldo; e.out_hi = h.hi; e.out_lo = h.lo; e.ldh = ldh;
+    return e;
+}
+
+static constexpr int STREAM_CONV_MAX = 48;               // k - 1 + q rows held in registers by stream_conv_kernel
+
+int Model::stream_open(StreamState &st, int S, int left, int right) {
+    if (!causal) { set_error("stream_open: cache-aware streaming needs a causal (Nemotron-style) encoder"); return -1; }
+    if (S <= 0 || left < 0 || right < 0) { set_error("stream_open: bad argument"); return -1; }
+    if (left > 0 && right + 1 > left) { set_error("stream_open: chunk of %d frames exceeds the left context %d", right + 1, left); return -1; }
+    if (conv_k - 1 + right + 1 > STREAM_CONV_MAX) { set_error("stream_open: conv kernel %d with chunks of %d frames is too long", conv_k, right + 1); return -1; }
+    for (const EncLayer &L : layers) if (L.cnorm_scale) { set_error("stream_open: streaming needs the LayerNorm conv norm"); return -1; }
+    st = StreamState();
+    st.S = S; st.left = left; st.right = right; st.q = right + 1;
+    const int C = channels;
+    int F = cfg.n_mels;
+    for (int s = 0; s < 3; s++) {
+        const size_t n = (size_t)S * F * (s == 0 ? 1 : C);
+        st.ss_cache[s] = (float *)dev_alloc(n * sizeof(float));
+        if (!st.ss_cache[s]) return -1;
+        MB_CUDA(cudaMemsetAsync(st.ss_cache[s], 0, n * sizeof(float), stream));
+        st.owned.push_back(st.ss_cache[s]);
+        F = F / 2 + 1;
+    }
+    const size_t kv = (size_t)n_layers * S * (left > 0 ? left : 1) * d_model, cv = (size_t)n_layers * S * (conv_k - 1) * d_model;
+    st.k_cache = (__half *)dev_alloc(kv * sizeof(__half));
+    st.v_cache = (__half *)dev_alloc(kv * sizeof(__half));
+    st.conv_cache = (float *)dev_alloc(cv * sizeof(float));
+    if (!st.k_cache || !st.v_cache || !st.conv_cache) return -1;
+    st.owned.push_back(st.k_cache); st.owned.push_back(st.v_cache); st.owned.push_back(st.conv_cache);
+    MB_CUDA(cudaMemsetAsync(st.k_cache, 0, kv * sizeof(__half), stream));
+    MB_CUDA(cudaMemsetAsync(st.v_cache, 0, kv * sizeof(__half), stream));
+    MB_CUDA(cudaMemsetAsync(st.conv_cache, 0, cv * sizeof(float), stream));
+    MB_CUDA(cudaStreamSynchronize(stream));
+    return 0;
+}
+
+void Model::stream_close(StreamState &st) {
+    for (void *p : st.owned) {
+        cudaFree(p);
+        for (auto it = owned.begin(); it != owned.end(); ++it) if (*it == p) { owned.erase(it); break; }
+    }
+    st = StreamState();
+}
+
+size_t Model::stream_bytes(const StreamState &st, int n_mel) const {
+    const size_t S = st.S, C = channels, d = d_model, Q = st.q + 2, M = S * Q, P = 2 * ((size_t)st.left + Q) - 1;
+    const size_t T1 = n_mel / 2 + 2, F1 = cfg.n_mels / 2 + 2;
+    return S * T1 * F1 * C * 4 * 4 + M * (d * 44 + (size_t)ffn_dim * 4) + P * d * 8 + (4 << 20);
+}
+
+int Model::stream_step(StreamState &st, const float *mel, int n_mel, int is_last, float *out) {
+    const int S = st.S, C = channels, d = d_model, F = ffn_dim, H = n_heads, dk = d_head;
+    if (n_mel <= 0) { set_error("stream_step: empty chunk"); return -1; }
+    const int lp = st.first ? 2 : 1, rp = is_last ? 1 : 0;
+    // ---- subsampling on the chunk (src/subsampling.c:320-370)
+    const int F0 = cfg.n_mels, F1 = F0 / 2 + 1, F2 = F1 / 2 + 1, F3 = F2 / 2 + 1;
+    auto stage_len = [&](int T) { return T + lp + rp >= 3 ? (T + lp + rp - 3) / 2 + 1 : 0; };
+    const int T1 = stage_len(n_mel), T2 = T1 > 0 ? stage_len(T1) : 0, T3 = T2 > 0 ? stage_len(T2) : 0;
+    if (T1 <= 0 || T2 <= 0 || T3 <= 0) { set_error("stream_step: a chunk of %d mel frames yields no encoder frame", n_mel); return -1; }
+    const int Q = T3, M = S * Q;
+    if (Q > st.q + 2 || conv_k - 1 + Q > STREAM_CONV_MAX || (st.left > 0 && Q > st.left)) { set_error("stream_step: chunk of %d encoder frames is too long", Q); return -1; }
+    const size_t mark = ws.off;
+    float *a0 = ws.get<float>((size_t)S * T1 * F1 * C);
+    H16 p1 = ws.planes((size_t)S * T2 * F2 * C);
+    float *a1 = ws.get<float>((size_t)S * T2 * F2 * C);
+    H16 p2 = ws.planes((size_t)S * T3 * F3 * C), flat = ws.planes((size_t)S * T3 * F3 * C);
+    float *x = ws.get<float>((size_t)M * d);
+    if (!a0 || !p1.lo || !a1 || !p2.lo || !flat.lo || !x) return -1;
+    const int TPB = 256;
+    {
+        const size_t n0 = (size_t)S * T1 * F1 * C, n1 = (size_t)S * T2 * F2 * C, n2 = (size_t)S * T3 * F3 * C;
+        ss_stream_stage0_kernel<<<(unsigned)cdiv(n0, TPB), TPB, 0, stream>>>(mel, st.ss_cache[0], conv_in_w, conv_in_b, a0, S, n_mel, F0, C, T1, F1, lp);
+        ss_stream_cache_kernel<<<(unsigned)cdiv((size_t)S * F0, TPB), TPB, 0, stream>>>(mel, st.ss_cache[0], S, n_mel, F0);
+        ss_stream_dw_kernel<<<(unsigned)cdiv(n1, TPB), TPB, 0, stream>>>(a0, st.ss_cache[1], dw_w[0], dw_b[0], p1, S, T1, F1, C, T2, F2, lp);
+        ss_stream_cache_kernel<<<(unsigned)cdiv((size_t)S * F1 * C, TPB), TPB, 0, stream>>>(a0, st.ss_cache[1], S, T1, F1 * C);
+        MB_CUDA(cudaGetLastError());
+        if (gemm(p1, C, pw[0], st_epi(OUT_F32, ACT_RELU, 1.f, pw[0].bias, a1, C), S * T2 * F2)) return -1;
+        ss_stream_dw_kernel<<<(unsigned)cdiv(n2, TPB), TPB, 0, stream>>>(a1, st.ss_cache[2], dw_w[1], dw_b[1], p2, S, T2, F2, C, T3, F3, lp);
+        ss_stream_cache_kernel<<<(unsigned)cdiv((size_t)S * F2 * C, TPB), TPB, 0, stream>>>(a1, st.ss_cache[2], S, T2, F2 * C);
+        MB_CUDA(cudaGetLastError());
+        if (gemm(p2, C, pw[1], st_epi(OUT_H16, ACT_RELU, 1.f, pw[1].bias, nullptr, 0, flat, C), S * T3 * F3)) return -1;
+        // flat is [S*Q, F3*C]: the linear's columns were permuted to this order at load. No xscale here, as in the reference's step.
+        if (gemm(flat, F3 * C, ss_lin, st_epi(OUT_F32, ACT_NONE, 1.f, ss_lin.bias, x, d), M)) return -1;
+        note_launch(6);
+    }
+    // ---- layers (src/encoder.c:826-866)
+    const int valid = st.valid, K = valid + Q, P = 2 * K - 1;
+    H16 hA = ws.planes((size_t)M * d), hC = ws.planes((size_t)M * d), hF = ws.planes((size_t)M * F);
+    float *qbuf = ws.get<float>((size_t)M * d), *h2 = ws.get<float>((size_t)M * 2 * d), *cbuf = ws.get<float>((size_t)M * d);
+    H16 kn = ws.planes((size_t)M * d, false), vn = ws.planes((size_t)M * d, false);
+    H16 pe = ws.planes((size_t)P * d), rk = ws.planes((size_t)P * d, false);
+    if (!hA.lo || !hC.lo || !hF.lo || !qbuf || !h2 || !cbuf || !kn.hi || !vn.hi || !pe.lo || !rk.hi) return -1;
+    if (pos_emb(pe, K, d, stream)) return -1;
+    note_launch();
+    const size_t attn_smem = ((size_t)K + 2 * dk + 32) * sizeof(float);
+    if (attn_smem > 200 * 1024) { set_error("stream_step: context too long for the attention kernel"); return -1; }
+    MB_CUDA(cudaFuncSetAttribute(stream_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem));
+    const H16 none{nullptr, nullptr};
+    const int leftn = st.left > 0 ? st.left : 1;
+    for (int li = 0; li < n_layers; li++) {
+        const EncLayer &L = layers[li];
+        __half *kc = st.k_cache + (size_t)li * S * leftn * d, *vc = st.v_cache + (size_t)li * S * leftn * d;
+        float *cc = st.conv_cache + (size_t)li * S * (conv_k - 1) * d;
+        if (layer_norm(x, L.ln_ff1_w, L.ln_ff1_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.ff1_w1, st_epi(OUT_H16, ACT_SILU, 1.f, L.ff1_w1.bias, nullptr, 0, hF, F), M)) return -1;
+        if (gemm(hF, F, L.ff1_w2, st_epi(OUT_RESID, ACT_NONE, 0.5f, L.ff1_w2.bias, x, d), M)) return -1;
+        if (layer_norm(x, L.ln_att_w, L.ln_att_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.q_w, st_epi(OUT_F32, ACT_NONE, 1.f, L.q_w.bias, qbuf, d), M)) return -1;
+        if (gemm(hA, d, L.k_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.k_w.bias, nullptr, 0, kn, d), M)) return -1;
+        if (gemm(hA, d, L.v_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.v_w.bias, nullptr, 0, vn, d), M)) return -1;
+        if (gemm(pe, d, L.relk, st_epi(OUT_H16, ACT_NONE, 1.f, nullptr, nullptr, 0, rk, d), P)) return -1;
+        stream_attn_kernel<<<dim3(H, S), 128, attn_smem, stream>>>(qbuf, kn.hi, vn.hi, kc, vc, rk.hi, L.bias_u, L.bias_v, hC, Q, valid,
+                                                                   st.start, leftn, d, dk);
+        if (st.left > 0)
+            stream_kv_update_kernel<<<(unsigned)cdiv((size_t)M * d, TPB), TPB, 0, stream>>>(kn.hi, vn.hi, kc, vc, S, Q, valid, st.start, st.left, d);
+        MB_CUDA(cudaGetLastError());
+        if (gemm(hC, d, L.o_w, st_epi(OUT_RESID, ACT_NONE, 1.f, L.o_w.bias, x, d), M)) return -1;
+        if (layer_norm(x, L.ln_conv_w, L.ln_conv_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.pw1_w, st_epi(OUT_F32, ACT_NONE, 1.f, L.pw1_w.bias, h2, 2 * d), M)) return -1;
+        stream_conv_kernel<STREAM_CONV_MAX><<<(unsigned)cdiv((size_t)S * d, 128), 128, 0, stream>>>(h2, L.dw_w, cc, cbuf, S, Q, d, conv_k);
+        MB_CUDA(cudaGetLastError());
+        if (layer_norm(cbuf, L.cnorm_w, L.cnorm_b, nullptr, hC, M, d, ACT_SILU, stream)) return -1;
+        if (gemm(hC, d, L.pw2_w, st_epi(OUT_RESID, ACT_NONE, 1.f, L.pw2_w.bias, x, d), M)) return -1;
+        if (layer_norm(x, L.ln_ff2_w, L.ln_ff2_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.ff2_w1, st_epi(OUT_H16, ACT_SILU, 1.f, L.ff2_w1.bias, nullptr, 0, hF, F), M)) return -1;
+        if (gemm(hF, F, L.ff2_w2, st_epi(OUT_RESID, ACT_NONE, 0.5f, L.ff2_w2.bias, x, d), M)) return -1;
+        if (layer_norm(x, L.ln_out_w, L.ln_out_b, x, none, M, d, ACT_NONE, stream)) return -1;
+        note_launch(9);
+    }
+    if (encoder_post(x, M, out)) return -1;
+    // cache bookkeeping of the host side (src/encoder.c:868 and the ring's start)
+    if (st.left > 0) {
+        const int total = valid + Q;
+        if (total > st.left) st.start = (st.start + (total - st.left)) % st.left;
+        st.valid = total < st.left ? total : st.left;
+    }
+    st.first = 0;
+    ws.off = mark;
+    return Q;
+}
+
+}  // namespace mb

@@ -1,0 +1,91 @@
+"""Cache-aware streaming encoder on the GPU (lock-step stream groups) against the compiled reference's
+streaming outputs (tests/golden/ref_rnnt_kq.npz: mynah_asr_enc_stream_step fed chunk by chunk), the numpy
+oracle, and the GPU's own offline limited-context path."""
+import os
+
+import numpy as np
+import pytest
+
+import cases
+from oracle import mynah_oracle as O, model_io
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+NAME = "rnnt_kq"          # Nemotron-style: causal convs, LayerNorm conv norm
+
+
+def rel(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)) / max(np.linalg.norm(b), 1e-30))
+
+
+@pytest.fixture(scope="module")
+def setup(gpu_pkg, synth):
+    cfg, tensors = cases.build(synth, NAME)
+    dm = cases.device_model(gpu_pkg, synth, cfg, tensors)
+    mels = []
+    for seed in (7, 21, 22):                       # stream 0 is the golden utterance
+        feats, valid = dm.log_mel(synth.synth_audio(2.0, seed=seed))
+        mels.append(feats[:valid])
+    yield cfg, tensors, dm, mels, np.load(os.path.join(GOLD, f"ref_{NAME}.npz"))
+    dm.close()
+
+
+def run_group(dm, mels, left, right):
+    g = dm.stream_open(len(mels), left, right)
+    outs, pos, T = [], 0, mels[0].shape[0]
+    while pos < T:
+        n = g.need()
+        chunk = np.stack([m[pos:pos + n] for m in mels])
+        outs.append(g.step(chunk, pos + n >= T))
+        pos += n
+    g.close()
+    return np.concatenate(outs, axis=1)            # [streams, T, d_out]
+
+
+@pytest.mark.parametrize("left,right", cases.STREAM_CONTEXTS)
+def test_streams_match_reference_and_oracle(setup, left, right):
+    cfg, tensors, dm, mels, g = setup
+    out = run_group(dm, mels, left, right)
+    ref = g[f"stream_{left}_{right}"]
+    assert out.shape[1:] == ref.shape
+    # tolerance of the path (north star): encoder output within relative L2 1e-3
+    assert rel(out[0], ref) < 1e-3
+    M = model_io.oracle_model(cfg, tensors)
+    for s in (1, 2):
+        assert rel(out[s], O.stream_encode(M, mels[s], left, right)) < 1e-3
+
+
+def test_stream_rows_do_not_depend_on_the_group(setup):
+    """A stream's output bits are the same alone, in a group of three, and at another position in it."""
+    cfg, tensors, dm, mels, g = setup
+    left, right = 8, 1
+    three = run_group(dm, mels, left, right)
+    assert np.array_equal(run_group(dm, mels[:1], left, right)[0], three[0])
+    assert np.array_equal(run_group(dm, [mels[2], mels[0]], left, right)[1], three[0])
+
+
+def test_streaming_equals_offline_tokens(setup):
+    """Streaming ~ the offline limited-context encoder on the same frames, and the greedy tokens are identical
+    (the reference's tests/test_streaming.c checks text equality)."""
+    cfg, tensors, dm, mels, g = setup
+    for left, right in ((6, 0), (8, 1)):
+        out = run_group(dm, mels, left, right)
+        for s in range(3):
+            off = dm.encoder_forward(mels[s], left=left, right=right)
+            assert off.shape == out[s].shape and rel(out[s], off) < 1e-3
+            ts, fs = dm.greedy_decode(out[s])
+            to, fo = dm.greedy_decode(off)
+            assert list(ts) == list(to) and list(fs) == list(fo)
+
+
+def test_stream_edges(setup, gpu_pkg):
+    cfg, tensors, dm, mels, g = setup
+    grp = dm.stream_open(2, 6, 0)
+    assert grp.need() == 1                         # first chunk: 1 + 8 * right mel frames
+    out = grp.step(np.stack([m[:1] for m in mels[:2]]))
+    assert out.shape == (2, 1, cfg.d_out) and grp.need() == 8
+    with pytest.raises(gpu_pkg.BackendError):      # wrong chunk size
+        grp.step(np.stack([m[1:4] for m in mels[:2]]))
+    grp.close()
+    with pytest.raises(gpu_pkg.BackendError):      # chunk longer than the left context
+        dm.stream_open(1, 2, 3)
