@@ -61,15 +61,17 @@ int layer_norm(const float *x, const float *w, const float *b, float *out_f32, H
 // -------------------------------------------------- GLU + depthwise conv (+BN+SiLU)
 // h2 [rows, 2d]: a = h2[:, :d], b = h2[:, d:], g = a * sigmoid(b). Depthwise conv of
 // width k along time with zero padding at the segment edges (causal: k-1 on the
-// left; symmetric: (k-1)/2 each side) — src/encoder.c:421-444. One thread per
-// channel, a time tile of TT rows plus the k-1 halo staged in shared memory so every
-// GLU value is computed once.
+// left; symmetric: (k-1)/2 each side) — src/encoder.c:421-444. A block covers 128 channels
+// x a time tile of TT rows; the tile plus its k-1 halo is staged in shared memory so every GLU
+// value is computed once. Four thread groups (threadIdx.y) share the staging and split the
+// output rows, which keeps 2048 threads resident per SM for this latency-bound pass.
 static constexpr int DW_TT = 64;
 static constexpr int DW_CH = 128;
+static constexpr int DW_TG = 4;
 static constexpr int DW_KMAX = 32;
 
 template <int KW>      // KW > 0: compile-time kernel width; 0: runtime width up to DW_KMAX
-__global__ void __launch_bounds__(DW_CH)
+__global__ void __launch_bounds__(DW_CH * DW_TG)
 glu_dw_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, const float *__restrict__ dw_b,
               const float *__restrict__ scale, const float *__restrict__ shift, float *__restrict__ out,
               __half *__restrict__ hi, __half *__restrict__ lo, const int *__restrict__ seg_off,
@@ -82,7 +84,7 @@ glu_dw_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, cons
     const int c = blockIdx.x * DW_CH + threadIdx.x;
     const bool cok = c < d;
     const int rows = DW_TT + k - 1;
-    for (int r = 0; r < rows; r++) {
+    for (int r = threadIdx.y; r < rows; r += DW_TG) {
         const int t = t0 - pad_left + r;
         float v = 0.0f;
         if (cok && t >= 0 && t < len) {
@@ -91,6 +93,7 @@ glu_dw_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, cons
         }
         g[r * DW_CH + threadIdx.x] = v;
     }
+    __syncthreads();
     if (!cok) return;
     constexpr int KU = KW > 0 ? KW : DW_KMAX;
     float w[KU];
@@ -99,7 +102,7 @@ glu_dw_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, cons
     const float bias = dw_b ? dw_b[c] : 0.0f;
     const float sc = scale ? scale[c] : 1.0f, sh = scale ? shift[c] : 0.0f;
     const int tend = len - t0 < DW_TT ? len - t0 : DW_TT;
-    for (int tt = 0; tt < tend; tt++) {
+    for (int tt = threadIdx.y * (DW_TT / DW_TG); tt < tend && tt < (threadIdx.y + 1) * (DW_TT / DW_TG); tt++) {
         float acc = bias;
 #pragma unroll
         for (int j = 0; j < KU; j++)
@@ -124,10 +127,10 @@ int glu_dwconv(const float *h2, const float *dw_w, const float *dw_b, const floa
     if (k > DW_KMAX) { set_error("glu_dwconv: kernel width %d > %d", k, DW_KMAX); return -1; }
     dim3 grid(cdiv(d, DW_CH), cdiv(max_len, DW_TT), batch);
     if (k == 9)
-        glu_dw_kernel<9><<<grid, DW_CH, 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
+        glu_dw_kernel<9><<<grid, dim3(DW_CH, DW_TG), 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
                                                  seg_len, d, k, pad_left);
     else
-        glu_dw_kernel<0><<<grid, DW_CH, 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
+        glu_dw_kernel<0><<<grid, dim3(DW_CH, DW_TG), 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
                                                  seg_len, d, k, pad_left);
     MB_CUDA(cudaGetLastError());
     return 0;
