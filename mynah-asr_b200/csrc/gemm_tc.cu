@@ -5,7 +5,7 @@
 // weights arrive already decoded to fp16 (hi, lo) planes resident in HBM, activations
 // as fp16 (hi, lo) planes written by the producing kernel's epilogue.
 //
-//   * TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) stages 128 x 64
+//   * TMA (cp.async.bulk.tensor.2d, 128-byte swizzle, every CTA loads its own tiles) stages 128 x 64
 //     A tiles and BN x 64 B tiles into a shared-memory ring guarded by mbarriers;
 //   * one elected thread issues tcgen05.mma (kind::f16, M=128, N=BN, K=16) into TMEM
 //     accumulators; with NTERMS=3 every k-step issues hi*hi into one accumulator and

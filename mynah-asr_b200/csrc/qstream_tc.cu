@@ -13,7 +13,7 @@
 //   * warps 0 and 5-7, one thread each: stream the stored bytes of every fourth stage (128 weight
 //     rows x 128 k: the quants and the four f16 block scales per row, laid out contiguously at
 //     load) from HBM into a shared-memory ring (4 to 16 stages deep) with bulk asynchronous copies
-//     (cp.async.bulk, no multicast) tracked by mbarriers — 70-140 KB in flight per SM to cover HBM
+//     (cp.async.bulk, one CTA each) tracked by mbarriers — 70-140 KB in flight per SM to cover HBM
 //     latency. One thread needs ~400 cycles per copy it starts, more than a stage may take;
 //   * warps 8-23, four groups of four: group g handles the stages g, g+4, ... A thread owns one
 //     weight row and moves its 32 integers into tensor memory with tcgen05.st, where they are the
