@@ -175,11 +175,13 @@ __device__ void lstm_phase(const GreedyDev &p, int l, int par, __half *xhi, __ha
     float *hnew = p.h[par ^ 1] + (size_t)l * B * H;
     float *cc = p.c + (size_t)l * B * H;
     const float *xin = l == 0 ? nullptr : p.h[par ^ 1] + (size_t)(l - 1) * B * H;
-    stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) { return ld4(l == 0 ? p.emb + (size_t)p.last_tok[b] * H + k : xin + (size_t)b * H + k); });
-    stage_x(xhi, xlo, xs, H, H, B, [&](int b, int k) { return ld4(hold + (size_t)b * H + k); });
-    __syncthreads();
     constexpr int NSL = 4;
     const int nrb = H / 4, chunks = K / 32, per = (chunks + NSL - 1) / NSL;
+    if (blockIdx.x * 8 < nrb * NSL) {        // a CTA without a row block to work on does not pull the activations either
+        stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) { return ld4(l == 0 ? p.emb + (size_t)p.last_tok[b] * H + k : xin + (size_t)b * H + k); });
+        stage_x(xhi, xlo, xs, H, H, B, [&](int b, int k) { return ld4(hold + (size_t)b * H + k); });
+    }
+    __syncthreads();
     const int g = lane >> 2, t = lane & 3;
     for (int base = blockIdx.x * 8; base < nrb * NSL; base += gridDim.x * 8) {
         const int task = base + wib, rb = task / NSL, sl = task % NSL;
@@ -240,10 +242,11 @@ __device__ void lstm_phase(const GreedyDev &p, int l, int par, __half *xhi, __ha
 __device__ void proj_phase(const GreedyDev &p, int par, bool all, __half *xhi, __half *xlo, float *red, int lane, int wib) {
     const int H = p.H, B = p.B, xs = 2 * H + XPAD;
     const float *hl = p.h[par] + (size_t)(p.L - 1) * B * H;
-    stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) { return ld4(hl + (size_t)b * H + k); });
-    __syncthreads();
     constexpr int NSL = 4;
     const int nrb = (H + 15) / 16, chunks = H / 32, per = (chunks + NSL - 1) / NSL;
+    if (blockIdx.x * 8 < nrb * NSL)
+        stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) { return ld4(hl + (size_t)b * H + k); });
+    __syncthreads();
     const int g = lane >> 2, t = lane & 3;
     for (int base = blockIdx.x * 8; base < nrb * NSL; base += gridDim.x * 8) {
         const int task = base + wib, rb = task / NSL, sl = task % NSL;
@@ -299,17 +302,30 @@ greedy_kernel(GreedyDev p) {
 
     constexpr int NSL = 2;
     const int nrb = (VL + 15) / 16, chunks = H / 32, per = (chunks + NSL - 1) / NSL;
+    __shared__ int srow[16];
     // optional phase timers (clock64 of CTA 0): head, sync, select+sync, lstm+syncs, proj+sync, steps, emit steps
     const bool timing = p.dbg != nullptr && blockIdx.x == 0 && threadIdx.x == 0;
     long long tq = timing ? clock64() : 0;
 #define PHASE_MARK(slot) do { if (timing) { const long long n_ = clock64(); p.dbg[slot] += n_ - tq; tq = n_; } } while (0)
     for (int step = 0; step < p.max_steps; step++) {
         // ---- head: joint = relu(enc[t] + g) -> logits -> first-argmax candidates per row block
+        // frame of every utterance first (one round trip), so that the row loads below depend on nothing
+        // they have to wait for: an utterance past its end reads its last frame and is zeroed afterwards
+        if (threadIdx.x < 16) {
+            int row = -1;
+            if (threadIdx.x < B) {
+                const int tb = p.t[threadIdx.x], len = p.enc_len[threadIdx.x];
+                if (tb < len) row = p.enc_off[threadIdx.x] + tb;
+            }
+            srow[threadIdx.x] = row;
+        }
+        __syncthreads();
+        if (blockIdx.x * 8 < nrb * NSL)
         stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) {
-            const int tb = p.t[b];
-            if (tb >= p.enc_len[b]) return make_float4(0.f, 0.f, 0.f, 0.f);
-            const float4 e = ld4(p.enc + (size_t)(p.enc_off[b] + tb) * H + k), gg = ld4(p.g + (size_t)b * H + k);
-            return make_float4(fmaxf(e.x + gg.x, 0.f), fmaxf(e.y + gg.y, 0.f), fmaxf(e.z + gg.z, 0.f), fmaxf(e.w + gg.w, 0.f));
+            const int row = srow[b];
+            const float4 e = ld4(p.enc + (size_t)(row < 0 ? 0 : row) * H + k), gg = ld4(p.g + (size_t)b * H + k);
+            const float z = row < 0 ? 0.f : 1.f;
+            return make_float4(z * fmaxf(e.x + gg.x, 0.f), z * fmaxf(e.y + gg.y, 0.f), z * fmaxf(e.z + gg.z, 0.f), z * fmaxf(e.w + gg.w, 0.f));
         });
         __syncthreads();
         PHASE_MARK(7);

@@ -44,3 +44,21 @@ def test_error_reporting_without_device(pkg):
     assert b"device" in L.mynah_b200_last_error()
     with pytest.raises(pkg.BackendError):
         pkg.QMat(pkg.F32, __import__("numpy").zeros((4, 64), "float32"), 4, 64)
+
+
+def test_header_is_plain_c_and_links_from_c(pkg, tmp_path):
+    """gcc -std=c11 -pedantic -Werror compiles the reference-side shim against the header and the
+    program runs against the built library."""
+    import shutil
+    import subprocess
+    if not shutil.which("gcc"):
+        pytest.skip("no gcc")
+    if not os.path.exists(pkg.LIB_PATH):
+        pytest.skip("library not built")
+    exe = str(tmp_path / "shim")
+    libdir = os.path.dirname(pkg.LIB_PATH)
+    subprocess.run(["gcc", "-std=c11", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(ROOT, "include"),
+                    os.path.join(ROOT, "tests", "c_abi_shim.c"), "-o", exe, "-L", libdir, "-l:" + os.path.basename(pkg.LIB_PATH),
+                    "-Wl,-rpath," + libdir], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0, (r.returncode, r.stdout, r.stderr)
