@@ -53,7 +53,14 @@ struct AedLayer {
 // oldest valid frame of every stream sits in slot (start + j) % left.
 struct StreamState {
     int S = 0, left = 0, right = 0, q = 1;
-    int first = 1, valid = 0, start = 0;
+    int first = 1, valid = 0;
+    int *d_start = nullptr;                             // ring offset of the oldest frame, kept on the device
+    // steady state (caches full, same buffers): one captured graph replays the whole step
+    cudaGraphExec_t exec = nullptr;
+    cudaGraph_t graph = nullptr;
+    const void *g_mel = nullptr, *g_out = nullptr, *g_base = nullptr;
+    size_t g_mark = 0;
+    int g_launches = 0, g_q = 0, steady_runs = 0;
     float *ss_cache[3] = {nullptr, nullptr, nullptr};   // last input frame of each subsampling stage: [S,F0], [S,F1,C], [S,F2,C]
     __half *k_cache = nullptr, *v_cache = nullptr;      // [L][S][left][d] fp16
     float *conv_cache = nullptr;                        // [L][S][k-1][d] GLU rows
@@ -141,6 +148,7 @@ struct Model {
     int stream_need(const StreamState &st) const { return st.valid == 0 && st.first ? 1 + 8 * st.right : 8 * (st.right + 1); }
     size_t stream_bytes(const StreamState &st, int n_mel) const;
     int stream_step(StreamState &st, const float *mel_dev, int n_mel, int is_last, float *out_dev);
+    int stream_step_eager(StreamState &st, const float *mel_dev, int n_mel, int is_last, float *out_dev);
     int log_mel(const float *audio_dev, size_t n, float *feats_dev, int T, int valid);
     static int sub_len(int n, bool causal) { return (n + (causal ? 3 : 2) - 3) / 2 + 1; }
     int enc_len(int t_mel) const { int t = t_mel; for (int i = 0; i < 3; i++) t = sub_len(t, causal); return t; }
@@ -174,5 +182,6 @@ struct GreedyDev {
 
 int greedy_launch(const GreedyDev &p, cudaStream_t st);
 void note_launch(int n = 1);
+long long launch_count(bool reset);
 
 }  // namespace mb
