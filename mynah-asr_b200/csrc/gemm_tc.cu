@@ -148,7 +148,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     } else if (warp >= 2) {
         // -------------------------------------------------------------- epilogue
         const int lg = warp & 3;                       // TMEM lane group this warp may read
-        const int half = (warp - 2) >> 2;              // which half of the tile's columns
+        const int half = (warp - 2) >> 2;              // even or odd 32-column chunks of the tile
         const int row = lg * 32 + lane;
         int lt = 0;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
@@ -163,7 +163,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
             const int m = m0 + row;
             if (num_k > 0) {
 #pragma unroll 1
-                for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); c++) {
+                for (int c = half; c < BN / 32; c += 2) {
                     float v[32];
                     tc_ld32(acc + (uint32_t)(c * 32), v);
                     if (NTERMS > 1) {
@@ -262,12 +262,26 @@ int gemm_tc(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, 
             int *status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % BK != 0) { set_error("gemm_tc: K=%d must be a positive multiple of %d", K, BK); return -1; }
+    // Narrower N tiles when the output has too few 128-wide tiles to occupy the SMs (small M: decoder
+    // positions, streaming chunks): more CTAs pull the operands. An output element sees the same k order
+    // and the same instruction sequence whatever the tile width, so its bits do not change with it.
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+    }
+    const int tm = cdiv(M, BM), want = (2 * sms) / 3;
+    const int bn = tm * cdiv(N, 128) >= want ? 128 : tm * cdiv(N, 64) >= want ? 64 : 32;
     if (nterms == 1) {
-        if (N >= 256) return launch<256, 1>(A, B, ep, M, N, K, status, stream);
-        return launch<128, 1>(A, B, ep, M, N, K, status, stream);
+        if (bn == 128 && N >= 256) return launch<256, 1>(A, B, ep, M, N, K, status, stream);
+        if (bn == 128) return launch<128, 1>(A, B, ep, M, N, K, status, stream);
+        if (bn == 64) return launch<64, 1>(A, B, ep, M, N, K, status, stream);
+        return launch<32, 1>(A, B, ep, M, N, K, status, stream);
     }
     if (!A.lo || !B.lo) { set_error("gemm_tc: 3-term mode needs lo planes"); return -1; }
-    return launch<128, 3>(A, B, ep, M, N, K, status, stream);
+    if (bn == 128) return launch<128, 3>(A, B, ep, M, N, K, status, stream);
+    if (bn == 64) return launch<64, 3>(A, B, ep, M, N, K, status, stream);
+    return launch<32, 3>(A, B, ep, M, N, K, status, stream);
 }
 
 }  // namespace mb
