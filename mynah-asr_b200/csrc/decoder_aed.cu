@@ -73,29 +73,50 @@ __global__ void aed_self_attn_kernel(const float *__restrict__ qkv, float *__res
 }
 
 // Cross-attention of one query per utterance over its T_b projected encoder frames
-// (src/decoder_aed.c:199-202). Grid (H, B). kv: planes [sum T, 2D] = (K | V) of this layer,
-// fp16 hi (+ lo * 2^-11 when present). q [B, D] f32 with bias.
-__global__ void aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ kv_hi, const __half *__restrict__ kv_lo,
-                                      const int *__restrict__ enc_off, const int *__restrict__ enc_len, int max_T, int D, int dk, H16 out) {
+// (src/decoder_aed.c:199-202). Grid (H, B), 256 threads. kv: planes [sum T, 2D] = (K | V) of this layer,
+// fp16 hi (+ lo * 2^-11 when present). q [B, D] f32 with bias. dk is a multiple of 4.
+// Scores: a warp takes four key rows at a time, a lane four consecutive elements of each (8-byte loads,
+// eight in flight per lane). Context: a thread owns two adjacent columns and every fourth key.
+__device__ __forceinline__ float4 ld_h4(const __half *hi, const __half *lo, size_t o) {
+    const uint2 a = *reinterpret_cast<const uint2 *>(hi + o);
+    const float2 a0 = __half22float2(*reinterpret_cast<const __half2 *>(&a.x)), a1 = __half22float2(*reinterpret_cast<const __half2 *>(&a.y));
+    float4 r = make_float4(a0.x, a0.y, a1.x, a1.y);
+    if (lo) {
+        const uint2 b = *reinterpret_cast<const uint2 *>(lo + o);
+        const float2 b0 = __half22float2(*reinterpret_cast<const __half2 *>(&b.x)), b1 = __half22float2(*reinterpret_cast<const __half2 *>(&b.y));
+        r.x = fmaf(b0.x, H16_LO_INV, r.x); r.y = fmaf(b0.y, H16_LO_INV, r.y); r.z = fmaf(b1.x, H16_LO_INV, r.z); r.w = fmaf(b1.y, H16_LO_INV, r.w);
+    }
+    return r;
+}
+__global__ void __launch_bounds__(256)
+aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ kv_hi, const __half *__restrict__ kv_lo,
+                      const int *__restrict__ enc_off, const int *__restrict__ enc_len, int max_T, int D, int dk, H16 out) {
     extern __shared__ float sm[];
-    float *sc = sm, *q = sm + max_T, *red = q + dk, *part = red + 32;     // part: [blockDim.x] partial outputs
+    float *sc = sm, *q = sm + ((max_T + 3) & ~3), *red = q + dk, *part = red + 32;     // part: [4][dk] partial outputs
     const int h = blockIdx.x, b = blockIdx.y;
-    const int T = enc_len[b], lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const size_t r0 = (size_t)enc_off[b];
+    const int T = enc_len[b], lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const size_t r0 = (size_t)enc_off[b], ld = 2 * (size_t)D;
     for (int i = threadIdx.x; i < dk; i += blockDim.x) q[i] = qm[(size_t)b * D + h * dk + i];
     __syncthreads();
     const float scale = 1.0f / sqrtf((float)dk);
-    // scores: one warp per key row, lanes over dk
-    for (int j = warp; j < T; j += nw) {
-        const size_t o = (r0 + j) * 2 * D + h * dk;
-        float s = 0.f;
-        for (int i = lane; i < dk; i += 32) {
-            float k = __half2float(kv_hi[o + i]);
-            if (kv_lo) k = fmaf(__half2float(kv_lo[o + i]), H16_LO_INV, k);
-            s = fmaf(q[i], k, s);
+    for (int j0 = warp * 4; j0 < T; j0 += 32) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i0 = lane * 4; i0 < dk; i0 += 128) {
+            float4 k[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int j = j0 + u < T ? j0 + u : T - 1;
+                k[u] = ld_h4(kv_hi, kv_lo, (r0 + j) * ld + h * dk + i0);
+            }
+            const float4 qq = *reinterpret_cast<const float4 *>(q + i0);
+#pragma unroll
+            for (int u = 0; u < 4; u++) s[u] = fmaf(qq.x, k[u].x, fmaf(qq.y, k[u].y, fmaf(qq.z, k[u].z, fmaf(qq.w, k[u].w, s[u]))));
         }
-        s = warp_sum(s);
-        if (lane == 0) sc[j] = s * scale;
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const float t = warp_sum(s[u]);
+            if (lane == 0 && j0 + u < T) sc[j0 + u] = t * scale;
+        }
     }
     __syncthreads();
     float m = -INFINITY;
@@ -105,27 +126,45 @@ __global__ void aed_cross_attn_kernel(const float *__restrict__ qm, const __half
     for (int j = threadIdx.x; j < T; j += blockDim.x) { const float e = expf(sc[j] - m); sc[j] = e; sum += e; }
     sum = block_reduce(sum, red, false);
     const float inv = 1.0f / sum;
-    // out[i] = sum_j pr[j] V[j][i]: thread (g, i) sums the keys j = g, g + G, ... of column i, then the G partials are added in order
-    const int G = blockDim.x / dk > 0 ? blockDim.x / dk : 1;
-    const int i = threadIdx.x % dk, g = threadIdx.x / dk;
-    float o = 0.f;
-    if (g < G) {
-        for (int j = g; j < T; j += G) {
-            const size_t a = (r0 + j) * 2 * D + D + h * dk + i;
-            float v = __half2float(kv_hi[a]);
-            if (kv_lo) v = fmaf(__half2float(kv_lo[a]), H16_LO_INV, v);
-            o = fmaf(sc[j] * inv, v, o);
+    // context: thread (g, c) sums the keys j = g, g + 4, ... of columns 2c, 2c+1; the four partials are added in order
+    const int nc = dk >> 1, g = threadIdx.x / nc, c = threadIdx.x % nc;
+    if (g < 4 && 4 * nc <= (int)blockDim.x) {
+        float o0 = 0.f, o1 = 0.f;
+        for (int j = g; j < T; j += 4) {
+            const size_t a = (r0 + j) * ld + D + h * dk + 2 * c;
+            float2 v = __half22float2(*reinterpret_cast<const __half2 *>(kv_hi + a));
+            if (kv_lo) {
+                const float2 l = __half22float2(*reinterpret_cast<const __half2 *>(kv_lo + a));
+                v.x = fmaf(l.x, H16_LO_INV, v.x); v.y = fmaf(l.y, H16_LO_INV, v.y);
+            }
+            const float p = sc[j] * inv;
+            o0 = fmaf(p, v.x, o0); o1 = fmaf(p, v.y, o1);
         }
-        part[threadIdx.x] = o;
+        part[g * dk + 2 * c] = o0; part[g * dk + 2 * c + 1] = o1;
+    } else if (4 * nc > (int)blockDim.x) {               // wide heads: one group only
+        for (int cc = threadIdx.x; cc < nc; cc += blockDim.x) {
+            float o0 = 0.f, o1 = 0.f;
+            for (int j = 0; j < T; j++) {
+                const size_t a = (r0 + j) * ld + D + h * dk + 2 * cc;
+                float2 v = __half22float2(*reinterpret_cast<const __half2 *>(kv_hi + a));
+                if (kv_lo) {
+                    const float2 l = __half22float2(*reinterpret_cast<const __half2 *>(kv_lo + a));
+                    v.x = fmaf(l.x, H16_LO_INV, v.x); v.y = fmaf(l.y, H16_LO_INV, v.y);
+                }
+                const float p = sc[j] * inv;
+                o0 = fmaf(p, v.x, o0); o1 = fmaf(p, v.y, o1);
+            }
+            part[2 * cc] = o0; part[2 * cc + 1] = o1;
+            for (int gg = 1; gg < 4; gg++) { part[gg * dk + 2 * cc] = 0.f; part[gg * dk + 2 * cc + 1] = 0.f; }
+        }
     }
     __syncthreads();
-    if (threadIdx.x < dk) {
-        float t = 0.f;
-        for (int gg = 0; gg < G; gg++) t += part[gg * dk + threadIdx.x];
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+        const float t = ((part[i] + part[dk + i]) + part[2 * dk + i]) + part[3 * dk + i];
         __half hi, lo;
         split_h16(t, hi, lo);
-        out.hi[(size_t)b * D + h * dk + threadIdx.x] = hi;
-        if (out.lo) out.lo[(size_t)b * D + h * dk + threadIdx.x] = lo;
+        out.hi[(size_t)b * D + h * dk + i] = hi;
+        if (out.lo) out.lo[(size_t)b * D + h * dk + i] = lo;
     }
 }
 
@@ -172,7 +211,7 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     tokens.assign(B, {});
     if (!has_aed) { set_error("model has no AED decoder"); return -1; }
     if (B == 0) return 0;
-    if (dk > 256) { set_error("aed_decode: head width %d above 256", dk); return -1; }
+    if (dk > 256 || dk % 4) { set_error("aed_decode: head width %d must be a multiple of 4 up to 256", dk); return -1; }
     if ((int)prompts.size() != B || (int)caps.size() != B) { set_error("aed_decode: one prompt and one cap per utterance"); return -1; }
     int cap = 0;
     for (int c : caps) cap = c > cap ? c : cap;
@@ -231,8 +270,8 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     MB_CUDA(cudaMemcpyAsync(d_prompts, hp.data(), hp.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
     MB_CUDA(cudaMemcpyAsync(d_off, ho.data(), ho.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
     const size_t self_smem = ((size_t)max_len + dk + 32) * sizeof(float);
-    const int cross_threads = dk >= 128 ? 256 : 128;
-    const size_t cross_smem = ((size_t)max_T + dk + 32 + cross_threads) * sizeof(float);
+    const int cross_threads = 256;
+    const size_t cross_smem = ((size_t)max_T + 4 + 5 * (size_t)dk + 32) * sizeof(float);
     if (self_smem > 200 * 1024 || cross_smem > 200 * 1024) { set_error("aed_decode: sequence too long for the attention kernels"); return -1; }
     MB_CUDA(cudaFuncSetAttribute(aed_self_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)self_smem));
     MB_CUDA(cudaFuncSetAttribute(aed_cross_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cross_smem));
