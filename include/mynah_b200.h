@@ -174,6 +174,12 @@ int mynah_b200_stream_need(const mynah_b200_stream_group *g);
  * per stream as in the reference's callers); n_mel = stream_need() except
  * for the last, shorter chunk (is_last = 1: causal right padding as offline). Returns q, -1 on error. */
 int mynah_b200_stream_step(mynah_b200_stream_group *g, const float *mel, int n_mel, int is_last, float *out);
+/* encoder step and greedy RNNT/TDT decoding of its q frames on the device, with the transducer state of every
+ * stream carried from chunk to chunk (mynah_asr_greedy_decode on a persistent mynah_asr_dec_state, as
+ * stream_flush_chunk calls it, src/mynah_asr.c:784-822): only the mel chunk and the new token ids cross PCIe.
+ * tokens[s] / frames[s] (absolute encoder frames; frames may be NULL) are malloc()'d per stream. Returns q. */
+int mynah_b200_stream_step_decode(mynah_b200_stream_group *g, const float *mel, int n_mel, int is_last, int **tokens,
+                                  int **frames, int *n_tokens);
 /* the same with device buffers on both sides (asynchronous on the model's stream) */
 int mynah_b200_stream_step_device(mynah_b200_stream_group *g, const float *mel_dev, int n_mel, int is_last,
                                   float *out_dev);

@@ -59,6 +59,16 @@ class StreamGroup:
             raise BackendError("stream_step: " + _err())
         return out.reshape(-1)[:self.n * q * self.model.d_out].reshape(self.n, q, self.model.d_out).copy()
 
+    def step_decode(self, mel, is_last=False):
+        """mel [n, n_mel, n_mels] -> per stream (tokens, absolute frames) emitted on this chunk"""
+        mel = np.ascontiguousarray(mel, np.float32)
+        assert mel.ndim == 3 and mel.shape[0] == self.n
+        tk, fr, nt = (C.c_void_p * self.n)(), (C.c_void_p * self.n)(), (C.c_int * self.n)()
+        q = lib().mynah_b200_stream_step_decode(self.h, _fp(mel), mel.shape[1], int(is_last), tk, fr, nt)
+        if q < 0:
+            raise BackendError("stream_step_decode: " + _err())
+        return [(_take_i32(tk[s], nt[s]), _take_i32(fr[s], nt[s])) for s in range(self.n)]
+
     def close(self):
         if self.h:
             lib().mynah_b200_stream_close(self.h)
@@ -110,6 +120,7 @@ def lib():
     L.mynah_b200_stream_need.argtypes = [vp]
     L.mynah_b200_stream_step.argtypes = [vp, c_fp, ci, ci, c_fp]
     L.mynah_b200_stream_step_device.argtypes = [vp, vp, ci, ci, vp]
+    L.mynah_b200_stream_step_decode.argtypes = [vp, c_fp, ci, ci, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), c_ip]
     L.mynah_b200_profile_bytes.argtypes = [vp, C.POINTER(C.c_double), ci]
     L.mynah_b200_decoder_clocks.argtypes = [vp, C.POINTER(C.c_longlong)]
     L.mynah_b200_model_new.restype = vp

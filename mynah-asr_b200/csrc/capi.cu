@@ -695,6 +695,36 @@ int mynah_b200_stream_step(mynah_b200_stream_group *g, const float *mel, int n_m
     return q;
 }
 
+int mynah_b200_stream_step_decode(mynah_b200_stream_group *g, const float *mel, int n_mel, int is_last, int **tokens,
+                                  int **frames, int *n_tokens) {
+    if (!g || !mel || n_mel <= 0 || !tokens || !n_tokens) { set_error("stream_step_decode: bad argument"); return -1; }
+    Model &m = g->model->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    if (!m.has_dec) { set_error("stream_step_decode: model has no transducer decoder"); return -1; }
+    if (n_mel != m.stream_need(g->st) && !is_last) { set_error("stream_step: %d mel frames given, %d needed", n_mel, m.stream_need(g->st)); return -1; }
+    const size_t S = g->st.S, nin = S * n_mel * m.cfg.n_mels, nout = S * (g->st.q + 2) * m.d_out;
+    const size_t nw = (size_t)(m.vocab + m.cfg.n_durations + 15) / 16, cap = (size_t)(g->st.q + 2) * m.cfg.max_symbols;
+    const size_t decb = S * (24 + 4 * nw + 2 * cap) * 4 + ((S + 15) / 16) * 1024 + (1 << 20);
+    if (m.ws.reserve(m.stream_bytes(g->st, n_mel) + (nin + nout) * 4 + decb + 4096)) return -1;
+    m.ws.reset();
+    float *md = m.ws.get<float>(nin), *od = m.ws.get<float>(nout);
+    if (!md || !od) return -1;
+    MB_CUDA(cudaMemcpyAsync(md, mel, nin * 4, cudaMemcpyHostToDevice, m.stream));
+    const int q = m.stream_step(g->st, md, n_mel, is_last, od);
+    if (q < 0) return -1;
+    std::vector<std::vector<int>> tk, fr;
+    if (m.stream_decode(g->st, od, q, tk, fr) || m.check_status("stream_step_decode")) return -1;
+    for (size_t s = 0; s < S; s++) {
+        n_tokens[s] = (int)tk[s].size();
+        tokens[s] = (int *)malloc((tk[s].size() ? tk[s].size() : 1) * sizeof(int));
+        if (frames) frames[s] = (int *)malloc((tk[s].size() ? tk[s].size() : 1) * sizeof(int));
+        if (!tokens[s] || (frames && !frames[s])) { set_error("out of host memory"); return -1; }
+        memcpy(tokens[s], tk[s].data(), tk[s].size() * sizeof(int));
+        if (frames) memcpy(frames[s], fr[s].data(), fr[s].size() * sizeof(int));
+    }
+    return q;
+}
+
 // ------------------------------------------------------------ resident pipeline
 mynah_b200_batch *mynah_b200_batch_upload(mynah_b200_model *h, const float *const *audio, const size_t *n_samples, int batch) {
     if (!h || !h->m.finalized || batch <= 0) { set_error("batch_upload: bad argument"); return nullptr; }

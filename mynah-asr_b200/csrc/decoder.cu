@@ -288,7 +288,7 @@ greedy_kernel(GreedyDev p) {
     float *red = reinterpret_cast<float *>(xlo + 16 * xs);          // [8 warps][32 lanes][8]
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
-    int par = 0;
+    int par = (!p.init_state && p.par_state) ? *p.par_state : 0;   // read before the first grid sync; written after the last
 
     if (p.init_state) {
         // SOS = blank on a zero state (src/decoder.c:151): run the prediction net once
@@ -440,7 +440,7 @@ greedy_kernel(GreedyDev p) {
         if (all_done) break;
     }
 #undef PHASE_MARK
-    if (blockIdx.x == 0 && threadIdx.x == 0) p.flags[4] = par;
+    if (blockIdx.x == 0 && threadIdx.x == 0) { p.flags[4] = par; if (p.par_state) *p.par_state = par; }
 }
 
 int greedy_launch(const GreedyDev &p, cudaStream_t st) {

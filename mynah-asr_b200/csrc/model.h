@@ -61,6 +61,12 @@ struct StreamState {
     const void *g_mel = nullptr, *g_out = nullptr, *g_base = nullptr;
     size_t g_mark = 0;
     int g_launches = 0, g_q = 0, steady_runs = 0;
+    // transducer state carried from chunk to chunk (mynah_asr_dec_state, src/decoder.h:31-38), one block per
+    // DEC_MAX_B streams: h[2][L][B][H], c[L][B][H], g[B][H] floats; last_tok[B] and the h parity as ints
+    float *dec_f = nullptr;
+    int *dec_i = nullptr;
+    int dec_started = 0;
+    long long t_abs = 0;                                // encoder frames decoded so far (same for every stream)
     float *ss_cache[3] = {nullptr, nullptr, nullptr};   // last input frame of each subsampling stage: [S,F0], [S,F1,C], [S,F2,C]
     __half *k_cache = nullptr, *v_cache = nullptr;      // [L][S][left][d] fp16
     float *conv_cache = nullptr;                        // [L][S][k-1][d] GLU rows
@@ -149,6 +155,10 @@ struct Model {
     size_t stream_bytes(const StreamState &st, int n_mel) const;
     int stream_step(StreamState &st, const float *mel_dev, int n_mel, int is_last, float *out_dev);
     int stream_step_eager(StreamState &st, const float *mel_dev, int n_mel, int is_last, float *out_dev);
+    // greedy RNNT/TDT over the q new frames of every stream with the state carried from the previous chunk
+    // (mynah_asr_greedy_decode with a persistent mynah_asr_dec_state); frames are absolute
+    int stream_decode(StreamState &st, const float *enc_dev, int q, std::vector<std::vector<int>> &tokens,
+                      std::vector<std::vector<int>> &frames);
     int log_mel(const float *audio_dev, size_t n, float *feats_dev, int T, int valid);
     static int sub_len(int n, bool causal) { return (n + (causal ? 3 : 2) - 3) / 2 + 1; }
     int enc_len(int t_mel) const { int t = t_mel; for (int i = 0; i < 3; i++) t = sub_len(t, causal); return t; }
@@ -177,6 +187,7 @@ struct GreedyDev {
     int *cand_i;
     int *flags;                  // [2][2] {any_emit, all_done} by step parity, [4] final h parity
     int max_steps, init_state;
+    int *par_state;              // optional: parity of h carried between launches on the same state
     long long *dbg;              // optional [8] phase timers (clock64 ticks of CTA 0), null = off
 };
 

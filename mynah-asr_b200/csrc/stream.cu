@@ -368,4 +368,86 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
     return Q;
 }
 
+// ---- per-chunk transducer decoding with carried state (src/decoder.c:112-265 called chunk by chunk, as
+// stream_flush_chunk does, src/mynah_asr.c:784-822). Streams are decoded DEC_MAX_B at a time by the lock-step
+// greedy kernel; every group keeps its LSTM state, pred-net output and last token on the device.
+int Model::stream_decode(StreamState &st, const float *enc_dev, int q, std::vector<std::vector<int>> &tokens,
+                         std::vector<std::vector<int>> &frames) {
+    const int S = st.S, H = pred_hidden, L = pred_layers;
+    tokens.assign(S, {}); frames.assign(S, {});
+    if (!has_dec) { set_error("stream_decode: model has no transducer decoder"); return -1; }
+    if (q <= 0) return 0;
+    const int ngroups = cdiv(S, DEC_MAX_B);
+    const size_t fblock = (size_t)(3 * L + 1) * DEC_MAX_B * H, iblock = DEC_MAX_B + 8;
+    if (!st.dec_f) {
+        st.dec_f = (float *)dev_alloc(ngroups * fblock * sizeof(float));
+        st.dec_i = (int *)dev_alloc(ngroups * iblock * sizeof(int));
+        if (!st.dec_f || !st.dec_i) return -1;
+        st.owned.push_back(st.dec_f); st.owned.push_back(st.dec_i);
+        MB_CUDA(cudaMemsetAsync(st.dec_f, 0, ngroups * fblock * sizeof(float), stream));
+        MB_CUDA(cudaMemsetAsync(st.dec_i, 0, ngroups * iblock * sizeof(int), stream));
+    }
+    const int nw = (vocab + cfg.n_durations + 15) / 16, cap = q * cfg.max_symbols;
+    const size_t mark = ws.off;
+    struct Out { int *n_out, *tokens, *frames; int B; };
+    std::vector<Out> outs(ngroups);
+    std::vector<int> hm(2 * (size_t)S);                      // per group: B frame offsets, then B lengths
+    for (int gi = 0, o = 0; gi < ngroups; gi++) {
+        const int g0 = gi * DEC_MAX_B, B = S - g0 < DEC_MAX_B ? S - g0 : DEC_MAX_B;
+        for (int b = 0; b < B; b++) { hm[o + b] = (g0 + b) * q; hm[o + B + b] = q; }
+        o += 2 * B;
+    }
+    for (int gi = 0; gi < ngroups; gi++) {
+        const int g0 = gi * DEC_MAX_B, B = S - g0 < DEC_MAX_B ? S - g0 : DEC_MAX_B;
+        const size_t nstate = (size_t)L * B * H;
+        float *fs = st.dec_f + gi * fblock;
+        int *is = st.dec_i + gi * iblock;
+        float *cand = ws.get<float>(2 * (size_t)B * nw);
+        int *iz = ws.get<int>(8 * (size_t)B + 2 * (size_t)B * nw + 2 * (size_t)B * cap + 16);
+        if (!cand || !iz) return -1;
+        MB_CUDA(cudaMemsetAsync(iz, 0, (8 * (size_t)B + 16) * sizeof(int), stream));
+        GreedyDev p;
+        memset(&p, 0, sizeof(p));
+        p.emb = emb; p.head_b = head_b; p.proj_b = proj_b;
+        p.head_hi = head.hi; p.head_lo = head.lo; p.proj_hi = dec_proj.hi; p.proj_lo = dec_proj.lo;
+        for (int l = 0; l < L; l++) { p.wcat_hi[l] = wcat[l].hi; p.wcat_lo[l] = wcat[l].lo; p.b_ih[l] = b_ih[l]; p.b_hh[l] = b_hh[l]; }
+        p.V = vocab; p.ND = cfg.n_durations; p.H = H; p.L = L; p.blank = cfg.blank_id; p.max_symbols = cfg.max_symbols;
+        for (int i = 0; i < cfg.n_durations; i++) p.durations[i] = cfg.durations[i];
+        p.B = B; p.enc = enc_dev;
+        p.h[0] = fs; p.h[1] = fs + nstate; p.c = fs + 2 * nstate; p.g = fs + 3 * nstate;
+        p.cand_v = cand;
+        int *qi = iz;
+        p.flags = qi; qi += 16;
+        p.t = qi; qi += B; p.emitted_here = qi; qi += B; p.n_out = qi; qi += B; p.emit = qi; qi += B;
+        int *d_off = qi; qi += B; int *d_len = qi; qi += B; qi += 2 * B;
+        p.cand_i = qi; qi += 2 * (size_t)B * nw;
+        p.tokens = qi; qi += (size_t)B * cap; p.frames = qi;
+        p.last_tok = is; p.par_state = is + DEC_MAX_B;
+        p.cap = cap; p.enc_off = d_off; p.enc_len = d_len;
+        p.max_steps = q * (cfg.max_symbols + 1) + 8; p.init_state = st.dec_started ? 0 : 1;
+        MB_CUDA(cudaMemcpyAsync(d_off, hm.data() + 2 * (size_t)g0, 2 * B * sizeof(int), cudaMemcpyHostToDevice, stream));
+        if (greedy_launch(p, stream)) return -1;
+        note_launch();
+        outs[gi] = Out{p.n_out, p.tokens, p.frames, B};
+    }
+    for (int gi = 0; gi < ngroups; gi++) {
+        const Out &o = outs[gi];
+        std::vector<int> hn(o.B), ht((size_t)o.B * cap), hf((size_t)o.B * cap);
+        MB_CUDA(cudaMemcpyAsync(hn.data(), o.n_out, o.B * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        MB_CUDA(cudaMemcpyAsync(ht.data(), o.tokens, ht.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        MB_CUDA(cudaMemcpyAsync(hf.data(), o.frames, hf.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        MB_CUDA(cudaStreamSynchronize(stream));
+        for (int b = 0; b < o.B; b++) {
+            const int s = gi * DEC_MAX_B + b;
+            tokens[s].assign(ht.begin() + (size_t)b * cap, ht.begin() + (size_t)b * cap + hn[b]);
+            frames[s].resize(hn[b]);
+            for (int i = 0; i < hn[b]; i++) frames[s][i] = (int)(st.t_abs + hf[(size_t)b * cap + i]);
+        }
+    }
+    st.dec_started = 1;
+    st.t_abs += q;
+    ws.off = mark;
+    return 0;
+}
+
 }  // namespace mb

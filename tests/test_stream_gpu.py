@@ -78,6 +78,30 @@ def test_streaming_equals_offline_tokens(setup):
             assert list(ts) == list(to) and list(fs) == list(fo)
 
 
+def test_chunkwise_decode_with_carried_state(setup):
+    """Greedy RNNT chunk by chunk with the transducer state kept on the device == greedy decode of the whole
+    streamed encoder output at once (tokens and absolute frames), for streams in different decode groups."""
+    cfg, tensors, dm, mels, g = setup
+    left, right = 8, 1
+    many = [mels[i % 3] for i in range(19)]                 # 19 streams: two lock-step decode groups
+    enc = run_group(dm, many, left, right)
+    grp = dm.stream_open(len(many), left, right)
+    toks = [[] for _ in many]
+    frs = [[] for _ in many]
+    pos, T = 0, many[0].shape[0]
+    while pos < T:
+        n = grp.need()
+        res = grp.step_decode(np.stack([m[pos:pos + n] for m in many]), pos + n >= T)
+        for s, (t, f) in enumerate(res):
+            toks[s] += list(t); frs[s] += list(f)
+        pos += n
+    grp.close()
+    for s in range(len(many)):
+        t, f = dm.greedy_decode(enc[s])
+        assert toks[s] == list(t) and frs[s] == list(f), s
+    assert any(len(t) > 3 for t in toks)
+
+
 def test_stream_edges(setup, gpu_pkg):
     cfg, tensors, dm, mels, g = setup
     grp = dm.stream_open(2, 6, 0)
