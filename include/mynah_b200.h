@@ -174,6 +174,13 @@ int mynah_b200_stream_need(const mynah_b200_stream_group *g);
  * per stream as in the reference's callers); n_mel = stream_need() except
  * for the last, shorter chunk (is_last = 1: causal right padding as offline). Returns q, -1 on error. */
 int mynah_b200_stream_step(mynah_b200_stream_group *g, const float *mel, int n_mel, int is_last, float *out);
+/* replaces mynah_asr_mel_stream_feed / _finish (src/features.h:54-62) for the streams of a group: appends n
+ * samples per stream (audio [n_streams, n], float in [-1, 1]) and writes the log-mel frames that became ready
+ * to out [n_streams, frames, n_mels] (at most cap_frames; finish = 1 also emits the remaining valid frames,
+ * zero-padded to the right). No per-feature normalisation, as in the reference's streaming front end; the
+ * frames are bit-identical to mynah_b200_log_mel on the whole signal. Returns the frame count, -1 on error. */
+int mynah_b200_stream_mel_feed(mynah_b200_stream_group *g, const float *audio, int n, int finish, float *out,
+                               int cap_frames);
 /* encoder step and greedy RNNT/TDT decoding of its q frames on the device, with the transducer state of every
  * stream carried from chunk to chunk (mynah_asr_greedy_decode on a persistent mynah_asr_dec_state, as
  * stream_flush_chunk calls it, src/mynah_asr.c:784-822): only the mel chunk and the new token ids cross PCIe.

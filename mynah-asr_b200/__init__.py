@@ -59,6 +59,16 @@ class StreamGroup:
             raise BackendError("stream_step: " + _err())
         return out.reshape(-1)[:self.n * q * self.model.d_out].reshape(self.n, q, self.model.d_out).copy()
 
+    def mel_feed(self, audio, finish=False, cap_frames=4096):
+        """audio [n, samples] -> the log-mel frames that became ready, [n, frames, n_mels]"""
+        audio = np.ascontiguousarray(audio, np.float32)
+        assert audio.ndim == 2 and audio.shape[0] == self.n
+        out = np.empty((self.n * cap_frames * self.model.n_mels,), np.float32)
+        k = lib().mynah_b200_stream_mel_feed(self.h, _fp(audio), audio.shape[1], int(finish), _fp(out), cap_frames)
+        if k < 0:
+            raise BackendError("stream_mel_feed: " + _err())
+        return out[:self.n * k * self.model.n_mels].reshape(self.n, k, self.model.n_mels).copy()
+
     def step_decode(self, mel, is_last=False):
         """mel [n, n_mel, n_mels] -> per stream (tokens, absolute frames) emitted on this chunk"""
         mel = np.ascontiguousarray(mel, np.float32)
@@ -120,6 +130,7 @@ def lib():
     L.mynah_b200_stream_need.argtypes = [vp]
     L.mynah_b200_stream_step.argtypes = [vp, c_fp, ci, ci, c_fp]
     L.mynah_b200_stream_step_device.argtypes = [vp, vp, ci, ci, vp]
+    L.mynah_b200_stream_mel_feed.argtypes = [vp, c_fp, ci, ci, c_fp, ci]
     L.mynah_b200_stream_step_decode.argtypes = [vp, c_fp, ci, ci, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), c_ip]
     L.mynah_b200_profile_bytes.argtypes = [vp, C.POINTER(C.c_double), ci]
     L.mynah_b200_decoder_clocks.argtypes = [vp, C.POINTER(C.c_longlong)]

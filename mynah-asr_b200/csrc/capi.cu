@@ -695,6 +695,15 @@ int mynah_b200_stream_step(mynah_b200_stream_group *g, const float *mel, int n_m
     return q;
 }
 
+int mynah_b200_stream_mel_feed(mynah_b200_stream_group *g, const float *audio, int n, int finish, float *out, int cap_frames) {
+    if (!g || !out) { set_error("stream_mel_feed: bad argument"); return -1; }
+    Model &m = g->model->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    if (m.ws.reserve((size_t)g->st.S * (size_t)(cap_frames > 0 ? cap_frames : 1) * m.cfg.n_mels * 4 + (1 << 20))) return -1;
+    m.ws.reset();
+    return m.stream_mel_feed(g->st, audio, n, finish, out, cap_frames);
+}
+
 int mynah_b200_stream_step_decode(mynah_b200_stream_group *g, const float *mel, int n_mel, int is_last, int **tokens,
                                   int **frames, int *n_tokens) {
     if (!g || !mel || n_mel <= 0 || !tokens || !n_tokens) { set_error("stream_step_decode: bad argument"); return -1; }

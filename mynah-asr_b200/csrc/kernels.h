@@ -69,6 +69,10 @@ int log_mel_device(const MelCfg &c, const float *audio, size_t n_samples, const 
                    const int *mel_hi, const double *win, const double *twiddle, float *feats, int T, int valid,
                    cudaStream_t st);
 
+int log_mel_stream_device(const MelCfg &c, const float *tail, long long base, long long total, long long sig_stride, int n_sig,
+                          const float *mel_fb, const int *mel_lo, const int *mel_hi, const double *win, const double *twiddle,
+                          float *feats, long long feat_stride, int t0, int n_frames, cudaStream_t st);
+
 // ---- qgemv.cu : out[T,n] = x[T,k] W^T for T <= 16 straight from the stored blocks
 struct QWeight;
 int qgemv(const QWeight &w, const float *x, int ldx, float *out, int ldo, const float *bias, int T, cudaStream_t st);

@@ -15,13 +15,18 @@ namespace mb {
 
 static constexpr int MEL_MAX_FFT = 1024;
 
+// blockIdx.y selects one of several signals (streams of a lock-step group): signal y starts at
+// audio + y * sig_stride and its frames go to feats + y * feat_stride. `base` is the absolute sample index
+// of audio[0] (streaming keeps only the tail of the signal; 0 offline), t0 the first frame of this launch.
 __global__ void __launch_bounds__(128)
-mel_frame_kernel(const float *__restrict__ audio, long long S, const double *__restrict__ win,
+mel_frame_kernel(const float *__restrict__ audio_all, long long S, const double *__restrict__ win,
                  const double *__restrict__ tw, const float *__restrict__ fb, const int *__restrict__ mlo,
-                 const int *__restrict__ mhi, float *__restrict__ feats, int n_fft, int log2n, int hop, int n_mels,
-                 double preemph, double guard) {
+                 const int *__restrict__ mhi, float *__restrict__ feats_all, int n_fft, int log2n, int hop, int n_mels,
+                 double preemph, double guard, long long base, int t0, long long sig_stride, long long feat_stride) {
     __shared__ double re[MEL_MAX_FFT], im[MEL_MAX_FFT];
-    const int t = blockIdx.x;
+    const float *audio = audio_all + blockIdx.y * sig_stride - base;      // audio[s] is sample s of the signal
+    float *feats = feats_all + blockIdx.y * feat_stride - (long long)t0 * n_mels;
+    const int t = t0 + blockIdx.x;
     const long long start = (long long)t * hop - n_fft / 2;      // index into the unpadded signal
     for (int i = threadIdx.x; i < n_fft; i += blockDim.x) {
         const long long s = start + i;
@@ -87,12 +92,28 @@ int log_mel_device(const MelCfg &c, const float *audio, size_t n_samples, const 
     int log2n = 0;
     while ((1 << log2n) < c.n_fft) log2n++;
     mel_frame_kernel<<<valid, 128, 0, st>>>(audio, (long long)n_samples, win, twiddle, mel_fb, mel_lo, mel_hi, feats,
-                                            c.n_fft, log2n, c.hop, c.n_mels, c.preemph, c.guard);
+                                            c.n_fft, log2n, c.hop, c.n_mels, c.preemph, c.guard, 0, 0, 0, 0);
     MB_CUDA(cudaGetLastError());
     if (c.normalize && valid > 1) {
         mel_norm_kernel<<<c.n_mels, 256, 0, st>>>(feats, valid, c.n_mels);
         MB_CUDA(cudaGetLastError());
     }
+    return 0;
+}
+
+// Frames [t0, t0 + n_frames) of `n_sig` signals whose samples [base, total) sit at tail + y * sig_stride
+// (the streaming counterpart: mel_one_frame of src/features.c:170-189, no normalisation). The caller
+// keeps sample base - 1 .. in the buffer when base > 0 (the pre-emphasis reads one sample back).
+int log_mel_stream_device(const MelCfg &c, const float *tail, long long base, long long total, long long sig_stride, int n_sig,
+                          const float *mel_fb, const int *mel_lo, const int *mel_hi, const double *win, const double *twiddle,
+                          float *feats, long long feat_stride, int t0, int n_frames, cudaStream_t st) {
+    if (c.n_fft > MEL_MAX_FFT || (c.n_fft & (c.n_fft - 1))) { set_error("log_mel: n_fft %d unsupported", c.n_fft); return -1; }
+    if (n_frames <= 0 || n_sig <= 0) return 0;
+    int log2n = 0;
+    while ((1 << log2n) < c.n_fft) log2n++;
+    mel_frame_kernel<<<dim3(n_frames, n_sig), 128, 0, st>>>(tail, total, win, twiddle, mel_fb, mel_lo, mel_hi, feats, c.n_fft, log2n,
+                                                            c.hop, c.n_mels, c.preemph, c.guard, base, t0, sig_stride, feat_stride);
+    MB_CUDA(cudaGetLastError());
     return 0;
 }
 

@@ -67,6 +67,11 @@ struct StreamState {
     int *dec_i = nullptr;
     int dec_started = 0;
     long long t_abs = 0;                                // encoder frames decoded so far (same for every stream)
+    // incremental log-mel (mynah_asr_mel_stream, src/features.h:40-52): the tail of every stream's signal,
+    // [S][MEL_CAP] floats in one of two buffers, samples [mel_base, mel_total) of the signal
+    float *mel_buf[2] = {nullptr, nullptr};
+    int mel_cur = 0;
+    long long mel_base = 0, mel_total = 0, mel_next = 0;
     float *ss_cache[3] = {nullptr, nullptr, nullptr};   // last input frame of each subsampling stage: [S,F0], [S,F1,C], [S,F2,C]
     __half *k_cache = nullptr, *v_cache = nullptr;      // [L][S][left][d] fp16
     float *conv_cache = nullptr;                        // [L][S][k-1][d] GLU rows
@@ -157,6 +162,9 @@ struct Model {
     int stream_step_eager(StreamState &st, const float *mel_dev, int n_mel, int is_last, float *out_dev);
     // greedy RNNT/TDT over the q new frames of every stream with the state carried from the previous chunk
     // (mynah_asr_greedy_decode with a persistent mynah_asr_dec_state); frames are absolute
+    // appends n samples per stream (host, [S][n]) and computes the mel frames that became ready (all of the
+    // remaining valid ones with finish): out_host [S][frames][n_mels]; returns the frame count
+    int stream_mel_feed(StreamState &st, const float *audio_host, int n, int finish, float *out_host, int cap_frames);
     int stream_decode(StreamState &st, const float *enc_dev, int q, std::vector<std::vector<int>> &tokens,
                       std::vector<std::vector<int>> &frames);
     int log_mel(const float *audio_dev, size_t n, float *feats_dev, int T, int valid);

@@ -368,6 +368,57 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
     return Q;
 }
 
+// ---- incremental log-mel for the streams of a group (mynah_asr_mel_stream_feed / _finish, src/features.c:229-272):
+// frame t is ready once the signal covers t*hop + n_fft/2; finish emits the remaining valid frames with
+// zeros to the right. Same frame kernel as the offline front end, so ready frames are bit-identical to it.
+static constexpr int MEL_CAP = 1 << 16;                  // samples of signal tail kept per stream
+
+int Model::stream_mel_feed(StreamState &st, const float *audio, int n, int finish, float *out, int cap_frames) {
+    if (!has_mel) { set_error("stream_mel_feed: mel filterbank not set"); return -1; }
+    if (n < 0 || (n > 0 && !audio) || cap_frames < 0) { set_error("stream_mel_feed: bad argument"); return -1; }
+    const int S = st.S, hop = cfg.hop_length, nf = cfg.n_fft, nm = cfg.n_mels;
+    if (!st.mel_buf[0]) {
+        for (int i = 0; i < 2; i++) {
+            st.mel_buf[i] = (float *)dev_alloc((size_t)S * MEL_CAP * sizeof(float));
+            if (!st.mel_buf[i]) return -1;
+            st.owned.push_back(st.mel_buf[i]);
+        }
+    }
+    // drop what no later frame needs (one sample more than the window: the pre-emphasis reads s - 1)
+    const long long min_keep = st.mel_next * hop - nf / 2 - 1;
+    if (min_keep > st.mel_base) {
+        const long long tail = st.mel_total - min_keep;
+        if (tail > 0)
+            MB_CUDA(cudaMemcpy2DAsync(st.mel_buf[st.mel_cur ^ 1], (size_t)MEL_CAP * 4, st.mel_buf[st.mel_cur] + (min_keep - st.mel_base),
+                                      (size_t)MEL_CAP * 4, (size_t)tail * 4, S, cudaMemcpyDeviceToDevice, stream));
+        st.mel_cur ^= 1;
+        st.mel_base = min_keep;
+    }
+    if (st.mel_total - st.mel_base + n > MEL_CAP) { set_error("stream_mel_feed: %d samples at once exceed the %d-sample window", n, MEL_CAP); return -1; }
+    if (n > 0) {
+        MB_CUDA(cudaMemcpy2DAsync(st.mel_buf[st.mel_cur] + (st.mel_total - st.mel_base), (size_t)MEL_CAP * 4, audio, (size_t)n * 4,
+                                  (size_t)n * 4, S, cudaMemcpyHostToDevice, stream));
+        st.mel_total += n;
+    }
+    long long t_end = st.mel_total >= nf / 2 ? (st.mel_total - nf / 2) / hop + 1 : 0;
+    if (finish) { const long long valid = st.mel_total / hop; if (valid > t_end) t_end = valid; else if (valid < t_end) t_end = valid > st.mel_next ? valid : st.mel_next; }
+    long long n_new = t_end - st.mel_next;
+    if (n_new > cap_frames) n_new = cap_frames;
+    if (n_new <= 0) { MB_CUDA(cudaStreamSynchronize(stream)); return 0; }
+    const size_t mark = ws.off;
+    float *fd = ws.get<float>((size_t)S * n_new * nm);
+    if (!fd) return -1;
+    MelCfg c{nm, nf, cfg.win_length, hop, cfg.preemphasis, cfg.log_zero_guard, 0};
+    if (log_mel_stream_device(c, st.mel_buf[st.mel_cur], st.mel_base, st.mel_total, MEL_CAP, S, mel_fb, mel_lo, mel_hi, mel_win, mel_tw, fd,
+                              (long long)n_new * nm, (int)st.mel_next, (int)n_new, stream)) return -1;
+    note_launch();
+    MB_CUDA(cudaMemcpyAsync(out, fd, (size_t)S * n_new * nm * sizeof(float), cudaMemcpyDeviceToHost, stream));
+    MB_CUDA(cudaStreamSynchronize(stream));
+    st.mel_next += n_new;
+    ws.off = mark;
+    return (int)n_new;
+}
+
 // ---- per-chunk transducer decoding with carried state (src/decoder.c:112-265 called chunk by chunk, as
 // stream_flush_chunk does, src/mynah_asr.c:784-822). Streams are decoded DEC_MAX_B at a time by the lock-step
 // greedy kernel; every group keeps its LSTM state, pred-net output and last token on the device.

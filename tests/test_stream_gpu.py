@@ -102,6 +102,36 @@ def test_chunkwise_decode_with_carried_state(setup):
     assert any(len(t) > 3 for t in toks)
 
 
+def test_incremental_mel_equals_offline_and_feeds_the_stream(setup, synth):
+    """Audio fed in 600-sample pieces (as the reference's tests/test_streaming.c does): the incremental
+    log-mel frames are bit-identical to the offline front end, and chunks cut from them as they arrive drive
+    the streaming encoder to the same output as chunks cut from the offline frames."""
+    cfg, tensors, dm, mels, g = setup
+    left, right = 6, 0
+    audios = np.stack([synth.synth_audio(2.0, seed=s) for s in (7, 21)])
+    grp = dm.stream_open(2, left, right)
+    got, pend, outs = [], np.zeros((2, 0, cfg.n_mels), np.float32), []
+    total, valid = audios.shape[1], audios.shape[1] // 160
+    for pos in range(0, total, 600):
+        piece = audios[:, pos:pos + 600]
+        fr = grp.mel_feed(piece, finish=pos + 600 >= total)
+        got.append(fr)
+        pend = np.concatenate([pend, fr], axis=1)
+        done = sum(f.shape[1] for f in got)
+        while pend.shape[1] >= grp.need() or (done >= valid and pend.shape[1] > 0):
+            n = min(grp.need(), pend.shape[1])
+            last = done >= valid and pend.shape[1] <= n
+            outs.append(grp.step(pend[:, :n], last))
+            pend = pend[:, n:]
+    grp.close()
+    feats = np.concatenate(got, axis=1)
+    assert feats.shape[1] == valid
+    for s in range(2):
+        assert np.array_equal(feats[s], mels[s][:valid])          # mels: offline log-mel of seeds 7, 21
+    ref = run_group(dm, mels[:2], left, right)
+    assert np.array_equal(np.concatenate(outs, axis=1), ref)
+
+
 def test_stream_edges(setup, gpu_pkg):
     cfg, tensors, dm, mels, g = setup
     grp = dm.stream_open(2, 6, 0)
