@@ -302,6 +302,11 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
     if (const HostTensor *e = find(m, "decoder.embedding.weight")) {
         m.vocab = (int)e->shape[0]; m.pred_hidden = (int)e->shape[1];
         m.emb = f32dev(m, "decoder.embedding.weight", true, &err);
+        if (m.emb) {                       // the same table as fp16 (hi, lo) planes: LSTM inputs are copied, not converted
+            const size_t ne = (size_t)m.vocab * m.pred_hidden;
+            m.emb_planes.hi = (__half *)m.dev_alloc(ne * 2); m.emb_planes.lo = (__half *)m.dev_alloc(ne * 2);
+            if (!m.emb_planes.hi || !m.emb_planes.lo || split_to_h16(m.emb, m.emb_planes.hi, m.emb_planes.lo, ne, m.stream)) return -1;
+        }
         m.proj_b = f32dev(m, "decoder.decoder_projector.bias", true, &err);
         m.head_b = f32dev(m, "joint.head.bias", true, &err);
         int n = 0;

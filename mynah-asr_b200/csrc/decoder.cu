@@ -160,6 +160,23 @@ __device__ __forceinline__ void stage_x(__half *xhi, __half *xlo, int xs, int ko
 }
 __device__ __forceinline__ float4 ld4(const float *p) { return *reinterpret_cast<const float4 *>(p); }
 
+// Rows that already exist as fp16 (hi, lo) planes in global memory (hidden states, embedding rows) go to
+// the X tile with 16-byte asynchronous copies: no registers, no conversion, one wait for all of them.
+// row_hi(b) / row_lo(b) return the H halves of utterance b; columns [koff, koff + H) of the tile are written.
+__device__ __forceinline__ void cp16(void *dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_wait_all() { asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory"); }
+template <typename FH, typename FL>
+__device__ __forceinline__ void stage_planes(__half *xhi, __half *xlo, int xs, int koff, int H, int B, FH row_hi, FL row_lo) {
+    const int cpr = H >> 3;                               // 16-byte chunks per row
+    for (int idx = threadIdx.x; idx < B * cpr; idx += blockDim.x) {
+        const int b = idx / cpr, c = idx - b * cpr;
+        cp16(xhi + b * xs + koff + 8 * c, row_hi(b) + 8 * c);
+        cp16(xlo + b * xs + koff + 8 * c, row_lo(b) + 8 * c);
+    }
+}
+
 struct Cand { float v; int i; };
 __device__ __forceinline__ void cand_take(Cand &a, float v, int i) {
     if (v > a.v || (v == a.v && i < a.i)) { a.v = v; a.i = i; }
@@ -171,15 +188,23 @@ __device__ __forceinline__ void cand_take(Cand &a, float v, int i) {
 // place. Utterances that did not emit copy their state through.
 __device__ void lstm_phase(const GreedyDev &p, int l, int par, __half *xhi, __half *xlo, float *red, int lane, int wib) {
     const int H = p.H, B = p.B, K = 2 * H, xs = K + XPAD;
-    const float *hold = p.h[par] + (size_t)l * B * H;
-    float *hnew = p.h[par ^ 1] + (size_t)l * B * H;
+    // hidden states live as fp16 (hi, lo) planes: h[parity] = [hi: L][B][H] then [lo: L][B][H] halves
+    const size_t nstate = (size_t)p.L * B * H;
+    const __half *hold_hi = reinterpret_cast<const __half *>(p.h[par]) + (size_t)l * B * H, *hold_lo = hold_hi + nstate;
+    __half *hnew_hi = reinterpret_cast<__half *>(p.h[par ^ 1]) + (size_t)l * B * H, *hnew_lo = hnew_hi + nstate;
     float *cc = p.c + (size_t)l * B * H;
-    const float *xin = l == 0 ? nullptr : p.h[par ^ 1] + (size_t)(l - 1) * B * H;
+    const __half *xin_hi = l == 0 ? nullptr : reinterpret_cast<const __half *>(p.h[par ^ 1]) + (size_t)(l - 1) * B * H;
+    const __half *xin_lo = l == 0 ? nullptr : xin_hi + nstate;
     constexpr int NSL = 4;
     const int nrb = H / 4, chunks = K / 32, per = (chunks + NSL - 1) / NSL;
     if (blockIdx.x * 8 < nrb * NSL) {        // a CTA without a row block to work on does not pull the activations either
-        stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) { return ld4(l == 0 ? p.emb + (size_t)p.last_tok[b] * H + k : xin + (size_t)b * H + k); });
-        stage_x(xhi, xlo, xs, H, H, B, [&](int b, int k) { return ld4(hold + (size_t)b * H + k); });
+        if (l == 0)
+            stage_planes(xhi, xlo, xs, 0, H, B, [&](int b) { return p.emb_hi + (size_t)p.last_tok[b] * H; },
+                         [&](int b) { return p.emb_lo + (size_t)p.last_tok[b] * H; });
+        else
+            stage_planes(xhi, xlo, xs, 0, H, B, [&](int b) { return xin_hi + (size_t)b * H; }, [&](int b) { return xin_lo + (size_t)b * H; });
+        stage_planes(xhi, xlo, xs, H, H, B, [&](int b) { return hold_hi + (size_t)b * H; }, [&](int b) { return hold_lo + (size_t)b * H; });
+        cp_wait_all();
     }
     __syncthreads();
     const int g = lane >> 2, t = lane & 3;
@@ -226,9 +251,11 @@ __device__ void lstm_phase(const GreedyDev &p, int l, int par, __half *xhi, __ha
                                 const float zo = ob + p.b_ih[l][3 * H + unit] + p.b_hh[l][3 * H + unit];
                                 const float cn = sigmoid_stable(zf) * cc[o] + sigmoid_stable(zi) * tanhf(zg);
                                 cc[o] = cn;
-                                hnew[o] = sigmoid_stable(zo) * tanhf(cn);
+                                __half hh, hl;
+                                split_h16(sigmoid_stable(zo) * tanhf(cn), hh, hl);
+                                hnew_hi[o] = hh; hnew_lo[o] = hl;
                             } else {
-                                hnew[o] = hold[o];
+                                hnew_hi[o] = hold_hi[o]; hnew_lo[o] = hold_lo[o];
                             }
                         }
                     }
@@ -241,11 +268,14 @@ __device__ void lstm_phase(const GreedyDev &p, int l, int par, __half *xhi, __ha
 // g[b] = proj_b + proj_w . h_last[b] for the utterances that emitted.
 __device__ void proj_phase(const GreedyDev &p, int par, bool all, __half *xhi, __half *xlo, float *red, int lane, int wib) {
     const int H = p.H, B = p.B, xs = 2 * H + XPAD;
-    const float *hl = p.h[par] + (size_t)(p.L - 1) * B * H;
+    const size_t nstate = (size_t)p.L * B * H;
+    const __half *hl_hi = reinterpret_cast<const __half *>(p.h[par]) + (size_t)(p.L - 1) * B * H, *hl_lo = hl_hi + nstate;
     constexpr int NSL = 4;
     const int nrb = (H + 15) / 16, chunks = H / 32, per = (chunks + NSL - 1) / NSL;
-    if (blockIdx.x * 8 < nrb * NSL)
-        stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) { return ld4(hl + (size_t)b * H + k); });
+    if (blockIdx.x * 8 < nrb * NSL) {
+        stage_planes(xhi, xlo, xs, 0, H, B, [&](int b) { return hl_hi + (size_t)b * H; }, [&](int b) { return hl_lo + (size_t)b * H; });
+        cp_wait_all();
+    }
     __syncthreads();
     const int g = lane >> 2, t = lane & 3;
     for (int base = blockIdx.x * 8; base < nrb * NSL; base += gridDim.x * 8) {
@@ -289,6 +319,8 @@ greedy_kernel(GreedyDev p) {
     const int lane = threadIdx.x & 31, wib = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     int par = (!p.init_state && p.par_state) ? *p.par_state : 0;   // read before the first grid sync; written after the last
+    for (int i = threadIdx.x; i < 16 * xs; i += blockDim.x) { xhi[i] = __float2half_rn(0.f); xlo[i] = __float2half_rn(0.f); }
+    __syncthreads();                                               // rows of absent utterances stay zero for every plane copy
 
     if (p.init_state) {
         // SOS = blank on a zero state (src/decoder.c:151): run the prediction net once

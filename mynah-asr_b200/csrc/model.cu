@@ -375,6 +375,7 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
         GreedyDev p;
         memset(&p, 0, sizeof(p));
         p.emb = emb; p.head_b = head_b; p.proj_b = proj_b;
+        p.emb_hi = emb_planes.hi; p.emb_lo = emb_planes.lo;
         p.head_hi = head.hi; p.head_lo = head.lo; p.proj_hi = dec_proj.hi; p.proj_lo = dec_proj.lo;
         for (int l = 0; l < L; l++) { p.wcat_hi[l] = wcat[l].hi; p.wcat_lo[l] = wcat[l].lo; p.b_ih[l] = b_ih[l]; p.b_hh[l] = b_hh[l]; }
         p.V = vocab; p.ND = cfg.n_durations; p.H = H; p.L = L; p.blank = cfg.blank_id; p.max_symbols = cfg.max_symbols;

@@ -115,6 +115,7 @@ struct Model {
     QWeight ctc_head;
     int ctc_vocab = 0;
     const float *emb = nullptr, *proj_b = nullptr, *head_b = nullptr;
+    H16 emb_planes{nullptr, nullptr};
     const float *b_ih[DEC_MAX_LAYERS], *b_hh[DEC_MAX_LAYERS];
     QWeight head, dec_proj, wcat[DEC_MAX_LAYERS];    // wcat[l] = [W_ih | W_hh] of LSTM layer l
     int vocab = 0, pred_hidden = 0, pred_layers = 0;
@@ -176,6 +177,7 @@ struct Model {
 struct GreedyDev {
     // model
     const float *emb, *head_b, *proj_b;
+    const __half *emb_hi, *emb_lo;                                 // embedding table as operand planes [V, H]
     const __half *head_hi, *head_lo, *proj_hi, *proj_lo;           // [V+ND, H], [H, H] operand planes
     const __half *wcat_hi[DEC_MAX_LAYERS], *wcat_lo[DEC_MAX_LAYERS];   // [4H, 2H] = [W_ih | W_hh]
     const float *b_ih[DEC_MAX_LAYERS], *b_hh[DEC_MAX_LAYERS];
@@ -186,7 +188,7 @@ struct GreedyDev {
     const float *enc;            // packed [sum T, H]
     const int *enc_off, *enc_len;
     // state
-    float *h[2], *c;             // h[parity][L][B][H], c[L][B][H]
+    float *h[2], *c;             // h[parity]: fp16 planes (hi [L][B][H] then lo [L][B][H], 4 bytes per value); c[L][B][H] f32
     float *g;                    // [B][H]
     int *t, *emitted_here, *n_out, *last_tok, *emit;
     int *tokens, *frames, cap;
