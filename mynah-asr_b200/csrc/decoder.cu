@@ -134,27 +134,24 @@ __device__ __forceinline__ void rowblock_mma(const __half *__restrict__ whi, con
 static constexpr int STAGE_NV = 16;                   // float4 per thread: covers K <= 1024
 template <typename F>
 __device__ __forceinline__ void stage_x(__half *xhi, __half *xlo, int xs, int koff, int K, int B, F value4) {
-    const int k4n = K >> 2, n4 = 16 * k4n;
+    // sixteen threads per row, 16-byte columns c0, c0 + 16, ...: no division, 256 contiguous bytes per row step
+    const int b = threadIdx.x >> 4, c0 = threadIdx.x & 15, k4n = K >> 2;
     float4 v[STAGE_NV];
 #pragma unroll
     for (int j = 0; j < STAGE_NV; j++) {
-        const int idx = threadIdx.x + j * 256;
+        const int c = c0 + 16 * j;
         v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (idx < n4) {
-            const int b = idx / k4n, k = (idx - b * k4n) * 4;
-            if (b < B) v[j] = value4(b, k);
-        }
+        if (c < k4n && b < B) v[j] = value4(b, c * 4);
     }
 #pragma unroll
     for (int j = 0; j < STAGE_NV; j++) {
-        const int idx = threadIdx.x + j * 256;
-        if (idx < n4) {
-            const int b = idx / k4n, k = (idx - b * k4n) * 4;
+        const int c = c0 + 16 * j;
+        if (c < k4n) {
             __align__(8) __half h[4], l[4];
             split_h16(v[j].x, h[0], l[0]); split_h16(v[j].y, h[1], l[1]);
             split_h16(v[j].z, h[2], l[2]); split_h16(v[j].w, h[3], l[3]);
-            *reinterpret_cast<uint2 *>(xhi + b * xs + koff + k) = *reinterpret_cast<uint2 *>(h);
-            *reinterpret_cast<uint2 *>(xlo + b * xs + koff + k) = *reinterpret_cast<uint2 *>(l);
+            *reinterpret_cast<uint2 *>(xhi + b * xs + koff + c * 4) = *reinterpret_cast<uint2 *>(h);
+            *reinterpret_cast<uint2 *>(xlo + b * xs + koff + c * 4) = *reinterpret_cast<uint2 *>(l);
         }
     }
 }
