@@ -270,8 +270,14 @@ int gemm_tc(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, 
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
     }
-    const int tm = cdiv(M, BM), want = (2 * sms) / 3;
-    const int bn = tm * cdiv(N, 128) >= want ? 128 : tm * cdiv(N, 64) >= want ? 64 : 32;
+    // waves of CTAs x time of one tile (the MMAs scale with the tile width, prologue and epilogue do not)
+    const int tm = cdiv(M, BM);
+    int bn = 128;
+    long best = -1;
+    for (int cand = 128; cand >= 32; cand >>= 1) {
+        const long cost = (long)cdiv(tm * cdiv(N, cand), sms) * (cand + 48);
+        if (best < 0 || cost < best) { best = cost; bn = cand; }
+    }
     if (nterms == 1) {
         if (bn == 128 && N >= 256) return launch<256, 1>(A, B, ep, M, N, K, status, stream);
         if (bn == 128) return launch<128, 1>(A, B, ep, M, N, K, status, stream);
