@@ -84,7 +84,7 @@ int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *sca
         note_launch();
         MB_CUDA(cudaStreamSynchronize(stream));
     }
-    if ((fmt == FMT_GGML_Q4_0 || fmt == FMT_GGML_Q8_0) && k % 128 == 0) {
+    if (((fmt == FMT_GGML_Q4_0 || fmt == FMT_GGML_Q8_0) && k % 128 == 0) || (fmt == FMT_GGML_Q4_K && k % 256 == 0)) {
         w.tc_q = (uint8_t *)dev_alloc(qstream_tc_bytes(fmt, n, k));
         if (!w.tc_q) return -1;
         if (const size_t sb = qstream_tc_scratch_bytes(n, k)) {

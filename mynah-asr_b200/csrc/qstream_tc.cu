@@ -1,5 +1,5 @@
 // Weight-streaming quantised matmul on the tcgen05 integer tensor path:
-// out[T,n] = x[T,k] W^T for T <= 8, W stored as ggml Q4_0 / Q8_0 blocks.
+// out[T,n] = x[T,k] W^T for T <= 8, W stored as ggml Q4_0 / Q8_0 / Q4_K blocks.
 // The bandwidth-bound half of the reference's mynah_asr_qmat_mul (src/qmat.c:508-597).
 //
 // Arithmetic. A stored block is 32 integers q and an f16 scale d (w = d*q, ingot dequant.c:72-83).
@@ -8,6 +8,9 @@
 // the row is reproduced to 2^-28 of the block's largest element. The tensor core then forms the
 // exact int32 dots q.p0 .. q.p3 of every (weight row, block), and a thread folds them in f32:
 // out += d * 2^e * (v0 + v1/2^7 + v2/2^14 + v3/2^21). No product is ever rounded before that fold.
+// Q4_K (256-element super-blocks, w = d*sc*q - dmin*m per 32-element sub-block with 6-bit sc, m;
+// ingot dequant.c:131-156): the dots are taken with the unsigned nibbles, the fold uses d*sc and the
+// offset term dmin*m times the block's activation sum.
 //
 // Per CTA (persistent, one per SM), 32 warps with fixed roles:
 //   * warps 0 and 5-7, one thread each: stream the stored bytes of every fourth stage (128 weight
@@ -50,15 +53,23 @@ static constexpr int QS_FIRST_SCALE = 24, QS_SCALE_WARPS = 8;
 static constexpr int QS_THREADS = (QS_FIRST_SCALE + QS_SCALE_WARPS) * 32;     // 1024
 static constexpr int QS_A_COLS = 8;                           // tensor-memory columns of one decoded block (32 int8)
 static constexpr int QS_TMEM_COLS = 512;
-static constexpr int QS_SC_COL0 = 384;                        // eight 2-column slots: the four f16 block scales of a row
+static constexpr int QS_SC_COL0 = 384;                        // eight 4-column slots: a row's scale record of the stage
 static constexpr int QS_SC_SLOTS = 8;
-static constexpr int QS_SCALE_BYTES = QS_NB * QS_ROWS * 2;    // 1 KB of f16 block scales per stage
+static constexpr int QS_SC_COLS = 4;
 
-__host__ __device__ constexpr int qs_quant_bytes(int fmt) { return fmt == FMT_GGML_Q4_0 ? QS_ROWS * QS_SK / 2 : QS_ROWS * QS_SK; }
-__host__ __device__ constexpr int qs_stage_bytes(int fmt) { return qs_quant_bytes(fmt) + QS_SCALE_BYTES; }
+// per row and stage: Q4_0 / Q8_0 four f16 block scales (8 bytes); Q4_K f16 d, f16 dmin, sc[4], m[4] (12 bytes)
+__host__ __device__ constexpr int qs_scale_rec(int fmt) { return fmt == FMT_GGML_Q4_K ? 12 : 8; }
+__host__ __device__ constexpr int qs_quant_bytes(int fmt) { return fmt == FMT_GGML_Q8_0 ? QS_ROWS * QS_SK : QS_ROWS * QS_SK / 2; }
+__host__ __device__ constexpr int qs_stage_bytes(int fmt) { return qs_quant_bytes(fmt) + QS_ROWS * qs_scale_rec(fmt); }
 // stored-byte stages in flight (a power of two): what fits beside 4096 k of activation planes
 // (64 KB for up to 4 rows, 128 KB for 8) — 144 / 72 KB of Q4_0, 136 / 68 KB of Q8_0
 __host__ __device__ constexpr int qs_raw_depth(int fmt, int nt) { return (fmt == FMT_GGML_Q4_0 ? 16 : 8) / (nt == 8 ? 2 : 1); }
+
+// 6-bit scale / min j of a Q4_K super-block (get_scale_min_k4, ingot dequant.c:120-129)
+__host__ __device__ inline void qs_k4_scale_min(const uint8_t *sc, int j, int *s, int *m) {
+    if (j < 4) { *s = sc[j] & 63; *m = sc[j + 4] & 63; }
+    else { *s = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4); *m = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+}
 
 // -------------------------------------------------------------------- re-tiling at load
 // [tile][stage][ quants: [16-byte chunk c][row 0..127][16 B] | scales: [row 0..127][block 0..3] f16 ]
@@ -79,6 +90,30 @@ __global__ void qs_retile_kernel(const uint8_t *__restrict__ raw, uint8_t *__res
     sc[1] = p[1];
 }
 
+// Q4_K: one thread per (row, super-block) fills the two stages the super-block spans. A stage holds the 64
+// quant bytes of its two 64-element groups A, B as four 16-byte chunks (bytes 0-15 and 16-31 of A, then of B;
+// low nibbles of a group's 32 bytes are its first sub-block, high nibbles its second) and the record
+// d, dmin, sc[4], m[4] of the stage's four sub-blocks.
+__global__ void qs_retile_q4k_kernel(const uint8_t *__restrict__ raw, uint8_t *__restrict__ dst, int n, int k) {
+    const size_t sbi = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    const int spr = k / 256;
+    if (sbi >= (size_t)n * spr) return;
+    const int row = (int)(sbi / spr), sb = (int)(sbi % spr);
+    const int tile = row / QS_ROWS, rl = row % QS_ROWS;
+    const uint8_t *p = raw + sbi * 144;                   // d, dmin (f16), scales[12], qs[128]
+    for (int half = 0; half < 2; half++) {
+        uint8_t *stage = dst + ((size_t)tile * (k / QS_SK) + 2 * sb + half) * qs_stage_bytes(FMT_GGML_Q4_K);
+        for (int i = 0; i < 64; i++) stage[((i / 16) * QS_ROWS + rl) * 16 + (i & 15)] = p[16 + 64 * half + i];
+        uint8_t *rec = stage + qs_quant_bytes(FMT_GGML_Q4_K) + rl * 12;
+        rec[0] = p[0]; rec[1] = p[1]; rec[2] = p[2]; rec[3] = p[3];
+        for (int b = 0; b < 4; b++) {
+            int sc, m;
+            qs_k4_scale_min(p + 4, 4 * half + b, &sc, &m);
+            rec[4 + b] = (uint8_t)sc; rec[8 + b] = (uint8_t)m;
+        }
+    }
+}
+
 size_t qstream_tc_bytes(int fmt, int n, int k) {
     return (size_t)cdiv(n, QS_ROWS) * (k / QS_SK) * qs_stage_bytes(fmt);
 }
@@ -86,6 +121,9 @@ size_t qstream_tc_bytes(int fmt, int n, int k) {
 int qstream_tc_retile(const QWeight &w, uint8_t *dst, cudaStream_t st) {
     MB_CUDA(cudaMemsetAsync(dst, 0, qstream_tc_bytes(w.fmt, w.n, w.k), st));
     const size_t nblk = (size_t)w.n * (w.k / 32);
+    if (w.fmt == FMT_GGML_Q4_K)
+        qs_retile_q4k_kernel<<<(unsigned)((nblk / 8 + 255) / 256), 256, 0, st>>>(w.raw, dst, w.n, w.k);
+    else
     qs_retile_kernel<<<(unsigned)((nblk + 255) / 256), 256, 0, st>>>(w.raw, dst, w.n, w.k, w.fmt);
     MB_CUDA(cudaGetLastError());
     return 0;
@@ -132,9 +170,9 @@ __device__ __forceinline__ void tc_mma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, u
         ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// instruction descriptor: D s32, A/B s8 K-major, M x N
-__host__ __device__ constexpr uint32_t qs_idesc_i8(int M, int N) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+// instruction descriptor: D s32, A s8 (or u8), B s8, both K-major, M x N
+__host__ __device__ constexpr uint32_t qs_idesc_i8(int M, int N, bool a_unsigned) {
+    return (2u << 4) | ((a_unsigned ? 0u : 1u) << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 // 8 registers per thread -> 32 lanes x 8 consecutive columns of tensor memory
 __device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t *r) {
@@ -142,11 +180,11 @@ __device__ __forceinline__ void tc_st8(uint32_t taddr, const uint32_t *r) {
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                  : "memory");
 }
-__device__ __forceinline__ void tc_st2(uint32_t taddr, uint32_t r0, uint32_t r1) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1, %2};" ::"r"(taddr), "r"(r0), "r"(r1) : "memory");
+__device__ __forceinline__ void tc_st4(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
 }
-__device__ __forceinline__ void tc_ld2(uint32_t taddr, uint32_t &r0, uint32_t &r1) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(taddr) : "memory");
+__device__ __forceinline__ void tc_ld4u(uint32_t taddr, uint32_t &r0, uint32_t &r1, uint32_t &r2, uint32_t &r3) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(taddr) : "memory");
 }
 // 32 registers per thread -> 32 lanes x 32 consecutive columns of tensor memory
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t *r) {
@@ -229,7 +267,8 @@ qstream_tc_kernel(const QsArgs a) {
     uint8_t *raw = x_tile + (size_t)a.max_slice_st * XT;                   // DEPTH x SB
     float *xch = reinterpret_cast<float *>(raw + DEPTH * SB);              // 2 x 8 x 128: sums of read-back group 1
     float *sxs = xch + 2 * 8 * QS_ROWS;                                    // [stage][block][NT] activation block scales 2^e
-    uint64_t *raw_full = reinterpret_cast<uint64_t *>(sxs + (size_t)a.max_slice_st * QS_NB * NT);
+    float *sxsum = sxs + (size_t)a.max_slice_st * QS_NB * NT;              // Q4_K: [stage][block][NT] sums of the activations
+    uint64_t *raw_full = reinterpret_cast<uint64_t *>(sxsum + (FMT == FMT_GGML_Q4_K ? (size_t)a.max_slice_st * QS_NB * NT : 0));
     uint64_t *raw_empty = raw_full + DEPTH;
     uint64_t *a_full = raw_empty + DEPTH;
     uint64_t *a_free = a_full + AP;                                        // used when DP != AP; else d_full says the same
@@ -318,6 +357,10 @@ qstream_tc_kernel(const QsArgs a) {
                         *reinterpret_cast<int8_t *>(x_tile + st * XT + row * 128 + (((kpos >> 4) ^ (row & 7)) << 4) + (kpos & 15)) = (int8_t)(int)pl;
                     }
                     if (lane == 0) sxs[(st * QS_NB + b) * NT + j] = m > 0.f ? __int_as_float((127 + eb) << 23) : 0.f;
+                    if (FMT == FMT_GGML_Q4_K) {
+                        const float sum = warp_sum(v[uu][b]);
+                        if (lane == 0) sxsum[(st * QS_NB + b) * NT + j] = sum;
+                    }
                 }
             }
         }
@@ -333,7 +376,7 @@ qstream_tc_kernel(const QsArgs a) {
                 const int i = warp - QS_FIRST_ISSUER;
                 bool ok = mbar_wait(x_full, 0);
                 const uint64_t bdesc0 = umma_desc_sw128(smem_u32(x_tile));
-                constexpr uint32_t idesc = qs_idesc_i8(QS_ROWS, N);
+                constexpr uint32_t idesc = qs_idesc_i8(QS_ROWS, N, FMT == FMT_GGML_Q4_K);
                 int st = i % nst;
                 for (int it = i; it < total && ok; it += DP) {
                     const int as = it & (AP - 1);
@@ -374,6 +417,20 @@ qstream_tc_kernel(const QsArgs a) {
                         rb[0] = ((q.x << 4) & HM) ^ FL; rb[1] = ((q.y << 4) & HM) ^ FL; rb[2] = ((q.z << 4) & HM) ^ FL; rb[3] = ((q.w << 4) & HM) ^ FL;
                         rb[4] = (q.x & HM) ^ FL; rb[5] = (q.y & HM) ^ FL; rb[6] = (q.z & HM) ^ FL; rb[7] = (q.w & HM) ^ FL;
                     }
+                } else if (FMT == FMT_GGML_Q4_K) {
+                    // 32 quant bytes hold two sub-blocks: low nibbles of byte i = element i of the first, high
+                    // nibbles = element i of the second; unsigned q*16 in the high half of a byte
+                    constexpr uint32_t HM = 0xF0F0F0F0u;
+#pragma unroll
+                    for (int gq = 0; gq < 2; gq++) {
+                        const uint4 q0 = *reinterpret_cast<const uint4 *>(src + (2 * gq) * QS_ROWS * 16);
+                        const uint4 q1 = *reinterpret_cast<const uint4 *>(src + (2 * gq + 1) * QS_ROWS * 16);
+                        uint32_t *lo = r + (2 * gq) * QS_A_COLS, *hi = lo + QS_A_COLS;
+                        lo[0] = (q0.x << 4) & HM; lo[1] = (q0.y << 4) & HM; lo[2] = (q0.z << 4) & HM; lo[3] = (q0.w << 4) & HM;
+                        lo[4] = (q1.x << 4) & HM; lo[5] = (q1.y << 4) & HM; lo[6] = (q1.z << 4) & HM; lo[7] = (q1.w << 4) & HM;
+                        hi[0] = q0.x & HM; hi[1] = q0.y & HM; hi[2] = q0.z & HM; hi[3] = q0.w & HM;
+                        hi[4] = q1.x & HM; hi[5] = q1.y & HM; hi[6] = q1.z & HM; hi[7] = q1.w & HM;
+                    }
                 } else {
 #pragma unroll
                     for (int c = 0; c < 2 * QS_NB; c++) {
@@ -381,7 +438,9 @@ qstream_tc_kernel(const QsArgs a) {
                         r[4 * c] = q.x; r[4 * c + 1] = q.y; r[4 * c + 2] = q.z; r[4 * c + 3] = q.w;
                     }
                 }
-                const uint2 sc = *reinterpret_cast<const uint2 *>(raw + rs * SB + QBYTES + row * (QS_NB * 2));
+                // the row's scale record of this stage (8 or 12 bytes)
+                const uint32_t *recp = reinterpret_cast<const uint32_t *>(raw + rs * SB + QBYTES + row * qs_scale_rec(FMT));
+                const uint32_t rec0 = recp[0], rec1 = recp[1], rec2 = FMT == FMT_GGML_Q4_K ? recp[2] : 0u;
                 // only now is A slot g needed: the MMAs of stage it-AP, its last user, must be done
                 // (the loads and the unpacking above are off the slot's critical path)
                 if (it >= AP && !__all_sync(0xffffffffu, mbar_wait(DP == AP ? &d_full[g] : &a_free[g], (uint32_t)(((it / AP) & 1) ^ 1)))) {
@@ -390,7 +449,7 @@ qstream_tc_kernel(const QsArgs a) {
                 }
                 tc_fence_after();
                 tc_st32(tdst + g * AST, r);
-                tc_st2(tdst + QS_SC_COL0 + (it & (QS_SC_SLOTS - 1)) * 2, sc.x, sc.y);   // slot it-8 was read before the MMAs of it-4 could start
+                tc_st4(tdst + QS_SC_COL0 + (it & (QS_SC_SLOTS - 1)) * QS_SC_COLS, rec0, rec1, rec2, 0u);   // slot it-8 was read before the MMAs of it-4 could start
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
@@ -403,7 +462,7 @@ qstream_tc_kernel(const QsArgs a) {
             const int h = (warp - QS_FIRST_SCALE) >> 2;
             const int row = (warp & 3) * 32 + lane;
             const uint32_t tsrc = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + D_COL0;
-            constexpr float DQ = FMT == FMT_GGML_Q4_0 ? 0.0625f : 1.f;     // Q4_0 weights sit in tensor memory as (q-8)*16
+            constexpr float DQ = FMT == FMT_GGML_Q8_0 ? 1.f : 0.0625f;     // 4-bit weights sit in tensor memory times 16
             constexpr float P7 = 0.0078125f;                              // 2^-7 between planes
             constexpr int BPL = NCOL <= 8 ? 4 : NCOL == 16 ? 2 : 1;        // blocks read back per tcgen05.wait::ld
             int it = 0;
@@ -421,9 +480,9 @@ qstream_tc_kernel(const QsArgs a) {
                     if (ok && !__all_sync(0xffffffffu, mbar_wait(&d_full[par], uph))) { ok = false; if (lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE); }
                     if (!ok) continue;
                     tc_fence_after();
-                    uint32_t sc0, sc1;                       // the row's four f16 block scales, left by the decode warps
-                    tc_ld2(tsrc - D_COL0 + QS_SC_COL0 + (it & (QS_SC_SLOTS - 1)) * 2, sc0, sc1);
-                    float d[QS_NB];
+                    uint32_t sc0, sc1, sc2, sc3;             // the row's scale record, left by the decode warps
+                    tc_ld4u(tsrc - D_COL0 + QS_SC_COL0 + (it & (QS_SC_SLOTS - 1)) * QS_SC_COLS, sc0, sc1, sc2, sc3);
+                    float d[QS_NB], dm[QS_NB];
 #pragma unroll
                     for (int b0 = 0; b0 < QS_NB; b0 += BPL) {
                         int v[BPL][NCOL];
@@ -432,7 +491,16 @@ qstream_tc_kernel(const QsArgs a) {
                         tc_wait_ld();
                         if (b0 == 0) {
                             const __half2 h01 = *reinterpret_cast<const __half2 *>(&sc0), h23 = *reinterpret_cast<const __half2 *>(&sc1);
-                            d[0] = __low2float(h01) * DQ; d[1] = __high2float(h01) * DQ; d[2] = __low2float(h23) * DQ; d[3] = __high2float(h23) * DQ;
+                            if (FMT == FMT_GGML_Q4_K) {      // record: d, dmin | sc[4] | m[4]; w = (d sc) q - (dmin m)
+                                const float dd = __low2float(h01) * DQ, dmin = __high2float(h01);
+#pragma unroll
+                                for (int b = 0; b < QS_NB; b++) {
+                                    d[b] = dd * (float)((sc1 >> (8 * b)) & 0xFFu);
+                                    dm[b] = dmin * (float)((sc2 >> (8 * b)) & 0xFFu);
+                                }
+                            } else {
+                                d[0] = __low2float(h01) * DQ; d[1] = __high2float(h01) * DQ; d[2] = __low2float(h23) * DQ; d[3] = __high2float(h23) * DQ;
+                            }
                         }
                         if (b0 + BPL == QS_NB) {             // the whole stage is in registers: its accumulators may be reused
                             tc_fence_before();
@@ -453,6 +521,7 @@ qstream_tc_kernel(const QsArgs a) {
                                 const float f = fmaf(fmaf(fmaf((float)v[bb][4 * j + 3], P7, (float)v[bb][4 * j + 2]), P7, (float)v[bb][4 * j + 1]), P7,
                                                      (float)v[bb][4 * j]);
                                 acc[j] = fmaf(ds[bb][j], f, acc[j]);
+                                if (FMT == FMT_GGML_Q4_K) acc[j] = fmaf(-dm[b0 + bb], sxsum[(st * QS_NB + b0 + bb) * NT + j], acc[j]);
                             }
                     }
                 }
@@ -496,7 +565,7 @@ __global__ void qs_reduce_kernel(const float *__restrict__ partial, float *__res
 static size_t qs_smem_bytes(int fmt, int nt, int max_slice_st) {
     const int nrows = nt <= 4 ? 16 : 32;
     return 1024 + (size_t)max_slice_st * nrows * 128 + (size_t)qs_raw_depth(fmt, nt) * qs_stage_bytes(fmt) + 2 * 8 * QS_ROWS * sizeof(float) +
-           (size_t)max_slice_st * QS_NB * nt * sizeof(float) + (2 * qs_raw_depth(fmt, nt) + 4 * 4 + 1) * 8 + 16;
+           (size_t)max_slice_st * QS_NB * nt * sizeof(float) * (fmt == FMT_GGML_Q4_K ? 2 : 1) + (2 * qs_raw_depth(fmt, nt) + 4 * 4 + 1) * 8 + 16;
 }
 
 template <int FMT, int NT>
@@ -536,6 +605,9 @@ int qstream_tc(const QWeight &w, const float *x, int ldx, float *out, int ldo, c
     if (w.fmt == FMT_GGML_Q4_0)
         rc = nt == 1 ? qs_launch<FMT_GGML_Q4_0, 1>(a, grid, st) : nt == 2 ? qs_launch<FMT_GGML_Q4_0, 2>(a, grid, st)
            : nt == 4 ? qs_launch<FMT_GGML_Q4_0, 4>(a, grid, st) : qs_launch<FMT_GGML_Q4_0, 8>(a, grid, st);
+    else if (w.fmt == FMT_GGML_Q4_K)
+        rc = nt == 1 ? qs_launch<FMT_GGML_Q4_K, 1>(a, grid, st) : nt == 2 ? qs_launch<FMT_GGML_Q4_K, 2>(a, grid, st)
+           : nt == 4 ? qs_launch<FMT_GGML_Q4_K, 4>(a, grid, st) : qs_launch<FMT_GGML_Q4_K, 8>(a, grid, st);
     else
         rc = nt == 1 ? qs_launch<FMT_GGML_Q8_0, 1>(a, grid, st) : nt == 2 ? qs_launch<FMT_GGML_Q8_0, 2>(a, grid, st)
            : nt == 4 ? qs_launch<FMT_GGML_Q8_0, 4>(a, grid, st) : qs_launch<FMT_GGML_Q8_0, 8>(a, grid, st);

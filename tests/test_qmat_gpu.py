@@ -62,19 +62,22 @@ def test_small_T_streams_stored_blocks(gpu_pkg, synth, fmt, T):
         x = np.random.default_rng(T).standard_normal((T, k)).astype(np.float32)
         ref = x.astype(np.float64) @ wd.astype(np.float64).T
         assert rel(q.mul(x), ref) < 3e-6, (fmt, n, k)
-        # Q4_0 / Q8_0 default to the tcgen05 streaming kernel (T <= 8); the warp-level tensor-core
-        # kernel and the scalar one must agree
+        # Q4_0 / Q8_0 / Q4_K default to the tcgen05 streaming kernel (T <= 8); the warp-level tensor-core
+        # kernel (Q4_0 / Q8_0) and the scalar one must agree
         assert rel(q.mul(x, gpu_pkg.MMA_SYNC), ref) < 3e-6, (fmt, n, k)
         assert rel(q.mul(x, gpu_pkg.SCALAR), ref) < 2e-6, (fmt, n, k)
         q.close()
 
 
-@pytest.mark.parametrize("fmt", ["q4_0", "q8_0"])
+@pytest.mark.parametrize("fmt", ["q4_0", "q8_0", "q4_k"])
 def test_streaming_kernel_work_splits(gpu_pkg, synth, fmt):
     """Shapes that drive the tcgen05 streaming kernel through each of its work splits: several row
     tiles per CTA (more tiles than multiprocessors), one K slice, many K slices, K beyond what one
     CTA holds (8192) with many tiles, and long runs of stages per CTA at every read-back width; ragged last tile everywhere."""
-    for n, k, Ts in ((20001, 256, (1, 5)), (19001, 128, (2,)), (300, 8192, (1, 8)), (9700, 8192, (1,)), (19000, 4096, (4, 8)), (129, 1024, (3,))):
+    shapes = ((20001, 256, (1, 5)), (19001, 128, (2,)), (300, 8192, (1, 8)), (9700, 8192, (1,)), (19000, 4096, (4, 8)), (129, 1024, (3,)))
+    if fmt == "q4_k":       # 256-element super-blocks; smaller matrices (the numpy K-quantiser is slow)
+        shapes = ((20001, 256, (1, 5)), (300, 8192, (1, 8)), (2500, 8192, (2,)), (19000, 1024, (4, 8)), (129, 1024, (3,)))
+    for n, k, Ts in shapes:
         q, wd = make(gpu_pkg, synth, fmt, n, k, seed=n)
         for T in Ts:
             x = np.random.default_rng(T).standard_normal((T, k)).astype(np.float32)
