@@ -54,8 +54,30 @@ const char *mynah_b200_last_error(void);
 /* ---- f32 GEMM hook ------------------------------------------------------------ */
 /* replaces mynah_asr_cuda_gemm_wt (src/backend.c:25, src/cuda_gemm.cu:144-190):
  * out[T,n] = x[T,k] W[n,k]^T, host pointers, synchronous. W is uploaded on every call
- * (no address-keyed cache; use a qmat handle for resident weights). */
+ * (no address-keyed cache: for a weight that may change between calls; mynah_asr_cuda_gemm_wt
+ * below keeps the reference's cache-by-address convention). */
 int mynah_b200_gemm_wt(const float *x, const float *w, float *out, int T, int n, int k);
+
+/* The reference's own hook names (src/backend.c:23-26, defined by src/cuda_gemm.cu:62-90,144-190), so
+ * that this library can stand where build/src/cuda_gemm.o stands in `make cuda`: same arguments, same
+ * return values (1/0; 0 = done, -1 = the caller falls back to the CPU), and the same convention that W
+ * is found again by its host address and must stay unchanged for the life of the process
+ * ("W must stay stable", src/backend.h:16-18) — it is uploaded on the first call only. */
+int mynah_asr_cuda_available(void);
+int mynah_asr_cuda_gemm_wt(const float *x, const float *w, float *out, int T, int n, int k);
+
+/* The same convention for a quantised operand, to be called at the top of mynah_asr_qmat_mul
+ * (src/qmat.c:503) with the blocks the weight file holds: wq (and scales, native formats only) are
+ * uploaded and re-tiled on the first call with this address and found by address afterwards.
+ * Host pointers, synchronous; flags as for mynah_b200_qmat_mul. 0, or -1 with mynah_b200_last_error. */
+int mynah_b200_qgemm(const void *wq, int fmt, const float *scales, int n, int k, const float *x, float *out,
+                     int T, int flags);
+/* Drops every weight the two calls above made resident; to be called where the reference drops its
+ * Metal cache (mynah_asr_metal_weights_evict from mynah_asr_free, src/mynah_asr.c:358-361): after the
+ * model file is unmapped the addresses mean nothing and a later load may reuse them. The reference's
+ * CUDA file has no such call (src/cuda_gemm.cu:96-103 only ever appends). */
+void mynah_b200_weights_evict(void);
+int mynah_b200_weights_resident(void);        /* entries held, for tests */
 
 /* ---- quantised weight matrix --------------------------------------------------- */
 /* replaces mynah_asr_qmat + mynah_asr_qmat_init (src/qmat.h:39-47, src/qmat.c:80-143): the

@@ -105,6 +105,9 @@ def lib():
     L.mynah_b200_launch_count.argtypes = [ci]
     L.mynah_b200_config_default.argtypes = [C.POINTER(Config)]
     L.mynah_b200_gemm_wt.argtypes = [c_fp, c_fp, c_fp, ci, ci, ci]
+    L.mynah_asr_cuda_gemm_wt.argtypes = [c_fp, c_fp, c_fp, ci, ci, ci]
+    L.mynah_b200_qgemm.argtypes = [vp, ci, c_fp, ci, ci, c_fp, c_fp, ci, ci]
+    L.mynah_b200_weights_evict.restype = None
     L.mynah_b200_qmat_create.restype = vp
     L.mynah_b200_qmat_create.argtypes = [ci, vp, c_fp, ci, ci]
     L.mynah_b200_qmat_free.argtypes = [vp]
@@ -213,6 +216,35 @@ def gemm_wt(x, w):
     out = np.empty((x.shape[0], w.shape[0]), np.float32)
     _check(lib().mynah_b200_gemm_wt(_fp(x), _fp(w), _fp(out), x.shape[0], w.shape[0], w.shape[1]), "gemm_wt")
     return out
+
+
+def cuda_gemm_wt(x, w):
+    """The reference's hook under its own name (mynah_asr_cuda_gemm_wt, src/cuda_gemm.cu:144-190): `w` must be a
+    C-contiguous float32 array that stays alive and unchanged; it is uploaded on the first call with this address."""
+    assert w.dtype == np.float32 and w.flags.c_contiguous
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty((x.shape[0], w.shape[0]), np.float32)
+    if lib().mynah_asr_cuda_gemm_wt(_fp(x), _fp(w), _fp(out), x.shape[0], w.shape[0], w.shape[1]) != 0:
+        raise BackendError("mynah_asr_cuda_gemm_wt: " + _err())
+    return out
+
+
+def qgemm(raw, fmt, n, k, x, flags=A16, scales=None):
+    """mynah_b200_qgemm: quantised operand found by the address of `raw` (a uint8 array the caller keeps alive)."""
+    assert raw.dtype == np.uint8 and raw.flags.c_contiguous
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty((x.shape[0], n), np.float32)
+    sc = None if scales is None else _fp(scales)
+    _check(lib().mynah_b200_qgemm(raw.ctypes.data, fmt, sc, n, k, _fp(x), _fp(out), x.shape[0], flags), "qgemm")
+    return out
+
+
+def weights_evict():
+    lib().mynah_b200_weights_evict()
+
+
+def weights_resident() -> int:
+    return int(lib().mynah_b200_weights_resident())
 
 
 class QMat:

@@ -1028,6 +1028,62 @@ int mynah_b200_gemm_wt(const float *x, const float *w, float *out, int T, int n,
     return rc;
 }
 
+// ---- address-keyed resident weights: the calling convention of the reference's own CUDA hook
+// (src/cuda_gemm.cu:92-130: every host weight pointer is uploaded once and found again by address).
+// One entry per (pointer, format, shape); calls on the same weight take the entry's lock (its
+// handle owns one stream and one scratch area), calls on different weights run side by side.
+namespace {
+struct ResidentWeight {
+    const void *host; int fmt, n, k;
+    mynah_b200_qmat *q;
+    std::mutex mu;
+};
+std::mutex g_resident_mu;
+std::vector<ResidentWeight *> g_resident;
+
+ResidentWeight *resident_weight(const void *host, int fmt, const float *scales, int n, int k) {
+    std::lock_guard<std::mutex> lk(g_resident_mu);
+    for (ResidentWeight *e : g_resident)
+        if (e->host == host && e->fmt == fmt && e->n == n && e->k == k) return e;
+    mynah_b200_qmat *q = mynah_b200_qmat_create(fmt, host, scales, n, k);
+    if (!q) return nullptr;
+    ResidentWeight *e = new ResidentWeight{host, fmt, n, k, q};
+    g_resident.push_back(e);
+    return e;
+}
+}  // namespace
+
+int mynah_b200_qgemm(const void *wq, int fmt, const float *scales, int n, int k, const float *x, float *out, int T, int flags) {
+    if (!wq || !x || !out || T < 0 || n <= 0 || k <= 0) { set_error("qgemm: bad argument"); return -1; }
+    if (!mynah_b200_available()) { set_error("qgemm: no sm_100 device"); return -1; }
+    ResidentWeight *e = resident_weight(wq, fmt, scales, n, k);
+    if (!e) return -1;
+    std::lock_guard<std::mutex> lk(e->mu);
+    return mynah_b200_qmat_mul(e->q, x, out, T, flags);
+}
+
+void mynah_b200_weights_evict(void) {
+    std::lock_guard<std::mutex> lk(g_resident_mu);
+    for (ResidentWeight *e : g_resident) {
+        { std::lock_guard<std::mutex> l2(e->mu); mynah_b200_qmat_free(e->q); }
+        delete e;
+    }
+    g_resident.clear();
+}
+
+int mynah_b200_weights_resident(void) {
+    std::lock_guard<std::mutex> lk(g_resident_mu);
+    return (int)g_resident.size();
+}
+
+// the two symbols src/backend.c:23-26 declares and src/cuda_gemm.cu defines, same meaning:
+// 1 / 0, and 0 = done, -1 = the caller falls back
+int mynah_asr_cuda_available(void) { return mynah_b200_available(); }
+
+int mynah_asr_cuda_gemm_wt(const float *x, const float *w, float *out, int T, int n, int k) {
+    return mynah_b200_qgemm(w, MYNAH_B200_F32, nullptr, n, k, x, out, T, MYNAH_B200_A16);
+}
+
 void mynah_b200_profile_begin(mynah_b200_model *h) {
     if (!h) return;
     Model &m = h->m;

@@ -201,3 +201,28 @@ def test_against_reference_qmat_outputs(gpu_pkg):
         assert rel(gpu_pkg.gemm_wt(g[f"x_{n}x{k}_T48"], w), g[f"y_{n}x{k}_T48_f32"]) < 5e-6
         for m in (mf, m8, m4):
             m.close()
+
+
+def test_address_keyed_hooks(gpu_pkg, synth):
+    """mynah_asr_cuda_gemm_wt under the reference's own name and mynah_b200_qgemm: a weight is uploaded on the
+    first call with its host address, found by address afterwards, and dropped by the evict call."""
+    pkg = gpu_pkg
+    pkg.weights_evict()
+    rng = np.random.default_rng(3)
+    w = (rng.standard_normal((96, 256)) * 0.05).astype(np.float32)
+    for T in (1, 5, 40):
+        x = rng.standard_normal((T, 256)).astype(np.float32)
+        assert rel(pkg.cuda_gemm_wt(x, w), x.astype(np.float64) @ w.astype(np.float64).T) < 3e-6
+    assert pkg.weights_resident() == 1
+    raw = synth.QUANTIZERS[2](w)                       # Q4_0 blocks of the same matrix
+    wd = O.ggml_dequant(2, raw).reshape(96, 256)
+    x = rng.standard_normal((3, 256)).astype(np.float32)
+    y = pkg.qgemm(raw, pkg.GGML_Q4_0, 96, 256, x)
+    assert rel(y, x.astype(np.float64) @ wd.astype(np.float64).T) < 3e-6
+    assert np.array_equal(y, pkg.qgemm(raw, pkg.GGML_Q4_0, 96, 256, x))
+    h = pkg.QMat(pkg.GGML_Q4_0, raw, 96, 256)
+    assert np.array_equal(y, h.mul(x))                 # the same bits as through a handle
+    h.close()
+    assert pkg.weights_resident() == 2
+    pkg.weights_evict()
+    assert pkg.weights_resident() == 0
