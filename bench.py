@@ -135,7 +135,7 @@ def run_reference(args, rank, world):
     from oracle import model_io, mynah_oracle as O, ref_binding as R
     cfg, tensors = cached_model(synth, args.workload, 0, lambda: None)
     cores = os.cpu_count() or 1
-    audio = synth.synth_audio(args.seconds, seed=100)
+    audio = synth.synth_audio(args.seconds, seed=100 + args.sample_index)
     fb, win = synth.mel_filterbank(cfg.n_mels), synth.hann_window()
     if R.available():
         kind = "reference"
@@ -176,7 +176,8 @@ def run_reference(args, rank, world):
         step()
     dt = time.perf_counter() - t0
     value = args.seconds * args.steps / dt
-    sample = f"1 utterance x {args.seconds:g} s per step (of the {args.batch} x {args.seconds:g} s batch)"
+    sample = (f"1 utterance x {args.seconds:g} s per step (the median of the {args.items} items)" if args.items else
+              f"1 utterance x {args.seconds:g} s per step (of the {args.batch} x {args.seconds:g} s batch)")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -193,13 +194,21 @@ SHAPES = {"cfg0": "Parakeet-TDT_CTC-110M", "cfg1": "Parakeet-TDT-0.6B", "cfg2": 
           "cfg3": "Nemotron-streaming-0.6B (offline path)", "cfg4": "Canary-1B"}
 
 
+def item_seconds(args, rank):
+    """Lengths of the length-bucketed workload of one rank: seeded U[min, max], whole 10 ms frames, ascending."""
+    rng = np.random.default_rng(4000 + rank)
+    return [float(v) for v in np.sort(np.round(rng.uniform(args.min_seconds, args.max_seconds, args.items), 2))]
+
+
 def workload_desc(args, cfg):
     dec = {"ctc": "CTC greedy", "tdt": "TDT greedy", "rnnt": "RNNT greedy",
            "aed": f"AED greedy ({cfg.aed_layers}-layer decoder, budget T+{cfg.aed_max_gen_delta})"}[cfg.decoder]
     return {"workload": f"{args.workload}: {SHAPES.get(args.workload, args.workload)}-shaped, {cfg.n_layers} layers d={cfg.d_model} "
                         f"ffn={cfg.ffn_dim}, {cfg.wtype.upper()} weights, {dec}, "
-                        f"{args.batch} x {args.seconds:g} s per GPU",
-            "batch_per_gpu": args.batch, "audio_seconds": args.seconds, "numerics": getattr(args, "mode", "strict"),
+                        + (f"{args.items} utterances per GPU, lengths U[{args.min_seconds:g}, {args.max_seconds:g}] s sorted into "
+                           f"batches of {args.batch}" if args.items else f"{args.batch} x {args.seconds:g} s per GPU"),
+            "batch_per_gpu": args.batch, "audio_seconds": args.seconds if not args.items else "per item, see workload",
+            "numerics": getattr(args, "mode", "strict"),
             "l2": "per-step working set (activations + weights, >1 GB) exceeds the 126 MB L2"}
 
 
@@ -215,7 +224,7 @@ def cpu_baseline(args, cfg, tensors, synth):
     rm = R.RefModel(os.path.join(d, "model.safetensors"), os.path.join(d, "mel_filters.safetensors"),
                     n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
                     max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), causal=int(cfg.causal))
-    audio = synth.synth_audio(args.seconds, seed=100)
+    audio = synth.synth_audio(args.seconds, seed=100 + args.sample_index)
     times = []
     for i in range(2):           # first pass warms the page cache / BLAS threads
         t0 = time.perf_counter()
@@ -234,7 +243,8 @@ def cpu_baseline(args, cfg, tensors, synth):
         times.append(time.perf_counter() - t0)
     rm.close()
     return {"value": args.seconds / min(times), "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
-            "sample": f"1 utterance x {args.seconds:g} s, best of 2 (the GPU step is {args.batch} of these)",
+            "sample": f"1 utterance x {args.seconds:g} s, best of 2 " +
+                      (f"(the median of the {args.items} items of a GPU step)" if args.items else f"(the GPU step is {args.batch} of these)"),
             "tokens": toks[0], "frames": toks[1]}
 
 
@@ -370,12 +380,24 @@ def main():
     ap.add_argument("--workload", default="cfg1")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--seconds", type=float, default=60.0)
+    ap.add_argument("--items", type=int, default=None,
+                    help="length-bucketed workload: utterances per GPU with lengths ~ U[--min-seconds, --max-seconds], sorted "
+                         "and cut into batches of --batch (default for cfg2: 256 items in batches of 64)")
+    ap.add_argument("--min-seconds", type=float, default=5.0)
+    ap.add_argument("--max-seconds", type=float, default=120.0)
     ap.add_argument("--streams", type=int, default=0, help="causal workloads: concurrent streams per GPU through the streaming step")
     ap.add_argument("--mode", default="strict", choices=["strict", "fast"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: only the resident-input timing")
     ap.add_argument("--blank-bias", type=float, default=None, help="bias of the blank logit of the synthetic transducer head")
     args = ap.parse_args()
+    if args.items is None:
+        args.items = 256 if args.workload == "cfg2" else 0
+        if args.items and args.batch == 16:
+            args.batch = 64
+    if args.items:
+        args.seconds = item_seconds(args, 0)[args.items // 2]          # the reference arm's sample: the median item
+    args.sample_index = args.items // 2 if args.items else 0
     if args.blank_bias is not None and args.workload in BLANK_BIAS:
         BLANK_BIAS[args.workload] = args.blank_bias
     rank = int(os.environ.get("RANK", "0"))
@@ -417,27 +439,45 @@ def main():
             dist.destroy_process_group()
         return
     # this rank's utterances: global item ids shard over ranks (weak scaling: batch per GPU fixed)
-    items = shard(args.batch * world, rank, world)
-    n = int(round(args.seconds * 16000))
-    pinned = torch.empty((len(items), n), dtype=torch.float32).pin_memory()
-    for i, it in enumerate(items):
-        pinned[i].copy_(torch.from_numpy(synth.synth_audio(args.seconds, seed=100 + it)))
-    audio = [pinned[i].numpy() for i in range(len(items))]
-    audio_s = args.seconds * len(items)
+    if args.items:
+        secs = item_seconds(args, rank)
+        seeds = [100 + rank * args.items + i for i in range(args.items)]
+    else:
+        items = shard(args.batch * world, rank, world)
+        secs, seeds = [args.seconds] * len(items), [100 + it for it in items]
+    lens = [int(round(v * 16000)) for v in secs]
+    pinned = torch.empty(sum(lens), dtype=torch.float32).pin_memory()
+    audio, off = [], 0
+    for v, sd, n in zip(secs, seeds, lens):
+        pinned[off:off + n].copy_(torch.from_numpy(synth.synth_audio(v, seed=sd)[:n]))
+        audio.append(pinned[off:off + n].numpy())
+        off += n
+    audio_s = sum(lens) / 16000.0
+    # one batch per step, or the sorted items cut into batches that a step runs one after the other
+    groups = [audio[i:i + args.batch] for i in range(0, len(audio), args.batch)]
     stream = torch.cuda.ExternalStream(model.stream())
 
     # ---- value: inputs resident in HBM
-    bh = model.batch_upload(audio)
+    bhs = [model.batch_upload(g) for g in groups]
     if dec_id == 2:
-        model.batch_set_aed(bh, AED_PROMPT, AED_EOS, cfg.aed_max_gen_delta)
+        for bh in bhs:
+            model.batch_set_aed(bh, AED_PROMPT, AED_EOS, cfg.aed_max_gen_delta)
+
+    def resident_step():
+        for bh in bhs:
+            model.batch_run(bh, dec_id)
 
     def public_call():
-        if dec_id == 2:
-            return [(t, [0] * len(t)) for t in model.transcribe_batch_aed(audio, AED_PROMPT, AED_EOS, cfg.aed_max_gen_delta)]
-        return model.transcribe_batch(audio, dec_id)
+        out = []
+        for g in groups:
+            if dec_id == 2:
+                out += [(t, [0] * len(t)) for t in model.transcribe_batch_aed(g, AED_PROMPT, AED_EOS, cfg.aed_max_gen_delta)]
+            else:
+                out += model.transcribe_batch(g, dec_id)
+        return out
 
     for _ in range(args.warmup):
-        model.batch_run(bh, dec_id)
+        resident_step()
     clocks = ClockSampler(local)
     barrier()
     if rank == 0:
@@ -448,7 +488,7 @@ def main():
     barrier()
     e0.record(stream)
     for _ in range(args.steps):
-        model.batch_run(bh, dec_id)
+        resident_step()
     e1.record(stream)
     e1.synchronize()
     barrier()
@@ -456,8 +496,10 @@ def main():
     prof = model.profile_end()
     ms = e0.elapsed_time(e1)
     clk = clocks.stop() if rank == 0 else None
-    resident_tokens = model.batch_fetch(bh, len(items))
-    model.batch_free(bh)
+    resident_tokens = []
+    for bh, g in zip(bhs, groups):
+        resident_tokens += model.batch_fetch(bh, len(g))
+        model.batch_free(bh)
 
     # ---- e2e: the public call with host (pinned) buffers, copies inside the timed region
     if args.skip_e2e:
@@ -530,8 +572,9 @@ def main():
             cb = cpu_baseline(args, cfg, tensors, synth)
             ref_t, ref_f = cb.pop("tokens", None), cb.pop("frames", None)
             if ref_t is not None:     # the reference decoded the same utterance as item 0 of this rank
-                line["parity"] = {"utterance": 0, "reference_tokens": len(ref_t), "distinct": len(set(ref_t)),
-                                  "tokens_identical": ref_t == res[0][0], "frames_identical": ref_f == res[0][1]}
+                u = args.sample_index
+                line["parity"] = {"utterance": u, "reference_tokens": len(ref_t), "distinct": len(set(ref_t)),
+                                  "tokens_identical": ref_t == res[u][0], "frames_identical": ref_f == res[u][1]}
             line["cpu_baseline"] = cb
         else:
             line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",

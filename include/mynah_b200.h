@@ -120,7 +120,7 @@ typedef struct {
     int n_durations;            /* TDT durations; 0 = RNNT */
     int durations[16];
     int strict;                 /* 1: 3-term fp16 split (f32-grade, default); 0: single fp16 pass */
-    int attn_impl;              /* 0 tiled tensor-core kernel (default), 1 plain kernel (cross-check) */
+    int attn_impl;              /* 0 tensor-core kernels (default: tcgen05 for full attention over 128-wide heads, else the warp-level tiled one), 1 plain kernel (cross-check), 2 warp-level tiled kernel */
     int aed_heads;              /* decoder.n_heads of an AED model (mynah_asr_aed_init's n_heads); layers, width,
                                  * vocabulary and max_seq are read off the tensors */
 } mynah_b200_config;

@@ -347,7 +347,8 @@ int attention_forward(const AttnArgs &a, int impl, cudaStream_t st) {
     dv.seg_off = a.seg_off; dv.seg_len = a.seg_len; dv.rk_off = a.rk_off;
     dv.d = a.d; dv.H = a.H; dv.left = a.left; dv.right = a.right;
     dv.scaling = 1.0f / sqrtf((float)dk);
-    if (impl == 0 && (dk == 64 || dk == 128) && (a.ldq % 2) == 0 && (a.d % 8) == 0) {
+    if (impl == 0 && attention_tc_eligible(a)) return attention_tc(a, st);
+    if ((impl == 0 || impl == 2) && (dk == 64 || dk == 128) && (a.ldq % 2) == 0 && (a.d % 8) == 0) {
         return dk == 64 ? launch_tiled<64>(dv, a.batch, a.max_len, st) : launch_tiled<128>(dv, a.batch, a.max_len, st);
     }
     if (dk % 32 != 0 || dk > 128) { set_error("attention: head dim %d unsupported", dk); return -1; }

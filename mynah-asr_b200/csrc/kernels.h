@@ -48,8 +48,15 @@ struct AttnArgs {
     const int *seg_off, *seg_len, *rk_off;   // device arrays [batch]
     int batch, max_len, d, H;
     int left, right;            // left < 0: full attention
+    long long rows = 0, rk_rows = 0;   // rows of k / v and of rk (bounds of the TMA descriptors); 0: unknown
+    int *status = nullptr;      // device status word for the bounded waits of the tcgen05 kernel
 };
-int attention_forward(const AttnArgs &a, int impl, cudaStream_t st);   // impl 0 = tiled tensor-core, 1 = plain
+// impl 0 = tensor cores (tcgen05 kernel for full attention over 128-wide heads, else the warp-level tiled
+// kernel), 1 = plain one-warp-per-query kernel, 2 = the warp-level tiled kernel
+int attention_forward(const AttnArgs &a, int impl, cudaStream_t st);
+// ---- attention_tc.cu
+bool attention_tc_eligible(const AttnArgs &a);
+int attention_tc(const AttnArgs &a, cudaStream_t st);
 
 // ---- subsampling.cu
 int conv_in_relu(const float *feats, const float *w, const float *b, float *out, int T, int F, int C, int To, int Fo,

@@ -262,6 +262,7 @@ int Model::encoder_layers(float *x, const std::vector<int> &lens, int left, int 
         at.bias_u = L.bias_u; at.bias_v = L.bias_v; at.ctx_f32 = nullptr; at.ctx_h = hC;
         at.seg_off = d_off; at.seg_len = d_len; at.rk_off = d_rk;
         at.batch = B; at.max_len = max_len; at.d = d; at.H = n_heads; at.left = left; at.right = right;
+        at.rows = M; at.rk_rows = rk_rows; at.status = status;
         { const int sp = prof_begin_span(PROF_ATTN);
           const int rc = attention_forward(at, cfg.attn_impl, stream);
           prof_end_span(sp);

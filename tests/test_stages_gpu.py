@@ -141,3 +141,34 @@ def test_fast_mode_within_tolerance(setup, gpu_pkg, synth):
     f = g["feats"][:int(g["valid"])]
     assert rel(fast.encoder_forward(f, raw=True), g["enc_raw"]) < 5e-3
     fast.close()
+
+
+def test_tcgen05_attention_long_segments(gpu_pkg, synth):
+    """Full attention over 128-wide heads runs on the tcgen05 kernel (128-query tiles, 64-key tiles, rk ring):
+    against the plain kernel, the warp-level tiled kernel and the oracle, over lengths that exercise one and
+    several query / key tiles, ragged last tiles and the ring wrap; and in a packed batch."""
+    cfg = synth.config("attn128", d_model=256, n_layers=1, n_heads=2, ffn_dim=256, n_mels=80, decoder="ctc", vocab=33,
+                       wtype="q8_0")
+    tensors = synth.make_model(cfg, seed=5)
+    tc = cases.device_model(gpu_pkg, synth, cfg, tensors)
+    plain = cases.device_model(gpu_pkg, synth, cfg, tensors, attn_impl=1)
+    tiled = cases.device_model(gpu_pkg, synth, cfg, tensors, attn_impl=2)
+    M = model_io.oracle_model(cfg, tensors)
+    rng = np.random.default_rng(11)
+    for T in (1, 5, 63, 64, 65, 128, 129, 200, 257, 400, 750):
+        x = rng.standard_normal((T, cfg.d_model)).astype(np.float32)
+        a = tc.encoder_layer(0, x)
+        assert np.all(np.isfinite(a))
+        assert rel(a, plain.encoder_layer(0, x)) < 1e-4, T
+        assert rel(a, tiled.encoder_layer(0, x)) < 1e-4, T
+        if T in (65, 257):
+            want = O.encoder_layer(M["layers"][0], x, O.pos_emb(T, cfg.d_model), cfg.n_heads, cfg.causal, -1, -1)
+            assert rel(a, want) < 2e-4, T
+    # packed batch: each item's bits equal the item alone (row stability through the new kernel)
+    feats = [rng.standard_normal((n, cfg.n_mels)).astype(np.float32) for n in (1100, 40, 2500)]
+    outs = tc.encoder_forward_batch(feats)
+    for f, o in zip(feats, outs):
+        assert np.array_equal(o, tc.encoder_forward(f))
+        assert rel(o, plain.encoder_forward(f)) < 1e-4
+    for m in (tc, plain, tiled):
+        m.close()
