@@ -6,9 +6,10 @@
 // One CTA owns 128 queries of one (segment, head) and walks the keys in tiles of 64.
 //   * Tensor memory (all 512 columns): the two query operands Qu = q + bias_u and Qv = q + bias_v as
 //     fp16 (the A operand is read from tensor memory, 64 columns each), the content scores S (64), the
-//     position band BD (192) and the context accumulator O (128). The probabilities P (fp16) overwrite S.
-//   * Shared memory: K and V tiles (two stages), a ring of four 64-row chunks of rk, all placed by TMA
-//     with the 128-byte swizzle, and a 48 KB buffer in which the band's skew is undone.
+//     position band BD (192) and the context accumulator O (128).
+//   * Shared memory: K and V tiles (two stages each), a ring of four 64-row chunks of rk, all placed by
+//     TMA with the 128-byte swizzle; the probabilities P as fp16 in the same swizzled layout (the A operand
+//     of P.V); and a 48 KB buffer in which the band's skew is undone.
 //   * Position term: the tile needs bd[t, T-1+j-t], i.e. for query row r and key column c of the tile
 //     the band column c - r + 127. The band of 128 rows x 64 keys spans 191 positions = three rk chunks;
 //     it is one or two tcgen05.mma per k-step (the ring wraps), 128 x 192. A softmax warp copies the 96
@@ -18,21 +19,30 @@
 //     accumulator is rescaled only when the maximum has grown by more than 2^8 (the stale reference
 //     cancels in the final division), P rounded to fp16 as in the warp-level kernel.
 //   * V is the B operand of P.V in its natural [key, dk] layout (MN-major descriptor).
-// Warps 0-3: softmax / epilogue; warp 4 (one thread): TMA producer; warp 5 (one thread): MMA issuer.
+//   * Pipeline: as soon as the softmax warps hold S(i) and BD(i) in registers / shared memory the issuers
+//     score tile i+1 under the exponentials of tile i; P.V(i) follows when P(i) is in shared memory.
+// Warps 0-3: softmax / epilogue; warp 4 (one thread): TMA producer; warps 5 and 6 (one thread each): MMA issuers
+// (content scores and P.V; position band) — one thread gets a tcgen05.mma out only every 45-90 cycles.
 // Every mbarrier wait is bounded; a wait that runs out sets the status word and the CTA unwinds.
 #include "kernels.h"
 
 namespace mb {
 
 static constexpr int TA_Q = 128, TA_K = 64, TA_DK = 128;
-static constexpr int TA_THREADS = 192;
+// softmax warps per quadrant of 32 query rows: with 2, each takes half of a tile's keys and the pair agrees on
+// the row maximum through shared memory (measured slower on the 16 x 60 s workload: 5.2 against 4.8 ms per step)
+static constexpr int TA_HALVES = 1;
+static constexpr int TA_SM_WARPS = 4 * TA_HALVES;            // softmax warps: quadrant = warp % 4, key half = warp / 4
+static constexpr int TA_W_TMA = TA_SM_WARPS, TA_W_MMA = TA_SM_WARPS + 1, TA_W_BD = TA_SM_WARPS + 2;
+static constexpr int TA_THREADS = (TA_SM_WARPS + 3) * 32;
 static constexpr int TA_COL_QU = 0, TA_COL_QV = 64, TA_COL_S = 128, TA_COL_BD = 192, TA_COL_O = 384, TA_TMEM = 512;
 static constexpr int TA_HALF = TA_K * 128;                 // one 64-row x 64-column fp16 box: 8 KB
-static constexpr int TA_KV_STAGE = 4 * TA_HALF;            // K halves 0,1 then V halves 0,1
+static constexpr int TA_KV_STAGE = 2 * TA_HALF;            // one K (or V) tile: dk halves 0, 1
 static constexpr int TA_RK_SLOTS = 4;
 static constexpr int TA_RK_PLANE = TA_RK_SLOTS * TA_HALF;  // one dk half of the ring: 32 KB
-static constexpr int TA_SKEW_COLS = 96;
-static constexpr int TA_SMEM = 2 * TA_KV_STAGE + 2 * TA_RK_PLANE + 4 * TA_SKEW_COLS * 32 * 4 + 256 + 1024;
+static constexpr int TA_SKEW_COLS = TA_K / TA_HALVES + 32;  // band columns one softmax warp needs: its keys + 31 rows of skew
+static constexpr int TA_P_BYTES = TA_Q * TA_K * 2;         // 16 KB
+static constexpr int TA_SMEM = 4 * TA_KV_STAGE + 2 * TA_RK_PLANE + TA_P_BYTES + TA_SM_WARPS * TA_SKEW_COLS * 32 * 4 + 3 * TA_Q * 4 + 256 + 1024;
 
 struct AttnTcDev {
     const float *q;
@@ -74,6 +84,11 @@ __device__ __forceinline__ void ta_st32(uint32_t taddr, const uint32_t *r) {
         : "memory");
 }
 __device__ __forceinline__ void ta_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float ta_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t ta_pack(float x, float y) {
     __half2 h = __floats2half2_rn(x, y);
     return *reinterpret_cast<uint32_t *>(&h);
@@ -98,18 +113,25 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     if (t0 >= len) return;                                   // the whole CTA leaves before any barrier exists
     extern __shared__ uint8_t ta_smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(ta_smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *kv = smem;                                      // 2 stages x 32 KB
-    uint8_t *rkr = kv + 2 * TA_KV_STAGE;                     // [dk half][slot][64 rows][128 B]
-    float *skew = reinterpret_cast<float *>(rkr + 2 * TA_RK_PLANE);          // [warp][96][32]
-    uint64_t *kv_full = reinterpret_cast<uint64_t *>(skew + 4 * TA_SKEW_COLS * 32);
-    uint64_t *kv_empty = kv_full + 2;
-    uint64_t *rk_full = kv_empty + 2;
+    uint8_t *kst = smem;                                     // K: 2 stages x (2 dk halves x 8 KB)
+    uint8_t *vst = kst + 2 * TA_KV_STAGE;                    // V: the same
+    uint8_t *rkr = vst + 2 * TA_KV_STAGE;                    // [dk half][slot][64 rows][128 B]
+    uint8_t *pst = rkr + 2 * TA_RK_PLANE;                    // P: 128 rows x 64 keys fp16, 128-byte swizzle
+    float *skew = reinterpret_cast<float *>(pst + TA_P_BYTES);               // [warp][64][32]
+    float *xmax = skew + TA_SM_WARPS * TA_SKEW_COLS * 32;                    // [tile parity][row]: tile maximum of key half 1
+    float *xsum = xmax + 2 * TA_Q;                                           // [row]: row sum of key half 1
+    uint64_t *k_full = reinterpret_cast<uint64_t *>(xsum + TA_Q);
+    uint64_t *k_empty = k_full + 2;
+    uint64_t *v_full = k_empty + 2;
+    uint64_t *v_empty = v_full + 2;
+    uint64_t *rk_full = v_empty + 2;
     uint64_t *rk_empty = rk_full + TA_RK_SLOTS;
     uint64_t *q_full = rk_empty + TA_RK_SLOTS;
     uint64_t *s_full = q_full + 1;
-    uint64_t *p_full = s_full + 1;
-    uint64_t *o_full = p_full + 1;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_full + 1);
+    uint64_t *sbd_free = s_full + 1;
+    uint64_t *p_full = sbd_free + 1;
+    uint64_t *pv_done = p_full + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pv_done + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int off = a.seg_off[b], ho = h * TA_DK;
@@ -119,31 +141,29 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
 
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmR);
-        for (int i = 0; i < 2; i++) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+        for (int i = 0; i < 2; i++) { mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1); mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1); }
         for (int i = 0; i < TA_RK_SLOTS; i++) { mbar_init(&rk_full[i], 1); mbar_init(&rk_empty[i], 1); }
-        mbar_init(q_full, 4); mbar_init(s_full, 1); mbar_init(p_full, 4); mbar_init(o_full, 1);
+        mbar_init(q_full, TA_SM_WARPS); mbar_init(s_full, 2); mbar_init(sbd_free, TA_SM_WARPS); mbar_init(p_full, TA_SM_WARPS); mbar_init(pv_done, 1);
         mbar_fence_init();
     }
-    if (warp == 5) { tc_alloc(tmem_slot, TA_TMEM); tc_relinquish(); }
+    if (warp == TA_W_MMA) { tc_alloc(tmem_slot, TA_TMEM); tc_relinquish(); }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 4) {
+    if (warp == TA_W_TMA) {
         if (lane == 0) {
             // ------------------------------------------------------------------ TMA producer
             bool ok = true;
             int loaded = 0;                                  // rk chunks requested so far
             for (int i = 0; i < nkt && ok; i++) {
                 const int s = i & 1;
-                if (i >= 2 && !mbar_wait(&kv_empty[s], (uint32_t)(((i >> 1) & 1) ^ 1))) { ok = false; break; }
-                uint8_t *st = kv + s * TA_KV_STAGE;
-                mbar_expect_tx(&kv_full[s], TA_KV_STAGE);
-                tma_load_2d(st, &tmK, ho, off + i * TA_K, &kv_full[s]);
-                tma_load_2d(st + TA_HALF, &tmK, ho + 64, off + i * TA_K, &kv_full[s]);
-                tma_load_2d(st + 2 * TA_HALF, &tmV, ho, off + i * TA_K, &kv_full[s]);
-                tma_load_2d(st + 3 * TA_HALF, &tmV, ho + 64, off + i * TA_K, &kv_full[s]);
+                const uint32_t eph = (uint32_t)(((i >> 1) & 1) ^ 1);
+                if (i >= 2 && !mbar_wait(&k_empty[s], eph)) { ok = false; break; }
+                mbar_expect_tx(&k_full[s], TA_KV_STAGE);
+                tma_load_2d(kst + s * TA_KV_STAGE, &tmK, ho, off + i * TA_K, &k_full[s]);
+                tma_load_2d(kst + s * TA_KV_STAGE + TA_HALF, &tmK, ho + 64, off + i * TA_K, &k_full[s]);
                 // rk chunks i, i+1, i+2 cover the band of key tile i; chunk c lives in slot c % 4
                 for (; loaded <= i + 2 && ok; loaded++) {
                     const int c = loaded, sl = c & (TA_RK_SLOTS - 1);
@@ -152,75 +172,112 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
                     tma_load_2d(rkr + sl * TA_HALF, &tmR, ho, rk0 + pbase + c * TA_K, &rk_full[sl]);
                     tma_load_2d(rkr + TA_RK_PLANE + sl * TA_HALF, &tmR, ho + 64, rk0 + pbase + c * TA_K, &rk_full[sl]);
                 }
+                if (!ok) break;
+                if (i >= 2 && !mbar_wait(&v_empty[s], eph)) { ok = false; break; }
+                mbar_expect_tx(&v_full[s], TA_KV_STAGE);
+                tma_load_2d(vst + s * TA_KV_STAGE, &tmV, ho, off + i * TA_K, &v_full[s]);
+                tma_load_2d(vst + s * TA_KV_STAGE + TA_HALF, &tmV, ho + 64, off + i * TA_K, &v_full[s]);
             }
             if (!ok) atomicExch(a.status, ST_TIMEOUT_PRODUCER);
         }
-    } else if (warp == 5) {
+    } else if (warp == TA_W_MMA) {
         if (lane == 0) {
-            // ------------------------------------------------------------------ MMA issuer
+            // ------------------------------------------------------------------ MMA issuer: content scores and P.V
             constexpr uint32_t idesc_s = umma_idesc_f16(TA_Q, TA_K);
             constexpr uint32_t idesc_pv = umma_idesc_f16(TA_Q, TA_DK) | (1u << 16);      // B operand MN-major
+            const uint64_t kdesc0 = umma_desc_sw128(smem_u32(kst));
+            const uint64_t pdesc0 = umma_desc_sw128(smem_u32(pst)), vdesc0 = ta_desc_mn(smem_u32(vst), TA_HALF);
             bool ok = mbar_wait(q_full, 0);
+            // S(i) = Qu K^T
+            auto issue_s = [&](int i) -> bool {
+                const int s = i & 1;
+                if (!mbar_wait(&k_full[s], (uint32_t)((i >> 1) & 1))) return false;
+                tc_fence_after();
+                const uint64_t kd = kdesc0 + (uint64_t)((s * TA_KV_STAGE) >> 4);
+#pragma unroll
+                for (int kk = 0; kk < TA_DK / 16; kk++)
+                    ta_mma_ts(tmem_base + TA_COL_S, tmem_base + TA_COL_QU + 8 * kk, kd + (uint64_t)(((kk >> 2) * TA_HALF + (kk & 3) * 32) >> 4),
+                              idesc_s, kk != 0);
+                tc_commit(s_full);
+                tc_commit(&k_empty[s]);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
             for (int i = 0; i < nkt && ok; i++) {
                 const int s = i & 1;
-                if (!mbar_wait(&kv_full[s], (uint32_t)((i >> 1) & 1))) { ok = false; break; }
+                if (i + 1 < nkt) {
+                    // the softmax warps hold S(i) and BD(i) in registers / shared memory: score the next tile under them
+                    if (!mbar_wait(sbd_free, (uint32_t)(i & 1))) { ok = false; break; }
+                    tc_fence_after();
+                    if (!issue_s(i + 1)) { ok = false; break; }
+                }
+                // O += P V
+                if (!mbar_wait(p_full, (uint32_t)(i & 1)) || !mbar_wait(&v_full[s], (uint32_t)((i >> 1) & 1))) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t vd = vdesc0 + (uint64_t)((s * TA_KV_STAGE) >> 4);
+#pragma unroll
+                for (int kk = 0; kk < TA_K / 16; kk++)
+                    tc_mma_f16(tmem_base + TA_COL_O, pdesc0 + (uint64_t)((kk * 32) >> 4), vd + (uint64_t)((kk * 2048) >> 4), idesc_pv, (i | kk) != 0);
+                tc_commit(pv_done);
+                tc_commit(&v_empty[s]);
+            }
+            if (!ok) atomicExch(a.status, ST_TIMEOUT_MMA);
+        }
+    } else if (warp == TA_W_BD) {
+        if (lane == 0) {
+            // ------------------------------------------------------------------ MMA issuer: position band
+            // BD(i) = Qv RK^T over the chunks i, i+1, i+2 (ring slots s0, s0+1, .., wrapping after slot 3). A second
+            // issuing thread, because one thread gets a tcgen05.mma out only every 45-90 cycles
+            const uint64_t rdesc0 = umma_desc_sw128(smem_u32(rkr));
+            bool ok = mbar_wait(q_full, 0);
+            for (int i = 0; i < nkt && ok; i++) {
+                if (i > 0 && !mbar_wait(sbd_free, (uint32_t)((i - 1) & 1))) { ok = false; break; }
                 for (int c = (i == 0 ? 0 : i + 2); c <= i + 2 && ok; c++)
                     ok = mbar_wait(&rk_full[c & (TA_RK_SLOTS - 1)], (uint32_t)((c >> 2) & 1));
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t ks = smem_u32(kv + s * TA_KV_STAGE), vs = ks + 2 * TA_HALF, rs = smem_u32(rkr);
-                // S = Qu K^T
-#pragma unroll
-                for (int kk = 0; kk < TA_DK / 16; kk++)
-                    ta_mma_ts(tmem_base + TA_COL_S, tmem_base + TA_COL_QU + 8 * kk,
-                              umma_desc_sw128(ks + (kk >> 2) * TA_HALF + (kk & 3) * 32), idesc_s, kk != 0);
-                // BD = Qv RK^T over the chunks i, i+1, i+2: the ring slots s0, s0+1, .. wrap after slot 3
                 const int s0 = i & (TA_RK_SLOTS - 1);
                 const int n1 = TA_RK_SLOTS - s0 < 3 ? TA_RK_SLOTS - s0 : 3, n2 = 3 - n1;
                 const uint32_t id1 = umma_idesc_f16(TA_Q, 64 * n1), id2 = umma_idesc_f16(TA_Q, n2 > 0 ? 64 * n2 : 64);
+                const uint64_t rd1 = rdesc0 + (uint64_t)((s0 * TA_HALF) >> 4);
 #pragma unroll
                 for (int kk = 0; kk < TA_DK / 16; kk++) {
-                    const uint32_t ko = (kk >> 2) * TA_RK_PLANE + (kk & 3) * 32;
-                    ta_mma_ts(tmem_base + TA_COL_BD, tmem_base + TA_COL_QV + 8 * kk, umma_desc_sw128(rs + ko + s0 * TA_HALF), id1, kk != 0);
-                    if (n2 > 0)
-                        ta_mma_ts(tmem_base + TA_COL_BD + 64 * n1, tmem_base + TA_COL_QV + 8 * kk, umma_desc_sw128(rs + ko), id2, kk != 0);
+                    const uint64_t ko = (uint64_t)(((kk >> 2) * TA_RK_PLANE + (kk & 3) * 32) >> 4);
+                    ta_mma_ts(tmem_base + TA_COL_BD, tmem_base + TA_COL_QV + 8 * kk, rd1 + ko, id1, kk != 0);
+                    if (n2 > 0) ta_mma_ts(tmem_base + TA_COL_BD + 64 * n1, tmem_base + TA_COL_QV + 8 * kk, rdesc0 + ko, id2, kk != 0);
                 }
                 tc_commit(s_full);
                 tc_commit(&rk_empty[s0]);                    // chunk i is not used after key tile i
-                // O += P V once the softmax warps have written P over S
-                if (!mbar_wait(p_full, (uint32_t)(i & 1))) { ok = false; break; }
-                tc_fence_after();
-#pragma unroll
-                for (int kk = 0; kk < TA_K / 16; kk++)
-                    ta_mma_ts(tmem_base + TA_COL_O, tmem_base + TA_COL_S + 8 * kk, ta_desc_mn(vs + kk * 2048, TA_HALF), idesc_pv,
-                              (i | kk) != 0);
-                tc_commit(&kv_empty[s]);
             }
-            tc_commit(o_full);
             if (!ok) atomicExch(a.status, ST_TIMEOUT_MMA);
         }
     } else {
         // ---------------------------------------------------------------------- softmax warps
-        const int r = warp * 32 + lane, t = t0 + r;
+        // Two warps share a quadrant of 32 query rows (tensor-memory lanes): warp qd handles keys 0-31 of
+        // every tile, warp qd + 4 keys 32-63. They agree on the tile maximum through shared memory.
+        const int qd = warp & 3, hf = warp >> 2;
+        const int r = qd * 32 + lane, t = t0 + r;
         const bool valid = t < len;
-        const uint32_t trow = tmem_base + ((uint32_t)(warp * 32) << 16);
-        // ---- Qu, Qv into tensor memory: column c holds elements 2c, 2c+1 of the row as fp16
+        const uint32_t trow = tmem_base + ((uint32_t)(qd * 32) << 16);
+        const int pair_bar = 1 + qd;                         // named barrier of the two warps of a quadrant
+        // ---- Qu (key half 0) / Qv (key half 1) into tensor memory: column c holds elements 2c, 2c+1 as fp16
         {
             const float *qrow = a.q + (size_t)(off + (valid ? t : 0)) * a.ldq + ho;
 #pragma unroll 1
-            for (int c4 = 0; c4 < TA_DK / 32; c4++) {
-                uint32_t ru[16], rv[16];
+            for (int w2 = hf; w2 < 2; w2 += TA_HALVES) {     // operand 0: Qu, 1: Qv
+                const float *bias = (w2 ? a.bias_v : a.bias_u) + ho;
+#pragma unroll 1
+                for (int c4 = 0; c4 < TA_DK / 32; c4++) {
+                    uint32_t ru[16];
 #pragma unroll
-                for (int j = 0; j < 8; j++) {
-                    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (valid) x = *reinterpret_cast<const float4 *>(qrow + c4 * 32 + 4 * j);
-                    const float4 u = *reinterpret_cast<const float4 *>(a.bias_u + ho + c4 * 32 + 4 * j);
-                    const float4 v = *reinterpret_cast<const float4 *>(a.bias_v + ho + c4 * 32 + 4 * j);
-                    ru[2 * j] = ta_pack(x.x + u.x, x.y + u.y); ru[2 * j + 1] = ta_pack(x.z + u.z, x.w + u.w);
-                    rv[2 * j] = ta_pack(x.x + v.x, x.y + v.y); rv[2 * j + 1] = ta_pack(x.z + v.z, x.w + v.w);
+                    for (int j = 0; j < 8; j++) {
+                        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (valid) x = *reinterpret_cast<const float4 *>(qrow + c4 * 32 + 4 * j);
+                        const float4 u = *reinterpret_cast<const float4 *>(bias + c4 * 32 + 4 * j);
+                        ru[2 * j] = ta_pack(x.x + u.x, x.y + u.y); ru[2 * j + 1] = ta_pack(x.z + u.z, x.w + u.w);
+                    }
+                    ta_st16(trow + (w2 ? TA_COL_QV : TA_COL_QU) + 16 * c4, ru);
                 }
-                ta_st16(trow + TA_COL_QU + 16 * c4, ru);
-                ta_st16(trow + TA_COL_QV + 16 * c4, rv);
             }
             ta_wait_st();
             tc_fence_before();
@@ -228,82 +285,118 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
             if (lane == 0) mbar_arrive(q_full);
         }
         float *skw = skew + warp * TA_SKEW_COLS * 32;
-        const int cbase = 96 - 32 * warp;                    // first band column this warp's rows touch
+        uint8_t *prow = pst + r * 128;                       // this row of P: eight 16-byte pieces at (piece ^ (r & 7))
+        constexpr int NC = TA_K / TA_HALVES;                 // keys per warp and tile
+        constexpr int OC = TA_DK / TA_HALVES;                // context columns per warp
+        const int cbase = 96 - 32 * qd + NC * hf;            // first band column this warp's rows and keys touch
         float m_ref = -3.0e38f, l = 0.f;
         bool ok = true;
+        // A wait that runs out clears `ok`: the warp then skips the work but still meets its partner at the
+        // pair barriers, so neither of the two can be left waiting at one.
         for (int i = 0; i < nkt; i++) {
-            if (!__all_sync(0xffffffffu, mbar_wait(s_full, (uint32_t)(i & 1)))) {
+            if (ok && !__all_sync(0xffffffffu, mbar_wait(s_full, (uint32_t)(i & 1)))) {
                 ok = false;
                 if (lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE);
-                break;
             }
             tc_fence_after();
-            // ---- band -> shared memory as [column][lane]
-#pragma unroll 1
-            for (int q3 = 0; q3 < 3; q3++) {
-                float v[32];
-                tc_ld32(trow + TA_COL_BD + cbase + 32 * q3, v);
+            // ---- band -> shared memory as [column][lane]; the content scores are fetched under the copy
+            float x[NC];
+            float mt = -3.0e38f;
+            if (ok) {
+            {
+                float v[TA_SKEW_COLS];
+#pragma unroll
+                for (int q3 = 0; q3 < TA_SKEW_COLS / 32; q3++) tc_ld32(trow + TA_COL_BD + cbase + 32 * q3, v + 32 * q3);
+#pragma unroll
+                for (int q3 = 0; q3 < NC / 32; q3++) tc_ld32(trow + TA_COL_S + NC * hf + 32 * q3, x + 32 * q3);
                 tc_wait_ld();
 #pragma unroll
-                for (int e = 0; e < 32; e++) skw[(32 * q3 + e) * 32 + lane] = v[e];
+                for (int e = 0; e < TA_SKEW_COLS; e++) skw[e * 32 + lane] = v[e];
             }
+            tc_fence_before();
             __syncwarp();
-            // ---- scores of this row against the 64 keys of the tile
-            float x[TA_K];
-            tc_ld32(trow + TA_COL_S, x);
-            tc_ld32(trow + TA_COL_S + 32, x + 32);
-            tc_wait_ld();
-            const int j0 = i * TA_K;
-            float mt = -3.0e38f;
+            if (lane == 0) mbar_arrive(sbd_free);            // S and BD may be overwritten by the next tile's MMAs
+            const int j0 = i * TA_K + NC * hf;
+            const float *sk = skw + (31 - lane) * 32 + lane;
 #pragma unroll
-            for (int c = 0; c < TA_K; c++) {
-                const float bd = skw[(c + 31 - lane) * 32 + lane];
-                x[c] = (x[c] + bd) * a.scale2;
-                if (j0 + c >= len) x[c] = -3.0e38f;
-                mt = fmaxf(mt, x[c]);
+            for (int c = 0; c < NC; c++) x[c] += sk[c * 32];          // unscaled; the scale is folded into the exponent below
+            if (j0 + NC > len) {                             // ragged last tile: keys past the segment
+#pragma unroll
+                for (int c = 0; c < NC; c++)
+                    if (j0 + c >= len) x[c] = -3.0e38f;
             }
-            __syncwarp();                                    // the skew buffer may be overwritten by the next tile
+#pragma unroll
+            for (int c = 0; c < NC; c += 4) mt = fmaxf(fmaxf(mt, fmaxf(x[c], x[c + 1])), fmaxf(x[c + 2], x[c + 3]));
+            }
+            // the two key halves agree on the tile maximum of the row (buffers alternate by tile parity)
+            if (TA_HALVES == 2) {
+                float *xm = xmax + (i & 1) * TA_Q;
+                if (hf) xm[r] = mt;
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+                if (!hf) { const float o = xm[r]; xm[r] = mt; mt = fmaxf(mt, o); }
+                asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+                if (hf) mt = fmaxf(mt, xm[r]);
+            }
+            // P(i-1) has to be consumed, and O at rest, before either is touched
+            if (ok && i > 0 && !__all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)((i - 1) & 1)))) {
+                ok = false;
+                if (lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE);
+            }
+            if (!ok) continue;
+            tc_fence_after();
             // ---- running maximum: move the reference only when it lags by more than 8 (in log2 units)
+            mt *= a.scale2;
             const bool grow = mt > m_ref + 8.f;
             if (__any_sync(0xffffffffu, grow)) {
-                const float alpha = grow ? exp2f(m_ref - mt) : 1.f;
+                const float alpha = grow ? ta_ex2(m_ref - mt) : 1.f;
                 if (grow) m_ref = mt;
                 l *= alpha;
-                if (i > 0) {
+                if (i > 0) {                                 // this warp's half of the accumulator columns
 #pragma unroll 1
-                    for (int c4 = 0; c4 < TA_DK / 32; c4++) {
+                    for (int c4 = 0; c4 < OC / 32; c4++) {
                         float o[32];
-                        tc_ld32(trow + TA_COL_O + 32 * c4, o);
+                        tc_ld32(trow + TA_COL_O + OC * hf + 32 * c4, o);
                         tc_wait_ld();
 #pragma unroll
                         for (int e = 0; e < 32; e++) o[e] *= alpha;
-                        ta_st32(trow + TA_COL_O + 32 * c4, reinterpret_cast<const uint32_t *>(o));
+                        ta_st32(trow + TA_COL_O + OC * hf + 32 * c4, reinterpret_cast<const uint32_t *>(o));
                     }
+                    ta_wait_st();
                 }
             }
-            uint32_t pp[TA_K / 2];
 #pragma unroll
-            for (int c = 0; c < TA_K; c += 2) {
-                const float p0 = exp2f(x[c] - m_ref), p1 = exp2f(x[c + 1] - m_ref);
-                l += p0 + p1;
-                pp[c >> 1] = ta_pack(p0, p1);
+            for (int c8 = 0; c8 < NC / 8; c8++) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float p0 = ta_ex2(fmaf(x[c8 * 8 + 2 * e], a.scale2, -m_ref)), p1 = ta_ex2(fmaf(x[c8 * 8 + 2 * e + 1], a.scale2, -m_ref));
+                    l += p0 + p1;
+                    w[e] = ta_pack(p0, p1);
+                }
+                *reinterpret_cast<uint4 *>(prow + (((c8 + (NC / 8) * hf) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            ta_st32(trow + TA_COL_S, pp);
-            ta_wait_st();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores -> visible to the tensor core
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
         }
-        // ---- normalise and store
-        if (ok && !__all_sync(0xffffffffu, mbar_wait(o_full, 0))) { ok = false; if (lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE); }
+        // ---- normalise and store: each warp its half of the context columns
+        if (TA_HALVES == 2) {
+            if (hf) xsum[r] = l;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            if (!hf) { const float o = xsum[r]; xsum[r] = l; l += o; }
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            if (hf) l += xsum[r];
+        }
+        if (ok && !__all_sync(0xffffffffu, mbar_wait(pv_done, (uint32_t)((nkt - 1) & 1)))) { ok = false; if (lane == 0) atomicExch(a.status, ST_TIMEOUT_EPILOGUE); }
         if (ok) {
             tc_fence_after();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
-            const size_t idx0 = (size_t)(off + t) * a.d + ho;
+            const size_t idx0 = (size_t)(off + t) * a.d + ho + OC * hf;
 #pragma unroll 1
-            for (int c4 = 0; c4 < TA_DK / 32; c4++) {
+            for (int c4 = 0; c4 < OC / 32; c4++) {
                 float o[32];
-                tc_ld32(trow + TA_COL_O + 32 * c4, o);
+                tc_ld32(trow + TA_COL_O + OC * hf + 32 * c4, o);
                 tc_wait_ld();
                 if (!valid) continue;
 #pragma unroll
@@ -328,7 +421,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ 
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tc_dealloc(tmem_base, TA_TMEM);
+    if (warp == TA_W_MMA) tc_dealloc(tmem_base, TA_TMEM);
 }
 
 // ------------------------------------------------------------------ host side
