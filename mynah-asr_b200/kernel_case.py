@@ -2,11 +2,15 @@
 
     python mynah-asr_b200/kernel_case.py gemm  --T 16384 --n 4096 --k 1024 [--fast] [--iters 3]
     python mynah-asr_b200/kernel_case.py qgemv --T 1 --n 65536 --k 4096 --fmt q4_0 [--iters 3]
+    python mynah-asr_b200/kernel_case.py attention --T 750 --batch 16 [--heads 8] [--impl 0] [--iters 3]
 
 gemm : the tcgen05 contraction on resident fp16 planes (large T).
 qgemv: the weight-streaming small-T kernel on the stored blocks; sizes above the 126 MB L2
        make the figure an HBM figure. Prints the CUDA-event time per launch, the algorithmic
        bytes / flops and the achieved rate.
+attention: the rel-pos self-attention kernel inside a one-layer encoder (d = 128 x heads) over a packed batch of
+       `batch` segments of T frames; the time is that of the attention launches alone (device events around
+       them), the flops are 6 T^2 d per segment: content scores, the needed half of the position band, P.V.
 """
 from __future__ import annotations
 
@@ -47,9 +51,33 @@ def random_blocks(fmt: str, n: int, k: int, rng) -> np.ndarray:
     return raw.reshape(-1)
 
 
+def attention_case(pkg, a, rng):
+    import mynah_asr_b200.synth as synth
+    T = a.T or 750
+    d = 128 * a.heads
+    cfg = synth.config("attention_case", d_model=d, n_layers=1, n_heads=a.heads, ffn_dim=256, n_mels=80, decoder="ctc",
+                       vocab=33, wtype="q8_0")
+    m = pkg.Model(synth.make_model(cfg, seed=1), n_mels=cfg.n_mels, mel_fb=synth.mel_filterbank(cfg.n_mels),
+                  window=synth.hann_window(), causal=0, normalize=True, blank=cfg.vocab - 1, attn_impl=a.impl)
+    feats = [rng.standard_normal((8 * T - 7, cfg.n_mels)).astype(np.float32) for _ in range(a.batch)]
+    frames = m.encoder_forward_batch(feats)[0].shape[0]           # warm-up
+    m.profile_begin()
+    for _ in range(a.iters):
+        m.encoder_forward_batch(feats)
+    prof = m.profile_end()["attention"]
+    ms = prof["ms"] / max(prof["launches"], 1)
+    flops = 6.0 * frames * frames * d * a.batch
+    print(json.dumps({"kernel": "attention", "impl": a.impl, "T": frames, "batch": a.batch, "heads": a.heads, "d": d,
+                      "ms": ms, "flops": flops, "tflops": flops / (ms * 1e-3) / 1e12}))
+    m.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "qgemv"])
+    ap.add_argument("kernel", choices=["gemm", "qgemv", "attention"])
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--heads", type=int, default=8)
+    ap.add_argument("--impl", type=int, default=0, help="attention: 0 default (tcgen05 where eligible), 2 warp-level tiled kernel")
     ap.add_argument("--T", type=int, default=0)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=1024)
@@ -61,6 +89,8 @@ def main():
     pkg = _pkg()
     assert pkg.available(), "no sm_100 device"
     rng = np.random.default_rng(0)
+    if a.kernel == "attention":
+        return attention_case(pkg, a, rng)
     T = a.T or (16384 if a.kernel == "gemm" else 1)
     fmt = {"f32": pkg.F32, "q8_0": pkg.GGML_Q8_0, "q4_0": pkg.GGML_Q4_0, "q4_k": pkg.GGML_Q4_K, "q6_k": pkg.GGML_Q6_K}[a.fmt]
     q = pkg.QMat(fmt, random_blocks(a.fmt, a.n, a.k, rng), a.n, a.k)
