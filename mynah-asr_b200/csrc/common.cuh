@@ -67,7 +67,11 @@ __device__ __forceinline__ float sigmoid_stable(float x) {
     const float e = expf(x);
     return e / (1.0f + e);
 }
-__device__ __forceinline__ float silu_f(float x) { return x * sigmoid_stable(x); }
+// The same function for the bulk element-wise passes (GLU, SiLU after the conv norm; the contraction epilogue
+// uses the same form): one ex2 and one reciprocal. exp(-x) = inf gives exactly 0, so no NaN for finite x;
+// relative error ~3e-7.
+__device__ __forceinline__ float sigmoid_fast(float x) { return __frcp_rn(1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x * sigmoid_fast(x); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -120,59 +120,79 @@ int layer_norm(const float *x, const float *w, const float *b, float *out_f32, H
 // width k along time with zero padding at the segment edges (causal: k-1 on the
 // left; symmetric: (k-1)/2 each side) — src/encoder.c:421-444. A block covers 128 channels
 // x a time tile of TT rows; the tile plus its k-1 halo is staged in shared memory so every GLU
-// value is computed once. Four thread groups (threadIdx.y) share the staging and split the
-// output rows, which keeps 2048 threads resident per SM for this latency-bound pass.
+// value is computed once. A thread owns four adjacent channels (16-byte loads, 8-byte plane
+// stores) and four consecutive output rows, whose windows it slides through registers.
 static constexpr int DW_TT = 64;
 static constexpr int DW_CH = 128;
-static constexpr int DW_TG = 4;
+static constexpr int DW_TY = 16;                  // thread rows per block: DW_TT / DW_TY outputs each
+static constexpr int DW_RPT = DW_TT / DW_TY;      // 4
 static constexpr int DW_KMAX = 32;
 
 template <int KW>      // KW > 0: compile-time kernel width; 0: runtime width up to DW_KMAX
-__global__ void __launch_bounds__(DW_CH * DW_TG)
+__global__ void __launch_bounds__(32 * DW_TY)
 glu_dw_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, const float *__restrict__ dw_b,
               const float *__restrict__ scale, const float *__restrict__ shift, float *__restrict__ out,
               __half *__restrict__ hi, __half *__restrict__ lo, const int *__restrict__ seg_off,
               const int *__restrict__ seg_len, int d, int k, int pad_left) {
-    __shared__ float g[(DW_TT + DW_KMAX - 1) * DW_CH];
+    __shared__ float4 g[(DW_TT + DW_KMAX - 1) * (DW_CH / 4)];
     const int b = blockIdx.z;
     const int len = seg_len[b], off = seg_off[b];
     const int t0 = blockIdx.y * DW_TT;
     if (t0 >= len) return;
-    const int c = blockIdx.x * DW_CH + threadIdx.x;
+    const int c = blockIdx.x * DW_CH + 4 * threadIdx.x;           // d is a multiple of 4
     const bool cok = c < d;
     const int rows = DW_TT + k - 1;
-    for (int r = threadIdx.y; r < rows; r += DW_TG) {
+    for (int r = threadIdx.y; r < rows; r += DW_TY) {
         const int t = t0 - pad_left + r;
-        float v = 0.0f;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (cok && t >= 0 && t < len) {
             const float *p = h2 + (size_t)(off + t) * (2 * d);
-            v = p[c] * sigmoid_stable(p[d + c]);
+            const float4 x = *reinterpret_cast<const float4 *>(p + c), y = *reinterpret_cast<const float4 *>(p + d + c);
+            v = make_float4(x.x * sigmoid_fast(y.x), x.y * sigmoid_fast(y.y), x.z * sigmoid_fast(y.z), x.w * sigmoid_fast(y.w));
         }
-        g[r * DW_CH + threadIdx.x] = v;
+        g[r * (DW_CH / 4) + threadIdx.x] = v;
     }
     __syncthreads();
     if (!cok) return;
-    constexpr int KU = KW > 0 ? KW : DW_KMAX;
-    float w[KU];
-#pragma unroll
-    for (int j = 0; j < KU; j++) w[j] = j < k ? dw_w[(size_t)c * k + j] : 0.0f;
-    const float bias = dw_b ? dw_b[c] : 0.0f;
-    const float sc = scale ? scale[c] : 1.0f, sh = scale ? shift[c] : 0.0f;
     const int tend = len - t0 < DW_TT ? len - t0 : DW_TT;
-    for (int tt = threadIdx.y * (DW_TT / DW_TG); tt < tend && tt < (threadIdx.y + 1) * (DW_TT / DW_TG); tt++) {
-        float acc = bias;
+    const int tt0 = threadIdx.y * DW_RPT;
+    if (tt0 >= tend) return;
+    float4 acc[DW_RPT];
+    const float4 bias = dw_b ? *reinterpret_cast<const float4 *>(dw_b + c) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int j = 0; j < KU; j++)
-            if (KW > 0 || j < k) acc += w[j] * g[(tt + j) * DW_CH + threadIdx.x];
-        const size_t o = (size_t)(off + t0 + tt) * d + c;
+    for (int i = 0; i < DW_RPT; i++) acc[i] = bias;
+    // row tt0 + i uses staged rows tt0 + i + j, j < k: walk the staged rows once, each feeds up to DW_RPT outputs
+    constexpr int KU = KW > 0 ? KW : DW_KMAX;
+    const float *w0 = dw_w + (size_t)c * k, *w1 = w0 + k, *w2 = w1 + k, *w3 = w2 + k;
+#pragma unroll
+    for (int rr = 0; rr < KU + DW_RPT - 1; rr++) {
+        if (KW == 0 && rr >= k + DW_RPT - 1) break;
+        const float4 v = g[(tt0 + rr) * (DW_CH / 4) + threadIdx.x];
+#pragma unroll
+        for (int i = 0; i < DW_RPT; i++) {
+            const int j = rr - i;                                 // tap of output i fed by this row
+            if (j >= 0 && j < KU && (KW > 0 || j < k)) {
+                acc[i].x = fmaf(w0[j], v.x, acc[i].x); acc[i].y = fmaf(w1[j], v.y, acc[i].y);
+                acc[i].z = fmaf(w2[j], v.z, acc[i].z); acc[i].w = fmaf(w3[j], v.w, acc[i].w);
+            }
+        }
+    }
+    float4 sc = make_float4(1.f, 1.f, 1.f, 1.f), sh = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (scale) { sc = *reinterpret_cast<const float4 *>(scale + c); sh = *reinterpret_cast<const float4 *>(shift + c); }
+#pragma unroll
+    for (int i = 0; i < DW_RPT; i++) {
+        if (tt0 + i >= tend) break;
+        const size_t o = (size_t)(off + t0 + tt0 + i) * d + c;
         if (scale) {
-            const float y = silu_f(acc * sc + sh);
-            __half h, l;
-            split_h16(y, h, l);
-            hi[o] = h;
-            if (lo) lo[o] = l;
+            const float y[4] = {silu_f(acc[i].x * sc.x + sh.x), silu_f(acc[i].y * sc.y + sh.y), silu_f(acc[i].z * sc.z + sh.z),
+                                silu_f(acc[i].w * sc.w + sh.w)};
+            __align__(8) __half h[4], l[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) split_h16(y[e], h[e], l[e]);
+            *reinterpret_cast<uint2 *>(hi + o) = *reinterpret_cast<const uint2 *>(h);
+            if (lo) *reinterpret_cast<uint2 *>(lo + o) = *reinterpret_cast<const uint2 *>(l);
         } else {
-            out[o] = acc;
+            *reinterpret_cast<float4 *>(out + o) = acc[i];
         }
     }
 }
@@ -182,12 +202,13 @@ int glu_dwconv(const float *h2, const float *dw_w, const float *dw_b, const floa
                int k, int pad_left, cudaStream_t st) {
     if (batch <= 0 || max_len <= 0) return 0;
     if (k > DW_KMAX) { set_error("glu_dwconv: kernel width %d > %d", k, DW_KMAX); return -1; }
+    if (d % 4) { set_error("glu_dwconv: d=%d must be a multiple of 4", d); return -1; }
     dim3 grid(cdiv(d, DW_CH), cdiv(max_len, DW_TT), batch);
     if (k == 9)
-        glu_dw_kernel<9><<<grid, dim3(DW_CH, DW_TG), 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
+        glu_dw_kernel<9><<<grid, dim3(32, DW_TY), 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
                                                  seg_len, d, k, pad_left);
     else
-        glu_dw_kernel<0><<<grid, dim3(DW_CH, DW_TG), 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
+        glu_dw_kernel<0><<<grid, dim3(32, DW_TY), 0, st>>>(h2, dw_w, dw_b, scale, shift, out_f32, out_h.hi, out_h.lo, seg_off,
                                                  seg_len, d, k, pad_left);
     MB_CUDA(cudaGetLastError());
     return 0;

@@ -166,7 +166,7 @@ __global__ void stream_conv_kernel(const float *__restrict__ h2, const float *__
     for (int j = 0; j < k - 1; j++) seq[j] = cc[(size_t)j * d];
     for (int t = 0; t < Q; t++) {
         const float *r = h2 + ((size_t)s * Q + t) * 2 * d;
-        seq[k - 1 + t] = r[i] * sigmoid_stable(r[d + i]);
+        seq[k - 1 + t] = r[i] * sigmoid_fast(r[d + i]);
     }
     for (int t = 0; t < Q; t++) {
         float o = 0.f;
