@@ -54,7 +54,8 @@ int conv_in_relu(const float *feats, const float *w, const float *b, float *out,
 // largest tensor of the whole model: 196 MB for 60 s of audio) is never materialised.
 // Every stage-1 output needs a 3x3 patch of stage-0 outputs, i.e. a 7x7 patch of the
 // input; a CTA stages the input rows it needs in shared memory (read by all channels as
-// broadcasts) and one thread per channel recomputes the nine stage-0 values in registers.
+// broadcasts, fetched as 16-byte pieces into registers) and one thread per channel recomputes the
+// nine stage-0 values in registers.
 // Stage-0 positions outside [0,T1) x [0,F1) are the depthwise conv's own zero padding.
 static constexpr int FUSE_F2 = 8;      // stage-1 frequency positions per CTA
 
@@ -62,7 +63,7 @@ __global__ void __launch_bounds__(256)
 conv_in_dw_kernel(const float *__restrict__ x, const float *__restrict__ w0, const float *__restrict__ b0,
                   const float *__restrict__ w1, const float *__restrict__ b1, __half *__restrict__ hi,
                   __half *__restrict__ lo, int T, int F, int C, int T1, int F1, int T2, int F2, int pl) {
-    __shared__ float patch[7][4 * FUSE_F2 + 4];
+    __shared__ __align__(16) float patch[7][4 * FUSE_F2 + 4];
     const int t2 = blockIdx.y, f2base = blockIdx.x * FUSE_F2;
     // stage-0 rows 2*t2 - pl + {0,1,2} need input rows 2*(that) - pl + {0,1,2}
     const int trow0 = 2 * (2 * t2 - pl) - pl;           // first input row of the patch
@@ -81,6 +82,16 @@ conv_in_dw_kernel(const float *__restrict__ x, const float *__restrict__ w0, con
         for (int j = 0; j < FUSE_F2; j++) {
             const int f2 = f2base + j;
             if (f2 >= F2) break;
+            // the 7 x 7 input window of this output, as 16-byte broadcast loads (one shared-memory
+            // instruction per four values instead of one per multiply-add)
+            float in[7][8];
+#pragma unroll
+            for (int r = 0; r < 7; r++) {
+                const float4 lo4 = *reinterpret_cast<const float4 *>(&patch[r][4 * j]);
+                const float4 hi4 = *reinterpret_cast<const float4 *>(&patch[r][4 * j + 4]);
+                in[r][0] = lo4.x; in[r][1] = lo4.y; in[r][2] = lo4.z; in[r][3] = lo4.w;
+                in[r][4] = hi4.x; in[r][5] = hi4.y; in[r][6] = hi4.z; in[r][7] = hi4.w;
+            }
             float acc = 0.0f;
 #pragma unroll
             for (int dt = 0; dt < 3; dt++) {
@@ -95,7 +106,7 @@ conv_in_dw_kernel(const float *__restrict__ x, const float *__restrict__ w0, con
 #pragma unroll
                     for (int a = 0; a < 3; a++)
 #pragma unroll
-                        for (int b = 0; b < 3; b++) v += k0[a * 3 + b] * patch[2 * dt + a][4 * j + 2 * df + b];
+                        for (int b = 0; b < 3; b++) v += k0[a * 3 + b] * in[2 * dt + a][2 * df + b];
                     acc += k1[dt * 3 + df] * fmaxf(v + bias0, 0.0f);
                 }
             }
