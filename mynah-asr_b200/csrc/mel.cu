@@ -59,25 +59,31 @@ mel_frame_kernel(const float *__restrict__ audio_all, long long S, const double 
     }
 }
 
-// per-feature normalisation: one CTA per mel bin
-__global__ void __launch_bounds__(256)
+// per-feature normalisation: a CTA owns eight adjacent mel bins, thread (x, y) walks the frames y, y + 128, ..
+// of bin x (a warp reads four 32-byte runs); mean, then the centred sum of squares, in double as the reference
+static constexpr int MN_BX = 8, MN_BY = 128;
+
+__device__ __forceinline__ double mel_norm_reduce(double v, double (*red)[MN_BX], int x, int y) {
+    red[y][x] = v;
+    __syncthreads();
+    for (int o = MN_BY / 2; o > 0; o >>= 1) { if (y < o) red[y][x] += red[y + o][x]; __syncthreads(); }
+    const double r = red[0][x];
+    __syncthreads();
+    return r;
+}
+
+__global__ void __launch_bounds__(MN_BX * MN_BY)
 mel_norm_kernel(float *feats, int valid, int n_mels) {
-    __shared__ double red[256];
-    const int m = blockIdx.x;
+    __shared__ double red[MN_BY][MN_BX];
+    const int x = threadIdx.x, y = threadIdx.y, m = blockIdx.x * MN_BX + x;
+    const bool on = m < n_mels;
     double s = 0.0;
-    for (int t = threadIdx.x; t < valid; t += 256) s += (double)feats[(size_t)t * n_mels + m];
-    red[threadIdx.x] = s;
-    __syncthreads();
-    for (int o = 128; o > 0; o >>= 1) { if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o]; __syncthreads(); }
-    const double mu = red[0] / valid;
-    __syncthreads();
+    if (on) for (int t = y; t < valid; t += MN_BY) s += (double)feats[(size_t)t * n_mels + m];
+    const double mu = mel_norm_reduce(s, red, x, y) / valid;
     double q = 0.0;
-    for (int t = threadIdx.x; t < valid; t += 256) { const double c = (double)feats[(size_t)t * n_mels + m] - mu; q += c * c; }
-    red[threadIdx.x] = q;
-    __syncthreads();
-    for (int o = 128; o > 0; o >>= 1) { if (threadIdx.x < o) red[threadIdx.x] += red[threadIdx.x + o]; __syncthreads(); }
-    const double inv = 1.0 / (sqrt(red[0] / (valid - 1)) + 1e-5);
-    for (int t = threadIdx.x; t < valid; t += 256) {
+    if (on) for (int t = y; t < valid; t += MN_BY) { const double c = (double)feats[(size_t)t * n_mels + m] - mu; q += c * c; }
+    const double inv = 1.0 / (sqrt(mel_norm_reduce(q, red, x, y) / (valid - 1)) + 1e-5);
+    if (on) for (int t = y; t < valid; t += MN_BY) {
         float *v = feats + (size_t)t * n_mels + m;
         *v = (float)(((double)*v - mu) * inv);
     }
@@ -95,7 +101,7 @@ int log_mel_device(const MelCfg &c, const float *audio, size_t n_samples, const 
                                             c.n_fft, log2n, c.hop, c.n_mels, c.preemph, c.guard, 0, 0, 0, 0);
     MB_CUDA(cudaGetLastError());
     if (c.normalize && valid > 1) {
-        mel_norm_kernel<<<c.n_mels, 256, 0, st>>>(feats, valid, c.n_mels);
+        mel_norm_kernel<<<cdiv(c.n_mels, MN_BX), dim3(MN_BX, MN_BY), 0, st>>>(feats, valid, c.n_mels);
         MB_CUDA(cudaGetLastError());
     }
     return 0;
