@@ -23,7 +23,10 @@ mel_frame_kernel(const float *__restrict__ audio_all, long long S, const double 
                  const double *__restrict__ tw, const float *__restrict__ fb, const int *__restrict__ mlo,
                  const int *__restrict__ mhi, float *__restrict__ feats_all, int n_fft, int log2n, int hop, int n_mels,
                  double preemph, double guard, long long base, int t0, long long sig_stride, long long feat_stride) {
-    __shared__ double re[MEL_MAX_FFT], im[MEL_MAX_FFT];
+    // one double of padding after every 16: the bit-reversed stores and the small-stride stages would
+    // otherwise pile a warp's accesses onto one bank pair
+#define PD(i) ((i) + ((i) >> 4))
+    __shared__ double re[MEL_MAX_FFT + MEL_MAX_FFT / 16], im[MEL_MAX_FFT + MEL_MAX_FFT / 16];
     const float *audio = audio_all + blockIdx.y * sig_stride - base;      // audio[s] is sample s of the signal
     float *feats = feats_all + blockIdx.y * feat_stride - (long long)t0 * n_mels;
     const int t = t0 + blockIdx.x;
@@ -33,15 +36,15 @@ mel_frame_kernel(const float *__restrict__ audio_all, long long S, const double 
         double y = 0.0;
         if (s >= 0 && s < S) y = s == 0 ? (double)audio[0] : (double)audio[s] - preemph * (double)audio[s - 1];
         const int r = (int)(__brev((unsigned)i) >> (32 - log2n));
-        re[r] = y * win[i];
-        im[r] = 0.0;
+        re[PD(r)] = y * win[i];
+        im[PD(r)] = 0.0;
     }
     __syncthreads();
     for (int len = 2, sh = log2n - 1; len <= n_fft; len <<= 1, sh--) {
         const int half = len >> 1;
         for (int i = threadIdx.x; i < n_fft / 2; i += blockDim.x) {
             const int grp = i / half, k = i % half;
-            const int a = grp * len + k, bq = a + half;
+            const int a0 = grp * len + k, a = PD(a0), bq = PD(a0 + half);
             const double wr = tw[2 * (k << sh)], wi = tw[2 * (k << sh) + 1];
             const double xr = re[bq] * wr - im[bq] * wi, xi = re[bq] * wi + im[bq] * wr;
             re[bq] = re[a] - xr; im[bq] = im[a] - xi;
@@ -50,13 +53,14 @@ mel_frame_kernel(const float *__restrict__ audio_all, long long S, const double 
         __syncthreads();
     }
     const int nb = n_fft / 2 + 1;
-    for (int i = threadIdx.x; i < nb; i += blockDim.x) re[i] = re[i] * re[i] + im[i] * im[i];   // power, in place
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) re[PD(i)] = re[PD(i)] * re[PD(i)] + im[PD(i)] * im[PD(i)];   // power, in place
     __syncthreads();
     for (int m = threadIdx.x; m < n_mels; m += blockDim.x) {
         double acc = 0.0;
-        for (int b = mlo[m]; b < mhi[m]; b++) acc += re[b] * (double)fb[(size_t)b * n_mels + m];
+        for (int b = mlo[m]; b < mhi[m]; b++) acc += re[PD(b)] * (double)fb[(size_t)b * n_mels + m];
         feats[(size_t)t * n_mels + m] = (float)log(acc + guard);
     }
+#undef PD
 }
 
 // per-feature normalisation: a CTA owns eight adjacent mel bins, thread (x, y) walks the frames y, y + 128, ..
