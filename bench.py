@@ -56,7 +56,7 @@ def shard(n_items: int, rank: int, world: int):
     return list(range(lo, lo + base + (1 if rank < extra else 0)))
 
 
-BLANK_BIAS = {"cfg1": 2.0, "cfg2": 2.0, "cfg3": 3.7}     # overridden by --blank-bias
+BLANK_BIAS = {"cfg1": 2.0, "cfg2": 2.8, "cfg3": 3.7}     # overridden by --blank-bias
 
 
 def workload_config(synth, name: str):
