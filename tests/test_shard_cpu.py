@@ -60,3 +60,17 @@ def test_two_rank_gloo_gather(tmp_path):
     s.close()
     mp.spawn(_rank_main, args=(2, port, 33, str(tmp_path)), nprocs=2, join=True)
     assert open(tmp_path / "ok").read() == "1"
+
+
+def test_length_bucketed_workload_is_seeded_sorted_and_per_rank():
+    """The cfg2 workload: lengths are a seeded draw per rank, ascending (so consecutive batches hold similar
+    lengths), inside the stated range and on whole 10 ms."""
+    import argparse
+    b = _bench()
+    args = argparse.Namespace(items=256, min_seconds=5.0, max_seconds=120.0)
+    a0, a0_again, a1 = b.item_seconds(args, 0), b.item_seconds(args, 0), b.item_seconds(args, 1)
+    assert a0 == a0_again and a0 != a1 and len(a0) == 256
+    assert a0 == sorted(a0) and 5.0 <= a0[0] and a0[-1] <= 120.0
+    assert all(abs(v * 100 - round(v * 100)) < 1e-6 for v in a0)
+    batches = [a0[i:i + 64] for i in range(0, 256, 64)]
+    assert all(batches[i][-1] <= batches[i + 1][0] for i in range(3))
