@@ -415,7 +415,7 @@ static size_t enc_bytes(const Model &m, size_t M, size_t rk_rows) {
 }
 static size_t dec_bytes(const Model &m, int max_len) {
     const size_t B = DEC_MAX_B;
-    return (size_t)max_len * m.cfg.max_symbols * B * 8 + B * 148 * 8 * 16 + 4 * (size_t)DEC_MAX_LAYERS * B * 1024 * 4 + (1 << 20);
+    return (size_t)max_len * m.cfg.max_symbols * B * 8 + B * 148 * 8 * 16 + 4 * (size_t)DEC_MAX_LAYERS * B * 1024 * 4 + B * (size_t)m.pred_hidden * 4 + (1 << 20);
 }
 
 // Full device pipeline for a packed batch whose mel features are already on the
@@ -718,7 +718,7 @@ int mynah_b200_stream_step_decode(mynah_b200_stream_group *g, const float *mel, 
     if (n_mel != m.stream_need(g->st) && !is_last) { set_error("stream_step: %d mel frames given, %d needed", n_mel, m.stream_need(g->st)); return -1; }
     const size_t S = g->st.S, nin = S * n_mel * m.cfg.n_mels, nout = S * (g->st.q + 2) * m.d_out;
     const size_t nw = (size_t)(m.vocab + m.cfg.n_durations + 15) / 16, cap = (size_t)(g->st.q + 2) * m.cfg.max_symbols;
-    const size_t decb = S * (24 + 4 * nw + 2 * cap) * 4 + ((S + 15) / 16) * 1024 + (1 << 20);
+    const size_t decb = S * (24 + 4 * nw + 2 * cap) * 4 + ((S + 15) / 16) * (1024 + (size_t)DEC_MAX_B * m.pred_hidden * 4) + (1 << 20);
     if (m.ws.reserve(m.stream_bytes(g->st, n_mel) + (nin + nout) * 4 + decb + 4096)) return -1;
     m.ws.reset();
     float *md = m.ws.get<float>(nin), *od = m.ws.get<float>(nout);

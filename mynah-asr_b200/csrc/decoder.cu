@@ -279,6 +279,27 @@ __device__ void proj_phase(const GreedyDev &p, int par, bool all, __half *xhi, _
         const int task = base + wib, rb = task / NSL, sl = task % NSL;
         const bool on = task < nrb * NSL;
         float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        // the encoder values the epilogue adds to g are fetched now, under the contraction (-1: past the end)
+        float ev[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int r = rb * 16 + g + (i >> 1) * 8, b = nb * 8 + 2 * t + (i & 1);
+                ev[nb][i] = -1.f;
+                if (on && sl == 0 && r < H && b < B) {
+                    const int tb = p.t[b];
+                    if (tb < p.enc_len[b]) ev[nb][i] = p.enc[(size_t)(p.enc_off[b] + tb) * H + r];
+                }
+            }
+        bool past[2][4];
+#pragma unroll
+        for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int b = nb * 8 + 2 * t + (i & 1);
+                past[nb][i] = !(on && sl == 0 && b < B && p.t[b] < p.enc_len[b]);
+            }
         if (on) {
             const int rA = rb * 16 + g, rB = rA + 8;
             const int c0 = sl * per, c1 = (sl + 1) * per < chunks ? (sl + 1) * per : chunks;
@@ -297,7 +318,17 @@ __device__ void proj_phase(const GreedyDev &p, int par, bool all, __half *xhi, _
                     float s = 0.f;
                     for (int q = 0; q < NSL; q++) s += red[((wib + q) * 32 + lane) * 8 + nb * 4 + i];
                     const int r = rb * 16 + g + (i >> 1) * 8, b = nb * 8 + 2 * t + (i & 1);
-                    if (r < H && b < B && (all || p.emit[b])) p.g[(size_t)b * H + r] = s + p.proj_b[r];
+                    if (r < H && b < B) {
+                        // g, and with it the joint input of the coming step for this utterance's current frame
+                        // (an utterance that did not emit keeps its g but may have moved to another frame)
+                        const size_t o = (size_t)b * H + r;
+                        float gv;
+                        if (all || p.emit[b]) { gv = s + p.proj_b[r]; p.g[o] = gv; } else { gv = p.g[o]; }
+                        const float jv = past[nb][i] ? 0.f : fmaxf(ev[nb][i] + gv, 0.f);
+                        __half jh, jl;
+                        split_h16(jv, jh, jl);
+                        p.jx_hi[o] = jh; p.jx_lo[o] = jl;
+                    }
                 }
         }
         __syncthreads();
@@ -328,6 +359,7 @@ greedy_kernel(GreedyDev p) {
         proj_phase(p, par, true, xhi, xlo, red, lane, wib);
         grid.sync();
     }
+    bool jx_valid = p.init_state != 0;     // the planes of relu(enc[t] + g) left by the last projector phase are current
 
     constexpr int NSL = 2;
     const int nrb = (VL + 15) / 16, chunks = H / 32, per = (chunks + NSL - 1) / NSL;
@@ -349,7 +381,10 @@ greedy_kernel(GreedyDev p) {
             srow[threadIdx.x] = row;
         }
         __syncthreads();
-        if (blockIdx.x * 8 < nrb * NSL)
+        if (blockIdx.x * 8 < nrb * NSL && jx_valid) {
+            stage_planes(xhi, xlo, xs, 0, H, B, [&](int b) { return p.jx_hi + (size_t)b * H; }, [&](int b) { return p.jx_lo + (size_t)b * H; });
+            cp_wait_all();
+        } else if (blockIdx.x * 8 < nrb * NSL)
         stage_x(xhi, xlo, xs, 0, H, B, [&](int b, int k) {
             const int row = srow[b];
             const float4 e = ld4(p.enc + (size_t)(row < 0 ? 0 : row) * H + k), gg = ld4(p.g + (size_t)b * H + k);
@@ -466,6 +501,7 @@ greedy_kernel(GreedyDev p) {
             grid.sync();
             PHASE_MARK(4);
         }
+        jx_valid = any_emit != 0;
         if (all_done) break;
     }
 #undef PHASE_MARK

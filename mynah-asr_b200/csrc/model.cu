@@ -368,7 +368,7 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
         const int cap = max_len * cfg.max_symbols;
         const size_t mark = ws.off;
         const size_t nstate = (size_t)L * B * H;
-        float *fz = ws.get<float>(3 * nstate + (size_t)B * H + 2 * (size_t)B * nw);
+        float *fz = ws.get<float>(3 * nstate + (size_t)B * H + 2 * (size_t)B * nw + (size_t)DEC_MAX_B * H);
         int *iz = ws.get<int>(8 * (size_t)B + 2 * (size_t)B * nw + 2 * (size_t)B * cap + 16);
         if (!fz || !iz) return -1;
         MB_CUDA(cudaMemsetAsync(fz, 0, (3 * nstate + (size_t)B * H) * sizeof(float), stream));
@@ -383,7 +383,9 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
         for (int i = 0; i < cfg.n_durations; i++) p.durations[i] = cfg.durations[i];
         p.B = B; p.enc = enc_dev;
         p.h[0] = fz; p.h[1] = fz + nstate; p.c = fz + 2 * nstate; p.g = fz + 3 * nstate;
-        p.cand_v = p.g + (size_t)B * H;
+        // the planes first: they are copied in 16-byte pieces and B * H floats keep that alignment
+        p.jx_hi = reinterpret_cast<__half *>(p.g + (size_t)B * H); p.jx_lo = p.jx_hi + (size_t)DEC_MAX_B * H;
+        p.cand_v = p.g + (size_t)B * H + (size_t)DEC_MAX_B * H;
         int *q = iz;
         p.flags = q; q += 16;
         p.t = q; q += B; p.emitted_here = q; q += B; p.n_out = q; q += B; p.last_tok = q; q += B; p.emit = q; q += B;

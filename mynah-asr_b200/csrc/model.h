@@ -190,6 +190,7 @@ struct GreedyDev {
     // state
     float *h[2], *c;             // h[parity]: fp16 planes (hi [L][B][H] then lo [L][B][H], 4 bytes per value); c[L][B][H] f32
     float *g;                    // [B][H]
+    __half *jx_hi, *jx_lo;       // [16][H] each: relu(enc[t] + g) of the coming step as operand planes (written with g)
     int *t, *emitted_here, *n_out, *last_tok, *emit;
     int *tokens, *frames, cap;
     // scratch

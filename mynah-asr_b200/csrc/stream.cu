@@ -453,7 +453,7 @@ int Model::stream_decode(StreamState &st, const float *enc_dev, int q, std::vect
         const size_t nstate = (size_t)L * B * H;
         float *fs = st.dec_f + gi * fblock;
         int *is = st.dec_i + gi * iblock;
-        float *cand = ws.get<float>(2 * (size_t)B * nw);
+        float *cand = ws.get<float>(2 * (size_t)B * nw + (size_t)DEC_MAX_B * H);
         int *iz = ws.get<int>(8 * (size_t)B + 2 * (size_t)B * nw + 2 * (size_t)B * cap + 16);
         if (!cand || !iz) return -1;
         MB_CUDA(cudaMemsetAsync(iz, 0, (8 * (size_t)B + 16) * sizeof(int), stream));
@@ -467,7 +467,8 @@ int Model::stream_decode(StreamState &st, const float *enc_dev, int q, std::vect
         for (int i = 0; i < cfg.n_durations; i++) p.durations[i] = cfg.durations[i];
         p.B = B; p.enc = enc_dev;
         p.h[0] = fs; p.h[1] = fs + nstate; p.c = fs + 2 * nstate; p.g = fs + 3 * nstate;
-        p.cand_v = cand;
+        p.jx_hi = reinterpret_cast<__half *>(cand); p.jx_lo = p.jx_hi + (size_t)DEC_MAX_B * H;
+        p.cand_v = cand + (size_t)DEC_MAX_B * H;
         int *qi = iz;
         p.flags = qi; qi += 16;
         p.t = qi; qi += B; p.emitted_here = qi; qi += B; p.n_out = qi; qi += B; p.emit = qi; qi += B;
