@@ -209,6 +209,22 @@ __device__ void lstm_phase(const GreedyDev &p, int l, int par, __half *xhi, __ha
         const int task = base + wib, rb = task / NSL, sl = task % NSL;
         const bool on = task < nrb * NSL;
         float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        // what the cell update needs besides the sums — biases, previous cell state, emission flags — is
+        // fetched now, under the contraction
+        float bih[4] = {0.f, 0.f, 0.f, 0.f}, bhh[4] = {0.f, 0.f, 0.f, 0.f}, cprev[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+        int em[2][2] = {{0, 0}, {0, 0}};
+        if (on && sl == 0 && g < 4) {
+            const int unit = rb * 4 + g;
+#pragma unroll
+            for (int q = 0; q < 4; q++) { bih[q] = p.b_ih[l][q * H + unit]; bhh[q] = p.b_hh[l][q * H + unit]; }
+#pragma unroll
+            for (int nb = 0; nb < 2; nb++)
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int b = nb * 8 + 2 * t + e;
+                    if (b < B) { em[nb][e] = p.emit[b]; cprev[nb][e] = cc[(size_t)b * H + unit]; }
+                }
+        }
         if (on) {
             // fragment row lr -> gate lr/4, unit rb*4 + lr%4
             const int rowA = (g >> 2) * H + rb * 4 + (g & 3), rowB = (2 + (g >> 2)) * H + rb * 4 + (g & 3);
@@ -241,12 +257,12 @@ __device__ void lstm_phase(const GreedyDev &p, int l, int par, __half *xhi, __ha
                         const int unit = rb * 4 + g, b = nb * 8 + 2 * t + e;
                         if (b < B) {
                             const size_t o = (size_t)b * H + unit;
-                            if (p.emit[b]) {
-                                const float zi = za + p.b_ih[l][unit] + p.b_hh[l][unit];
-                                const float zf = oa + p.b_ih[l][H + unit] + p.b_hh[l][H + unit];
-                                const float zg = zb + p.b_ih[l][2 * H + unit] + p.b_hh[l][2 * H + unit];
-                                const float zo = ob + p.b_ih[l][3 * H + unit] + p.b_hh[l][3 * H + unit];
-                                const float cn = sigmoid_stable(zf) * cc[o] + sigmoid_stable(zi) * tanhf(zg);
+                            if (em[nb][e]) {
+                                const float zi = za + bih[0] + bhh[0];
+                                const float zf = oa + bih[1] + bhh[1];
+                                const float zg = zb + bih[2] + bhh[2];
+                                const float zo = ob + bih[3] + bhh[3];
+                                const float cn = sigmoid_stable(zf) * cprev[nb][e] + sigmoid_stable(zi) * tanhf(zg);
                                 cc[o] = cn;
                                 __half hh, hl;
                                 split_h16(sigmoid_stable(zo) * tanhf(cn), hh, hl);
