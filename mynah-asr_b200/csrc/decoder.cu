@@ -414,6 +414,7 @@ greedy_kernel(GreedyDev p) {
             const bool on = task < nrb * NSL;
             float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
             const int rA = rb * 16 + g, rB = rA + 8;
+            const float biasA = on && sl == 0 && rA < VL ? p.head_b[rA] : 0.f, biasB = on && sl == 0 && rB < VL ? p.head_b[rB] : 0.f;
             if (on) {
                 const int c0 = sl * per, c1 = (sl + 1) * per < chunks ? (sl + 1) * per : chunks;
                 rowblock_mma(p.head_hi, p.head_lo, H, rA < VL ? rA : VL - 1, rB < VL ? rB : VL - 1, c0, c1, xhi, xlo, xs, lane, acc);
@@ -424,7 +425,6 @@ greedy_kernel(GreedyDev p) {
                 for (int i = 0; i < 4; i++) red[(wib * 32 + lane) * 8 + nb * 4 + i] = acc[nb][i];
             __syncthreads();
             if (on && sl == 0) {
-                const float biasA = rA < VL ? p.head_b[rA] : 0.f, biasB = rB < VL ? p.head_b[rB] : 0.f;
 #pragma unroll
                 for (int nb = 0; nb < 2; nb++)
 #pragma unroll
@@ -459,37 +459,44 @@ greedy_kernel(GreedyDev p) {
         // ---- select: CTA b merges candidates and applies the emission rule
         if (blockIdx.x < B) {
             const int b = blockIdx.x;
-            __shared__ float sv[2][256];
-            __shared__ int si[2][256];
+            __shared__ float sv[2][8];
+            __shared__ int si[2][8];
+            // the utterance's state is fetched while the candidates are merged
+            int tb = 0, st_len = 0, st_no = 0, st_eh = 0;
+            if (threadIdx.x == 0) { tb = p.t[b]; st_len = p.enc_len[b]; st_no = p.n_out[b]; st_eh = p.emitted_here[b]; }
+            Cand best[2];
             for (int kind = 0; kind < 2; kind++) {
                 Cand c{-3.0e38f, 0x7fffffff};
                 for (int w = threadIdx.x; w < nrb; w += blockDim.x)
                     cand_take(c, p.cand_v[((size_t)b * 2 + kind) * nrb + w], p.cand_i[((size_t)b * 2 + kind) * nrb + w]);
-                sv[kind][threadIdx.x] = c.v; si[kind][threadIdx.x] = c.i;
+                best[kind] = c;
+            }
+#pragma unroll
+            for (int kind = 0; kind < 2; kind++) {
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+                    cand_take(best[kind], __shfl_xor_sync(0xffffffffu, best[kind].v, o), __shfl_xor_sync(0xffffffffu, best[kind].i, o));
+                if (lane == 0) { sv[kind][wib] = best[kind].v; si[kind][wib] = best[kind].i; }
             }
             __syncthreads();
-            for (int o = 128; o > 0; o >>= 1) {
-                if (threadIdx.x < o)
-                    for (int kind = 0; kind < 2; kind++) {
-                        const float v = sv[kind][threadIdx.x + o]; const int ix = si[kind][threadIdx.x + o];
-                        if (v > sv[kind][threadIdx.x] || (v == sv[kind][threadIdx.x] && ix < si[kind][threadIdx.x])) {
-                            sv[kind][threadIdx.x] = v; si[kind][threadIdx.x] = ix;
-                        }
-                    }
-                __syncthreads();
-            }
             if (threadIdx.x == 0) {
-                int tb = p.t[b];
+#pragma unroll
+                for (int kind = 0; kind < 2; kind++) {
+                    Cand c{sv[kind][0], si[kind][0]};
+#pragma unroll
+                    for (int w = 1; w < 8; w++) cand_take(c, sv[kind][w], si[kind][w]);
+                    best[kind] = c;
+                }
                 int em = 0;
-                if (tb < p.enc_len[b]) {
-                    const int k = si[0][0];
-                    int dur = p.ND > 0 ? p.durations[si[1][0] - V] : (k == p.blank ? 1 : 0);
+                if (tb < st_len) {
+                    const int k = best[0].i;
+                    int dur = p.ND > 0 ? p.durations[best[1].i - V] : (k == p.blank ? 1 : 0);
                     if (k != p.blank) {
-                        const int no = p.n_out[b];
+                        const int no = st_no;
                         if (no < p.cap) { p.tokens[(size_t)b * p.cap + no] = k; p.frames[(size_t)b * p.cap + no] = tb; p.n_out[b] = no + 1; }
                         em = 1;
                         p.last_tok[b] = k;
-                        const int eh = p.emitted_here[b] + 1;
+                        const int eh = st_eh + 1;
                         p.emitted_here[b] = eh;
                         if (dur == 0 && eh >= p.max_symbols) dur = 1;
                     } else if (dur == 0) {
@@ -501,7 +508,7 @@ greedy_kernel(GreedyDev p) {
                 }
                 p.emit[b] = em;
                 if (em) atomicExch(&fl[0], 1);
-                if (tb < p.enc_len[b]) atomicExch(&fl[1], 0);
+                if (tb < st_len) atomicExch(&fl[1], 0);
             }
         }
         grid.sync();
