@@ -296,14 +296,18 @@ __device__ void proj_phase(const GreedyDev &p, int par, bool all, __half *xhi, _
         const bool on = task < nrb * NSL;
         float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         // the encoder values the epilogue adds to g are fetched now, under the contraction (-1: past the end)
-        float ev[2][4];
+        // likewise the projector bias of an utterance that emitted, or the g an utterance that did not keeps
+        float ev[2][4], addv[2][4];
+        bool fresh[2][4];
 #pragma unroll
         for (int nb = 0; nb < 2; nb++)
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const int r = rb * 16 + g + (i >> 1) * 8, b = nb * 8 + 2 * t + (i & 1);
-                ev[nb][i] = -1.f;
+                ev[nb][i] = -1.f; addv[nb][i] = 0.f; fresh[nb][i] = false;
                 if (on && sl == 0 && r < H && b < B) {
+                    fresh[nb][i] = all || p.emit[b] != 0;
+                    addv[nb][i] = fresh[nb][i] ? p.proj_b[r] : p.g[(size_t)b * H + r];
                     const int tb = p.t[b];
                     if (tb < p.enc_len[b]) ev[nb][i] = p.enc[(size_t)(p.enc_off[b] + tb) * H + r];
                 }
@@ -338,8 +342,8 @@ __device__ void proj_phase(const GreedyDev &p, int par, bool all, __half *xhi, _
                         // g, and with it the joint input of the coming step for this utterance's current frame
                         // (an utterance that did not emit keeps its g but may have moved to another frame)
                         const size_t o = (size_t)b * H + r;
-                        float gv;
-                        if (all || p.emit[b]) { gv = s + p.proj_b[r]; p.g[o] = gv; } else { gv = p.g[o]; }
+                        float gv = addv[nb][i];
+                        if (fresh[nb][i]) { gv = s + addv[nb][i]; p.g[o] = gv; }
                         const float jv = past[nb][i] ? 0.f : fmaxf(ev[nb][i] + gv, 0.f);
                         __half jh, jl;
                         split_h16(jv, jh, jl);
