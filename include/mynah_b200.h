@@ -45,7 +45,8 @@ enum {
 };
 
 /* ---- backend presence and errors --------------------------------------------- */
-/* replaces mynah_asr_cuda_available (src/backend.c:24): 1 when an sm_100 device is usable */
+/* replaces mynah_asr_cuda_available (src/backend.c:24): 1 when the current device has compute capability 10.0
+ * (the library holds sm_100a code only) */
 int mynah_b200_available(void);
 /* picks the GPU for this process: explicit index, else env MYNAH_B200_DEVICE, else LOCAL_RANK, else 0 */
 int mynah_b200_select_device(int index);
@@ -93,18 +94,31 @@ int mynah_b200_qmat_mul(const mynah_b200_qmat *m, const float *x, float *out, in
 int mynah_b200_qmat_block_dots(const mynah_b200_qmat *m, const float *x, int T, int32_t *dots, float *sx, float *out);
 /* replaces mynah_asr_qmat_dequant (src/qmat.c:171-177): wd[n,k] f32 on the host */
 int mynah_b200_qmat_dequant(const mynah_b200_qmat *m, float *wd);
-/* same product with x, out already on the device (for callers that keep activations resident) */
+/* same product with x, out already on the device (for callers that keep activations resident).
+ * ASYNCHRONOUS: the work is queued on the handle's own stream (created non-blocking: it does not wait
+ * for the legacy default stream, so x_dev must be complete before the call) and the return value only
+ * says that it was queued. mynah_b200_qmat_sync waits for it and reports what the kernels found.
+ * One handle owns one stream, one status word and one scratch area: do not use the same handle from
+ * two threads at once (different handles are independent). */
 int mynah_b200_qmat_mul_device(const mynah_b200_qmat *m, const float *x_dev, float *out_dev, int T, int flags);
+/* waits for everything queued on the handle; -1 if a kernel reported a bounded wait that ran out or a
+ * value outside the fp16 operand range (|v| >= 65504, inf, NaN) since the last sync, else 0 */
+int mynah_b200_qmat_sync(const mynah_b200_qmat *m);
 
 /* No counterpart in the reference. The int8-activation product of mynah_b200_qmat_mul(.., A8) for
  * hosts that must not allocate device memory while running (a real-time streaming thread, a process
  * with a fixed GPU memory budget): x_dev [T,k] and out_dev [T,n] are DEVICE pointers owned by the
  * caller, and the only scratch (quantised activations + scales) is a fixed ~128 KB array inside the
  * library, so the call makes no cudaMalloc/cudaFree and uses no allocating library routine.
- * Limits: T <= 16 rows and k <= 8192 per call, larger sizes are refused with -1. The first call on
- * a device resolves the array's address (make it before any stream capture). All calls share the
+ * Limits: T <= 16 rows and k <= 8192 per call, larger sizes are refused with -1; so are the formats
+ * without an int8-activation mode (F32, Q4_K, Q6_K: only Q8_0, Q4_0 and the two native formats have
+ * one). Every refusal happens before anything is launched. The first call on a device resolves the
+ * array's address, and the first call with a given weight format on a device loads that format's
+ * kernel: make one call per format you will use before any stream capture. All calls share the
  * array: it keeps the previous call's contents and calls that overlap on the GPU race — serialise
- * them. Synchronous: out_dev is complete on return. */
+ * them. The kernels run on the handle's own non-blocking stream, which does not wait for the legacy
+ * default stream: x_dev must be completely written (its producer synchronised) before the call.
+ * Synchronous: out_dev is complete on return. */
 int mynah_b200_qmat_mul_a8_static(const mynah_b200_qmat *m, const float *x_dev, float *out_dev, int T);
 
 /* ---- model --------------------------------------------------------------------- */
@@ -192,6 +206,9 @@ mynah_b200_stream_group *mynah_b200_stream_open(mynah_b200_model *m, int n_strea
 void mynah_b200_stream_close(mynah_b200_stream_group *g);
 /* mel frames every stream must supply to the next step: 1 + 8 right_ctx first, then 8 (right_ctx + 1) */
 int mynah_b200_stream_need(const mynah_b200_stream_group *g);
+/* prompt-conditioned encoders (the prompt_id argument of mynah_asr_enc_stream_step, src/encoder.h:119-120): one id
+ * per stream, to be set before the first step; without this call every stream uses prompt 0 */
+int mynah_b200_stream_set_prompts(mynah_b200_stream_group *g, const int *prompt_ids);
 /* mel [n_streams, n_mel, n_mels] -> out [n_streams, q, d_out] (host buffers, room for right_ctx + 3 frames
  * per stream as in the reference's callers); n_mel = stream_need() except
  * for the last, shorter chunk (is_last = 1: causal right padding as offline). Returns q, -1 on error. */
@@ -222,6 +239,12 @@ int mynah_b200_stream_step_device(mynah_b200_stream_group *g, const float *mel_d
 int mynah_b200_transcribe_batch(mynah_b200_model *m, const float *const *audio, const size_t *n_samples, int batch,
                                 int decoder, int **tokens, int **frames, int *n_tokens);
 
+/* the same with one prompt id per utterance for prompt-conditioned encoders (the prompt_ids of
+ * mynah_asr_encoder_forward_batch, src/encoder.h:82-85, as resolve_prompt fills them, src/mynah_asr.c:416-421);
+ * prompt_ids NULL = 0 for all; ignored by models without a prompt projector */
+int mynah_b200_transcribe_batch_prompts(mynah_b200_model *m, const float *const *audio, const size_t *n_samples, int batch,
+                                        const int *prompt_ids, int decoder, int **tokens, int **frames, int *n_tokens);
+
 /* The AED engine's wave (eng_decode_aed, src/mynah_asr.c:147-160): every utterance starts from the same prompt
  * and may generate T + max_gen_delta tokens (T = its encoder frames). */
 int mynah_b200_transcribe_batch_aed(mynah_b200_model *m, const float *const *audio, const size_t *n_samples, int batch,
@@ -233,6 +256,8 @@ int mynah_b200_transcribe_batch_aed(mynah_b200_model *m, const float *const *aud
 typedef struct mynah_b200_batch mynah_b200_batch;
 mynah_b200_batch *mynah_b200_batch_upload(mynah_b200_model *m, const float *const *audio, const size_t *n_samples,
                                           int batch);
+/* one prompt id per utterance for prompt-conditioned encoders (NULL: back to 0 for all) */
+void mynah_b200_batch_set_prompts(mynah_b200_batch *h, const int *prompt_ids);
 /* decoder 2 (AED) needs its prompt, EOS id and generation allowance set on the handle first */
 void mynah_b200_batch_set_aed(mynah_b200_batch *h, const int *prompt, int n_prompt, int eos, int max_gen_delta);
 int mynah_b200_batch_run(mynah_b200_model *m, mynah_b200_batch *h, int decoder);

@@ -49,6 +49,12 @@ class StreamGroup:
     def need(self):
         return lib().mynah_b200_stream_need(self.h)
 
+    def set_prompts(self, prompt_ids):
+        """one prompt id per stream (prompt-conditioned encoders), before the first step"""
+        assert len(prompt_ids) == self.n
+        if lib().mynah_b200_stream_set_prompts(self.h, (C.c_int * self.n)(*prompt_ids)) != 0:
+            raise BackendError("stream_set_prompts: " + _err())
+
     def step(self, mel, is_last=False):
         """mel [n, n_mel, n_mels] -> [n, q, d_out]"""
         mel = np.ascontiguousarray(mel, np.float32)
@@ -161,6 +167,12 @@ def lib():
     L.mynah_b200_greedy_decode.argtypes = [vp, c_fp, ci, c_ip, c_ip, ci]
     L.mynah_b200_transcribe_batch.argtypes = [vp, C.POINTER(c_fp), C.POINTER(C.c_size_t), ci, ci, C.POINTER(vp),
                                               C.POINTER(vp), c_ip]
+    L.mynah_b200_transcribe_batch_prompts.argtypes = [vp, C.POINTER(c_fp), C.POINTER(C.c_size_t), ci, c_ip, ci, C.POINTER(vp),
+                                                      C.POINTER(vp), c_ip]
+    L.mynah_b200_stream_set_prompts.argtypes = [vp, c_ip]
+    L.mynah_b200_batch_set_prompts.argtypes = [vp, c_ip]
+    L.mynah_b200_batch_set_prompts.restype = None
+    L.mynah_b200_qmat_sync.argtypes = [vp]
     L.mynah_b200_batch_upload.restype = vp
     L.mynah_b200_batch_upload.argtypes = [vp, C.POINTER(c_fp), C.POINTER(C.c_size_t), ci]
     L.mynah_b200_batch_run.argtypes = [vp, vp, ci]
@@ -384,23 +396,23 @@ class Model:
         _check(lib().mynah_b200_encoder_layer(self.h, li, _fp(x), x.shape[0], left, right), "encoder_layer")
         return x
 
-    def encoder_forward(self, feats, left=-1, right=-1, raw=False):
+    def encoder_forward(self, feats, left=-1, right=-1, raw=False, prompt_id=0):
         feats = np.ascontiguousarray(feats, np.float32)
         t = C.c_int()
         if raw:
             p = lib().mynah_b200_encoder_forward_raw(self.h, _fp(feats), feats.shape[0], feats.shape[1], left, right,
                                                      C.byref(t))
         else:
-            p = lib().mynah_b200_encoder_forward(self.h, _fp(feats), feats.shape[0], feats.shape[1], 0, left, right,
+            p = lib().mynah_b200_encoder_forward(self.h, _fp(feats), feats.shape[0], feats.shape[1], prompt_id, left, right,
                                                  C.byref(t))
         return _take_f32(p, (t.value, self.d_model if raw else self.d_out))
 
-    def encoder_forward_batch(self, feats_list, left=-1, right=-1):
+    def encoder_forward_batch(self, feats_list, left=-1, right=-1, prompt_ids=None):
         B = len(feats_list)
         fl = [np.ascontiguousarray(f, np.float32) for f in feats_list]
         ptrs = (c_fp * B)(*[_fp(f) for f in fl])
         tm = (C.c_int * B)(*[f.shape[0] for f in fl])
-        pid = (C.c_int * B)()
+        pid = (C.c_int * B)(*(prompt_ids if prompt_ids is not None else [0] * B))
         outs = (C.c_void_p * B)()
         touts = (C.c_int * B)()
         _check(lib().mynah_b200_encoder_forward_batch(self.h, ptrs, tm, B, self.n_mels, pid, left, right, outs, touts),
@@ -470,11 +482,12 @@ class Model:
         ns = (C.c_size_t * B)(*[a.size for a in al])
         return al, ptrs, ns
 
-    def transcribe_batch(self, audio_list, decoder=0):
+    def transcribe_batch(self, audio_list, decoder=0, prompt_ids=None):
         B = len(audio_list)
         al, ptrs, ns = self._audio_args(audio_list)
         tk, fr, nt = (C.c_void_p * B)(), (C.c_void_p * B)(), (C.c_int * B)()
-        _check(lib().mynah_b200_transcribe_batch(self.h, ptrs, ns, B, decoder, tk, fr, nt), "transcribe_batch")
+        pid = None if prompt_ids is None else (C.c_int * B)(*prompt_ids)
+        _check(lib().mynah_b200_transcribe_batch_prompts(self.h, ptrs, ns, B, pid, decoder, tk, fr, nt), "transcribe_batch")
         return [(_take_i32(tk[b], nt[b]), _take_i32(fr[b], nt[b])) for b in range(B)]
 
     def batch_upload(self, audio_list):

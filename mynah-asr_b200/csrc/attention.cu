@@ -326,10 +326,11 @@ template <int DK>
 static int launch_tiled(const AttnDev &dv, int batch, int max_len, cudaStream_t st) {
     constexpr int LD = DK + 8;
     const int smem = (2 * AT_K + 128) * LD * 2 + 4 * 16 * AT_BDS * 4;
-    static bool set = false;
-    if (!set) {
+    static PerDevice configured = {};
+    int dev = 0;
+    if (configured.below((size_t)smem, &dev)) {
         MB_CUDA(cudaFuncSetAttribute(attn_tiled_kernel<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        set = true;
+        configured.record(dev, (size_t)smem);
     }
     dim3 grid(cdiv(max_len, AT_Q), dv.H, batch);
     attn_tiled_kernel<DK><<<grid, 128, smem, st>>>(dv);

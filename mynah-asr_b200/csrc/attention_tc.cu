@@ -459,10 +459,11 @@ bool attention_tc_eligible(const AttnArgs &a) {
 int attention_tc(const AttnArgs &a, cudaStream_t st) {
     CUtensorMap tk, tv, tr;
     if (ta_make_map(&tk, a.k, a.rows, a.d) || ta_make_map(&tv, a.v, a.rows, a.d) || ta_make_map(&tr, a.rk, a.rk_rows, a.d)) return -1;
-    static bool set = false;
-    if (!set) {
+    static PerDevice configured = {};
+    int dev = 0;
+    if (configured.below((size_t)TA_SMEM, &dev)) {
         MB_CUDA(cudaFuncSetAttribute(attn_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TA_SMEM));
-        set = true;
+        configured.record(dev, (size_t)TA_SMEM);
     }
     AttnTcDev dv;
     dv.q = a.q; dv.ldq = a.ldq; dv.bias_u = a.bias_u; dv.bias_v = a.bias_v; dv.ctx_f32 = a.ctx_f32;

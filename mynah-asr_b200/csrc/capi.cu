@@ -4,6 +4,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <memory>
+
 #include "model.h"
 
 using namespace mb;
@@ -22,6 +24,7 @@ struct mynah_b200_batch {
     std::vector<float *> audio;          // device
     std::vector<size_t> n_samples;
     std::vector<std::vector<int>> tokens, frames;
+    std::vector<int> prompt_ids;         // prompt-conditioned encoders: one id per utterance (empty = 0 for all)
     std::vector<int> aed_prompt;         // decoder 2 (AED): the prompt every utterance starts from,
     int aed_eos = -1, aed_delta = 0;     // the end-of-sequence id and the generation allowance beyond T
 };
@@ -62,7 +65,7 @@ int mynah_b200_available(void) {
     cudaGetDevice(&dev);
     cudaDeviceProp p;
     if (cudaGetDeviceProperties(&p, dev) != cudaSuccess) { cudaGetLastError(); return 0; }
-    return p.major == 10 ? 1 : 0;
+    return p.major == 10 && p.minor == 0 ? 1 : 0;      // the library holds sm_100a code only
 }
 
 int mynah_b200_select_device(int index) {
@@ -244,7 +247,6 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
     if (!bu || !dw) { set_error("missing encoder.layers.0 tensors"); return -1; }
     m.n_heads = (int)bu->shape[0]; m.d_head = (int)bu->shape[1]; m.conv_k = (int)dw->shape[2];
     if (m.cfg.xscaling) m.xscale = sqrtf((float)m.d_model);
-    if (find(m, "prompt_projector.linear_1.weight")) { set_error("prompt projector models are not supported"); return -1; }
     int nl = 0;
     while (find(m, "encoder.layers." + std::to_string(nl) + ".norm_out.weight")) nl++;
     if (nl == 0) { set_error("no encoder layers found"); return -1; }
@@ -293,6 +295,28 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
         m.has_encproj = true;
         m.d_out = m.encproj.n;
     }
+    if (const HostTensor *p1 = find(m, "prompt_projector.linear_1.weight")) {
+        // Nemotron-style prompt MLP (mynah_asr_encoder_init, src/encoder.c:65-77,173-176): linear_1 is [inter, d + num_prompts]
+        const HostTensor *b1 = find(m, "prompt_projector.linear_1.bias"), *p2 = find(m, "prompt_projector.linear_2.weight");
+        const int d = m.d_model;
+        if (!m.has_encproj || !b1 || !p2 || p1->fmt != FMT_F32 || b1->fmt != FMT_F32 || p1->shape.size() != 2 || (int)p1->shape[1] <= d) {
+            set_error("prompt_projector needs f32 linear_1 [inter, d + prompts] with its bias, linear_2 and an encoder_projector"); return -1;
+        }
+        const int di = (int)p1->shape[0], dcat = (int)p1->shape[1], np = dcat - d;
+        if (di % 64) { set_error("prompt_projector width %d must be a multiple of 64", di); return -1; }
+        const float *w1 = (const float *)p1->data, *bb = (const float *)b1->data;
+        std::vector<float> main((size_t)di * d), table((size_t)np * di);
+        for (int i = 0; i < di; i++) {
+            memcpy(&main[(size_t)i * d], w1 + (size_t)i * dcat, (size_t)d * sizeof(float));
+            // the reference adds b1 to (x W^T + W[:, d + p]); the sum of the two constants first differs by an ulp at most
+            for (int p = 0; p < np; p++) table[(size_t)p * di + i] = w1[(size_t)i * dcat + d + p] + bb[i];
+        }
+        if (m.upload_weight(m.prompt_l1, FMT_F32, main.data(), nullptr, di, d, true, false)) return -1;
+        m.prompt_bias1 = m.upload_f32(table.data(), table.size());
+        if (!m.prompt_bias1 || lin(m, m.prompt_l2, "prompt_projector.linear_2.weight", true, false)) return -1;
+        if (!m.prompt_l2.bias || m.prompt_l2.n != d || m.prompt_l2.k != di) { set_error("prompt_projector.linear_2 must be [d, inter] with a bias"); return -1; }
+        m.has_prompt = true; m.num_prompts = np; m.prompt_inter = di;
+    }
     if (find(m, "ctc_head.weight")) {
         if (lin(m, m.ctc_head, "ctc_head.weight", true, false)) return -1;
         if (!m.ctc_head.bias) { set_error("missing ctc_head.bias"); return -1; }
@@ -305,7 +329,7 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
         if (m.emb) {                       // the same table as fp16 (hi, lo) planes: LSTM inputs are copied, not converted
             const size_t ne = (size_t)m.vocab * m.pred_hidden;
             m.emb_planes.hi = (__half *)m.dev_alloc(ne * 2); m.emb_planes.lo = (__half *)m.dev_alloc(ne * 2);
-            if (!m.emb_planes.hi || !m.emb_planes.lo || split_to_h16(m.emb, m.emb_planes.hi, m.emb_planes.lo, ne, m.stream)) return -1;
+            if (!m.emb_planes.hi || !m.emb_planes.lo || split_to_h16(m.emb, m.emb_planes.hi, m.emb_planes.lo, ne, m.stream, m.status)) return -1;
         }
         m.proj_b = f32dev(m, "decoder.decoder_projector.bias", true, &err);
         m.head_b = f32dev(m, "joint.head.bias", true, &err);
@@ -385,8 +409,9 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
         m.has_aed = true;
     }
     m.host.clear();
-    m.finalized = true;
     MB_CUDA(cudaDeviceSynchronize());
+    if (m.check_status("model_finalize (a weight does not fit the fp16 operand planes)")) return -1;
+    m.finalized = true;
     return 0;
 }
 
@@ -492,7 +517,6 @@ int mynah_b200_encoder_layer(mynah_b200_model *h, int li, float *x, int T, int l
 
 int mynah_b200_encoder_forward_batch(mynah_b200_model *h, const float *const *feats, const int *t_mel, int batch,
                                      int n_mels, const int *prompt_ids, int left, int right, float **outs, int *t_outs) {
-    (void)prompt_ids;
     if (!h || !h->m.finalized || batch <= 0 || n_mels != h->m.cfg.n_mels) { set_error("encoder_forward_batch: bad argument"); return -1; }
     Model &m = h->m;
     std::lock_guard<std::mutex> lk(m.mu);
@@ -515,7 +539,7 @@ int mynah_b200_encoder_forward_batch(mynah_b200_model *h, const float *const *fe
     float *x = m.ws.get<float>((M ? M : 1) * m.d_model), *y = m.ws.get<float>((M ? M : 1) * m.d_out);
     if (!x || !y) return -1;
     if (encode_batch_dev(m, fd, tm, left, right, x, lens)) return -1;
-    if (m.encoder_post(x, (int)M, y) || m.check_status("encoder_forward_batch")) return -1;
+    if (m.encoder_post(x, lens, prompt_ids, y) || m.check_status("encoder_forward_batch")) return -1;
     size_t off = 0;
     for (int b = 0; b < batch; b++) {
         t_outs[b] = lens[b];
@@ -528,8 +552,8 @@ int mynah_b200_encoder_forward_batch(mynah_b200_model *h, const float *const *fe
     return 0;
 }
 
-static float *forward_one(mynah_b200_model *h, const float *feats, int t_mel, int n_mels, int left, int right, int raw,
-                          int *t_out) {
+static float *forward_one(mynah_b200_model *h, const float *feats, int t_mel, int n_mels, int prompt_id, int left, int right,
+                          int raw, int *t_out) {
     if (!h || !h->m.finalized || !feats || t_mel <= 0 || n_mels != h->m.cfg.n_mels) { set_error("encoder_forward: bad argument"); return nullptr; }
     Model &m = h->m;
     std::lock_guard<std::mutex> lk(m.mu);
@@ -543,7 +567,7 @@ static float *forward_one(mynah_b200_model *h, const float *feats, int t_mel, in
     std::vector<int> tm{t_mel}, lens;
     if (encode_batch_dev(m, fd, tm, left, right, x, lens)) return nullptr;
     const int wout = raw ? m.d_model : m.d_out;
-    if (!raw && m.encoder_post(x, (int)M, y)) return nullptr;
+    if (!raw && m.encoder_post(x, lens, &prompt_id, y)) return nullptr;
     if (m.check_status("encoder_forward")) return nullptr;
     float *out = (float *)malloc(M * wout * sizeof(float));
     if (!out) { set_error("out of host memory"); return nullptr; }
@@ -555,12 +579,11 @@ static float *forward_one(mynah_b200_model *h, const float *feats, int t_mel, in
 
 float *mynah_b200_encoder_forward(mynah_b200_model *h, const float *feats, int t_mel, int n_mels, int prompt_id,
                                   int left, int right, int *t_out) {
-    (void)prompt_id;
-    return forward_one(h, feats, t_mel, n_mels, left, right, 0, t_out);
+    return forward_one(h, feats, t_mel, n_mels, prompt_id, left, right, 0, t_out);
 }
 float *mynah_b200_encoder_forward_raw(mynah_b200_model *h, const float *feats, int t_mel, int n_mels, int left,
                                       int right, int *t_out) {
-    return forward_one(h, feats, t_mel, n_mels, left, right, 1, t_out);
+    return forward_one(h, feats, t_mel, n_mels, 0, left, right, 1, t_out);
 }
 
 int mynah_b200_ctc_decode(mynah_b200_model *h, const float *enc_out, int T, int *tokens, int *frames, int cap) {
@@ -645,6 +668,11 @@ int mynah_b200_aed_decode(mynah_b200_model *h, const float *enc, int T, const in
     return n;
 }
 
+void mynah_b200_batch_set_prompts(mynah_b200_batch *bt, const int *prompt_ids) {
+    if (!bt) return;
+    if (prompt_ids) bt->prompt_ids.assign(prompt_ids, prompt_ids + bt->batch); else bt->prompt_ids.clear();
+}
+
 void mynah_b200_batch_set_aed(mynah_b200_batch *bt, const int *prompt, int n_prompt, int eos, int max_gen_delta) {
     if (!bt) return;
     bt->aed_prompt.assign(prompt, prompt + (n_prompt > 0 ? n_prompt : 0));
@@ -665,6 +693,15 @@ void mynah_b200_stream_close(mynah_b200_stream_group *g) {
     if (!g) return;
     { std::lock_guard<std::mutex> lk(g->model->m.mu); g->model->m.stream_close(g->st); }
     delete g;
+}
+
+int mynah_b200_stream_set_prompts(mynah_b200_stream_group *g, const int *prompt_ids) {
+    if (!g || !prompt_ids) { set_error("stream_set_prompts: bad argument"); return -1; }
+    Model &m = g->model->m;
+    std::lock_guard<std::mutex> lk(m.mu);
+    if (g->st.exec) { set_error("stream_set_prompts: set the prompts before the first step"); return -1; }
+    g->st.prompt_ids.assign(prompt_ids, prompt_ids + g->st.S);
+    return 0;
 }
 
 int mynah_b200_stream_need(const mynah_b200_stream_group *g) { return g ? g->model->m.stream_need(g->st) : -1; }
@@ -818,7 +855,7 @@ static int run_batch_locked(Model &m, mynah_b200_batch *bt, const float *const *
     } else if (decoder == 2) {
         // AED engine: projected encoder output, generation budget T + max_gen_delta per utterance
         // (eng_decode_aed, src/mynah_asr.c:147-160, without timestamp tokens)
-        if (m.encoder_post(x, (int)M, y)) return -1;
+        if (m.encoder_post(x, lens, bt->prompt_ids.empty() ? nullptr : bt->prompt_ids.data(), y)) return -1;
         std::vector<std::vector<int>> pr(B, bt->aed_prompt);
         std::vector<int> caps(B);
         for (int b = 0; b < B; b++) caps[b] = lens[b] + bt->aed_delta;
@@ -835,7 +872,7 @@ static int run_batch_locked(Model &m, mynah_b200_batch *bt, const float *const *
         }
         for (int b = 0; b < B; b++) bt->frames[b].assign(bt->tokens[b].size(), 0);
     } else {
-        if (m.encoder_post(x, (int)M, y)) return -1;
+        if (m.encoder_post(x, lens, bt->prompt_ids.empty() ? nullptr : bt->prompt_ids.data(), y)) return -1;
         if (m.decode_greedy(y, lens, bt->tokens, bt->frames)) return -1;
     }
     return m.check_status("batch_run");
@@ -867,10 +904,16 @@ int mynah_b200_batch_fetch(mynah_b200_model *h, mynah_b200_batch *bt, int **toke
 
 int mynah_b200_transcribe_batch(mynah_b200_model *h, const float *const *audio, const size_t *n_samples, int batch,
                                 int decoder, int **tokens, int **frames, int *n_tokens) {
+    return mynah_b200_transcribe_batch_prompts(h, audio, n_samples, batch, nullptr, decoder, tokens, frames, n_tokens);
+}
+
+int mynah_b200_transcribe_batch_prompts(mynah_b200_model *h, const float *const *audio, const size_t *n_samples, int batch,
+                                        const int *prompt_ids, int decoder, int **tokens, int **frames, int *n_tokens) {
     if (!h || !h->m.finalized || batch <= 0 || !audio || !n_samples) { set_error("transcribe_batch: bad argument"); return -1; }
     mynah_b200_batch bt;
     bt.batch = batch;
     bt.n_samples.assign(n_samples, n_samples + batch);
+    mynah_b200_batch_set_prompts(&bt, prompt_ids);
     int rc;
     {
         std::lock_guard<std::mutex> lk(h->m.mu);
@@ -906,9 +949,11 @@ mynah_b200_qmat *mynah_b200_qmat_create(int fmt, const void *data, const float *
     if (cudaStreamCreateWithFlags(&tmp.stream, cudaStreamNonBlocking) != cudaSuccess) { set_error("cudaStreamCreate failed"); return nullptr; }
     mynah_b200_qmat *q = new mynah_b200_qmat();
     const bool planes = (k % 64) == 0;
-    if (tmp.upload_weight(q->w, f, data, scales, n, k, planes, false)) { delete q; return nullptr; }
-    q->status = (int *)tmp.dev_alloc(sizeof(int));
+    tmp.status = q->status = (int *)tmp.dev_alloc(sizeof(int));
+    if (!q->status) { delete q; return nullptr; }
     cudaMemset(q->status, 0, sizeof(int));
+    cudaDeviceSynchronize();
+    if (tmp.upload_weight(q->w, f, data, scales, n, k, planes, false) || tmp.check_status("qmat_create")) { delete q; return nullptr; }
     cudaDeviceSynchronize();
     q->owned.swap(tmp.owned);
     q->stream = tmp.stream;
@@ -953,8 +998,10 @@ int mynah_b200_qmat_mul_device(const mynah_b200_qmat *q, const float *x, float *
     if (!w.hi) { set_error("qmat_mul: large-T path needs k %% 64 == 0 (k=%d)", w.k); return -1; }
     __half *hi = nullptr, *lo = nullptr;
     MB_CUDA(cudaMallocAsync(&hi, (size_t)T * w.k * 2, q->stream));
-    MB_CUDA(cudaMallocAsync(&lo, (size_t)T * w.k * 2, q->stream));
-    int rc = split_to_h16(x, hi, lo, (size_t)T * w.k, q->stream);
+    if (cudaMallocAsync(&lo, (size_t)T * w.k * 2, q->stream) != cudaSuccess) {
+        cudaGetLastError(); cudaFreeAsync(hi, q->stream); set_error("qmat_mul: device allocation failed"); return -1;
+    }
+    int rc = split_to_h16(x, hi, lo, (size_t)T * w.k, q->stream, q->status);
     GemmEpilogue e;
     memset(&e, 0, sizeof(e));
     e.mode = OUT_F32; e.act = ACT_NONE; e.alpha = 1.f; e.out = out; e.ldo = w.n;
@@ -966,21 +1013,36 @@ int mynah_b200_qmat_mul_device(const mynah_b200_qmat *q, const float *x, float *
     return rc;
 }
 
+int mynah_b200_qmat_sync(const mynah_b200_qmat *q) {
+    if (!q) { set_error("qmat_sync: null handle"); return -1; }
+    int st = 0;
+    MB_CUDA(cudaMemcpyAsync(&st, q->status, sizeof(int), cudaMemcpyDeviceToHost, q->stream));
+    MB_CUDA(cudaStreamSynchronize(q->stream));
+    if (st != 0) {
+        if (st == ST_RANGE) set_error("qmat: a value reached the fp16 operand range (|v| >= 65504) or was not finite");
+        else set_error("qmat: a bounded wait inside the contraction kernel ran out (code %d)", st);
+        cudaMemsetAsync(q->status, 0, sizeof(int), q->stream);
+        cudaStreamSynchronize(q->stream);
+        return -1;
+    }
+    return 0;
+}
+
 int mynah_b200_qmat_mul(const mynah_b200_qmat *q, const float *x, float *out, int T, int flags) {
     if (!q || !x || !out || T < 0) { set_error("qmat_mul: bad argument"); return -1; }
     if (T == 0) return 0;
     float *xd = nullptr, *od = nullptr;
     MB_CUDA(cudaMallocAsync(&xd, (size_t)T * q->w.k * 4, q->stream));
-    MB_CUDA(cudaMallocAsync(&od, (size_t)T * q->w.n * 4, q->stream));
-    MB_CUDA(cudaMemcpyAsync(xd, x, (size_t)T * q->w.k * 4, cudaMemcpyHostToDevice, q->stream));
-    int rc = mynah_b200_qmat_mul_device(q, xd, od, T, flags);
-    if (rc == 0) MB_CUDA(cudaMemcpyAsync(out, od, (size_t)T * q->w.n * 4, cudaMemcpyDeviceToHost, q->stream));
-    int st = 0;
-    cudaMemcpyAsync(&st, q->status, sizeof(int), cudaMemcpyDeviceToHost, q->stream);
+    if (cudaMallocAsync(&od, (size_t)T * q->w.n * 4, q->stream) != cudaSuccess) {
+        cudaGetLastError(); cudaFreeAsync(xd, q->stream); set_error("qmat_mul: device allocation failed"); return -1;
+    }
+    int rc = 0;
+    if (cudaMemcpyAsync(xd, x, (size_t)T * q->w.k * 4, cudaMemcpyHostToDevice, q->stream) != cudaSuccess) { set_error("qmat_mul: H2D copy failed"); rc = -1; }
+    if (rc == 0) rc = mynah_b200_qmat_mul_device(q, xd, od, T, flags);
+    if (rc == 0 && cudaMemcpyAsync(out, od, (size_t)T * q->w.n * 4, cudaMemcpyDeviceToHost, q->stream) != cudaSuccess) { set_error("qmat_mul: D2H copy failed"); rc = -1; }
     cudaFreeAsync(xd, q->stream);
     cudaFreeAsync(od, q->stream);
-    MB_CUDA(cudaStreamSynchronize(q->stream));
-    if (st != 0) { set_error("qmat_mul: a bounded wait inside the contraction kernel ran out (code %d)", st); cudaMemset(q->status, 0, sizeof(int)); return -1; }
+    if (mynah_b200_qmat_sync(q)) return -1;
     return rc;
 }
 
@@ -990,11 +1052,14 @@ int mynah_b200_qmat_block_dots(const mynah_b200_qmat *q, const float *x, int T, 
     const size_t nd = (size_t)T * w.n * (w.k / 32);
     float *xd = nullptr, *od = nullptr, *sd = nullptr;
     int32_t *dd = nullptr;
-    MB_CUDA(cudaMalloc(&xd, (size_t)T * w.k * 4));
-    MB_CUDA(cudaMalloc(&od, (size_t)T * w.n * 4));
-    MB_CUDA(cudaMalloc(&sd, (size_t)T * 4));
-    MB_CUDA(cudaMalloc(&dd, nd * 4));
-    MB_CUDA(cudaMemcpyAsync(xd, x, (size_t)T * w.k * 4, cudaMemcpyHostToDevice, q->stream));
+    if (cudaMalloc(&xd, (size_t)T * w.k * 4) != cudaSuccess || cudaMalloc(&od, (size_t)T * w.n * 4) != cudaSuccess ||
+        cudaMalloc(&sd, (size_t)T * 4) != cudaSuccess || cudaMalloc(&dd, nd * 4) != cudaSuccess ||
+        cudaMemcpyAsync(xd, x, (size_t)T * w.k * 4, cudaMemcpyHostToDevice, q->stream) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(xd); cudaFree(od); cudaFree(sd); cudaFree(dd);
+        set_error("qmat_block_dots: device allocation or copy failed");
+        return -1;
+    }
     int rc = qgemv_a8(w, xd, od, T, dd, sd, q->stream);
     if (rc == 0) note_launch(2);
     cudaStreamSynchronize(q->stream);
@@ -1033,42 +1098,56 @@ int mynah_b200_gemm_wt(const float *x, const float *w, float *out, int T, int n,
 // One entry per (pointer, format, shape); calls on the same weight take the entry's lock (its
 // handle owns one stream and one scratch area), calls on different weights run side by side.
 namespace {
+// Entries are reference-counted: a call keeps its entry alive while it runs even if another thread
+// evicts the cache meanwhile (the device memory goes when the last user lets go).
 struct ResidentWeight {
     const void *host; int fmt, n, k;
     mynah_b200_qmat *q;
     std::mutex mu;
+    ResidentWeight(const void *h, int f, int n_, int k_, mynah_b200_qmat *q_) : host(h), fmt(f), n(n_), k(k_), q(q_) {}
+    ~ResidentWeight() { mynah_b200_qmat_free(q); }
 };
 std::mutex g_resident_mu;
-std::vector<ResidentWeight *> g_resident;
+std::vector<std::shared_ptr<ResidentWeight>> g_resident;
 
-ResidentWeight *resident_weight(const void *host, int fmt, const float *scales, int n, int k) {
-    std::lock_guard<std::mutex> lk(g_resident_mu);
-    for (ResidentWeight *e : g_resident)
+std::shared_ptr<ResidentWeight> resident_lookup(const void *host, int fmt, int n, int k) {
+    for (auto &e : g_resident)
         if (e->host == host && e->fmt == fmt && e->n == n && e->k == k) return e;
+    return nullptr;
+}
+
+std::shared_ptr<ResidentWeight> resident_weight(const void *host, int fmt, const float *scales, int n, int k) {
+    {
+        std::lock_guard<std::mutex> lk(g_resident_mu);
+        if (auto e = resident_lookup(host, fmt, n, k)) return e;
+    }
+    // upload and re-tile outside the lock: first-touch calls on different weights run side by side
     mynah_b200_qmat *q = mynah_b200_qmat_create(fmt, host, scales, n, k);
     if (!q) return nullptr;
-    ResidentWeight *e = new ResidentWeight{host, fmt, n, k, q};
-    g_resident.push_back(e);
-    return e;
+    auto fresh = std::make_shared<ResidentWeight>(host, fmt, n, k, q);
+    std::lock_guard<std::mutex> lk(g_resident_mu);
+    if (auto e = resident_lookup(host, fmt, n, k)) return e;      // another thread was first; ours is dropped
+    g_resident.push_back(fresh);
+    return fresh;
 }
 }  // namespace
 
 int mynah_b200_qgemm(const void *wq, int fmt, const float *scales, int n, int k, const float *x, float *out, int T, int flags) {
     if (!wq || !x || !out || T < 0 || n <= 0 || k <= 0) { set_error("qgemm: bad argument"); return -1; }
     if (!mynah_b200_available()) { set_error("qgemm: no sm_100 device"); return -1; }
-    ResidentWeight *e = resident_weight(wq, fmt, scales, n, k);
+    std::shared_ptr<ResidentWeight> e = resident_weight(wq, fmt, scales, n, k);
     if (!e) return -1;
     std::lock_guard<std::mutex> lk(e->mu);
     return mynah_b200_qmat_mul(e->q, x, out, T, flags);
 }
 
 void mynah_b200_weights_evict(void) {
-    std::lock_guard<std::mutex> lk(g_resident_mu);
-    for (ResidentWeight *e : g_resident) {
-        { std::lock_guard<std::mutex> l2(e->mu); mynah_b200_qmat_free(e->q); }
-        delete e;
+    std::vector<std::shared_ptr<ResidentWeight>> drop;
+    {
+        std::lock_guard<std::mutex> lk(g_resident_mu);
+        drop.swap(g_resident);
     }
-    g_resident.clear();
+    // entries still in use by a running call are freed when that call returns
 }
 
 int mynah_b200_weights_resident(void) {

@@ -30,11 +30,24 @@ const char *last_error();
         }                                                                                \
     } while (0)
 
+// CUDA keeps function attributes and the SM count per device; a process may drive several devices.
+// PerDevice remembers, for every device, the largest value configured so far (0 = nothing yet).
+static constexpr int MB_MAX_DEVICES = 64;
+struct PerDevice {
+    size_t v[MB_MAX_DEVICES];
+    // true when the current device has less than `want` on record; *dev receives the current device
+    bool below(size_t want, int *dev) const;
+    void record(int dev, size_t want);
+};
+int device_sm_count();      // SM count of the current device (cached per device; 148 if the query fails)
+
 static inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // Device status word codes written by kernels whose bounded waits ran out.
-enum { ST_OK = 0, ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA = 2, ST_TIMEOUT_EPILOGUE = 3 };
+// ST_RANGE: a value that had to become an fp16 (hi, lo) operand pair was not finite or reached 65504 in
+// magnitude (the planes cannot hold it), so the result is not to be trusted.
+enum { ST_OK = 0, ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA = 2, ST_TIMEOUT_EPILOGUE = 3, ST_RANGE = 4 };
 
 // A matrix stored as two fp16 planes: value = hi + lo * 2^-11 (22 significant bits).
 // The residual is kept pre-scaled by 2^11 so that it has the magnitude of hi and never
@@ -55,9 +68,13 @@ __device__ __forceinline__ uint32_t smem_u32(const void *p) {
 
 static constexpr float H16_LO_SCALE = 2048.0f;          // 2^11
 static constexpr float H16_LO_INV = 1.0f / 2048.0f;
-__device__ __forceinline__ void split_h16(float v, __half &hi, __half &lo) {
+// Returns false when v does not fit the planes (|v| >= 65504, inf or NaN): hi would be infinite and lo a NaN.
+// Producers that own a status word report ST_RANGE then.
+static constexpr float H16_MAX = 65504.0f;
+__device__ __forceinline__ bool split_h16(float v, __half &hi, __half &lo) {
     hi = __float2half_rn(v);
     lo = __float2half_rn((v - __half2float(hi)) * H16_LO_SCALE);
+    return fabsf(v) < H16_MAX;
 }
 
 // Stable sigmoid: never exponentiates a positive argument (the reference's

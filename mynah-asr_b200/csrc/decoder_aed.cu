@@ -236,7 +236,7 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     H16 enc_h = ws.planes((size_t)total_T * d_out);
     H16 encp = enc_h;
     if (!enc_h.hi) return -1;
-    if (split_to_h16(enc_dev, enc_h.hi, enc_h.lo, (size_t)total_T * d_out, stream)) return -1;
+    if (split_to_h16(enc_dev, enc_h.hi, enc_h.lo, (size_t)total_T * d_out, stream, status)) return -1;
     note_launch();
     if (has_aed_proj) {
         encp = ws.planes((size_t)total_T * D);

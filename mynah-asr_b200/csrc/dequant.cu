@@ -152,22 +152,25 @@ int format_block(int fmt) {
 
 // f32 -> (hi, lo) fp16 planes -------------------------------------------------------
 __global__ void split_kernel(const float *__restrict__ x, __half *__restrict__ hi, __half *__restrict__ lo,
-                             size_t n4, float scale) {
+                             size_t n4, float scale, int *status) {
     size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     if (i >= n4) return;
     const float4 v = reinterpret_cast<const float4 *>(x)[i];
     __align__(8) __half h[4], l[4];
-    split_h16(v.x * scale, h[0], l[0]); split_h16(v.y * scale, h[1], l[1]);
-    split_h16(v.z * scale, h[2], l[2]); split_h16(v.w * scale, h[3], l[3]);
+    bool fits = split_h16(v.x * scale, h[0], l[0]);
+    fits &= split_h16(v.y * scale, h[1], l[1]);
+    fits &= split_h16(v.z * scale, h[2], l[2]);
+    fits &= split_h16(v.w * scale, h[3], l[3]);
     reinterpret_cast<uint2 *>(hi)[i] = *reinterpret_cast<uint2 *>(h);
     if (lo) reinterpret_cast<uint2 *>(lo)[i] = *reinterpret_cast<uint2 *>(l);
+    if (!fits && status) atomicCAS(status, ST_OK, ST_RANGE);
 }
 
-int split_to_h16(const float *x, __half *hi, __half *lo, size_t n, cudaStream_t st) {
+int split_to_h16(const float *x, __half *hi, __half *lo, size_t n, cudaStream_t st, int *status) {
     if (n == 0) return 0;
     if (n % 4) { set_error("split_to_h16: element count %zu not a multiple of 4", n); return -1; }
     const size_t n4 = n / 4;
-    split_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(x, hi, lo, n4, 1.0f);
+    split_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(x, hi, lo, n4, 1.0f, status);
     MB_CUDA(cudaGetLastError());
     return 0;
 }

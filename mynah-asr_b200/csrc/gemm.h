@@ -33,7 +33,9 @@ struct GemmEpilogue {
 
 #ifdef __CUDACC__
 // Fused tail for 32 consecutive columns [nb, nb+32) of output row m.
-__device__ __forceinline__ void gemm_epilogue_row(const GemmEpilogue &ep, float (&v)[32], int m, int nb, int N) {
+// Returns false if a value written as fp16 planes was out of their range (see split_h16).
+__device__ __forceinline__ bool gemm_epilogue_row(const GemmEpilogue &ep, float (&v)[32], int m, int nb, int N) {
+    bool fits = true;
     const int nvalid = N - nb < 32 ? N - nb : 32;
 #pragma unroll
     for (int j = 0; j < 32; j++) {
@@ -79,7 +81,7 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmEpilogue &ep, float 
             for (int j = 0; j < 32; j += 8) {
                 __align__(16) __half h[8], l[8];
 #pragma unroll
-                for (int i = 0; i < 8; i++) split_h16(v[j + i], h[i], l[i]);
+                for (int i = 0; i < 8; i++) fits &= split_h16(v[j + i], h[i], l[i]);
                 *reinterpret_cast<uint4 *>(ph + j) = *reinterpret_cast<uint4 *>(h);
                 if (pl) *reinterpret_cast<uint4 *>(pl + j) = *reinterpret_cast<uint4 *>(l);
             }
@@ -88,13 +90,14 @@ __device__ __forceinline__ void gemm_epilogue_row(const GemmEpilogue &ep, float 
             for (int j = 0; j < 32; j++) {
                 if (j < nvalid) {
                     __half h, l;
-                    split_h16(v[j], h, l);
+                    fits &= split_h16(v[j], h, l);
                     ph[j] = h;
                     if (pl) pl[j] = l;
                 }
             }
         }
     }
+    return fits;
 }
 #endif
 

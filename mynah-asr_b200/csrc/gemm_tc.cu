@@ -181,6 +181,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
         const int half = (warp - 2) >> 2;              // even or odd 32-column chunks of the tile
         const int row = lg * 32 + lane;
         int lt = 0;
+        bool fits = true;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
             int m0, n0, width;
             units.at(tile, BN, m0, n0, width);
@@ -207,13 +208,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
                         tc_wait_ld();
                     }
                     const int nb = n0 + c * 32;
-                    if (m < M && nb < N) gemm_epilogue_row(ep, v, m, nb, N);
+                    if (m < M && nb < N) fits &= gemm_epilogue_row(ep, v, m, nb, N);
                 }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
         }
+        if (!fits) atomicCAS(status, ST_OK, ST_RANGE);
     }
     tc_fence_before();
     __syncthreads();
@@ -269,18 +271,14 @@ static int launch(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue
     } else {
         ta_lo = ta_hi; tb_lo = tb_hi;
     }
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDevice configured = {};
+    int dev = 0;
+    if (configured.below(Cfg::SMEM_BYTES, &dev)) {
         MB_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, NTERMS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg::SMEM_BYTES));
-        attr_set = true;
+        configured.record(dev, Cfg::SMEM_BYTES);
     }
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        MB_CUDA(cudaGetDevice(&dev));
-        MB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    }
+    const int sms = device_sm_count();
     // fewer tiles than SMs: the kernel cuts them into column strips (GemmUnits) when the grid leaves room
     const int total = cdiv(N, BN) * cdiv(M, BM), strips = BN % 128 == 0 ? 4 : BN % 64 == 0 ? 2 : 1;
     dim3 grid(total >= sms ? sms : total * strips <= sms ? total * strips : total * 2 <= sms && strips >= 2 ? total * 2 : total);
@@ -297,11 +295,7 @@ int gemm_tc(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, 
     // Narrower N tiles when the output has too few 128-wide tiles to occupy the SMs (small M: decoder
     // positions, streaming chunks): more CTAs pull the operands. An output element sees the same k order
     // and the same instruction sequence whatever the tile width, so its bits do not change with it.
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
-    }
+    const int sms = device_sm_count();
     // waves of CTAs x time of one tile (the MMAs scale with the tile width, prologue and epilogue do not)
     const int tm = cdiv(M, BM);
     int bn = 128;

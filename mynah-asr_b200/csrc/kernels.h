@@ -20,7 +20,8 @@ enum {
 int dequant_to_f32(int fmt, const void *src, const float *scales, float *dst, int n, int k, cudaStream_t st);
 size_t format_bytes(int fmt, int n, int k);
 int format_block(int fmt);
-int split_to_h16(const float *x, __half *hi, __half *lo, size_t n, cudaStream_t st);
+// status (optional): device word that receives ST_RANGE when a value does not fit the planes (|v| >= 65504 or not finite)
+int split_to_h16(const float *x, __half *hi, __half *lo, size_t n, cudaStream_t st, int *status = nullptr);
 
 // ---- elementwise.cu
 // Row LayerNorm (mean/var accumulated in double, eps 1e-5) with optional SiLU;
@@ -93,6 +94,10 @@ size_t qstream_tc_scratch_bytes(int n, int k);
 int qstream_tc(const QWeight &w, const float *x, int ldx, float *out, int ldo, const float *bias, int T, int *status,
                cudaStream_t st);
 int qgemv_a8(const QWeight &w, const float *x, float *out, int T, int32_t *block_dots, float *sx_out, cudaStream_t st);
+
+// ---- launch accounting (model.cu): every kernel launch of the library is counted
+void note_launch(int n = 1);
+long long launch_count(bool reset);
 
 // ---- decoder.cu
 int argmax_rows(const float *logits, int ld, const float *bias, int T, int V, int *best, cudaStream_t st);

@@ -114,7 +114,7 @@ int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *sca
         w.hi = (__half *)dev_alloc((size_t)n * k * 2);
         w.lo = (__half *)dev_alloc((size_t)n * k * 2);
         if (!w.hi || !w.lo) rc = -1;
-        else { rc = split_to_h16(tmp, w.hi, w.lo, (size_t)n * k, stream); note_launch(); }
+        else { rc = split_to_h16(tmp, w.hi, w.lo, (size_t)n * k, stream, status); note_launch(); }
     }
     cudaStreamSynchronize(stream);
     if (rc == 0 && want_f32) { w.f32 = tmp; owned.push_back(tmp); }
@@ -143,7 +143,8 @@ int Model::check_status(const char *where) {
     MB_CUDA(cudaMemcpyAsync(&st, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
     MB_CUDA(cudaStreamSynchronize(stream));
     if (st != 0) {
-        set_error("%s: a bounded wait inside the contraction kernel ran out (code %d)", where, st);
+        if (st == ST_RANGE) set_error("%s: a value reached the fp16 operand range (|v| >= 65504) or was not finite", where);
+        else set_error("%s: a bounded wait inside the contraction kernel ran out (code %d)", where, st);
         cudaMemsetAsync(status, 0, sizeof(int), stream);
         return -1;
     }
@@ -294,7 +295,10 @@ int Model::encoder_layers(float *x, const std::vector<int> &lens, int left, int 
 }
 
 // encoder_projector when present, else copy (src/encoder.c:573-590)
-int Model::encoder_post(const float *x, int M, float *out) {
+int Model::encoder_post(const float *x, const std::vector<int> &lens, const int *prompt_ids, float *out) {
+    int M = 0;
+    for (int l : lens) M += l;
+    if (M == 0) return 0;
     if (!has_encproj) {
         MB_CUDA(cudaMemcpyAsync(out, x, (size_t)M * d_model * sizeof(float), cudaMemcpyDeviceToDevice, stream));
         return 0;
@@ -302,8 +306,32 @@ int Model::encoder_post(const float *x, int M, float *out) {
     const size_t mark = ws.off;
     H16 h = ws.planes((size_t)M * d_model);
     if (!h.lo) return -1;
-    if (split_to_h16(x, h.hi, h.lo, (size_t)M * d_model, stream)) return -1;
+    if (split_to_h16(x, h.hi, h.lo, (size_t)M * d_model, stream, status)) return -1;
     note_launch();
+    if (has_prompt) {
+        // concat(x, onehot(p)) W1^T + b1 = x W1[:, :d]^T + bias1[p]; ReLU; W2 (+b2); then the projector
+        // (src/encoder.c:591-614). Runs of segments with the same prompt share one contraction.
+        const int di = prompt_inter;
+        H16 mid = ws.planes((size_t)M * di), fused = ws.planes((size_t)M * d_model);
+        if (!mid.lo || !fused.lo) return -1;
+        int row = 0;
+        for (size_t b = 0; b < lens.size();) {
+            const int pid = prompt_ids ? prompt_ids[b] : 0;
+            if (pid < 0 || pid >= num_prompts) { set_error("encoder_post: prompt id %d outside [0, %d)", pid, num_prompts); return -1; }
+            int rows = 0;
+            size_t e = b;
+            while (e < lens.size() && (prompt_ids ? prompt_ids[e] : 0) == pid) rows += lens[e++];
+            if (rows > 0) {
+                H16 hs{h.hi + (size_t)row * d_model, h.lo + (size_t)row * d_model};
+                H16 ms{mid.hi + (size_t)row * di, mid.lo + (size_t)row * di};
+                if (gemm(hs, d_model, prompt_l1, epi(OUT_H16, ACT_RELU, 1.f, prompt_bias1 + (size_t)pid * di, nullptr, 0, ms, di), rows)) return -1;
+            }
+            row += rows;
+            b = e;
+        }
+        if (gemm(mid, di, prompt_l2, epi(OUT_H16, ACT_NONE, 1.f, prompt_l2.bias, nullptr, 0, fused, d_model), M)) return -1;
+        h = fused;
+    }
     if (gemm(h, d_model, encproj, epi(OUT_F32, ACT_NONE, 1.f, encproj.bias, out, d_out), M)) return -1;
     ws.off = mark;
     return 0;
@@ -332,7 +360,7 @@ int Model::decode_ctc(const float *enc_dev, int T, std::vector<int> &tokens, std
     float *logits = ws.get<float>((size_t)T * V);
     int *best = ws.get<int>(T);
     if (!h.lo || !logits || !best) return -1;
-    if (split_to_h16(enc_dev, h.hi, h.lo, (size_t)T * d, stream)) return -1;
+    if (split_to_h16(enc_dev, h.hi, h.lo, (size_t)T * d, stream, status)) return -1;
     if (gemm(h, d, ctc_head, epi(OUT_F32, ACT_NONE, 1.f, ctc_head.bias, logits, V), T)) return -1;
     if (argmax_rows(logits, V, nullptr, T, V, best, stream)) return -1;
     note_launch(2);
@@ -356,10 +384,7 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
     if (!has_dec) { set_error("model has no transducer decoder"); return -1; }
     std::vector<int> offs(Ball);
     for (int b = 0, o = 0; b < Ball; o += lens[b], b++) offs[b] = o;
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
     const int nw = (vocab + cfg.n_durations + 15) / 16;     // candidate slots: one per 16-row block of the head
-    (void)sms;
     for (int g0 = 0; g0 < Ball; g0 += DEC_MAX_B) {
         const int B = Ball - g0 < DEC_MAX_B ? Ball - g0 : DEC_MAX_B;
         int max_len = 0;

@@ -75,6 +75,7 @@ struct StreamState {
     float *ss_cache[3] = {nullptr, nullptr, nullptr};   // last input frame of each subsampling stage: [S,F0], [S,F1,C], [S,F2,C]
     __half *k_cache = nullptr, *v_cache = nullptr;      // [L][S][left][d] fp16
     float *conv_cache = nullptr;                        // [L][S][k-1][d] GLU rows
+    std::vector<int> prompt_ids;                        // prompt-conditioned encoders: one id per stream (empty = 0)
     std::vector<void *> owned;
 };
 
@@ -109,6 +110,12 @@ struct Model {
     const float *conv_in_w = nullptr, *conv_in_b = nullptr, *dw_w[2] = {nullptr, nullptr}, *dw_b[2] = {nullptr, nullptr};
     QWeight pw[2], ss_lin, encproj;
     bool has_encproj = false;
+    // prompt MLP of encoder_post (src/encoder.c:591-614): the one-hot columns of linear_1 are folded into a
+    // per-prompt bias table, bias1[p] = b1 + W1[:, d + p]
+    bool has_prompt = false;
+    int num_prompts = 0, prompt_inter = 0;
+    QWeight prompt_l1, prompt_l2;                    // [inter, d] (the first d columns of linear_1), [d, inter]
+    float *prompt_bias1 = nullptr;                   // [num_prompts, inter]
 
     // decoders
     bool has_ctc = false, has_dec = false;
@@ -146,7 +153,9 @@ struct Model {
     int gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep, int M);
     int subsample_item(const float *feats_dev, int t_mel, float *x_out, int *t_out);
     int encoder_layers(float *x, const std::vector<int> &lens, int left, int right, int first_layer, int n_run);
-    int encoder_post(const float *x, int M, float *out);
+    // x [sum lens, d_model] -> out [sum lens, d_out]; prompt_ids (one per segment, may be null = all 0) select the
+    // one-hot column of a prompt-conditioned model and are ignored otherwise
+    int encoder_post(const float *x, const std::vector<int> &lens, const int *prompt_ids, float *out);
     int decode_ctc(const float *enc_dev, int T, std::vector<int> &tokens, std::vector<int> &frames);
     int decode_greedy(const float *enc_dev, const std::vector<int> &lens, std::vector<std::vector<int>> &tokens,
                       std::vector<std::vector<int>> &frames);
@@ -203,7 +212,5 @@ struct GreedyDev {
 };
 
 int greedy_launch(const GreedyDev &p, cudaStream_t st);
-void note_launch(int n = 1);
-long long launch_count(bool reset);
 
 }  // namespace mb

@@ -461,6 +461,11 @@ extern "C" int mynah_b200_qmat_mul_a8_static(const mynah_b200_qmat *m, const flo
         return -1;
     }
     if (w.k % 32) { set_error("qmat_mul_a8_static: k=%d not a multiple of 32", w.k); return -1; }
+    // every refusal happens before the first launch, so a refused call never touches the shared array
+    if (w.fmt != FMT_GGML_Q8_0 && w.fmt != FMT_GGML_Q4_0 && w.fmt != FMT_MYNAH_Q8 && w.fmt != FMT_MYNAH_Q4) {
+        set_error("qmat_mul_a8_static: format %d has no int8-activation mode (Q8_0, Q4_0 and the two native formats have)", w.fmt);
+        return -1;
+    }
     unsigned char *scratch = a8_scratch_for_current_device();      // first call on a device resolves the symbol
     if (!scratch) return -1;
     int8_t *qx = reinterpret_cast<int8_t *>(scratch);
@@ -474,10 +479,12 @@ extern "C" int mynah_b200_qmat_mul_a8_static(const mynah_b200_qmat *m, const flo
     case FMT_GGML_Q4_0: qgemv_a8_kernel<FMT_GGML_Q4_0><<<grid, 256, 0, v.stream>>>(w.raw, w.scales, w.n, w.k, rb, qx, sx, out_dev, nullptr, T); break;
     case FMT_MYNAH_Q8: qgemv_a8_kernel<FMT_MYNAH_Q8><<<grid, 256, 0, v.stream>>>(w.raw, w.scales, w.n, w.k, rb, qx, sx, out_dev, nullptr, T); break;
     case FMT_MYNAH_Q4: qgemv_a8_kernel<FMT_MYNAH_Q4><<<grid, 256, 0, v.stream>>>(w.raw, w.scales, w.n, w.k, rb, qx, sx, out_dev, nullptr, T); break;
-    default: set_error("qmat_mul_a8_static: format %d has no int8-activation mode", w.fmt); return -1;
+    default: break;      // refused above
     }
-    if (cudaGetLastError() != cudaSuccess) { set_error("qmat_mul_a8_static: launch failed"); return -1; }
-    const cudaError_t e = cudaStreamSynchronize(v.stream);
+    const cudaError_t le = cudaGetLastError();
+    note_launch(2);
+    const cudaError_t e = le != cudaSuccess ? le : cudaStreamSynchronize(v.stream);
+    if (le != cudaSuccess) cudaStreamSynchronize(v.stream);    // the first kernel may be running: do not return over it
     if (e != cudaSuccess) { set_error("qmat_mul_a8_static: %s", cudaGetErrorString(e)); return -1; }
     return 0;
 }

@@ -258,12 +258,7 @@ qgemv_mma_kernel(const QmArgs a, const int ks_log2) {
 
 int qgemv_mma(const QWeight &w, const float *x, int ldx, float *out, int ldo, const float *bias, int T, cudaStream_t st) {
     if (!w.mma_q || !w.mma_d) { set_error("qgemv_mma: weight has no re-tiled planes"); return -1; }
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        MB_CUDA(cudaGetDevice(&dev));
-        MB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-    }
+    const int sms = device_sm_count();
     const int ntiles = cdiv(w.n, 16);
     int ks_log2 = 0;                      // split K over warps until the grid is full (or slices get short)
     while (ks_log2 < 3 && (ntiles << ks_log2) < sms * QM_WARPS * 2 && (w.k >> (ks_log2 + 1)) >= 512) ks_log2++;

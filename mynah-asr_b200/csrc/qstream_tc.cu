@@ -141,12 +141,7 @@ static int qs_pick_nslice(int n, int k, int sms) {
 }
 
 static int qs_sm_count() {
-    static int sms = 0;
-    if (!sms) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 0;
-    }
-    return sms > 0 ? sms : 148;
+    return device_sm_count();
 }
 
 size_t qstream_tc_scratch_bytes(int n, int k) {
@@ -585,11 +580,12 @@ static size_t qs_smem_bytes(int fmt, int nt, int max_slice_st) {
 
 template <int FMT, int NT>
 static int qs_launch(const QsArgs &a, int grid, cudaStream_t st) {
-    static size_t configured = 0;                // largest dynamic shared memory size requested so far
+    static PerDevice configured = {};            // largest dynamic shared memory size requested so far, per device
     const size_t smem = qs_smem_bytes(FMT, NT, a.max_slice_st);
-    if (smem > configured) {
+    int dev = 0;
+    if (configured.below(smem, &dev)) {
         MB_CUDA(cudaFuncSetAttribute(qstream_tc_kernel<FMT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
+        configured.record(dev, smem);
     }
     qstream_tc_kernel<FMT, NT><<<grid, QS_THREADS, smem, st>>>(a);
     MB_CUDA(cudaGetLastError());

@@ -317,10 +317,11 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
     note_launch();
     const size_t attn_smem = ((size_t)K + 2 * dk + 32) * sizeof(float);
     if (attn_smem > 200 * 1024) { set_error("stream_step: context too long for the attention kernel"); return -1; }
-    static size_t attn_smem_set = 0;
-    if (attn_smem > attn_smem_set) {
+    static PerDevice attn_smem_set = {};
+    int cur_dev = 0;
+    if (attn_smem_set.below(attn_smem, &cur_dev)) {
         MB_CUDA(cudaFuncSetAttribute(stream_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem));
-        attn_smem_set = attn_smem;
+        attn_smem_set.record(cur_dev, attn_smem);
     }
     const H16 none{nullptr, nullptr};
     const int leftn = st.left > 0 ? st.left : 1;
@@ -354,7 +355,10 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
         if (layer_norm(x, L.ln_out_w, L.ln_out_b, x, none, M, d, ACT_NONE, stream)) return -1;
         note_launch(9);
     }
-    if (encoder_post(x, M, out)) return -1;
+    {   // rows are stream-major: Q rows per stream, each stream with its own prompt id
+        const std::vector<int> post_lens((size_t)st.S, Q);
+        if (encoder_post(x, post_lens, st.prompt_ids.empty() ? nullptr : st.prompt_ids.data(), out)) return -1;
+    }
     // cache bookkeeping of the host side (src/encoder.c:868 and the ring's start)
     if (st.left > 0) {
         const int total = valid + Q;

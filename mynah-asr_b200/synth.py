@@ -173,6 +173,9 @@ class ModelConfig:
     aed_ffn: int = 0
     aed_max_seq: int = 1024
     aed_max_gen_delta: int = 50
+    # Nemotron-style prompt-conditioned post-encoder MLP (src/encoder.c:591-614); 0 = none
+    num_prompts: int = 0
+    prompt_inter: int = 0
     d_out: int = field(init=False, default=0)
 
     def __post_init__(self):
@@ -330,6 +333,12 @@ def make_model(cfg: ModelConfig, seed: int = 0, weight_std: float = 0.02):
         H, V, ND = cfg.pred_hidden, cfg.vocab, len(cfg.durations)
         f32t("encoder_projector.weight", rng.standard_normal((H, d), dtype=np.float32) / np.sqrt(d))
         f32t("encoder_projector.bias", np.zeros(H))
+        if cfg.num_prompts:
+            di = cfg.prompt_inter or 2 * d
+            f32t("prompt_projector.linear_1.weight", rng.standard_normal((di, d + cfg.num_prompts), dtype=np.float32) / np.sqrt(d))
+            f32t("prompt_projector.linear_1.bias", normal(di))
+            f32t("prompt_projector.linear_2.weight", rng.standard_normal((d, di), dtype=np.float32) / np.sqrt(di))
+            f32t("prompt_projector.linear_2.bias", normal(d))
         f32t("decoder.embedding.weight", rng.standard_normal((V, H), dtype=np.float32))
         for l in range(cfg.pred_layers):
             f32t(f"decoder.lstm.weight_ih_l{l}", rng.standard_normal((4 * H, H), dtype=np.float32) / np.sqrt(H))

@@ -64,6 +64,9 @@ def oracle_model(cfg, tensors) -> dict:
         M["layers"].append(L)
     if "encoder_projector.weight" in W:
         M["encproj_w"], M["encproj_b"] = W["encoder_projector.weight"], W["encoder_projector.bias"]
+    if "prompt_projector.linear_1.weight" in W:
+        for i in (1, 2):
+            M[f"prompt_l{i}_w"], M[f"prompt_l{i}_b"] = W[f"prompt_projector.linear_{i}.weight"], W[f"prompt_projector.linear_{i}.bias"]
     if "ctc_head.weight" in W:
         M["ctc_w"] = W["ctc_head.weight"].reshape(W["ctc_head.weight"].shape[0], -1)
         M["ctc_b"] = W["ctc_head.bias"]

@@ -404,15 +404,24 @@ def encoder_layer(L, x, pe, H, causal, left=-1, right=-1):
     return layer_norm(x, L["ln_out_w"], L["ln_out_b"])
 
 
-def encoder_post(M, x):
-    """encoder_projector when present, else identity (encoder.c:573-590).
-    The prompt MLP (Nemotron) is not restated: no config here carries one."""
+def encoder_post(M, x, prompt_id=0):
+    """encoder_projector when present, else identity (encoder.c:573-590); for a
+    prompt-conditioned model the one-hot prompt is concatenated to every frame and goes
+    through linear_1 (+b, ReLU) and linear_2 (+b) first (encoder.c:591-614)."""
     if M.get("encproj_w") is None:
         return x.copy()
+    if M.get("prompt_l1_w") is not None:
+        T, d = x.shape
+        np_ = M["prompt_l1_w"].shape[1] - d
+        cat = np.zeros((T, d + np_), f32)
+        cat[:, :d] = x
+        cat[:, d + prompt_id] = 1.0
+        mid = np.maximum(gemm_wt(cat, M["prompt_l1_w"]) + M["prompt_l1_b"][None, :], f32(0)).astype(f32)
+        x = (gemm_wt(mid, M["prompt_l2_w"]) + M["prompt_l2_b"][None, :]).astype(f32)
     return (gemm_wt(x, M["encproj_w"]) + M["encproj_b"][None, :]).astype(f32)
 
 
-def encoder_forward(M, feats, left=-1, right=-1, raw=False, n_layers=None):
+def encoder_forward(M, feats, left=-1, right=-1, raw=False, n_layers=None, prompt_id=0):
     """feats [T_mel, n_mels] (valid frames) -> [T, d_out] (encoder.c:1013-1039)."""
     x = subsampling_forward(M["ss"], feats, M["causal"])
     if M.get("xscale", 1.0) != 1.0:
@@ -421,7 +430,7 @@ def encoder_forward(M, feats, left=-1, right=-1, raw=False, n_layers=None):
     pe = pos_emb(T, d)
     for L in M["layers"][:n_layers]:
         x = encoder_layer(L, x, pe, M["n_heads"], M["causal"], left, right)
-    return x if raw else encoder_post(M, x)
+    return x if raw else encoder_post(M, x, prompt_id)
 
 
 # --------------------------------------------------------------------------
@@ -669,7 +678,7 @@ def _stream_conv_module(L, x, cache):
     return _lin(L, "pw2_w", silu(layer_norm(c, L["cnorm_w"], L["cnorm_b"]))), gp[Q:].copy()
 
 
-def enc_stream_step(st, mel, is_last=False):
+def enc_stream_step(st, mel, is_last=False, prompt_id=0):
     """mynah_asr_enc_stream_step (src/encoder.c:809-872): one chunk of mel frames [n, n_mels] (n = st.need())
     through the subsampling and every layer with the caches; returns [q, d_out]."""
     M = st.M
@@ -688,16 +697,16 @@ def enc_stream_step(st, mel, is_last=False):
         x = (x + f32(0.5) * half_ffn(L, x, 1)).astype(f32)
         x = layer_norm(x, L["ln_out_w"], L["ln_out_b"])
     st.valid = min(st.valid + Q, st.left)
-    return encoder_post(M, x)
+    return encoder_post(M, x, prompt_id)
 
 
-def stream_encode(M, mel, left, right):
+def stream_encode(M, mel, left, right, prompt_id=0):
     """Feeds valid mel frames through the streaming encoder in the chunk sizes it asks for
     (the loop of mynah_asr_stream_feed, src/mynah_asr.c:868-890); returns the concatenated [T, d_out]."""
     st = EncStream(M, left, right, mel.shape[1])
     outs, pos, T = [], 0, mel.shape[0]
     while pos < T:
         n = st.need()
-        outs.append(enc_stream_step(st, mel[pos:pos + n], pos + n >= T))
+        outs.append(enc_stream_step(st, mel[pos:pos + n], pos + n >= T, prompt_id))
         pos += n
     return np.concatenate(outs)

@@ -46,6 +46,11 @@ def lib():
         L.ref_encoder_forward.argtypes = [C.c_void_p, c_fp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, c_ip]
         L.ref_encoder_forward_batch.argtypes = [C.c_void_p, C.POINTER(c_fp), c_ip, C.c_int, C.c_int, C.c_int,
                                                 C.c_int, C.POINTER(C.c_void_p), c_ip]
+        L.ref_encoder_forward_p.restype = C.c_void_p
+        L.ref_encoder_forward_p.argtypes = [C.c_void_p, c_fp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, c_ip]
+        L.ref_encoder_forward_batch_p.argtypes = [C.c_void_p, C.POINTER(c_fp), c_ip, C.c_int, C.c_int, c_ip, C.c_int,
+                                                  C.c_int, C.POINTER(C.c_void_p), c_ip]
+        L.ref_stream_step_p.argtypes = [C.c_void_p, c_fp, C.c_int, C.c_int, C.c_int, C.c_int, c_fp]
         L.ref_ctc_decode.argtypes = [C.c_void_p, c_fp, C.c_int, c_ip, c_ip, C.c_int]
         L.ref_greedy_decode.argtypes = [C.c_void_p, c_fp, C.c_int, c_ip, c_ip, C.c_int]
         L.ref_aed_open.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
@@ -154,22 +159,30 @@ class RefModel:
         lib().ref_encoder_post(self.h, _fp(x), x.shape[0], _fp(out))
         return out
 
-    def encoder_forward(self, feats, left=-1, right=-1, raw=False):
+    def encoder_forward(self, feats, left=-1, right=-1, raw=False, prompt_id=0):
         feats = np.ascontiguousarray(feats, np.float32)
         t = C.c_int()
-        p = lib().ref_encoder_forward(self.h, _fp(feats), feats.shape[0], feats.shape[1], left, right, int(raw),
-                                      C.byref(t))
+        if prompt_id and not raw:
+            p = lib().ref_encoder_forward_p(self.h, _fp(feats), feats.shape[0], feats.shape[1], prompt_id, left, right,
+                                            C.byref(t))
+        else:
+            p = lib().ref_encoder_forward(self.h, _fp(feats), feats.shape[0], feats.shape[1], left, right, int(raw),
+                                          C.byref(t))
         assert p
         return _take(p, (t.value, self.d_model if raw else self.d_out))
 
-    def encoder_forward_batch(self, feats_list, left=-1, right=-1):
+    def encoder_forward_batch(self, feats_list, left=-1, right=-1, prompt_ids=None):
         B = len(feats_list)
         fl = [np.ascontiguousarray(f, np.float32) for f in feats_list]
         ptrs = (c_fp * B)(*[_fp(f) for f in fl])
         tm = (C.c_int * B)(*[f.shape[0] for f in fl])
         outs = (C.c_void_p * B)()
         touts = (C.c_int * B)()
-        rc = lib().ref_encoder_forward_batch(self.h, ptrs, tm, B, fl[0].shape[1], left, right, outs, touts)
+        if prompt_ids is not None:
+            pid = (C.c_int * B)(*prompt_ids)
+            rc = lib().ref_encoder_forward_batch_p(self.h, ptrs, tm, B, fl[0].shape[1], pid, left, right, outs, touts)
+        else:
+            rc = lib().ref_encoder_forward_batch(self.h, ptrs, tm, B, fl[0].shape[1], left, right, outs, touts)
         assert rc == 0
         return [_take(outs[b], (touts[b], self.d_out)) for b in range(B)]
 
@@ -201,7 +214,7 @@ class RefModel:
         assert n >= 0
         return out[:n].copy()
 
-    def stream_encode(self, mel, left, right):
+    def stream_encode(self, mel, left, right, prompt_id=0):
         """Feed valid mel frames through the cache-aware streaming encoder in the
         exact chunk sizes it asks for; returns the concatenated [T, d_out]."""
         es = lib().ref_stream_open(self.h, left, right, self.n_mels)
@@ -212,7 +225,7 @@ class RefModel:
             need = lib().ref_stream_need(es)
             chunk = np.ascontiguousarray(mel[pos:pos + need], np.float32)
             last = int(pos + need >= T)
-            q = lib().ref_stream_step(es, _fp(chunk), chunk.shape[0], mel.shape[1], last, _fp(buf))
+            q = lib().ref_stream_step_p(es, _fp(chunk), chunk.shape[0], mel.shape[1], prompt_id, last, _fp(buf))
             if q <= 0:
                 break
             outs.append(buf[:q].copy())

@@ -139,6 +139,25 @@ float *ref_encoder_forward(const ref_model *m, const float *feats, int t_mel, in
                : mynah_asr_encoder_forward(&m->enc, feats, t_mel, n_mels, 0, left, right, t_out);
 }
 
+/* the same two with a prompt id (prompt-conditioned models, src/encoder.c:591-614) */
+void ref_encoder_post_p(const ref_model *m, const float *x, int T, int prompt_id, float *out) {
+    mynah_asr_encoder_post(&m->enc, x, T, prompt_id, out);
+}
+float *ref_encoder_forward_p(const ref_model *m, const float *feats, int t_mel, int n_mels, int prompt_id,
+                             int left, int right, int *t_out) {
+    return mynah_asr_encoder_forward(&m->enc, feats, t_mel, n_mels, prompt_id, left, right, t_out);
+}
+int ref_encoder_forward_batch_p(const ref_model *m, const float *const *feats, const int *t_mel,
+                                int batch, int n_mels, const int *prompt_ids, int left, int right,
+                                float **outs, int *t_outs) {
+    return mynah_asr_encoder_forward_batch(&m->enc, feats, t_mel, batch, n_mels, prompt_ids, left,
+                                           right, outs, t_outs);
+}
+int ref_stream_step_p(mynah_asr_enc_stream *es, const float *mel, int n_mel, int n_mels, int prompt_id,
+                      int is_last, float *out) {
+    return mynah_asr_enc_stream_step(es, mel, n_mel, n_mels, prompt_id, is_last, out);
+}
+
 int ref_encoder_forward_batch(const ref_model *m, const float *const *feats, const int *t_mel,
                               int batch, int n_mels, int left, int right, float **outs,
                               int *t_outs) {

@@ -24,6 +24,11 @@ AED = {
     "aed_proj": dict(d_model=128, n_layers=1, n_heads=4, ffn_dim=256, n_mels=80, decoder="aed", vocab=211,
                      aed_d=64, aed_layers=3, aed_heads=2, aed_ffn=192, aed_max_seq=48, wtype="q4_0"),
 }
+# Nemotron-style prompt-conditioned model: causal RNNT whose post-encoder MLP takes a one-hot prompt id
+PROMPT = {"rnnt_prompt": dict(d_model=128, n_layers=1, n_heads=2, ffn_dim=256, n_mels=80, decoder="rnnt", vocab=49,
+                              pred_hidden=64, pred_layers=1, wtype="q8_0", causal=True, normalize=False, blank_bias=1.5,
+                              max_symbols=3, num_prompts=5, prompt_inter=192)}
+PROMPT_IDS = (3, 0, 4)
 STREAM_CONTEXTS = ((6, 0), (8, 1), (70, 0))      # (left, right) attention contexts of the streaming tests
 AED_PROMPT = (7, 9, 200, 11)
 AED_CAP = 24
@@ -32,7 +37,7 @@ SEEDS = {"aed_same": 4}       # weight seeds whose greedy streams do not fall in
 
 def build(synth, name, seed=None):
     seed = SEEDS.get(name, 1) if seed is None else seed
-    cfg = synth.config(name, **(TINY[name] if name in TINY else AED[name]))
+    cfg = synth.config(name, **(TINY[name] if name in TINY else AED[name] if name in AED else PROMPT[name]))
     return cfg, synth.make_model(cfg, seed=seed)
 
 

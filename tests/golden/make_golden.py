@@ -5,7 +5,7 @@ on seeded synthetic models and audio. Run in a container that has the reference:
     make -C oracle && python tests/golden/make_golden.py
 
 The fixtures pin both the numpy oracle (tests/test_oracle_pin.py) and the CUDA path
-(tests/test_golden_gpu.py) on machines where the reference itself is absent.
+(tests/test_stages_gpu.py, tests/test_qmat_gpu.py, tests/test_aed_gpu.py, tests/test_stream_gpu.py) on machines where the reference itself is absent.
 Inputs are regenerated from seeds by the tests; only reference OUTPUTS are stored.
 """
 import os
@@ -85,6 +85,34 @@ def aed(name):
     np.savez_compressed(os.path.join(HERE, f"ref_{name}.npz"), **out)
 
 
+def prompt(name):
+    """mynah_asr_encoder_post with a prompt id (src/encoder.c:591-614): single, packed batch with one id per item,
+    streaming, and the greedy tokens that follow."""
+    cfg, tensors = cases.build(synth, name)
+    d = tempfile.mkdtemp()
+    wp, mp = model_io.write_reference_files(d, cfg, tensors, synth)
+    rm = R.RefModel(wp, mp, n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
+                    max_symbols=cfg.max_symbols, causal=int(cfg.causal))
+    audio = [synth.synth_audio(s, seed=21 + i) for i, s in enumerate((1.6, 1.0, 1.3))]
+    feats = []
+    for a in audio:
+        f, v = rm.log_mel(a)
+        feats.append(f[:v])
+    out = {}
+    for i, pid in enumerate(cases.PROMPT_IDS):
+        out[f"enc{i}"] = rm.encoder_forward(feats[i], prompt_id=pid)
+        t, f = rm.greedy_decode(out[f"enc{i}"], cfg.max_symbols)
+        out[f"tokens{i}"], out[f"frames{i}"] = np.array(t, np.int32), np.array(f, np.int32)
+    out["enc0_p0"] = rm.encoder_forward(feats[0])
+    b = rm.encoder_forward_batch(feats, prompt_ids=cases.PROMPT_IDS)
+    for i in range(3):
+        out[f"batch{i}"] = b[i]
+    out["stream0"] = rm.stream_encode(feats[0], 6, 0, prompt_id=cases.PROMPT_IDS[0])
+    rm.close()
+    np.savez_compressed(os.path.join(HERE, f"ref_{name}.npz"), **out)
+    print(name, {k: v.shape for k, v in out.items()}, "distinct", [len(set(out[f"tokens{i}"].tolist())) for i in range(3)])
+
+
 def qmat():
     """mynah_asr_qmat_mul on weights quantised by the reference's own load-time
     quantiser, T = 1, 4 (int8-activation dots) and 48 (dequant + sgemm): the cases
@@ -105,8 +133,15 @@ def qmat():
 
 if __name__ == "__main__":
     assert R.available(), "build oracle/_ref first: make -C oracle"
+    only = sys.argv[1:]
+    if only:                      # regenerate only the named fixtures
+        for name in only:
+            (prompt if name in cases.PROMPT else aed if name in cases.AED else pipeline)(name)
+        sys.exit(0)
     for name in cases.TINY:
         pipeline(name)
     for name in cases.AED:
         aed(name)
+    for name in cases.PROMPT:
+        prompt(name)
     qmat()

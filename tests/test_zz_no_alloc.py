@@ -45,6 +45,9 @@ def test_static_scratch_matches_regular_entry_point(gpu_pkg, synth):
             m.mul_a8_static(xd.data_ptr(), od.data_ptr(), T)
             got = od.cpu().numpy()
             assert np.array_equal(got, want), what             # same kernels, same bits
+            if what == "native int8":
+                # the native format has a bit-exact CPU restatement: (float)int32 * ws * sx
+                assert np.array_equal(got, O.qmat_mul_a8_q8(x, q8, s8)), "native int8 against the oracle"
         m.close()
 
 
@@ -64,3 +67,9 @@ def test_static_scratch_limits(gpu_pkg):
     with pytest.raises(gpu_pkg.BackendError, match="exceed"):  # k beyond the limit
         big.mul_a8_static(xd.data_ptr(), od.data_ptr(), 1)
     big.close()
+    # a format without an int8-activation mode is refused before anything is launched
+    f32 = gpu_pkg.QMat(gpu_pkg.F32, np.ones((4, 64), np.float32), 4, 64)
+    xd, od = _device_buffers(torch, np.ones((2, 64), np.float32), 4)
+    with pytest.raises(gpu_pkg.BackendError, match="int8-activation"):
+        f32.mul_a8_static(xd.data_ptr(), od.data_ptr(), 2)
+    f32.close()
