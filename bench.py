@@ -64,13 +64,22 @@ def workload_config(synth, name: str):
     return synth.config(name, blank_bias=BLANK_BIAS[name]) if name in BLANK_BIAS else synth.config(name)
 
 
-def cached_model(synth, name: str, rank: int, barrier):
+def recipe_std(cfg, recipe: str) -> float:
+    """Standard deviation of the quantised linears. "baseline": N(0, 0.02) as the configs word it — through 17-42
+    random layers the encoder output then hardly moves over time and the greedy stream repeats one token.
+    "diverse": 0.32 / sqrt(d_model) (0.01 at d = 1024), under which the time-varying part of the signal
+    survives the stack and the greedy stream has tens of distinct tokens; used for the supplementary parity
+    report, never for the timing."""
+    return 0.02 if recipe == "baseline" else 0.32 / float(np.sqrt(cfg.d_model))
+
+
+def cached_model(synth, name: str, rank: int, barrier, recipe: str = "baseline"):
     """Synthetic weights are generated once per box (rank 0) and shared through a file."""
     os.makedirs(CACHE, exist_ok=True)
     cfg = workload_config(synth, name)
-    path = os.path.join(CACHE, f"{name}_seed0_bb{cfg.blank_bias:g}.pkl")
+    path = os.path.join(CACHE, f"{name}_seed0_bb{cfg.blank_bias:g}" + ("" if recipe == "baseline" else "_" + recipe) + ".pkl")
     if rank == 0 and not os.path.exists(path):
-        tensors = synth.make_model(cfg, seed=0)
+        tensors = synth.make_model(cfg, seed=0, weight_std=recipe_std(cfg, recipe))
         with open(path + ".tmp", "wb") as f:
             pickle.dump({k: (t.ggml_type, t.shape, t.raw) for k, t in tensors.items()}, f, protocol=4)
         os.replace(path + ".tmp", path)
@@ -125,9 +134,82 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+CPU_MODES = {"f32": 0, "int8": 1, "int4": 2}     # quant argument of the reference's loaders (src/qmat.h:6-9)
+
+
+def ref_paths(args, cfg, tensors, synth, recipe="baseline"):
+    from oracle import model_io
+    d = os.path.join(CACHE, f"{args.workload}_ref" + ("" if recipe == "baseline" else "_" + recipe))
+    if not os.path.exists(os.path.join(d, "model.safetensors")):
+        model_io.write_reference_files(d, cfg, tensors, synth)
+    return os.path.join(d, "model.safetensors"), os.path.join(d, "mel_filters.safetensors")
+
+
+def ref_open(args, cfg, tensors, synth, recipe="baseline", cpu_mode="f32"):
+    """The compiled reference over the same effective weights. cpu_mode f32: its default path for a ggml-quantised
+    file (blocks decoded to f32 at load, OpenBLAS sgemm); int8 / int4: its own load-time quantisation of those
+    weights (`--quant`, src/qmat.c:80-143: integer dots below 17 rows, dequant + sgemm above, or the threaded
+    int8 GEMM above when MYNAH_ASR_QGEMM=1 is in the environment)."""
+    from oracle import ref_binding as R
+    wp, mp = ref_paths(args, cfg, tensors, synth, recipe)
+    rm = R.RefModel(wp, mp, quant=CPU_MODES[cpu_mode], n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
+                    max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), causal=int(cfg.causal))
+    if cfg.decoder == "aed":
+        rm.aed_open(cfg.aed_layers, cfg.aed_heads, cfg.aed_max_seq, cfg.aed_max_gen_delta, quant=CPU_MODES[cpu_mode])
+    return rm
+
+
+def ref_transcribe(rm, cfg, audios):
+    """One wave of the reference: log-mel per item, the packed-batch encoder when there are several items
+    (mynah_asr_encoder_forward_batch, src/encoder.c:948-1010), greedy decoding per item."""
+    feats = []
+    for a in audios:
+        f, v = rm.log_mel(a)
+        feats.append(f[:v])
+    if cfg.decoder == "ctc":
+        return [rm.ctc_decode(rm.encoder_forward(f, cfg.left, cfg.right, raw=True)) for f in feats]
+    encs = rm.encoder_forward_batch(feats, cfg.left, cfg.right) if len(feats) > 1 else [rm.encoder_forward(feats[0], cfg.left, cfg.right)]
+    if cfg.decoder == "aed":
+        out = []
+        for e in encs:
+            t = rm.aed_decode(e, AED_PROMPT, AED_EOS, e.shape[0] + cfg.aed_max_gen_delta).tolist()
+            out.append((t, [0] * len(t)))
+        return out
+    return [rm.greedy_decode(e, cfg.max_symbols) for e in encs]
+
+
+def ref_stream_latencies(rm, cfg, synth, seconds, seed):
+    """Per-chunk wall time of the reference's cache-aware streaming encoder step on one stream
+    (mynah_asr_enc_stream_step, src/encoder.c:809-872), chunks of 8 (right + 1) mel frames."""
+    from oracle import ref_binding as R
+    feats, valid = rm.log_mel(synth.synth_audio(seconds, seed=seed))
+    mel = feats[:valid]
+    es = R.lib().ref_stream_open(rm.h, cfg.left, cfg.right, cfg.n_mels)
+    buf = np.empty((cfg.right + 3, rm.d_out), np.float32)
+    lat, pos, frames = [], 0, 0
+    while pos < mel.shape[0]:
+        need = R.lib().ref_stream_need(es)
+        chunk = np.ascontiguousarray(mel[pos:pos + need], np.float32)
+        t0 = time.perf_counter()
+        q = R.lib().ref_stream_step(es, R._fp(chunk), chunk.shape[0], mel.shape[1], int(pos + need >= mel.shape[0]), R._fp(buf))
+        lat.append((time.perf_counter() - t0) * 1e3)
+        if q <= 0:
+            break
+        frames += q
+        pos += need
+    R.lib().ref_stream_close(es)
+    return lat, frames
+
+
+def cpu_mode_name(args):
+    return args.cpu_mode + ("+qgemm" if os.environ.get("MYNAH_ASR_QGEMM") == "1" else "")
+
+
 def run_reference(args, rank, world):
-    """--impl reference: the reference's own CPU implementation of the path on this
-    host's cores, on a bounded sample of the same workload (one utterance per step)."""
+    """--impl reference: the reference's own CPU implementation of the path on this host's cores, on a bounded
+    sample of the same workload: --cpu-batch utterances per step through its packed-batch encoder (default 1;
+    the GPU step is --batch of them), --cpu-mode f32 | int8 | int4, MYNAH_ASR_QGEMM=1 in the environment for
+    its threaded int8 GEMM. Streaming workloads (--streams): one stream, per-chunk latency."""
     if rank != 0:
         return
     pkg = load_package()
@@ -135,58 +217,72 @@ def run_reference(args, rank, world):
     from oracle import model_io, mynah_oracle as O, ref_binding as R
     cfg, tensors = cached_model(synth, args.workload, 0, lambda: None)
     cores = os.cpu_count() or 1
-    audio = synth.synth_audio(args.seconds, seed=100 + args.sample_index)
+    nb = max(1, args.cpu_batch)
+    audios = [synth.synth_audio(args.seconds, seed=100 + args.sample_index + i) for i in range(nb)]
     fb, win = synth.mel_filterbank(cfg.n_mels), synth.hann_window()
+    extra = {}
     if R.available():
         kind = "reference"
-        d = os.path.join(CACHE, f"{args.workload}_ref")
-        if not os.path.exists(os.path.join(d, "model.safetensors")):
-            model_io.write_reference_files(d, cfg, tensors, synth)
-        rm = R.RefModel(os.path.join(d, "model.safetensors"), os.path.join(d, "mel_filters.safetensors"),
-                        n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
-                        max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), causal=int(cfg.causal))
-
-        if cfg.decoder == "aed":
-            rm.aed_open(cfg.aed_layers, cfg.aed_heads, cfg.aed_max_seq, cfg.aed_max_gen_delta)
-
-        def step():
-            feats, valid = rm.log_mel(audio)
-            if cfg.decoder == "ctc":
-                return rm.ctc_decode(rm.encoder_forward(feats[:valid], cfg.left, cfg.right, raw=True))
-            enc = rm.encoder_forward(feats[:valid], cfg.left, cfg.right)
-            if cfg.decoder == "aed":
-                return rm.aed_decode(enc, AED_PROMPT, AED_EOS, enc.shape[0] + cfg.aed_max_gen_delta)
-            return rm.greedy_decode(enc, cfg.max_symbols)
+        rm = ref_open(args, cfg, tensors, synth, cpu_mode=args.cpu_mode)
+        if args.streams > 0:
+            secs = min(args.seconds, 12.0)
+            def step():
+                lat, frames = ref_stream_latencies(rm, cfg, synth, secs, 100)
+                extra["lat"] = sorted(lat[1:]) or lat
+                return frames
+        else:
+            def step():
+                return ref_transcribe(rm, cfg, audios)
     else:
         kind = "port"
         M = model_io.oracle_model(cfg, tensors)
 
         def step():
-            feats, valid = O.log_mel(audio, fb, win, normalize_per_feature=cfg.normalize)
-            if cfg.decoder == "ctc":
-                return O.ctc_decode(O.encoder_forward(M, feats[:valid], cfg.left, cfg.right, raw=True), M["ctc_w"], M["ctc_b"])
-            enc = O.encoder_forward(M, feats[:valid], cfg.left, cfg.right)
-            if cfg.decoder == "aed":
-                return O.aed_decode(M["aed"], enc, AED_PROMPT, AED_EOS, enc.shape[0] + cfg.aed_max_gen_delta)
-            return O.greedy_decode(M["dec"], enc)
+            out = []
+            for audio in audios:
+                feats, valid = O.log_mel(audio, fb, win, normalize_per_feature=cfg.normalize)
+                if cfg.decoder == "ctc":
+                    out.append(O.ctc_decode(O.encoder_forward(M, feats[:valid], cfg.left, cfg.right, raw=True), M["ctc_w"], M["ctc_b"]))
+                    continue
+                enc = O.encoder_forward(M, feats[:valid], cfg.left, cfg.right)
+                if cfg.decoder == "aed":
+                    out.append(O.aed_decode(M["aed"], enc, AED_PROMPT, AED_EOS, enc.shape[0] + cfg.aed_max_gen_delta))
+                else:
+                    out.append(O.greedy_decode(M["dec"], enc))
+            return out
     for _ in range(args.warmup):
         step()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         step()
     dt = time.perf_counter() - t0
-    value = args.seconds * args.steps / dt
-    sample = (f"1 utterance x {args.seconds:g} s per step (the median of the {args.items} items)" if args.items else
-              f"1 utterance x {args.seconds:g} s per step (of the {args.batch} x {args.seconds:g} s batch)")
-    print(json.dumps({
+    if args.streams > 0 and "lat" in extra:
+        secs = min(args.seconds, 12.0)
+        value = secs * args.steps / dt
+        sample = (f"1 stream x {secs:g} s per step through the streaming encoder step, chunk by chunk "
+                  f"({0.08 * (cfg.right + 1) * 1e3:g} ms chunks; the GPU step is {args.streams} streams in lock step), encoder only")
+    else:
+        value = args.seconds * nb * args.steps / dt
+        sample = (f"{nb} utterance(s) x {args.seconds:g} s per step" +
+                  (f" (the median of the {args.items} items)" if args.items else f" (of the {args.batch} x {args.seconds:g} s batch)") +
+                  (", packed-batch encoder" if nb > 1 else ""))
+    conf = workload_desc(args, cfg)
+    conf["reference_sample"] = sample
+    conf["cpu_mode"] = cpu_mode_name(args)
+    line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_desc(args, cfg),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "vs_baseline": None, "dtype": "f32" if args.cpu_mode == "f32" else args.cpu_mode, "data": "synthetic",
+        "config": conf,
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample, "mode": cpu_mode_name(args)},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }))
+    }
+    if "lat" in extra:
+        lat = extra["lat"]
+        pct = lambda v, p: v[min(len(v) - 1, int(round(p * (len(v) - 1))))]
+        line["chunk_latency_ms"] = {"p50": pct(lat, 0.5), "p99": pct(lat, 0.99), "max": lat[-1], "streams": 1}
+    print(json.dumps(line))
 
 
 AED_PROMPT, AED_EOS = (3, 4, 5, 6, 7), 2     # stand-ins for the canary2 prompt and <|endoftext|>
@@ -212,40 +308,47 @@ def workload_desc(args, cfg):
             "l2": "per-step working set (activations + weights, >1 GB) exceeds the 126 MB L2"}
 
 
-def cpu_baseline(args, cfg, tensors, synth):
-    """The reference's CPU path on one utterance of the workload (bounded sample)."""
-    from oracle import model_io, ref_binding as R
+def cpu_baseline(args, cfg, tensors, synth, model=None):
+    """The reference's CPU path on a bounded sample of the workload (one utterance, f32 path, best of 2), and —
+    the reference being loaded anyway — the parity report of the device model against it on that utterance."""
+    from oracle import parity, ref_binding as R
     if not R.available():
         return {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
-                "sample": "oracle/_ref not built on this box"}
-    d = os.path.join(CACHE, f"{args.workload}_ref")
-    if not os.path.exists(os.path.join(d, "model.safetensors")):
-        model_io.write_reference_files(d, cfg, tensors, synth)
-    rm = R.RefModel(os.path.join(d, "model.safetensors"), os.path.join(d, "mel_filters.safetensors"),
-                    n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
-                    max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), causal=int(cfg.causal))
+                "sample": "oracle/_ref not built on this box"}, None
+    rm = ref_open(args, cfg, tensors, synth)
     audio = synth.synth_audio(args.seconds, seed=100 + args.sample_index)
     times = []
     for i in range(2):           # first pass warms the page cache / BLAS threads
         t0 = time.perf_counter()
-        feats, valid = rm.log_mel(audio)
-        if cfg.decoder == "ctc":
-            toks = rm.ctc_decode(rm.encoder_forward(feats[:valid], cfg.left, cfg.right, raw=True))
-        elif cfg.decoder == "aed":
-            if i == 0:
-                rm.aed_open(cfg.aed_layers, cfg.aed_heads, cfg.aed_max_seq, cfg.aed_max_gen_delta)
-            enc = rm.encoder_forward(feats[:valid], cfg.left, cfg.right)
-            t = rm.aed_decode(enc, AED_PROMPT, AED_EOS, enc.shape[0] + cfg.aed_max_gen_delta)
-            toks = (t.tolist(), [0] * len(t))
-        else:
-            enc = rm.encoder_forward(feats[:valid], cfg.left, cfg.right)
-            toks = rm.greedy_decode(enc, cfg.max_symbols)
+        ref_transcribe(rm, cfg, [audio])
         times.append(time.perf_counter() - t0)
+    rep = None
+    if model is not None:
+        rep = parity.parity_report(model, rm, cfg, tensors, audio, aed_prompt=AED_PROMPT, aed_eos=AED_EOS)
     rm.close()
-    return {"value": args.seconds / min(times), "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+    return {"value": args.seconds / min(times), "unit": UNIT, "cores": os.cpu_count(), "kind": "reference", "mode": "f32",
             "sample": f"1 utterance x {args.seconds:g} s, best of 2 " +
-                      (f"(the median of the {args.items} items of a GPU step)" if args.items else f"(the GPU step is {args.batch} of these)"),
-            "tokens": toks[0], "frames": toks[1]}
+                      (f"(the median of the {args.items} items of a GPU step)" if args.items else f"(the GPU step is {args.batch} of these)")}, rep
+
+
+def parity_diverse(args, pkg, synth, seconds):
+    """Supplementary parity report on a second seeded model of the same architecture whose weights keep the
+    encoder output varying over time (recipe "diverse"), so that the full-size greedy stream has many distinct
+    tokens. One utterance; nothing here is timed."""
+    from oracle import parity, ref_binding as R
+    if not R.available():
+        return None
+    cfg, tensors = cached_model(synth, args.workload, 0, lambda: None, recipe="diverse")
+    dm = pkg.Model(tensors, n_mels=cfg.n_mels, mel_fb=synth.mel_filterbank(cfg.n_mels), window=synth.hann_window(),
+                   causal=int(cfg.causal), normalize=cfg.normalize, left=cfg.left, right=cfg.right, blank=cfg.vocab - 1,
+                   max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), strict=True, aed_heads=cfg.aed_heads)
+    rm = ref_open(args, cfg, tensors, synth, recipe="diverse")
+    audio = synth.synth_audio(seconds, seed=100 + args.sample_index)
+    rep = parity.parity_report(dm, rm, cfg, tensors, audio, aed_prompt=AED_PROMPT, aed_eos=AED_EOS)
+    rm.close()
+    dm.close()
+    rep["recipe"] = f"diverse: linears ~ N(0, 0.32 / sqrt(d_model)) = N(0, {recipe_std(cfg, 'diverse'):.4f}), seed 0"
+    return {k: v for k, v in rep.items() if not k.startswith("_")}
 
 
 def run_streaming(args, pkg, synth, torch, dist, cfg, tensors, model, rank, world, local, barrier):
@@ -390,7 +493,17 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: only the resident-input timing")
     ap.add_argument("--blank-bias", type=float, default=None, help="bias of the blank logit of the synthetic transducer head")
+    ap.add_argument("--cpu-mode", default="f32", choices=list(CPU_MODES), help="reference arm: f32 (blocks decoded at load + sgemm), "
+                    "or the reference's own int8 / int4 load-time quantisation; MYNAH_ASR_QGEMM=1 in the environment adds its threaded int8 GEMM")
+    ap.add_argument("--cpu-batch", type=int, default=1, help="reference arm: utterances per step through its packed-batch encoder")
+    ap.add_argument("--no-diverse", action="store_true", help="skip the supplementary parity report on the diverse-recipe model")
     args = ap.parse_args()
+    defaults = {"cfg0": (1, 30.0), "cfg4": (32, 20.0)}           # batch, seconds as the configs word them
+    if args.workload in defaults:
+        if args.batch == 16:
+            args.batch = defaults[args.workload][0]
+        if args.seconds == 60.0:
+            args.seconds = defaults[args.workload][1]
     if args.items is None:
         args.items = 256 if args.workload == "cfg2" else 0
         if args.items and args.batch == 16:
@@ -558,6 +671,7 @@ def main():
                          # of the output is still in L2 when the kernel ends)
                          "traffic": g["bytes"] / args.steps * GEMM_TRAFFIC_RATIO,
                          "traffic_unit": "bytes per step (all contraction launches)",
+                         "traffic_source": "estimate: algorithmic bytes x 0.853, the dram/algorithmic ratio ncu measured on one launch",
                          "algorithmic_bytes_per_step": g["bytes"] / args.steps,
                          "launches": g["launches"], "kernel_ms_per_step": g["ms"] / args.steps,
                          "flops_per_step": g["flops"] / args.steps,
@@ -569,12 +683,16 @@ def main():
             "clocks": clk,
         }
         if world == 1 and not args.no_cpu_baseline:
-            cb = cpu_baseline(args, cfg, tensors, synth)
-            ref_t, ref_f = cb.pop("tokens", None), cb.pop("frames", None)
-            if ref_t is not None:     # the reference decoded the same utterance as item 0 of this rank
+            cb, rep = cpu_baseline(args, cfg, tensors, synth, model)
+            if rep is not None:       # the reference decoded the same utterance as item `sample_index` of this rank
                 u = args.sample_index
-                line["parity"] = {"utterance": u, "reference_tokens": len(ref_t), "distinct": len(set(ref_t)),
-                                  "tokens_identical": ref_t == res[u][0], "frames_identical": ref_f == res[u][1]}
+                ref_t, ref_f = rep.pop("_ref_tokens"), rep.pop("_ref_frames")
+                rep["utterance"] = u
+                rep["tokens"]["timed_batch_item_identical"] = ref_t == res[u][0] and (ref_f is None or ref_f == res[u][1])
+                rep["recipe"] = "baseline: linears ~ N(0, 0.02), seed 0 (the timed model)"
+                line["parity"] = rep
+                if not args.no_diverse:
+                    line["parity_diverse"] = parity_diverse(args, pkg, synth, args.seconds)
             line["cpu_baseline"] = cb
         else:
             line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",

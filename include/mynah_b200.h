@@ -137,6 +137,11 @@ typedef struct {
     int attn_impl;              /* 0 tensor-core kernels (default: tcgen05 for full attention over 128-wide heads, else the warp-level tiled one), 1 plain kernel (cross-check), 2 warp-level tiled kernel */
     int aed_heads;              /* decoder.n_heads of an AED model (mynah_asr_aed_init's n_heads); layers, width,
                                  * vocabulary and max_seq are read off the tensors */
+    int a8;                     /* 1: the ten linears of every encoder layer take int8 activations (quantize_act_int8,
+                                 * src/qmat.c:186-202) and run as integer contractions on the tensor cores — the reference's
+                                 * arithmetic with MYNAH_ASR_QGEMM=1 (src/qmat.c:598-643), bit-exact int32 sums. Needs those
+                                 * weights in the reference-native per-row int8 format (MYNAH_B200_MYNAH_Q8) with k % 128 == 0.
+                                 * 0 (default): float activations (the reference's default path above 16 rows). */
 } mynah_b200_config;
 
 void mynah_b200_config_default(mynah_b200_config *cfg);
@@ -155,6 +160,11 @@ int mynah_b200_model_set_mel(mynah_b200_model *m, const float *mel_fb, const flo
  * (src/encoder.c:56-183, src/subsampling.c:14-58, src/decoder.c:14-62, src/decoder_ctc.c:11-22),
  * uploads and decodes them; replaces the lazy per-pointer upload of src/cuda_gemm.cu:96-130 */
 int mynah_b200_model_finalize(mynah_b200_model *m);
+/* switches the numerics of the tensor-core contractions of later calls: 1 = three fp16 products per term
+ * (f32-grade, the default), 0 = a single fp16 product. The weights serve both. A stream group keeps the
+ * mode of the step it captured: do not switch while one is open. No counterpart in the reference (its
+ * sgemm has one precision); used to report both modes against the same weights. */
+int mynah_b200_model_set_strict(mynah_b200_model *m, int strict);
 /* replaces mynah_asr_metal_weights_evict / mynah_asr_encoder_free */
 void mynah_b200_model_free(mynah_b200_model *m);
 /* dims[0..7] = d_model, n_layers, n_heads, ffn_dim, conv_k, d_out, causal, channels */

@@ -33,7 +33,7 @@ class Config(C.Structure):
                 ("preemphasis", C.c_double), ("log_zero_guard", C.c_double), ("normalize_per_feature", C.c_int),
                 ("causal", C.c_int), ("xscaling", C.c_int), ("left_ctx", C.c_int), ("right_ctx", C.c_int),
                 ("blank_id", C.c_int), ("max_symbols", C.c_int), ("n_durations", C.c_int),
-                ("durations", C.c_int * 16), ("strict", C.c_int), ("attn_impl", C.c_int), ("aed_heads", C.c_int)]
+                ("durations", C.c_int * 16), ("strict", C.c_int), ("attn_impl", C.c_int), ("aed_heads", C.c_int), ("a8", C.c_int)]
 
 
 class BackendError(RuntimeError):
@@ -149,6 +149,7 @@ def lib():
     L.mynah_b200_model_set_mel.argtypes = [vp, c_fp, c_fp]
     L.mynah_b200_model_finalize.argtypes = [vp]
     L.mynah_b200_model_free.argtypes = [vp]
+    L.mynah_b200_model_set_strict.argtypes = [vp, ci]
     L.mynah_b200_model_dims.argtypes = [vp, c_ip]
     L.mynah_b200_model_stream.restype = vp
     L.mynah_b200_model_stream.argtypes = [vp]
@@ -318,7 +319,7 @@ class Model:
     (the weight side of mynah_asr_load_quant, src/mynah_asr.c:167-350)."""
 
     def __init__(self, tensors, *, n_mels, mel_fb=None, window=None, causal=-1, xscaling=False, normalize=True,
-                 left=-1, right=-1, blank=0, max_symbols=10, durations=(), strict=True, attn_impl=0, aed_heads=8):
+                 left=-1, right=-1, blank=0, max_symbols=10, durations=(), strict=True, attn_impl=0, aed_heads=8, a8=False):
         L = lib()
         cfg = Config()
         L.mynah_b200_config_default(C.byref(cfg))
@@ -327,14 +328,14 @@ class Model:
         cfg.blank_id, cfg.max_symbols, cfg.n_durations = blank, max_symbols, len(durations)
         for i, d in enumerate(durations):
             cfg.durations[i] = d
-        cfg.strict, cfg.attn_impl, cfg.aed_heads = int(strict), attn_impl, aed_heads
+        cfg.strict, cfg.attn_impl, cfg.aed_heads, cfg.a8 = int(strict), attn_impl, aed_heads, int(a8)
         self.cfg = cfg
         self.h = L.mynah_b200_model_new(C.byref(cfg))
         if not self.h:
             raise BackendError("model_new: " + _err())
         keep = []
         for name, t in tensors.items():
-            fmt = {0: F32, 2: GGML_Q4_0, 8: GGML_Q8_0, 12: GGML_Q4_K, 14: GGML_Q6_K}[t.ggml_type]
+            fmt = {0: F32, 2: GGML_Q4_0, 8: GGML_Q8_0, 12: GGML_Q4_K, 14: GGML_Q6_K, -8: MYNAH_Q8, -4: MYNAH_Q4}[t.ggml_type]
             shape = (C.c_int64 * len(t.shape))(*t.shape)
             raw = np.ascontiguousarray(t.raw)
             keep.append(raw)
@@ -357,6 +358,10 @@ class Model:
             self.h = None
 
     __del__ = close
+
+    def set_strict(self, strict: bool):
+        """f32-grade three-product contractions (True) or a single fp16 product (False) for later calls"""
+        _check(lib().mynah_b200_model_set_strict(self.h, int(strict)), "model_set_strict")
 
     def stream(self):
         return lib().mynah_b200_model_stream(self.h)

@@ -89,7 +89,7 @@ void mynah_b200_config_default(mynah_b200_config *c) {
     c->preemphasis = 0.97; c->log_zero_guard = 5.9604644775390625e-8;
     c->normalize_per_feature = 1; c->causal = -1; c->xscaling = 0;
     c->left_ctx = -1; c->right_ctx = -1; c->blank_id = 0; c->max_symbols = 10;
-    c->n_durations = 0; c->strict = 1; c->attn_impl = 0; c->aed_heads = 8;
+    c->n_durations = 0; c->strict = 1; c->attn_impl = 0; c->aed_heads = 8; c->a8 = 0;
 }
 
 // ------------------------------------------------------------------- model
@@ -290,6 +290,18 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
     }
     m.ffn_dim = m.layers[0].ff1_w1.n;
     m.d_out = m.d_model;
+    if (m.cfg.a8) {
+        for (int li = 0; li < nl; li++) {
+            const EncLayer &L = m.layers[li];
+            const QWeight *ws[10] = {&L.ff1_w1, &L.ff1_w2, &L.ff2_w1, &L.ff2_w2, &L.q_w, &L.k_w, &L.v_w, &L.o_w, &L.pw1_w, &L.pw2_w};
+            for (const QWeight *w : ws)
+                if (!m.a8_ok(*w)) {
+                    set_error("a8 mode: the linears of encoder layer %d must be reference-native int8 [n,k] with k %% 128 == 0 (got format %d, k=%d)", li, w->fmt, w->k);
+                    return -1;
+                }
+        }
+        m.a8_layers = true;
+    }
     if (find(m, "encoder_projector.weight")) {
         if (lin(m, m.encproj, "encoder_projector.weight", true, false)) return -1;
         m.has_encproj = true;
@@ -417,6 +429,13 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
 
 void mynah_b200_model_free(mynah_b200_model *h) { delete h; }
 
+int mynah_b200_model_set_strict(mynah_b200_model *h, int strict) {
+    if (!h) { set_error("model_set_strict: null model"); return -1; }
+    std::lock_guard<std::mutex> lk(h->m.mu);
+    h->m.cfg.strict = strict ? 1 : 0;
+    return 0;
+}
+
 void mynah_b200_model_dims(const mynah_b200_model *h, int *dims) {
     const Model &m = h->m;
     dims[0] = m.d_model; dims[1] = m.n_layers; dims[2] = m.n_heads; dims[3] = m.ffn_dim;
@@ -436,7 +455,8 @@ static size_t ss_bytes(const Model &m, int t_mel) {
     return T1 * F1 * C * 4 + T2 * F2 * C * 8 + T3 * F3 * C * 8 + (1 << 16);
 }
 static size_t enc_bytes(const Model &m, size_t M, size_t rk_rows) {
-    return M * ((size_t)m.d_model * 44 + (size_t)m.ffn_dim * 4) + rk_rows * m.d_model * 6 + (1 << 20);
+    return M * ((size_t)m.d_model * 44 + (size_t)m.ffn_dim * 4) + rk_rows * m.d_model * 6 + (1 << 20) +
+           (m.a8_layers ? M * ((size_t)m.d_model + 5 * (size_t)m.ffn_dim + 64) + 4096 : 0);
 }
 static size_t dec_bytes(const Model &m, int max_len) {
     const size_t B = DEC_MAX_B;
@@ -973,6 +993,24 @@ int mynah_b200_qmat_mul_device(const mynah_b200_qmat *q, const float *x, float *
     if (T == 0) return 0;
     const QWeight &w = q->w;
     if (flags & MYNAH_B200_A8) {
+        if (w.fmt == FMT_MYNAH_Q8 && T > 16 && w.k % 128 == 0) {
+            // many rows: the same integers on the tensor cores (bit-identical to the row-dot kernel below)
+            int8_t *qx = nullptr;
+            float *sx = nullptr;
+            MB_CUDA(cudaMallocAsync(&qx, (size_t)T * w.k, q->stream));
+            if (cudaMallocAsync(&sx, (size_t)T * sizeof(float), q->stream) != cudaSuccess) {
+                cudaGetLastError(); cudaFreeAsync(qx, q->stream); set_error("qmat_mul: device allocation failed"); return -1;
+            }
+            GemmEpilogue e;
+            memset(&e, 0, sizeof(e));
+            e.mode = OUT_F32; e.act = ACT_NONE; e.alpha = 1.f; e.out = out; e.ldo = w.n;
+            int rc = act_quant_rows(x, qx, sx, T, w.k, q->stream);
+            if (rc == 0) rc = gemm_i8(qx, w.k, sx, reinterpret_cast<const int8_t *>(w.raw), w.k, w.scales, e, T, w.n, w.k, q->status, q->stream);
+            if (rc == 0) note_launch(2);
+            cudaFreeAsync(qx, q->stream);
+            cudaFreeAsync(sx, q->stream);
+            return rc;
+        }
         const int rc = qgemv_a8(w, x, out, T, nullptr, nullptr, q->stream);
         if (rc == 0) note_launch(2);
         return rc;

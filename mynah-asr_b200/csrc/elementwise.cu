@@ -9,9 +9,18 @@ namespace mb {
 // ---------------------------------------------------------------- LayerNorm
 // One warp per row. Mean and variance are accumulated in double like the
 // reference's layer_norm_f (src/encoder.c:25-37): y = ((x - mu) * inv) * w + b.
+// int8 row by the reference's activation rule (quantize_act_int8, src/qmat.c:186-202)
+__device__ __forceinline__ int8_t act_q8(float y, float inv) {
+    const float v = __fmul_rn(y, inv);
+    int q = (int)(v >= 0.0f ? __fadd_rn(v, 0.5f) : __fsub_rn(v, 0.5f));
+    q = q > 127 ? 127 : (q < -127 ? -127 : q);
+    return (int8_t)q;
+}
+
 __global__ void __launch_bounds__(256)
 ln_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b,
-          float *__restrict__ out, __half *__restrict__ hi, __half *__restrict__ lo, int T, int d, int act) {
+          float *__restrict__ out, __half *__restrict__ hi, __half *__restrict__ lo, int8_t *__restrict__ q8,
+          float *__restrict__ sx8, int T, int d, int act) {
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= T) return;
     const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * d);
@@ -28,6 +37,22 @@ ln_kernel(const float *__restrict__ x, const float *__restrict__ w, const float 
     const double var = warp_sum_d(q) / d;
     const float inv = (float)(1.0 / sqrt(var + 1e-5));
     const float muf = (float)mu;
+    float qinv = 0.0f;
+    if (q8) {               // one more pass for the row's absolute maximum
+        float amax = 0.0f;
+        for (int i = lane; i < n4; i += 32) {
+            const float4 v = xr[i];
+            const float4 ww = reinterpret_cast<const float4 *>(w)[i];
+            const float4 bb = reinterpret_cast<const float4 *>(b)[i];
+            float y[4] = {((v.x - muf) * inv) * ww.x + bb.x, ((v.y - muf) * inv) * ww.y + bb.y,
+                          ((v.z - muf) * inv) * ww.z + bb.z, ((v.w - muf) * inv) * ww.w + bb.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) amax = fmaxf(amax, fabsf(act == ACT_SILU ? silu_f(y[j]) : y[j]));
+        }
+        amax = warp_max(amax);
+        qinv = amax > 0.0f ? 127.0f / amax : 0.0f;
+        if (lane == 0) sx8[row] = amax > 0.0f ? amax / 127.0f : 0.0f;
+    }
     for (int i = lane; i < n4; i += 32) {
         const float4 v = xr[i];
         const float4 ww = reinterpret_cast<const float4 *>(w)[i];
@@ -38,6 +63,7 @@ ln_kernel(const float *__restrict__ x, const float *__restrict__ w, const float 
 #pragma unroll
             for (int j = 0; j < 4; j++) y[j] = silu_f(y[j]);
         }
+        if (q8) reinterpret_cast<char4 *>(q8 + (size_t)row * d)[i] = make_char4(act_q8(y[0], qinv), act_q8(y[1], qinv), act_q8(y[2], qinv), act_q8(y[3], qinv));
         if (out) reinterpret_cast<float4 *>(out + (size_t)row * d)[i] = make_float4(y[0], y[1], y[2], y[3]);
         if (hi) {
             __align__(8) __half h[4], l[4];
@@ -53,7 +79,8 @@ ln_kernel(const float *__restrict__ x, const float *__restrict__ w, const float 
 template <int NV>
 __global__ void __launch_bounds__(256)
 ln_reg_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b,
-              float *__restrict__ out, __half *__restrict__ hi, __half *__restrict__ lo, int T, int act) {
+              float *__restrict__ out, __half *__restrict__ hi, __half *__restrict__ lo, int8_t *__restrict__ q8,
+              float *__restrict__ sx8, int T, int act) {
     constexpr int d = NV * 128;
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= T) return;
@@ -74,8 +101,9 @@ ln_reg_kernel(const float *__restrict__ x, const float *__restrict__ w, const fl
     const double var = warp_sum_d(q) / d;
     const float inv = (float)(1.0 / sqrt(var + 1e-5));
     const float muf = (float)mu;
+    float amax = 0.0f;
 #pragma unroll
-    for (int j = 0; j < NV; j++) {
+    for (int j = 0; j < NV; j++) {          // the finished values replace the inputs in the registers
         const int i = lane + 32 * j;
         const float4 ww = reinterpret_cast<const float4 *>(w)[i];
         const float4 bb = reinterpret_cast<const float4 *>(b)[i];
@@ -85,6 +113,20 @@ ln_reg_kernel(const float *__restrict__ x, const float *__restrict__ w, const fl
 #pragma unroll
             for (int e = 0; e < 4; e++) y[e] = silu_f(y[e]);
         }
+        v[j] = make_float4(y[0], y[1], y[2], y[3]);
+        amax = fmaxf(fmaxf(amax, fmaxf(fabsf(y[0]), fabsf(y[1]))), fmaxf(fabsf(y[2]), fabsf(y[3])));
+    }
+    float qinv = 0.0f;
+    if (q8) {
+        amax = warp_max(amax);
+        qinv = amax > 0.0f ? 127.0f / amax : 0.0f;
+        if (lane == 0) sx8[row] = amax > 0.0f ? amax / 127.0f : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        const int i = lane + 32 * j;
+        const float y[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+        if (q8) reinterpret_cast<char4 *>(q8 + (size_t)row * d)[i] = make_char4(act_q8(y[0], qinv), act_q8(y[1], qinv), act_q8(y[2], qinv), act_q8(y[3], qinv));
         if (out) reinterpret_cast<float4 *>(out + (size_t)row * d)[i] = make_float4(y[0], y[1], y[2], y[3]);
         if (hi) {
             __align__(8) __half h[4], l[4];
@@ -98,10 +140,15 @@ ln_reg_kernel(const float *__restrict__ x, const float *__restrict__ w, const fl
 
 int layer_norm(const float *x, const float *w, const float *b, float *out_f32, H16 out_h, int T, int d, int act,
                cudaStream_t st) {
+    return layer_norm_q8(x, w, b, out_f32, out_h, nullptr, nullptr, T, d, act, st);
+}
+
+int layer_norm_q8(const float *x, const float *w, const float *b, float *out_f32, H16 out_h, int8_t *q8, float *sx8, int T, int d,
+                  int act, cudaStream_t st) {
     if (T <= 0) return 0;
     if (d % 4) { set_error("layer_norm: d=%d must be a multiple of 4", d); return -1; }
     const dim3 grid(cdiv(T, 8));
-#define LN_REG(NV) ln_reg_kernel<NV><<<grid, 256, 0, st>>>(x, w, b, out_f32, out_h.hi, out_h.lo, T, act)
+#define LN_REG(NV) ln_reg_kernel<NV><<<grid, 256, 0, st>>>(x, w, b, out_f32, out_h.hi, out_h.lo, q8, sx8, T, act)
     if (d == 128) LN_REG(1);
     else if (d == 256) LN_REG(2);
     else if (d == 512) LN_REG(4);
@@ -110,7 +157,7 @@ int layer_norm(const float *x, const float *w, const float *b, float *out_f32, H
     else if (d == 2048) LN_REG(16);
     else
 #undef LN_REG
-    ln_kernel<<<cdiv(T, 8), 256, 0, st>>>(x, w, b, out_f32, out_h.hi, out_h.lo, T, d, act);
+    ln_kernel<<<cdiv(T, 8), 256, 0, st>>>(x, w, b, out_f32, out_h.hi, out_h.lo, q8, sx8, T, d, act);
     MB_CUDA(cudaGetLastError());
     return 0;
 }
@@ -186,11 +233,14 @@ glu_dw_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, cons
         if (scale) {
             const float y[4] = {silu_f(acc[i].x * sc.x + sh.x), silu_f(acc[i].y * sc.y + sh.y), silu_f(acc[i].z * sc.z + sh.z),
                                 silu_f(acc[i].w * sc.w + sh.w)};
-            __align__(8) __half h[4], l[4];
+            if (hi) {
+                __align__(8) __half h[4], l[4];
 #pragma unroll
-            for (int e = 0; e < 4; e++) split_h16(y[e], h[e], l[e]);
-            *reinterpret_cast<uint2 *>(hi + o) = *reinterpret_cast<const uint2 *>(h);
-            if (lo) *reinterpret_cast<uint2 *>(lo + o) = *reinterpret_cast<const uint2 *>(l);
+                for (int e = 0; e < 4; e++) split_h16(y[e], h[e], l[e]);
+                *reinterpret_cast<uint2 *>(hi + o) = *reinterpret_cast<const uint2 *>(h);
+                if (lo) *reinterpret_cast<uint2 *>(lo + o) = *reinterpret_cast<const uint2 *>(l);
+            }
+            if (out) *reinterpret_cast<float4 *>(out + o) = make_float4(y[0], y[1], y[2], y[3]);
         } else {
             *reinterpret_cast<float4 *>(out + o) = acc[i];
         }

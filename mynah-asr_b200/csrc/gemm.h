@@ -31,7 +31,36 @@ struct GemmEpilogue {
     int ldh;
 };
 
+static constexpr int GEMM_BM = 128;      // rows of an output tile (one tcgen05.mma M)
+
 #ifdef __CUDACC__
+// Work units of the persistent loop. Whole waves of gridDim.x tiles come first; the tiles of the last, partial
+// wave are cut into 2 or 4 column strips when that still fits one wave, so that the tail costs a half or a
+// quarter of a tile time instead of a whole one (752 tiles on 148 CTAs: 5.25 instead of 6 tile times). A strip
+// runs the same instruction sequence over its columns as the whole tile would, so no output bit depends on it.
+struct GemmUnits {
+    int tiles_n, full, split, total;          // full: tiles in whole waves; split: strips per tail tile
+    __device__ GemmUnits(int M, int N, int BN_, int ctas) {
+        tiles_n = (N + BN_ - 1) / BN_;
+        const int tiles = tiles_n * ((M + GEMM_BM - 1) / GEMM_BM);
+        full = tiles / ctas * ctas;
+        const int rem = tiles - full;
+        split = 1;
+        if (rem > 0) {
+            if (rem * 4 <= ctas && BN_ % 128 == 0) split = 4;
+            else if (rem * 2 <= ctas && BN_ % 64 == 0) split = 2;
+        }
+        total = full + rem * split;
+    }
+    __device__ void at(int u, int BN_, int &m0, int &n0, int &width) const {
+        int tile = u, sub = 0;
+        if (u >= full) { tile = full + (u - full) / split; sub = (u - full) % split; }
+        width = u >= full ? BN_ / split : BN_;
+        m0 = (tile / tiles_n) * GEMM_BM;
+        n0 = (tile % tiles_n) * BN_ + sub * width;
+    }
+};
+
 // Fused tail for 32 consecutive columns [nb, nb+32) of output row m.
 // Returns false if a value written as fp16 planes was out of their range (see split_h16).
 __device__ __forceinline__ bool gemm_epilogue_row(const GemmEpilogue &ep, float (&v)[32], int m, int nb, int N) {
@@ -106,5 +135,13 @@ __device__ __forceinline__ bool gemm_epilogue_row(const GemmEpilogue &ep, float 
 // bounded wait inside the kernel ran out.
 int gemm_tc(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, int M, int N, int K, int nterms,
             int *status, cudaStream_t stream);
+
+// Integer contraction on the tensor cores (gemm_i8.cu): acc[m,n] = sum_k a[m,k] * b[n,k] in int32 (exact), then
+// v = (float)acc * col_scale[n] * row_scale[m] — the arithmetic of the reference's int8-activation dots
+// (dot_q8_*, src/qmat.c:285-364: (float)int32 * ws * sx) — followed by the same fused tail as gemm_tc.
+// a: [M, K] int8 row-major (activation rows quantised by quantize_act_int8's rule), b: [N, K] int8 row-major
+// (reference-native per-row int8 weights). K must be a multiple of 128; lda / ldb in bytes, multiples of 16.
+int gemm_i8(const int8_t *a, int lda, const float *row_scale, const int8_t *b, int ldb, const float *col_scale,
+            const GemmEpilogue &ep, int M, int N, int K, int *status, cudaStream_t stream);
 
 }  // namespace mb

@@ -27,7 +27,7 @@
 
 namespace mb {
 
-static constexpr int BM = 128;
+static constexpr int BM = GEMM_BM;
 static constexpr int BK = 64;
 static constexpr int EPI_WARPS = 8;
 static constexpr int GEMM_THREADS = (2 + EPI_WARPS) * 32;   // warp 0 TMA, warp 1 MMA, warps 2..9 epilogue
@@ -47,33 +47,6 @@ struct GemmCfg {
     static constexpr int ACC_COLS = NTERMS == 1 ? BN : 2 * BN;
     static constexpr int TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;
     static_assert(TMEM_COLS <= 512, "TMEM has 512 columns");
-};
-
-// Work units of the persistent loop. Whole waves of gridDim.x tiles come first; the tiles of the last, partial
-// wave are cut into 2 or 4 column strips when that still fits one wave, so that the tail costs a half or a
-// quarter of a tile time instead of a whole one (752 tiles on 148 CTAs: 5.25 instead of 6 tile times). A strip
-// runs the same instruction sequence over its columns as the whole tile would, so no output bit depends on it.
-struct GemmUnits {
-    int tiles_n, full, split, total;          // full: tiles in whole waves; split: strips per tail tile
-    __device__ GemmUnits(int M, int N, int BN_, int ctas) {
-        tiles_n = (N + BN_ - 1) / BN_;
-        const int tiles = tiles_n * ((M + BM - 1) / BM);
-        full = tiles / ctas * ctas;
-        const int rem = tiles - full;
-        split = 1;
-        if (rem > 0) {
-            if (rem * 4 <= ctas && BN_ % 128 == 0) split = 4;
-            else if (rem * 2 <= ctas && BN_ % 64 == 0) split = 2;
-        }
-        total = full + rem * split;
-    }
-    __device__ void at(int u, int BN_, int &m0, int &n0, int &width) const {
-        int tile = u, sub = 0;
-        if (u >= full) { tile = full + (u - full) / split; sub = (u - full) % split; }
-        width = u >= full ? BN_ / split : BN_;
-        m0 = (tile / tiles_n) * BM;
-        n0 = (tile % tiles_n) * BN_ + sub * width;
-    }
 };
 
 // Persistent kernel: one CTA per SM walks the output tiles (n fastest, so the CTAs in

@@ -28,9 +28,14 @@ int split_to_h16(const float *x, __half *hi, __half *lo, size_t n, cudaStream_t 
 // writes f32 and/or fp16 (hi,lo) planes. out_f32 may alias x.
 int layer_norm(const float *x, const float *w, const float *b, float *out_f32, H16 out_h, int T, int d, int act,
                cudaStream_t st);
+// the same with the row also (or only) written as int8 + per-row scale by the reference's activation rule
+// (quantize_act_int8, src/qmat.c:186-202): the operand of an int8-activation contraction
+int layer_norm_q8(const float *x, const float *w, const float *b, float *out_f32, H16 out_h, int8_t *q8, float *sx8, int T, int d,
+                  int act, cudaStream_t st);
 // Conv-module middle: GLU over h2 [T,2d], depthwise conv k along time inside each
 // segment, then either a per-channel affine (folded BatchNorm) + SiLU -> planes, or
-// (affine null) the raw depthwise output as f32 for a following LayerNorm.
+// (affine null) the raw depthwise output as f32 for a following LayerNorm. With an affine, out_f32 (if given)
+// receives the same values as the planes (either may be null).
 int glu_dwconv(const float *h2, const float *dw_w, const float *dw_b, const float *scale, const float *shift,
                float *out_f32, H16 out_h, const int *seg_off, const int *seg_len, int batch, int max_len, int d,
                int k, int pad_left, cudaStream_t st);
@@ -93,6 +98,9 @@ int qstream_tc_retile(const QWeight &w, uint8_t *dst, cudaStream_t st);
 size_t qstream_tc_scratch_bytes(int n, int k);
 int qstream_tc(const QWeight &w, const float *x, int ldx, float *out, int ldo, const float *bias, int T, int *status,
                cudaStream_t st);
+// int8 activation rows by the reference's rule (quantize_act_int8, src/qmat.c:186-202): per row scale = amax / 127,
+// q = round-half-away(x * 127 / amax) clamped to +-127; x [T, k] f32 -> qx [T, k] int8, sx [T]
+int act_quant_rows(const float *x, int8_t *qx, float *sx, int T, int k, cudaStream_t st);
 int qgemv_a8(const QWeight &w, const float *x, float *out, int T, int32_t *block_dots, float *sx_out, cudaStream_t st);
 
 // ---- launch accounting (model.cu): every kernel launch of the library is counted

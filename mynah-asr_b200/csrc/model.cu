@@ -169,6 +169,21 @@ int Model::gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep,
     return rc;
 }
 
+int Model::gemm_q8(const int8_t *qa, const float *sx, const QWeight &w, const GemmEpilogue &ep, int M) {
+    if (!a8_ok(w)) { set_error("int8-activation contraction on a weight that is not reference-native int8 with k %% 128 == 0"); return -1; }
+    const int sp = prof_begin_span(PROF_GEMM);
+    const int rc = gemm_i8(qa, w.k, sx, reinterpret_cast<const int8_t *>(w.raw), w.k, w.scales, ep, M, w.n, w.k, status, stream);
+    prof_end_span(sp);
+    if (sp >= 0) {
+        prof_flops[PROF_GEMM] += 2.0 * M * (double)w.n * w.k;
+        const double out_b = ep.mode == OUT_H16 ? 4.0 : ep.mode == OUT_F32_H16 ? 8.0 : ep.mode == OUT_RESID ? 8.0 : 4.0;
+        prof_bytes[PROF_GEMM] += (double)M * w.k + (double)w.n * w.k + 4.0 * (M + w.n) + out_b * M * (double)w.n;
+        prof_launches[PROF_GEMM]++;
+    }
+    if (rc == 0) note_launch();
+    return rc;
+}
+
 static GemmEpilogue epi(int mode, int act, float alpha, const float *bias, float *out, int ldo, H16 h = H16{nullptr, nullptr},
                         int ldh = 0) {
     GemmEpilogue e;
@@ -239,6 +254,16 @@ int Model::encoder_layers(float *x, const std::vector<int> &lens, int left, int 
     H16 rk = ws.planes((size_t)rk_rows * d, false);
     if (!hA.lo || !hC.lo || !hF.lo || !qbuf || !kbuf.hi || !vbuf.hi || !h2 || !cbuf || !pe.lo || !rk.hi) return -1;
 
+    // int8-activation mode: quantised rows of the LayerNorm outputs / attention context / conv middle (qA) and of
+    // SiLU(FFN1) (qF), their scales, and the f32 values that get quantised
+    const bool a8 = a8_layers;
+    int8_t *qA = nullptr, *qF = nullptr;
+    float *sxA = nullptr, *sxF = nullptr, *fF = nullptr;
+    if (a8) {
+        qA = ws.get<int8_t>((size_t)M * d); qF = ws.get<int8_t>((size_t)M * F);
+        sxA = ws.get<float>(M); sxF = ws.get<float>(M); fF = ws.get<float>((size_t)M * F);
+        if (!qA || !qF || !sxA || !sxF || !fF) return -1;
+    }
     for (size_t i = 0; i < distinct.size(); i++) {
         H16 p{pe.hi + (size_t)rk_base[i] * d, pe.lo + (size_t)rk_base[i] * d};
         if (pos_emb(p, distinct[i], d, stream)) return -1;
@@ -248,6 +273,51 @@ int Model::encoder_layers(float *x, const std::vector<int> &lens, int left, int 
     const H16 none{nullptr, nullptr};
     for (int li = first_layer; li < first_layer + n_run; li++) {
         const EncLayer &L = layers[li];
+        if (a8) {
+            // the same block with int8 activations into every linear (the reference with MYNAH_ASR_QGEMM=1:
+            // qmat_mul quantises the input rows of each of the ten linears, src/qmat.c:615-618)
+            if (layer_norm_q8(x, L.ln_ff1_w, L.ln_ff1_b, nullptr, none, qA, sxA, M, d, ACT_NONE, stream)) return -1;
+            if (gemm_q8(qA, sxA, L.ff1_w1, epi(OUT_F32, ACT_SILU, 1.f, L.ff1_w1.bias, fF, F), M)) return -1;
+            if (act_quant_rows(fF, qF, sxF, M, F, stream)) return -1;
+            if (gemm_q8(qF, sxF, L.ff1_w2, epi(OUT_RESID, ACT_NONE, 0.5f, L.ff1_w2.bias, x, d), M)) return -1;
+            if (layer_norm_q8(x, L.ln_att_w, L.ln_att_b, nullptr, none, qA, sxA, M, d, ACT_NONE, stream)) return -1;
+            if (gemm_q8(qA, sxA, L.q_w, epi(OUT_F32, ACT_NONE, 1.f, L.q_w.bias, qbuf, d), M)) return -1;
+            if (gemm_q8(qA, sxA, L.k_w, epi(OUT_H16, ACT_NONE, 1.f, L.k_w.bias, nullptr, 0, kbuf, d), M)) return -1;
+            if (gemm_q8(qA, sxA, L.v_w, epi(OUT_H16, ACT_NONE, 1.f, L.v_w.bias, nullptr, 0, vbuf, d), M)) return -1;
+            if (gemm(pe, d, L.relk, epi(OUT_H16, ACT_NONE, 1.f, nullptr, nullptr, 0, rk, d), rk_rows)) return -1;
+            AttnArgs at;
+            at.q = qbuf; at.ldq = d; at.k = kbuf.hi; at.v = vbuf.hi; at.rk = rk.hi;
+            at.bias_u = L.bias_u; at.bias_v = L.bias_v; at.ctx_f32 = cbuf; at.ctx_h = none;
+            at.seg_off = d_off; at.seg_len = d_len; at.rk_off = d_rk;
+            at.batch = B; at.max_len = max_len; at.d = d; at.H = n_heads; at.left = left; at.right = right;
+            at.rows = M; at.rk_rows = rk_rows; at.status = status;
+            { const int sp = prof_begin_span(PROF_ATTN);
+              const int rc = attention_forward(at, cfg.attn_impl, stream);
+              prof_end_span(sp);
+              if (sp >= 0) prof_launches[PROF_ATTN]++;
+              if (rc) return -1; }
+            if (act_quant_rows(cbuf, qA, sxA, M, d, stream)) return -1;
+            if (gemm_q8(qA, sxA, L.o_w, epi(OUT_RESID, ACT_NONE, 1.f, L.o_w.bias, x, d), M)) return -1;
+            if (layer_norm_q8(x, L.ln_conv_w, L.ln_conv_b, nullptr, none, qA, sxA, M, d, ACT_NONE, stream)) return -1;
+            if (gemm_q8(qA, sxA, L.pw1_w, epi(OUT_F32, ACT_NONE, 1.f, L.pw1_w.bias, h2, 2 * d), M)) return -1;
+            if (L.cnorm_scale) {
+                if (glu_dwconv(h2, L.dw_w, L.dw_b, L.cnorm_scale, L.cnorm_shift, cbuf, none, d_off, d_len, B, max_len, d,
+                               conv_k, pad_left, stream)) return -1;
+                if (act_quant_rows(cbuf, qA, sxA, M, d, stream)) return -1;
+            } else {
+                if (glu_dwconv(h2, L.dw_w, L.dw_b, nullptr, nullptr, cbuf, none, d_off, d_len, B, max_len, d, conv_k,
+                               pad_left, stream)) return -1;
+                if (layer_norm_q8(cbuf, L.cnorm_w, L.cnorm_b, nullptr, none, qA, sxA, M, d, ACT_SILU, stream)) return -1;
+            }
+            if (gemm_q8(qA, sxA, L.pw2_w, epi(OUT_RESID, ACT_NONE, 1.f, L.pw2_w.bias, x, d), M)) return -1;
+            if (layer_norm_q8(x, L.ln_ff2_w, L.ln_ff2_b, nullptr, none, qA, sxA, M, d, ACT_NONE, stream)) return -1;
+            if (gemm_q8(qA, sxA, L.ff2_w1, epi(OUT_F32, ACT_SILU, 1.f, L.ff2_w1.bias, fF, F), M)) return -1;
+            if (act_quant_rows(fF, qF, sxF, M, F, stream)) return -1;
+            if (gemm_q8(qF, sxF, L.ff2_w2, epi(OUT_RESID, ACT_NONE, 0.5f, L.ff2_w2.bias, x, d), M)) return -1;
+            if (layer_norm(x, L.ln_out_w, L.ln_out_b, x, none, M, d, ACT_NONE, stream)) return -1;
+            note_launch(11);   // 5 LayerNorms + attention + glu_dwconv + 4 activation quantisations (the contractions count themselves)
+            continue;
+        }
         // half FFN 1 (src/encoder.c:464-482,495-496)
         if (layer_norm(x, L.ln_ff1_w, L.ln_ff1_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
         if (gemm(hA, d, L.ff1_w1, epi(OUT_H16, ACT_SILU, 1.f, L.ff1_w1.bias, nullptr, 0, hF, F), M)) return -1;

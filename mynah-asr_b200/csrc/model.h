@@ -151,6 +151,10 @@ struct Model {
 
     // drivers (device pointers in / out, all on `stream`)
     int gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep, int M);
+    // int8-activation mode: qa [M, w.k] int8 rows with their scales sx [M] times a reference-native int8 weight
+    bool a8_ok(const QWeight &w) const { return w.fmt == FMT_MYNAH_Q8 && w.k % 128 == 0 && w.scales != nullptr; }
+    bool a8_layers = false;                          // cfg.a8 and every encoder-layer linear is a8_ok
+    int gemm_q8(const int8_t *qa, const float *sx, const QWeight &w, const GemmEpilogue &ep, int M);
     int subsample_item(const float *feats_dev, int t_mel, float *x_out, int *t_out);
     int encoder_layers(float *x, const std::vector<int> &lens, int left, int right, int first_layer, int n_run);
     // x [sum lens, d_model] -> out [sum lens, d_out]; prompt_ids (one per segment, may be null = all 0) select the

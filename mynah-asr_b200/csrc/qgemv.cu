@@ -392,6 +392,13 @@ qgemv_a8_kernel(const uint8_t *__restrict__ raw, const float *__restrict__ scale
     }
 }
 
+int act_quant_rows(const float *x, int8_t *qx, float *sx, int T, int k, cudaStream_t st) {
+    if (T <= 0) return 0;
+    act_quant_kernel<<<cdiv(T, 8), 256, 0, st>>>(x, qx, sx, T, k);
+    MB_CUDA(cudaGetLastError());
+    return 0;
+}
+
 int qgemv_a8(const QWeight &w, const float *x, float *out, int T, int32_t *block_dots, float *sx_out, cudaStream_t st) {
     if (T <= 0) return 0;
     if (w.k % 32) { set_error("qgemv_a8: k=%d not a multiple of 32", w.k); return -1; }

@@ -27,6 +27,7 @@ from dataclasses import dataclass, field
 import numpy as np
 
 GGML_F32, GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 8, 12, 14
+NATIVE_Q8 = -8        # not a ggml type: the reference's own per-row int8 (src/qmat.h:6-9), stored as int8 [n,k] + f32 scales [n]
 GGML_NAMES = {"f32": GGML_F32, "q4_0": GGML_Q4_0, "q8_0": GGML_Q8_0, "q4_k": GGML_Q4_K, "q6_k": GGML_Q6_K}
 
 
@@ -353,11 +354,45 @@ def make_model(cfg: ModelConfig, seed: int = 0, weight_std: float = 0.02):
         if gt in (GGML_Q4_K, GGML_Q6_K) and H % 256 != 0:
             gt = GGML_Q8_0
         T["joint.head.weight"] = Tensor("joint.head.weight", gt, (V + ND, H), QUANTIZERS[gt](w)) if gt != GGML_F32 \
-            else Tensor("joint.head.weight", GGML_F32, (V + ND, H), w)
+            else Tensor("joint.head.weight", GGML_F32, (V + ND, H), w.astype(np.float32))
         hb = np.zeros(V + ND, np.float32)
         hb[V - 1] = cfg.blank_bias
         f32t("joint.head.bias", hb)
     return T
+
+
+def quantize_rows_int8(w: np.ndarray):
+    """Per-row symmetric int8 as the reference's load-time quantiser writes it (mynah_asr_quantize_int8,
+    src/qmat.c:19-36): scale = amax / 127 (1 for an all-zero row), q = round-half-away(w * (1 / scale))."""
+    w = np.ascontiguousarray(w, np.float32)
+    amax = np.abs(w).max(axis=1)
+    scale = np.where(amax > 0, amax / np.float32(127.0), np.float32(1.0)).astype(np.float32)
+    v = (w * (np.float32(1.0) / scale)[:, None]).astype(np.float32)
+    q = np.where(v >= 0, v + np.float32(0.5), v - np.float32(0.5)).astype(np.float32).astype(np.int32).astype(np.int8)
+    return q, scale
+
+
+ENCODER_LINEARS = ("feed_forward1.linear1", "feed_forward1.linear2", "feed_forward2.linear1", "feed_forward2.linear2",
+                   "self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+                   "conv.pointwise_conv1", "conv.pointwise_conv2")
+
+
+def to_native_int8(tensors: dict, decode) -> dict:
+    """The same model with the ten linears of every encoder layer re-quantised to the reference-native per-row int8
+    format (what `--quant int8` does to them at load, src/encoder.c:121-137): tensor `name` becomes type NATIVE_Q8
+    with int8 data and `name.scales` holds the f32 row scales. decode(ggml_type, raw) -> f32 array decodes a stored
+    tensor. Everything else is kept."""
+    out = {}
+    for name, t in tensors.items():
+        if name.startswith("encoder.layers.") and name.endswith(".weight") and name.split(".", 3)[3][:-7] in ENCODER_LINEARS:
+            n = t.shape[0]
+            w = np.asarray(decode(t.ggml_type, t.raw), np.float32).reshape(n, -1)
+            q, s = quantize_rows_int8(w)
+            out[name] = Tensor(name, NATIVE_Q8, (n, w.shape[1]), q)
+            out[name + ".scales"] = Tensor(name + ".scales", GGML_F32, (n,), s)
+        else:
+            out[name] = t
+    return out
 
 
 def synth_audio(seconds: float, seed: int = 0, sample_rate: int = 16000) -> np.ndarray:
@@ -371,17 +406,18 @@ def synth_audio(seconds: float, seed: int = 0, sample_rate: int = 16000) -> np.n
 
 
 def write_safetensors(path: str, tensors: dict) -> None:
-    """name -> float32 ndarray, in the safetensors container the reference's
+    """name -> float32 (or int8) ndarray, in the safetensors container the reference's
     loader opens (8-byte little-endian header length, JSON header, raw data)."""
-    hdr, off = {}, 0
+    hdr, off, arrs = {}, 0, []
     for name, a in tensors.items():
-        a = np.ascontiguousarray(a, np.float32)
-        hdr[name] = {"dtype": "F32", "shape": list(a.shape), "data_offsets": [off, off + a.nbytes]}
+        a = np.ascontiguousarray(a) if getattr(a, "dtype", None) == np.int8 else np.ascontiguousarray(a, np.float32)
+        hdr[name] = {"dtype": "I8" if a.dtype == np.int8 else "F32", "shape": list(a.shape), "data_offsets": [off, off + a.nbytes]}
         off += a.nbytes
+        arrs.append(a)
     js = json.dumps(hdr, separators=(",", ":")).encode()
     js += b" " * ((8 - len(js) % 8) % 8)
     with open(path, "wb") as f:
         f.write(struct.pack("<Q", len(js)))
         f.write(js)
-        for a in tensors.values():
-            f.write(np.ascontiguousarray(a, np.float32).tobytes())
+        for a in arrs:
+            f.write(a.tobytes())

@@ -324,7 +324,13 @@ def pos_emb(T, d):
 def _lin(L, name, x):
     """A quantisable linear; L[name] is the EFFECTIVE f32 weight (what the
     reference holds after its eager block decode, src/weights.c:90-115)."""
-    y = gemm_wt(x, L[name])
+    if L.get("a8") and (name + "_q8") in L:
+        # int8 activations x reference-native int8 weights for every row count: the reference's arithmetic below
+        # 17 rows, and above with MYNAH_ASR_QGEMM=1 (src/qmat.c:508-551, 598-643)
+        q, s = L[name + "_q8"]
+        y = qmat_mul_a8_q8(x, q, s)
+    else:
+        y = gemm_wt(x, L[name])
     b = L.get(name + "_b")
     return y if b is None else (y + b[None, :]).astype(f32)
 

@@ -52,7 +52,8 @@ void ref_close(ref_model *m) {
     free(m);
 }
 
-/* quant: 0 f32, 1 int8, 2 int4 (mynah-native load-time quantisation).
+/* quant: 0 f32, 1 int8, 2 int4 (mynah-native load-time quantisation); + 16 keeps the transducer
+ * decoder's joint head in f32 while the encoder is quantised.
  * causal: -1 keeps what the tensor naming implies. durations NULL => RNNT. */
 ref_model *ref_open(const char *weights, const char *mel_filters, int quant, int causal,
                     int xscaling, int n_mels, int normalize_per_feature, int blank,
@@ -61,11 +62,13 @@ ref_model *ref_open(const char *weights, const char *mel_filters, int quant, int
     if (!m) return NULL;
     m->st = mynah_asr_st_open(weights);
     if (!m->st) { free(m); return NULL; }
+    const int dec_quant = (quant & 16) ? 0 : quant;
+    quant &= 15;
     if (mynah_asr_encoder_init(&m->enc, m->st, quant) != 0) { ref_close(m); return NULL; }
     if (causal >= 0) { m->enc.causal = causal; m->enc.ss.causal = causal; }
     if (xscaling) m->enc.xscale = sqrtf((float)m->enc.d_model);
     if (mynah_asr_st_get(m->st, "decoder.embedding.weight")) {
-        if (mynah_asr_decoder_init(&m->dec, m->st, blank, max_symbols, quant, durations,
+        if (mynah_asr_decoder_init(&m->dec, m->st, blank, max_symbols, dec_quant, durations,
                                    n_durations) != 0) { ref_close(m); return NULL; }
         m->has_dec = 1;
     }

@@ -47,3 +47,18 @@ def device_model(pkg, synth, cfg, tensors, **over):
               max_symbols=cfg.max_symbols, durations=tuple(cfg.durations))
     kw.update(over)
     return pkg.Model(tensors, **kw)
+
+# int8-activation mode (the reference's `--quant int8` with MYNAH_ASR_QGEMM=1): the ten linears of every layer stored
+# in the reference-native per-row int8 format; widths are multiples of 128 as the tensor-core path wants
+A8 = {
+    "ctc_a8": dict(d_model=256, n_layers=2, n_heads=4, ffn_dim=512, n_mels=80, decoder="ctc", vocab=65, wtype="f32"),
+    "tdt_a8": dict(d_model=256, n_layers=2, n_heads=2, ffn_dim=512, n_mels=128, decoder="tdt", vocab=97, pred_hidden=64,
+                   pred_layers=1, durations=(0, 1, 2, 3, 4), wtype="f32", causal=True, normalize=False, blank_bias=1.0),
+}
+A8_SECONDS = {"ctc_a8": 2.5, "tdt_a8": 2.0}
+
+
+def build_a8(synth, name, seed=1):
+    cfg = synth.config(name, **A8[name])
+    t = synth.make_model(cfg, seed=seed)
+    return cfg, synth.to_native_int8(t, lambda ty, raw: raw.view("float32"))

@@ -3,6 +3,7 @@
 on seeded synthetic models and audio. Run in a container that has the reference:
 
     make -C oracle && python tests/golden/make_golden.py
+    MYNAH_ASR_QGEMM=1 python tests/golden/make_golden.py ctc_a8 tdt_a8      (the int8-activation fixtures)
 
 The fixtures pin both the numpy oracle (tests/test_oracle_pin.py) and the CUDA path
 (tests/test_stages_gpu.py, tests/test_qmat_gpu.py, tests/test_aed_gpu.py, tests/test_stream_gpu.py) on machines where the reference itself is absent.
@@ -113,6 +114,37 @@ def prompt(name):
     print(name, {k: v.shape for k, v in out.items()}, "distinct", [len(set(out[f"tokens{i}"].tolist())) for i in range(3)])
 
 
+def a8(name):
+    """The reference with its int8 quantisation of the encoder linears (pre-quantised tensors, mapped as they are) and
+    its threaded int8 GEMM switched on (MYNAH_ASR_QGEMM=1: int8 activations for every row count, src/qmat.c:598-643).
+    The switch is read once per process, so this runs in a process of its own: `make_golden.py ctc_a8 tdt_a8`."""
+    assert os.environ.get("MYNAH_ASR_QGEMM") == "1"
+    cfg, tensors = cases.build_a8(synth, name)
+    d = tempfile.mkdtemp()
+    wp, mp = model_io.write_reference_files(d, cfg, tensors, synth)
+    rm = R.RefModel(wp, mp, quant=1 + 16, n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
+                    max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), causal=int(cfg.causal))
+    audio = synth.synth_audio(cases.A8_SECONDS[name], seed=7)
+    feats, valid = rm.log_mel(audio)
+    f = feats[:valid]
+    out = {"enc_raw": rm.encoder_forward(f, raw=True), "enc": rm.encoder_forward(f)}
+    pe = rm.pos_emb(rm.subsampling(f).shape[0])
+    out["layer0"] = rm.encoder_layer(0, rm.subsampling(f), pe)
+    f2, v2 = rm.log_mel(synth.synth_audio(cases.A8_SECONDS[name] * 0.5, seed=8))
+    b = rm.encoder_forward_batch([f, f2[:v2]])
+    out["batch0"], out["batch1"] = b[0], b[1]
+    t, fr = rm.ctc_decode(out["enc_raw"]) if cfg.decoder == "ctc" else rm.greedy_decode(out["enc"], cfg.max_symbols)
+    out["tokens"], out["frames"] = np.array(t, np.int32), np.array(fr, np.int32)
+    rm.close()
+    # the same weights through the float-activation path, to show the two modes differ by far more than the tolerance
+    rf = R.RefModel(wp, mp, quant=0, n_mels=cfg.n_mels, normalize=int(cfg.normalize), causal=int(cfg.causal))
+    out["enc_raw_f32"] = rf.encoder_forward(f, raw=True)
+    rf.close()
+    np.savez_compressed(os.path.join(HERE, f"ref_{name}.npz"), **out)
+    print(name, {k: v.shape for k, v in out.items()}, "tokens", len(t), "distinct", len(set(t)),
+          "a8 vs f32 rel", float(np.linalg.norm(out["enc_raw"] - out["enc_raw_f32"]) / np.linalg.norm(out["enc_raw_f32"])))
+
+
 def qmat():
     """mynah_asr_qmat_mul on weights quantised by the reference's own load-time
     quantiser, T = 1, 4 (int8-activation dots) and 48 (dequant + sgemm): the cases
@@ -136,7 +168,7 @@ if __name__ == "__main__":
     only = sys.argv[1:]
     if only:                      # regenerate only the named fixtures
         for name in only:
-            (prompt if name in cases.PROMPT else aed if name in cases.AED else pipeline)(name)
+            (a8 if name in cases.A8 else prompt if name in cases.PROMPT else aed if name in cases.AED else pipeline)(name)
         sys.exit(0)
     for name in cases.TINY:
         pipeline(name)

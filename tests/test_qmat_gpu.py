@@ -226,3 +226,53 @@ def test_address_keyed_hooks(gpu_pkg, synth):
     assert pkg.weights_resident() == 2
     pkg.weights_evict()
     assert pkg.weights_resident() == 0
+
+
+def test_values_outside_the_fp16_operand_range_are_reported(gpu_pkg):
+    """The tensor-core path carries operands as fp16 (hi, lo) pairs, which end at 65504. A larger activation or
+    weight must not come back as a silent inf/NaN: the call fails (-1), so a host using the reference's hook
+    convention falls back to its CPU path. Just below the limit the product is still f32-grade."""
+    rng = np.random.default_rng(5)
+    n, k, T = 64, 256, 40                                   # T > 16: the contraction kernel
+    w = rng.uniform(-1, 1, (n, k)).astype(np.float32)
+    x = rng.uniform(-1, 1, (T, k)).astype(np.float32)
+    m = gpu_pkg.QMat(gpu_pkg.F32, w, n, k)
+    big = (x * 6.0e4).astype(np.float32)                    # |x| < 65504
+    want = big.astype(np.float64) @ w.astype(np.float64).T
+    assert np.abs(m.mul(big) - want).max() <= 2e-6 * np.abs(want).max()
+    bad = x.copy()
+    bad[3, 7] = 1.0e5
+    with pytest.raises(gpu_pkg.BackendError, match="65504"):
+        m.mul(bad)
+    assert np.abs(m.mul(x) - x.astype(np.float64) @ w.astype(np.float64).T).max() <= 1e-4     # the handle still works
+    m.close()
+    wbad = w.copy()
+    wbad[0, 0] = 7.0e4
+    with pytest.raises(gpu_pkg.BackendError, match="65504"):
+        gpu_pkg.QMat(gpu_pkg.F32, wbad, n, k)
+    # the reference's hook under its own name returns -1 (the caller's cue to fall back)
+    wk = np.ascontiguousarray(w)
+    with pytest.raises(gpu_pkg.BackendError):
+        gpu_pkg.cuda_gemm_wt(bad, wk)
+    gpu_pkg.weights_evict()
+
+
+def test_a8_many_rows_on_the_tensor_cores_bit_exact(gpu_pkg):
+    """Int8 activations x reference-native int8 weights for more than 16 rows (tcgen05 kind::i8 contraction): the
+    result is (float)int32 * ws * sx with the exact int32 dot, so it equals the CPU restatement bit for bit, and a
+    row's bits do not depend on how many rows are multiplied with it (the reference's MYNAH_ASR_QGEMM=1 arithmetic,
+    src/qmat.c:598-643)."""
+    rng = np.random.default_rng(17)
+    for n, k in ((384, 1024), (200, 256), (1025, 512)):
+        w = rng.uniform(-1, 1, (n, k)).astype(np.float32)
+        q8, s8 = O.quantize_int8(w)
+        m = gpu_pkg.QMat(gpu_pkg.MYNAH_Q8, q8, n, k, scales=s8)
+        x = (rng.standard_normal((300, k)) * rng.uniform(0.1, 30, (300, 1))).astype(np.float32)
+        x[5] = 0.0                                              # an all-zero row: scale 0, output 0
+        want = O.qmat_mul_a8_q8(x, q8, s8)
+        got = m.mul(x, gpu_pkg.A8)
+        assert np.array_equal(got, want), (n, k)
+        for T in (17, 129):                                     # fewer rows, other tile counts: same bits per row
+            assert np.array_equal(m.mul(x[:T], gpu_pkg.A8), want[:T]), (n, k, T)
+        assert np.array_equal(m.mul(x[:9], gpu_pkg.A8), want[:9])          # the row-dot kernel below 17 rows agrees too
+        m.close()
