@@ -73,13 +73,22 @@ def recipe_std(cfg, recipe: str) -> float:
     return 0.02 if recipe == "baseline" else 0.32 / float(np.sqrt(cfg.d_model))
 
 
-def cached_model(synth, name: str, rank: int, barrier, recipe: str = "baseline"):
-    """Synthetic weights are generated once per box (rank 0) and shared through a file."""
+def cached_model(synth, name: str, rank: int, barrier, recipe: str = "baseline", native_int8: bool = False):
+    """Synthetic weights are generated once per box (rank 0) and shared through a file. native_int8: the same
+    architecture and recipe with the encoder linears drawn in f32 and quantised per row to the reference-native
+    int8 format, as the reference's `--quant int8` does at load (the weights of the int8-activation mode)."""
     os.makedirs(CACHE, exist_ok=True)
     cfg = workload_config(synth, name)
-    path = os.path.join(CACHE, f"{name}_seed0_bb{cfg.blank_bias:g}" + ("" if recipe == "baseline" else "_" + recipe) + ".pkl")
+    path = os.path.join(CACHE, f"{name}_seed0_bb{cfg.blank_bias:g}" + ("" if recipe == "baseline" else "_" + recipe) +
+                        ("_int8" if native_int8 else "") + ".pkl")
     if rank == 0 and not os.path.exists(path):
-        tensors = synth.make_model(cfg, seed=0, weight_std=recipe_std(cfg, recipe))
+        if native_int8:
+            import dataclasses
+            cfg_f = dataclasses.replace(cfg, wtype="f32", wtype_out="")
+            tensors = synth.to_native_int8(synth.make_model(cfg_f, seed=0, weight_std=recipe_std(cfg, recipe)),
+                                           lambda ty, raw: raw.view(np.float32))
+        else:
+            tensors = synth.make_model(cfg, seed=0, weight_std=recipe_std(cfg, recipe))
         with open(path + ".tmp", "wb") as f:
             pickle.dump({k: (t.ggml_type, t.shape, t.raw) for k, t in tensors.items()}, f, protocol=4)
         os.replace(path + ".tmp", path)
@@ -301,8 +310,9 @@ def workload_desc(args, cfg):
            "aed": f"AED greedy ({cfg.aed_layers}-layer decoder, budget T+{cfg.aed_max_gen_delta})"}[cfg.decoder]
     return {"workload": f"{args.workload}: {SHAPES.get(args.workload, args.workload)}-shaped, {cfg.n_layers} layers d={cfg.d_model} "
                         f"ffn={cfg.ffn_dim}, {cfg.wtype.upper()} weights, {dec}, "
-                        + (f"{args.items} utterances per GPU, lengths U[{args.min_seconds:g}, {args.max_seconds:g}] s sorted into "
-                           f"batches of {args.batch}" if args.items else f"{args.batch} x {args.seconds:g} s per GPU"),
+                        + ((f"{args.items} utterances {'in all, dispatched over the GPUs longest-first' if getattr(args, 'scaling', 'weak') == 'strong' else 'per GPU'}, "
+                            f"lengths U[{args.min_seconds:g}, {args.max_seconds:g}] s sorted into batches of {args.batch}") if args.items else
+                           f"{args.batch} x {args.seconds:g} s {'in all' if getattr(args, 'scaling', 'weak') == 'strong' else 'per GPU'}"),
             "batch_per_gpu": args.batch, "audio_seconds": args.seconds if not args.items else "per item, see workload",
             "numerics": getattr(args, "mode", "strict"),
             "l2": "per-step working set (activations + weights, >1 GB) exceeds the 126 MB L2"}
@@ -331,6 +341,128 @@ def cpu_baseline(args, cfg, tensors, synth, model=None):
                       (f"(the median of the {args.items} items of a GPU step)" if args.items else f"(the GPU step is {args.batch} of these)")}, rep
 
 
+def int8_peak_tops(torch):
+    """Dense int8 tensor-core rate of this GPU as a library GEMM reaches it (torch._int_mm, 8192^3, best of 10,
+    CUDA events): the denominator for the int8-activation contractions. None if the library call is unavailable."""
+    try:
+        a = torch.randint(-127, 127, (8192, 8192), dtype=torch.int8, device="cuda")
+        b = torch.randint(-127, 127, (8192, 8192), dtype=torch.int8, device="cuda")
+        best = None
+        for _ in range(3):
+            torch._int_mm(a, b)
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); torch._int_mm(a, b); e1.record(); e1.synchronize()
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None or ms < best else best
+        return 2.0 * 8192 ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
+def hbm_roofline(pkg, synth, cfg, peaks):
+    """The bandwidth-bound half of the quantised matmul, timed live: one weight matrix larger than L2 in the
+    workload's own block format, streamed once per launch by the small-T kernel (qstream_tc_kernel for Q4_0 / Q8_0 /
+    Q4_K, the scalar kernel otherwise) at T = 1 and T = 8 rows. achieved = algorithmic bytes
+    (n k bytes-per-parameter + 4 T k + 4 T n) / average launch time (CUDA events on the kernel's stream, 50
+    launches after 2 warm-up launches)."""
+    fmt_of = {"q4_0": (pkg.GGML_Q4_0, synth.GGML_Q4_0, 18 / 32), "q8_0": (pkg.GGML_Q8_0, synth.GGML_Q8_0, 34 / 32),
+              "q4_k": (pkg.GGML_Q4_K, synth.GGML_Q4_K, 144 / 256)}
+    if cfg.wtype not in fmt_of:
+        return None
+    fmt, gt, bpp = fmt_of[cfg.wtype]
+    n, k = 65536, 4096                                     # 151 MB of Q4_0, 285 MB of Q8_0: larger than the 126 MB L2
+    rng = np.random.default_rng(7)
+    w = (rng.standard_normal((2048, k), dtype=np.float32) * np.float32(0.02))
+    raw = np.tile(synth.QUANTIZERS[gt](w), n // 2048)      # the same 2048 rows repeated: the kernel reads every byte anyway
+    m = pkg.QMat(fmt, raw, n, k)
+    peak = peaks.get("hbm_gbs") or 6650.0
+    out = {"kernel": "qstream_tc_kernel (tcgen05 kind::i8, block decode fused)", "bound": "hbm", "unit": "GB/s", "peak": peak,
+           "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs, a device-to-device copy)" if peaks.get("hbm_gbs") else "fallback 6.65 TB/s",
+           "weight": f"[{n}, {k}] {cfg.wtype.upper()}, {n * k * bpp / 1e6:.0f} MB", "rows": {}}
+    for T in (1, 8):
+        ms = m.time_ms(T, pkg.A16, 50)
+        algo = n * k * bpp + 4.0 * T * k + 4.0 * T * n
+        out["rows"][str(T)] = {"ms": ms, "achieved": algo / (ms * 1e-3) / 1e9, "frac": algo / (ms * 1e-3) / 1e9 / peak,
+                               "algorithmic_bytes": algo}
+    out["achieved"], out["frac"] = out["rows"]["1"]["achieved"], out["rows"]["1"]["frac"]
+    out["traffic"] = out["rows"]["1"]["algorithmic_bytes"] * 1.03
+    out["traffic_source"] = "estimate: algorithmic bytes x 1.03, the dram/algorithmic ratio ncu measured on this kernel and shape"
+    m.close()
+    return out
+
+
+def timed_steps(torch, model, bhs, dec_id, steps, warmup):
+    """`steps` resident passes over the uploaded batches after `warmup`: (milliseconds, per-category profile)."""
+    stream = torch.cuda.ExternalStream(model.stream())
+    for _ in range(warmup):
+        for bh in bhs:
+            model.batch_run(bh, dec_id)
+    torch.cuda.synchronize()
+    model.profile_begin()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        for bh in bhs:
+            model.batch_run(bh, dec_id)
+    e1.record(stream)
+    e1.synchronize()
+    return e0.elapsed_time(e1), model.profile_end()
+
+
+def a8_section(args, pkg, synth, torch, groups, dec_id, audio_s, peaks):
+    """The int8-activation mode on the same architecture: encoder linears as reference-native int8 weights,
+    int8 activations, integer contractions on the tensor cores (tcgen05 kind::i8). Timed like the headline
+    (inputs resident), with its own roofline entry against the measured int8 rate and its own parity report
+    against the reference run with the same int8 weights and MYNAH_ASR_QGEMM=1."""
+    cfg, tensors = cached_model(synth, args.workload, 0, lambda: None, native_int8=True)
+    dm = pkg.Model(tensors, n_mels=cfg.n_mels, mel_fb=synth.mel_filterbank(cfg.n_mels), window=synth.hann_window(),
+                   causal=int(cfg.causal), normalize=cfg.normalize, left=cfg.left, right=cfg.right, blank=cfg.vocab - 1,
+                   max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), strict=True, aed_heads=cfg.aed_heads, a8=True)
+    bhs = [dm.batch_upload(g) for g in groups]
+    if dec_id == 2:
+        for bh in bhs:
+            dm.batch_set_aed(bh, AED_PROMPT, AED_EOS, cfg.aed_max_gen_delta)
+    steps = max(2, min(args.steps, 5))
+    ms, prof = timed_steps(torch, dm, bhs, dec_id, steps, 2)
+    for bh in bhs:
+        dm.batch_free(bh)
+    g = prof["gemm"]
+    achieved = g["flops"] / (g["ms"] * 1e-3) / 1e12 if g["ms"] > 0 else None
+    peak = int8_peak_tops(torch)
+    src = "measured: torch._int_mm 8192^3, best of 10 (burst)"
+    if not peak:
+        peak, src = 4500.0, "nominal dense int8 rate (the library int8 GEMM was unavailable)"
+    out = {"value": audio_s * steps / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms / steps, "steps": steps,
+           "weights": "encoder linears per-row int8 (reference-native), the rest f32",
+           "roofline": {"kernel": "gemm_i8_kernel (tcgen05 kind::i8 contraction) + the fp16 contractions of subsampling / rel-pos / projector",
+                        "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOP/s", "frac": achieved / peak if achieved else None,
+                        "peak_source": src, "frac_of_bf16_sustained": achieved / peaks["bf16_tflops_sustained"] if achieved and peaks.get("bf16_tflops_sustained") else None,
+                        "launches": g["launches"], "kernel_ms_per_step": g["ms"] / steps, "flops_per_step": g["flops"] / steps},
+           "breakdown_ms_per_step": {k: v["ms"] / steps for k, v in prof.items()}}
+    if not args.no_cpu_baseline:
+        from oracle import parity, ref_binding as R
+        if R.available():
+            os.environ["MYNAH_ASR_QGEMM"] = "1"       # read once, at the reference's first many-row quantised product
+            wp, mp = ref_paths(args, cfg, tensors, synth, recipe="int8")
+            rm = R.RefModel(wp, mp, quant=1 + 16, n_mels=cfg.n_mels, normalize=int(cfg.normalize), blank=cfg.vocab - 1,
+                            max_symbols=cfg.max_symbols, durations=tuple(cfg.durations), causal=int(cfg.causal))
+            if cfg.decoder == "aed":
+                rm.aed_open(cfg.aed_layers, cfg.aed_heads, cfg.aed_max_seq, cfg.aed_max_gen_delta)
+            audio = synth.synth_audio(args.seconds, seed=100 + args.sample_index)
+            t0 = time.perf_counter()
+            ref_transcribe(rm, cfg, [audio])
+            ref_s = time.perf_counter() - t0
+            rep = parity.parity_report(dm, rm, cfg, tensors, audio, aed_prompt=AED_PROMPT, aed_eos=AED_EOS, fast=False, layerwise=True)
+            rm.close()
+            rep["reference"] = "oracle/_ref with the same int8 encoder weights (mapped pre-quantised), joint head f32, MYNAH_ASR_QGEMM=1"
+            out["parity"] = {k: v for k, v in rep.items() if not k.startswith("_")}
+            out["cpu_baseline"] = {"value": args.seconds / ref_s, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
+                                   "mode": "int8+qgemm", "sample": f"1 utterance x {args.seconds:g} s, one pass"}
+    dm.close()
+    return out
+
+
 def parity_diverse(args, pkg, synth, seconds):
     """Supplementary parity report on a second seeded model of the same architecture whose weights keep the
     encoder output varying over time (recipe "diverse"), so that the full-size greedy stream has many distinct
@@ -356,9 +488,17 @@ def run_streaming(args, pkg, synth, torch, dist, cfg, tensors, model, rank, worl
     (one step = one chunk of 8 (right + 1) mel frames = 80 (right + 1) ms of audio per stream). Steady state:
     the K/V caches are full before the timed region. Encoder step only; greedy decoding runs on the
     collected frames at stream end, as in the tests."""
-    S, left, right = args.streams, cfg.left, cfg.right
+    left, right = cfg.left, cfg.right
     q = right + 1
     chunk_mel, chunk_s = 8 * q, 0.08 * q
+    # --scaling strong: --streams is the total, every stream stays on one GPU (contiguous blocks);
+    # weak: --streams per GPU
+    import mynah_asr_b200.dispatch as dispatch
+    S = len(dispatch.sticky_streams(args.streams, world)[rank]) if args.scaling == "strong" else args.streams
+    S_total = args.streams if args.scaling == "strong" else args.streams * world
+    # a step feeds --chunk-ms of audio per stream: n_sub consecutive chunks of the encoder's own size
+    n_sub = max(1, int(round(args.chunk_ms / (chunk_s * 1e3)))) if args.chunk_ms else 1
+    step_s = chunk_s * n_sub
     grp = model.stream_open(S, left, right)
     lib = pkg.lib()
     # one long synthetic utterance supplies mel frames; stream s reads it at offset 13 s frames
@@ -397,7 +537,8 @@ def run_streaming(args, pkg, synth, torch, dist, cfg, tensors, model, rank, worl
     t_all0.record(stream)
     for a, b in evs:                                                     # value: chunks already resident in HBM
         a.record(stream)
-        dev_step()
+        for _ in range(n_sub):
+            dev_step()
         b.record(stream)
     t_all1.record(stream)
     t_all1.synchronize()
@@ -416,18 +557,19 @@ def run_streaming(args, pkg, synth, torch, dist, cfg, tensors, model, rank, worl
     prof = model.profile_end()
     # e2e: the public call with host buffers — mel chunk H2D, encoder step, greedy decoding of the chunk with the
     # transducer state carried on the device, new token ids D2H — all inside the timed region
-    host_chunks = [chunk_for(step_no + i, chunk_mel) for i in range(args.steps + 2)]
+    host_chunks = [chunk_for(step_no + i, chunk_mel) for i in range(args.steps * n_sub + 2)]
     e2e_lat, n_tok = [], 0
     for c in host_chunks[:2]:                                            # warm-up (first decode call builds the state)
         grp.step_decode(c)
     barrier()
     t0 = time.perf_counter()
-    for c in host_chunks[2:]:
-        pinned.copy_(torch.from_numpy(c))
+    for i in range(args.steps):
         t1 = time.perf_counter()
-        res = grp.step_decode(pinned.numpy())
+        for c in host_chunks[2 + i * n_sub:2 + (i + 1) * n_sub]:
+            pinned.copy_(torch.from_numpy(c))
+            res = grp.step_decode(pinned.numpy())
+            n_tok += sum(len(t) for t, _ in res)
         e2e_lat.append((time.perf_counter() - t1) * 1e3)
-        n_tok += sum(len(t) for t, _ in res)
     e2e_ms = (time.perf_counter() - t0) * 1e3
     barrier()
     grp.close()
@@ -448,30 +590,52 @@ def run_streaming(args, pkg, synth, torch, dist, cfg, tensors, model, rank, worl
     pct = lambda v, p: v[min(len(v) - 1, int(round(p * (len(v) - 1))))]
     e2e_sorted = sorted(e2e_lat)
     print(json.dumps({
-        "metric": METRIC, "value": S * world * chunk_s * args.steps / (ms_max * 1e-3), "unit": UNIT, "n_gpus": world,
+        "metric": METRIC, "value": S_total * step_s * args.steps / (ms_max * 1e-3), "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None,
+        "scaling": args.scaling, "vs_baseline": None,
         "dtype": "f16 x3 split (f32 accumulate)" if args.mode == "strict" else "f16 (f32 accumulate)", "data": "synthetic",
         "config": {"workload": f"{args.workload}: {SHAPES.get(args.workload, args.workload)}-shaped cache-aware streaming, {cfg.n_layers} layers "
-                               f"d={cfg.d_model}, {cfg.wtype.upper()} weights, left {left} right {right}, {S} streams per GPU in lock step, "
-                               f"{chunk_s * 1e3:g} ms chunks, caches full; value = encoder step, e2e = encoder step + per-chunk greedy decoding",
-                   "streams_per_gpu": S, "chunk_seconds": chunk_s, "numerics": args.mode,
+                               f"d={cfg.d_model}, {cfg.wtype.upper()} weights, left {left} right {right}, {S_total} streams over {world} GPU(s) "
+                               f"({S} on rank 0, each stream stays on its GPU) in lock step, {step_s * 1e3:g} ms of audio per stream and step "
+                               f"= {n_sub} chunk(s) of the encoder's {chunk_s * 1e3:g} ms, caches full; value = encoder steps, "
+                               f"e2e = encoder steps + per-chunk greedy decoding",
+                   "streams_total": S_total, "streams_rank0": S, "step_seconds": step_s, "chunk_seconds": chunk_s, "numerics": args.mode,
                    "l2": "weights (> 600 MB) exceed the 126 MB L2"},
         "chunk_latency_ms": {"p50": pct(lat, 0.5), "p99": pct(lat, 0.99), "max": lat[-1],
-                             "e2e_p50": pct(e2e_sorted, 0.5), "e2e_p99": pct(e2e_sorted, 0.99)},
-        "e2e": {"value": S * world * chunk_s * args.steps / (e2e_max * 1e-3), "unit": UNIT,
-                "h2d_bytes_per_step": int(S * chunk_mel * cfg.n_mels * 4), "d2h_bytes_per_step": int(8 * n_tok / max(args.steps, 1)),
+                             "e2e_p50": pct(e2e_sorted, 0.5), "e2e_p99": pct(e2e_sorted, 0.99),
+                             "per": f"step of {step_s * 1e3:g} ms of audio per stream (rank 0)"},
+        "e2e": {"value": S_total * step_s * args.steps / (e2e_max * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": int(S * chunk_mel * n_sub * cfg.n_mels * 4), "d2h_bytes_per_step": int(8 * n_tok / max(args.steps, 1)),
                 "includes": "encoder step + per-chunk greedy decoding", "tokens_per_step": n_tok / max(args.steps, 1)},
         "gpu_launches": launches,
         "roofline": {"kernel": "gemm_tc_kernel (tcgen05 contraction)", "bound": "tensor", "achieved": achieved, "peak": peak_tf,
                      "unit": "TFLOP/s", "frac": achieved / peak_tf if achieved else None,
-                     "traffic": g["bytes"] / prof_steps * GEMM_TRAFFIC_RATIO, "traffic_unit": "bytes per step (all contraction launches)",
-                     "launches": g["launches"], "kernel_ms_per_step": g["ms"] / prof_steps, "flops_per_step": g["flops"] / prof_steps,
+                     "traffic": g["bytes"] / prof_steps * GEMM_TRAFFIC_RATIO, "traffic_unit": "bytes per chunk (all contraction launches)",
+                     "traffic_source": "estimate: algorithmic bytes x 0.853, the dram/algorithmic ratio ncu measured on one launch",
+                     "launches": g["launches"], "kernel_ms_per_chunk": g["ms"] / prof_steps, "flops_per_chunk": g["flops"] / prof_steps,
                      "mma_flops_multiplier": 3 if args.mode == "strict" else 1},
         "clocks": clk,
-        "cpu_baseline": {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference",
-                         "sample": "not timed for the streaming mode"},
+        "cpu_baseline": stream_cpu_baseline(args, cfg, tensors, synth) if world == 1 and not args.no_cpu_baseline else
+                        {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference", "sample": "timed at N=1 only"},
     }))
+
+
+def stream_cpu_baseline(args, cfg, tensors, synth):
+    """One stream through the reference's streaming encoder step on this host, chunk by chunk (bounded: 10 s)."""
+    from oracle import ref_binding as R
+    if not R.available():
+        return {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference", "sample": "oracle/_ref not built on this box"}
+    rm = ref_open(args, cfg, tensors, synth)
+    secs = 10.0
+    t0 = time.perf_counter()
+    lat, frames = ref_stream_latencies(rm, cfg, synth, secs, 100)
+    dt = time.perf_counter() - t0
+    rm.close()
+    lat = sorted(lat[1:]) or lat
+    pct = lambda v, p: v[min(len(v) - 1, int(round(p * (len(v) - 1))))]
+    return {"value": secs / dt, "unit": UNIT, "cores": os.cpu_count(), "kind": "reference", "mode": "f32",
+            "sample": f"1 stream x {secs:g} s through mynah_asr_enc_stream_step chunk by chunk (encoder only; the GPU step is {args.streams} streams)",
+            "chunk_latency_ms": {"p50": pct(lat, 0.5), "p99": pct(lat, 0.99), "chunk_ms": 80 * (cfg.right + 1)}}
 
 
 def main():
@@ -490,12 +654,17 @@ def main():
     ap.add_argument("--max-seconds", type=float, default=120.0)
     ap.add_argument("--streams", type=int, default=0, help="causal workloads: concurrent streams per GPU through the streaming step")
     ap.add_argument("--mode", default="strict", choices=["strict", "fast"])
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
+                    help="weak: the workload per GPU is fixed; strong: ONE seeded workload (all --items, or all --streams) is "
+                         "dispatched over the GPUs (longest-first buckets offline, sticky streams online)")
+    ap.add_argument("--chunk-ms", type=float, default=0.0, help="streaming: audio fed per stream and step (a multiple of the encoder's chunk)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: only the resident-input timing")
     ap.add_argument("--blank-bias", type=float, default=None, help="bias of the blank logit of the synthetic transducer head")
     ap.add_argument("--cpu-mode", default="f32", choices=list(CPU_MODES), help="reference arm: f32 (blocks decoded at load + sgemm), "
                     "or the reference's own int8 / int4 load-time quantisation; MYNAH_ASR_QGEMM=1 in the environment adds its threaded int8 GEMM")
     ap.add_argument("--cpu-batch", type=int, default=1, help="reference arm: utterances per step through its packed-batch encoder")
+    ap.add_argument("--no-extra", action="store_true", help="skip the extra sections (fast numerics, batch 1, int8-activation mode)")
     ap.add_argument("--no-diverse", action="store_true", help="skip the supplementary parity report on the diverse-recipe model")
     args = ap.parse_args()
     defaults = {"cfg0": (1, 30.0), "cfg4": (32, 20.0)}           # batch, seconds as the configs word them
@@ -552,7 +721,17 @@ def main():
             dist.destroy_process_group()
         return
     # this rank's utterances: global item ids shard over ranks (weak scaling: batch per GPU fixed)
-    if args.items:
+    import mynah_asr_b200.dispatch as dispatch
+    strong = None
+    if args.scaling == "strong":
+        # ONE seeded workload for every N: all ranks compute the same assignment from the lengths alone
+        all_secs = item_seconds(args, 0) if args.items else [args.seconds] * args.batch
+        parts = dispatch.lpt_assign(all_secs, world, bucket=args.batch)
+        mine = [i for b in dispatch.rank_batches(parts[rank], all_secs, args.batch) for i in b]
+        secs, seeds = [all_secs[i] for i in mine], [100 + i for i in mine]
+        strong = {"items_total": len(all_secs), "items_per_rank": [len(p_) for p_ in parts],
+                  "imbalance_modelled": dispatch.imbalance(all_secs, parts), "mine": mine, "audio_total_s": float(sum(all_secs))}
+    elif args.items:
         secs = item_seconds(args, rank)
         seeds = [100 + rank * args.items + i for i in range(args.items)]
     else:
@@ -635,10 +814,24 @@ def main():
     d2h = sum(8 * len(r[0]) for r in res)
 
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device="cuda")
+    per_rank = [t.clone() for _ in range(world)]
     if world > 1:
+        dist.all_gather(per_rank, t)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_max, e2e_max = t.tolist()
-    total_audio = audio_s * world
+    total_audio = strong["audio_total_s"] if strong else audio_s * world
+    if strong:
+        # transcripts gathered on the host by item index (the only thing that crosses ranks, off the timed path)
+        part = {i: r for i, r in zip(strong.pop("mine"), res)}
+        parts_all = [None] * world
+        if world > 1:
+            dist.all_gather_object(parts_all, part)
+        else:
+            parts_all = [part]
+        merged = dispatch.gather_by_index(parts_all, strong["items_total"])
+        busy = [float(p_[0]) / args.steps for p_ in per_rank]
+        strong.update({"per_rank_ms_per_step": busy, "imbalance_measured": max(busy) / (sum(busy) / len(busy)),
+                       "transcripts_gathered": len(merged), "tokens_total": sum(len(r[0]) for r in merged)})
 
     if rank == 0:
         import json as _json
@@ -656,7 +849,7 @@ def main():
         line = {
             "metric": METRIC, "value": total_audio * args.steps / (ms_max * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_max / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None,
+            "scaling": args.scaling, "vs_baseline": None,
             "dtype": "f16 x3 split (f32 accumulate)" if args.mode == "strict" else "f16 (f32 accumulate)",
             "data": "synthetic", "config": workload_desc(args, cfg),
             "e2e": {"value": total_audio * args.steps / (e2e_max * 1e-3), "unit": UNIT,
@@ -682,6 +875,45 @@ def main():
                                        model.decoder_clocks())),
             "clocks": clk,
         }
+        if strong:
+            line["dispatch"] = strong
+        if world == 1 and not args.no_extra and args.mode == "strict":
+            # fast numerics (one fp16 product per term) on the same model and inputs; its accuracy is in `parity`
+            model.set_strict(False)
+            bh2 = [model.batch_upload(g_) for g_ in groups]
+            if dec_id == 2:
+                for bh in bh2:
+                    model.batch_set_aed(bh, AED_PROMPT, AED_EOS, cfg.aed_max_gen_delta)
+            fsteps = max(2, min(args.steps, 5))
+            fms, fprof = timed_steps(torch, model, bh2, dec_id, fsteps, 2)
+            model.set_strict(True)
+            fg = fprof["gemm"]
+            fach = fg["flops"] / (fg["ms"] * 1e-3) / 1e12 if fg["ms"] > 0 else None
+            line["fast"] = {"value": audio_s * fsteps / (fms * 1e-3), "unit": UNIT, "ms_per_step": fms / fsteps,
+                            "roofline": {"kernel": "gemm_tc_kernel<.,1>", "bound": "tensor", "achieved": fach, "peak": peak_tf,
+                                         "unit": "TFLOP/s", "frac": fach / peak_tf if fach else None,
+                                         "kernel_ms_per_step": fg["ms"] / fsteps},
+                            "note": "single fp16 product per term; encoder rel-L2 against the reference under parity.encoder_rel_l2.fast_raw"}
+            if not args.items and args.batch > 1:
+                # one utterance per step (the configuration is quoted at batch 1 as well)
+                one = [model.batch_upload(groups[0][:1])]
+                if dec_id == 2:
+                    model.batch_set_aed(one[0], AED_PROMPT, AED_EOS, cfg.aed_max_gen_delta)
+                bms, _ = timed_steps(torch, model, one, dec_id, 5, 2)
+                model.batch_free(one[0])
+                t0 = time.perf_counter()
+                for _ in range(5):
+                    model.transcribe_batch(groups[0][:1], dec_id) if dec_id != 2 else model.transcribe_batch_aed(groups[0][:1], AED_PROMPT, AED_EOS, cfg.aed_max_gen_delta)
+                b1_e2e = (time.perf_counter() - t0) / 5
+                line["batch1"] = {"value": secs[0] * 5 / (bms * 1e-3), "unit": UNIT, "ms_per_step": bms / 5,
+                                  "e2e": secs[0] / b1_e2e, "workload": f"1 x {secs[0]:g} s per step"}
+            for bh in bh2:
+                model.batch_free(bh)
+            line["roofline_hbm"] = hbm_roofline(pkg, synth, cfg, peaks)
+            try:
+                line["a8"] = a8_section(args, pkg, synth, torch, groups, dec_id, audio_s, peaks)
+            except pkg.BackendError as e:
+                line["a8"] = {"unavailable": str(e)}
         if world == 1 and not args.no_cpu_baseline:
             cb, rep = cpu_baseline(args, cfg, tensors, synth, model)
             if rep is not None:       # the reference decoded the same utterance as item `sample_index` of this rank

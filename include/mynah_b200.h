@@ -8,10 +8,17 @@
  * caller are malloc()'d and freed by the caller with free(); inputs are borrowed.
  * There is no CPU fallback inside: if the device path cannot run, the call fails.
  *
- * Threading: a model is immutable after mynah_b200_model_finalize() and may be
- * shared; calls that run the encoder or a decoder on the same model serialise on
- * the model's stream and workspace. One process drives one GPU (cudaSetDevice by
- * the caller, or MYNAH_B200_DEVICE / LOCAL_RANK through mynah_b200_select_device).
+ * Threading: a model is immutable after mynah_b200_model_finalize() and may be shared by
+ * several host threads. Every call that runs the encoder or a decoder takes one of the
+ * model's execution contexts (its own CUDA stream, workspace arena and status word over the
+ * shared weights) for its duration: up to max_contexts (default 4, env MYNAH_B200_CONTEXTS,
+ * mynah_b200_model_set_max_contexts) calls run side by side, further ones wait for a free
+ * context; there is no lock around the compute. A single-threaded caller always runs on the
+ * first context. A stream group stays on the context that opened it. The result of a call does
+ * not depend on the context it ran on nor on what runs beside it. One process drives one GPU
+ * (cudaSetDevice by the caller, or MYNAH_B200_DEVICE / LOCAL_RANK through
+ * mynah_b200_select_device); the model remembers its device and makes it current for the
+ * calling thread.
  */
 #ifndef MYNAH_B200_H
 #define MYNAH_B200_H
@@ -160,6 +167,10 @@ int mynah_b200_model_set_mel(mynah_b200_model *m, const float *mel_fb, const flo
  * (src/encoder.c:56-183, src/subsampling.c:14-58, src/decoder.c:14-62, src/decoder_ctc.c:11-22),
  * uploads and decodes them; replaces the lazy per-pointer upload of src/cuda_gemm.cu:96-130 */
 int mynah_b200_model_finalize(mynah_b200_model *m);
+/* upper bound of execution contexts (concurrent calls) of a model; contexts are created on demand, each
+ * with its own workspace (sized by the largest call it has served). No counterpart in the reference, whose
+ * per-thread state is thread-local (src/cuda_gemm.cu:50-60). */
+int mynah_b200_model_set_max_contexts(mynah_b200_model *m, int n);
 /* switches the numerics of the tensor-core contractions of later calls: 1 = three fp16 products per term
  * (f32-grade, the default), 0 = a single fp16 product. The weights serve both. A stream group keeps the
  * mode of the step it captured: do not switch while one is open. No counterpart in the reference (its
@@ -277,7 +288,7 @@ void mynah_b200_batch_free(mynah_b200_batch *h);
 /* ---- introspection for tests and benchmarks ------------------------------------- */
 /* number of kernels this library launched since the last reset (its own launches only) */
 long long mynah_b200_launch_count(int reset);
-/* CUDA stream the model runs on (a cudaStream_t), for event timing by the caller */
+/* CUDA stream of the model's first execution context (a cudaStream_t), for event timing by a single-threaded caller */
 void *mynah_b200_model_stream(mynah_b200_model *m);
 /* Per-category device timing of a model's launches (CUDA events recorded on the model's stream
  * around each launch): categories 0 contraction (tcgen05), 1 attention, 2 element-wise,

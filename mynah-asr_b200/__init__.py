@@ -150,6 +150,7 @@ def lib():
     L.mynah_b200_model_finalize.argtypes = [vp]
     L.mynah_b200_model_free.argtypes = [vp]
     L.mynah_b200_model_set_strict.argtypes = [vp, ci]
+    L.mynah_b200_model_set_max_contexts.argtypes = [vp, ci]
     L.mynah_b200_model_dims.argtypes = [vp, c_ip]
     L.mynah_b200_model_stream.restype = vp
     L.mynah_b200_model_stream.argtypes = [vp]
@@ -358,6 +359,10 @@ class Model:
             self.h = None
 
     __del__ = close
+
+    def set_max_contexts(self, n: int):
+        """upper bound of calls that may run side by side on this model (one execution context each)"""
+        _check(lib().mynah_b200_model_set_max_contexts(self.h, n), "model_set_max_contexts")
 
     def set_strict(self, strict: bool):
         """f32-grade three-product contractions (True) or a single fp16 product (False) for later calls"""

@@ -4,6 +4,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <condition_variable>
 #include <memory>
 
 #include "model.h"
@@ -12,7 +13,84 @@ using namespace mb;
 
 namespace mb { long long launch_count(bool reset); }
 
-struct mynah_b200_model { Model m; };
+// A model handle = the immutable weights + a small pool of execution contexts. Context 0 is `m` itself; further
+// contexts are shallow copies of it made on demand (same device pointers to the weights, their own CUDA stream,
+// workspace arena, status word and profiling state), so calls from several host threads run side by side on the
+// same weights — the counterpart of the reference's per-thread cuBLAS handle / stream / buffers over a shared
+// weight cache (src/cuda_gemm.cu:50-60,92-130).
+struct mynah_b200_model {
+    Model m;
+    std::vector<std::unique_ptr<Model>> extra;      // contexts 1..
+    std::vector<char> busy{0};                      // per context
+    std::mutex pool_mu;
+    std::condition_variable pool_cv;
+    int max_ctx = 4;
+    int device = 0;                                 // the GPU the model lives on
+    Model &ctx(int i) { return i == 0 ? m : *extra[(size_t)i - 1]; }
+    int n_ctx() const { return 1 + (int)extra.size(); }
+};
+
+namespace {
+// Takes a free context for the duration of a call (lowest index first, so a single-threaded caller always runs on
+// context 0); creates one while fewer than max_ctx exist, else waits. want >= 0: that context and no other (a
+// stream group's caches and captured graph belong to the context that opened it).
+class Lease {
+public:
+    explicit Lease(mynah_b200_model *h, int want = -1) : h_(h) {
+        cudaSetDevice(h->device);                    // a fresh host thread starts on device 0
+        std::unique_lock<std::mutex> lk(h->pool_mu);
+        for (;;) {
+            if (want >= 0) {
+                if (want < h->n_ctx() && !h->busy[(size_t)want]) { idx_ = want; break; }
+            } else {
+                for (int i = 0; i < h->n_ctx(); i++) if (!h->busy[(size_t)i]) { idx_ = i; break; }
+                if (idx_ >= 0) break;
+                if (h->n_ctx() < h->max_ctx && h->m.finalized) {
+                    if (Model *c = clone_context(h->m)) {
+                        h->extra.emplace_back(c);
+                        h->busy.push_back(0);
+                        idx_ = h->n_ctx() - 1;
+                        break;
+                    }
+                }
+            }
+            h->pool_cv.wait(lk);
+        }
+        h->busy[(size_t)idx_] = 1;
+    }
+    ~Lease() {
+        { std::lock_guard<std::mutex> lk(h_->pool_mu); h_->busy[(size_t)idx_] = 0; }
+        h_->pool_cv.notify_all();
+    }
+    Model &model() { return h_->ctx(idx_); }
+    int index() const { return idx_; }
+    Lease(const Lease &) = delete;
+    Lease &operator=(const Lease &) = delete;
+
+private:
+    static Model *clone_context(const Model &src) {
+        Model *c = new Model(src);                   // weights: the same device pointers
+        c->owned.clear();                            // ... which only context 0 owns
+        c->prof_spans.clear(); c->prof_used = 0; c->prof_on = false;
+        c->ws = Arena();
+        c->stream = nullptr; c->status = nullptr;
+        if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); delete c; return nullptr; }
+        c->status = (int *)c->dev_alloc(sizeof(int));
+        if (!c->status || cudaMemset(c->status, 0, sizeof(int)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) { delete c; return nullptr; }
+        return c;
+    }
+    mynah_b200_model *h_;
+    int idx_ = -1;
+};
+
+// Runs fn on every context while none of them is in a call.
+template <typename F>
+void with_all_contexts_idle(mynah_b200_model *h, F fn) {
+    std::unique_lock<std::mutex> lk(h->pool_mu);
+    h->pool_cv.wait(lk, [&] { for (char b : h->busy) if (b) return false; return true; });
+    for (int i = 0; i < h->n_ctx(); i++) fn(h->ctx(i));
+}
+}  // namespace
 struct mynah_b200_qmat {
     QWeight w;
     std::vector<void *> owned;
@@ -31,6 +109,7 @@ struct mynah_b200_batch {
 
 struct mynah_b200_stream_group {
     mynah_b200_model *model = nullptr;
+    int ctx = 0;                         // the execution context the group lives on
     mb::StreamState st;
 };
 
@@ -97,6 +176,8 @@ mynah_b200_model *mynah_b200_model_new(const mynah_b200_config *cfg) {
     if (!mynah_b200_available()) { set_error("no sm_100 CUDA device available"); return nullptr; }
     mynah_b200_model *h = new mynah_b200_model();
     if (cfg) h->m.cfg = *cfg; else mynah_b200_config_default(&h->m.cfg);
+    cudaGetDevice(&h->device);
+    if (const char *e = getenv("MYNAH_B200_CONTEXTS")) { const int n = atoi(e); if (n >= 1 && n <= 64) h->max_ctx = n; }
     if (cudaStreamCreateWithFlags(&h->m.stream, cudaStreamNonBlocking) != cudaSuccess) {
         set_error("cudaStreamCreate failed"); delete h; return nullptr;
     }
@@ -429,10 +510,17 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
 
 void mynah_b200_model_free(mynah_b200_model *h) { delete h; }
 
+int mynah_b200_model_set_max_contexts(mynah_b200_model *h, int n) {
+    if (!h || n < 1 || n > 64) { set_error("model_set_max_contexts: 1..64"); return -1; }
+    std::lock_guard<std::mutex> lk(h->pool_mu);
+    if (n < h->n_ctx()) { set_error("model_set_max_contexts: %d contexts already exist", h->n_ctx()); return -1; }
+    h->max_ctx = n;
+    return 0;
+}
+
 int mynah_b200_model_set_strict(mynah_b200_model *h, int strict) {
     if (!h) { set_error("model_set_strict: null model"); return -1; }
-    std::lock_guard<std::mutex> lk(h->m.mu);
-    h->m.cfg.strict = strict ? 1 : 0;
+    with_all_contexts_idle(h, [&](Model &c) { c.cfg.strict = strict ? 1 : 0; });
     return 0;
 }
 
@@ -484,8 +572,8 @@ extern "C" {
 
 float *mynah_b200_log_mel(mynah_b200_model *h, const float *audio, size_t n, int *n_frames, int *valid_frames) {
     if (!h || !h->m.finalized || (!audio && n)) { set_error("log_mel: bad argument"); return nullptr; }
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(h);
+    Model &m = lease.model();
     const int hop = m.cfg.hop_length, T = 1 + (int)(n / hop), valid = (int)(n / hop), nm = m.cfg.n_mels;
     if (m.ws.reserve(n * 4 + (size_t)T * nm * 4 + (1 << 20))) return nullptr;
     m.ws.reset();
@@ -503,8 +591,8 @@ float *mynah_b200_log_mel(mynah_b200_model *h, const float *audio, size_t n, int
 
 float *mynah_b200_subsampling_forward(mynah_b200_model *h, const float *feats, int T, int n_mels, int *t_out) {
     if (!h || !h->m.finalized || !feats || T <= 0 || n_mels != h->m.cfg.n_mels) { set_error("subsampling_forward: bad argument"); return nullptr; }
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(h);
+    Model &m = lease.model();
     const int T3 = m.enc_len(T);
     if (m.ws.reserve(ss_bytes(m, T) + (size_t)T * n_mels * 4 + (size_t)T3 * m.d_model * 4 + (1 << 20))) return nullptr;
     m.ws.reset();
@@ -522,8 +610,8 @@ float *mynah_b200_subsampling_forward(mynah_b200_model *h, const float *feats, i
 
 int mynah_b200_encoder_layer(mynah_b200_model *h, int li, float *x, int T, int left, int right) {
     if (!h || !h->m.finalized || !x || T <= 0 || li < 0 || li >= h->m.n_layers) { set_error("encoder_layer: bad argument"); return -1; }
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(h);
+    Model &m = lease.model();
     if (m.ws.reserve(enc_bytes(m, T, 2 * T - 1) + (size_t)T * m.d_model * 4)) return -1;
     m.ws.reset();
     float *xd = m.ws.get<float>((size_t)T * m.d_model);
@@ -538,8 +626,8 @@ int mynah_b200_encoder_layer(mynah_b200_model *h, int li, float *x, int T, int l
 int mynah_b200_encoder_forward_batch(mynah_b200_model *h, const float *const *feats, const int *t_mel, int batch,
                                      int n_mels, const int *prompt_ids, int left, int right, float **outs, int *t_outs) {
     if (!h || !h->m.finalized || batch <= 0 || n_mels != h->m.cfg.n_mels) { set_error("encoder_forward_batch: bad argument"); return -1; }
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(h);
+    Model &m = lease.model();
     size_t M = 0, rk = 0, fbytes = 0, ssmax = 0;
     for (int b = 0; b < batch; b++) {
         const size_t t = t_mel[b] > 0 ? m.enc_len(t_mel[b]) : 0;
@@ -575,8 +663,8 @@ int mynah_b200_encoder_forward_batch(mynah_b200_model *h, const float *const *fe
 static float *forward_one(mynah_b200_model *h, const float *feats, int t_mel, int n_mels, int prompt_id, int left, int right,
                           int raw, int *t_out) {
     if (!h || !h->m.finalized || !feats || t_mel <= 0 || n_mels != h->m.cfg.n_mels) { set_error("encoder_forward: bad argument"); return nullptr; }
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(h);
+    Model &m = lease.model();
     const size_t M = m.enc_len(t_mel);
     if (m.ws.reserve((size_t)t_mel * n_mels * 4 + ss_bytes(m, t_mel) + enc_bytes(m, M, 2 * M) + M * ((size_t)m.d_model + m.d_out) * 4 + (1 << 20))) return nullptr;
     m.ws.reset();
@@ -608,8 +696,8 @@ float *mynah_b200_encoder_forward_raw(mynah_b200_model *h, const float *feats, i
 
 int mynah_b200_ctc_decode(mynah_b200_model *h, const float *enc_out, int T, int *tokens, int *frames, int cap) {
     if (!h || !h->m.finalized || !enc_out || T < 0) { set_error("ctc_decode: bad argument"); return -1; }
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(h);
+    Model &m = lease.model();
     if (T == 0) return 0;
     if (m.ws.reserve((size_t)T * (m.d_model * 8 + m.ctc_vocab * 4 + 8) + (1 << 20))) return -1;
     m.ws.reset();
@@ -624,8 +712,8 @@ int mynah_b200_ctc_decode(mynah_b200_model *h, const float *enc_out, int T, int 
 
 int mynah_b200_greedy_decode(mynah_b200_model *h, const float *enc, int T, int *tokens, int *frames, int cap) {
     if (!h || !h->m.finalized || !enc || T < 0) { set_error("greedy_decode: bad argument"); return -1; }
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(h);
+    Model &m = lease.model();
     if (T == 0) return 0;
     if (m.ws.reserve((size_t)T * m.d_out * 4 + dec_bytes(m, T))) return -1;
     m.ws.reset();
@@ -644,8 +732,8 @@ int mynah_b200_aed_decode_batch(mynah_b200_model *h, const float *const *encs, c
     if (!h || !h->m.finalized || !encs || !Ts || batch <= 0 || !prompts || !n_prompts || !caps || !tokens || !n_tokens) {
         set_error("aed_decode_batch: bad argument"); return -1;
     }
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(h);
+    Model &m = lease.model();
     if (!m.has_aed) { set_error("model has no AED decoder"); return -1; }
     size_t total = 0;
     int max_len = 0;
@@ -702,23 +790,25 @@ void mynah_b200_batch_set_aed(mynah_b200_batch *bt, const int *prompt, int n_pro
 // ------------------------------------------------------------ cache-aware streaming
 mynah_b200_stream_group *mynah_b200_stream_open(mynah_b200_model *h, int n_streams, int left_ctx, int right_ctx) {
     if (!h || !h->m.finalized) { set_error("stream_open: bad argument"); return nullptr; }
-    std::lock_guard<std::mutex> lk(h->m.mu);
+    Lease lease(h);
+    Model &m = lease.model();
     mynah_b200_stream_group *g = new mynah_b200_stream_group();
     g->model = h;
-    if (h->m.stream_open(g->st, n_streams, left_ctx, right_ctx)) { h->m.stream_close(g->st); delete g; return nullptr; }
+    g->ctx = lease.index();
+    if (m.stream_open(g->st, n_streams, left_ctx, right_ctx)) { m.stream_close(g->st); delete g; return nullptr; }
     return g;
 }
 
 void mynah_b200_stream_close(mynah_b200_stream_group *g) {
     if (!g) return;
-    { std::lock_guard<std::mutex> lk(g->model->m.mu); g->model->m.stream_close(g->st); }
+    { Lease lease(g->model, g->ctx); lease.model().stream_close(g->st); }
     delete g;
 }
 
 int mynah_b200_stream_set_prompts(mynah_b200_stream_group *g, const int *prompt_ids) {
     if (!g || !prompt_ids) { set_error("stream_set_prompts: bad argument"); return -1; }
-    Model &m = g->model->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(g->model, g->ctx);
+    Model &m = lease.model();
     if (g->st.exec) { set_error("stream_set_prompts: set the prompts before the first step"); return -1; }
     g->st.prompt_ids.assign(prompt_ids, prompt_ids + g->st.S);
     return 0;
@@ -728,8 +818,8 @@ int mynah_b200_stream_need(const mynah_b200_stream_group *g) { return g ? g->mod
 
 int mynah_b200_stream_step_device(mynah_b200_stream_group *g, const float *mel_dev, int n_mel, int is_last, float *out_dev) {
     if (!g || !mel_dev || !out_dev) { set_error("stream_step: bad argument"); return -1; }
-    Model &m = g->model->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(g->model, g->ctx);
+    Model &m = lease.model();
     if (n_mel != m.stream_need(g->st) && !is_last) { set_error("stream_step: %d mel frames given, %d needed", n_mel, m.stream_need(g->st)); return -1; }
     if (m.ws.reserve(m.stream_bytes(g->st, n_mel))) return -1;
     m.ws.reset();
@@ -740,8 +830,8 @@ int mynah_b200_stream_step_device(mynah_b200_stream_group *g, const float *mel_d
 
 int mynah_b200_stream_step(mynah_b200_stream_group *g, const float *mel, int n_mel, int is_last, float *out) {
     if (!g || !mel || !out || n_mel <= 0) { set_error("stream_step: bad argument"); return -1; }
-    Model &m = g->model->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(g->model, g->ctx);
+    Model &m = lease.model();
     if (n_mel != m.stream_need(g->st) && !is_last) { set_error("stream_step: %d mel frames given, %d needed", n_mel, m.stream_need(g->st)); return -1; }
     const size_t S = g->st.S, nin = S * n_mel * m.cfg.n_mels, nout = S * (g->st.q + 2) * m.d_out;
     if (m.ws.reserve(m.stream_bytes(g->st, n_mel) + (nin + nout) * 4 + 4096)) return -1;
@@ -759,8 +849,8 @@ int mynah_b200_stream_step(mynah_b200_stream_group *g, const float *mel, int n_m
 
 int mynah_b200_stream_mel_feed(mynah_b200_stream_group *g, const float *audio, int n, int finish, float *out, int cap_frames) {
     if (!g || !out) { set_error("stream_mel_feed: bad argument"); return -1; }
-    Model &m = g->model->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(g->model, g->ctx);
+    Model &m = lease.model();
     if (m.ws.reserve((size_t)g->st.S * (size_t)(cap_frames > 0 ? cap_frames : 1) * m.cfg.n_mels * 4 + (1 << 20))) return -1;
     m.ws.reset();
     return m.stream_mel_feed(g->st, audio, n, finish, out, cap_frames);
@@ -769,8 +859,8 @@ int mynah_b200_stream_mel_feed(mynah_b200_stream_group *g, const float *audio, i
 int mynah_b200_stream_step_decode(mynah_b200_stream_group *g, const float *mel, int n_mel, int is_last, int **tokens,
                                   int **frames, int *n_tokens) {
     if (!g || !mel || n_mel <= 0 || !tokens || !n_tokens) { set_error("stream_step_decode: bad argument"); return -1; }
-    Model &m = g->model->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(g->model, g->ctx);
+    Model &m = lease.model();
     if (!m.has_dec) { set_error("stream_step_decode: model has no transducer decoder"); return -1; }
     if (n_mel != m.stream_need(g->st) && !is_last) { set_error("stream_step: %d mel frames given, %d needed", n_mel, m.stream_need(g->st)); return -1; }
     const size_t S = g->st.S, nin = S * n_mel * m.cfg.n_mels, nout = S * (g->st.q + 2) * m.d_out;
@@ -900,8 +990,8 @@ static int run_batch_locked(Model &m, mynah_b200_batch *bt, const float *const *
 
 int mynah_b200_batch_run(mynah_b200_model *h, mynah_b200_batch *bt, int decoder) {
     if (!h || !bt) { set_error("batch_run: bad argument"); return -1; }
-    std::lock_guard<std::mutex> lk(h->m.mu);
-    return run_batch_locked(h->m, bt, bt->audio.data(), nullptr, decoder);
+    Lease lease(h);
+    return run_batch_locked(lease.model(), bt, bt->audio.data(), nullptr, decoder);
 }
 
 int mynah_b200_batch_fetch(mynah_b200_model *h, mynah_b200_batch *bt, int **tokens, int **frames, int *n_tokens) {
@@ -936,8 +1026,8 @@ int mynah_b200_transcribe_batch_prompts(mynah_b200_model *h, const float *const 
     mynah_b200_batch_set_prompts(&bt, prompt_ids);
     int rc;
     {
-        std::lock_guard<std::mutex> lk(h->m.mu);
-        rc = run_batch_locked(h->m, &bt, nullptr, audio, decoder);
+        Lease lease(h);
+        rc = run_batch_locked(lease.model(), &bt, nullptr, audio, decoder);
     }
     if (rc == 0) rc = mynah_b200_batch_fetch(h, &bt, tokens, frames, n_tokens);
     return rc;
@@ -952,8 +1042,8 @@ int mynah_b200_transcribe_batch_aed(mynah_b200_model *h, const float *const *aud
     mynah_b200_batch_set_aed(&bt, prompt, n_prompt, eos, max_gen_delta);
     int rc;
     {
-        std::lock_guard<std::mutex> lk(h->m.mu);
-        rc = run_batch_locked(h->m, &bt, nullptr, audio, 2);
+        Lease lease(h);
+        rc = run_batch_locked(lease.model(), &bt, nullptr, audio, 2);
     }
     if (rc == 0) rc = mynah_b200_batch_fetch(h, &bt, tokens, nullptr, n_tokens);
     return rc;
@@ -1203,16 +1293,16 @@ int mynah_asr_cuda_gemm_wt(const float *x, const float *w, float *out, int T, in
 
 void mynah_b200_profile_begin(mynah_b200_model *h) {
     if (!h) return;
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(h, 0);      // the first context: the one a single-threaded caller always runs on
+    Model &m = lease.model();
     m.prof_on = true; m.prof_used = 0;
     for (int i = 0; i < Model::PROF_NCAT; i++) { m.prof_flops[i] = 0; m.prof_bytes[i] = 0; m.prof_launches[i] = 0; }
 }
 
 int mynah_b200_profile_end(mynah_b200_model *h, double *ms, double *flops, long long *launches, int ncat) {
     if (!h) { set_error("profile_end: null model"); return -1; }
-    Model &m = h->m;
-    std::lock_guard<std::mutex> lk(m.mu);
+    Lease lease(h, 0);      // the first context: the one a single-threaded caller always runs on
+    Model &m = lease.model();
     m.prof_on = false;
     MB_CUDA(cudaStreamSynchronize(m.stream));
     for (int i = 0; i < ncat; i++) { ms[i] = 0; flops[i] = 0; launches[i] = 0; }

@@ -85,8 +85,7 @@ struct Model {
     std::map<std::string, float *> f32;              // small f32 tensors on the device
     std::vector<void *> owned;                       // every device allocation of the model
     bool finalized = false;
-    cudaStream_t stream = nullptr;
-    std::mutex mu;                                   // serialises forward calls on the workspace
+    cudaStream_t stream = nullptr;                   // of this execution context (the weights are shared between contexts)
     Arena ws;
     int *status = nullptr;                           // device status word (bounded waits)
 

@@ -52,7 +52,7 @@ def _first_divergence(a, b):
     return None if len(a) == len(b) else n
 
 
-def parity_report(dm, rm, cfg, tensors, audio, *, aed_prompt=None, aed_eos=None, fast=True) -> dict:
+def parity_report(dm, rm, cfg, tensors, audio, *, aed_prompt=None, aed_eos=None, fast=True, layerwise=False) -> dict:
     """dm: device Model (strict numerics on entry and on return), rm: ref_binding.RefModel of the same weights."""
     heads = model_io.oracle_heads(cfg, tensors)
     feats_r, valid = rm.log_mel(audio)
@@ -73,6 +73,17 @@ def parity_report(dm, rm, cfg, tensors, audio, *, aed_prompt=None, aed_eos=None,
         finally:
             dm.set_strict(True)
         rep["encoder_rel_l2"]["fast_raw"] = rel_l2(raw_f, raw_r)
+    if layerwise:
+        # every layer from the reference's own input to it: what one layer adds, apart from what the stack amplifies
+        x = rm.subsampling(f)
+        pe = rm.pos_emb(x.shape[0])
+        worst, errs = 0.0, []
+        for li in range(rm.n_layers):
+            xr = rm.encoder_layer(li, x, pe, left, right)
+            errs.append(rel_l2(dm.encoder_layer(li, x, left, right), xr))
+            x = xr
+        rep["encoder_rel_l2"]["layerwise_max"] = float(max(errs))
+        rep["encoder_rel_l2"]["layerwise_median"] = float(np.median(errs))
     # ---- per-frame head logits
     lg_r = _probe_logits(cfg, heads, raw_r, enc_r)
     if lg_r is not None:
