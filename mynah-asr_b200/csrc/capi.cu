@@ -1063,8 +1063,14 @@ mynah_b200_qmat *mynah_b200_qmat_create(int fmt, const void *data, const float *
     if (!q->status) { delete q; return nullptr; }
     cudaMemset(q->status, 0, sizeof(int));
     cudaDeviceSynchronize();
-    if (tmp.upload_weight(q->w, f, data, scales, n, k, planes, false) || tmp.check_status("qmat_create")) { delete q; return nullptr; }
+    if (tmp.upload_weight(q->w, f, data, scales, n, k, planes, false)) { delete q; return nullptr; }
     cudaDeviceSynchronize();
+    if (planes && tmp.check_status("qmat_create")) {
+        // a weight value outside the fp16 operand range: the handle keeps the stored blocks (small-T products,
+        // dequantisation) and drops the planes, so the many-row tensor-core product refuses instead of
+        // returning inf / NaN
+        q->w.hi = q->w.lo = nullptr;
+    }
     q->owned.swap(tmp.owned);
     q->stream = tmp.stream;
     tmp.stream = nullptr;
@@ -1123,7 +1129,7 @@ int mynah_b200_qmat_mul_device(const mynah_b200_qmat *q, const float *x, float *
         if (rc == 0) note_launch((T + 3) / 4);
         return rc;
     }
-    if (!w.hi) { set_error("qmat_mul: large-T path needs k %% 64 == 0 (k=%d)", w.k); return -1; }
+    if (!w.hi) { set_error("qmat_mul: the many-row path needs k %% 64 == 0 (k=%d) and weights below the fp16 operand limit 65504", w.k); return -1; }
     __half *hi = nullptr, *lo = nullptr;
     MB_CUDA(cudaMallocAsync(&hi, (size_t)T * w.k * 2, q->stream));
     if (cudaMallocAsync(&lo, (size_t)T * w.k * 2, q->stream) != cudaSuccess) {

@@ -70,6 +70,10 @@ def parity_report(dm, rm, cfg, tensors, audio, *, aed_prompt=None, aed_eos=None,
         dm.set_strict(False)
         try:
             raw_f = dm.encoder_forward(f, left, right, raw=True)
+            if cfg.decoder == "aed":
+                tok_f = dm.transcribe_batch_aed([audio], aed_prompt, aed_eos, cfg.aed_max_gen_delta)[0]
+            else:
+                tok_f = dm.transcribe_batch([audio], 1 if cfg.decoder == "ctc" else 0)[0][0]
         finally:
             dm.set_strict(True)
         rep["encoder_rel_l2"]["fast_raw"] = rel_l2(raw_f, raw_r)
@@ -124,5 +128,8 @@ def parity_report(dm, rm, cfg, tensors, audio, *, aed_prompt=None, aed_eos=None,
                      "first_divergence": fd,
                      "device_decoder_on_reference_frames_identical": tf_dev == tok_r,
                      "reference_decoder_on_device_frames_identical": tf_ref == tok_d}
+    if fast:
+        rep["tokens"]["fast_mode_identical"] = list(tok_f) == list(tok_r)
+        rep["tokens"]["fast_mode_first_divergence"] = _first_divergence(list(tok_f), list(tok_r))
     rep["_ref_tokens"], rep["_ref_frames"] = tok_r, fr_r
     return rep

@@ -23,12 +23,34 @@ def available() -> bool:
 
 
 _lib = None
+CUDA_LIB_PATH = os.path.join(_HERE, "_ref", "libmynah_ref_cuda.so")      # `make -C oracle cuda`: the reference on the B200 backend
 
 
 def lib():
     global _lib
     if _lib is None:
-        L = C.CDLL(LIB_PATH)
+        _lib = load(LIB_PATH)
+    return _lib
+
+
+_cuda_lib = None
+
+
+def cuda_lib():
+    """The reference with integration/*.patch applied, compiled with -DMYNAH_ASR_CUDA and linked against
+    libmynah_b200.so: its own mynah_asr_set_backend("cuda") routes the GEMMs and quantised products there."""
+    global _cuda_lib
+    if _cuda_lib is None:
+        L = load(CUDA_LIB_PATH)
+        L.mynah_asr_set_backend.argtypes = [C.c_char_p]
+        L.mynah_asr_backend.restype = C.c_int
+        _cuda_lib = L
+    return _cuda_lib
+
+
+def load(path):
+    if True:
+        L = C.CDLL(path)
         L.ref_open.restype = C.c_void_p
         L.ref_open.argtypes = [C.c_char_p, C.c_char_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                C.c_int, C.c_int, c_ip, C.c_int]
@@ -63,8 +85,7 @@ def lib():
         L.ref_qmat_mul_from_f32.argtypes = [c_fp, C.c_int, C.c_int, C.c_int, c_fp, c_fp, C.c_int]
         L.ingot_dequant.argtypes = [C.c_int, C.c_void_p, C.c_size_t, c_fp]
         L.ingot_quantize.argtypes = [C.c_int, c_fp, C.c_size_t, C.c_void_p]
-        _lib = L
-    return _lib
+    return L
 
 
 def _fp(a):
@@ -95,13 +116,13 @@ def ggml_quantize(ggml_type: int, w: np.ndarray, nbytes: int) -> np.ndarray:
     return out
 
 
-def qmat_mul(w: np.ndarray, qtype: int, x: np.ndarray) -> np.ndarray:
+def qmat_mul(w: np.ndarray, qtype: int, x: np.ndarray, library=None) -> np.ndarray:
     """The reference's mynah_asr_qmat_mul on W quantised by its own load-time
     quantiser (qtype 0 f32, 1 int8, 2 int4)."""
     w = np.ascontiguousarray(w, np.float32)
     x = np.ascontiguousarray(x, np.float32)
     out = np.empty((x.shape[0], w.shape[0]), np.float32)
-    rc = lib().ref_qmat_mul_from_f32(_fp(w), w.shape[0], w.shape[1], qtype, _fp(x), _fp(out), x.shape[0])
+    rc = (library or lib()).ref_qmat_mul_from_f32(_fp(w), w.shape[0], w.shape[1], qtype, _fp(x), _fp(out), x.shape[0])
     assert rc == 0
     return out
 
@@ -110,63 +131,64 @@ class RefModel:
     """The reference encoder/decoder over a safetensors file of f32 weights."""
 
     def __init__(self, weights_path, mel_path=None, *, quant=0, causal=-1, xscaling=0, n_mels=80,
-                 normalize=1, blank=0, max_symbols=10, durations=()):
+                 normalize=1, blank=0, max_symbols=10, durations=(), library=None):
+        self.L = library or lib()
         d = (C.c_int * max(1, len(durations)))(*durations)
-        self.h = lib().ref_open(weights_path.encode(), mel_path.encode() if mel_path else None, quant, causal,
+        self.h = self.L.ref_open(weights_path.encode(), mel_path.encode() if mel_path else None, quant, causal,
                                 xscaling, n_mels, normalize, blank, max_symbols, d if durations else None,
                                 len(durations))
         if not self.h:
             raise RuntimeError("reference failed to open " + weights_path)
         dims = (C.c_int * 8)()
-        lib().ref_dims(self.h, dims)
+        self.L.ref_dims(self.h, dims)
         (self.d_model, self.n_layers, self.n_heads, self.ffn_dim, self.conv_k, self.d_out, self.causal,
          self.channels) = list(dims)
         self.n_mels = n_mels
 
     def close(self):
         if self.h:
-            lib().ref_close(self.h)
+            self.L.ref_close(self.h)
             self.h = None
 
     def log_mel(self, audio):
         audio = np.ascontiguousarray(audio, np.float32)
         T, v = C.c_int(), C.c_int()
-        p = lib().ref_log_mel(self.h, _fp(audio), audio.size, C.byref(T), C.byref(v))
+        p = self.L.ref_log_mel(self.h, _fp(audio), audio.size, C.byref(T), C.byref(v))
         assert p
         return _take(p, (T.value, self.n_mels)), v.value
 
     def subsampling(self, feats):
         feats = np.ascontiguousarray(feats, np.float32)
         t = C.c_int()
-        p = lib().ref_subsampling(self.h, _fp(feats), feats.shape[0], feats.shape[1], C.byref(t))
+        p = self.L.ref_subsampling(self.h, _fp(feats), feats.shape[0], feats.shape[1], C.byref(t))
         assert p
         return _take(p, (t.value, self.d_model))
 
     def pos_emb(self, T):
         pe = np.empty((2 * T - 1, self.d_model), np.float32)
-        lib().ref_pos_emb(self.h, T, _fp(pe))
+        self.L.ref_pos_emb(self.h, T, _fp(pe))
         return pe
 
     def encoder_layer(self, li, x, pe, left=-1, right=-1):
         x = np.ascontiguousarray(x, np.float32).copy()
-        rc = lib().ref_encoder_layer(self.h, li, _fp(x), x.shape[0], _fp(pe), left, right)
+        rc = self.L.ref_encoder_layer(self.h, li, _fp(x), x.shape[0], _fp(pe), left, right)
         assert rc == 0
         return x
 
     def encoder_post(self, x):
         x = np.ascontiguousarray(x, np.float32)
         out = np.empty((x.shape[0], self.d_out), np.float32)
-        lib().ref_encoder_post(self.h, _fp(x), x.shape[0], _fp(out))
+        self.L.ref_encoder_post(self.h, _fp(x), x.shape[0], _fp(out))
         return out
 
     def encoder_forward(self, feats, left=-1, right=-1, raw=False, prompt_id=0):
         feats = np.ascontiguousarray(feats, np.float32)
         t = C.c_int()
         if prompt_id and not raw:
-            p = lib().ref_encoder_forward_p(self.h, _fp(feats), feats.shape[0], feats.shape[1], prompt_id, left, right,
+            p = self.L.ref_encoder_forward_p(self.h, _fp(feats), feats.shape[0], feats.shape[1], prompt_id, left, right,
                                             C.byref(t))
         else:
-            p = lib().ref_encoder_forward(self.h, _fp(feats), feats.shape[0], feats.shape[1], left, right, int(raw),
+            p = self.L.ref_encoder_forward(self.h, _fp(feats), feats.shape[0], feats.shape[1], left, right, int(raw),
                                           C.byref(t))
         assert p
         return _take(p, (t.value, self.d_model if raw else self.d_out))
@@ -180,9 +202,9 @@ class RefModel:
         touts = (C.c_int * B)()
         if prompt_ids is not None:
             pid = (C.c_int * B)(*prompt_ids)
-            rc = lib().ref_encoder_forward_batch_p(self.h, ptrs, tm, B, fl[0].shape[1], pid, left, right, outs, touts)
+            rc = self.L.ref_encoder_forward_batch_p(self.h, ptrs, tm, B, fl[0].shape[1], pid, left, right, outs, touts)
         else:
-            rc = lib().ref_encoder_forward_batch(self.h, ptrs, tm, B, fl[0].shape[1], left, right, outs, touts)
+            rc = self.L.ref_encoder_forward_batch(self.h, ptrs, tm, B, fl[0].shape[1], left, right, outs, touts)
         assert rc == 0
         return [_take(outs[b], (touts[b], self.d_out)) for b in range(B)]
 
@@ -195,13 +217,13 @@ class RefModel:
         return toks[:n].tolist(), frames[:n].tolist()
 
     def ctc_decode(self, enc):
-        return self._decode(lib().ref_ctc_decode, enc, enc.shape[0])
+        return self._decode(self.L.ref_ctc_decode, enc, enc.shape[0])
 
     def greedy_decode(self, enc, max_symbols=10):
-        return self._decode(lib().ref_greedy_decode, enc, enc.shape[0] * max_symbols)
+        return self._decode(self.L.ref_greedy_decode, enc, enc.shape[0] * max_symbols)
 
     def aed_open(self, n_layers, n_heads, max_seq, max_gen_delta, quant=0):
-        if lib().ref_aed_open(self.h, n_layers, n_heads, max_seq, max_gen_delta, quant) != 0:
+        if self.L.ref_aed_open(self.h, n_layers, n_heads, max_seq, max_gen_delta, quant) != 0:
             raise RuntimeError("reference: AED weights missing or incomplete")
 
     def aed_decode(self, enc, prompt, eos, cap):
@@ -209,7 +231,7 @@ class RefModel:
         enc = np.ascontiguousarray(enc, np.float32)
         pr = np.ascontiguousarray(prompt, np.int32)
         out = np.zeros(max(cap, 1), np.int32)
-        n = lib().ref_aed_decode(self.h, _fp(enc), enc.shape[0], pr.ctypes.data_as(C.POINTER(C.c_int)), pr.size, eos,
+        n = self.L.ref_aed_decode(self.h, _fp(enc), enc.shape[0], pr.ctypes.data_as(C.POINTER(C.c_int)), pr.size, eos,
                                  out.ctypes.data_as(C.POINTER(C.c_int)), cap)
         assert n >= 0
         return out[:n].copy()
@@ -217,18 +239,18 @@ class RefModel:
     def stream_encode(self, mel, left, right, prompt_id=0):
         """Feed valid mel frames through the cache-aware streaming encoder in the
         exact chunk sizes it asks for; returns the concatenated [T, d_out]."""
-        es = lib().ref_stream_open(self.h, left, right, self.n_mels)
+        es = self.L.ref_stream_open(self.h, left, right, self.n_mels)
         assert es
         outs, pos, T = [], 0, mel.shape[0]
         buf = np.empty((right + 3, self.d_out), np.float32)
         while pos < T:
-            need = lib().ref_stream_need(es)
+            need = self.L.ref_stream_need(es)
             chunk = np.ascontiguousarray(mel[pos:pos + need], np.float32)
             last = int(pos + need >= T)
-            q = lib().ref_stream_step_p(es, _fp(chunk), chunk.shape[0], mel.shape[1], prompt_id, last, _fp(buf))
+            q = self.L.ref_stream_step_p(es, _fp(chunk), chunk.shape[0], mel.shape[1], prompt_id, last, _fp(buf))
             if q <= 0:
                 break
             outs.append(buf[:q].copy())
             pos += need
-        lib().ref_stream_close(es)
+        self.L.ref_stream_close(es)
         return np.concatenate(outs, 0) if outs else np.zeros((0, self.d_out), np.float32)

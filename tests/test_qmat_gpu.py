@@ -248,8 +248,12 @@ def test_values_outside_the_fp16_operand_range_are_reported(gpu_pkg):
     m.close()
     wbad = w.copy()
     wbad[0, 0] = 7.0e4
+    mb = gpu_pkg.QMat(gpu_pkg.F32, wbad, n, k)              # the handle exists (stored values, small-T products) ...
+    want4 = x[:4].astype(np.float64) @ wbad.astype(np.float64).T
+    assert np.abs(mb.mul(x[:4]) - want4).max() <= 1e-5 * np.abs(want4).max()
     with pytest.raises(gpu_pkg.BackendError, match="65504"):
-        gpu_pkg.QMat(gpu_pkg.F32, wbad, n, k)
+        mb.mul(x)                                           # ... but the many-row tensor-core product refuses
+    mb.close()
     # the reference's hook under its own name returns -1 (the caller's cue to fall back)
     wk = np.ascontiguousarray(w)
     with pytest.raises(gpu_pkg.BackendError):
