@@ -167,6 +167,17 @@ int mynah_b200_model_set_mel(mynah_b200_model *m, const float *mel_fb, const flo
  * (src/encoder.c:56-183, src/subsampling.c:14-58, src/decoder.c:14-62, src/decoder_ctc.c:11-22),
  * uploads and decodes them; replaces the lazy per-pointer upload of src/cuda_gemm.cu:96-130 */
 int mynah_b200_model_finalize(mynah_b200_model *m);
+/* replaces mynah_asr_st_open + the loaders of mynah_asr_load_quant in one step (src/weights.c:60-117,
+ * src/mynah_asr.c:167-350) for the device path: weights_path is a safetensors or GGUF file with the HF-verbatim
+ * tensor names, mel_path the mel_filters.safetensors beside it (NULL: no front end). The file is mapped
+ * read-only and every tensor goes from the mapping through pinned staging buffers into device memory; GGUF
+ * block tensors (Q4_0, Q8_0, Q4_K, Q6_K) stay blocks and are re-tiled and decoded by kernels — the reference
+ * decodes them to f32 on the host at load. quant as in mynah_asr_load_quant: 1 / 2 take the pre-quantised
+ * "<name>.q8" / "<name>.q4" + "<name>.scales" tensors of a reference int8 / int4 checkpoint where present.
+ * NULL on error. mynah_b200_model_load_stats: wall seconds of the load, host bytes copied, device bytes held. */
+mynah_b200_model *mynah_b200_model_load(const char *weights_path, const char *mel_path, const mynah_b200_config *cfg,
+                                        int quant);
+void mynah_b200_model_load_stats(const mynah_b200_model *m, double *seconds, double *host_bytes, double *device_bytes);
 /* upper bound of execution contexts (concurrent calls) of a model; contexts are created on demand, each
  * with its own workspace (sized by the largest call it has served). No counterpart in the reference, whose
  * per-thread state is thread-local (src/cuda_gemm.cu:50-60). */

@@ -150,6 +150,9 @@ def lib():
     L.mynah_b200_model_finalize.argtypes = [vp]
     L.mynah_b200_model_free.argtypes = [vp]
     L.mynah_b200_model_set_strict.argtypes = [vp, ci]
+    L.mynah_b200_model_load.restype = vp
+    L.mynah_b200_model_load.argtypes = [C.c_char_p, C.c_char_p, C.POINTER(Config), ci]
+    L.mynah_b200_model_load_stats.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_double)]
     L.mynah_b200_model_set_max_contexts.argtypes = [vp, ci]
     L.mynah_b200_model_dims.argtypes = [vp, c_ip]
     L.mynah_b200_model_stream.restype = vp
@@ -319,17 +322,48 @@ class Model:
     """Device-resident encoder + decoders built from named tensors
     (the weight side of mynah_asr_load_quant, src/mynah_asr.c:167-350)."""
 
-    def __init__(self, tensors, *, n_mels, mel_fb=None, window=None, causal=-1, xscaling=False, normalize=True,
-                 left=-1, right=-1, blank=0, max_symbols=10, durations=(), strict=True, attn_impl=0, aed_heads=8, a8=False):
-        L = lib()
+    @staticmethod
+    def _config(n_mels, causal=-1, xscaling=False, normalize=True, left=-1, right=-1, blank=0, max_symbols=10,
+                durations=(), strict=True, attn_impl=0, aed_heads=8, a8=False):
         cfg = Config()
-        L.mynah_b200_config_default(C.byref(cfg))
+        lib().mynah_b200_config_default(C.byref(cfg))
         cfg.n_mels, cfg.causal, cfg.xscaling = n_mels, causal, int(xscaling)
         cfg.normalize_per_feature, cfg.left_ctx, cfg.right_ctx = int(normalize), left, right
         cfg.blank_id, cfg.max_symbols, cfg.n_durations = blank, max_symbols, len(durations)
         for i, d in enumerate(durations):
             cfg.durations[i] = d
         cfg.strict, cfg.attn_impl, cfg.aed_heads, cfg.a8 = int(strict), attn_impl, aed_heads, int(a8)
+        return cfg
+
+    @classmethod
+    def load(cls, weights_path, mel_path=None, *, quant=0, n_mels, **kw):
+        """The model straight from a safetensors or GGUF file (mynah_b200_model_load): the file is mapped and its
+        tensors go to the device without a host-side decode. quant as in the reference's mynah_asr_load_quant."""
+        self = cls.__new__(cls)
+        self.cfg = cls._config(n_mels, **kw)
+        self.h = lib().mynah_b200_model_load(weights_path.encode(), mel_path.encode() if mel_path else None,
+                                             C.byref(self.cfg), quant)
+        if not self.h:
+            raise BackendError("model_load: " + _err())
+        self._dims(n_mels, kw.get("max_symbols", 10))
+        return self
+
+    def load_stats(self):
+        s, hb, db = C.c_double(), C.c_double(), C.c_double()
+        lib().mynah_b200_model_load_stats(self.h, C.byref(s), C.byref(hb), C.byref(db))
+        return {"seconds": s.value, "host_bytes": hb.value, "device_slab_bytes": db.value}
+
+    def _dims(self, n_mels, max_symbols):
+        dims = (C.c_int * 8)()
+        lib().mynah_b200_model_dims(self.h, dims)
+        (self.d_model, self.n_layers, self.n_heads, self.ffn_dim, self.conv_k, self.d_out, self.causal,
+         self.channels) = list(dims)
+        self.n_mels = n_mels
+        self.max_symbols = max_symbols
+
+    def __init__(self, tensors, *, n_mels, mel_fb=None, window=None, max_symbols=10, **kw):
+        L = lib()
+        cfg = self._config(n_mels, max_symbols=max_symbols, **kw)
         self.cfg = cfg
         self.h = L.mynah_b200_model_new(C.byref(cfg))
         if not self.h:
@@ -346,12 +380,7 @@ class Model:
             fb = np.ascontiguousarray(mel_fb, np.float32); win = np.ascontiguousarray(window, np.float32)
             _check(L.mynah_b200_model_set_mel(self.h, _fp(fb), _fp(win)), "set_mel")
         _check(L.mynah_b200_model_finalize(self.h), "finalize")
-        dims = (C.c_int * 8)()
-        L.mynah_b200_model_dims(self.h, dims)
-        (self.d_model, self.n_layers, self.n_heads, self.ffn_dim, self.conv_k, self.d_out, self.causal,
-         self.channels) = list(dims)
-        self.n_mels = n_mels
-        self.max_symbols = max_symbols
+        self._dims(n_mels, max_symbols)
 
     def close(self):
         if getattr(self, "h", None):

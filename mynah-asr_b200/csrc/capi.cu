@@ -4,6 +4,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <chrono>
 #include <condition_variable>
 #include <memory>
 
@@ -71,6 +72,7 @@ private:
     static Model *clone_context(const Model &src) {
         Model *c = new Model(src);                   // weights: the same device pointers
         c->owned.clear();                            // ... which only context 0 owns
+        c->slabs.clear(); c->use_slabs = false;
         c->prof_spans.clear(); c->prof_used = 0; c->prof_on = false;
         c->ws = Arena();
         c->stream = nullptr; c->status = nullptr;
@@ -114,6 +116,7 @@ struct mynah_b200_stream_group {
 };
 
 namespace mb {
+void set_load_seconds(mynah_b200_model *h, double seconds) { if (h) h->m.load_seconds = seconds; }
 QmatView qmat_view(const void *handle) {
     const mynah_b200_qmat *q = static_cast<const mynah_b200_qmat *>(handle);
     return QmatView{&q->w, q->stream};
@@ -183,6 +186,7 @@ mynah_b200_model *mynah_b200_model_new(const mynah_b200_config *cfg) {
     }
     h->m.status = (int *)h->m.dev_alloc(sizeof(int));
     if (!h->m.status) { delete h; return nullptr; }
+    h->m.use_slabs = true;
     cudaMemset(h->m.status, 0, sizeof(int));
     cudaDeviceSynchronize();
     return h;
@@ -288,6 +292,7 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
     if (!h) { set_error("finalize: null model"); return -1; }
     Model &m = h->m;
     if (m.finalized) return 0;
+    const auto t_load0 = std::chrono::steady_clock::now();
     int err = 0;
     const std::string ss = "encoder.subsampling.";
     std::string cin, dwn[2], pwn[2];
@@ -504,6 +509,8 @@ int mynah_b200_model_finalize(mynah_b200_model *h) {
     m.host.clear();
     MB_CUDA(cudaDeviceSynchronize());
     if (m.check_status("model_finalize (a weight does not fit the fp16 operand planes)")) return -1;
+    m.release_load_buffers();
+    m.load_seconds += std::chrono::duration<double>(std::chrono::steady_clock::now() - t_load0).count();
     m.finalized = true;
     return 0;
 }
@@ -531,6 +538,15 @@ void mynah_b200_model_dims(const mynah_b200_model *h, int *dims) {
 }
 
 void *mynah_b200_model_stream(mynah_b200_model *h) { return h ? (void *)h->m.stream : nullptr; }
+
+void mynah_b200_model_load_stats(const mynah_b200_model *h, double *seconds, double *host_bytes, double *device_bytes) {
+    if (!h) return;
+    double dev = 0.0;
+    for (const auto &sl : h->m.slabs) dev += (double)sl.off;
+    if (seconds) *seconds = h->m.load_seconds;
+    if (host_bytes) *host_bytes = (double)h->m.load_bytes;
+    if (device_bytes) *device_bytes = dev;
+}
 
 }  // extern "C"
 

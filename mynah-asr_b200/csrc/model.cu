@@ -35,26 +35,92 @@ void *Arena::take(size_t bytes) {
 void Arena::release() { if (base) cudaFree(base); base = nullptr; cap = off = 0; }
 
 // -------------------------------------------------------------------- model
+static constexpr size_t SLAB_BYTES = 256u << 20;
+static constexpr size_t STAGE_BYTES = 32u << 20;
+
 Model::~Model() {
+    release_load_buffers();
     for (void *p : owned) cudaFree(p);
     for (auto &s : prof_spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     ws.release();
     if (stream) cudaStreamDestroy(stream);
 }
+void Model::release_load_buffers() {
+    for (int i = 0; i < 2; i++) {
+        if (stage_ev[i]) { cudaEventSynchronize(stage_ev[i]); cudaEventDestroy(stage_ev[i]); stage_ev[i] = nullptr; }
+        if (stage[i]) { cudaFreeHost(stage[i]); stage[i] = nullptr; }
+    }
+    if (load_tmp) { cudaStreamSynchronize(stream); cudaFree(load_tmp); load_tmp = nullptr; load_tmp_cap = 0; }
+}
 void *Model::dev_alloc(size_t bytes) {
+    bytes = align_up(bytes ? bytes : 16, 256);
+    if (use_slabs && bytes <= SLAB_BYTES / 4) {
+        if (slabs.empty() || slabs.back().off + bytes > slabs.back().cap) {
+            void *p = nullptr;
+            if (cudaMalloc(&p, SLAB_BYTES) != cudaSuccess) { set_error("cudaMalloc(%zu) failed", SLAB_BYTES); cudaGetLastError(); return nullptr; }
+            owned.push_back(p);
+            slabs.push_back(Slab{(uint8_t *)p, SLAB_BYTES, 0});
+        }
+        Slab &sl = slabs.back();
+        void *p = sl.base + sl.off;
+        sl.off += bytes;
+        return p;
+    }
     void *p = nullptr;
-    if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess) { set_error("cudaMalloc(%zu) failed", bytes); cudaGetLastError(); return nullptr; }
+    if (cudaMalloc(&p, bytes) != cudaSuccess) { set_error("cudaMalloc(%zu) failed", bytes); cudaGetLastError(); return nullptr; }
     owned.push_back(p);
     return p;
+}
+// Host bytes -> device through the pinned staging pair, asynchronously on the model's stream. The source is
+// consumed before this returns (it may be a temporary); kernels launched later on the stream see the data.
+int Model::upload_bytes(void *dst, const void *src, size_t n) {
+    if (!use_slabs) {            // one matrix: a plain copy, waited for because src may be a temporary
+        MB_CUDA(cudaMemcpyAsync(dst, src, n, cudaMemcpyHostToDevice, stream));
+        MB_CUDA(cudaStreamSynchronize(stream));
+        load_bytes += n;
+        return 0;
+    }
+    for (int i = 0; i < 2; i++) {
+        if (!stage[i]) {
+            MB_CUDA(cudaMallocHost((void **)&stage[i], STAGE_BYTES));
+            MB_CUDA(cudaEventCreateWithFlags(&stage_ev[i], cudaEventDisableTiming));
+            MB_CUDA(cudaEventRecord(stage_ev[i], stream));
+        }
+    }
+    for (size_t off = 0; off < n;) {
+        const size_t piece = n - off < STAGE_BYTES ? n - off : STAGE_BYTES;
+        const int b = stage_next;
+        stage_next ^= 1;
+        MB_CUDA(cudaEventSynchronize(stage_ev[b]));                 // the previous DMA out of this buffer has finished
+        memcpy(stage[b], (const uint8_t *)src + off, piece);
+        MB_CUDA(cudaMemcpyAsync((uint8_t *)dst + off, stage[b], piece, cudaMemcpyHostToDevice, stream));
+        MB_CUDA(cudaEventRecord(stage_ev[b], stream));
+        off += piece;
+    }
+    load_bytes += n;
+    return 0;
+}
+float *Model::decode_scratch(size_t nfloats) {
+    if (nfloats > load_tmp_cap) {
+        if (load_tmp) { cudaStreamSynchronize(stream); cudaFree(load_tmp); load_tmp = nullptr; load_tmp_cap = 0; }
+        const size_t want = nfloats > (16u << 20) ? nfloats : (16u << 20);
+        if (cudaMalloc((void **)&load_tmp, want * sizeof(float)) != cudaSuccess) { set_error("cudaMalloc(%zu) failed", want * sizeof(float)); cudaGetLastError(); return nullptr; }
+        load_tmp_cap = want;
+    }
+    return load_tmp;
 }
 float *Model::upload_f32(const float *src, size_t n) {
     float *d = (float *)dev_alloc(n * sizeof(float));
     if (!d) return nullptr;
-    // on the model's stream: it does not synchronise with the legacy default stream, so every
-    // upload is ordered on the stream the kernels that consume it run on
-    if (cudaMemcpyAsync(d, src, n * sizeof(float), cudaMemcpyHostToDevice, stream) != cudaSuccess ||
-        cudaStreamSynchronize(stream) != cudaSuccess) { set_error("H2D copy failed"); return nullptr; }
+    if (upload_bytes(d, src, n * sizeof(float))) return nullptr;
     return d;
+}
+
+__global__ void permute_cols_kernel(const float *__restrict__ in, float *__restrict__ out, const int *__restrict__ perm, int n, int k) {
+    const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (i >= (size_t)n * k) return;
+    const int r = (int)(i / k), c = (int)(i % k);
+    out[i] = in[(size_t)r * k + perm[c]];
 }
 
 int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *scales, int n, int k, bool want_planes,
@@ -66,9 +132,8 @@ int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *sca
     if (!w.raw_bytes) { set_error("unknown weight format %d", fmt); return -1; }
     w.raw = (uint8_t *)dev_alloc(w.raw_bytes + 64);          // slack for aligned over-reads
     if (!w.raw) return -1;
-    MB_CUDA(cudaMemcpyAsync(w.raw, data, w.raw_bytes, cudaMemcpyHostToDevice, stream));
+    if (upload_bytes(w.raw, data, w.raw_bytes)) return -1;
     MB_CUDA(cudaMemsetAsync(w.raw + w.raw_bytes, 0, 64, stream));
-    MB_CUDA(cudaStreamSynchronize(stream));
     if (fmt == FMT_MYNAH_Q8 || fmt == FMT_MYNAH_Q4) {
         if (!scales) { set_error("native quantised weight without scales"); return -1; }
         const size_t ns = fmt == FMT_MYNAH_Q8 ? (size_t)n : (size_t)n * (k / 32);
@@ -82,7 +147,6 @@ int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *sca
         if (!w.mma_q || !w.mma_d) return -1;
         if (qgemv_mma_retile(w, w.mma_q, w.mma_d, stream)) return -1;
         note_launch();
-        MB_CUDA(cudaStreamSynchronize(stream));
     }
     if (((fmt == FMT_GGML_Q4_0 || fmt == FMT_GGML_Q8_0) && k % 128 == 0) || (fmt == FMT_GGML_Q4_K && k % 256 == 0)) {
         w.tc_q = (uint8_t *)dev_alloc(qstream_tc_bytes(fmt, n, k));
@@ -93,32 +157,37 @@ int Model::upload_weight(QWeight &w, int fmt, const void *data, const float *sca
         }
         if (qstream_tc_retile(w, w.tc_q, stream)) return -1;
         note_launch();
-        MB_CUDA(cudaStreamSynchronize(stream));
     }
     if (!want_planes && !want_f32) return 0;
-    float *tmp = nullptr;
-    MB_CUDA(cudaMalloc(&tmp, (size_t)n * k * sizeof(float)));
+    // decode once on the device: into the reused scratch, or into a buffer of its own when the f32 copy is kept
+    float *tmp = want_f32 ? (float *)dev_alloc((size_t)n * k * sizeof(float)) : decode_scratch((size_t)n * k);
+    if (!tmp) return -1;
     int rc = dequant_to_f32(fmt, w.raw, w.scales, tmp, n, k, stream);
     note_launch();
+    float *permuted = nullptr;
     if (rc == 0 && col_perm) {
-        // column permutation on the host (only the subsampling linear, once at load)
-        std::vector<float> a((size_t)n * k), b((size_t)n * k);
-        MB_CUDA(cudaMemcpyAsync(a.data(), tmp, a.size() * 4, cudaMemcpyDeviceToHost, stream));
-        MB_CUDA(cudaStreamSynchronize(stream));
-        for (int r = 0; r < n; r++)
-            for (int c = 0; c < k; c++) b[(size_t)r * k + c] = a[(size_t)r * k + col_perm[c]];
-        MB_CUDA(cudaMemcpyAsync(tmp, b.data(), b.size() * 4, cudaMemcpyHostToDevice, stream));
-        MB_CUDA(cudaStreamSynchronize(stream));
+        // column permutation (only the subsampling linear, once at load)
+        int *perm_dev = nullptr;
+        if (cudaMalloc((void **)&perm_dev, (size_t)k * sizeof(int)) != cudaSuccess || cudaMalloc((void **)&permuted, (size_t)n * k * sizeof(float)) != cudaSuccess) {
+            cudaGetLastError(); cudaFree(perm_dev); set_error("cudaMalloc failed"); return -1;
+        }
+        rc = upload_bytes(perm_dev, col_perm, (size_t)k * sizeof(int));
+        if (rc == 0) {
+            permute_cols_kernel<<<(unsigned)(((size_t)n * k + 255) / 256), 256, 0, stream>>>(tmp, permuted, perm_dev, n, k);
+            note_launch();
+            if (want_f32) cudaMemcpyAsync(tmp, permuted, (size_t)n * k * sizeof(float), cudaMemcpyDeviceToDevice, stream);
+        }
+        cudaStreamSynchronize(stream);
+        cudaFree(perm_dev);
     }
     if (rc == 0 && want_planes) {
         w.hi = (__half *)dev_alloc((size_t)n * k * 2);
         w.lo = (__half *)dev_alloc((size_t)n * k * 2);
         if (!w.hi || !w.lo) rc = -1;
-        else { rc = split_to_h16(tmp, w.hi, w.lo, (size_t)n * k, stream, status); note_launch(); }
+        else { rc = split_to_h16(permuted ? permuted : tmp, w.hi, w.lo, (size_t)n * k, stream, status); note_launch(); }
     }
-    cudaStreamSynchronize(stream);
-    if (rc == 0 && want_f32) { w.f32 = tmp; owned.push_back(tmp); }
-    else cudaFree(tmp);
+    if (permuted) { cudaStreamSynchronize(stream); cudaFree(permuted); }
+    if (rc == 0 && want_f32) w.f32 = tmp;
     return rc;
 }
 

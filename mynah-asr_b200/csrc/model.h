@@ -141,6 +141,24 @@ struct Model {
     double *mel_win = nullptr, *mel_tw = nullptr;
     bool has_mel = false;
 
+    // ---- load path: device memory for the weights comes from a few large slabs (one cudaMalloc per 256 MB instead
+    // of one per tensor), host bytes reach the device through two pinned staging buffers (the copy of piece i + 1
+    // into its buffer overlaps the DMA of piece i; nothing waits for the stream), and the f32 scratch of the block
+    // decode is one buffer reused by every tensor
+    struct Slab { uint8_t *base; size_t cap, off; };
+    std::vector<Slab> slabs;
+    bool use_slabs = false;                          // a whole model loads through slabs and staging; a single qmat handle does not
+    uint8_t *stage[2] = {nullptr, nullptr};
+    cudaEvent_t stage_ev[2] = {nullptr, nullptr};
+    int stage_next = 0;
+    float *load_tmp = nullptr;
+    size_t load_tmp_cap = 0;
+    double load_seconds = 0.0;                       // wall time of add_tensor .. finalize (or of model_load)
+    size_t load_bytes = 0;                           // host bytes copied to the device while loading
+    int upload_bytes(void *dst, const void *src, size_t n);
+    float *decode_scratch(size_t nfloats);
+    void release_load_buffers();
+
     ~Model();
     void *dev_alloc(size_t bytes);
     float *upload_f32(const float *src, size_t n);
@@ -215,5 +233,6 @@ struct GreedyDev {
 };
 
 int greedy_launch(const GreedyDev &p, cudaStream_t st);
+void set_load_seconds(mynah_b200_model *h, double seconds);     // capi.cu: the loader reports its whole wall time
 
 }  // namespace mb

@@ -405,6 +405,49 @@ def synth_audio(seconds: float, seed: int = 0, sample_rate: int = 16000) -> np.n
     return (x.astype(np.float32) / np.float32(32768.0)).astype(np.float32)
 
 
+def write_gguf(path: str, tensors: dict, alignment: int = 32) -> None:
+    """name -> Tensor (ggml types only) as a GGUF v3 file: magic, version, tensor and key/value counts, the
+    key/value pairs (general.architecture, general.alignment), the tensor infos (name, dims with the fastest
+    dimension first, ggml type, offset into the data section), then the aligned data."""
+    def s(x: str) -> bytes:
+        b = x.encode()
+        return struct.pack("<Q", len(b)) + b
+    kv = [s("general.architecture") + struct.pack("<I", 8) + s("mynah-asr"),
+          s("general.alignment") + struct.pack("<II", 4, alignment)]
+    infos, blobs, off = [], [], 0
+    for name, t in tensors.items():
+        if t.ggml_type < 0:
+            raise ValueError(f"{name}: not a ggml type")
+        infos.append(s(name) + struct.pack("<I", len(t.shape)) + b"".join(struct.pack("<Q", d) for d in reversed(t.shape)) +
+                     struct.pack("<IQ", t.ggml_type, off))
+        blobs.append((off, t.raw))
+        off += (t.raw.size + alignment - 1) // alignment * alignment
+    head = b"GGUF" + struct.pack("<IQQ", 3, len(infos), len(kv)) + b"".join(kv) + b"".join(infos)
+    pad = (-len(head)) % alignment
+    with open(path, "wb") as f:
+        f.write(head + b"\0" * pad)
+        for o, raw in blobs:
+            f.write(raw.tobytes())
+            f.write(b"\0" * ((-raw.size) % alignment))
+
+
+def write_model_file(path: str, tensors: dict) -> None:
+    """A tensor dict as the reference would find it on disk: .gguf (all ggml types) or .safetensors (f32 tensors as
+    they are, reference-native int8 as `<name>.q8` + `<name>.scales`)."""
+    if path.endswith(".gguf"):
+        write_gguf(path, tensors)
+        return
+    files = {}
+    for name, t in tensors.items():
+        if t.ggml_type == NATIVE_Q8:
+            files[name + ".q8"] = t.raw.view(np.int8).reshape(t.shape)
+        elif t.ggml_type == GGML_F32:
+            files[name] = t.raw.view(np.float32).reshape(t.shape)
+        else:
+            raise ValueError(f"{name}: block-quantised tensors need a .gguf file")
+    write_safetensors(path, files)
+
+
 def write_safetensors(path: str, tensors: dict) -> None:
     """name -> float32 (or int8) ndarray, in the safetensors container the reference's
     loader opens (8-byte little-endian header length, JSON header, raw data)."""
