@@ -227,6 +227,17 @@ int mynah_b200_aed_decode_batch(mynah_b200_model *m, const float *const *encs, c
                                 const int *const *prompts, const int *n_prompts, int eos, const int *caps, int **tokens,
                                 int *n_tokens);
 
+/* ---- CTC forced alignment (word timestamps of the AED engine) ----------------------- */
+/* replaces mynah_asr_align_ctc / mynah_asr_align_min_frames (src/align.h:27-32): Viterbi alignment of `tokens`
+ * (none of them `blank`) over scores [T, V] (raw logits do); t0[j] / t1[j] receive the first and last frame of
+ * token j's run. Host pointers, synchronous; 0, or -1 for bad arguments or when no path exists (T shorter than
+ * the tokens plus the blanks repeated labels need). Same result as the reference on the same scores, ties included. */
+int mynah_b200_align_ctc(const float *scores, int T, int V, const int *tokens, int n_tokens, int blank, int *t0, int *t1);
+int mynah_b200_align_min_frames(const int *tokens, int n_tokens);
+/* the aligner step of align_words_ctc (src/mynah_asr.c:1102-1134) with the scores never leaving the device: the
+ * model's CTC head over enc_out [T, d_model] (raw encoder output, blank = vocab - 1), then the alignment */
+int mynah_b200_ctc_align(mynah_b200_model *m, const float *enc_out, int T, const int *tokens, int n_tokens, int *t0, int *t1);
+
 /* ---- cache-aware streaming (Nemotron-style causal encoders) ------------------------ */
 /* replaces mynah_asr_enc_stream_init / _need / _step / _free (src/encoder.h:110-120) for n_streams
  * streams that advance in lock step: every step takes one chunk of mel frames from each stream and

@@ -178,6 +178,9 @@ def lib():
     L.mynah_b200_batch_set_prompts.argtypes = [vp, c_ip]
     L.mynah_b200_batch_set_prompts.restype = None
     L.mynah_b200_qmat_sync.argtypes = [vp]
+    L.mynah_b200_align_ctc.argtypes = [c_fp, ci, ci, c_ip, ci, ci, c_ip, c_ip]
+    L.mynah_b200_align_min_frames.argtypes = [c_ip, ci]
+    L.mynah_b200_ctc_align.argtypes = [vp, c_fp, ci, c_ip, ci, c_ip, c_ip]
     L.mynah_b200_batch_upload.restype = vp
     L.mynah_b200_batch_upload.argtypes = [vp, C.POINTER(c_fp), C.POINTER(C.c_size_t), ci]
     L.mynah_b200_batch_run.argtypes = [vp, vp, ci]
@@ -262,6 +265,20 @@ def weights_evict():
 
 def weights_resident() -> int:
     return int(lib().mynah_b200_weights_resident())
+
+
+def align_ctc(scores, tokens, blank):
+    """mynah_asr_align_ctc (src/align.c) on the device: (rc, t0, t1) for scores [T, V] and a label sequence."""
+    scores = np.ascontiguousarray(scores, np.float32)
+    n = len(tokens)
+    tk = (C.c_int * max(n, 1))(*tokens)
+    t0, t1 = (C.c_int * max(n, 1))(), (C.c_int * max(n, 1))()
+    rc = lib().mynah_b200_align_ctc(_fp(scores), scores.shape[0], scores.shape[1], tk, n, blank, t0, t1)
+    return rc, list(t0[:n]), list(t1[:n])
+
+
+def align_min_frames(tokens):
+    return lib().mynah_b200_align_min_frames((C.c_int * max(len(tokens), 1))(*tokens), len(tokens))
 
 
 class QMat:
@@ -469,6 +486,15 @@ class Model:
 
     def ctc_decode(self, enc):
         return self._decode(lib().mynah_b200_ctc_decode, enc, enc.shape[0], "ctc_decode")
+
+    def ctc_align(self, enc_raw, tokens):
+        """first / last frame of every token's run: the model's CTC head over enc_raw, then forced alignment"""
+        enc = np.ascontiguousarray(enc_raw, np.float32)
+        n = len(tokens)
+        tk = (C.c_int * n)(*tokens)
+        t0, t1 = (C.c_int * n)(), (C.c_int * n)()
+        _check(lib().mynah_b200_ctc_align(self.h, _fp(enc), enc.shape[0], tk, n, t0, t1), "ctc_align")
+        return list(t0), list(t1)
 
     def greedy_decode(self, enc):
         return self._decode(lib().mynah_b200_greedy_decode, enc, enc.shape[0] * self.max_symbols, "greedy_decode")

@@ -803,6 +803,44 @@ void mynah_b200_batch_set_aed(mynah_b200_batch *bt, const int *prompt, int n_pro
     bt->aed_eos = eos; bt->aed_delta = max_gen_delta;
 }
 
+// ------------------------------------------------------------ CTC forced alignment
+int mynah_b200_align_min_frames(const int *tokens, int n_tokens) { return tokens ? align_min_frames(tokens, n_tokens) : 0; }
+
+int mynah_b200_align_ctc(const float *scores, int T, int V, const int *tokens, int n_tokens, int blank, int *t0, int *t1) {
+    if (!scores || T <= 0 || V <= 0) { set_error("align_ctc: bad argument"); return -1; }
+    if (!mynah_b200_available()) { set_error("align_ctc: no sm_100 device"); return -1; }
+    float *d = nullptr;
+    MB_CUDA(cudaMalloc((void **)&d, (size_t)T * V * sizeof(float)));
+    int rc = -1;
+    if (cudaMemcpy(d, scores, (size_t)T * V * sizeof(float), cudaMemcpyHostToDevice) == cudaSuccess)
+        rc = align_ctc_device(d, T, V, tokens, n_tokens, blank, t0, t1, nullptr);
+    else set_error("align_ctc: H2D copy failed");
+    cudaFree(d);
+    return rc;
+}
+
+int mynah_b200_ctc_align(mynah_b200_model *h, const float *enc_out, int T, const int *tokens, int n_tokens, int *t0, int *t1) {
+    if (!h || !h->m.finalized || !enc_out || T <= 0 || !tokens || n_tokens <= 0) { set_error("ctc_align: bad argument"); return -1; }
+    Lease lease(h);
+    Model &m = lease.model();
+    if (!m.has_ctc) { set_error("ctc_align: model has no CTC head"); return -1; }
+    const int V = m.ctc_vocab, d = m.d_model;
+    if (m.ws.reserve((size_t)T * ((size_t)d * 8 + (size_t)V * 4 + 8) + (1 << 20))) return -1;
+    m.ws.reset();
+    float *e = m.ws.get<float>((size_t)T * d), *logits = m.ws.get<float>((size_t)T * V);
+    H16 hp = m.ws.planes((size_t)T * d);
+    if (!e || !logits || !hp.lo) return -1;
+    MB_CUDA(cudaMemcpyAsync(e, enc_out, (size_t)T * d * 4, cudaMemcpyHostToDevice, m.stream));
+    if (split_to_h16(e, hp.hi, hp.lo, (size_t)T * d, m.stream, m.status)) return -1;
+    note_launch();
+    GemmEpilogue ep;
+    memset(&ep, 0, sizeof(ep));
+    ep.mode = OUT_F32; ep.act = ACT_NONE; ep.alpha = 1.f; ep.bias = m.ctc_head.bias; ep.out = logits; ep.ldo = V;
+    if (m.gemm(hp, d, m.ctc_head, ep, T)) return -1;
+    if (m.check_status("ctc_align")) return -1;
+    return align_ctc_device(logits, T, V, tokens, n_tokens, V - 1, t0, t1, m.stream);
+}
+
 // ------------------------------------------------------------ cache-aware streaming
 mynah_b200_stream_group *mynah_b200_stream_open(mynah_b200_model *h, int n_streams, int left_ctx, int right_ctx) {
     if (!h || !h->m.finalized) { set_error("stream_open: bad argument"); return nullptr; }

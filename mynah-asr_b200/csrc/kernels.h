@@ -103,6 +103,10 @@ int qstream_tc(const QWeight &w, const float *x, int ldx, float *out, int ldo, c
 int act_quant_rows(const float *x, int8_t *qx, float *sx, int T, int k, cudaStream_t st);
 int qgemv_a8(const QWeight &w, const float *x, float *out, int T, int32_t *block_dots, float *sx_out, cudaStream_t st);
 
+// ---- align.cu : CTC forced alignment (mynah_asr_align_ctc, src/align.c) with the scores resident
+int align_min_frames(const int *tokens, int n);
+int align_ctc_device(const float *scores_dev, int T, int V, const int *tokens, int n, int blank, int *t0, int *t1, cudaStream_t st);
+
 // ---- launch accounting (model.cu): every kernel launch of the library is counted
 void note_launch(int n = 1);
 long long launch_count(bool reset);

@@ -593,6 +593,60 @@ def aed_decode(A, enc, prompt, eos, cap):
     return np.asarray(out, np.int32)
 
 
+# ------------------------------------------------------------------ CTC forced alignment (src/align.c)
+ALIGN_NEG_BIG, ALIGN_UNREACHABLE = f32(-1.0e30), f32(-1.0e29)
+
+
+def align_min_frames(tokens):
+    """One frame per token plus a blank between identical neighbours (align.c:24-30)."""
+    return len(tokens) + sum(1 for a, b in zip(tokens[1:], tokens[:-1]) if a == b)
+
+
+def align_ctc(scores, tokens, blank):
+    """Viterbi over blank, tok0, blank, tok1, ..., blank (align.c:32-97): moves stay / from s-1 / from s-2 (only into a
+    label that differs from the label two states back), the later candidate wins only when strictly greater, states
+    that can no longer finish or cannot be reached yet are pruned, raw logits as scores. Returns (rc, t0, t1): first
+    and last frame of every token's run, rc -1 when the arguments are bad or no path exists."""
+    scores = np.asarray(scores, f32)
+    T, V = scores.shape
+    n = len(tokens)
+    if T <= 0 or V <= 0 or n <= 0 or blank < 0 or blank >= V or any(t < 0 or t >= V or t == blank for t in tokens):
+        return -1, [], []
+    if T < align_min_frames(tokens):
+        return -1, [], []
+    S = 2 * n + 1
+    ext = np.full(S, blank, np.int64)
+    ext[1::2] = tokens
+    can_skip = np.zeros(S, bool)
+    can_skip[2:] = (ext[2:] != blank) & (ext[2:] != ext[:-2])
+    prv = np.full(S, ALIGN_NEG_BIG, f32)
+    prv[0], prv[1] = scores[0, ext[0]], scores[0, ext[1]]
+    bp = np.zeros((T, S), np.uint8)
+    for t in range(1, T):
+        s_lo, s_hi = max(S - 2 * (T - t), 0), min(2 * t + 1, S - 1)
+        best, frm = prv.copy(), np.zeros(S, np.uint8)
+        m1 = np.zeros(S, bool); m1[1:] = prv[:-1] > best[1:]
+        best[m1] = np.concatenate([[ALIGN_NEG_BIG], prv[:-1]])[m1]; frm[m1] = 1
+        m2 = np.zeros(S, bool); m2[2:] = can_skip[2:] & (prv[:-2] > best[2:])
+        best[m2] = np.concatenate([[ALIGN_NEG_BIG, ALIGN_NEG_BIG], prv[:-2]])[m2]; frm[m2] = 2
+        cur = np.where(best > ALIGN_UNREACHABLE, (best + scores[t, ext]).astype(f32), ALIGN_NEG_BIG).astype(f32)
+        live = np.zeros(S, bool); live[s_lo:s_hi + 1] = True
+        cur[~live] = ALIGN_NEG_BIG; frm[~live] = 0
+        bp[t], prv = frm, cur
+    s = S - 1 if prv[S - 1] >= prv[S - 2] else S - 2
+    if prv[s] <= ALIGN_UNREACHABLE:
+        return -1, [], []
+    t0, t1 = [-1] * n, [-1] * n
+    for t in range(T - 1, -1, -1):
+        if s % 2 == 1:
+            j = s // 2
+            if t1[j] < 0:
+                t1[j] = t
+            t0[j] = t
+        s -= int(bp[t, s])
+    return (0 if all(v >= 0 for v in t0) else -1), t0, t1
+
+
 # ------------------------------------------------------------------ cache-aware streaming
 class EncStream:
     """State of mynah_asr_enc_stream (src/encoder.h:93-108): per-layer K/V caches of up to `left`

@@ -83,6 +83,8 @@ def load(path):
         L.ref_stream_step.argtypes = [C.c_void_p, c_fp, C.c_int, C.c_int, C.c_int, c_fp]
         L.ref_stream_close.argtypes = [C.c_void_p]
         L.ref_qmat_mul_from_f32.argtypes = [c_fp, C.c_int, C.c_int, C.c_int, c_fp, c_fp, C.c_int]
+        L.ref_align_ctc.argtypes = [c_fp, C.c_int, C.c_int, c_ip, C.c_int, C.c_int, c_ip, c_ip]
+        L.ref_align_min_frames.argtypes = [c_ip, C.c_int]
         L.ingot_dequant.argtypes = [C.c_int, C.c_void_p, C.c_size_t, c_fp]
         L.ingot_quantize.argtypes = [C.c_int, c_fp, C.c_size_t, C.c_void_p]
     return L
@@ -114,6 +116,17 @@ def ggml_quantize(ggml_type: int, w: np.ndarray, nbytes: int) -> np.ndarray:
     rc = lib().ingot_quantize(ggml_type, _fp(w), w.size, out.ctypes.data)
     assert rc == 0
     return out
+
+
+def align_ctc(scores, tokens, blank):
+    """mynah_asr_align_ctc (src/align.c): (rc, t0, t1) for scores [T, V] and a label sequence."""
+    scores = np.ascontiguousarray(scores, np.float32)
+    tk = np.ascontiguousarray(tokens, np.int32)
+    t0 = np.full(max(tk.size, 1), -1, np.int32)
+    t1 = np.full(max(tk.size, 1), -1, np.int32)
+    rc = lib().ref_align_ctc(_fp(scores), scores.shape[0], scores.shape[1], tk.ctypes.data_as(c_ip), tk.size, blank,
+                             t0.ctypes.data_as(c_ip), t1.ctypes.data_as(c_ip))
+    return rc, t0[:tk.size].tolist(), t1[:tk.size].tolist()
 
 
 def qmat_mul(w: np.ndarray, qtype: int, x: np.ndarray, library=None) -> np.ndarray:

@@ -14,6 +14,7 @@
  *   src/decoder_ctc.c mynah_asr_ctc_decode
  *   src/decoder_aed.c mynah_asr_aed_{init,decode}
  *   src/qmat.c       mynah_asr_qmat_{init,mul}
+ *   src/align.c      mynah_asr_align_ctc, mynah_asr_align_min_frames
  *
  * Every function below only forwards to the reference; no arithmetic lives
  * here. Weights arrive as a safetensors file with HF-verbatim tensor names,
@@ -22,6 +23,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include "align.h"
 #include "decoder.h"
 #include "decoder_aed.h"
 #include "decoder_ctc.h"
@@ -206,6 +208,15 @@ int ref_stream_step(mynah_asr_enc_stream *es, const float *mel, int n_mel, int n
 }
 void ref_stream_close(mynah_asr_enc_stream *es) {
     if (es) { mynah_asr_enc_stream_free(es); free(es); }
+}
+
+/* ---- CTC forced alignment (src/align.c) ---- */
+int ref_align_ctc(const float *scores, int T, int V, const int *tokens, int n_tokens, int blank,
+                  int *t0, int *t1) {
+    return mynah_asr_align_ctc(scores, T, V, tokens, n_tokens, blank, t0, t1);
+}
+int ref_align_min_frames(const int *tokens, int n_tokens) {
+    return mynah_asr_align_min_frames(tokens, n_tokens);
 }
 
 /* ---- one quantised linear: out[T,n] = x[T,k] W^T with W given as f32 and

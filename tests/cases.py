@@ -62,3 +62,27 @@ def build_a8(synth, name, seed=1):
     cfg = synth.config(name, **A8[name])
     t = synth.make_model(cfg, seed=seed)
     return cfg, synth.to_native_int8(t, lambda ty, raw: raw.view("float32"))
+
+
+def align_cases():
+    """Seeded inputs of the alignment fixtures (the tests regenerate them): random logits with the label path made
+    more or less attractive, repeated labels, the shortest possible T, flat scores (every path ties), an impossible T."""
+    import numpy as np
+    rng = np.random.default_rng(77)
+    out = []
+    for T, V, n, boost in ((40, 9, 6, 3.0), (25, 5, 12, 0.0), (120, 33, 30, 1.0), (9, 5, 3, 10.0), (64, 17, 1, 0.5), (300, 129, 70, 2.0)):
+        toks = rng.integers(0, V - 1, n).tolist()
+        if n > 3:
+            toks[2] = toks[1]                                   # a repeated label: the blank between is mandatory
+        sc = rng.standard_normal((T, V)).astype(np.float32)
+        pos = np.sort(rng.choice(T, n, replace=False))
+        for j, p in enumerate(pos):
+            sc[p, toks[j]] += boost
+        out.append((sc, toks, V - 1))
+    toks = [1, 1, 2, 2, 3]
+    out.append((rng.standard_normal((len(toks) + 2, 6)).astype(np.float32), toks, 5))      # T = the minimum (7)
+    out.append((np.zeros((40, 5), np.float32), [0, 1, 0, 2], 4))                           # flat scores
+    out.append((rng.standard_normal((3, 5)).astype(np.float32), [0, 0, 1], 4))              # impossible: needs 4 frames
+    return out
+
+

@@ -145,6 +145,15 @@ def a8(name):
           "a8 vs f32 rel", float(np.linalg.norm(out["enc_raw"] - out["enc_raw_f32"]) / np.linalg.norm(out["enc_raw_f32"])))
 
 
+def align():
+    out = {}
+    for i, (sc, toks, blank) in enumerate(cases.align_cases()):
+        rc, t0, t1 = R.align_ctc(sc, toks, blank)
+        out[f"rc{i}"], out[f"t0_{i}"], out[f"t1_{i}"] = np.int32(rc), np.array(t0, np.int32), np.array(t1, np.int32)
+        print("align", i, sc.shape, len(toks), "rc", rc)
+    np.savez_compressed(os.path.join(HERE, "ref_align.npz"), **out)
+
+
 def qmat():
     """mynah_asr_qmat_mul on weights quantised by the reference's own load-time
     quantiser, T = 1, 4 (int8-activation dots) and 48 (dequant + sgemm): the cases
@@ -168,6 +177,9 @@ if __name__ == "__main__":
     only = sys.argv[1:]
     if only:                      # regenerate only the named fixtures
         for name in only:
+            if name == "align":
+                align()
+                continue
             (a8 if name in cases.A8 else prompt if name in cases.PROMPT else aed if name in cases.AED else pipeline)(name)
         sys.exit(0)
     for name in cases.TINY:
@@ -176,4 +188,5 @@ if __name__ == "__main__":
         aed(name)
     for name in cases.PROMPT:
         prompt(name)
+    align()
     qmat()
