@@ -73,6 +73,8 @@ private:
         Model *c = new Model(src);                   // weights: the same device pointers
         c->owned.clear();                            // ... which only context 0 owns
         c->slabs.clear(); c->use_slabs = false;
+        for (int i = 0; i < Model::DEC_LANES; i++) { c->lane[i] = nullptr; c->lane_done[i] = nullptr; }
+        c->lane_fork = nullptr;
         c->prof_spans.clear(); c->prof_used = 0; c->prof_on = false;
         c->ws = Arena();
         c->stream = nullptr; c->status = nullptr;
@@ -1392,8 +1394,15 @@ double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iter
     if (cudaMalloc(&x, (size_t)T * w.k * 4) != cudaSuccess || cudaMalloc(&out, (size_t)T * w.n * 4) != cudaSuccess) { set_error("qmat_time: cudaMalloc failed"); return -1.0; }
     cudaMemset(x, 0, (size_t)T * w.k * 4);
     cudaDeviceSynchronize();
-    const bool small = (T <= 16 && w.k <= 8192) || (flags & MYNAH_B200_A8);
-    if (!small) {
+    const bool i8 = (flags & MYNAH_B200_A8) && w.fmt == FMT_MYNAH_Q8 && T > 16 && w.k % 128 == 0;
+    int8_t *qx = nullptr;
+    float *sx = nullptr;
+    if (i8) {          // the integer contraction alone: rows quantised once, outside the timed launches
+        if (cudaMalloc((void **)&qx, (size_t)T * w.k) != cudaSuccess || cudaMalloc((void **)&sx, (size_t)T * 4) != cudaSuccess ||
+            act_quant_rows(x, qx, sx, T, w.k, q->stream)) { cudaFree(x); cudaFree(out); cudaFree(qx); cudaFree(sx); set_error("qmat_time: setup failed"); return -1.0; }
+    }
+    const bool small = !i8 && ((T <= 16 && w.k <= 8192) || (flags & MYNAH_B200_A8));
+    if (!small && !i8) {
         if (!w.hi) { set_error("qmat_time: no operand planes"); cudaFree(x); cudaFree(out); return -1.0; }
         cudaMalloc(&hi, (size_t)T * w.k * 2); cudaMalloc(&lo, (size_t)T * w.k * 2);
         split_to_h16(x, hi, lo, (size_t)T * w.k, q->stream);
@@ -1403,7 +1412,12 @@ double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iter
     int rc = 0;
     for (int it = -2; it < iters && rc == 0; it++) {
         if (it == 0) cudaEventRecord(e0, q->stream);
-        if (small) rc = (flags & MYNAH_B200_A8) ? qgemv_a8(w, x, out, T, nullptr, nullptr, q->stream)
+        if (i8) {
+            GemmEpilogue e;
+            memset(&e, 0, sizeof(e));
+            e.mode = OUT_F32; e.alpha = 1.f; e.out = out; e.ldo = w.n;
+            rc = gemm_i8(qx, w.k, sx, reinterpret_cast<const int8_t *>(w.raw), w.k, w.scales, e, T, w.n, w.k, q->status, q->stream);
+        } else if (small) rc = (flags & MYNAH_B200_A8) ? qgemv_a8(w, x, out, T, nullptr, nullptr, q->stream)
                    : (w.tc_q && T <= 8 && !(flags & (MYNAH_B200_SCALAR | MYNAH_B200_MMA_SYNC))) ? qstream_tc(w, x, w.k, out, w.n, nullptr, T, q->status, q->stream)
                    : (w.mma_q && !(flags & MYNAH_B200_SCALAR)) ? qgemv_mma(w, x, w.k, out, w.n, nullptr, T, q->stream)
                    : qgemv(w, x, w.k, out, w.n, nullptr, T, q->stream);
@@ -1421,7 +1435,7 @@ double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iter
     float ms = 0.f;
     cudaEventElapsedTime(&ms, e0, e1);
     cudaEventDestroy(e0); cudaEventDestroy(e1);
-    cudaFree(x); cudaFree(out); if (hi) cudaFree(hi); if (lo) cudaFree(lo);
+    cudaFree(x); cudaFree(out); if (hi) cudaFree(hi); if (lo) cudaFree(lo); if (qx) cudaFree(qx); if (sx) cudaFree(sx);
     if (rc != 0 || cudaGetLastError() != cudaSuccess) { if (rc == 0) set_error("qmat_time: device error"); return -1.0; }
     return (double)ms / iters;
 }

@@ -535,7 +535,7 @@ greedy_kernel(GreedyDev p) {
     if (blockIdx.x == 0 && threadIdx.x == 0) { p.flags[4] = par; if (p.par_state) *p.par_state = par; }
 }
 
-int greedy_launch(const GreedyDev &p, cudaStream_t st) {
+int greedy_launch(const GreedyDev &p, cudaStream_t st, int want_blocks) {
     int dev = 0, sms = 0, coop = 0;
     MB_CUDA(cudaGetDevice(&dev));
     MB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
@@ -547,7 +547,7 @@ int greedy_launch(const GreedyDev &p, cudaStream_t st) {
     int per_sm = 0;
     MB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, greedy_kernel, 256, smem));
     if (per_sm < 1) { set_error("greedy decode: kernel does not fit an SM"); return -1; }
-    int blocks = sms;
+    int blocks = want_blocks > 0 && want_blocks < sms ? want_blocks : sms;
     if (blocks < p.B) { set_error("greedy decode: batch %d exceeds SM count", p.B); return -1; }
     GreedyDev pc = p;
     void *args[] = {&pc};

@@ -43,7 +43,34 @@ Model::~Model() {
     for (void *p : owned) cudaFree(p);
     for (auto &s : prof_spans) { cudaEventDestroy(s.a); cudaEventDestroy(s.b); }
     ws.release();
+    for (int i = 0; i < DEC_LANES; i++) {
+        if (lane_done[i]) cudaEventDestroy(lane_done[i]);
+        if (lane[i]) cudaStreamDestroy(lane[i]);
+    }
+    if (lane_fork) cudaEventDestroy(lane_fork);
     if (stream) cudaStreamDestroy(stream);
+}
+int Model::lanes_begin(int n_groups) {
+    const int lanes = n_groups < DEC_LANES ? n_groups : DEC_LANES;
+    if (lanes <= 1) return 1;
+    if (!lane_fork) MB_CUDA(cudaEventCreateWithFlags(&lane_fork, cudaEventDisableTiming));
+    MB_CUDA(cudaEventRecord(lane_fork, stream));
+    for (int i = 0; i < lanes; i++) {
+        if (!lane[i]) {
+            MB_CUDA(cudaStreamCreateWithFlags(&lane[i], cudaStreamNonBlocking));
+            MB_CUDA(cudaEventCreateWithFlags(&lane_done[i], cudaEventDisableTiming));
+        }
+        MB_CUDA(cudaStreamWaitEvent(lane[i], lane_fork, 0));
+    }
+    return lanes;
+}
+int Model::lanes_join(int lanes) {
+    if (lanes <= 1) return 0;
+    for (int i = 0; i < lanes; i++) {
+        MB_CUDA(cudaEventRecord(lane_done[i], lane[i]));
+        MB_CUDA(cudaStreamWaitEvent(stream, lane_done[i], 0));
+    }
+    return 0;
 }
 void Model::release_load_buffers() {
     for (int i = 0; i < 2; i++) {
@@ -524,19 +551,36 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
     std::vector<int> offs(Ball);
     for (int b = 0, o = 0; b < Ball; o += lens[b], b++) offs[b] = o;
     const int nw = (vocab + cfg.n_durations + 15) / 16;     // candidate slots: one per 16-row block of the head
+    // lock-step groups of DEC_MAX_B utterances; with several groups they run side by side on the decode lanes
+    struct Group { int g0, B, cap; int *n_out, *tokens, *frames; long long *dbg; };
+    std::vector<Group> groups;
     for (int g0 = 0; g0 < Ball; g0 += DEC_MAX_B) {
         const int B = Ball - g0 < DEC_MAX_B ? Ball - g0 : DEC_MAX_B;
         int max_len = 0;
         for (int b = 0; b < B; b++) if (lens[g0 + b] > max_len) max_len = lens[g0 + b];
-        if (max_len == 0) continue;
-        const int cap = max_len * cfg.max_symbols;
-        const size_t mark = ws.off;
+        if (max_len > 0) groups.push_back(Group{g0, B, max_len * cfg.max_symbols, nullptr, nullptr, nullptr, nullptr});
+    }
+    if (groups.empty()) return 0;
+    const size_t mark = ws.off;
+    int *hm_dev = ws.get<int>(2 * (size_t)Ball);
+    if (!hm_dev) return -1;
+    std::vector<int> hm(2 * (size_t)Ball);
+    for (int b = 0; b < Ball; b++) { hm[b] = offs[b]; hm[Ball + b] = lens[b]; }
+    MB_CUDA(cudaMemcpyAsync(hm_dev, hm.data(), hm.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
+    MB_CUDA(cudaStreamSynchronize(stream));          // hm is a stack-lifetime buffer
+    const int lanes = lanes_begin((int)groups.size());
+    if (lanes < 1) return -1;
+    const int lane_blocks = lanes > 1 ? (device_sm_count() / lanes > DEC_MAX_B ? device_sm_count() / lanes : DEC_MAX_B) : 0;
+    for (size_t gi = 0; gi < groups.size(); gi++) {
+        Group &G = groups[gi];
+        const int B = G.B, cap = G.cap;
+        cudaStream_t ls = lane_stream(lanes, (int)gi);
         const size_t nstate = (size_t)L * B * H;
         float *fz = ws.get<float>(3 * nstate + (size_t)B * H + 2 * (size_t)B * nw + (size_t)DEC_MAX_B * H);
         int *iz = ws.get<int>(8 * (size_t)B + 2 * (size_t)B * nw + 2 * (size_t)B * cap + 16);
         if (!fz || !iz) return -1;
-        MB_CUDA(cudaMemsetAsync(fz, 0, (3 * nstate + (size_t)B * H) * sizeof(float), stream));
-        MB_CUDA(cudaMemsetAsync(iz, 0, (8 * (size_t)B + 16) * sizeof(int), stream));
+        MB_CUDA(cudaMemsetAsync(fz, 0, (3 * nstate + (size_t)B * H) * sizeof(float), ls));
+        MB_CUDA(cudaMemsetAsync(iz, 0, (8 * (size_t)B + 16) * sizeof(int), ls));
         GreedyDev p;
         memset(&p, 0, sizeof(p));
         p.emb = emb; p.head_b = head_b; p.proj_b = proj_b;
@@ -553,36 +597,38 @@ int Model::decode_greedy(const float *enc_dev, const std::vector<int> &lens, std
         int *q = iz;
         p.flags = q; q += 16;
         p.t = q; q += B; p.emitted_here = q; q += B; p.n_out = q; q += B; p.last_tok = q; q += B; p.emit = q; q += B;
-        int *d_off = q; q += B; int *d_len = q; q += B; q += B;
+        q += 3 * B;
         p.cand_i = q; q += 2 * (size_t)B * nw;
         p.tokens = q; q += (size_t)B * cap; p.frames = q;
-        p.cap = cap; p.enc_off = d_off; p.enc_len = d_len;
+        p.cap = cap; p.enc_off = hm_dev + G.g0; p.enc_len = hm_dev + Ball + G.g0;
+        int max_len = cap / cfg.max_symbols;
         p.max_steps = max_len * (cfg.max_symbols + 1) + 8; p.init_state = 1;
-        long long *dbg_dev = nullptr;
-        if (prof_on) { dbg_dev = reinterpret_cast<long long *>(ws.get<long long>(8)); if (dbg_dev) MB_CUDA(cudaMemsetAsync(dbg_dev, 0, 64, stream)); }
-        p.dbg = dbg_dev;
-        std::vector<int> hm(2 * B);
-        for (int b = 0; b < B; b++) { hm[b] = offs[g0 + b]; hm[B + b] = lens[g0 + b]; }
-        MB_CUDA(cudaMemcpyAsync(d_off, hm.data(), B * sizeof(int), cudaMemcpyHostToDevice, stream));
-        MB_CUDA(cudaMemcpyAsync(d_len, hm.data() + B, B * sizeof(int), cudaMemcpyHostToDevice, stream));
-        { const int sp = prof_begin_span(PROF_DECODE);
-          const int rc = greedy_launch(p, stream);
-          prof_end_span(sp);
-          if (sp >= 0) prof_launches[PROF_DECODE]++;
+        if (prof_on && gi == 0) { G.dbg = reinterpret_cast<long long *>(ws.get<long long>(8)); if (G.dbg) MB_CUDA(cudaMemsetAsync(G.dbg, 0, 64, ls)); }
+        p.dbg = G.dbg;
+        G.n_out = p.n_out; G.tokens = p.tokens; G.frames = p.frames;
+        { const int sp = gi == 0 ? prof_begin_span(PROF_DECODE) : -1;       // the span of group 0 brackets the fork; the rest overlap it
+          const int rc = greedy_launch(p, ls, lane_blocks);
+          if (sp >= 0 && lanes <= 1) { prof_end_span(sp); prof_launches[PROF_DECODE]++; }
+          else if (sp >= 0) prof_pending = sp;
           if (rc) return -1; }
         note_launch();
+    }
+    if (lanes_join(lanes)) return -1;
+    if (prof_pending >= 0) { prof_end_span(prof_pending); prof_launches[PROF_DECODE] += (long long)groups.size(); prof_pending = -1; }
+    for (const Group &G : groups) {
+        const int B = G.B, cap = G.cap;
         std::vector<int> hn(B), ht((size_t)B * cap), hf((size_t)B * cap);
-        MB_CUDA(cudaMemcpyAsync(hn.data(), p.n_out, B * sizeof(int), cudaMemcpyDeviceToHost, stream));
-        MB_CUDA(cudaMemcpyAsync(ht.data(), p.tokens, ht.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
-        MB_CUDA(cudaMemcpyAsync(hf.data(), p.frames, hf.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
-        if (dbg_dev) MB_CUDA(cudaMemcpyAsync(dec_dbg, dbg_dev, 64, cudaMemcpyDeviceToHost, stream));
+        MB_CUDA(cudaMemcpyAsync(hn.data(), G.n_out, B * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        MB_CUDA(cudaMemcpyAsync(ht.data(), G.tokens, ht.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        MB_CUDA(cudaMemcpyAsync(hf.data(), G.frames, hf.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
+        if (G.dbg) MB_CUDA(cudaMemcpyAsync(dec_dbg, G.dbg, 64, cudaMemcpyDeviceToHost, stream));
         MB_CUDA(cudaStreamSynchronize(stream));
         for (int b = 0; b < B; b++) {
-            tokens[g0 + b].assign(ht.begin() + (size_t)b * cap, ht.begin() + (size_t)b * cap + hn[b]);
-            frames[g0 + b].assign(hf.begin() + (size_t)b * cap, hf.begin() + (size_t)b * cap + hn[b]);
+            tokens[G.g0 + b].assign(ht.begin() + (size_t)b * cap, ht.begin() + (size_t)b * cap + hn[b]);
+            frames[G.g0 + b].assign(hf.begin() + (size_t)b * cap, hf.begin() + (size_t)b * cap + hn[b]);
         }
-        ws.off = mark;
     }
+    ws.off = mark;
     return 0;
 }
 

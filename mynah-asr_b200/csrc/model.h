@@ -96,6 +96,7 @@ struct Model {
     long long dec_dbg[8] = {0};                      // greedy-decoder phase clocks of the last profiled run
     std::vector<ProfSpan> prof_spans;
     size_t prof_used = 0;
+    int prof_pending = -1;                           // decode span left open until the lanes have joined
     double prof_flops[PROF_NCAT] = {0}, prof_bytes[PROF_NCAT] = {0};
     long long prof_launches[PROF_NCAT] = {0};
     int prof_begin_span(int cat);                    // returns span index or -1
@@ -158,6 +159,16 @@ struct Model {
     int upload_bytes(void *dst, const void *src, size_t n);
     float *decode_scratch(size_t nfloats);
     void release_load_buffers();
+
+    // decode lanes: lock-step groups of DEC_MAX_B utterances run side by side on these streams, each on a share
+    // of the SMs (a group's steps are latency-bound, not bandwidth-bound, so four groups on a quarter of the
+    // SMs each finish sooner than four groups one after the other on all of them)
+    static constexpr int DEC_LANES = 4;
+    cudaStream_t lane[DEC_LANES] = {nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t lane_done[DEC_LANES] = {nullptr, nullptr, nullptr, nullptr}, lane_fork = nullptr;
+    int lanes_begin(int n_groups);                   // lanes in use (1 = everything stays on `stream`); forks them off `stream`
+    cudaStream_t lane_stream(int lanes, int gi) const { return lanes > 1 ? lane[gi % lanes] : stream; }
+    int lanes_join(int lanes);                       // `stream` waits for every lane
 
     ~Model();
     void *dev_alloc(size_t bytes);
@@ -232,7 +243,8 @@ struct GreedyDev {
     long long *dbg;              // optional [8] phase timers (clock64 ticks of CTA 0), null = off
 };
 
-int greedy_launch(const GreedyDev &p, cudaStream_t st);
+// blocks: CTAs of the cooperative grid (0 = one per SM); at least p.B
+int greedy_launch(const GreedyDev &p, cudaStream_t st, int blocks = 0);
 void set_load_seconds(mynah_b200_model *h, double seconds);     // capi.cu: the loader reports its whole wall time
 
 }  // namespace mb

@@ -185,6 +185,14 @@ static GemmEpilogue st_epi(int mode, int act, float alpha, const float *bias, fl
 
 static constexpr int STREAM_CONV_MAX = 48;               // k - 1 + q rows held in registers by stream_conv_kernel
 
+// Device memory of a stream group belongs to the group (plain allocations, freed at close), not to the model's slabs.
+static void *stream_alloc(StreamState &st, size_t bytes) {
+    void *p = nullptr;
+    if (cudaMalloc(&p, bytes ? bytes : 16) != cudaSuccess) { cudaGetLastError(); set_error("cudaMalloc(%zu) failed", bytes); return nullptr; }
+    st.owned.push_back(p);
+    return p;
+}
+
 int Model::stream_open(StreamState &st, int S, int left, int right) {
     if (!causal) { set_error("stream_open: cache-aware streaming needs a causal (Nemotron-style) encoder"); return -1; }
     if (S <= 0 || left < 0 || right < 0) { set_error("stream_open: bad argument"); return -1; }
@@ -197,20 +205,18 @@ int Model::stream_open(StreamState &st, int S, int left, int right) {
     int F = cfg.n_mels;
     for (int s = 0; s < 3; s++) {
         const size_t n = (size_t)S * F * (s == 0 ? 1 : C);
-        st.ss_cache[s] = (float *)dev_alloc(n * sizeof(float));
+        st.ss_cache[s] = (float *)stream_alloc(st, n * sizeof(float));
         if (!st.ss_cache[s]) return -1;
         MB_CUDA(cudaMemsetAsync(st.ss_cache[s], 0, n * sizeof(float), stream));
-        st.owned.push_back(st.ss_cache[s]);
         F = F / 2 + 1;
     }
     const size_t kv = (size_t)n_layers * S * (left > 0 ? left : 1) * d_model, cv = (size_t)n_layers * S * (conv_k - 1) * d_model;
-    st.k_cache = (__half *)dev_alloc(kv * sizeof(__half));
-    st.v_cache = (__half *)dev_alloc(kv * sizeof(__half));
-    st.conv_cache = (float *)dev_alloc(cv * sizeof(float));
+    st.k_cache = (__half *)stream_alloc(st, kv * sizeof(__half));
+    st.v_cache = (__half *)stream_alloc(st, kv * sizeof(__half));
+    st.conv_cache = (float *)stream_alloc(st, cv * sizeof(float));
     if (!st.k_cache || !st.v_cache || !st.conv_cache) return -1;
-    st.d_start = (int *)dev_alloc(sizeof(int));
+    st.d_start = (int *)stream_alloc(st, sizeof(int));
     if (!st.d_start) return -1;
-    st.owned.push_back(st.k_cache); st.owned.push_back(st.v_cache); st.owned.push_back(st.conv_cache); st.owned.push_back(st.d_start);
     MB_CUDA(cudaMemsetAsync(st.d_start, 0, sizeof(int), stream));
     MB_CUDA(cudaMemsetAsync(st.k_cache, 0, kv * sizeof(__half), stream));
     MB_CUDA(cudaMemsetAsync(st.v_cache, 0, kv * sizeof(__half), stream));
@@ -222,10 +228,7 @@ int Model::stream_open(StreamState &st, int S, int left, int right) {
 void Model::stream_close(StreamState &st) {
     if (st.exec) cudaGraphExecDestroy(st.exec);
     if (st.graph) cudaGraphDestroy(st.graph);
-    for (void *p : st.owned) {
-        cudaFree(p);
-        for (auto it = owned.begin(); it != owned.end(); ++it) if (*it == p) { owned.erase(it); break; }
-    }
+    for (void *p : st.owned) cudaFree(p);
     st = StreamState();
 }
 
@@ -383,9 +386,8 @@ int Model::stream_mel_feed(StreamState &st, const float *audio, int n, int finis
     const int S = st.S, hop = cfg.hop_length, nf = cfg.n_fft, nm = cfg.n_mels;
     if (!st.mel_buf[0]) {
         for (int i = 0; i < 2; i++) {
-            st.mel_buf[i] = (float *)dev_alloc((size_t)S * MEL_CAP * sizeof(float));
+            st.mel_buf[i] = (float *)stream_alloc(st, (size_t)S * MEL_CAP * sizeof(float));
             if (!st.mel_buf[i]) return -1;
-            st.owned.push_back(st.mel_buf[i]);
         }
     }
     // drop what no later frame needs (one sample more than the window: the pre-emphasis reads s - 1)
@@ -435,10 +437,9 @@ int Model::stream_decode(StreamState &st, const float *enc_dev, int q, std::vect
     const int ngroups = cdiv(S, DEC_MAX_B);
     const size_t fblock = (size_t)(3 * L + 1) * DEC_MAX_B * H, iblock = DEC_MAX_B + 8;
     if (!st.dec_f) {
-        st.dec_f = (float *)dev_alloc(ngroups * fblock * sizeof(float));
-        st.dec_i = (int *)dev_alloc(ngroups * iblock * sizeof(int));
+        st.dec_f = (float *)stream_alloc(st, ngroups * fblock * sizeof(float));
+        st.dec_i = (int *)stream_alloc(st, ngroups * iblock * sizeof(int));
         if (!st.dec_f || !st.dec_i) return -1;
-        st.owned.push_back(st.dec_f); st.owned.push_back(st.dec_i);
         MB_CUDA(cudaMemsetAsync(st.dec_f, 0, ngroups * fblock * sizeof(float), stream));
         MB_CUDA(cudaMemsetAsync(st.dec_i, 0, ngroups * iblock * sizeof(int), stream));
     }
@@ -452,15 +453,27 @@ int Model::stream_decode(StreamState &st, const float *enc_dev, int q, std::vect
         for (int b = 0; b < B; b++) { hm[o + b] = (g0 + b) * q; hm[o + B + b] = q; }
         o += 2 * B;
     }
+    // every group's integer block (flags, per-utterance state, candidates, emitted tokens and frames) sits in one
+    // region so that a single copy brings all results back
+    const size_t ipg = 8 * (size_t)DEC_MAX_B + 2 * (size_t)DEC_MAX_B * nw + 2 * (size_t)DEC_MAX_B * cap + 16;
+    int *iz_all = ws.get<int>(ipg * ngroups);
+    if (!iz_all) return -1;
+    MB_CUDA(cudaMemsetAsync(iz_all, 0, ipg * ngroups * sizeof(int), stream));
+    int *hm_dev = ws.get<int>(hm.size());
+    if (!hm_dev) return -1;
+    MB_CUDA(cudaMemcpyAsync(hm_dev, hm.data(), hm.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
+    MB_CUDA(cudaStreamSynchronize(stream));          // hm is a stack-lifetime buffer
+    const int lanes = lanes_begin(ngroups);
+    if (lanes < 1) return -1;
+    const int lane_blocks = lanes > 1 ? (device_sm_count() / lanes > DEC_MAX_B ? device_sm_count() / lanes : DEC_MAX_B) : 0;
     for (int gi = 0; gi < ngroups; gi++) {
         const int g0 = gi * DEC_MAX_B, B = S - g0 < DEC_MAX_B ? S - g0 : DEC_MAX_B;
         const size_t nstate = (size_t)L * B * H;
         float *fs = st.dec_f + gi * fblock;
         int *is = st.dec_i + gi * iblock;
         float *cand = ws.get<float>(2 * (size_t)B * nw + (size_t)DEC_MAX_B * H);
-        int *iz = ws.get<int>(8 * (size_t)B + 2 * (size_t)B * nw + 2 * (size_t)B * cap + 16);
-        if (!cand || !iz) return -1;
-        MB_CUDA(cudaMemsetAsync(iz, 0, (8 * (size_t)B + 16) * sizeof(int), stream));
+        int *iz = iz_all + gi * ipg;
+        if (!cand) return -1;
         GreedyDev p;
         memset(&p, 0, sizeof(p));
         p.emb = emb; p.head_b = head_b; p.proj_b = proj_b;
@@ -476,27 +489,26 @@ int Model::stream_decode(StreamState &st, const float *enc_dev, int q, std::vect
         int *qi = iz;
         p.flags = qi; qi += 16;
         p.t = qi; qi += B; p.emitted_here = qi; qi += B; p.n_out = qi; qi += B; p.emit = qi; qi += B;
-        int *d_off = qi; qi += B; int *d_len = qi; qi += B; qi += 2 * B;
+        qi += 4 * B;
         p.cand_i = qi; qi += 2 * (size_t)B * nw;
         p.tokens = qi; qi += (size_t)B * cap; p.frames = qi;
         p.last_tok = is; p.par_state = is + DEC_MAX_B;
-        p.cap = cap; p.enc_off = d_off; p.enc_len = d_len;
+        p.cap = cap; p.enc_off = hm_dev + 2 * (size_t)g0; p.enc_len = hm_dev + 2 * (size_t)g0 + B;
         p.max_steps = q * (cfg.max_symbols + 1) + 8; p.init_state = st.dec_started ? 0 : 1;
-        MB_CUDA(cudaMemcpyAsync(d_off, hm.data() + 2 * (size_t)g0, 2 * B * sizeof(int), cudaMemcpyHostToDevice, stream));
-        if (greedy_launch(p, stream)) return -1;
+        if (greedy_launch(p, lane_stream(lanes, gi), lane_blocks)) return -1;
         note_launch();
         outs[gi] = Out{p.n_out, p.tokens, p.frames, B};
     }
+    if (lanes_join(lanes)) return -1;
+    std::vector<int> hz(ipg * ngroups);
+    MB_CUDA(cudaMemcpyAsync(hz.data(), iz_all, hz.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
+    MB_CUDA(cudaStreamSynchronize(stream));
     for (int gi = 0; gi < ngroups; gi++) {
         const Out &o = outs[gi];
-        std::vector<int> hn(o.B), ht((size_t)o.B * cap), hf((size_t)o.B * cap);
-        MB_CUDA(cudaMemcpyAsync(hn.data(), o.n_out, o.B * sizeof(int), cudaMemcpyDeviceToHost, stream));
-        MB_CUDA(cudaMemcpyAsync(ht.data(), o.tokens, ht.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
-        MB_CUDA(cudaMemcpyAsync(hf.data(), o.frames, hf.size() * sizeof(int), cudaMemcpyDeviceToHost, stream));
-        MB_CUDA(cudaStreamSynchronize(stream));
+        const int *hn = hz.data() + (o.n_out - iz_all), *ht = hz.data() + (o.tokens - iz_all), *hf = hz.data() + (o.frames - iz_all);
         for (int b = 0; b < o.B; b++) {
             const int s = gi * DEC_MAX_B + b;
-            tokens[s].assign(ht.begin() + (size_t)b * cap, ht.begin() + (size_t)b * cap + hn[b]);
+            tokens[s].assign(ht + (size_t)b * cap, ht + (size_t)b * cap + hn[b]);
             frames[s].resize(hn[b]);
             for (int i = 0; i < hn[b]; i++) frames[s][i] = (int)(st.t_abs + hf[(size_t)b * cap + i]);
         }

@@ -1,10 +1,12 @@
 """One kernel on one synthetic case, for timing and for profiler captures.
 
     python mynah-asr_b200/kernel_case.py gemm  --T 16384 --n 4096 --k 1024 [--fast] [--iters 3]
+    python mynah-asr_b200/kernel_case.py gemm  --T 16384 --n 4096 --k 1024 --fmt q8n --a8 [--iters 3]
     python mynah-asr_b200/kernel_case.py qgemv --T 1 --n 65536 --k 4096 --fmt q4_0 [--iters 3]
     python mynah-asr_b200/kernel_case.py attention --T 750 --batch 16 [--heads 8] [--impl 0] [--iters 3]
 
-gemm : the tcgen05 contraction on resident fp16 planes (large T).
+gemm : the tcgen05 contraction on resident fp16 planes (large T); with --fmt q8n --a8 the integer contraction
+       (tcgen05 kind::i8) on reference-native int8 weights and int8 activation rows.
 qgemv: the weight-streaming small-T kernel on the stored blocks; sizes above the 126 MB L2
        make the figure an HBM figure. Prints the CUDA-event time per launch, the algorithmic
        bytes / flops and the achieved rate.
@@ -34,7 +36,7 @@ def _pkg():
     return mod
 
 
-BPP = {"f32": 4.0, "q8_0": 34 / 32, "q4_0": 18 / 32, "q4_k": 144 / 256, "q6_k": 210 / 256}
+BPP = {"q8n": 1.0, "f32": 4.0, "q8_0": 34 / 32, "q4_0": 18 / 32, "q4_k": 144 / 256, "q6_k": 210 / 256}
 
 
 def random_blocks(fmt: str, n: int, k: int, rng) -> np.ndarray:
@@ -92,8 +94,12 @@ def main():
     if a.kernel == "attention":
         return attention_case(pkg, a, rng)
     T = a.T or (16384 if a.kernel == "gemm" else 1)
-    fmt = {"f32": pkg.F32, "q8_0": pkg.GGML_Q8_0, "q4_0": pkg.GGML_Q4_0, "q4_k": pkg.GGML_Q4_K, "q6_k": pkg.GGML_Q6_K}[a.fmt]
-    q = pkg.QMat(fmt, random_blocks(a.fmt, a.n, a.k, rng), a.n, a.k)
+    if a.fmt == "q8n":
+        wq = rng.integers(-127, 128, (a.n, a.k), dtype=np.int8)
+        q = pkg.QMat(pkg.MYNAH_Q8, wq, a.n, a.k, scales=rng.uniform(1e-4, 2e-4, a.n).astype(np.float32))
+    fmt = {"q8n": pkg.MYNAH_Q8, "f32": pkg.F32, "q8_0": pkg.GGML_Q8_0, "q4_0": pkg.GGML_Q4_0, "q4_k": pkg.GGML_Q4_K, "q6_k": pkg.GGML_Q6_K}[a.fmt]
+    if a.fmt != "q8n":
+        q = pkg.QMat(fmt, random_blocks(a.fmt, a.n, a.k, rng), a.n, a.k)
     flags = (pkg.FAST if a.fast else pkg.A16) | (pkg.A8 if a.a8 else 0)
     ms = q.time_ms(T, flags, a.iters)
     out = {"kernel": a.kernel, "T": T, "n": a.n, "k": a.k, "fmt": a.fmt, "ms": ms}
