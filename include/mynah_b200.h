@@ -238,6 +238,36 @@ int mynah_b200_align_min_frames(const int *tokens, int n_tokens);
  * model's CTC head over enc_out [T, d_model] (raw encoder output, blank = vocab - 1), then the alignment */
 int mynah_b200_ctc_align(mynah_b200_model *m, const float *enc_out, int T, const int *tokens, int n_tokens, int *t0, int *t1);
 
+/* ---- voice activity and offline segment planning ------------------------------------ */
+/* the "vad" section of a VAD model's mynah.json (tools/convert_silero.py:192-215) */
+typedef struct {
+    int frame_samples, context_samples, reflect_pad, n_fft, hop_length, n_bins, lstm_hidden;
+    int n_enc;                                   /* conv blocks (Silero v5: 4) */
+    int enc_channels[8], enc_kernels[8], enc_strides[8], enc_pads[16];   /* pads: left, right per block */
+    double threshold, neg_threshold;
+    int min_speech_ms, min_silence_ms, speech_pad_ms;
+} mynah_b200_vad_config;
+typedef struct mynah_b200_vad mynah_b200_vad;
+/* replaces mynah_asr_vad_open (src/vad.h:19-21) for tensors already read by the host: the STFT basis
+ * [2 n_bins, n_fft], per block the conv weight [cout, cin, k] and bias, the LSTM (gate order i f g o, both
+ * biases), the 1x1 head. NULL on error. */
+mynah_b200_vad *mynah_b200_vad_new(const mynah_b200_vad_config *cfg, const float *basis, const float *const *enc_w,
+                                   const float *const *enc_b, const float *w_ih, const float *w_hh, const float *b_ih,
+                                   const float *b_hh, const float *head_w, float head_b);
+void mynah_b200_vad_free(mynah_b200_vad *v);
+int mynah_b200_vad_frame_samples(const mynah_b200_vad *v);
+/* the probabilities mynah_asr_vad_feed (src/vad.h:29-31) returns frame by frame from a fresh state, for the whole
+ * signal in one call: probs[ceil(n / frame_samples)]; returns the frame count, -1 on error */
+int mynah_b200_vad_probs(mynah_b200_vad *v, const float *samples, size_t n_samples, float *probs, int cap);
+/* replaces mynah_asr_vad_speech_spans (src/vad.h:80-84): padded speech spans as pairs t0, t1 (sample offsets,
+ * [t0, t1)); returns their number, -1 on error or when there are more than cap */
+int mynah_b200_vad_speech_spans(mynah_b200_vad *v, const float *samples, size_t n_samples, long long *spans, int cap);
+/* replaces plan_segments (src/mynah_asr.c:1287-1323; with a VAD the plan of :1216-1280): the ranges the offline
+ * path decodes independently, as pairs offset, length. v may be NULL (energy planner). seg_sec is the model's
+ * segment limit (mynah_asr_segment_limit). Returns the number of segments (at least one), -1 on error. */
+int mynah_b200_plan_segments(mynah_b200_vad *v, const float *samples, size_t n_samples, int sample_rate, double seg_sec,
+                             long long *segs, int cap);
+
 /* ---- cache-aware streaming (Nemotron-style causal encoders) ------------------------ */
 /* replaces mynah_asr_enc_stream_init / _need / _step / _free (src/encoder.h:110-120) for n_streams
  * streams that advance in lock step: every step takes one chunk of mel frames from each stream and

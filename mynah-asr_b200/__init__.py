@@ -36,6 +36,14 @@ class Config(C.Structure):
                 ("durations", C.c_int * 16), ("strict", C.c_int), ("attn_impl", C.c_int), ("aed_heads", C.c_int), ("a8", C.c_int)]
 
 
+class VadConfig(C.Structure):
+    _fields_ = [("frame_samples", C.c_int), ("context_samples", C.c_int), ("reflect_pad", C.c_int), ("n_fft", C.c_int),
+                ("hop_length", C.c_int), ("n_bins", C.c_int), ("lstm_hidden", C.c_int), ("n_enc", C.c_int),
+                ("enc_channels", C.c_int * 8), ("enc_kernels", C.c_int * 8), ("enc_strides", C.c_int * 8),
+                ("enc_pads", C.c_int * 16), ("threshold", C.c_double), ("neg_threshold", C.c_double),
+                ("min_speech_ms", C.c_int), ("min_silence_ms", C.c_int), ("speech_pad_ms", C.c_int)]
+
+
 class BackendError(RuntimeError):
     pass
 
@@ -181,6 +189,13 @@ def lib():
     L.mynah_b200_align_ctc.argtypes = [c_fp, ci, ci, c_ip, ci, ci, c_ip, c_ip]
     L.mynah_b200_align_min_frames.argtypes = [c_ip, ci]
     L.mynah_b200_ctc_align.argtypes = [vp, c_fp, ci, c_ip, ci, c_ip, c_ip]
+    L.mynah_b200_vad_new.restype = vp
+    L.mynah_b200_vad_new.argtypes = [C.POINTER(VadConfig), c_fp, C.POINTER(c_fp), C.POINTER(c_fp), c_fp, c_fp, c_fp, c_fp, c_fp, cf]
+    L.mynah_b200_vad_free.argtypes = [vp]
+    L.mynah_b200_vad_free.restype = None
+    L.mynah_b200_vad_probs.argtypes = [vp, c_fp, C.c_size_t, c_fp, ci]
+    L.mynah_b200_vad_speech_spans.argtypes = [vp, c_fp, C.c_size_t, C.POINTER(C.c_longlong), ci]
+    L.mynah_b200_plan_segments.argtypes = [vp, c_fp, C.c_size_t, ci, C.c_double, C.POINTER(C.c_longlong), ci]
     L.mynah_b200_batch_upload.restype = vp
     L.mynah_b200_batch_upload.argtypes = [vp, C.POINTER(c_fp), C.POINTER(C.c_size_t), ci]
     L.mynah_b200_batch_run.argtypes = [vp, vp, ci]
@@ -279,6 +294,69 @@ def align_ctc(scores, tokens, blank):
 
 def align_min_frames(tokens):
     return lib().mynah_b200_align_min_frames((C.c_int * max(len(tokens), 1))(*tokens), len(tokens))
+
+
+class Vad:
+    """Silero-style voice activity model on the device (mynah_asr_vad, src/vad.h): cfg = the "vad" section of the
+    model's mynah.json, tensors = {name: float32 array} with the names of its model.safetensors."""
+
+    def __init__(self, cfg, tensors):
+        c = VadConfig()
+        for k in ("frame_samples", "context_samples", "reflect_pad", "n_fft", "hop_length", "n_bins", "lstm_hidden",
+                  "min_speech_ms", "min_silence_ms", "speech_pad_ms"):
+            setattr(c, k, int(cfg[k]))
+        c.threshold, c.neg_threshold = float(cfg["threshold"]), float(cfg["neg_threshold"])
+        ne = len(cfg["encoder_strides"])
+        c.n_enc = ne
+        for i in range(ne):
+            c.enc_channels[i], c.enc_kernels[i], c.enc_strides[i] = cfg["encoder_channels"][i], cfg["encoder_kernels"][i], cfg["encoder_strides"][i]
+            c.enc_pads[2 * i], c.enc_pads[2 * i + 1] = cfg["encoder_pads"][i]
+        t = {k: np.ascontiguousarray(v, np.float32) for k, v in tensors.items()}
+        self._keep = t
+        ew = (c_fp * ne)(*[_fp(t[f"encoder.{i}.reparam_conv.weight"]) for i in range(ne)])
+        eb = (c_fp * ne)(*[_fp(t[f"encoder.{i}.reparam_conv.bias"]) for i in range(ne)])
+        self.frame = c.frame_samples
+        self.h = lib().mynah_b200_vad_new(C.byref(c), _fp(t["stft.forward_basis_buffer"]), ew, eb, _fp(t["decoder.rnn.weight_ih"]),
+                                          _fp(t["decoder.rnn.weight_hh"]), _fp(t["decoder.rnn.bias_ih"]), _fp(t["decoder.rnn.bias_hh"]),
+                                          _fp(t["decoder.decoder.2.weight"]), float(t["decoder.decoder.2.bias"].reshape(-1)[0]))
+        if not self.h:
+            raise BackendError("vad_new: " + _err())
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().mynah_b200_vad_free(self.h)
+            self.h = None
+
+    __del__ = close
+
+    def probs(self, samples):
+        s = np.ascontiguousarray(samples, np.float32)
+        cap = s.size // self.frame + 2
+        out = np.empty(cap, np.float32)
+        k = lib().mynah_b200_vad_probs(self.h, _fp(s), s.size, _fp(out), cap)
+        if k < 0:
+            raise BackendError("vad_probs: " + _err())
+        return out[:k].copy()
+
+    def speech_spans(self, samples):
+        s = np.ascontiguousarray(samples, np.float32)
+        cap = s.size // (2 * self.frame) + 2
+        buf = (C.c_longlong * (2 * cap))()
+        k = lib().mynah_b200_vad_speech_spans(self.h, _fp(s), s.size, buf, cap)
+        if k < 0:
+            raise BackendError("vad_speech_spans: " + _err())
+        return [(int(buf[2 * i]), int(buf[2 * i + 1])) for i in range(k)]
+
+
+def plan_segments(samples, sample_rate, seg_sec, vad=None):
+    """plan_segments (src/mynah_asr.c:1287-1323) with the signal on the device: [(offset, length)]."""
+    s = np.ascontiguousarray(samples, np.float32)
+    cap = max(16, int(s.size / max(sample_rate, 1)) + 16)
+    buf = (C.c_longlong * (2 * cap))()
+    k = lib().mynah_b200_plan_segments(vad.h if vad else None, _fp(s), s.size, sample_rate, seg_sec, buf, cap)
+    if k < 0:
+        raise BackendError("plan_segments: " + _err())
+    return [(int(buf[2 * i]), int(buf[2 * i + 1])) for i in range(k)]
 
 
 class QMat:

@@ -361,6 +361,66 @@ def make_model(cfg: ModelConfig, seed: int = 0, weight_std: float = 0.02):
     return T
 
 
+VAD_GEOMETRY = dict(frame_samples=512, context_samples=64, reflect_pad=64, n_fft=256, hop_length=128, n_bins=129,
+                    stft_frames=4, encoder_channels=[128, 64, 64, 128], encoder_kernels=[3, 3, 3, 3],
+                    encoder_strides=[1, 2, 2, 1], encoder_pads=[[1, 1], [1, 1], [1, 1], [1, 1]], lstm_hidden=128,
+                    threshold=0.5, neg_threshold=0.35, min_speech_ms=250, min_silence_ms=100, speech_pad_ms=30)
+
+
+def make_vad(seed: int = 3, head_bias: float = -2.4):
+    """A voice-activity model with the geometry of Silero VAD v5 as the reference converts it
+    (tools/convert_silero.py:143-215): STFT basis [2 * 129, 1, 256] (real rows, then imaginary rows, Hann-windowed
+    DFT), four conv1d + ReLU blocks, one 128-wide LSTM, a 1x1 head. The network weights are random (seeded), with an
+    LSTM input gain and a head scale under which the probability follows the signal's level; with the default seed
+    and head bias it crosses both thresholds between the loud and the quiet stretches of speech_like_audio(). Returns (config dict for mynah.json, {name: float32 array})."""
+    rng = np.random.default_rng(seed)
+    g = VAD_GEOMETRY
+    n_fft, nb, H = g["n_fft"], g["n_bins"], g["lstm_hidden"]
+    k = np.arange(n_fft)
+    win = 0.5 - 0.5 * np.cos(2.0 * np.pi * k / n_fft)
+    ang = 2.0 * np.pi * np.outer(np.arange(nb), k) / n_fft
+    basis = np.concatenate([np.cos(ang) * win, -np.sin(ang) * win]).astype(np.float32)[:, None, :]
+    T = {"stft.forward_basis_buffer": basis}
+    cin = nb
+    for i, (cout, kk) in enumerate(zip(g["encoder_channels"], g["encoder_kernels"])):
+        T[f"encoder.{i}.reparam_conv.weight"] = (rng.standard_normal((cout, cin, kk)) * (1.6 / np.sqrt(cin * kk))).astype(np.float32)
+        T[f"encoder.{i}.reparam_conv.bias"] = (rng.standard_normal(cout) * 0.05).astype(np.float32)
+        cin = cout
+    T["decoder.rnn.weight_ih"] = (rng.standard_normal((4 * H, H)) * (2.0 / np.sqrt(H))).astype(np.float32)
+    T["decoder.rnn.weight_hh"] = (rng.standard_normal((4 * H, H)) * (1.0 / np.sqrt(H))).astype(np.float32)
+    T["decoder.rnn.bias_ih"] = (rng.standard_normal(4 * H) * 0.1).astype(np.float32)
+    T["decoder.rnn.bias_hh"] = (rng.standard_normal(4 * H) * 0.1).astype(np.float32)
+    T["decoder.decoder.2.weight"] = (rng.standard_normal((1, H, 1)) * 0.9).astype(np.float32)
+    T["decoder.decoder.2.bias"] = np.array([head_bias], np.float32)
+    cfg = {"mynah_asr_format": 1, "name": "synthetic-vad", "arch": "silero_vad_v5", "engine": "vad",
+           "weights": "model.safetensors", "sample_rate": 16000, "vad": dict(g)}
+    return cfg, T
+
+
+def write_vad_dir(dirpath: str, cfg: dict, tensors: dict) -> None:
+    import os
+    os.makedirs(dirpath, exist_ok=True)
+    write_safetensors(os.path.join(dirpath, "model.safetensors"), tensors)
+    with open(os.path.join(dirpath, "mynah.json"), "w") as f:
+        json.dump(cfg, f, indent=1)
+
+
+def speech_like_audio(seconds: float, seed: int = 0, sample_rate: int = 16000) -> np.ndarray:
+    """Bursts of noise of varying level separated by near-silence (0.3 - 2 s each), int16-quantised: a signal on
+    which a level-sensitive detector opens and closes spans."""
+    n = int(round(seconds * sample_rate))
+    rng = np.random.default_rng(7000003 * (seed + 1))
+    env = np.zeros(n)
+    pos, loud = 0, False
+    while pos < n:
+        ln = int(rng.uniform(0.3, 2.0) * sample_rate)
+        env[pos:pos + ln] = rng.uniform(0.3, 1.0) if loud else rng.uniform(0.0, 0.01)
+        pos += ln
+        loud = not loud
+    x = np.clip(np.rint(6000.0 * rng.standard_normal(n) * env), -32768, 32767).astype(np.int16)
+    return (x.astype(np.float32) / np.float32(32768.0)).astype(np.float32)
+
+
 def quantize_rows_int8(w: np.ndarray):
     """Per-row symmetric int8 as the reference's load-time quantiser writes it (mynah_asr_quantize_int8,
     src/qmat.c:19-36): scale = amax / 127 (1 for an all-zero row), q = round-half-away(w * (1 / scale))."""

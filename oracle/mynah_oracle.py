@@ -647,6 +647,161 @@ def align_ctc(scores, tokens, blank):
     return (0 if all(v >= 0 for v in t0) else -1), t0, t1
 
 
+# ------------------------------------------------------------------ voice activity (src/vad.c) and segment planning
+class Vad:
+    """mynah_asr_vad (src/vad.c): cfg = the "vad" section of mynah.json, W = {tensor name: f32 array}. One frame of
+    frame_samples in, one speech probability out, with the LSTM state and the lookbehind carried between calls."""
+
+    def __init__(self, cfg, W):
+        self.c, self.W = cfg, W
+        self.reset()
+
+    def reset(self):
+        H = self.c["lstm_hidden"]
+        self.look = np.zeros(self.c["context_samples"], f32)
+        self.h, self.cell = np.zeros(H, f32), np.zeros(H, f32)
+
+    def features(self, samples):
+        """lookbehind | frame (zero-padded) | reflect pad -> STFT magnitude -> conv blocks (vad.c:316-352): [hidden]"""
+        c = self.c
+        C, F, P = c["context_samples"], c["frame_samples"], c["reflect_pad"]
+        buf = np.zeros(C + F + P, f32)
+        buf[:C] = self.look
+        buf[C:C + len(samples)] = samples
+        N = C + F
+        buf[N:] = buf[N - 2 - np.arange(P)]
+        self.look = buf[N - C:N].copy()
+        T0, nf, hop, B = c["stft_frames"], c["n_fft"], c["hop_length"], c["n_bins"]
+        win = np.stack([buf[f * hop:f * hop + nf] for f in range(T0)])
+        spec = gemm_wt(self.W["stft.forward_basis_buffer"].reshape(2 * B, nf), win)       # [2B, T0]
+        x = np.sqrt((spec[:B] * spec[:B] + spec[B:] * spec[B:]).astype(f32)).astype(f32)
+        for i, (st, (pl, pr)) in enumerate(zip(c["encoder_strides"], c["encoder_pads"])):
+            w, b = self.W[f"encoder.{i}.reparam_conv.weight"], self.W[f"encoder.{i}.reparam_conv.bias"]
+            cout, cin, k = w.shape
+            t_in = x.shape[1]
+            t_out = (t_in + pl + pr - k) // st + 1
+            xp = np.zeros((cin, t_in + pl + pr), f32)
+            xp[:, pl:pl + t_in] = x
+            col = np.stack([xp[:, t * st:t * st + k].reshape(-1) for t in range(t_out)])   # [t_out, cin * k]
+            x = np.maximum(gemm_wt(w.reshape(cout, cin * k), col) + b[:, None], f32(0)).astype(f32)
+        return x[:, 0]
+
+    def feed(self, samples):
+        """mynah_asr_vad_feed (vad.c:316-385)."""
+        H = self.c["lstm_hidden"]
+        x = self.features(np.asarray(samples, f32))
+        z = (self.W["decoder.rnn.bias_ih"] + self.W["decoder.rnn.bias_hh"]).astype(f32)
+        z = (z + self.W["decoder.rnn.weight_ih"] @ x).astype(f32)
+        z = (z + self.W["decoder.rnn.weight_hh"] @ self.h).astype(f32)
+        ig, fg, gg, og = sigmoid(z[:H]), sigmoid(z[H:2 * H]), np.tanh(z[2 * H:3 * H]).astype(f32), sigmoid(z[3 * H:])
+        self.cell = (fg * self.cell + ig * gg).astype(f32)
+        self.h = (og * np.tanh(self.cell).astype(f32)).astype(f32)
+        acc = f32(self.W["decoder.decoder.2.bias"][0]) + f32(np.sum(self.W["decoder.decoder.2.weight"].reshape(-1) * np.maximum(self.h, 0), dtype=f32))
+        return float(sigmoid(np.array([acc], f32))[0])
+
+    def probs(self, samples):
+        self.reset()
+        F = self.c["frame_samples"]
+        return [self.feed(samples[o:o + F]) for o in range(0, len(samples), F)]
+
+
+def vad_spans_from_probs(cfg, probs, n_samples, sample_rate=16000):
+    """The hysteresis of mynah_asr_vad_seg_feed / _finish and the padding of mynah_asr_vad_pad_spans
+    (vad.c:417-474): spans [t0, t1) in samples."""
+    F = cfg["frame_samples"]
+    ms = lambda v: float(sample_rate) * float(v) / 1000.0
+    spans, trig, start, temp_end = [], False, 0, -1
+    for i, p in enumerate(probs):
+        cur = F * i
+        if p >= cfg["threshold"]:
+            temp_end = -1
+            if not trig:
+                trig, start = True, cur
+            continue
+        if p < cfg["neg_threshold"] and trig:
+            if temp_end < 0:
+                temp_end = cur
+            if float(cur - temp_end) < ms(cfg["min_silence_ms"]):
+                continue
+            end, trig, temp_end = temp_end, False, -1
+            if float(end - start) > ms(cfg["min_speech_ms"]):
+                spans.append([start, end])
+    if trig and float(n_samples - start) > ms(cfg["min_speech_ms"]):
+        spans.append([start, n_samples])
+    pad = int(float(sample_rate) * float(cfg["speech_pad_ms"]) / 1000.0)
+    for i in range(len(spans)):
+        if i == 0:
+            spans[0][0] = max(spans[0][0] - pad, 0)
+        if i != len(spans) - 1:
+            gap = spans[i + 1][0] - spans[i][1]
+            if gap < 2 * pad:
+                spans[i][1] += gap // 2
+                spans[i + 1][0] = max(spans[i + 1][0] - gap // 2, 0)
+            else:
+                spans[i][1] = min(spans[i][1] + pad, n_samples)
+                spans[i + 1][0] = max(spans[i + 1][0] - pad, 0)
+        else:
+            spans[i][1] = min(spans[i][1] + pad, n_samples)
+    return [tuple(s) for s in spans]
+
+
+def find_split_point(s, lo, hi, sr):
+    """Centre of the 20 ms window of least energy in [lo, hi), windows every 10 ms, the first minimum wins; the
+    energy is a double sum of squares (src/mynah_asr.c:1178-1192)."""
+    win = sr // 50
+    hop = win // 2
+    best, best_pos = 1e300, hi
+    p = lo
+    while p + win <= hi:
+        v = s[p:p + win].astype(np.float64)
+        e = 0.0
+        for x in v:                       # the reference's summation order
+            e += x * x
+        if e < best:
+            best, best_pos = e, p + win // 2
+        p += hop
+    return best_pos
+
+
+def plan_segments(samples, sr, seg_sec, vad_spans=None, context_sec=0.6):
+    """plan_segments / plan_segments_vad (src/mynah_asr.c:1216-1323): [(offset, length)]. vad_spans: padded speech
+    spans or None for the energy planner."""
+    n = len(samples)
+    seg_max = int(seg_sec * sr)
+
+    def cut(cur, stop, bound_end):
+        out = []
+        while cur < stop:
+            end = stop
+            if stop - cur > seg_max + seg_max // 10:
+                hi = cur + seg_max
+                lo = hi - 20 * sr if seg_max > 20 * sr else cur + sr
+                if lo <= cur:
+                    lo = cur + 1
+                end = find_split_point(samples, lo, hi, sr)
+                if bound_end and (end <= cur or end > stop):
+                    end = hi
+            if end <= cur:
+                end = cur + 1
+            out.append((cur, end - cur))
+            cur = end
+        return out
+    if vad_spans is not None and n > 0:
+        ctx = int(context_sec * sr)
+        sp = [[max(a - ctx, 0), min(b + ctx, n)] for a, b in vad_spans]
+        merged = []
+        for a, b in sp:
+            if merged and a <= merged[-1][1]:
+                merged[-1][1] = max(merged[-1][1], b)
+            else:
+                merged.append([a, b])
+        segs = [s for a, b in merged for s in cut(a, b, True)]
+        if segs or len(vad_spans) == 0:
+            return segs if segs else [(0, 0)]
+    segs = cut(0, n, False)
+    return segs if segs else [(0, 0)]
+
+
 # ------------------------------------------------------------------ cache-aware streaming
 class EncStream:
     """State of mynah_asr_enc_stream (src/encoder.h:93-108): per-layer K/V caches of up to `left`

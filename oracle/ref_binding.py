@@ -85,6 +85,14 @@ def load(path):
         L.ref_qmat_mul_from_f32.argtypes = [c_fp, C.c_int, C.c_int, C.c_int, c_fp, c_fp, C.c_int]
         L.ref_align_ctc.argtypes = [c_fp, C.c_int, C.c_int, c_ip, C.c_int, C.c_int, c_ip, c_ip]
         L.ref_align_min_frames.argtypes = [c_ip, C.c_int]
+        L.ref_vad_open.restype = C.c_void_p
+        L.ref_vad_open.argtypes = [C.c_char_p]
+        L.ref_vad_close.argtypes = [C.c_void_p]
+        L.ref_vad_reset.argtypes = [C.c_void_p]
+        L.ref_vad_feed.restype = C.c_float
+        L.ref_vad_feed.argtypes = [C.c_void_p, c_fp, C.c_size_t]
+        L.ref_vad_speech_spans.argtypes = [C.c_void_p, c_fp, C.c_size_t, C.POINTER(C.c_longlong), C.c_int]
+        L.ref_plan_segments.argtypes = [c_fp, C.c_size_t, C.c_int, C.c_double, C.c_void_p, C.POINTER(C.c_longlong), C.c_int]
         L.ingot_dequant.argtypes = [C.c_int, C.c_void_p, C.c_size_t, c_fp]
         L.ingot_quantize.argtypes = [C.c_int, c_fp, C.c_size_t, C.c_void_p]
     return L
@@ -116,6 +124,47 @@ def ggml_quantize(ggml_type: int, w: np.ndarray, nbytes: int) -> np.ndarray:
     rc = lib().ingot_quantize(ggml_type, _fp(w), w.size, out.ctypes.data)
     assert rc == 0
     return out
+
+
+class RefVad:
+    """mynah_asr_vad over a model directory (mynah.json + model.safetensors), src/vad.c."""
+
+    def __init__(self, model_dir):
+        self.h = lib().ref_vad_open(model_dir.encode())
+        if not self.h:
+            raise RuntimeError("reference failed to open the VAD at " + model_dir)
+
+    def close(self):
+        if self.h:
+            lib().ref_vad_close(self.h)
+            self.h = None
+
+    def probs(self, samples, frame=512):
+        samples = np.ascontiguousarray(samples, np.float32)
+        lib().ref_vad_reset(self.h)
+        out = []
+        for o in range(0, samples.size, frame):
+            piece = np.ascontiguousarray(samples[o:o + frame])
+            out.append(float(lib().ref_vad_feed(self.h, _fp(piece), piece.size)))
+        return out
+
+    def speech_spans(self, samples):
+        samples = np.ascontiguousarray(samples, np.float32)
+        cap = samples.size // 1024 + 2
+        buf = (C.c_longlong * (2 * cap))()
+        k = lib().ref_vad_speech_spans(self.h, _fp(samples), samples.size, buf, cap)
+        assert k >= 0
+        return [(int(buf[2 * i]), int(buf[2 * i + 1])) for i in range(k)]
+
+
+def plan_segments(samples, sample_rate, seg_sec, vad=None):
+    """plan_segments (src/mynah_asr.c:1287-1323; the VAD plan :1216-1280 when vad is a RefVad): [(offset, length)]."""
+    samples = np.ascontiguousarray(samples, np.float32)
+    cap = max(16, int(samples.size / max(sample_rate * 1.0, 1)) + 16)
+    buf = (C.c_longlong * (2 * cap))()
+    k = lib().ref_plan_segments(_fp(samples), samples.size, sample_rate, seg_sec, vad.h if vad else None, buf, cap)
+    assert 0 <= k <= cap
+    return [(int(buf[2 * i]), int(buf[2 * i + 1])) for i in range(k)]
 
 
 def align_ctc(scores, tokens, blank):

@@ -86,3 +86,8 @@ def align_cases():
     return out
 
 
+
+
+# voice activity / segment planning fixtures: (seconds, seed) of synth.speech_like_audio and the segment limits
+VAD_AUDIO = ((30.0, 1), (12.3, 2))
+VAD_SEG_SECONDS = (5.0, 8.0)

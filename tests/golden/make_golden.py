@@ -154,6 +154,31 @@ def align():
     np.savez_compressed(os.path.join(HERE, "ref_align.npz"), **out)
 
 
+def vad():
+    """mynah_asr_vad_feed / _speech_spans (src/vad.c) on the synthetic Silero-shaped model, and plan_segments
+    (src/mynah_asr.c:1216-1323) with and without it."""
+    cfg, T = synth.make_vad()
+    d = tempfile.mkdtemp()
+    synth.write_vad_dir(d, cfg, T)
+    rv = R.RefVad(d)
+    out = {}
+    for i, (secs, seed) in enumerate(cases.VAD_AUDIO):
+        a = synth.speech_like_audio(secs, seed=seed)
+        out[f"probs{i}"] = np.array(rv.probs(a), np.float32)
+        sp = rv.speech_spans(a)
+        out[f"spans{i}"] = np.array(sp, np.int64).reshape(-1, 2)
+        for seg in cases.VAD_SEG_SECONDS:
+            out[f"plan_energy{i}_{seg:g}"] = np.array(R.plan_segments(a, 16000, seg), np.int64).reshape(-1, 2)
+            out[f"plan_vad{i}_{seg:g}"] = np.array(R.plan_segments(a, 16000, seg, rv), np.int64).reshape(-1, 2)
+        print("vad", i, len(out[f"probs{i}"]), "frames", len(sp), "spans",
+              {k: len(v) for k, v in out.items() if k.startswith("plan") and k[10] == str(i) or k.startswith(f"plan_vad{i}")})
+    quiet = np.zeros(16000, np.float32)
+    out["spans_quiet"] = np.array(rv.speech_spans(quiet), np.int64).reshape(-1, 2)
+    out["plan_quiet"] = np.array(R.plan_segments(quiet, 16000, 5.0, rv), np.int64).reshape(-1, 2)
+    rv.close()
+    np.savez_compressed(os.path.join(HERE, "ref_vad.npz"), **out)
+
+
 def qmat():
     """mynah_asr_qmat_mul on weights quantised by the reference's own load-time
     quantiser, T = 1, 4 (int8-activation dots) and 48 (dequant + sgemm): the cases
@@ -177,8 +202,8 @@ if __name__ == "__main__":
     only = sys.argv[1:]
     if only:                      # regenerate only the named fixtures
         for name in only:
-            if name == "align":
-                align()
+            if name in ("align", "vad"):
+                (align if name == "align" else vad)()
                 continue
             (a8 if name in cases.A8 else prompt if name in cases.PROMPT else aed if name in cases.AED else pipeline)(name)
         sys.exit(0)
@@ -189,4 +214,5 @@ if __name__ == "__main__":
     for name in cases.PROMPT:
         prompt(name)
     align()
+    vad()
     qmat()
