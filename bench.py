@@ -457,6 +457,18 @@ def a8_section(args, pkg, synth, torch, groups, dec_id, audio_s, peaks):
                         "peak_source": src, "frac_of_bf16_sustained": achieved / peaks["bf16_tflops_sustained"] if achieved and peaks.get("bf16_tflops_sustained") else None,
                         "launches": g["launches"], "kernel_ms_per_step": g["ms"] / steps, "flops_per_step": g["flops"] / steps},
            "breakdown_ms_per_step": {k: v["ms"] / steps for k, v in prof.items()}}
+    # the integer contraction alone on the layer's shapes at this step's row count (CUDA events around 20 launches each,
+    # rows quantised beforehand): what the kernel reaches where the output is wide or narrow relative to K
+    rows = int(sum(len(a_) // 160 // 8 for g_ in groups for a_ in g_))
+    rng = np.random.default_rng(3)
+    per_shape = {}
+    for n_, k_ in ((cfg.ffn_dim, cfg.d_model), (cfg.d_model, cfg.ffn_dim), (cfg.d_model, cfg.d_model)):
+        qm = pkg.QMat(pkg.MYNAH_Q8, rng.integers(-127, 128, (n_, k_), dtype=np.int8), n_, k_, scales=np.full(n_, 1e-4, np.float32))
+        ms_ = qm.time_ms(rows, pkg.A8, 20)
+        tops = 2.0 * rows * n_ * k_ / (ms_ * 1e-3) / 1e12
+        per_shape[f"[{rows} x {n_} x {k_}]"] = {"us": ms_ * 1e3, "achieved": tops, "frac": tops / peak}
+        qm.close()
+    out["roofline"]["per_shape_isolated"] = per_shape
     if not args.no_cpu_baseline:
         from oracle import parity, ref_binding as R
         if R.available():
