@@ -61,15 +61,9 @@ struct GemmUnits {
     }
 };
 
-// Fused tail for a 32 x 32 block of the output handled by one warp: on entry lane r holds the 32 consecutive columns
-// [nb, nb + 32) of row m_base + r (the layout tcgen05.ld delivers: lane = row). A thread writing its own row would
-// make every store instruction of the warp touch 32 different rows; instead the block goes through `stage` (32 x 32
-// floats of shared memory owned by the warp, XOR-swizzled so that both the row-wise writes and the column-wise reads
-// are free of bank conflicts) and leaves row by row, lane = column: every store (and the read of a residual
-// accumulate) is one contiguous 128-byte line. Returns false if a value written as fp16 planes was out of range.
-static constexpr int GEMM_EPI_STAGE_FLOATS = 32 * 32;
-__device__ __forceinline__ bool gemm_epilogue_warp(const GemmEpilogue &ep, float (&v)[32], int m_base, int M, int nb, int N,
-                                                   float *stage, int lane) {
+// Fused tail for 32 consecutive columns [nb, nb+32) of output row m.
+// Returns false if a value written as fp16 planes was out of their range (see split_h16).
+__device__ __forceinline__ bool gemm_epilogue_row(const GemmEpilogue &ep, float (&v)[32], int m, int nb, int N) {
     bool fits = true;
     const int nvalid = N - nb < 32 ? N - nb : 32;
 #pragma unroll
@@ -78,46 +72,62 @@ __device__ __forceinline__ bool gemm_epilogue_warp(const GemmEpilogue &ep, float
         if (ep.bias && j < nvalid) x += ep.bias[nb + j];
         if (ep.act == ACT_SILU) x = x * __frcp_rn(1.0f + __expf(-x));   // exp(-x) -> inf gives x * 0
         else if (ep.act == ACT_RELU) x = fmaxf(x, 0.0f);
-        stage[lane * 32 + (j ^ lane)] = x;
+        v[j] = x;
     }
-    __syncwarp();
-    const int rows = M - m_base < 32 ? M - m_base : 32;
     if (ep.mode != OUT_H16) {
-        const bool in_n = lane < nvalid;
-        float *o = ep.out + (size_t)m_base * ep.ldo + nb + lane;
+        float *o = ep.out + (size_t)m * ep.ldo + nb;
+        const bool vec = nvalid == 32 && ((reinterpret_cast<uintptr_t>(o) & 15) == 0);
         if (ep.mode == OUT_RESID) {
-#pragma unroll 4
-            for (int r = 0; r < rows; r++) if (in_n) o[(size_t)r * ep.ldo] += ep.alpha * stage[r * 32 + (lane ^ r)];
-        } else {
-#pragma unroll 4
-            for (int r = 0; r < rows; r++) if (in_n) o[(size_t)r * ep.ldo] = stage[r * 32 + (lane ^ r)];
-        }
-    }
-    if (ep.mode == OUT_H16 || ep.mode == OUT_F32_H16) {
-        // two rows per pass: lanes 0..15 take columns 2l, 2l + 1 of row r, lanes 16..31 those of row r + 1
-        const int half = lane >> 4, c = 2 * (lane & 15);
-        const bool pair_ok = c + 1 < nvalid && (ep.ldh & 1) == 0 && (nb & 1) == 0;
-        for (int r0 = 0; r0 < rows; r0 += 2) {
-            const int r = r0 + half;
-            if (r >= rows) continue;
-            const float a = stage[r * 32 + (c ^ r)], b = stage[r * 32 + ((c + 1) ^ r)];
-            __half ah, al, bh, bl;
-            const size_t off = (size_t)(m_base + r) * ep.ldh + nb + c;
-            if (pair_ok) {
-                fits &= split_h16(a, ah, al);
-                fits &= split_h16(b, bh, bl);
-                *reinterpret_cast<__half2 *>(ep.out_hi + off) = __halves2half2(ah, bh);
-                if (ep.out_lo) *reinterpret_cast<__half2 *>(ep.out_lo + off) = __halves2half2(al, bl);
+            if (vec) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    float4 r = *reinterpret_cast<float4 *>(o + j);
+                    r.x += ep.alpha * v[j]; r.y += ep.alpha * v[j + 1];
+                    r.z += ep.alpha * v[j + 2]; r.w += ep.alpha * v[j + 3];
+                    *reinterpret_cast<float4 *>(o + j) = r;
+                }
             } else {
-                if (c < nvalid) { fits &= split_h16(a, ah, al); ep.out_hi[off] = ah; if (ep.out_lo) ep.out_lo[off] = al; }
-                if (c + 1 < nvalid) { fits &= split_h16(b, bh, bl); ep.out_hi[off + 1] = bh; if (ep.out_lo) ep.out_lo[off + 1] = bl; }
+#pragma unroll
+                for (int j = 0; j < 32; j++) if (j < nvalid) o[j] += ep.alpha * v[j];
+            }
+        } else {
+            if (vec) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4 *>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) if (j < nvalid) o[j] = v[j];
             }
         }
     }
-    __syncwarp();
+    if (ep.mode == OUT_H16 || ep.mode == OUT_F32_H16) {
+        __half *ph = ep.out_hi + (size_t)m * ep.ldh + nb;
+        __half *pl = ep.out_lo ? ep.out_lo + (size_t)m * ep.ldh + nb : nullptr;
+        const bool vec = nvalid == 32 && ((reinterpret_cast<uintptr_t>(ph) & 15) == 0);
+        if (vec) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                __align__(16) __half h[8], l[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) fits &= split_h16(v[j + i], h[i], l[i]);
+                *reinterpret_cast<uint4 *>(ph + j) = *reinterpret_cast<uint4 *>(h);
+                if (pl) *reinterpret_cast<uint4 *>(pl + j) = *reinterpret_cast<uint4 *>(l);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; j++) {
+                if (j < nvalid) {
+                    __half h, l;
+                    fits &= split_h16(v[j], h, l);
+                    ph[j] = h;
+                    if (pl) pl[j] = l;
+                }
+            }
+        }
+    }
     return fits;
 }
-
 #endif
 
 // C = A * B^T on tcgen05 tensor cores; nterms 1 (hi*hi) or 3 (hi*hi + lo*hi + hi*lo).

@@ -34,10 +34,9 @@ struct I8Cfg {
     static constexpr int A_BYTES = GEMM_BM * I8_BK;
     static constexpr int B_BYTES = BN * I8_BK;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int EPI_BYTES = I8_EPI_WARPS * GEMM_EPI_STAGE_FLOATS * 4;   // one 32 x 32 f32 block per epilogue warp
-    static constexpr int STAGES_RAW = (I8_SMEM_LIMIT - 2048 - EPI_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES_RAW = (I8_SMEM_LIMIT - 2048) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2048 + EPI_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2048;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
     static_assert(TMEM_COLS <= 512, "TMEM has 512 columns");
 };
@@ -70,7 +69,6 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     uint64_t *acc_full = empty_bar + Cfg::STAGES;      // [2] MMA -> epilogue
     uint64_t *acc_empty = acc_full + 2;                // [2] epilogue -> MMA
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
-    float *epi_stage = reinterpret_cast<float *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + 1024);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_k = K / I8_BK;
@@ -168,14 +166,14 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tc_ld32(acc + (uint32_t)(c * 32), v);
                     tc_wait_ld();
                     const int nb = n0 + c * 32;
-                    if (m0 + lg * 32 < M && nb < N) {    // warp-uniform
+                    if (m < M && nb < N) {
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
                             // (float)int32 * ws * sx, left to right (src/qmat.c:299)
                             const float ws = nb + j < N ? col_scale[nb + j] : 0.0f;
                             v[j] = __fmul_rn(__fmul_rn(__int2float_rn(__float_as_int(v[j])), ws), sx);
                         }
-                        fits &= gemm_epilogue_warp(ep, v, m0 + lg * 32, M, nb, N, epi_stage + (warp - 2) * GEMM_EPI_STAGE_FLOATS, lane);
+                        fits &= gemm_epilogue_row(ep, v, m, nb, N);
                     }
                 }
             }

@@ -39,10 +39,9 @@ struct GemmCfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = NPLANES * (A_BYTES + B_BYTES);
-    static constexpr int EPI_BYTES = EPI_WARPS * GEMM_EPI_STAGE_FLOATS * 4;      // one 32 x 32 f32 block per epilogue warp
-    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048 - EPI_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2048 + EPI_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2048;
     // NTERMS == 3 keeps a second accumulator for the cross terms (lo*hi + hi*lo);
     // everything is double-buffered so the epilogue of tile i overlaps the MMAs of tile i+1
     static constexpr int ACC_COLS = NTERMS == 1 ? BN : 2 * BN;
@@ -66,7 +65,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
     uint64_t *acc_full = empty_bar + Cfg::STAGES;      // [2] MMA -> epilogue
     uint64_t *acc_empty = acc_full + 2;                // [2] epilogue -> MMA
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
-    float *epi_stage = reinterpret_cast<float *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + 1024);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_k = K / BK;
@@ -183,8 +181,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
                         tc_wait_ld();
                     }
                     const int nb = n0 + c * 32;
-                    if (m0 + lg * 32 < M && nb < N)      // warp-uniform: the block has rows and columns inside the output
-                        fits &= gemm_epilogue_warp(ep, v, m0 + lg * 32, M, nb, N, epi_stage + (warp - 2) * GEMM_EPI_STAGE_FLOATS, lane);
+                    if (m < M && nb < N) fits &= gemm_epilogue_row(ep, v, m, nb, N);
                 }
             }
             tc_fence_before();

@@ -85,14 +85,15 @@ def load(path):
         L.ref_qmat_mul_from_f32.argtypes = [c_fp, C.c_int, C.c_int, C.c_int, c_fp, c_fp, C.c_int]
         L.ref_align_ctc.argtypes = [c_fp, C.c_int, C.c_int, c_ip, C.c_int, C.c_int, c_ip, c_ip]
         L.ref_align_min_frames.argtypes = [c_ip, C.c_int]
-        L.ref_vad_open.restype = C.c_void_p
-        L.ref_vad_open.argtypes = [C.c_char_p]
-        L.ref_vad_close.argtypes = [C.c_void_p]
-        L.ref_vad_reset.argtypes = [C.c_void_p]
-        L.ref_vad_feed.restype = C.c_float
-        L.ref_vad_feed.argtypes = [C.c_void_p, c_fp, C.c_size_t]
-        L.ref_vad_speech_spans.argtypes = [C.c_void_p, c_fp, C.c_size_t, C.POINTER(C.c_longlong), C.c_int]
-        L.ref_plan_segments.argtypes = [c_fp, C.c_size_t, C.c_int, C.c_double, C.c_void_p, C.POINTER(C.c_longlong), C.c_int]
+        if hasattr(L, "ref_vad_open"):        # the planner shim is part of the plain build only
+            L.ref_vad_open.restype = C.c_void_p
+            L.ref_vad_open.argtypes = [C.c_char_p]
+            L.ref_vad_close.argtypes = [C.c_void_p]
+            L.ref_vad_reset.argtypes = [C.c_void_p]
+            L.ref_vad_feed.restype = C.c_float
+            L.ref_vad_feed.argtypes = [C.c_void_p, c_fp, C.c_size_t]
+            L.ref_vad_speech_spans.argtypes = [C.c_void_p, c_fp, C.c_size_t, C.POINTER(C.c_longlong), C.c_int]
+            L.ref_plan_segments.argtypes = [c_fp, C.c_size_t, C.c_int, C.c_double, C.c_void_p, C.POINTER(C.c_longlong), C.c_int]
         L.ingot_dequant.argtypes = [C.c_int, C.c_void_p, C.c_size_t, c_fp]
         L.ingot_quantize.argtypes = [C.c_int, c_fp, C.c_size_t, C.c_void_p]
     return L
