@@ -738,10 +738,13 @@ def main():
         torch.cuda.synchronize()
 
     cfg, tensors = cached_model(synth, args.workload, rank, barrier)
+    t_load = time.perf_counter()
     model = pkg.Model(tensors, n_mels=cfg.n_mels, mel_fb=synth.mel_filterbank(cfg.n_mels),
                       window=synth.hann_window(), causal=int(cfg.causal), normalize=cfg.normalize, left=cfg.left,
                       right=cfg.right, blank=cfg.vocab - 1, max_symbols=cfg.max_symbols,
                       durations=tuple(cfg.durations), strict=args.mode == "strict", aed_heads=cfg.aed_heads)
+    t_load = time.perf_counter() - t_load
+    load_stats = model.load_stats()
     dec_id = {"ctc": 1, "aed": 2}.get(cfg.decoder, 0)
     if args.streams > 0:
         if not cfg.causal or cfg.left < 0:
@@ -905,6 +908,10 @@ def main():
                                        model.decoder_clocks())),
             "clocks": clk,
         }
+        line["model_load"] = {"seconds_host_call": t_load, "seconds_upload_and_decode": load_stats["seconds"],
+                              "host_bytes": load_stats["host_bytes"], "device_slab_bytes": load_stats["device_slab_bytes"],
+                              "what": "tensors handed over by name, copied through pinned staging into device slabs, blocks re-tiled "
+                                      "and decoded to operand planes by kernels (the reference decodes GGUF blocks to f32 on the host)"}
         if strong:
             line["dispatch"] = strong
         if world == 1 and not args.no_extra and args.mode == "strict":

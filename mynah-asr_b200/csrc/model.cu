@@ -341,14 +341,17 @@ int Model::encoder_layers(float *x, const std::vector<int> &lens, int left, int 
     MB_CUDA(cudaStreamSynchronize(stream));      // hmeta is a stack-lifetime buffer
     const int *d_off = meta, *d_len = meta + B, *d_rk = meta + 2 * B;
 
-    H16 hA = ws.planes((size_t)M * d), hC = ws.planes((size_t)M * d), hF = ws.planes((size_t)M * F);
+    // the single-product mode never reads the lo planes: its producers do not write them (half the bytes of every
+    // plane-writing epilogue, LayerNorm and conv-middle pass)
+    const bool with_lo = cfg.strict != 0;
+    H16 hA = ws.planes((size_t)M * d, with_lo), hC = ws.planes((size_t)M * d, with_lo), hF = ws.planes((size_t)M * F, with_lo);
     float *qbuf = ws.get<float>((size_t)M * d);
     H16 kbuf = ws.planes((size_t)M * d, false), vbuf = ws.planes((size_t)M * d, false);
     float *h2 = ws.get<float>((size_t)M * 2 * d);
     float *cbuf = ws.get<float>((size_t)M * d);
     H16 pe = ws.planes((size_t)rk_rows * d);
     H16 rk = ws.planes((size_t)rk_rows * d, false);
-    if (!hA.lo || !hC.lo || !hF.lo || !qbuf || !kbuf.hi || !vbuf.hi || !h2 || !cbuf || !pe.lo || !rk.hi) return -1;
+    if (!hA.hi || !hC.hi || !hF.hi || (with_lo && (!hA.lo || !hC.lo || !hF.lo)) || !qbuf || !kbuf.hi || !vbuf.hi || !h2 || !cbuf || !pe.lo || !rk.hi) return -1;
 
     // int8-activation mode: quantised rows of the LayerNorm outputs / attention context / conv middle (qA) and of
     // SiLU(FFN1) (qF), their scales, and the f32 values that get quantised
