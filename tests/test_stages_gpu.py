@@ -135,11 +135,20 @@ def test_whole_path_tokens(setup, synth):
 
 
 def test_fast_mode_within_tolerance(setup, gpu_pkg, synth):
-    """Single fp16 pass (the mode the roofline numbers are quoted on)."""
-    _, cfg, tensors, _, g = setup
+    """Single fp16 product per term (the extra `fast` key of the benchmark), held to the stated bar of relative L2 1e-3
+    against the compiled reference — the same bound the full-size models are held to in test_config_shapes_gpu.py —
+    and switchable at run time on one model: back in strict mode the bits are those of a model built strict."""
+    name, cfg, tensors, dm, g = setup
     fast = cases.device_model(gpu_pkg, synth, cfg, tensors, strict=False)
     f = g["feats"][:int(g["valid"])]
-    assert rel(fast.encoder_forward(f, raw=True), g["enc_raw"]) < 5e-3
+    e = rel(fast.encoder_forward(f, raw=True), g["enc_raw"])
+    print(name, "fast-mode encoder rel-L2", e)
+    assert e < 1e-3
+    strict_out = dm.encoder_forward(f, raw=True)
+    dm.set_strict(False)
+    assert np.array_equal(dm.encoder_forward(f, raw=True), fast.encoder_forward(f, raw=True))
+    dm.set_strict(True)
+    assert np.array_equal(dm.encoder_forward(f, raw=True), strict_out)
     fast.close()
 
 
