@@ -202,7 +202,8 @@ static GemmEpilogue aed_epi(int mode, int act, float alpha, const float *bias, f
 size_t Model::aed_bytes(int total_T, int B, int max_len) const {
     const size_t D = aed_d, F = aed_ffn, L = aed_layers.size();
     return (size_t)total_T * (d_out * 4 + D * 4 + L * 2 * D * 4) + L * 2 * (size_t)B * max_len * D * 4 +
-           (size_t)B * (D * 24 + 3 * D * 4 + F * 4 + (size_t)aed_vocab * 4) + (size_t)B * (max_len + 64) * 8 + (1 << 20);
+           (size_t)B * (D * 24 + 3 * D * 4 + F * 4 + (size_t)aed_vocab * 4) + (size_t)B * (max_len + 64) * 8 + (1 << 20) +
+           (size_t)((B + GEMM_BM - 1) / GEMM_BM) * (device_sm_count() + 8) * GEMM_BM * GEMM_SPLIT_BN * 4 + 65536;   // split-K slices
 }
 
 int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const std::vector<std::vector<int>> &prompts, int eos,
@@ -257,6 +258,21 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     int *st = ws.get<int>(6 * (size_t)B + 4), *best = ws.get<int>(B), *d_prompts = ws.get<int>((size_t)B * max_prompt);
     int *d_tokens = ws.get<int>((size_t)B * capn), *d_off = ws.get<int>(2 * (size_t)B);
     if (!sk || !x || !qkv || !q || !logits || !xn.hi || !att.hi || !ff.hi || !st || !best || !d_prompts || !d_tokens || !d_off) return -1;
+    // With B rows the contractions of a position have far fewer output tiles than the device has SMs; split-K lets
+    // all of them pull the weights. The slice count depends on the weight's shape alone, so a row's bits do not
+    // depend on B.
+    const int sms = device_sm_count();
+    size_t part_floats = 0, n_counters = 0;
+    auto split_need = [&](const QWeight &w) {
+        const size_t pf = gemm_split_part_floats(B, w.n, w.k, sms), nc = gemm_split_counters(B, w.n);
+        part_floats = pf > part_floats ? pf : part_floats;
+        n_counters = nc > n_counters ? nc : n_counters;
+    };
+    for (const AedLayer &A : aed_layers) { split_need(A.sqkv); split_need(A.so); split_need(A.cq); split_need(A.co); split_need(A.ff1); split_need(A.ff2); }
+    split_need(aed_head);
+    GemmSplit split{0, ws.get<float>(part_floats), ws.get<int>(n_counters)};
+    if (!split.part || !split.counters) return -1;
+    MB_CUDA(cudaMemsetAsync(split.counters, 0, n_counters * sizeof(int), stream));
     std::vector<int> hst(6 * (size_t)B + 4, 0), hp((size_t)B * max_prompt, 0), ho(2 * (size_t)B);
     for (int b = 0; b < B; b++) {
         hst[b] = prompts[b][0];                              // cur
@@ -285,20 +301,20 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
             const AedLayer &A = aed_layers[l];
             float *K = sk + (size_t)(2 * l) * B * max_len * D, *Vc = K + (size_t)B * max_len * D;
             if (layer_norm(x, A.ln_self_w, A.ln_self_b, nullptr, xn, B, D, 0, stream)) return -1;
-            if (gemm(xn, D, A.sqkv, aed_epi(OUT_F32, ACT_NONE, 1.f, A.sqkv_b, qkv, 3 * D), B)) return -1;
+            if (gemm(xn, D, A.sqkv, aed_epi(OUT_F32, ACT_NONE, 1.f, A.sqkv_b, qkv, 3 * D), B, &split)) return -1;
             aed_self_attn_kernel<<<dim3(H, B), 128, self_smem, stream>>>(qkv, K, Vc, pd, max_len, D, dk, att);
-            if (gemm(att, D, A.so, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.so_b, x, D), B)) return -1;
+            if (gemm(att, D, A.so, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.so_b, x, D), B, &split)) return -1;
             if (layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream)) return -1;
-            if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B)) return -1;
+            if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B, &split)) return -1;
             aed_cross_attn_kernel<<<dim3(H, B), cross_threads, cross_smem, stream>>>(q, ckv[l].hi, ckv[l].lo, d_off, d_off + B, max_T, D, dk, att);
-            if (gemm(att, D, A.co, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.co_b, x, D), B)) return -1;
+            if (gemm(att, D, A.co, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.co_b, x, D), B, &split)) return -1;
             if (layer_norm(x, A.ln_ffn_w, A.ln_ffn_b, nullptr, xn, B, D, 0, stream)) return -1;
-            if (gemm(xn, D, A.ff1, aed_epi(OUT_H16, ACT_RELU, 1.f, A.ff1_b, nullptr, 0, ff, F), B)) return -1;
-            if (gemm(ff, F, A.ff2, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.ff2_b, x, D), B)) return -1;
+            if (gemm(xn, D, A.ff1, aed_epi(OUT_H16, ACT_RELU, 1.f, A.ff1_b, nullptr, 0, ff, F), B, &split)) return -1;
+            if (gemm(ff, F, A.ff2, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.ff2_b, x, D), B, &split)) return -1;
         }
         // the head is evaluated at prompt positions too (its result is ignored there): one graph for all positions
         if (layer_norm(x, aed_fin_w, aed_fin_b, nullptr, xn, B, D, 0, stream)) return -1;
-        if (gemm(xn, D, aed_head, aed_epi(OUT_F32, ACT_NONE, 1.f, aed_head_b, logits, V), B)) return -1;
+        if (gemm(xn, D, aed_head, aed_epi(OUT_F32, ACT_NONE, 1.f, aed_head_b, logits, V), B, &split)) return -1;
         if (argmax_rows(logits, V, nullptr, B, V, best, stream)) return -1;
         aed_select_kernel<<<1, ((B + 31) / 32) * 32, 0, stream>>>(best, eos, capn, B, st, d_prompts, max_prompt, d_tokens);
         MB_CUDA(cudaGetLastError());

@@ -33,16 +33,46 @@ struct GemmEpilogue {
 
 static constexpr int GEMM_BM = 128;      // rows of an output tile (one tcgen05.mma M)
 
+// Split-K for contractions with few rows and few output tiles (one decoder position): `splits` CTAs share an output
+// tile, each sums a K slice into `part` (f32, [unit][128][tile width]); the last to arrive (counted in `counters`, one int
+// per tile, zero between launches) adds the slices in slice order and applies the fused tail, so the result does not
+// depend on which CTA came last. splits <= 1: off.
+struct GemmSplit {
+    int splits;
+    float *part;
+    int *counters;
+};
+static constexpr int GEMM_SPLIT_BN = 64;                 // tile width of the split-K path
+// K slices for an [*, N] x [N, K] contraction on `sms` SMs: a function of the weight's shape alone (never of the row
+// count), so a row's bits do not depend on how many rows share the launch.
+inline int gemm_split_slices(int N, int K, int sms) {
+    const int tiles = (N + GEMM_SPLIT_BN - 1) / GEMM_SPLIT_BN, num_k = K / 64;
+    int s = 1;
+    while (tiles * s * 2 <= sms && s * 2 <= 16 && num_k % (s * 2) == 0 && num_k / (s * 2) >= 2) s *= 2;
+    return s;
+}
+// floats of `part` / ints of `counters` that M rows of such a contraction need
+inline size_t gemm_split_part_floats(int M, int N, int K, int sms) {
+    const size_t tiles = (size_t)((N + GEMM_SPLIT_BN - 1) / GEMM_SPLIT_BN) * ((M + GEMM_BM - 1) / GEMM_BM);
+    const int s = gemm_split_slices(N, K, sms);
+    return s > 1 ? tiles * s * GEMM_BM * GEMM_SPLIT_BN : 0;       // at most ceil(M / 128) * sms * 128 * 64
+}
+inline size_t gemm_split_counters(int M, int N) {
+    return (size_t)((N + GEMM_SPLIT_BN - 1) / GEMM_SPLIT_BN) * ((M + GEMM_BM - 1) / GEMM_BM);
+}
+
 #ifdef __CUDACC__
 // Work units of the persistent loop. Whole waves of gridDim.x tiles come first; the tiles of the last, partial
 // wave are cut into 2 or 4 column strips when that still fits one wave, so that the tail costs a half or a
 // quarter of a tile time instead of a whole one (752 tiles on 148 CTAs: 5.25 instead of 6 tile times). A strip
 // runs the same instruction sequence over its columns as the whole tile would, so no output bit depends on it.
 struct GemmUnits {
-    int tiles_n, full, split, total;          // full: tiles in whole waves; split: strips per tail tile
-    __device__ GemmUnits(int M, int N, int BN_, int ctas) {
+    int tiles_n, full, split, total, slices;  // full: tiles in whole waves; split: strips per tail tile; slices: K slices per tile
+    __device__ GemmUnits(int M, int N, int BN_, int ctas, int slices_ = 1) {
         tiles_n = (N + BN_ - 1) / BN_;
+        slices = slices_;
         const int tiles = tiles_n * ((M + GEMM_BM - 1) / GEMM_BM);
+        if (slices > 1) { full = tiles * slices; split = 1; total = full; return; }   // split-K: no column strips
         full = tiles / ctas * ctas;
         const int rem = tiles - full;
         split = 1;
@@ -58,6 +88,15 @@ struct GemmUnits {
         width = u >= full ? BN_ / split : BN_;
         m0 = (tile / tiles_n) * GEMM_BM;
         n0 = (tile % tiles_n) * BN_ + sub * width;
+    }
+    // split-K form: unit u = tile * slices + slice (for slices == 1 the same as above with slice = 0)
+    __device__ void at(int u, int BN_, int &m0, int &n0, int &width, int &slice) const {
+        if (slices <= 1) { slice = 0; at(u, BN_, m0, n0, width); return; }
+        const int tile = u / slices;
+        slice = u % slices;
+        width = BN_;
+        m0 = (tile / tiles_n) * GEMM_BM;
+        n0 = (tile % tiles_n) * BN_;
     }
 };
 
@@ -133,8 +172,10 @@ __device__ __forceinline__ bool gemm_epilogue_row(const GemmEpilogue &ep, float 
 // C = A * B^T on tcgen05 tensor cores; nterms 1 (hi*hi) or 3 (hi*hi + lo*hi + hi*lo).
 // K must be a multiple of 64. status: device int receiving a non-zero code if a
 // bounded wait inside the kernel ran out.
+// split: optional split-K workspace (see GemmSplit; the slice count is gemm_split_slices(N, K, SMs), `splits` of the
+// argument is ignored); null = every tile sums its whole K.
 int gemm_tc(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, int M, int N, int K, int nterms,
-            int *status, cudaStream_t stream);
+            int *status, cudaStream_t stream, const GemmSplit *split = nullptr);
 
 // Integer contraction on the tensor cores (gemm_i8.cu): acc[m,n] = sum_k a[m,k] * b[n,k] in int32 (exact), then
 // v = (float)acc * col_scale[n] * row_scale[m] — the arithmetic of the reference's int8-activation dots
