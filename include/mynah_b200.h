@@ -47,8 +47,11 @@ enum {
     MYNAH_B200_A8 = 1,         /* int8 activations, integer block dots (src/qmat.c:186-202,285-364)      */
     MYNAH_B200_FAST = 2,       /* large T: single fp16 tensor-core pass instead of the 3-term split      */
     MYNAH_B200_SCALAR = 4,     /* small T: force the scalar-FMA streaming kernel; for cross-checks        */
-    MYNAH_B200_MMA_SYNC = 8    /* small T: force the warp-level (mma.sync) streaming kernel; Q4_0/Q8_0 with
+    MYNAH_B200_MMA_SYNC = 8,   /* small T: force the warp-level (mma.sync) streaming kernel; Q4_0/Q8_0 with
                                   T <= 8 default to the tcgen05 streaming kernel                          */
+    MYNAH_B200_FEW_ROWS = 16   /* any T: the operand-plane contraction of a decoder position (weights as the
+                                  128-row side of the MMA, K slices over a thread-block cluster) — what the
+                                  AED decoder runs its linears on; here for cross-checks and timing          */
 };
 
 /* ---- backend presence and errors --------------------------------------------- */

@@ -22,7 +22,7 @@ LIB_PATH = os.path.join(_HERE, "libmynah_b200.so")
 
 F32, MYNAH_Q8, MYNAH_Q4 = 0, 1, 2
 GGML_Q4_0, GGML_Q8_0, GGML_Q4_K, GGML_Q6_K = 102, 108, 112, 114
-A16, A8, FAST, SCALAR, MMA_SYNC = 0, 1, 2, 4, 8
+A16, A8, FAST, SCALAR, MMA_SYNC, FEW_ROWS = 0, 1, 2, 4, 8, 16
 
 c_fp = C.POINTER(C.c_float)
 c_ip = C.POINTER(C.c_int)

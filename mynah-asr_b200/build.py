@@ -8,7 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libmynah_b200.so")
-SOURCES = ["util.cu", "gemm_tc.cu", "gemm_i8.cu", "dequant.cu", "elementwise.cu", "attention.cu", "attention_tc.cu", "subsampling.cu", "mel.cu",
+SOURCES = ["util.cu", "gemm_tc.cu", "gemm_i8.cu", "gemm_skinny.cu", "dequant.cu", "elementwise.cu", "attention.cu", "attention_tc.cu", "subsampling.cu", "mel.cu",
            "qgemv.cu", "qgemv_mma.cu", "qstream_tc.cu", "decoder.cu", "decoder_aed.cu", "align.cu", "vad.cu", "stream.cu", "model.cu", "loader.cu", "capi.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]

@@ -1167,7 +1167,7 @@ int mynah_b200_qmat_mul_device(const mynah_b200_qmat *q, const float *x, float *
         if (rc == 0) note_launch(2);
         return rc;
     }
-    if (T <= 16 && w.k <= 8192) {     // QMAT_SMALL_T / QMAT_K_MAX of the reference (src/qmat.c:180-181)
+    if (T <= 16 && w.k <= 8192 && !(flags & MYNAH_B200_FEW_ROWS)) {     // QMAT_SMALL_T / QMAT_K_MAX of the reference (src/qmat.c:180-181)
         if (w.tc_q && !(flags & (MYNAH_B200_SCALAR | MYNAH_B200_MMA_SYNC))) {
             int rc = 0;
             for (int t0 = 0; t0 < T && rc == 0; t0 += 8)
@@ -1196,7 +1196,8 @@ int mynah_b200_qmat_mul_device(const mynah_b200_qmat *q, const float *x, float *
     memset(&e, 0, sizeof(e));
     e.mode = OUT_F32; e.act = ACT_NONE; e.alpha = 1.f; e.out = out; e.ldo = w.n;
     GemmOperand A{hi, lo, w.k}, B{w.hi, w.lo, w.k};
-    if (rc == 0) rc = gemm_tc(A, B, e, T, w.n, w.k, (flags & MYNAH_B200_FAST) ? 1 : 3, q->status, q->stream);
+    if (rc == 0) rc = (flags & MYNAH_B200_FEW_ROWS) ? gemm_skinny(A, B, e, T, w.n, w.k, (flags & MYNAH_B200_FAST) ? 1 : 3, q->status, q->stream)
+                                                    : gemm_tc(A, B, e, T, w.n, w.k, (flags & MYNAH_B200_FAST) ? 1 : 3, q->status, q->stream);
     if (rc == 0) note_launch(2);
     cudaFreeAsync(hi, q->stream);
     cudaFreeAsync(lo, q->stream);
@@ -1401,7 +1402,7 @@ double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iter
         if (cudaMalloc((void **)&qx, (size_t)T * w.k) != cudaSuccess || cudaMalloc((void **)&sx, (size_t)T * 4) != cudaSuccess ||
             act_quant_rows(x, qx, sx, T, w.k, q->stream)) { cudaFree(x); cudaFree(out); cudaFree(qx); cudaFree(sx); set_error("qmat_time: setup failed"); return -1.0; }
     }
-    const bool small = !i8 && ((T <= 16 && w.k <= 8192) || (flags & MYNAH_B200_A8));
+    const bool small = !i8 && !(flags & MYNAH_B200_FEW_ROWS) && ((T <= 16 && w.k <= 8192) || (flags & MYNAH_B200_A8));
     if (!small && !i8) {
         if (!w.hi) { set_error("qmat_time: no operand planes"); cudaFree(x); cudaFree(out); return -1.0; }
         cudaMalloc(&hi, (size_t)T * w.k * 2); cudaMalloc(&lo, (size_t)T * w.k * 2);
@@ -1426,7 +1427,8 @@ double mynah_b200_qmat_time(const mynah_b200_qmat *q, int T, int flags, int iter
             memset(&e, 0, sizeof(e));
             e.mode = OUT_F32; e.alpha = 1.f; e.out = out; e.ldo = w.n;
             GemmOperand A{hi, lo, w.k}, B{w.hi, w.lo, w.k};
-            rc = gemm_tc(A, B, e, T, w.n, w.k, (flags & MYNAH_B200_FAST) ? 1 : 3, q->status, q->stream);
+            rc = (flags & MYNAH_B200_FEW_ROWS) ? gemm_skinny(A, B, e, T, w.n, w.k, (flags & MYNAH_B200_FAST) ? 1 : 3, q->status, q->stream)
+                                               : gemm_tc(A, B, e, T, w.n, w.k, (flags & MYNAH_B200_FAST) ? 1 : 3, q->status, q->stream);
         }
         if (it >= 0) note_launch();
     }

@@ -31,14 +31,18 @@ __device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) 
 }
 
 // Causal self-attention of one new position (src/decoder_aed.c:191-196 with attend, :117-131):
-// appends this step's k, v to the cache and attends over positions 0..p. Grid (H, B).
-// qkv [B, 3D] = (q | k | v) with biases already added; cache [B, max_len, D] each.
-__global__ void aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, float *__restrict__ cv,
-                                     const int *__restrict__ pd, int max_len, int D, int dk, H16 out) {
+// appends this step's k, v to the cache and attends over positions 0..p. Grid (H, B), 128 threads.
+// qkv [B, 3D] = (q | k | v) with biases already added; cache [B, max_len, D] each. dk is a multiple of 4.
+// Scores: a warp takes a key at a time, a lane four consecutive elements of it (one 16-byte load; four keys in
+// flight). Context: warp w sums the keys j = w, w + 4, ... for the lane's four columns; the four partial sums are
+// added in warp order.
+__global__ void __launch_bounds__(128)
+aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, float *__restrict__ cv,
+                     const int *__restrict__ pd, int max_len, int D, int dk, H16 out) {
     extern __shared__ float sm[];
     const int p = *pd;
-    float *sc = sm, *q = sm + max_len, *red = q + dk;
-    const int h = blockIdx.x, b = blockIdx.y;
+    float *sc = sm, *q = sm + ((max_len + 3) & ~3), *red = q + dk, *part = red + 32;     // part: [4][dk]
+    const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float *row = qkv + (size_t)b * 3 * D + h * dk;
     float *K = ck + (size_t)b * max_len * D + h * dk, *V = cv + (size_t)b * max_len * D + h * dk;
     for (int i = threadIdx.x; i < dk; i += blockDim.x) {
@@ -48,35 +52,65 @@ __global__ void aed_self_attn_kernel(const float *__restrict__ qkv, float *__res
     }
     __syncthreads();
     const float scale = 1.0f / sqrtf((float)dk);
-    float m = -INFINITY;
-    for (int j = threadIdx.x; j <= p; j += blockDim.x) {
-        const float *kj = K + (size_t)j * D;
-        float s = 0.f;
-        for (int i = 0; i < dk; i++) s = fmaf(q[i], kj[i], s);
-        s *= scale;
-        sc[j] = s;
-        m = fmaxf(m, s);
+    for (int j0 = warp * 4; j0 <= p; j0 += 16) {
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int i0 = lane * 4; i0 < dk; i0 += 128) {
+            float4 k[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) k[u] = *reinterpret_cast<const float4 *>(K + (size_t)(j0 + u <= p ? j0 + u : p) * D + i0);
+            const float4 qq = *reinterpret_cast<const float4 *>(q + i0);
+#pragma unroll
+            for (int u = 0; u < 4; u++) s[u] = fmaf(qq.x, k[u].x, fmaf(qq.y, k[u].y, fmaf(qq.z, k[u].z, fmaf(qq.w, k[u].w, s[u]))));
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const float t = warp_sum(s[u]);
+            if (lane == 0 && j0 + u <= p) sc[j0 + u] = t * scale;
+        }
     }
+    __syncthreads();
+    float m = -INFINITY;
+    for (int j = threadIdx.x; j <= p; j += blockDim.x) m = fmaxf(m, sc[j]);
     m = block_reduce(m, red, true);
     float sum = 0.f;
     for (int j = threadIdx.x; j <= p; j += blockDim.x) { const float e = expf(sc[j] - m); sc[j] = e; sum += e; }
     sum = block_reduce(sum, red, false);
     const float inv = 1.0f / sum;
+    for (int c0 = lane * 4; c0 < dk; c0 += 128) {
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        int j = warp;
+        for (; j + 12 <= p; j += 16) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = *reinterpret_cast<const float4 *>(V + (size_t)(j + 4 * u) * D + c0);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float w = sc[j + 4 * u] * inv;
+                o.x = fmaf(w, v[u].x, o.x); o.y = fmaf(w, v[u].y, o.y); o.z = fmaf(w, v[u].z, o.z); o.w = fmaf(w, v[u].w, o.w);
+            }
+        }
+        for (; j <= p; j += 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(V + (size_t)j * D + c0);
+            const float w = sc[j] * inv;
+            o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+        }
+        *reinterpret_cast<float4 *>(part + warp * dk + c0) = o;
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < dk; i += blockDim.x) {
-        float o = 0.f;
-        for (int j = 0; j <= p; j++) o = fmaf(sc[j] * inv, V[(size_t)j * D + i], o);
+        const float t = ((part[i] + part[dk + i]) + part[2 * dk + i]) + part[3 * dk + i];
         __half hi, lo;
-        split_h16(o, hi, lo);
+        split_h16(t, hi, lo);
         out.hi[(size_t)b * D + h * dk + i] = hi;
         if (out.lo) out.lo[(size_t)b * D + h * dk + i] = lo;
     }
 }
 
 // Cross-attention of one query per utterance over its T_b projected encoder frames
-// (src/decoder_aed.c:199-202). Grid (H, B), 256 threads. kv: planes [sum T, 2D] = (K | V) of this layer,
+// (src/decoder_aed.c:199-202). Grid (H, B), 512 threads. kv: planes [sum T, 2D] = (K | V) of this layer,
 // fp16 hi (+ lo * 2^-11 when present). q [B, D] f32 with bias. dk is a multiple of 4.
 // Scores: a warp takes four key rows at a time, a lane four consecutive elements of each (8-byte loads,
-// eight in flight per lane). Context: a thread owns two adjacent columns and every fourth key.
+// eight in flight per lane). Context: a warp owns every sixteenth key, a lane four adjacent columns.
 __device__ __forceinline__ float4 ld_h4(const __half *hi, const __half *lo, size_t o) {
     const uint2 a = *reinterpret_cast<const uint2 *>(hi + o);
     const float2 a0 = __half22float2(*reinterpret_cast<const __half2 *>(&a.x)), a1 = __half22float2(*reinterpret_cast<const __half2 *>(&a.y));
@@ -88,18 +122,19 @@ __device__ __forceinline__ float4 ld_h4(const __half *hi, const __half *lo, size
     }
     return r;
 }
-__global__ void __launch_bounds__(256)
+static constexpr int CROSS_WARPS = 16;
+__global__ void __launch_bounds__(CROSS_WARPS * 32)
 aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ kv_hi, const __half *__restrict__ kv_lo,
                       const int *__restrict__ enc_off, const int *__restrict__ enc_len, int max_T, int D, int dk, H16 out) {
     extern __shared__ float sm[];
-    float *sc = sm, *q = sm + ((max_T + 3) & ~3), *red = q + dk, *part = red + 32;     // part: [4][dk] partial outputs
+    float *sc = sm, *q = sm + ((max_T + 3) & ~3), *red = q + dk, *part = red + 32;     // part: [CROSS_WARPS][dk] partial outputs
     const int h = blockIdx.x, b = blockIdx.y;
     const int T = enc_len[b], lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const size_t r0 = (size_t)enc_off[b], ld = 2 * (size_t)D;
     for (int i = threadIdx.x; i < dk; i += blockDim.x) q[i] = qm[(size_t)b * D + h * dk + i];
     __syncthreads();
     const float scale = 1.0f / sqrtf((float)dk);
-    for (int j0 = warp * 4; j0 < T; j0 += 32) {
+    for (int j0 = warp * 4; j0 < T; j0 += 4 * CROSS_WARPS) {
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         for (int i0 = lane * 4; i0 < dk; i0 += 128) {
             float4 k[4];
@@ -126,41 +161,33 @@ aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ k
     for (int j = threadIdx.x; j < T; j += blockDim.x) { const float e = expf(sc[j] - m); sc[j] = e; sum += e; }
     sum = block_reduce(sum, red, false);
     const float inv = 1.0f / sum;
-    // context: thread (g, c) sums the keys j = g, g + 4, ... of columns 2c, 2c+1; the four partials are added in order
-    const int nc = dk >> 1, g = threadIdx.x / nc, c = threadIdx.x % nc;
-    if (g < 4 && 4 * nc <= (int)blockDim.x) {
-        float o0 = 0.f, o1 = 0.f;
-        for (int j = g; j < T; j += 4) {
-            const size_t a = (r0 + j) * ld + D + h * dk + 2 * c;
-            float2 v = __half22float2(*reinterpret_cast<const __half2 *>(kv_hi + a));
-            if (kv_lo) {
-                const float2 l = __half22float2(*reinterpret_cast<const __half2 *>(kv_lo + a));
-                v.x = fmaf(l.x, H16_LO_INV, v.x); v.y = fmaf(l.y, H16_LO_INV, v.y);
+    // context: warp w sums the keys j = w, w + CROSS_WARPS, ... for the lane's four columns (8-byte loads of each plane,
+    // four keys in flight); the partial sums are added in warp order
+    for (int c0 = lane * 4; c0 < dk; c0 += 128) {
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        const size_t col = D + h * dk + c0;
+        int j = warp;
+        for (; j + 3 * CROSS_WARPS < T; j += 4 * CROSS_WARPS) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = ld_h4(kv_hi, kv_lo, (r0 + j + CROSS_WARPS * u) * ld + col);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float w = sc[j + CROSS_WARPS * u] * inv;
+                o.x = fmaf(w, v[u].x, o.x); o.y = fmaf(w, v[u].y, o.y); o.z = fmaf(w, v[u].z, o.z); o.w = fmaf(w, v[u].w, o.w);
             }
-            const float p = sc[j] * inv;
-            o0 = fmaf(p, v.x, o0); o1 = fmaf(p, v.y, o1);
         }
-        part[g * dk + 2 * c] = o0; part[g * dk + 2 * c + 1] = o1;
-    } else if (4 * nc > (int)blockDim.x) {               // wide heads: one group only
-        for (int cc = threadIdx.x; cc < nc; cc += blockDim.x) {
-            float o0 = 0.f, o1 = 0.f;
-            for (int j = 0; j < T; j++) {
-                const size_t a = (r0 + j) * ld + D + h * dk + 2 * cc;
-                float2 v = __half22float2(*reinterpret_cast<const __half2 *>(kv_hi + a));
-                if (kv_lo) {
-                    const float2 l = __half22float2(*reinterpret_cast<const __half2 *>(kv_lo + a));
-                    v.x = fmaf(l.x, H16_LO_INV, v.x); v.y = fmaf(l.y, H16_LO_INV, v.y);
-                }
-                const float p = sc[j] * inv;
-                o0 = fmaf(p, v.x, o0); o1 = fmaf(p, v.y, o1);
-            }
-            part[2 * cc] = o0; part[2 * cc + 1] = o1;
-            for (int gg = 1; gg < 4; gg++) { part[gg * dk + 2 * cc] = 0.f; part[gg * dk + 2 * cc + 1] = 0.f; }
+        for (; j < T; j += CROSS_WARPS) {
+            const float4 v = ld_h4(kv_hi, kv_lo, (r0 + j) * ld + col);
+            const float w = sc[j] * inv;
+            o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
         }
+        *reinterpret_cast<float4 *>(part + warp * dk + c0) = o;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < dk; i += blockDim.x) {
-        const float t = ((part[i] + part[dk + i]) + part[2 * dk + i]) + part[3 * dk + i];
+        float t = part[i];
+        for (int w = 1; w < CROSS_WARPS; w++) t += part[w * dk + i];
         __half hi, lo;
         split_h16(t, hi, lo);
         out.hi[(size_t)b * D + h * dk + i] = hi;
@@ -202,8 +229,7 @@ static GemmEpilogue aed_epi(int mode, int act, float alpha, const float *bias, f
 size_t Model::aed_bytes(int total_T, int B, int max_len) const {
     const size_t D = aed_d, F = aed_ffn, L = aed_layers.size();
     return (size_t)total_T * (d_out * 4 + D * 4 + L * 2 * D * 4) + L * 2 * (size_t)B * max_len * D * 4 +
-           (size_t)B * (D * 24 + 3 * D * 4 + F * 4 + (size_t)aed_vocab * 4) + (size_t)B * (max_len + 64) * 8 + (1 << 20) +
-           (size_t)((B + GEMM_BM - 1) / GEMM_BM) * (device_sm_count() + 8) * GEMM_BM * GEMM_SPLIT_BN * 4 + 65536;   // split-K slices
+           (size_t)B * (D * 24 + 3 * D * 4 + F * 4 + (size_t)aed_vocab * 4) + (size_t)B * (max_len + 64) * 8 + (1 << 20);
 }
 
 int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const std::vector<std::vector<int>> &prompts, int eos,
@@ -258,21 +284,6 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     int *st = ws.get<int>(6 * (size_t)B + 4), *best = ws.get<int>(B), *d_prompts = ws.get<int>((size_t)B * max_prompt);
     int *d_tokens = ws.get<int>((size_t)B * capn), *d_off = ws.get<int>(2 * (size_t)B);
     if (!sk || !x || !qkv || !q || !logits || !xn.hi || !att.hi || !ff.hi || !st || !best || !d_prompts || !d_tokens || !d_off) return -1;
-    // With B rows the contractions of a position have far fewer output tiles than the device has SMs; split-K lets
-    // all of them pull the weights. The slice count depends on the weight's shape alone, so a row's bits do not
-    // depend on B.
-    const int sms = device_sm_count();
-    size_t part_floats = 0, n_counters = 0;
-    auto split_need = [&](const QWeight &w) {
-        const size_t pf = gemm_split_part_floats(B, w.n, w.k, sms), nc = gemm_split_counters(B, w.n);
-        part_floats = pf > part_floats ? pf : part_floats;
-        n_counters = nc > n_counters ? nc : n_counters;
-    };
-    for (const AedLayer &A : aed_layers) { split_need(A.sqkv); split_need(A.so); split_need(A.cq); split_need(A.co); split_need(A.ff1); split_need(A.ff2); }
-    split_need(aed_head);
-    GemmSplit split{0, ws.get<float>(part_floats), ws.get<int>(n_counters)};
-    if (!split.part || !split.counters) return -1;
-    MB_CUDA(cudaMemsetAsync(split.counters, 0, n_counters * sizeof(int), stream));
     std::vector<int> hst(6 * (size_t)B + 4, 0), hp((size_t)B * max_prompt, 0), ho(2 * (size_t)B);
     for (int b = 0; b < B; b++) {
         hst[b] = prompts[b][0];                              // cur
@@ -285,9 +296,9 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     MB_CUDA(cudaMemcpyAsync(st, hst.data(), hst.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
     MB_CUDA(cudaMemcpyAsync(d_prompts, hp.data(), hp.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
     MB_CUDA(cudaMemcpyAsync(d_off, ho.data(), ho.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
-    const size_t self_smem = ((size_t)max_len + dk + 32) * sizeof(float);
-    const int cross_threads = 256;
-    const size_t cross_smem = ((size_t)max_T + 4 + 5 * (size_t)dk + 32) * sizeof(float);
+    const size_t self_smem = ((size_t)max_len + 4 + 5 * (size_t)dk + 32) * sizeof(float);
+    const int cross_threads = CROSS_WARPS * 32;
+    const size_t cross_smem = ((size_t)max_T + 4 + (1 + CROSS_WARPS) * (size_t)dk + 32) * sizeof(float);
     if (self_smem > 200 * 1024 || cross_smem > 200 * 1024) { set_error("aed_decode: sequence too long for the attention kernels"); return -1; }
     MB_CUDA(cudaFuncSetAttribute(aed_self_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)self_smem));
     MB_CUDA(cudaFuncSetAttribute(aed_cross_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)cross_smem));
@@ -301,20 +312,20 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
             const AedLayer &A = aed_layers[l];
             float *K = sk + (size_t)(2 * l) * B * max_len * D, *Vc = K + (size_t)B * max_len * D;
             if (layer_norm(x, A.ln_self_w, A.ln_self_b, nullptr, xn, B, D, 0, stream)) return -1;
-            if (gemm(xn, D, A.sqkv, aed_epi(OUT_F32, ACT_NONE, 1.f, A.sqkv_b, qkv, 3 * D), B, &split)) return -1;
+            if (gemm(xn, D, A.sqkv, aed_epi(OUT_F32, ACT_NONE, 1.f, A.sqkv_b, qkv, 3 * D), B, true)) return -1;
             aed_self_attn_kernel<<<dim3(H, B), 128, self_smem, stream>>>(qkv, K, Vc, pd, max_len, D, dk, att);
-            if (gemm(att, D, A.so, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.so_b, x, D), B, &split)) return -1;
+            if (gemm(att, D, A.so, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.so_b, x, D), B, true)) return -1;
             if (layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream)) return -1;
-            if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B, &split)) return -1;
+            if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B, true)) return -1;
             aed_cross_attn_kernel<<<dim3(H, B), cross_threads, cross_smem, stream>>>(q, ckv[l].hi, ckv[l].lo, d_off, d_off + B, max_T, D, dk, att);
-            if (gemm(att, D, A.co, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.co_b, x, D), B, &split)) return -1;
+            if (gemm(att, D, A.co, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.co_b, x, D), B, true)) return -1;
             if (layer_norm(x, A.ln_ffn_w, A.ln_ffn_b, nullptr, xn, B, D, 0, stream)) return -1;
-            if (gemm(xn, D, A.ff1, aed_epi(OUT_H16, ACT_RELU, 1.f, A.ff1_b, nullptr, 0, ff, F), B, &split)) return -1;
-            if (gemm(ff, F, A.ff2, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.ff2_b, x, D), B, &split)) return -1;
+            if (gemm(xn, D, A.ff1, aed_epi(OUT_H16, ACT_RELU, 1.f, A.ff1_b, nullptr, 0, ff, F), B, true)) return -1;
+            if (gemm(ff, F, A.ff2, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.ff2_b, x, D), B, true)) return -1;
         }
         // the head is evaluated at prompt positions too (its result is ignored there): one graph for all positions
         if (layer_norm(x, aed_fin_w, aed_fin_b, nullptr, xn, B, D, 0, stream)) return -1;
-        if (gemm(xn, D, aed_head, aed_epi(OUT_F32, ACT_NONE, 1.f, aed_head_b, logits, V), B, &split)) return -1;
+        if (gemm(xn, D, aed_head, aed_epi(OUT_F32, ACT_NONE, 1.f, aed_head_b, logits, V), B, true)) return -1;
         if (argmax_rows(logits, V, nullptr, B, V, best, stream)) return -1;
         aed_select_kernel<<<1, ((B + 31) / 32) * 32, 0, stream>>>(best, eos, capn, B, st, d_prompts, max_prompt, d_tokens);
         MB_CUDA(cudaGetLastError());

@@ -33,46 +33,16 @@ struct GemmEpilogue {
 
 static constexpr int GEMM_BM = 128;      // rows of an output tile (one tcgen05.mma M)
 
-// Split-K for contractions with few rows and few output tiles (one decoder position): `splits` CTAs share an output
-// tile, each sums a K slice into `part` (f32, [unit][128][tile width]); the last to arrive (counted in `counters`, one int
-// per tile, zero between launches) adds the slices in slice order and applies the fused tail, so the result does not
-// depend on which CTA came last. splits <= 1: off.
-struct GemmSplit {
-    int splits;
-    float *part;
-    int *counters;
-};
-static constexpr int GEMM_SPLIT_BN = 64;                 // tile width of the split-K path
-// K slices for an [*, N] x [N, K] contraction on `sms` SMs: a function of the weight's shape alone (never of the row
-// count), so a row's bits do not depend on how many rows share the launch.
-inline int gemm_split_slices(int N, int K, int sms) {
-    const int tiles = (N + GEMM_SPLIT_BN - 1) / GEMM_SPLIT_BN, num_k = K / 64;
-    int s = 1;
-    while (tiles * s * 2 <= sms && s * 2 <= 16 && num_k % (s * 2) == 0 && num_k / (s * 2) >= 2) s *= 2;
-    return s;
-}
-// floats of `part` / ints of `counters` that M rows of such a contraction need
-inline size_t gemm_split_part_floats(int M, int N, int K, int sms) {
-    const size_t tiles = (size_t)((N + GEMM_SPLIT_BN - 1) / GEMM_SPLIT_BN) * ((M + GEMM_BM - 1) / GEMM_BM);
-    const int s = gemm_split_slices(N, K, sms);
-    return s > 1 ? tiles * s * GEMM_BM * GEMM_SPLIT_BN : 0;       // at most ceil(M / 128) * sms * 128 * 64
-}
-inline size_t gemm_split_counters(int M, int N) {
-    return (size_t)((N + GEMM_SPLIT_BN - 1) / GEMM_SPLIT_BN) * ((M + GEMM_BM - 1) / GEMM_BM);
-}
-
 #ifdef __CUDACC__
 // Work units of the persistent loop. Whole waves of gridDim.x tiles come first; the tiles of the last, partial
 // wave are cut into 2 or 4 column strips when that still fits one wave, so that the tail costs a half or a
 // quarter of a tile time instead of a whole one (752 tiles on 148 CTAs: 5.25 instead of 6 tile times). A strip
 // runs the same instruction sequence over its columns as the whole tile would, so no output bit depends on it.
 struct GemmUnits {
-    int tiles_n, full, split, total, slices;  // full: tiles in whole waves; split: strips per tail tile; slices: K slices per tile
-    __device__ GemmUnits(int M, int N, int BN_, int ctas, int slices_ = 1) {
+    int tiles_n, full, split, total;          // full: tiles in whole waves; split: strips per tail tile
+    __device__ GemmUnits(int M, int N, int BN_, int ctas) {
         tiles_n = (N + BN_ - 1) / BN_;
-        slices = slices_;
         const int tiles = tiles_n * ((M + GEMM_BM - 1) / GEMM_BM);
-        if (slices > 1) { full = tiles * slices; split = 1; total = full; return; }   // split-K: no column strips
         full = tiles / ctas * ctas;
         const int rem = tiles - full;
         split = 1;
@@ -88,15 +58,6 @@ struct GemmUnits {
         width = u >= full ? BN_ / split : BN_;
         m0 = (tile / tiles_n) * GEMM_BM;
         n0 = (tile % tiles_n) * BN_ + sub * width;
-    }
-    // split-K form: unit u = tile * slices + slice (for slices == 1 the same as above with slice = 0)
-    __device__ void at(int u, int BN_, int &m0, int &n0, int &width, int &slice) const {
-        if (slices <= 1) { slice = 0; at(u, BN_, m0, n0, width); return; }
-        const int tile = u / slices;
-        slice = u % slices;
-        width = BN_;
-        m0 = (tile / tiles_n) * GEMM_BM;
-        n0 = (tile % tiles_n) * BN_;
     }
 };
 
@@ -167,15 +128,98 @@ __device__ __forceinline__ bool gemm_epilogue_row(const GemmEpilogue &ep, float 
     }
     return fits;
 }
+
+// ---- the same fused tail for a 32 x 32 block (32 rows from m_base, columns [nb, nb + 32)) held one row per lane.
+// Stored row by row, every store instruction of a warp touches 32 different 128-byte lines with 16 bytes each, and the
+// load/store unit spends one cycle per line. Here the block is turned through 4 KB of shared memory (float4 columns
+// XOR-swizzled by the row: no bank conflicts either way) so that an instruction covers four whole lines: eight lanes
+// take the eight float4 of one row. Values and operation order per element are those of gemm_epilogue_row.
+static constexpr int GEMM_BLOCK_STAGE_FLOATS = 32 * 32;           // shared memory per epilogue warp
+
+// true if the block form can be used for every full-width chunk of this contraction (pointer and stride alignment)
+__device__ __forceinline__ bool gemm_block_ok(const GemmEpilogue &ep) {
+    bool ok = !ep.bias || (reinterpret_cast<uintptr_t>(ep.bias) & 15) == 0;
+    if (ep.mode != OUT_H16) ok = ok && (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0 && (ep.ldo & 3) == 0;
+    if (ep.mode == OUT_H16 || ep.mode == OUT_F32_H16)
+        ok = ok && (reinterpret_cast<uintptr_t>(ep.out_hi) & 7) == 0 && (reinterpret_cast<uintptr_t>(ep.out_lo) & 7) == 0 && (ep.ldh & 3) == 0;
+    return ok;
+}
+
+// residual values of this lane's eight float4 positions (rows i * 4 + lane / 8, columns 4 (lane % 8) ..), asked for
+// before the accumulator is read so that the loads are in flight meanwhile
+__device__ __forceinline__ void gemm_block_prefetch(const GemmEpilogue &ep, int m_base, int M, int nb, int lane, float4 (&res)[8]) {
+    if (ep.mode != OUT_RESID) return;
+    const float *o = ep.out + (size_t)(m_base + (lane >> 3)) * ep.ldo + nb + (lane & 7) * 4;
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+        res[i] = m_base + i * 4 + (lane >> 3) < M ? *reinterpret_cast<const float4 *>(o + (size_t)i * 4 * ep.ldo) : make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+__device__ __forceinline__ float gemm_act(const GemmEpilogue &ep, float x) {
+    if (ep.act == ACT_SILU) return x * __frcp_rn(1.0f + __expf(-x));
+    if (ep.act == ACT_RELU) return fmaxf(x, 0.0f);
+    return x;
+}
+
+// this lane's row, columns [16 h, 16 h + 16) of the block, into the turning buffer
+__device__ __forceinline__ void gemm_block_stage(const float (&v)[16], int h, float *stage, int lane) {
+    float4 *s4 = reinterpret_cast<float4 *>(stage);
+#pragma unroll
+    for (int j = 0; j < 4; j++) s4[lane * 8 + ((4 * h + j) ^ (lane & 7))] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+}
+
+// after both halves were staged: the fused tail and the stores
+__device__ __forceinline__ bool gemm_block_store(const GemmEpilogue &ep, const float4 (&res)[8], int m_base, int M,
+                                                 int nb, float *stage, int lane) {
+    float4 *s4 = reinterpret_cast<float4 *>(stage);
+    __syncwarp();
+    const int q = lane & 7, r0 = lane >> 3, col = nb + q * 4;
+    const float4 b = ep.bias ? *reinterpret_cast<const float4 *>(ep.bias + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+    bool fits = true;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int r = i * 4 + r0, m = m_base + r;
+        float4 t = s4[r * 8 + (q ^ (r & 7))];
+        if (ep.bias) { t.x += b.x; t.y += b.y; t.z += b.z; t.w += b.w; }
+        t.x = gemm_act(ep, t.x); t.y = gemm_act(ep, t.y); t.z = gemm_act(ep, t.z); t.w = gemm_act(ep, t.w);
+        if (m >= M) continue;
+        if (ep.mode != OUT_H16) {
+            float4 *o = reinterpret_cast<float4 *>(ep.out + (size_t)m * ep.ldo + col);
+            if (ep.mode == OUT_RESID) {
+                float4 a = res[i];
+                a.x += ep.alpha * t.x; a.y += ep.alpha * t.y; a.z += ep.alpha * t.z; a.w += ep.alpha * t.w;
+                *o = a;
+            } else {
+                *o = t;
+            }
+        }
+        if (ep.mode == OUT_H16 || ep.mode == OUT_F32_H16) {
+            __half h0, h1, h2, h3, l0, l1, l2, l3;
+            fits &= split_h16(t.x, h0, l0);
+            fits &= split_h16(t.y, h1, l1);
+            fits &= split_h16(t.z, h2, l2);
+            fits &= split_h16(t.w, h3, l3);
+            const size_t off = (size_t)m * ep.ldh + col;
+            const __half2 ha = __halves2half2(h0, h1), hb = __halves2half2(h2, h3), la = __halves2half2(l0, l1), lb = __halves2half2(l2, l3);
+            *reinterpret_cast<uint2 *>(ep.out_hi + off) = make_uint2(*reinterpret_cast<const uint32_t *>(&ha), *reinterpret_cast<const uint32_t *>(&hb));
+            if (ep.out_lo) *reinterpret_cast<uint2 *>(ep.out_lo + off) = make_uint2(*reinterpret_cast<const uint32_t *>(&la), *reinterpret_cast<const uint32_t *>(&lb));
+        }
+    }
+    __syncwarp();                                                   // the stage is free for the next block
+    return fits;
+}
 #endif
 
 // C = A * B^T on tcgen05 tensor cores; nterms 1 (hi*hi) or 3 (hi*hi + lo*hi + hi*lo).
 // K must be a multiple of 64. status: device int receiving a non-zero code if a
 // bounded wait inside the kernel ran out.
-// split: optional split-K workspace (see GemmSplit; the slice count is gemm_split_slices(N, K, SMs), `splits` of the
-// argument is ignored); null = every tile sums its whole K.
 int gemm_tc(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, int M, int N, int K, int nterms,
-            int *status, cudaStream_t stream, const GemmSplit *split = nullptr);
+            int *status, cudaStream_t stream);
+
+// The same contraction for a handful of rows (a decoder position): gemm_skinny.cu. X: [M, K] activation planes, W: [N, K]
+// weight planes; K slices over the CTAs of a cluster, added in slice order (the count depends on N and K alone).
+int gemm_skinny(const GemmOperand &X, const GemmOperand &W, const GemmEpilogue &ep, int M, int N, int K, int nterms, int *status,
+                cudaStream_t stream);
 
 // Integer contraction on the tensor cores (gemm_i8.cu): acc[m,n] = sum_k a[m,k] * b[n,k] in int32 (exact), then
 // v = (float)acc * col_scale[n] * row_scale[m] — the arithmetic of the reference's int8-activation dots

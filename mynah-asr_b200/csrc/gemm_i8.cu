@@ -34,9 +34,10 @@ struct I8Cfg {
     static constexpr int A_BYTES = GEMM_BM * I8_BK;
     static constexpr int B_BYTES = BN * I8_BK;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES_RAW = (I8_SMEM_LIMIT - 2048) / STAGE_BYTES;
+    static constexpr int EPI_BYTES = I8_EPI_WARPS * GEMM_BLOCK_STAGE_FLOATS * 4;   // the epilogue warps' turning buffers
+    static constexpr int STAGES_RAW = (I8_SMEM_LIMIT - 2048 - EPI_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2048;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 2048;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
     static_assert(TMEM_COLS <= 512, "TMEM has 512 columns");
 };
@@ -64,7 +65,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *tiles = smem;
-    uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    float *epi_stage = reinterpret_cast<float *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
     uint64_t *empty_bar = full_bar + Cfg::STAGES;
     uint64_t *acc_full = empty_bar + Cfg::STAGES;      // [2] MMA -> epilogue
     uint64_t *acc_empty = acc_full + 2;                // [2] epilogue -> MMA
@@ -147,6 +149,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int row = lg * 32 + lane;
         int lt = 0;
         bool fits = true;
+        const bool blk_ok = gemm_block_ok(ep);
+        float *stage = epi_stage + (warp - 2) * GEMM_BLOCK_STAGE_FLOATS;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
             int m0, n0, width;
             units.at(tile, BN, m0, n0, width);
@@ -162,10 +166,27 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (num_k > 0) {
 #pragma unroll 1
                 for (int c = half; c < width / 32; c += 2) {
+                    const int nb = n0 + c * 32;
+                    const bool blk = blk_ok && nb + 32 <= N;            // warp-uniform
+                    float4 res[8];
+                    if (blk) gemm_block_prefetch(ep, m0 + lg * 32, M, nb, lane, res);
+                    if (blk) {
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            float v[16];
+                            tc_ld16(acc + (uint32_t)(c * 32 + h * 16), v);
+                            tc_wait_ld();
+#pragma unroll
+                            for (int j = 0; j < 16; j++)     // (float)int32 * ws * sx, left to right (src/qmat.c:299)
+                                v[j] = __fmul_rn(__fmul_rn(__int2float_rn(__float_as_int(v[j])), col_scale[nb + h * 16 + j]), sx);
+                            gemm_block_stage(v, h, stage, lane);
+                        }
+                        fits &= gemm_block_store(ep, res, m0 + lg * 32, M, nb, stage, lane);
+                        continue;
+                    }
                     float v[32];
                     tc_ld32(acc + (uint32_t)(c * 32), v);
                     tc_wait_ld();
-                    const int nb = n0 + c * 32;
                     if (m < M && nb < N) {
 #pragma unroll
                         for (int j = 0; j < 32; j++) {

@@ -39,9 +39,10 @@ struct GemmCfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = NPLANES * (A_BYTES + B_BYTES);
-    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048) / STAGE_BYTES;
+    static constexpr int EPI_BYTES = EPI_WARPS * GEMM_BLOCK_STAGE_FLOATS * 4;      // the epilogue warps' turning buffers
+    static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048 - EPI_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2048;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 2048;
     // NTERMS == 3 keeps a second accumulator for the cross terms (lo*hi + hi*lo);
     // everything is double-buffered so the epilogue of tile i overlaps the MMAs of tile i+1
     static constexpr int ACC_COLS = NTERMS == 1 ? BN : 2 * BN;
@@ -55,22 +56,21 @@ template <int BN, int NTERMS>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant__ CUtensorMap tmA_lo,
                const __grid_constant__ CUtensorMap tmB_hi, const __grid_constant__ CUtensorMap tmB_lo,
-               const GemmEpilogue ep, const int M, const int N, const int K, int *status, const GemmSplit sk) {
+               const GemmEpilogue ep, const int M, const int N, const int K, int *status) {
     using Cfg = GemmCfg<BN, NTERMS>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *tiles = smem;
-    uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    float *epi_stage = reinterpret_cast<float *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t *full_bar = reinterpret_cast<uint64_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
     uint64_t *empty_bar = full_bar + Cfg::STAGES;
     uint64_t *acc_full = empty_bar + Cfg::STAGES;      // [2] MMA -> epilogue
     uint64_t *acc_empty = acc_full + 2;                // [2] epilogue -> MMA
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // split-K (sk.splits > 1): a unit is (tile, K slice); unit u = tile * splits + slice, so the slices of a tile run side by side
-    const int splits = sk.splits > 1 ? sk.splits : 1;
-    const int num_k = K / BK / splits;                // k-blocks per unit
-    const GemmUnits units(M, N, BN, gridDim.x, splits);
+    const int num_k = K / BK;
+    const GemmUnits units(M, N, BN, gridDim.x);
     const int total = units.total;
 
     if (threadIdx.x == 0) {
@@ -92,10 +92,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
         int it = 0;                                    // k-blocks issued so far (ring position)
         bool ok = true;
         for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-            int m0, n0, width, kb0;
-            units.at(tile, BN, m0, n0, width, kb0);          // a strip still loads BN rows of B: the MMAs read the first `width`
-            kb0 *= num_k;
-            for (int kb = kb0; kb < kb0 + num_k; kb++, it++) {
+            int m0, n0, width;
+            units.at(tile, BN, m0, n0, width);               // a strip still loads BN rows of B: the MMAs read the first `width`
+            for (int kb = 0; kb < num_k; kb++, it++) {
                 const int s = it % Cfg::STAGES;
                 const uint32_t ph = (it / Cfg::STAGES) & 1;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1)) { ok = false; break; }
@@ -119,8 +118,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
         int it = 0, lt = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, lt++) {
-            int m0, n0, width, slice;
-            units.at(tile, BN, m0, n0, width, slice);
+            int m0, n0, width;
+            units.at(tile, BN, m0, n0, width);
             const uint32_t idesc = umma_idesc_f16(BM, width);
             const int buf = lt & 1;
             const uint32_t acc = tmem_base + buf * Cfg::ACC_COLS;
@@ -158,9 +157,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
         const int row = lg * 32 + lane;
         int lt = 0;
         bool fits = true;
+        const bool blk_ok = gemm_block_ok(ep);
+        float *stage = epi_stage + (warp - 2) * GEMM_BLOCK_STAGE_FLOATS;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
-            int m0, n0, width, slice;
-            units.at(tile, BN, m0, n0, width, slice);
+            int m0, n0, width;
+            units.at(tile, BN, m0, n0, width);
             const int buf = lt & 1;
             const uint32_t acc = tmem_base + buf * Cfg::ACC_COLS + ((uint32_t)(lg * 32) << 16);
             if (!mbar_wait(&acc_full[buf], (lt >> 1) & 1)) {
@@ -172,6 +173,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
             if (num_k > 0) {
 #pragma unroll 1
                 for (int c = half; c < width / 32; c += 2) {
+                    const int nb = n0 + c * 32;
+                    const bool blk = blk_ok && nb + 32 <= N;            // warp-uniform
+                    float4 res[8];
+                    if (blk) gemm_block_prefetch(ep, m0 + lg * 32, M, nb, lane, res);
+                    if (blk) {
+                        // two halves of 16 columns: fewer live registers than the whole 32 x (hi*hi, cross) at once
+#pragma unroll
+                        for (int h = 0; h < 2; h++) {
+                            float v[16];
+                            tc_ld16(acc + (uint32_t)(c * 32 + h * 16), v);
+                            if (NTERMS > 1) {
+                                float x[16];
+                                tc_ld16(acc + (uint32_t)(BN + c * 32 + h * 16), x);
+                                tc_wait_ld();
+#pragma unroll
+                                for (int j = 0; j < 16; j++) v[j] = fmaf(x[j], H16_LO_INV, v[j]);
+                            } else {
+                                tc_wait_ld();
+                            }
+                            gemm_block_stage(v, h, stage, lane);
+                        }
+                        fits &= gemm_block_store(ep, res, m0 + lg * 32, M, nb, stage, lane);
+                        continue;
+                    }
                     float v[32];
                     tc_ld32(acc + (uint32_t)(c * 32), v);
                     if (NTERMS > 1) {
@@ -183,15 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
                     } else {
                         tc_wait_ld();
                     }
-                    const int nb = n0 + c * 32;
-                    if (splits > 1) {
-                        // this slice's sums of 32 columns of row m, for whichever warp adds the slices up
-                        if (m < M) {
-                            float4 *pp = reinterpret_cast<float4 *>(sk.part + ((size_t)tile * BM + row) * BN + c * 32);
-#pragma unroll
-                            for (int j = 0; j < 8; j++) __stcg(pp + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
-                        }
-                    } else if (m < M && nb < N) {
+                    if (m < M && nb < N) {
                         fits &= gemm_epilogue_row(ep, v, m, nb, N);
                     }
                 }
@@ -199,38 +216,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
-            if (splits > 1) {
-                // every epilogue warp of every slice counts in once its part is visible; the warp that completes the
-                // count adds the slices in slice order (so the sum does not depend on who came last) and runs the tail
-                const int t = tile / splits;
-                __threadfence();
-                __syncwarp();
-                int last = 0;
-                if (lane == 0) last = atomicAdd(sk.counters + t, 1) == splits * EPI_WARPS - 1;
-                last = __shfl_sync(0xffffffffu, last, 0);
-                if (last) {
-                    __threadfence();
-                    if (lane == 0) sk.counters[t] = 0;                 // ready for the next launch
-                    const float *base = sk.part + (size_t)t * splits * BM * BN;
-                    for (int r = lane; r < BM && m0 + r < M; r += 32) {
-#pragma unroll 1
-                        for (int c = 0; c < BN / 32 && n0 + c * 32 < N; c++) {
-                            float v[32];
-#pragma unroll 1
-                            for (int s = 0; s < splits; s++) {
-                                const float4 *pp = reinterpret_cast<const float4 *>(base + ((size_t)s * BM + r) * BN + c * 32);
-#pragma unroll
-                                for (int j = 0; j < 8; j++) {
-                                    const float4 q = __ldcg(pp + j);
-                                    if (s == 0) { v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w; }
-                                    else { v[4 * j] += q.x; v[4 * j + 1] += q.y; v[4 * j + 2] += q.z; v[4 * j + 3] += q.w; }
-                                }
-                            }
-                            fits &= gemm_epilogue_row(ep, v, m0 + r, n0 + c * 32, N);
-                        }
-                    }
-                }
-            }
         }
         if (!fits) atomicCAS(status, ST_OK, ST_RANGE);
     }
@@ -277,7 +262,7 @@ static int make_map(CUtensorMap *m, const __half *base, int rows, int K, int ld,
 
 template <int BN, int NTERMS>
 static int launch(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, int M, int N, int K,
-                  int *status, cudaStream_t stream, const GemmSplit &sk = GemmSplit{1, nullptr, nullptr}) {
+                  int *status, cudaStream_t stream) {
     using Cfg = GemmCfg<BN, NTERMS>;
     CUtensorMap ta_hi, ta_lo, tb_hi, tb_lo;
     if (make_map(&ta_hi, A.hi, M, K, A.ld, BM)) return -1;
@@ -299,25 +284,17 @@ static int launch(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue
     // fewer tiles than SMs: the kernel cuts them into column strips (GemmUnits) when the grid leaves room
     const int total = cdiv(N, BN) * cdiv(M, BM), strips = BN % 128 == 0 ? 4 : BN % 64 == 0 ? 2 : 1;
     dim3 grid(total >= sms ? sms : total * strips <= sms ? total * strips : total * 2 <= sms && strips >= 2 ? total * 2 : total);
-    if (sk.splits > 1) grid.x = total * sk.splits < sms ? total * sk.splits : sms;
     gemm_tc_kernel<BN, NTERMS><<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(ta_hi, ta_lo, tb_hi, tb_lo, ep, M,
-                                                                               N, K, status, sk);
+                                                                               N, K, status);
     MB_CUDA(cudaGetLastError());
     return 0;
 }
 
 int gemm_tc(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, int M, int N, int K, int nterms,
-            int *status, cudaStream_t stream, const GemmSplit *split) {
+            int *status, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % BK != 0) { set_error("gemm_tc: K=%d must be a positive multiple of %d", K, BK); return -1; }
     if (nterms != 1 && (!A.lo || !B.lo)) { set_error("gemm_tc: 3-term mode needs lo planes"); return -1; }
-    if (split && split->part && split->counters) {
-        const GemmSplit sk{gemm_split_slices(N, K, device_sm_count()), split->part, split->counters};
-        if (sk.splits > 1) {
-            static_assert(GEMM_SPLIT_BN == 64, "the split-K path launches the 64-wide tile");
-            return nterms == 1 ? launch<64, 1>(A, B, ep, M, N, K, status, stream, sk) : launch<64, 3>(A, B, ep, M, N, K, status, stream, sk);
-        }
-    }
     // Narrower N tiles when the output has too few 128-wide tiles to occupy the SMs (small M: decoder
     // positions, streaming chunks): more CTAs pull the operands. An output element sees the same k order
     // and the same instruction sequence whatever the tile width, so its bits do not change with it.

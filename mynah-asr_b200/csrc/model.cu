@@ -247,11 +247,12 @@ int Model::check_status(const char *where) {
     return 0;
 }
 
-int Model::gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep, int M, const GemmSplit *split) {
+int Model::gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep, int M, bool few_rows) {
     if (!w.hi) { set_error("contraction on a weight without operand planes"); return -1; }
     GemmOperand A{a.hi, a.lo, lda}, B{w.hi, w.lo, w.k};
     const int sp = prof_begin_span(PROF_GEMM);
-    const int rc = gemm_tc(A, B, ep, M, w.n, w.k, cfg.strict ? 3 : 1, status, stream, split);
+    const int rc = few_rows ? gemm_skinny(A, B, ep, M, w.n, w.k, cfg.strict ? 3 : 1, status, stream)
+                            : gemm_tc(A, B, ep, M, w.n, w.k, cfg.strict ? 3 : 1, status, stream);
     prof_end_span(sp);
     if (sp >= 0) {
         prof_flops[PROF_GEMM] += 2.0 * M * (double)w.n * w.k;

@@ -178,7 +178,7 @@ struct Model {
     int check_status(const char *where);
 
     // drivers (device pointers in / out, all on `stream`)
-    int gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep, int M, const GemmSplit *split = nullptr);
+    int gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep, int M, bool few_rows = false);   // few_rows: the decoder-position kernel (gemm_skinny.cu)
     // int8-activation mode: qa [M, w.k] int8 rows with their scales sx [M] times a reference-native int8 weight
     bool a8_ok(const QWeight &w) const { return w.fmt == FMT_MYNAH_Q8 && w.k % 128 == 0 && w.scales != nullptr; }
     bool a8_layers = false;                          // cfg.a8 and every encoder-layer linear is a8_ok

@@ -2,6 +2,7 @@
 
     python mynah-asr_b200/kernel_case.py gemm  --T 16384 --n 4096 --k 1024 [--fast] [--iters 3]
     python mynah-asr_b200/kernel_case.py gemm  --T 16384 --n 4096 --k 1024 --fmt q8n --a8 [--iters 3]
+    python mynah-asr_b200/kernel_case.py gemm  --T 32 --n 4096 --k 1024 --few-rows [--iters 3]
     python mynah-asr_b200/kernel_case.py qgemv --T 1 --n 65536 --k 4096 --fmt q4_0 [--iters 3]
     python mynah-asr_b200/kernel_case.py attention --T 750 --batch 16 [--heads 8] [--impl 0] [--iters 3]
 
@@ -85,6 +86,7 @@ def main():
     ap.add_argument("--k", type=int, default=1024)
     ap.add_argument("--fmt", default="q4_0", choices=list(BPP))
     ap.add_argument("--fast", action="store_true")
+    ap.add_argument("--few-rows", action="store_true", help="gemm: the decoder-position kernel (weights on the 128-row side, K slices over a cluster)")
     ap.add_argument("--a8", action="store_true")
     ap.add_argument("--iters", type=int, default=3)
     a = ap.parse_args()
@@ -100,13 +102,16 @@ def main():
     fmt = {"q8n": pkg.MYNAH_Q8, "f32": pkg.F32, "q8_0": pkg.GGML_Q8_0, "q4_0": pkg.GGML_Q4_0, "q4_k": pkg.GGML_Q4_K, "q6_k": pkg.GGML_Q6_K}[a.fmt]
     if a.fmt != "q8n":
         q = pkg.QMat(fmt, random_blocks(a.fmt, a.n, a.k, rng), a.n, a.k)
-    flags = (pkg.FAST if a.fast else pkg.A16) | (pkg.A8 if a.a8 else 0)
+    flags = (pkg.FAST if a.fast else pkg.A16) | (pkg.A8 if a.a8 else 0) | (pkg.FEW_ROWS if a.few_rows else 0)
     ms = q.time_ms(T, flags, a.iters)
     out = {"kernel": a.kernel, "T": T, "n": a.n, "k": a.k, "fmt": a.fmt, "ms": ms}
     if a.kernel == "gemm":
-        assert T > 16
+        assert T > 16 or a.few_rows
         out["flops"] = 2.0 * T * a.n * a.k
         out["tflops"] = out["flops"] / (ms * 1e-3) / 1e12
+        if a.few_rows:          # a streaming kernel: operand planes of the weight (2 B per plane and element) + rows in and out
+            out["bytes"] = a.n * a.k * (2.0 if a.fast else 4.0) * 1.0 + T * a.k * (2.0 if a.fast else 4.0) + T * a.n * 4
+            out["gbs"] = out["bytes"] / (ms * 1e-3) / 1e9
     else:
         assert T <= 16
         out["bytes"] = a.n * a.k * BPP[a.fmt] + T * a.k * 4 + T * a.n * 4

@@ -135,6 +135,30 @@ def test_row_stability(gpu_pkg, synth):
     q.close()
 
 
+@pytest.mark.parametrize("fmt", ["f32", "q8_0", "q4_k"])
+def test_few_rows_kernel(gpu_pkg, synth, fmt):
+    """The decoder-position contraction (weights on the 128-row side of the MMA, K slices over the CTAs of a cluster,
+    slice sums added in slice order): f32-grade against the f64 product at every row count and at shapes with 1, 2, 4
+    and 8 slices, ragged weight-row tiles included; a row's bits depend neither on the number of rows in the launch (so
+    neither on the 32 / 64 / 128-wide variant nor on the 128-row grouping) nor on its place among them."""
+    FR = gpu_pkg.FEW_ROWS
+    for n, k in ((300, 256), (1024, 1024), (4096 + 40, 512), (136, 4096), (16384, 256)):
+        q, wd = make(gpu_pkg, synth, fmt, n, k, seed=n + k)
+        rng = np.random.default_rng(n)
+        x = rng.standard_normal((200, k)).astype(np.float32)
+        ref = x.astype(np.float64) @ wd.astype(np.float64).T
+        full = q.mul(x, FR)                                             # 128 + 72 rows: two groups
+        assert rel(full, ref) < 2e-5, (fmt, n, k)
+        for T in (1, 2, 31, 32, 33, 64, 65, 128, 129):
+            assert np.array_equal(q.mul(x[:T], FR), full[:T]), (fmt, n, k, T)
+        assert np.array_equal(q.mul(x[150:181], FR), full[150:181])
+        perm = rng.permutation(200)
+        assert np.array_equal(q.mul(x[perm], FR), full[perm])
+        assert rel(q.mul(x[:40], FR | gpu_pkg.FAST), ref[:40]) < 1e-3   # single fp16 product
+        assert rel(full, q.mul(x)) < 1e-5                               # and next to the many-row kernel on the same planes
+        q.close()
+
+
 def test_a8_block_dots_bit_exact(gpu_pkg, synth):
     """int8 activations: the int32 dot of every 32-element block is exact
     (quantize_act_int8 + dot kernels, src/qmat.c:186-202,285-364)."""
