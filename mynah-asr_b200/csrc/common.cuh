@@ -61,6 +61,37 @@ struct H16 {
 };
 
 #ifdef __CUDACC__
+// ---- chained launches (programmatic dependent launch) --------------------------------------------------------
+// A decoder position is some fifty small kernels, each waiting for the one before. Launched with `chain`, a kernel's
+// blocks may be placed on the SMs while its predecessor in the stream is still running; the kernel calls
+// chain_trigger() when it starts (its successor may be placed) and chain_wait() before it touches any memory a
+// predecessor writes or reads: chain_wait() returns once every earlier kernel of the stream has finished and its
+// writes are visible. What comes before chain_wait() may only read constants (weights) and set up the block.
+// Both calls are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool chain,
+                                        int cluster_x, Args... args) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = grid; lc.blockDim = block; lc.dynamicSmemBytes = smem; lc.stream = st;
+    cudaLaunchAttribute at[2];
+    int n = 0;
+    if (cluster_x > 1) {
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = (unsigned)cluster_x; at[n].val.clusterDim.y = 1; at[n].val.clusterDim.z = 1;
+        n++;
+    }
+    if (chain) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    lc.attrs = at; lc.numAttrs = (unsigned)n;
+    return cudaLaunchKernelEx(&lc, kernel, KArgs(args)...);
+}
+
 // ------------------------------------------------------------- device helpers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);

@@ -36,6 +36,8 @@ __global__ void __launch_bounds__(256)
 argmax_kernel(const float *__restrict__ logits, int ld, const float *__restrict__ bias, int V, int *__restrict__ best) {
     __shared__ float sv[256];
     __shared__ int si[256];
+    chain_trigger();
+    chain_wait();
     const float *row = logits + (size_t)blockIdx.x * ld;
     float bv = -3.0e38f;
     int bi = 0x7fffffff;
@@ -56,10 +58,9 @@ argmax_kernel(const float *__restrict__ logits, int ld, const float *__restrict_
     if (threadIdx.x == 0) best[blockIdx.x] = si[0];
 }
 
-int argmax_rows(const float *logits, int ld, const float *bias, int T, int V, int *best, cudaStream_t st) {
+int argmax_rows(const float *logits, int ld, const float *bias, int T, int V, int *best, cudaStream_t st, bool chain) {
     if (T <= 0) return 0;
-    argmax_kernel<<<T, 256, 0, st>>>(logits, ld, bias, V, best);
-    MB_CUDA(cudaGetLastError());
+    MB_CUDA(launch_kernel(argmax_kernel, dim3(T), dim3(256), 0, st, chain, 1, logits, ld, bias, V, best));
     return 0;
 }
 

@@ -13,6 +13,8 @@ namespace mb {
 // x[b] = emb[cur[b]] + pos[p]   (src/decoder_aed.c:183-184; the LayerNorm follows as its own launch)
 __global__ void aed_embed_kernel(const float *__restrict__ emb, const float *__restrict__ pos, const int *__restrict__ cur,
                                  const int *__restrict__ pd, float *__restrict__ x, int D) {
+    chain_trigger();
+    chain_wait();
     const int b = blockIdx.x, p = *pd;
     const float *e = emb + (size_t)cur[b] * D, *pe = pos + (size_t)p * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)b * D + i] = e[i] + pe[i];
@@ -40,6 +42,8 @@ __global__ void __launch_bounds__(128)
 aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, float *__restrict__ cv,
                      const int *__restrict__ pd, int max_len, int D, int dk, H16 out) {
     extern __shared__ float sm[];
+    chain_trigger();
+    chain_wait();
     const int p = *pd;
     float *sc = sm, *q = sm + ((max_len + 3) & ~3), *red = q + dk, *part = red + 32;     // part: [4][dk]
     const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -127,6 +131,8 @@ __global__ void __launch_bounds__(CROSS_WARPS * 32)
 aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ kv_hi, const __half *__restrict__ kv_lo,
                       const int *__restrict__ enc_off, const int *__restrict__ enc_len, int max_T, int D, int dk, H16 out) {
     extern __shared__ float sm[];
+    chain_trigger();
+    chain_wait();
     float *sc = sm, *q = sm + ((max_T + 3) & ~3), *red = q + dk, *part = red + 32;     // part: [CROSS_WARPS][dk] partial outputs
     const int h = blockIdx.x, b = blockIdx.y;
     const int T = enc_len[b], lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -199,6 +205,8 @@ aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ k
 // st: [cur | n_out | done | n_prompt | max_len | cap] x B, then n_done, p.
 __global__ void aed_select_kernel(const int *__restrict__ best, int eos, int cap_stride, int B, int *st, const int *__restrict__ prompts,
                                   int max_prompt, int *__restrict__ tokens) {
+    chain_trigger();
+    chain_wait();
     const int b = threadIdx.x;
     int *cur = st, *n_out = st + B, *done = st + 2 * B, *n_prompt = st + 3 * B, *max_len = st + 4 * B, *n_done = st + 6 * B;
     const int p = st[6 * B + 1];
@@ -306,29 +314,31 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     const int *pd = st + 6 * B + 1;
     // everything one position needs, in stream order; no host value changes between positions
     auto position = [&]() -> int {
-        aed_embed_kernel<<<B, 128, 0, stream>>>(aed_emb, aed_pos, st, pd, x, D);
-        if (layer_norm(x, aed_embln_w, aed_embln_b, x, H16{nullptr, nullptr}, B, D, 0, stream)) return -1;
+        // every launch of a position is chained: blocks of the next kernel are placed while the one before drains
+        MB_CUDA(launch_kernel(aed_embed_kernel, dim3(B), dim3(128), 0, stream, true, 1, aed_emb, aed_pos, (const int *)st, pd, x, D));
+        if (layer_norm(x, aed_embln_w, aed_embln_b, x, H16{nullptr, nullptr}, B, D, 0, stream, true)) return -1;
         for (int l = 0; l < L; l++) {
             const AedLayer &A = aed_layers[l];
             float *K = sk + (size_t)(2 * l) * B * max_len * D, *Vc = K + (size_t)B * max_len * D;
-            if (layer_norm(x, A.ln_self_w, A.ln_self_b, nullptr, xn, B, D, 0, stream)) return -1;
+            if (layer_norm(x, A.ln_self_w, A.ln_self_b, nullptr, xn, B, D, 0, stream, true)) return -1;
             if (gemm(xn, D, A.sqkv, aed_epi(OUT_F32, ACT_NONE, 1.f, A.sqkv_b, qkv, 3 * D), B, true)) return -1;
-            aed_self_attn_kernel<<<dim3(H, B), 128, self_smem, stream>>>(qkv, K, Vc, pd, max_len, D, dk, att);
+            MB_CUDA(launch_kernel(aed_self_attn_kernel, dim3(H, B), dim3(128), self_smem, stream, true, 1, (const float *)qkv, K, Vc, pd, max_len, D, dk, att));
             if (gemm(att, D, A.so, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.so_b, x, D), B, true)) return -1;
-            if (layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream)) return -1;
+            if (layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream, true)) return -1;
             if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B, true)) return -1;
-            aed_cross_attn_kernel<<<dim3(H, B), cross_threads, cross_smem, stream>>>(q, ckv[l].hi, ckv[l].lo, d_off, d_off + B, max_T, D, dk, att);
+            MB_CUDA(launch_kernel(aed_cross_attn_kernel, dim3(H, B), dim3(cross_threads), cross_smem, stream, true, 1, (const float *)q, (const __half *)ckv[l].hi,
+                                  (const __half *)ckv[l].lo, (const int *)d_off, (const int *)(d_off + B), max_T, D, dk, att));
             if (gemm(att, D, A.co, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.co_b, x, D), B, true)) return -1;
-            if (layer_norm(x, A.ln_ffn_w, A.ln_ffn_b, nullptr, xn, B, D, 0, stream)) return -1;
+            if (layer_norm(x, A.ln_ffn_w, A.ln_ffn_b, nullptr, xn, B, D, 0, stream, true)) return -1;
             if (gemm(xn, D, A.ff1, aed_epi(OUT_H16, ACT_RELU, 1.f, A.ff1_b, nullptr, 0, ff, F), B, true)) return -1;
             if (gemm(ff, F, A.ff2, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.ff2_b, x, D), B, true)) return -1;
         }
         // the head is evaluated at prompt positions too (its result is ignored there): one graph for all positions
-        if (layer_norm(x, aed_fin_w, aed_fin_b, nullptr, xn, B, D, 0, stream)) return -1;
+        if (layer_norm(x, aed_fin_w, aed_fin_b, nullptr, xn, B, D, 0, stream, true)) return -1;
         if (gemm(xn, D, aed_head, aed_epi(OUT_F32, ACT_NONE, 1.f, aed_head_b, logits, V), B, true)) return -1;
-        if (argmax_rows(logits, V, nullptr, B, V, best, stream)) return -1;
-        aed_select_kernel<<<1, ((B + 31) / 32) * 32, 0, stream>>>(best, eos, capn, B, st, d_prompts, max_prompt, d_tokens);
-        MB_CUDA(cudaGetLastError());
+        if (argmax_rows(logits, V, nullptr, B, V, best, stream, true)) return -1;
+        MB_CUDA(launch_kernel(aed_select_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, stream, true, 1, (const int *)best, eos, capn, B, st, (const int *)d_prompts,
+                              max_prompt, d_tokens));
         return 0;
     };
     const int launches_per_position = 2 + L * 13 + 4, gemms_per_position = 7 * L + 1;   // (the contraction wrapper counts its own launches)

@@ -82,6 +82,8 @@ ln_reg_kernel(const float *__restrict__ x, const float *__restrict__ w, const fl
               float *__restrict__ out, __half *__restrict__ hi, __half *__restrict__ lo, int8_t *__restrict__ q8,
               float *__restrict__ sx8, int T, int act) {
     constexpr int d = NV * 128;
+    chain_trigger();
+    chain_wait();
     const int row = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= T) return;
     const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)row * d);
@@ -139,16 +141,16 @@ ln_reg_kernel(const float *__restrict__ x, const float *__restrict__ w, const fl
 }
 
 int layer_norm(const float *x, const float *w, const float *b, float *out_f32, H16 out_h, int T, int d, int act,
-               cudaStream_t st) {
-    return layer_norm_q8(x, w, b, out_f32, out_h, nullptr, nullptr, T, d, act, st);
+               cudaStream_t st, bool chain) {
+    return layer_norm_q8(x, w, b, out_f32, out_h, nullptr, nullptr, T, d, act, st, chain);
 }
 
 int layer_norm_q8(const float *x, const float *w, const float *b, float *out_f32, H16 out_h, int8_t *q8, float *sx8, int T, int d,
-                  int act, cudaStream_t st) {
+                  int act, cudaStream_t st, bool chain) {
     if (T <= 0) return 0;
     if (d % 4) { set_error("layer_norm: d=%d must be a multiple of 4", d); return -1; }
     const dim3 grid(cdiv(T, 8));
-#define LN_REG(NV) ln_reg_kernel<NV><<<grid, 256, 0, st>>>(x, w, b, out_f32, out_h.hi, out_h.lo, q8, sx8, T, act)
+#define LN_REG(NV) MB_CUDA(launch_kernel(ln_reg_kernel<NV>, grid, dim3(256), 0, st, chain, 1, x, w, b, out_f32, out_h.hi, out_h.lo, q8, sx8, T, act))
     if (d == 128) LN_REG(1);
     else if (d == 256) LN_REG(2);
     else if (d == 512) LN_REG(4);

@@ -218,8 +218,9 @@ int gemm_tc(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, 
 
 // The same contraction for a handful of rows (a decoder position): gemm_skinny.cu. X: [M, K] activation planes, W: [N, K]
 // weight planes; K slices over the CTAs of a cluster, added in slice order (the count depends on N and K alone).
+// chain: launched as a chained kernel (common.cuh): its weight tiles are requested while the kernel before it still runs.
 int gemm_skinny(const GemmOperand &X, const GemmOperand &W, const GemmEpilogue &ep, int M, int N, int K, int nterms, int *status,
-                cudaStream_t stream);
+                cudaStream_t stream, bool chain = false);
 
 // Integer contraction on the tensor cores (gemm_i8.cu): acc[m,n] = sum_k a[m,k] * b[n,k] in int32 (exact), then
 // v = (float)acc * col_scale[n] * row_scale[m] — the arithmetic of the reference's int8-activation dots

@@ -92,6 +92,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW_hi, const __grid_cons
     const int n0 = tile * SK_ROWS;
     const int num_k = K / SK_BK / S, kb0 = slice * num_k;
 
+    chain_trigger();
     if (threadIdx.x == 0) {
         tma_prefetch_desc(&tmW_hi);
         tma_prefetch_desc(&tmX_hi);
@@ -109,7 +110,24 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW_hi, const __grid_cons
     if (warp == 0 && lane == 0) {
         // ---------------------------------------------------------- TMA producer
         bool ok = true;
-        int it = 0;
+        // the weights do not depend on the kernels before this one: the first ring of W tiles is under way before
+        // chain_wait() lets the activation rows be read
+        const int pre = num_k < Cfg::STAGES ? num_k : Cfg::STAGES;
+        for (int it = 0; it < pre; it++) {
+            uint8_t *st = tiles + it * Cfg::STAGE_BYTES;
+            const int k = (kb0 + it) * SK_BK;
+            mbar_expect_tx(&full_bar[it], Cfg::STAGE_BYTES);
+            tma_load_2d(st, &tmW_hi, k, n0, &full_bar[it]);
+            if (NTERMS > 1) tma_load_2d(st + Cfg::W_BYTES, &tmW_lo, k, n0, &full_bar[it]);
+        }
+        chain_wait();
+        for (int it = 0; it < pre; it++) {
+            uint8_t *xt = tiles + it * Cfg::STAGE_BYTES + Cfg::NPLANES * Cfg::W_BYTES;
+            const int k = (kb0 + it) * SK_BK;
+            tma_load_2d(xt, &tmX_hi, k, 0, &full_bar[it]);
+            if (NTERMS > 1) tma_load_2d(xt + Cfg::X_BYTES, &tmX_lo, k, 0, &full_bar[it]);
+        }
+        int it = pre;
         for (; it < num_k; it++) {
             const int s = it % Cfg::STAGES;
             const uint32_t ph = (it / Cfg::STAGES) & 1;
@@ -163,6 +181,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW_hi, const __grid_cons
         const bool have = mbar_wait(acc_full, 0);
         if (!have && lane == 0) atomicExch(status, ST_TIMEOUT_EPILOGUE);
         tc_fence_after();
+        chain_wait();                                             // before the residual is read or anything is written
         const float bias = ep.bias && n < N ? ep.bias[n] : 0.0f;
         bool fits = true;
 #pragma unroll 1
@@ -273,7 +292,7 @@ static int gemm_skinny_slices(int N, int K, int sms) {
 
 template <int NB, int NTERMS>
 static int sk_launch(const GemmOperand &X, const GemmOperand &W, const GemmEpilogue &ep, int Mb, int N, int K, int *status,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, bool chain) {
     using Cfg = SkinnyCfg<NB, NTERMS>;
     CUtensorMap tw_hi, tw_lo, tx_hi, tx_lo;
     if (sk_map(&tw_hi, W.hi, N, K, W.ld, SK_ROWS)) return -1;
@@ -291,22 +310,13 @@ static int sk_launch(const GemmOperand &X, const GemmOperand &W, const GemmEpilo
         configured.record(dev, Cfg::SMEM_BYTES);
     }
     const int S = gemm_skinny_slices(N, K, device_sm_count());
-    cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3((unsigned)(cdiv(N, SK_ROWS) * S));
-    lc.blockDim = dim3(SK_THREADS);
-    lc.dynamicSmemBytes = Cfg::SMEM_BYTES;
-    lc.stream = stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeClusterDimension;
-    at[0].val.clusterDim.x = (unsigned)S; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-    lc.attrs = at;
-    lc.numAttrs = 1;
-    MB_CUDA(cudaLaunchKernelEx(&lc, gemm_skinny_kernel<NB, NTERMS>, tw_hi, tw_lo, tx_hi, tx_lo, ep, Mb, N, K, S, status));
+    MB_CUDA(launch_kernel(gemm_skinny_kernel<NB, NTERMS>, dim3((unsigned)(cdiv(N, SK_ROWS) * S)), dim3(SK_THREADS), Cfg::SMEM_BYTES, stream, chain, S,
+                          tw_hi, tw_lo, tx_hi, tx_lo, ep, Mb, N, K, S, status));
     return 0;
 }
 
 int gemm_skinny(const GemmOperand &X, const GemmOperand &W, const GemmEpilogue &ep, int M, int N, int K, int nterms, int *status,
-                cudaStream_t stream) {
+                cudaStream_t stream, bool chain) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % SK_BK != 0) { set_error("gemm_skinny: K=%d must be a positive multiple of %d", K, SK_BK); return -1; }
     if (nterms != 1 && (!X.lo || !W.lo)) { set_error("gemm_skinny: 3-term mode needs lo planes"); return -1; }
@@ -319,8 +329,8 @@ int gemm_skinny(const GemmOperand &X, const GemmOperand &W, const GemmEpilogue &
         if (e.out_hi) e.out_hi += (size_t)r * e.ldh;
         if (e.out_lo) e.out_lo += (size_t)r * e.ldh;
         int rc;
-        if (nterms == 1) rc = mb <= 32 ? sk_launch<32, 1>(x, W, e, mb, N, K, status, stream) : mb <= 64 ? sk_launch<64, 1>(x, W, e, mb, N, K, status, stream) : sk_launch<128, 1>(x, W, e, mb, N, K, status, stream);
-        else rc = mb <= 32 ? sk_launch<32, 3>(x, W, e, mb, N, K, status, stream) : mb <= 64 ? sk_launch<64, 3>(x, W, e, mb, N, K, status, stream) : sk_launch<128, 3>(x, W, e, mb, N, K, status, stream);
+        if (nterms == 1) rc = mb <= 32 ? sk_launch<32, 1>(x, W, e, mb, N, K, status, stream, chain) : mb <= 64 ? sk_launch<64, 1>(x, W, e, mb, N, K, status, stream, chain) : sk_launch<128, 1>(x, W, e, mb, N, K, status, stream, chain);
+        else rc = mb <= 32 ? sk_launch<32, 3>(x, W, e, mb, N, K, status, stream, chain) : mb <= 64 ? sk_launch<64, 3>(x, W, e, mb, N, K, status, stream, chain) : sk_launch<128, 3>(x, W, e, mb, N, K, status, stream, chain);
         if (rc) return rc;
     }
     return 0;

@@ -26,12 +26,13 @@ int split_to_h16(const float *x, __half *hi, __half *lo, size_t n, cudaStream_t 
 // ---- elementwise.cu
 // Row LayerNorm (mean/var accumulated in double, eps 1e-5) with optional SiLU;
 // writes f32 and/or fp16 (hi,lo) planes. out_f32 may alias x.
+// chain: launched as a chained kernel (see chain_wait in common.cuh); the widths without a register kernel ignore it.
 int layer_norm(const float *x, const float *w, const float *b, float *out_f32, H16 out_h, int T, int d, int act,
-               cudaStream_t st);
+               cudaStream_t st, bool chain = false);
 // the same with the row also (or only) written as int8 + per-row scale by the reference's activation rule
 // (quantize_act_int8, src/qmat.c:186-202): the operand of an int8-activation contraction
 int layer_norm_q8(const float *x, const float *w, const float *b, float *out_f32, H16 out_h, int8_t *q8, float *sx8, int T, int d,
-                  int act, cudaStream_t st);
+                  int act, cudaStream_t st, bool chain = false);
 // Conv-module middle: GLU over h2 [T,2d], depthwise conv k along time inside each
 // segment, then either a per-channel affine (folded BatchNorm) + SiLU -> planes, or
 // (affine null) the raw depthwise output as f32 for a following LayerNorm. With an affine, out_f32 (if given)
@@ -112,6 +113,6 @@ void note_launch(int n = 1);
 long long launch_count(bool reset);
 
 // ---- decoder.cu
-int argmax_rows(const float *logits, int ld, const float *bias, int T, int V, int *best, cudaStream_t st);
+int argmax_rows(const float *logits, int ld, const float *bias, int T, int V, int *best, cudaStream_t st, bool chain = false);
 
 }  // namespace mb

@@ -251,7 +251,7 @@ int Model::gemm(const H16 &a, int lda, const QWeight &w, const GemmEpilogue &ep,
     if (!w.hi) { set_error("contraction on a weight without operand planes"); return -1; }
     GemmOperand A{a.hi, a.lo, lda}, B{w.hi, w.lo, w.k};
     const int sp = prof_begin_span(PROF_GEMM);
-    const int rc = few_rows ? gemm_skinny(A, B, ep, M, w.n, w.k, cfg.strict ? 3 : 1, status, stream)
+    const int rc = few_rows ? gemm_skinny(A, B, ep, M, w.n, w.k, cfg.strict ? 3 : 1, status, stream, true)
                             : gemm_tc(A, B, ep, M, w.n, w.k, cfg.strict ? 3 : 1, status, stream);
     prof_end_span(sp);
     if (sp >= 0) {
