@@ -313,35 +313,49 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     const int sp = prof_begin_span(PROF_DECODE);
     const int *pd = st + 6 * B + 1;
     // everything one position needs, in stream order; no host value changes between positions
+    // The LayerNorm that follows a residual update runs inside the contraction that makes the update (GemmEpilogue::ln_*)
+    // when the width is one the register LayerNorm serves; otherwise as a launch of its own.
+    const bool ln_tail = gemm_skinny_ln_width(D);
+    int *ln_count = ws.get<int>(B);
+    if (!ln_count) return -1;
+    MB_CUDA(cudaMemsetAsync(ln_count, 0, (size_t)B * sizeof(int), stream));
+    auto resid = [&](const float *bias, const float *nw, const float *nb) {     // x += y, then xn = LN(x; nw, nb)
+        GemmEpilogue e = aed_epi(OUT_RESID, ACT_NONE, 1.f, bias, x, D);
+        if (ln_tail) { e.ln_w = nw; e.ln_b = nb; e.ln_hi = xn.hi; e.ln_lo = xn.lo; e.ln_count = ln_count; }
+        return e;
+    };
     auto position = [&]() -> int {
         // every launch of a position is chained: blocks of the next kernel are placed while the one before drains
         MB_CUDA(launch_kernel(aed_embed_kernel, dim3(B), dim3(128), 0, stream, true, 1, aed_emb, aed_pos, (const int *)st, pd, x, D));
         if (layer_norm(x, aed_embln_w, aed_embln_b, x, H16{nullptr, nullptr}, B, D, 0, stream, true)) return -1;
+        if (layer_norm(x, aed_layers[0].ln_self_w, aed_layers[0].ln_self_b, nullptr, xn, B, D, 0, stream, true)) return -1;
         for (int l = 0; l < L; l++) {
             const AedLayer &A = aed_layers[l];
             float *K = sk + (size_t)(2 * l) * B * max_len * D, *Vc = K + (size_t)B * max_len * D;
-            if (layer_norm(x, A.ln_self_w, A.ln_self_b, nullptr, xn, B, D, 0, stream, true)) return -1;
+            // LayerNorm after the last contraction of this layer: the next layer's first one, or the final one
+            const float *nw = l + 1 < L ? aed_layers[l + 1].ln_self_w : aed_fin_w, *nb = l + 1 < L ? aed_layers[l + 1].ln_self_b : aed_fin_b;
             if (gemm(xn, D, A.sqkv, aed_epi(OUT_F32, ACT_NONE, 1.f, A.sqkv_b, qkv, 3 * D), B, true)) return -1;
             MB_CUDA(launch_kernel(aed_self_attn_kernel, dim3(H, B), dim3(128), self_smem, stream, true, 1, (const float *)qkv, K, Vc, pd, max_len, D, dk, att));
-            if (gemm(att, D, A.so, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.so_b, x, D), B, true)) return -1;
-            if (layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream, true)) return -1;
+            if (gemm(att, D, A.so, resid(A.so_b, A.ln_cross_w, A.ln_cross_b), B, true)) return -1;
+            if (!ln_tail && layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream, true)) return -1;
             if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B, true)) return -1;
             MB_CUDA(launch_kernel(aed_cross_attn_kernel, dim3(H, B), dim3(cross_threads), cross_smem, stream, true, 1, (const float *)q, (const __half *)ckv[l].hi,
                                   (const __half *)ckv[l].lo, (const int *)d_off, (const int *)(d_off + B), max_T, D, dk, att));
-            if (gemm(att, D, A.co, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.co_b, x, D), B, true)) return -1;
-            if (layer_norm(x, A.ln_ffn_w, A.ln_ffn_b, nullptr, xn, B, D, 0, stream, true)) return -1;
+            if (gemm(att, D, A.co, resid(A.co_b, A.ln_ffn_w, A.ln_ffn_b), B, true)) return -1;
+            if (!ln_tail && layer_norm(x, A.ln_ffn_w, A.ln_ffn_b, nullptr, xn, B, D, 0, stream, true)) return -1;
             if (gemm(xn, D, A.ff1, aed_epi(OUT_H16, ACT_RELU, 1.f, A.ff1_b, nullptr, 0, ff, F), B, true)) return -1;
-            if (gemm(ff, F, A.ff2, aed_epi(OUT_RESID, ACT_NONE, 1.f, A.ff2_b, x, D), B, true)) return -1;
+            if (gemm(ff, F, A.ff2, resid(A.ff2_b, nw, nb), B, true)) return -1;
+            if (!ln_tail && layer_norm(x, nw, nb, nullptr, xn, B, D, 0, stream, true)) return -1;
         }
         // the head is evaluated at prompt positions too (its result is ignored there): one graph for all positions
-        if (layer_norm(x, aed_fin_w, aed_fin_b, nullptr, xn, B, D, 0, stream, true)) return -1;
         if (gemm(xn, D, aed_head, aed_epi(OUT_F32, ACT_NONE, 1.f, aed_head_b, logits, V), B, true)) return -1;
         if (argmax_rows(logits, V, nullptr, B, V, best, stream, true)) return -1;
         MB_CUDA(launch_kernel(aed_select_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, stream, true, 1, (const int *)best, eos, capn, B, st, (const int *)d_prompts,
                               max_prompt, d_tokens));
         return 0;
     };
-    const int launches_per_position = 2 + L * 13 + 4, gemms_per_position = 7 * L + 1;   // (the contraction wrapper counts its own launches)
+    const int lns_per_position = ln_tail ? 2 : 2 + 3 * L;
+    const int launches_per_position = 1 + lns_per_position + L * 8 + 3, gemms_per_position = 6 * L + 1;   // (the contraction wrapper counts its own launches)
     (void)min_prompt;
     int n_done = 0;
     cudaGraph_t graph = nullptr;

@@ -29,6 +29,15 @@ struct GemmEpilogue {
     __half *out_hi;      // fp16 planes (OUT_H16 / OUT_F32_H16)
     __half *out_lo;
     int ldh;
+    // Optional LayerNorm of the finished rows (few-row kernel with OUT_RESID only; the other kernels ignore it): when the
+    // last tile of row m has been accumulated into `out`, that row (ldo == N == ln_d, one of ln_row's widths) is
+    // normalised with (ln_w, ln_b) into the planes (ln_hi, ln_lo) by the CTA that completed it — the LayerNorm that
+    // follows a residual update, without a launch of its own. ln_count: one int per row, zero between launches.
+    const float *ln_w = nullptr;
+    const float *ln_b = nullptr;
+    __half *ln_hi = nullptr;
+    __half *ln_lo = nullptr;
+    int *ln_count = nullptr;
 };
 
 static constexpr int GEMM_BM = 128;      // rows of an output tile (one tcgen05.mma M)
@@ -218,6 +227,8 @@ int gemm_tc(const GemmOperand &A, const GemmOperand &B, const GemmEpilogue &ep, 
 
 // The same contraction for a handful of rows (a decoder position): gemm_skinny.cu. X: [M, K] activation planes, W: [N, K]
 // weight planes; K slices over the CTAs of a cluster, added in slice order (the count depends on N and K alone).
+// GemmEpilogue's ln_* fields are honoured for the widths gemm_skinny_ln_width accepts (and ldo == N).
+bool gemm_skinny_ln_width(int d);
 // chain: launched as a chained kernel (common.cuh): its weight tiles are requested while the kernel before it still runs.
 int gemm_skinny(const GemmOperand &X, const GemmOperand &W, const GemmEpilogue &ep, int M, int N, int K, int nterms, int *status,
                 cudaStream_t stream, bool chain = false);

@@ -34,7 +34,9 @@ struct I8Cfg {
     static constexpr int A_BYTES = GEMM_BM * I8_BK;
     static constexpr int B_BYTES = BN * I8_BK;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int EPI_BYTES = I8_EPI_WARPS * GEMM_BLOCK_STAGE_FLOATS * 4;   // the epilogue warps' turning buffers
+    // the epilogue warps' turning buffers: only the wide tiles have them (the narrow ones serve few-row contractions)
+    static constexpr bool BLOCK_EPILOGUE = BN >= 128;
+    static constexpr int EPI_BYTES = BLOCK_EPILOGUE ? I8_EPI_WARPS * GEMM_BLOCK_STAGE_FLOATS * 4 : 0;
     static constexpr int STAGES_RAW = (I8_SMEM_LIMIT - 2048 - EPI_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 2048;
@@ -149,7 +151,9 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int row = lg * 32 + lane;
         int lt = 0;
         bool fits = true;
-        const bool blk_ok = gemm_block_ok(ep);
+        // the block form pays when a CTA walks several tiles (stores set the pace); with one tile per CTA the run is
+        // latency-bound and the shorter row form is used. Both produce the same bits.
+        const bool blk_ok = Cfg::BLOCK_EPILOGUE && gemm_block_ok(ep) && total > (int)gridDim.x;
         float *stage = epi_stage + (warp - 2) * GEMM_BLOCK_STAGE_FLOATS;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
             int m0, n0, width;
@@ -168,6 +172,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 for (int c = half; c < width / 32; c += 2) {
                     const int nb = n0 + c * 32;
                     const bool blk = blk_ok && nb + 32 <= N;            // warp-uniform
+                    if (blk && m0 + lg * 32 >= M) continue;             // none of this warp's 32 rows exists
                     float4 res[8];
                     if (blk) gemm_block_prefetch(ep, m0 + lg * 32, M, nb, lane, res);
                     if (blk) {

@@ -12,6 +12,7 @@
 // depend on how many rows share the launch. Operands are the same fp16 (hi, lo) planes and the same three products
 // per term (one in fast mode) as in gemm_tc.cu. No multicast; every CTA loads its own tiles.
 #include "gemm.h"
+#include "ln_row.cuh"
 
 namespace mb {
 
@@ -70,6 +71,38 @@ __device__ __forceinline__ bool skinny_store(const GemmEpilogue &ep, float x, fl
     }
     return fits;
 }
+
+// LayerNorm of row m of ep.out (width N) into the planes ep.ln_hi / ep.ln_lo, by one warp
+__device__ __forceinline__ void ln_tail(const GemmEpilogue &ep, int N, int m, int lane) {
+    switch (N) {
+        case 128: ln_row<1, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
+        case 256: ln_row<2, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
+        case 512: ln_row<4, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
+        case 640: ln_row<5, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
+        case 1024: ln_row<8, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
+        case 2048: ln_row<16, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
+        default: break;                                           // the host does not ask for the tail at other widths
+    }
+}
+// LayerNorm of the rows this launch completes. Called by the four epilogue warps of a CTA after they have stored their
+// 128 columns of rows first, first + step, ...: every CTA counts in on each of its rows; the warp that brings a row's
+// count to the number of tiles normalises it (its reads go to the L2, where the other CTAs' stores are).
+__device__ __forceinline__ void ln_finished_rows(const GemmEpilogue &ep, int N, int Mb, int first, int step, int tiles, int w, int lane) {
+    __threadfence();
+    asm volatile("bar.sync 1, 128;" ::: "memory");                // the four epilogue warps: all columns of this CTA's rows are out
+    for (int m = first + w * step; m < Mb; m += 4 * step) {
+        int last = 0;
+        if (lane == 0) last = atomicAdd(ep.ln_count + m, 1) == tiles - 1;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+            __threadfence();
+            if (lane == 0) ep.ln_count[m] = 0;                    // ready for the next launch
+            ln_tail(ep, N, m, lane);
+        }
+    }
+}
+// widths ln_tail serves
+bool gemm_skinny_ln_width(int d) { return d == 128 || d == 256 || d == 512 || d == 640 || d == 1024 || d == 2048; }
 
 // grid = tiles * S CTAs in clusters of S; CTA = (tile of 128 W rows, K slice)
 template <int NB, int NTERMS>
@@ -176,14 +209,12 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW_hi, const __grid_cons
     } else if (warp >= 2) {
         // ------------------------------------------------- epilogue, first half: this slice's sums
         const int lg = warp & 3;                                  // TMEM lane group of this warp
-        const int nl = lg * 32 + lane, n = n0 + nl;
+        const int nl = lg * 32 + lane;
         const uint32_t acc = tmem_base + ((uint32_t)(lg * 32) << 16);
         const bool have = mbar_wait(acc_full, 0);
         if (!have && lane == 0) atomicExch(status, ST_TIMEOUT_EPILOGUE);
         tc_fence_after();
         chain_wait();                                             // before the residual is read or anything is written
-        const float bias = ep.bias && n < N ? ep.bias[n] : 0.0f;
-        bool fits = true;
 #pragma unroll 1
         for (int c = 0; c < NB / 32; c++) {
             float v[32];
@@ -202,20 +233,23 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW_hi, const __grid_cons
 #pragma unroll
                 for (int j = 0; j < 32; j++) v[j] = 0.0f;
             }
-            if (S == 1) {
 #pragma unroll
-                for (int j = 0; j < 32; j++)
-                    if (c * 32 + j < Mb && n < N) fits &= skinny_store(ep, v[j], bias, c * 32 + j, n);
-            } else {
-#pragma unroll
-                for (int j = 0; j < 32; j++) part[(c * 32 + j) * SK_ROWS + nl] = v[j];
-            }
+            for (int j = 0; j < 32; j++) part[(c * 32 + j) * SK_ROWS + nl] = v[j];
         }
-        if (!fits) atomicCAS(status, ST_OK, ST_RANGE);
     }
     tc_fence_before();
     __syncthreads();
-    if (S > 1) {
+    if (S == 1) {
+        if (warp >= 2) {                                          // a single slice: the fused tail straight from this CTA's sums
+            const int nl = (warp - 2) * 32 + lane, n = n0 + nl;
+            const float bias = ep.bias && n < N ? ep.bias[n] : 0.0f;
+            bool fits = true;
+            if (n < N)
+                for (int m = 0; m < Mb; m++) fits &= skinny_store(ep, part[m * SK_ROWS + nl], bias, m, n);
+            if (!fits) atomicCAS(status, ST_OK, ST_RANGE);
+            if (ep.ln_w) ln_finished_rows(ep, N, Mb, 0, 1, (int)gridDim.x, warp - 2, lane);
+        }
+    } else {
         cluster_barrier();                                        // every slice's sums are in place
         if (warp >= 2) {
             // -------------------------------------------- second half: rows m = slice, slice + S, ... of this tile
@@ -245,6 +279,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tmW_hi, const __grid_cons
                 }
             }
             if (!fits) atomicCAS(status, ST_OK, ST_RANGE);
+            if (ep.ln_w) ln_finished_rows(ep, N, Mb, slice, S, (int)gridDim.x / S, warp - 2, lane);
         }
         cluster_barrier();                                        // nobody's shared memory goes away while it is read
     }
@@ -320,6 +355,10 @@ int gemm_skinny(const GemmOperand &X, const GemmOperand &W, const GemmEpilogue &
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % SK_BK != 0) { set_error("gemm_skinny: K=%d must be a positive multiple of %d", K, SK_BK); return -1; }
     if (nterms != 1 && (!X.lo || !W.lo)) { set_error("gemm_skinny: 3-term mode needs lo planes"); return -1; }
+    if (ep.ln_w && (!ep.ln_b || !ep.ln_hi || !ep.ln_count || !ep.out || ep.mode == OUT_H16 || ep.ldo != N || !gemm_skinny_ln_width(N))) {
+        set_error("gemm_skinny: the LayerNorm tail needs an f32 output of row stride N = %d (a register-LayerNorm width), planes and counters", N);
+        return -1;
+    }
     // more than 128 rows: groups of 128 (a row's bits do not depend on the group it is in)
     for (int r = 0; r < M; r += 128) {
         const int mb = M - r < 128 ? M - r : 128;
@@ -328,6 +367,7 @@ int gemm_skinny(const GemmOperand &X, const GemmOperand &W, const GemmEpilogue &
         if (e.out) e.out += (size_t)r * e.ldo;
         if (e.out_hi) e.out_hi += (size_t)r * e.ldh;
         if (e.out_lo) e.out_lo += (size_t)r * e.ldh;
+        if (e.ln_w) { e.ln_hi += (size_t)r * N; if (e.ln_lo) e.ln_lo += (size_t)r * N; e.ln_count += r; }
         int rc;
         if (nterms == 1) rc = mb <= 32 ? sk_launch<32, 1>(x, W, e, mb, N, K, status, stream, chain) : mb <= 64 ? sk_launch<64, 1>(x, W, e, mb, N, K, status, stream, chain) : sk_launch<128, 1>(x, W, e, mb, N, K, status, stream, chain);
         else rc = mb <= 32 ? sk_launch<32, 3>(x, W, e, mb, N, K, status, stream, chain) : mb <= 64 ? sk_launch<64, 3>(x, W, e, mb, N, K, status, stream, chain) : sk_launch<128, 3>(x, W, e, mb, N, K, status, stream, chain);

@@ -39,7 +39,10 @@ struct GemmCfg {
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = NPLANES * (A_BYTES + B_BYTES);
-    static constexpr int EPI_BYTES = EPI_WARPS * GEMM_BLOCK_STAGE_FLOATS * 4;      // the epilogue warps' turning buffers
+    // the epilogue warps' turning buffers: only the wide tiles have them — the narrow ones serve contractions with few
+    // rows, which are latency-bound and want every stage of the operand ring instead
+    static constexpr bool BLOCK_EPILOGUE = BN >= 128;
+    static constexpr int EPI_BYTES = BLOCK_EPILOGUE ? EPI_WARPS * GEMM_BLOCK_STAGE_FLOATS * 4 : 0;
     static constexpr int STAGES_RAW = (SMEM_LIMIT - 2048 - EPI_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 6 ? 6 : STAGES_RAW;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + EPI_BYTES + 2048;
@@ -157,7 +160,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
         const int row = lg * 32 + lane;
         int lt = 0;
         bool fits = true;
-        const bool blk_ok = gemm_block_ok(ep);
+        // the block form pays when a CTA walks several tiles (stores set the pace); with one tile per CTA the run is
+        // latency-bound and the shorter row form is used. Both produce the same bits.
+        const bool blk_ok = Cfg::BLOCK_EPILOGUE && gemm_block_ok(ep) && total > (int)gridDim.x;
         float *stage = epi_stage + (warp - 2) * GEMM_BLOCK_STAGE_FLOATS;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, lt++) {
             int m0, n0, width;
@@ -175,6 +180,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA_hi, const __grid_constant
                 for (int c = half; c < width / 32; c += 2) {
                     const int nb = n0 + c * 32;
                     const bool blk = blk_ok && nb + 32 <= N;            // warp-uniform
+                    if (blk && m0 + lg * 32 >= M) continue;             // none of this warp's 32 rows exists
                     float4 res[8];
                     if (blk) gemm_block_prefetch(ep, m0 + lg * 32, M, nb, lane, res);
                     if (blk) {

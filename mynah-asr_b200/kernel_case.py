@@ -5,12 +5,15 @@
     python mynah-asr_b200/kernel_case.py gemm  --T 32 --n 4096 --k 1024 --few-rows [--iters 3]
     python mynah-asr_b200/kernel_case.py qgemv --T 1 --n 65536 --k 4096 --fmt q4_0 [--iters 3]
     python mynah-asr_b200/kernel_case.py attention --T 750 --batch 16 [--heads 8] [--impl 0] [--iters 3]
+    python mynah-asr_b200/kernel_case.py aed --batch 32 --T 250 [--positions 64] [--iters 3]
 
 gemm : the tcgen05 contraction on resident fp16 planes (large T); with --fmt q8n --a8 the integer contraction
        (tcgen05 kind::i8) on reference-native int8 weights and int8 activation rows.
 qgemv: the weight-streaming small-T kernel on the stored blocks; sizes above the 126 MB L2
        make the figure an HBM figure. Prints the CUDA-event time per launch, the algorithmic
        bytes / flops and the achieved rate.
+aed  : the kernels of one AED decode position (few-row contractions, single-query self- and cross-attention,
+       LayerNorms) on a Canary-1B-shaped decoder behind a tiny encoder: a profiler target that holds < 1 GB.
 attention: the rel-pos self-attention kernel inside a one-layer encoder (d = 128 x heads) over a packed batch of
        `batch` segments of T frames; the time is that of the attention launches alone (device events around
        them), the flops are 6 T^2 d per segment: content scores, the needed half of the position band, P.V.
@@ -75,9 +78,39 @@ def attention_case(pkg, a, rng):
     m.close()
 
 
+def aed_case(pkg, a, rng):
+    """The AED decoder of the Canary-1B shape (4 layers, d = 1024, 8 heads, FFN 4096, vocab 16384, Q8_0) behind a one-layer
+    128-wide encoder, so that the process holds well under 1 GB on the device: `batch` utterances of T encoder frames,
+    `iters` decodes of `--positions` positions each (no token is EOS: every decode runs to its cap)."""
+    import time
+    import mynah_asr_b200.synth as synth
+    T = a.T or 250
+    cfg = synth.config("aed_case", d_model=128, n_layers=1, n_heads=4, ffn_dim=256, n_mels=80, decoder="aed", vocab=16384,
+                       aed_d=1024, aed_layers=4, aed_heads=8, aed_ffn=4096, aed_max_seq=1024, wtype="q8_0")
+    m = pkg.Model(synth.make_model(cfg, seed=1), n_mels=cfg.n_mels, mel_fb=synth.mel_filterbank(cfg.n_mels),
+                  window=synth.hann_window(), causal=0, normalize=True, blank=cfg.vocab - 1, aed_heads=cfg.aed_heads)
+    encs = [rng.standard_normal((T, cfg.d_model)).astype(np.float32) for _ in range(a.batch)]
+    prompts = [[3, 4, 5, 6, 7]] * a.batch
+    caps = [a.positions - 5] * a.batch
+    m.aed_decode_batch(encs, prompts, -1, caps)                   # warm-up
+    t0 = time.perf_counter()
+    for _ in range(a.iters):
+        toks = m.aed_decode_batch(encs, prompts, -1, caps)
+    dt = (time.perf_counter() - t0) / a.iters
+    D, F, V, L = 1024, 4096, 16384, 4
+    w_bytes = (L * (6 * D * D + 2 * D * F) + V * D) * 4.0          # fp16 (hi, lo) planes of the position's linears
+    kv_bytes = L * a.batch * T * 2 * D * 4.0                        # cross K / V planes
+    print(json.dumps({"kernel": "aed", "batch": a.batch, "T": T, "positions": a.positions, "tokens": int(sum(len(t) for t in toks)),
+                      "ms_per_decode_wall": dt * 1e3, "us_per_position_wall": dt * 1e6 / a.positions,
+                      "bytes_per_position": w_bytes + kv_bytes, "note": "wall clock around the whole call: projection of the encoder "
+                      "output, cross K/V, all positions, token read-back"}))
+    m.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "qgemv", "attention"])
+    ap.add_argument("kernel", choices=["gemm", "qgemv", "attention", "aed"])
+    ap.add_argument("--positions", type=int, default=64, help="aed: decode positions per call (prompt of 5 included)")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--heads", type=int, default=8)
     ap.add_argument("--impl", type=int, default=0, help="attention: 0 default (tcgen05 where eligible), 2 warp-level tiled kernel")
@@ -95,6 +128,8 @@ def main():
     rng = np.random.default_rng(0)
     if a.kernel == "attention":
         return attention_case(pkg, a, rng)
+    if a.kernel == "aed":
+        return aed_case(pkg, a, rng)
     T = a.T or (16384 if a.kernel == "gemm" else 1)
     if a.fmt == "q8n":
         wq = rng.integers(-127, 128, (a.n, a.k), dtype=np.int8)
