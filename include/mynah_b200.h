@@ -276,7 +276,11 @@ int mynah_b200_plan_segments(mynah_b200_vad *v, const float *samples, size_t n_s
  * streams that advance in lock step: every step takes one chunk of mel frames from each stream and
  * returns q = right_ctx + 1 encoder frames per stream. The K/V caches (left_ctx frames per layer), the
  * conv caches and the subsampling's one-frame caches of all streams stay on the device; all streams of a
- * group start together (open one group per start time). */
+ * group start together (open one group per start time).
+ * A stream's output does not depend on the other streams of its group. Groups come in two size classes, fixed when the
+ * group opens: with n_streams * (right_ctx + 1) <= 128 rows per step the linears of the layers run on the few-row
+ * kernel, larger groups on the many-row kernel; inside a class a stream's bits are the same whatever the group's size,
+ * across the classes they agree to f32 rounding (relative 1e-5). */
 typedef struct mynah_b200_stream_group mynah_b200_stream_group;
 mynah_b200_stream_group *mynah_b200_stream_open(mynah_b200_model *m, int n_streams, int left_ctx, int right_ctx);
 void mynah_b200_stream_close(mynah_b200_stream_group *g);

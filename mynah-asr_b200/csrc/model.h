@@ -54,6 +54,10 @@ struct AedLayer {
 struct StreamState {
     int S = 0, left = 0, right = 0, q = 1;
     int first = 1, valid = 0;
+    // a group of at most 128 rows per regular step (S q <= 128) runs the linears of its layers on the few-row kernel
+    // (gemm_skinny.cu), a larger one on the many-row kernel: fixed when the group opens, for its whole life
+    bool few_rows = false;
+    int *ln_count = nullptr;                            // row counters of the LayerNorms that run inside those contractions
     int *d_start = nullptr;                             // ring offset of the oldest frame, kept on the device
     // steady state (caches full, same buffers): one captured graph replays the whole step
     cudaGraphExec_t exec = nullptr;

@@ -75,6 +75,7 @@ __global__ void stream_attn_kernel(const float *__restrict__ q, const __half *__
                                    const float *__restrict__ bias_u, const float *__restrict__ bias_v, H16 ctx, int Q, int valid,
                                    const int *__restrict__ d_start, int left, int d, int dk) {
     extern __shared__ float sm[];
+    chain_trigger();                   // a chained contraction behind this kernel may start fetching its weights
     const int K = valid + Q, start = *d_start;
     float *sc = sm;                    // [K]
     float *qu = sc + K, *qv = qu + dk; // [dk] each
@@ -137,6 +138,7 @@ __global__ void stream_attn_kernel(const float *__restrict__ q, const __half *__
 // new k / v rows of the chunk into their ring slots (update_kv_cache, src/encoder.c:763-776)
 __global__ void stream_kv_update_kernel(const __half *__restrict__ kn, const __half *__restrict__ vn, __half *__restrict__ kc,
                                         __half *__restrict__ vc, int S, int Q, int valid, const int *__restrict__ d_start, int left, int d) {
+    chain_trigger();                   // a chained contraction behind this kernel may start fetching its weights
     const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     if (idx >= (size_t)S * Q * d) return;
     const int start = *d_start;
@@ -201,6 +203,13 @@ int Model::stream_open(StreamState &st, int S, int left, int right) {
     for (const EncLayer &L : layers) if (L.cnorm_scale) { set_error("stream_open: streaming needs the LayerNorm conv norm"); return -1; }
     st = StreamState();
     st.S = S; st.left = left; st.right = right; st.q = right + 1;
+    st.few_rows = S * st.q <= 128;
+    if (st.few_rows) {
+        const size_t rows = (size_t)S * (st.q + 2);
+        st.ln_count = (int *)stream_alloc(st, rows * sizeof(int));
+        if (!st.ln_count) return -1;
+        MB_CUDA(cudaMemsetAsync(st.ln_count, 0, rows * sizeof(int), stream));
+    }
     const int C = channels;
     int F = cfg.n_mels;
     for (int s = 0; s < 3; s++) {
@@ -306,7 +315,7 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
         MB_CUDA(cudaGetLastError());
         if (gemm(p2, C, pw[1], st_epi(OUT_H16, ACT_RELU, 1.f, pw[1].bias, nullptr, 0, flat, C), S * T3 * F3)) return -1;
         // flat is [S*Q, F3*C]: the linear's columns were permuted to this order at load. No xscale here, as in the reference's step.
-        if (gemm(flat, F3 * C, ss_lin, st_epi(OUT_F32, ACT_NONE, 1.f, ss_lin.bias, x, d), M)) return -1;
+        if (gemm(flat, F3 * C, ss_lin, st_epi(OUT_F32, ACT_NONE, 1.f, ss_lin.bias, x, d), M, st.few_rows)) return -1;
         note_launch(6);
     }
     // ---- layers (src/encoder.c:826-866)
@@ -328,35 +337,42 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
     }
     const H16 none{nullptr, nullptr};
     const int leftn = st.left > 0 ? st.left : 1;
+    // In a few-row group the LayerNorm that follows a residual update runs inside the contraction that makes it
+    const bool tail = st.few_rows && st.ln_count && gemm_skinny_ln_width(d);
+    auto resid = [&](float alpha, const float *bias, const float *nw, const float *nb) {
+        GemmEpilogue e = st_epi(OUT_RESID, ACT_NONE, alpha, bias, x, d);
+        if (tail) { e.ln_w = nw; e.ln_b = nb; e.ln_hi = hA.hi; e.ln_lo = hA.lo; e.ln_count = st.ln_count; }
+        return e;
+    };
     for (int li = 0; li < n_layers; li++) {
         const EncLayer &L = layers[li];
         __half *kc = st.k_cache + (size_t)li * S * leftn * d, *vc = st.v_cache + (size_t)li * S * leftn * d;
         float *cc = st.conv_cache + (size_t)li * S * (conv_k - 1) * d;
         if (layer_norm(x, L.ln_ff1_w, L.ln_ff1_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
-        if (gemm(hA, d, L.ff1_w1, st_epi(OUT_H16, ACT_SILU, 1.f, L.ff1_w1.bias, nullptr, 0, hF, F), M)) return -1;
-        if (gemm(hF, F, L.ff1_w2, st_epi(OUT_RESID, ACT_NONE, 0.5f, L.ff1_w2.bias, x, d), M)) return -1;
-        if (layer_norm(x, L.ln_att_w, L.ln_att_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
-        if (gemm(hA, d, L.q_w, st_epi(OUT_F32, ACT_NONE, 1.f, L.q_w.bias, qbuf, d), M)) return -1;
-        if (gemm(hA, d, L.k_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.k_w.bias, nullptr, 0, kn, d), M)) return -1;
-        if (gemm(hA, d, L.v_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.v_w.bias, nullptr, 0, vn, d), M)) return -1;
+        if (gemm(hA, d, L.ff1_w1, st_epi(OUT_H16, ACT_SILU, 1.f, L.ff1_w1.bias, nullptr, 0, hF, F), M, st.few_rows)) return -1;
+        if (gemm(hF, F, L.ff1_w2, resid(0.5f, L.ff1_w2.bias, L.ln_att_w, L.ln_att_b), M, st.few_rows)) return -1;
+        if (!tail && layer_norm(x, L.ln_att_w, L.ln_att_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.q_w, st_epi(OUT_F32, ACT_NONE, 1.f, L.q_w.bias, qbuf, d), M, st.few_rows)) return -1;
+        if (gemm(hA, d, L.k_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.k_w.bias, nullptr, 0, kn, d), M, st.few_rows)) return -1;
+        if (gemm(hA, d, L.v_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.v_w.bias, nullptr, 0, vn, d), M, st.few_rows)) return -1;
         if (gemm(pe, d, L.relk, st_epi(OUT_H16, ACT_NONE, 1.f, nullptr, nullptr, 0, rk, d), P)) return -1;
         stream_attn_kernel<<<dim3(H, S), 128, attn_smem, stream>>>(qbuf, kn.hi, vn.hi, kc, vc, rk.hi, L.bias_u, L.bias_v, hC, Q, valid,
                                                                    st.d_start, leftn, d, dk);
         if (st.left > 0)
             stream_kv_update_kernel<<<(unsigned)cdiv((size_t)M * d, TPB), TPB, 0, stream>>>(kn.hi, vn.hi, kc, vc, S, Q, valid, st.d_start, st.left, d);
         MB_CUDA(cudaGetLastError());
-        if (gemm(hC, d, L.o_w, st_epi(OUT_RESID, ACT_NONE, 1.f, L.o_w.bias, x, d), M)) return -1;
-        if (layer_norm(x, L.ln_conv_w, L.ln_conv_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
-        if (gemm(hA, d, L.pw1_w, st_epi(OUT_F32, ACT_NONE, 1.f, L.pw1_w.bias, h2, 2 * d), M)) return -1;
+        if (gemm(hC, d, L.o_w, resid(1.f, L.o_w.bias, L.ln_conv_w, L.ln_conv_b), M, st.few_rows)) return -1;
+        if (!tail && layer_norm(x, L.ln_conv_w, L.ln_conv_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.pw1_w, st_epi(OUT_F32, ACT_NONE, 1.f, L.pw1_w.bias, h2, 2 * d), M, st.few_rows)) return -1;
         stream_conv_kernel<STREAM_CONV_MAX><<<(unsigned)cdiv((size_t)S * d, 128), 128, 0, stream>>>(h2, L.dw_w, cc, cbuf, S, Q, d, conv_k);
         MB_CUDA(cudaGetLastError());
         if (layer_norm(cbuf, L.cnorm_w, L.cnorm_b, nullptr, hC, M, d, ACT_SILU, stream)) return -1;
-        if (gemm(hC, d, L.pw2_w, st_epi(OUT_RESID, ACT_NONE, 1.f, L.pw2_w.bias, x, d), M)) return -1;
-        if (layer_norm(x, L.ln_ff2_w, L.ln_ff2_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
-        if (gemm(hA, d, L.ff2_w1, st_epi(OUT_H16, ACT_SILU, 1.f, L.ff2_w1.bias, nullptr, 0, hF, F), M)) return -1;
-        if (gemm(hF, F, L.ff2_w2, st_epi(OUT_RESID, ACT_NONE, 0.5f, L.ff2_w2.bias, x, d), M)) return -1;
+        if (gemm(hC, d, L.pw2_w, resid(1.f, L.pw2_w.bias, L.ln_ff2_w, L.ln_ff2_b), M, st.few_rows)) return -1;
+        if (!tail && layer_norm(x, L.ln_ff2_w, L.ln_ff2_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (gemm(hA, d, L.ff2_w1, st_epi(OUT_H16, ACT_SILU, 1.f, L.ff2_w1.bias, nullptr, 0, hF, F), M, st.few_rows)) return -1;
+        if (gemm(hF, F, L.ff2_w2, st_epi(OUT_RESID, ACT_NONE, 0.5f, L.ff2_w2.bias, x, d), M, st.few_rows)) return -1;
         if (layer_norm(x, L.ln_out_w, L.ln_out_b, x, none, M, d, ACT_NONE, stream)) return -1;
-        note_launch(9);
+        note_launch(tail ? 6 : 9);
     }
     {   // rows are stream-major: Q rows per stream, each stream with its own prompt id
         const std::vector<int> post_lens((size_t)st.S, Q);

@@ -64,6 +64,22 @@ def test_stream_rows_do_not_depend_on_the_group(setup):
     assert np.array_equal(run_group(dm, [mels[2], mels[0]], left, right)[1], three[0])
 
 
+def test_group_size_classes(setup):
+    """Groups of at most 128 rows per step (streams x frames per chunk) run the linears of their layers on the few-row
+    kernel, larger groups on the many-row kernel: inside a class a stream's bits depend neither on the group's size nor
+    on its place in the group; across the two classes the outputs agree to f32 rounding (both kernels sum the same
+    three fp16 products per term, in different orders)."""
+    cfg, tensors, dm, mels, g = setup
+    left, right = 8, 1                                                    # two frames per chunk: 64 streams = 128 rows
+    small = run_group(dm, mels, left, right)
+    edge = run_group(dm, [mels[1]] * 63 + [mels[0]], left, right)         # 64 streams: still the few-row class
+    assert np.array_equal(edge[63], small[0]) and np.array_equal(edge[5], small[1])
+    big = run_group(dm, [mels[1]] * 64 + [mels[0]], left, right)          # 65 streams: the many-row class
+    bigger = run_group(dm, [mels[0]] + [mels[2]] * 70, left, right)
+    assert np.array_equal(big[64], bigger[0])
+    assert rel(big[64], small[0]) < 1e-5 and rel(big[0], small[1]) < 1e-5
+
+
 def test_streaming_equals_offline_tokens(setup):
     """Streaming ~ the offline limited-context encoder on the same frames, and the greedy tokens are identical
     (the reference's tests/test_streaming.c checks text equality)."""
