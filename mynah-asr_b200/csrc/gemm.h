@@ -29,12 +29,17 @@ struct GemmEpilogue {
     __half *out_hi;      // fp16 planes (OUT_H16 / OUT_F32_H16)
     __half *out_lo;
     int ldh;
-    // Optional LayerNorm of the finished rows (few-row kernel with OUT_RESID only; the other kernels ignore it): when the
-    // last tile of row m has been accumulated into `out`, that row (ldo == N == ln_d, one of ln_row's widths) is
-    // normalised with (ln_w, ln_b) into the planes (ln_hi, ln_lo) by the CTA that completed it — the LayerNorm that
-    // follows a residual update, without a launch of its own. ln_count: one int per row, zero between launches.
+    // Optional LayerNorm of the finished rows (few-row kernel only; the other kernels ignore it): when the last tile of
+    // row m has been written to `out`, that row (ldo == N, one of ln_row's widths) is normalised by the CTA that
+    // completed it — the LayerNorm that follows a residual update, without a launch of its own.
+    //   ln_w, ln_b alone: into the planes (ln_hi, ln_lo), or, without planes, into `out` in place;
+    //   with ln2_w, ln2_b: (ln_w, ln_b) into `out` in place, then (ln2_w, ln2_b) of that result into the planes
+    //   (a block's closing LayerNorm followed by the next block's opening one).
+    // ln_count: one int per row, zero between launches.
     const float *ln_w = nullptr;
     const float *ln_b = nullptr;
+    const float *ln2_w = nullptr;
+    const float *ln2_b = nullptr;
     __half *ln_hi = nullptr;
     __half *ln_lo = nullptr;
     int *ln_count = nullptr;

@@ -72,18 +72,31 @@ __device__ __forceinline__ bool skinny_store(const GemmEpilogue &ep, float x, fl
     return fits;
 }
 
-// LayerNorm of row m of ep.out (width N) into the planes ep.ln_hi / ep.ln_lo, by one warp
+// LayerNorm(s) of row m of ep.out (width N = NV * 128) by one warp, as GemmEpilogue describes them
+template <int NV>
+__device__ __forceinline__ void ln_tail_nv(const GemmEpilogue &ep, int m, int lane) {
+    if (ep.ln2_w) {
+        ln_row<NV, true>(ep.out, ep.ln_w, ep.ln_b, ep.out, nullptr, nullptr, nullptr, nullptr, m, ACT_NONE, lane);
+        __syncwarp();                                             // every lane reads back what it wrote itself
+        ln_row<NV, true>(ep.out, ep.ln2_w, ep.ln2_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane);
+    } else {
+        ln_row<NV, true>(ep.out, ep.ln_w, ep.ln_b, ep.ln_hi ? nullptr : ep.out, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane);
+    }
+}
 __device__ __forceinline__ void ln_tail(const GemmEpilogue &ep, int N, int m, int lane) {
     switch (N) {
-        case 128: ln_row<1, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
-        case 256: ln_row<2, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
-        case 512: ln_row<4, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
-        case 640: ln_row<5, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
-        case 1024: ln_row<8, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
-        case 2048: ln_row<16, true>(ep.out, ep.ln_w, ep.ln_b, nullptr, ep.ln_hi, ep.ln_lo, nullptr, nullptr, m, ACT_NONE, lane); break;
+        case 128: ln_tail_nv<1>(ep, m, lane); break;
+        case 256: ln_tail_nv<2>(ep, m, lane); break;
+        case 512: ln_tail_nv<4>(ep, m, lane); break;
+        case 640: ln_tail_nv<5>(ep, m, lane); break;
+        case 1024: ln_tail_nv<8>(ep, m, lane); break;
+        case 2048: ln_tail_nv<16>(ep, m, lane); break;
         default: break;                                           // the host does not ask for the tail at other widths
     }
 }
+// widths ln_tail serves
+bool gemm_skinny_ln_width(int d) { return d == 128 || d == 256 || d == 512 || d == 640 || d == 1024 || d == 2048; }
+
 // LayerNorm of the rows this launch completes. Called by the four epilogue warps of a CTA after they have stored their
 // 128 columns of rows first, first + step, ...: every CTA counts in on each of its rows; the warp that brings a row's
 // count to the number of tiles normalises it (its reads go to the L2, where the other CTAs' stores are).
@@ -101,8 +114,6 @@ __device__ __forceinline__ void ln_finished_rows(const GemmEpilogue &ep, int N, 
         }
     }
 }
-// widths ln_tail serves
-bool gemm_skinny_ln_width(int d) { return d == 128 || d == 256 || d == 512 || d == 640 || d == 1024 || d == 2048; }
 
 // grid = tiles * S CTAs in clusters of S; CTA = (tile of 128 W rows, K slice)
 template <int NB, int NTERMS>
@@ -355,7 +366,8 @@ int gemm_skinny(const GemmOperand &X, const GemmOperand &W, const GemmEpilogue &
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % SK_BK != 0) { set_error("gemm_skinny: K=%d must be a positive multiple of %d", K, SK_BK); return -1; }
     if (nterms != 1 && (!X.lo || !W.lo)) { set_error("gemm_skinny: 3-term mode needs lo planes"); return -1; }
-    if (ep.ln_w && (!ep.ln_b || !ep.ln_hi || !ep.ln_count || !ep.out || ep.mode == OUT_H16 || ep.ldo != N || !gemm_skinny_ln_width(N))) {
+    if (ep.ln_w && (!ep.ln_b || !ep.ln_count || !ep.out || ep.mode == OUT_H16 || ep.ldo != N || !gemm_skinny_ln_width(N) ||
+                    (ep.ln2_w && (!ep.ln2_b || !ep.ln_hi)))) {
         set_error("gemm_skinny: the LayerNorm tail needs an f32 output of row stride N = %d (a register-LayerNorm width), planes and counters", N);
         return -1;
     }
@@ -367,7 +379,7 @@ int gemm_skinny(const GemmOperand &X, const GemmOperand &W, const GemmEpilogue &
         if (e.out) e.out += (size_t)r * e.ldo;
         if (e.out_hi) e.out_hi += (size_t)r * e.ldh;
         if (e.out_lo) e.out_lo += (size_t)r * e.ldh;
-        if (e.ln_w) { e.ln_hi += (size_t)r * N; if (e.ln_lo) e.ln_lo += (size_t)r * N; e.ln_count += r; }
+        if (e.ln_w) { if (e.ln_hi) e.ln_hi += (size_t)r * N; if (e.ln_lo) e.ln_lo += (size_t)r * N; e.ln_count += r; }
         int rc;
         if (nterms == 1) rc = mb <= 32 ? sk_launch<32, 1>(x, W, e, mb, N, K, status, stream, chain) : mb <= 64 ? sk_launch<64, 1>(x, W, e, mb, N, K, status, stream, chain) : sk_launch<128, 1>(x, W, e, mb, N, K, status, stream, chain);
         else rc = mb <= 32 ? sk_launch<32, 3>(x, W, e, mb, N, K, status, stream, chain) : mb <= 64 ? sk_launch<64, 3>(x, W, e, mb, N, K, status, stream, chain) : sk_launch<128, 3>(x, W, e, mb, N, K, status, stream, chain);

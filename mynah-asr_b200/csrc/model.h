@@ -57,6 +57,10 @@ struct StreamState {
     // a group of at most 128 rows per regular step (S q <= 128) runs the linears of its layers on the few-row kernel
     // (gemm_skinny.cu), a larger one on the many-row kernel: fixed when the group opens, for its whole life
     bool few_rows = false;
+    // rel-pos key projections rk = pos_emb(K) relk^T of every layer for the steady key count K = left + q: they depend on
+    // nothing but the weights, so they are computed on the first full step with full caches and reused afterwards
+    __half *rk_cache = nullptr;                         // [L][2 (left + q) - 1][d] fp16
+    bool rk_ready = false;
     int *ln_count = nullptr;                            // row counters of the LayerNorms that run inside those contractions
     int *d_start = nullptr;                             // ring offset of the oldest frame, kept on the device
     // steady state (caches full, same buffers): one captured graph replays the whole step

@@ -226,6 +226,10 @@ int Model::stream_open(StreamState &st, int S, int left, int right) {
     if (!st.k_cache || !st.v_cache || !st.conv_cache) return -1;
     st.d_start = (int *)stream_alloc(st, sizeof(int));
     if (!st.d_start) return -1;
+    if (left > 0) {
+        st.rk_cache = (__half *)stream_alloc(st, (size_t)n_layers * (2 * (size_t)(left + st.q) - 1) * d_model * sizeof(__half));
+        if (!st.rk_cache) return -1;
+    }
     MB_CUDA(cudaMemsetAsync(st.d_start, 0, sizeof(int), stream));
     MB_CUDA(cudaMemsetAsync(st.k_cache, 0, kv * sizeof(__half), stream));
     MB_CUDA(cudaMemsetAsync(st.v_cache, 0, kv * sizeof(__half), stream));
@@ -325,8 +329,13 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
     H16 kn = ws.planes((size_t)M * d, false), vn = ws.planes((size_t)M * d, false);
     H16 pe = ws.planes((size_t)P * d), rk = ws.planes((size_t)P * d, false);
     if (!hA.lo || !hC.lo || !hF.lo || !qbuf || !h2 || !cbuf || !kn.hi || !vn.hi || !pe.lo || !rk.hi) return -1;
-    if (pos_emb(pe, K, d, stream)) return -1;
-    note_launch();
+    // full caches and a full-size chunk: the key count of every later step, whose rk the group keeps
+    const bool rk_keep = st.rk_cache && valid == st.left && Q == st.q;
+    const bool rk_have = rk_keep && st.rk_ready;
+    if (!rk_have) {
+        if (pos_emb(pe, K, d, stream)) return -1;
+        note_launch();
+    }
     const size_t attn_smem = ((size_t)K + 2 * dk + 32) * sizeof(float);
     if (attn_smem > 200 * 1024) { set_error("stream_step: context too long for the attention kernel"); return -1; }
     static PerDevice attn_smem_set = {};
@@ -348,15 +357,17 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
         const EncLayer &L = layers[li];
         __half *kc = st.k_cache + (size_t)li * S * leftn * d, *vc = st.v_cache + (size_t)li * S * leftn * d;
         float *cc = st.conv_cache + (size_t)li * S * (conv_k - 1) * d;
-        if (layer_norm(x, L.ln_ff1_w, L.ln_ff1_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        // (with the tails, a layer's opening LayerNorm comes out of the contraction that closes the layer before it)
+        if ((!tail || li == 0) && layer_norm(x, L.ln_ff1_w, L.ln_ff1_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
         if (gemm(hA, d, L.ff1_w1, st_epi(OUT_H16, ACT_SILU, 1.f, L.ff1_w1.bias, nullptr, 0, hF, F), M, st.few_rows)) return -1;
         if (gemm(hF, F, L.ff1_w2, resid(0.5f, L.ff1_w2.bias, L.ln_att_w, L.ln_att_b), M, st.few_rows)) return -1;
         if (!tail && layer_norm(x, L.ln_att_w, L.ln_att_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
         if (gemm(hA, d, L.q_w, st_epi(OUT_F32, ACT_NONE, 1.f, L.q_w.bias, qbuf, d), M, st.few_rows)) return -1;
         if (gemm(hA, d, L.k_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.k_w.bias, nullptr, 0, kn, d), M, st.few_rows)) return -1;
         if (gemm(hA, d, L.v_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.v_w.bias, nullptr, 0, vn, d), M, st.few_rows)) return -1;
-        if (gemm(pe, d, L.relk, st_epi(OUT_H16, ACT_NONE, 1.f, nullptr, nullptr, 0, rk, d), P)) return -1;
-        stream_attn_kernel<<<dim3(H, S), 128, attn_smem, stream>>>(qbuf, kn.hi, vn.hi, kc, vc, rk.hi, L.bias_u, L.bias_v, hC, Q, valid,
+        __half *rk_l = rk_keep ? st.rk_cache + (size_t)li * P * d : rk.hi;
+        if (!rk_have && gemm(pe, d, L.relk, st_epi(OUT_H16, ACT_NONE, 1.f, nullptr, nullptr, 0, H16{rk_l, nullptr}, d), P)) return -1;
+        stream_attn_kernel<<<dim3(H, S), 128, attn_smem, stream>>>(qbuf, kn.hi, vn.hi, kc, vc, rk_l, L.bias_u, L.bias_v, hC, Q, valid,
                                                                    st.d_start, leftn, d, dk);
         if (st.left > 0)
             stream_kv_update_kernel<<<(unsigned)cdiv((size_t)M * d, TPB), TPB, 0, stream>>>(kn.hi, vn.hi, kc, vc, S, Q, valid, st.d_start, st.left, d);
@@ -370,9 +381,16 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
         if (gemm(hC, d, L.pw2_w, resid(1.f, L.pw2_w.bias, L.ln_ff2_w, L.ln_ff2_b), M, st.few_rows)) return -1;
         if (!tail && layer_norm(x, L.ln_ff2_w, L.ln_ff2_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
         if (gemm(hA, d, L.ff2_w1, st_epi(OUT_H16, ACT_SILU, 1.f, L.ff2_w1.bias, nullptr, 0, hF, F), M, st.few_rows)) return -1;
-        if (gemm(hF, F, L.ff2_w2, st_epi(OUT_RESID, ACT_NONE, 0.5f, L.ff2_w2.bias, x, d), M, st.few_rows)) return -1;
-        if (layer_norm(x, L.ln_out_w, L.ln_out_b, x, none, M, d, ACT_NONE, stream)) return -1;
-        note_launch(tail ? 6 : 9);
+        {
+            GemmEpilogue e = st_epi(OUT_RESID, ACT_NONE, 0.5f, L.ff2_w2.bias, x, d);
+            if (tail) {                    // x = LN_out(x) in place, then the next layer's LN_ff1 of it into hA
+                e.ln_w = L.ln_out_w; e.ln_b = L.ln_out_b; e.ln_count = st.ln_count;
+                if (li + 1 < n_layers) { e.ln2_w = layers[li + 1].ln_ff1_w; e.ln2_b = layers[li + 1].ln_ff1_b; e.ln_hi = hA.hi; e.ln_lo = hA.lo; }
+            }
+            if (gemm(hF, F, L.ff2_w2, e, M, st.few_rows)) return -1;
+        }
+        if (!tail && layer_norm(x, L.ln_out_w, L.ln_out_b, x, none, M, d, ACT_NONE, stream)) return -1;
+        note_launch(tail ? (li == 0 ? 5 : 4) : 9);
     }
     {   // rows are stream-major: Q rows per stream, each stream with its own prompt id
         const std::vector<int> post_lens((size_t)st.S, Q);
@@ -386,6 +404,7 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
         note_launch();
         st.valid = total < st.left ? total : st.left;
     }
+    if (rk_keep) st.rk_ready = true;
     st.first = 0;
     ws.off = mark;
     return Q;
