@@ -70,12 +70,16 @@ __global__ void ss_stream_cache_kernel(const float *__restrict__ x, float *__res
 
 // ---- attention of the chunk's Q rows over [valid cached frames ; chunk], no mask. Grid (H, S), 128 threads.
 // score[t][j] = ((q_t + u) . k_j + (q_t + v) . rk[K-1-valid-t+j]) / sqrt(dk); ctx planes [S*Q, d].
+// update != 0: afterwards the chunk's k / v rows of this head go to their ring slots (update_kv_cache,
+// src/encoder.c:763-776) — the columns of head h of stream s are read by this block alone, so it may overwrite them
+// once its own reads are done.
 __global__ void stream_attn_kernel(const float *__restrict__ q, const __half *__restrict__ kn, const __half *__restrict__ vn,
-                                   const __half *__restrict__ kc, const __half *__restrict__ vc, const __half *__restrict__ rk,
+                                   __half *kc, __half *vc, const __half *__restrict__ rk,
                                    const float *__restrict__ bias_u, const float *__restrict__ bias_v, H16 ctx, int Q, int valid,
-                                   const int *__restrict__ d_start, int left, int d, int dk) {
+                                   const int *__restrict__ d_start, int left, int d, int dk, int update) {
     extern __shared__ float sm[];
     chain_trigger();                   // a chained contraction behind this kernel may start fetching its weights
+    chain_wait();
     const int K = valid + Q, start = *d_start;
     float *sc = sm;                    // [K]
     float *qu = sc + K, *qv = qu + dk; // [dk] each
@@ -133,20 +137,14 @@ __global__ void stream_attn_kernel(const float *__restrict__ q, const __half *__
         }
         __syncthreads();
     }
-}
-
-// new k / v rows of the chunk into their ring slots (update_kv_cache, src/encoder.c:763-776)
-__global__ void stream_kv_update_kernel(const __half *__restrict__ kn, const __half *__restrict__ vn, __half *__restrict__ kc,
-                                        __half *__restrict__ vc, int S, int Q, int valid, const int *__restrict__ d_start, int left, int d) {
-    chain_trigger();                   // a chained contraction behind this kernel may start fetching its weights
-    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
-    if (idx >= (size_t)S * Q * d) return;
-    const int start = *d_start;
-    const int i = (int)(idx % d);
-    const int t = (int)((idx / d) % Q), s = (int)(idx / ((size_t)d * Q));
-    const int slot = (start + valid + t) % left;
-    kc[((size_t)s * left + slot) * d + i] = kn[idx];
-    vc[((size_t)s * left + slot) * d + i] = vn[idx];
+    if (update) {
+        for (int idx = threadIdx.x; idx < Q * dk; idx += blockDim.x) {
+            const int t = idx / dk, i = idx - t * dk;
+            const size_t src = ((size_t)s * Q + t) * d + h * dk + i, dst = cbase + (size_t)((start + valid + t) % left) * d + h * dk + i;
+            kc[dst] = kn[src];
+            vc[dst] = vn[src];
+        }
+    }
 }
 
 // after the last layer: the ring's oldest frame moves on by the frames that were overwritten
@@ -160,6 +158,8 @@ __global__ void stream_advance_kernel(int *d_start, int valid, int Q, int left) 
 template <int KMAX>
 __global__ void stream_conv_kernel(const float *__restrict__ h2, const float *__restrict__ dw_w, float *__restrict__ cache,
                                    float *__restrict__ out, int S, int Q, int d, int k) {
+    chain_trigger();
+    chain_wait();
     const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     if (idx >= (size_t)S * d) return;
     const int s = (int)(idx / d), i = (int)(idx % d);
@@ -358,28 +358,25 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
         __half *kc = st.k_cache + (size_t)li * S * leftn * d, *vc = st.v_cache + (size_t)li * S * leftn * d;
         float *cc = st.conv_cache + (size_t)li * S * (conv_k - 1) * d;
         // (with the tails, a layer's opening LayerNorm comes out of the contraction that closes the layer before it)
-        if ((!tail || li == 0) && layer_norm(x, L.ln_ff1_w, L.ln_ff1_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if ((!tail || li == 0) && layer_norm(x, L.ln_ff1_w, L.ln_ff1_b, nullptr, hA, M, d, ACT_NONE, stream, true)) return -1;
         if (gemm(hA, d, L.ff1_w1, st_epi(OUT_H16, ACT_SILU, 1.f, L.ff1_w1.bias, nullptr, 0, hF, F), M, st.few_rows)) return -1;
         if (gemm(hF, F, L.ff1_w2, resid(0.5f, L.ff1_w2.bias, L.ln_att_w, L.ln_att_b), M, st.few_rows)) return -1;
-        if (!tail && layer_norm(x, L.ln_att_w, L.ln_att_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (!tail && layer_norm(x, L.ln_att_w, L.ln_att_b, nullptr, hA, M, d, ACT_NONE, stream, true)) return -1;
         if (gemm(hA, d, L.q_w, st_epi(OUT_F32, ACT_NONE, 1.f, L.q_w.bias, qbuf, d), M, st.few_rows)) return -1;
         if (gemm(hA, d, L.k_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.k_w.bias, nullptr, 0, kn, d), M, st.few_rows)) return -1;
         if (gemm(hA, d, L.v_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.v_w.bias, nullptr, 0, vn, d), M, st.few_rows)) return -1;
         __half *rk_l = rk_keep ? st.rk_cache + (size_t)li * P * d : rk.hi;
         if (!rk_have && gemm(pe, d, L.relk, st_epi(OUT_H16, ACT_NONE, 1.f, nullptr, nullptr, 0, H16{rk_l, nullptr}, d), P)) return -1;
-        stream_attn_kernel<<<dim3(H, S), 128, attn_smem, stream>>>(qbuf, kn.hi, vn.hi, kc, vc, rk_l, L.bias_u, L.bias_v, hC, Q, valid,
-                                                                   st.d_start, leftn, d, dk);
-        if (st.left > 0)
-            stream_kv_update_kernel<<<(unsigned)cdiv((size_t)M * d, TPB), TPB, 0, stream>>>(kn.hi, vn.hi, kc, vc, S, Q, valid, st.d_start, st.left, d);
-        MB_CUDA(cudaGetLastError());
+        MB_CUDA(launch_kernel(stream_attn_kernel, dim3(H, S), dim3(128), attn_smem, stream, true, 1, (const float *)qbuf, (const __half *)kn.hi, (const __half *)vn.hi,
+                              kc, vc, (const __half *)rk_l, L.bias_u, L.bias_v, hC, Q, valid, (const int *)st.d_start, leftn, d, dk, st.left > 0 ? 1 : 0));
         if (gemm(hC, d, L.o_w, resid(1.f, L.o_w.bias, L.ln_conv_w, L.ln_conv_b), M, st.few_rows)) return -1;
-        if (!tail && layer_norm(x, L.ln_conv_w, L.ln_conv_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (!tail && layer_norm(x, L.ln_conv_w, L.ln_conv_b, nullptr, hA, M, d, ACT_NONE, stream, true)) return -1;
         if (gemm(hA, d, L.pw1_w, st_epi(OUT_F32, ACT_NONE, 1.f, L.pw1_w.bias, h2, 2 * d), M, st.few_rows)) return -1;
-        stream_conv_kernel<STREAM_CONV_MAX><<<(unsigned)cdiv((size_t)S * d, 128), 128, 0, stream>>>(h2, L.dw_w, cc, cbuf, S, Q, d, conv_k);
-        MB_CUDA(cudaGetLastError());
-        if (layer_norm(cbuf, L.cnorm_w, L.cnorm_b, nullptr, hC, M, d, ACT_SILU, stream)) return -1;
+        MB_CUDA(launch_kernel(stream_conv_kernel<STREAM_CONV_MAX>, dim3((unsigned)cdiv((size_t)S * d, 128)), dim3(128), 0, stream, true, 1, (const float *)h2, L.dw_w, cc, cbuf,
+                              S, Q, d, conv_k));
+        if (layer_norm(cbuf, L.cnorm_w, L.cnorm_b, nullptr, hC, M, d, ACT_SILU, stream, true)) return -1;
         if (gemm(hC, d, L.pw2_w, resid(1.f, L.pw2_w.bias, L.ln_ff2_w, L.ln_ff2_b), M, st.few_rows)) return -1;
-        if (!tail && layer_norm(x, L.ln_ff2_w, L.ln_ff2_b, nullptr, hA, M, d, ACT_NONE, stream)) return -1;
+        if (!tail && layer_norm(x, L.ln_ff2_w, L.ln_ff2_b, nullptr, hA, M, d, ACT_NONE, stream, true)) return -1;
         if (gemm(hA, d, L.ff2_w1, st_epi(OUT_H16, ACT_SILU, 1.f, L.ff2_w1.bias, nullptr, 0, hF, F), M, st.few_rows)) return -1;
         {
             GemmEpilogue e = st_epi(OUT_RESID, ACT_NONE, 0.5f, L.ff2_w2.bias, x, d);
@@ -389,8 +386,8 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
             }
             if (gemm(hF, F, L.ff2_w2, e, M, st.few_rows)) return -1;
         }
-        if (!tail && layer_norm(x, L.ln_out_w, L.ln_out_b, x, none, M, d, ACT_NONE, stream)) return -1;
-        note_launch(tail ? (li == 0 ? 5 : 4) : 9);
+        if (!tail && layer_norm(x, L.ln_out_w, L.ln_out_b, x, none, M, d, ACT_NONE, stream, true)) return -1;
+        note_launch((tail ? (li == 0 ? 4 : 3) : 8));
     }
     {   // rows are stream-major: Q rows per stream, each stream with its own prompt id
         const std::vector<int> post_lens((size_t)st.S, Q);
