@@ -33,19 +33,20 @@ __device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) 
 }
 
 // Causal self-attention of one new position (src/decoder_aed.c:191-196 with attend, :117-131):
-// appends this step's k, v to the cache and attends over positions 0..p. Grid (H, B), 128 threads.
+// appends this step's k, v to the cache and attends over positions 0..p. Grid (H, B), SELF_WARPS warps.
 // qkv [B, 3D] = (q | k | v) with biases already added; cache [B, max_len, D] each. dk is a multiple of 4.
 // Scores: a warp takes a key at a time, a lane four consecutive elements of it (one 16-byte load; four keys in
-// flight). Context: warp w sums the keys j = w, w + 4, ... for the lane's four columns; the four partial sums are
+// flight). Context: warp w sums the keys j = w, w + SELF_WARPS, ... for the lane's four columns; the partial sums are
 // added in warp order.
-__global__ void __launch_bounds__(128)
+static constexpr int SELF_WARPS = 16;
+__global__ void __launch_bounds__(SELF_WARPS * 32)
 aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, float *__restrict__ cv,
                      const int *__restrict__ pd, int max_len, int D, int dk, H16 out) {
     extern __shared__ float sm[];
     chain_trigger();
     chain_wait();
     const int p = *pd;
-    float *sc = sm, *q = sm + ((max_len + 3) & ~3), *red = q + dk, *part = red + 32;     // part: [4][dk]
+    float *sc = sm, *q = sm + ((max_len + 3) & ~3), *red = q + dk, *part = red + 32;     // part: [SELF_WARPS][dk]
     const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float *row = qkv + (size_t)b * 3 * D + h * dk;
     float *K = ck + (size_t)b * max_len * D + h * dk, *V = cv + (size_t)b * max_len * D + h * dk;
@@ -56,7 +57,7 @@ aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, floa
     }
     __syncthreads();
     const float scale = 1.0f / sqrtf((float)dk);
-    for (int j0 = warp * 4; j0 <= p; j0 += 16) {
+    for (int j0 = warp * 4; j0 <= p; j0 += 4 * SELF_WARPS) {
         float s[4] = {0.f, 0.f, 0.f, 0.f};
         for (int i0 = lane * 4; i0 < dk; i0 += 128) {
             float4 k[4];
@@ -83,17 +84,17 @@ aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, floa
     for (int c0 = lane * 4; c0 < dk; c0 += 128) {
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
         int j = warp;
-        for (; j + 12 <= p; j += 16) {
+        for (; j + 3 * SELF_WARPS <= p; j += 4 * SELF_WARPS) {
             float4 v[4];
 #pragma unroll
-            for (int u = 0; u < 4; u++) v[u] = *reinterpret_cast<const float4 *>(V + (size_t)(j + 4 * u) * D + c0);
+            for (int u = 0; u < 4; u++) v[u] = *reinterpret_cast<const float4 *>(V + (size_t)(j + SELF_WARPS * u) * D + c0);
 #pragma unroll
             for (int u = 0; u < 4; u++) {
-                const float w = sc[j + 4 * u] * inv;
+                const float w = sc[j + SELF_WARPS * u] * inv;
                 o.x = fmaf(w, v[u].x, o.x); o.y = fmaf(w, v[u].y, o.y); o.z = fmaf(w, v[u].z, o.z); o.w = fmaf(w, v[u].w, o.w);
             }
         }
-        for (; j <= p; j += 4) {
+        for (; j <= p; j += SELF_WARPS) {
             const float4 v = *reinterpret_cast<const float4 *>(V + (size_t)j * D + c0);
             const float w = sc[j] * inv;
             o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
@@ -102,7 +103,8 @@ aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, floa
     }
     __syncthreads();
     for (int i = threadIdx.x; i < dk; i += blockDim.x) {
-        const float t = ((part[i] + part[dk + i]) + part[2 * dk + i]) + part[3 * dk + i];
+        float t = part[i];
+        for (int w = 1; w < SELF_WARPS; w++) t += part[w * dk + i];
         __half hi, lo;
         split_h16(t, hi, lo);
         out.hi[(size_t)b * D + h * dk + i] = hi;
@@ -127,6 +129,7 @@ __device__ __forceinline__ float4 ld_h4(const __half *hi, const __half *lo, size
     return r;
 }
 static constexpr int CROSS_WARPS = 16;
+static constexpr int CROSS_KU = 8;              // key rows a warp has in flight
 __global__ void __launch_bounds__(CROSS_WARPS * 32)
 aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ kv_hi, const __half *__restrict__ kv_lo,
                       const int *__restrict__ enc_off, const int *__restrict__ enc_len, int max_T, int D, int dk, H16 out) {
@@ -140,21 +143,23 @@ aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ k
     for (int i = threadIdx.x; i < dk; i += blockDim.x) q[i] = qm[(size_t)b * D + h * dk + i];
     __syncthreads();
     const float scale = 1.0f / sqrtf((float)dk);
-    for (int j0 = warp * 4; j0 < T; j0 += 4 * CROSS_WARPS) {
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int i0 = lane * 4; i0 < dk; i0 += 128) {
-            float4 k[4];
+    for (int j0 = warp * CROSS_KU; j0 < T; j0 += CROSS_KU * CROSS_WARPS) {
+        float s[CROSS_KU];
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < CROSS_KU; u++) s[u] = 0.f;
+        for (int i0 = lane * 4; i0 < dk; i0 += 128) {
+            float4 k[CROSS_KU];
+#pragma unroll
+            for (int u = 0; u < CROSS_KU; u++) {
                 const int j = j0 + u < T ? j0 + u : T - 1;
                 k[u] = ld_h4(kv_hi, kv_lo, (r0 + j) * ld + h * dk + i0);
             }
             const float4 qq = *reinterpret_cast<const float4 *>(q + i0);
 #pragma unroll
-            for (int u = 0; u < 4; u++) s[u] = fmaf(qq.x, k[u].x, fmaf(qq.y, k[u].y, fmaf(qq.z, k[u].z, fmaf(qq.w, k[u].w, s[u]))));
+            for (int u = 0; u < CROSS_KU; u++) s[u] = fmaf(qq.x, k[u].x, fmaf(qq.y, k[u].y, fmaf(qq.z, k[u].z, fmaf(qq.w, k[u].w, s[u]))));
         }
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
+        for (int u = 0; u < CROSS_KU; u++) {
             const float t = warp_sum(s[u]);
             if (lane == 0 && j0 + u < T) sc[j0 + u] = t * scale;
         }
@@ -168,17 +173,17 @@ aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ k
     sum = block_reduce(sum, red, false);
     const float inv = 1.0f / sum;
     // context: warp w sums the keys j = w, w + CROSS_WARPS, ... for the lane's four columns (8-byte loads of each plane,
-    // four keys in flight); the partial sums are added in warp order
+    // CROSS_KU keys in flight); the partial sums are added in warp order
     for (int c0 = lane * 4; c0 < dk; c0 += 128) {
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
         const size_t col = D + h * dk + c0;
         int j = warp;
-        for (; j + 3 * CROSS_WARPS < T; j += 4 * CROSS_WARPS) {
-            float4 v[4];
+        for (; j + (CROSS_KU - 1) * CROSS_WARPS < T; j += CROSS_KU * CROSS_WARPS) {
+            float4 v[CROSS_KU];
 #pragma unroll
-            for (int u = 0; u < 4; u++) v[u] = ld_h4(kv_hi, kv_lo, (r0 + j + CROSS_WARPS * u) * ld + col);
+            for (int u = 0; u < CROSS_KU; u++) v[u] = ld_h4(kv_hi, kv_lo, (r0 + j + CROSS_WARPS * u) * ld + col);
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < CROSS_KU; u++) {
                 const float w = sc[j + CROSS_WARPS * u] * inv;
                 o.x = fmaf(w, v[u].x, o.x); o.y = fmaf(w, v[u].y, o.y); o.z = fmaf(w, v[u].z, o.z); o.w = fmaf(w, v[u].w, o.w);
             }
@@ -304,7 +309,7 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     MB_CUDA(cudaMemcpyAsync(st, hst.data(), hst.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
     MB_CUDA(cudaMemcpyAsync(d_prompts, hp.data(), hp.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
     MB_CUDA(cudaMemcpyAsync(d_off, ho.data(), ho.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
-    const size_t self_smem = ((size_t)max_len + 4 + 5 * (size_t)dk + 32) * sizeof(float);
+    const size_t self_smem = ((size_t)max_len + 4 + (1 + SELF_WARPS) * (size_t)dk + 32) * sizeof(float);
     const int cross_threads = CROSS_WARPS * 32;
     const size_t cross_smem = ((size_t)max_T + 4 + (1 + CROSS_WARPS) * (size_t)dk + 32) * sizeof(float);
     if (self_smem > 200 * 1024 || cross_smem > 200 * 1024) { set_error("aed_decode: sequence too long for the attention kernels"); return -1; }
@@ -335,7 +340,7 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
             // LayerNorm after the last contraction of this layer: the next layer's first one, or the final one
             const float *nw = l + 1 < L ? aed_layers[l + 1].ln_self_w : aed_fin_w, *nb = l + 1 < L ? aed_layers[l + 1].ln_self_b : aed_fin_b;
             if (gemm(xn, D, A.sqkv, aed_epi(OUT_F32, ACT_NONE, 1.f, A.sqkv_b, qkv, 3 * D), B, true)) return -1;
-            MB_CUDA(launch_kernel(aed_self_attn_kernel, dim3(H, B), dim3(128), self_smem, stream, true, 1, (const float *)qkv, K, Vc, pd, max_len, D, dk, att));
+            MB_CUDA(launch_kernel(aed_self_attn_kernel, dim3(H, B), dim3(SELF_WARPS * 32), self_smem, stream, true, 1, (const float *)qkv, K, Vc, pd, max_len, D, dk, att));
             if (gemm(att, D, A.so, resid(A.so_b, A.ln_cross_w, A.ln_cross_b), B, true)) return -1;
             if (!ln_tail && layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream, true)) return -1;
             if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B, true)) return -1;

@@ -68,25 +68,40 @@ __global__ void ss_stream_cache_kernel(const float *__restrict__ x, float *__res
     cache[idx] = x[((size_t)s * T + (T - 1)) * W + i];
 }
 
-// ---- attention of the chunk's Q rows over [valid cached frames ; chunk], no mask. Grid (H, S), 128 threads.
-// score[t][j] = ((q_t + u) . k_j + (q_t + v) . rk[K-1-valid-t+j]) / sqrt(dk); ctx planes [S*Q, d].
+// ---- attention of the chunk's Q rows over [valid cached frames ; chunk], no mask. Grid (H, S), STREAM_ATTN_WARPS warps.
+// score[t][j] = ((q_t + u) . k_j + (q_t + v) . rk[K-1-valid-t+j]) / sqrt(dk); ctx planes [S*Q, d]. dk is a multiple of 4.
+// Scores: a warp takes four keys at a time, a lane four consecutive elements of each k and rk row (8-byte loads, eight in
+// flight per lane). Context: warp w sums the keys j = w, w + warps, ... for the lane's four columns (four keys in flight);
+// the partial sums are added in warp order.
 // update != 0: afterwards the chunk's k / v rows of this head go to their ring slots (update_kv_cache,
 // src/encoder.c:763-776) — the columns of head h of stream s are read by this block alone, so it may overwrite them
 // once its own reads are done.
-__global__ void stream_attn_kernel(const float *__restrict__ q, const __half *__restrict__ kn, const __half *__restrict__ vn,
-                                   __half *kc, __half *vc, const __half *__restrict__ rk,
-                                   const float *__restrict__ bias_u, const float *__restrict__ bias_v, H16 ctx, int Q, int valid,
-                                   const int *__restrict__ d_start, int left, int d, int dk, int update) {
+static constexpr int STREAM_ATTN_WARPS = 8;
+__device__ __forceinline__ float4 ld_half4(const __half *p) {
+    const uint2 a = *reinterpret_cast<const uint2 *>(p);
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&a.x)), hi = __half22float2(*reinterpret_cast<const __half2 *>(&a.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__global__ void __launch_bounds__(STREAM_ATTN_WARPS * 32)
+stream_attn_kernel(const float *__restrict__ q, const __half *__restrict__ kn, const __half *__restrict__ vn,
+                   __half *kc, __half *vc, const __half *__restrict__ rk,
+                   const float *__restrict__ bias_u, const float *__restrict__ bias_v, H16 ctx, int Q, int valid,
+                   const int *__restrict__ d_start, int left, int d, int dk, int update) {
     extern __shared__ float sm[];
     chain_trigger();                   // a chained contraction behind this kernel may start fetching its weights
     chain_wait();
+    constexpr int NW = STREAM_ATTN_WARPS;
     const int K = valid + Q, start = *d_start;
-    float *sc = sm;                    // [K]
-    float *qu = sc + K, *qv = qu + dk; // [dk] each
-    float *red = qv + dk;              // [32]
-    const int h = blockIdx.x, s = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float *sc = sm;                                    // [K] (rounded up to a multiple of 4)
+    float *qu = sc + ((K + 3) & ~3), *qv = qu + dk;    // [dk] each
+    float *red = qv + dk;                              // [32]
+    float *part = red + 32;                            // [NW][dk]
+    const int h = blockIdx.x, s = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float scale = 1.0f / sqrtf((float)dk);
-    const size_t cbase = (size_t)s * left * d;
+    const size_t cbase = (size_t)s * left * d + h * dk, nbase = (size_t)s * Q * d + h * dk;
+    // row j of the keys / values: a cached frame in its ring slot, or a row of the chunk
+    auto krow = [&](int j) { int x = start + j; if (x >= left) x -= left; return j < valid ? kc + cbase + (size_t)x * d : kn + nbase + (size_t)(j - valid) * d; };
+    auto vrow = [&](int j) { int x = start + j; if (x >= left) x -= left; return j < valid ? vc + cbase + (size_t)x * d : vn + nbase + (size_t)(j - valid) * d; };
     for (int t = 0; t < Q; t++) {
         const size_t row = (size_t)s * Q + t;
         for (int i = threadIdx.x; i < dk; i += blockDim.x) {
@@ -96,16 +111,30 @@ __global__ void stream_attn_kernel(const float *__restrict__ q, const __half *__
         }
         __syncthreads();
         const int base = K - 1 - valid - t;
-        for (int j = warp; j < K; j += nw) {
-            const __half *kj = j < valid ? kc + cbase + (size_t)((start + j) % left) * d : kn + ((size_t)s * Q + (j - valid)) * d;
-            const __half *rj = rk + (size_t)(base + j) * d;
-            float a = 0.f;
-            for (int i = lane; i < dk; i += 32) {
-                a = fmaf(qu[i], __half2float(kj[h * dk + i]), a);
-                a = fmaf(qv[i], __half2float(rj[h * dk + i]), a);
+        for (int j0 = warp * 4; j0 < K; j0 += 4 * NW) {
+            float a[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int i0 = lane * 4; i0 < dk; i0 += 128) {
+                float4 kk[4], rr[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int j = j0 + u < K ? j0 + u : K - 1;
+                    kk[u] = ld_half4(krow(j) + i0);
+                    rr[u] = ld_half4(rk + (size_t)(base + j) * d + h * dk + i0);
+                }
+                const float4 u4 = *reinterpret_cast<const float4 *>(qu + i0), v4 = *reinterpret_cast<const float4 *>(qv + i0);
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    a[u] = fmaf(u4.x, kk[u].x, a[u]); a[u] = fmaf(v4.x, rr[u].x, a[u]);
+                    a[u] = fmaf(u4.y, kk[u].y, a[u]); a[u] = fmaf(v4.y, rr[u].y, a[u]);
+                    a[u] = fmaf(u4.z, kk[u].z, a[u]); a[u] = fmaf(v4.z, rr[u].z, a[u]);
+                    a[u] = fmaf(u4.w, kk[u].w, a[u]); a[u] = fmaf(v4.w, rr[u].w, a[u]);
+                }
             }
-            a = warp_sum(a);
-            if (lane == 0) sc[j] = a * scale;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const float r = warp_sum(a[u]);
+                if (lane == 0 && j0 + u < K) sc[j0 + u] = r * scale;
+            }
         }
         __syncthreads();
         float m = -INFINITY;
@@ -114,7 +143,7 @@ __global__ void stream_attn_kernel(const float *__restrict__ q, const __half *__
         if (lane == 0) red[warp] = m;
         __syncthreads();
         m = red[0];
-        for (int i = 1; i < nw; i++) m = fmaxf(m, red[i]);
+        for (int i = 1; i < NW; i++) m = fmaxf(m, red[i]);
         __syncthreads();
         float sum = 0.f;
         for (int j = threadIdx.x; j < K; j += blockDim.x) { const float e = expf(sc[j] - m); sc[j] = e; sum += e; }
@@ -122,14 +151,32 @@ __global__ void stream_attn_kernel(const float *__restrict__ q, const __half *__
         if (lane == 0) red[warp] = sum;
         __syncthreads();
         sum = 0.f;
-        for (int i = 0; i < nw; i++) sum += red[i];
+        for (int i = 0; i < NW; i++) sum += red[i];
         const float inv = 1.0f / sum;
-        for (int i = threadIdx.x; i < dk; i += blockDim.x) {
-            float o = 0.f;
-            for (int j = 0; j < K; j++) {
-                const __half *vj = j < valid ? vc + cbase + (size_t)((start + j) % left) * d : vn + ((size_t)s * Q + (j - valid)) * d;
-                o = fmaf(sc[j] * inv, __half2float(vj[h * dk + i]), o);
+        for (int c0 = lane * 4; c0 < dk; c0 += 128) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            int j = warp;
+            for (; j + 3 * NW < K; j += 4 * NW) {
+                float4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) v[u] = ld_half4(vrow(j + NW * u) + c0);
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const float w = sc[j + NW * u] * inv;
+                    o.x = fmaf(w, v[u].x, o.x); o.y = fmaf(w, v[u].y, o.y); o.z = fmaf(w, v[u].z, o.z); o.w = fmaf(w, v[u].w, o.w);
+                }
             }
+            for (; j < K; j += NW) {
+                const float4 v = ld_half4(vrow(j) + c0);
+                const float w = sc[j] * inv;
+                o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
+            }
+            *reinterpret_cast<float4 *>(part + warp * dk + c0) = o;
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+            float o = part[i];
+            for (int w = 1; w < NW; w++) o += part[w * dk + i];
             __half hi, lo;
             split_h16(o, hi, lo);
             ctx.hi[row * d + h * dk + i] = hi;
@@ -140,9 +187,10 @@ __global__ void stream_attn_kernel(const float *__restrict__ q, const __half *__
     if (update) {
         for (int idx = threadIdx.x; idx < Q * dk; idx += blockDim.x) {
             const int t = idx / dk, i = idx - t * dk;
-            const size_t src = ((size_t)s * Q + t) * d + h * dk + i, dst = cbase + (size_t)((start + valid + t) % left) * d + h * dk + i;
-            kc[dst] = kn[src];
-            vc[dst] = vn[src];
+            int x = start + valid + t;
+            x %= left;
+            kc[cbase + (size_t)x * d + i] = kn[nbase + (size_t)t * d + i];
+            vc[cbase + (size_t)x * d + i] = vn[nbase + (size_t)t * d + i];
         }
     }
 }
@@ -336,7 +384,8 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
         if (pos_emb(pe, K, d, stream)) return -1;
         note_launch();
     }
-    const size_t attn_smem = ((size_t)K + 2 * dk + 32) * sizeof(float);
+    const size_t attn_smem = ((size_t)K + 4 + (2 + STREAM_ATTN_WARPS) * (size_t)dk + 32) * sizeof(float);
+    if (dk % 4) { set_error("stream_step: head width %d must be a multiple of 4", dk); return -1; }
     if (attn_smem > 200 * 1024) { set_error("stream_step: context too long for the attention kernel"); return -1; }
     static PerDevice attn_smem_set = {};
     int cur_dev = 0;
@@ -367,7 +416,7 @@ int Model::stream_step_eager(StreamState &st, const float *mel, int n_mel, int i
         if (gemm(hA, d, L.v_w, st_epi(OUT_H16, ACT_NONE, 1.f, L.v_w.bias, nullptr, 0, vn, d), M, st.few_rows)) return -1;
         __half *rk_l = rk_keep ? st.rk_cache + (size_t)li * P * d : rk.hi;
         if (!rk_have && gemm(pe, d, L.relk, st_epi(OUT_H16, ACT_NONE, 1.f, nullptr, nullptr, 0, H16{rk_l, nullptr}, d), P)) return -1;
-        MB_CUDA(launch_kernel(stream_attn_kernel, dim3(H, S), dim3(128), attn_smem, stream, true, 1, (const float *)qbuf, (const __half *)kn.hi, (const __half *)vn.hi,
+        MB_CUDA(launch_kernel(stream_attn_kernel, dim3(H, S), dim3(STREAM_ATTN_WARPS * 32), attn_smem, stream, true, 1, (const float *)qbuf, (const __half *)kn.hi, (const __half *)vn.hi,
                               kc, vc, (const __half *)rk_l, L.bias_u, L.bias_v, hC, Q, valid, (const int *)st.d_start, leftn, d, dk, st.left > 0 ? 1 : 0));
         if (gemm(hC, d, L.o_w, resid(1.f, L.o_w.bias, L.ln_conv_w, L.ln_conv_b), M, st.few_rows)) return -1;
         if (!tail && layer_norm(x, L.ln_conv_w, L.ln_conv_b, nullptr, hA, M, d, ACT_NONE, stream, true)) return -1;
