@@ -1,5 +1,6 @@
-// Contraction for a handful of rows: out[m, n] = sum_k X[m, k] W[n, k], m < 128 — the linears of one decoder
-// position (mynah_asr_aed_decode, src/decoder_aed.c:183-228, calls mynah_asr_qmat_mul with one row per utterance).
+// Contraction for a handful of rows: out[m, n] = sum_k X[m, k] W[n, k], 128 rows per launch at most — the linears of one
+// decoder position (mynah_asr_aed_decode, src/decoder_aed.c:183-228, calls mynah_asr_qmat_mul with one row per
+// utterance) and of a streaming step of a small stream group (mynah_asr_enc_stream_step, src/encoder.c:826-866).
 //
 // With so few rows the work is streaming W once; the output has too few 128-wide tiles to occupy the device, and a
 // tile of the large-M kernel would spend most of its TMA traffic on zero-filled activation rows. So the roles are
@@ -11,6 +12,9 @@
 // the additions is fixed by the slice index and S depends only on the weight's shape, so an output row's bits do not
 // depend on how many rows share the launch. Operands are the same fp16 (hi, lo) planes and the same three products
 // per term (one in fast mode) as in gemm_tc.cu. No multicast; every CTA loads its own tiles.
+// The kernel is launched chained (common.cuh): its first ring of weight tiles is requested before it waits for the
+// kernel in front of it. Optionally the rows it completes are layer-normalised on the spot (GemmEpilogue::ln_*): per-row
+// counters tell the warp that stores a row's last tile, and that warp normalises the row.
 #include "gemm.h"
 #include "ln_row.cuh"
 
