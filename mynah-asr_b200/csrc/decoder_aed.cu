@@ -6,6 +6,7 @@
 // The large linears run on the tcgen05 contraction (model.cu); this file holds what sits
 // between them: embedding, the two single-query attentions and the greedy selection.
 #include "model.h"
+#include "ln_row.cuh"
 
 namespace mb {
 
@@ -41,11 +42,11 @@ __device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) 
 static constexpr int SELF_WARPS = 16;
 __global__ void __launch_bounds__(SELF_WARPS * 32)
 aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, float *__restrict__ cv,
-                     const int *__restrict__ pd, int max_len, int D, int dk, H16 out) {
+                     const int *__restrict__ pd, int pd_stride, int max_len, int D, int dk, H16 out) {
     extern __shared__ float sm[];
     chain_trigger();
     chain_wait();
-    const int p = *pd;
+    const int p = pd[blockIdx.y * pd_stride];         // one position for all (stride 0) or a copy per utterance
     float *sc = sm, *q = sm + ((max_len + 3) & ~3), *red = q + dk, *part = red + 32;     // part: [SELF_WARPS][dk]
     const int h = blockIdx.x, b = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float *row = qkv + (size_t)b * 3 * D + h * dk;
@@ -232,6 +233,74 @@ __global__ void aed_select_kernel(const int *__restrict__ best, int eos, int cap
     if (fin) { done[b] = 1; atomicAdd(n_done, 1); }
 }
 
+// The turn from one position to the next in one launch, one block per utterance: greedy selection at position p
+// (src/decoder_aed.c:211-223; the first maximum of the logits row, as argmax_kernel finds it), then the next position's
+// input x[b] = emb[cur[b]] + pos[p + 1] (:183-184) with the embedding LayerNorm in place and the first layer's opening
+// LayerNorm into the planes xn — the same row arithmetic as ln_reg_kernel (ln_row). first != 0: no selection, position 0.
+// st: [cur | n_out | done | n_prompt | max_len | cap] x B, then n_done, (unused), .., then at 6B + 4 the position of
+// every utterance (all equal; a copy each, so that no block reads what another one writes).
+template <int NV>
+__global__ void __launch_bounds__(256)
+aed_next_kernel(const float *__restrict__ logits, int V, int eos, int cap_stride, int B, int *st, const int *__restrict__ prompts, int max_prompt,
+                int *__restrict__ tokens, const float *__restrict__ emb, const float *__restrict__ pos, int max_seq,
+                const float *__restrict__ ln1_w, const float *__restrict__ ln1_b, const float *__restrict__ ln2_w, const float *__restrict__ ln2_b,
+                float *__restrict__ x, H16 xn, int first) {
+    constexpr int D = NV * 128;
+    __shared__ float sv[256];
+    __shared__ int si[256];
+    chain_trigger();
+    chain_wait();
+    const int b = blockIdx.x;
+    int *cur = st, *n_out = st + B, *done = st + 2 * B, *n_prompt = st + 3 * B, *max_len = st + 4 * B, *n_done = st + 6 * B, *pos_b = st + 6 * B + 4;
+    int p = pos_b[b];
+    if (!first) {
+        const float *row = logits + (size_t)b * V;
+        float bv = -3.0e38f;
+        int bi = 0x7fffffff;
+        for (int k = threadIdx.x; k < V; k += 256) {
+            const float v = row[k];
+            if (v > bv) { bv = v; bi = k; }          // ascending k per thread: first maximum kept
+        }
+        sv[threadIdx.x] = bv; si[threadIdx.x] = bi;
+        __syncthreads();
+        for (int o = 128; o > 0; o >>= 1) {
+            if (threadIdx.x < o) {
+                const float v = sv[threadIdx.x + o];
+                const int i = si[threadIdx.x + o];
+                if (v > sv[threadIdx.x] || (v == sv[threadIdx.x] && i < si[threadIdx.x])) { sv[threadIdx.x] = v; si[threadIdx.x] = i; }
+            }
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) {
+            if (!done[b]) {
+                const int cap = st[5 * B + b];
+                bool fin = false;
+                if (p + 1 < n_prompt[b]) {
+                    cur[b] = prompts[b * max_prompt + p + 1];
+                } else {
+                    const int t = si[0];
+                    if (t == eos || n_out[b] >= cap) fin = true;
+                    else { tokens[(size_t)b * cap_stride + n_out[b]] = t; n_out[b]++; cur[b] = t; }
+                }
+                if (p + 1 >= max_len[b]) fin = true;
+                if (fin) { done[b] = 1; atomicAdd(n_done, 1); }
+            }
+            pos_b[b] = p + 1;
+        }
+        __syncthreads();                              // cur[b] is final for the threads below
+        p += 1;
+    }
+    if (p >= max_seq) return;                         // beyond the position table: no further position is decoded
+    const float *e = emb + (size_t)cur[b] * D, *pe = pos + (size_t)p * D;
+    for (int i = threadIdx.x; i < D; i += 256) x[(size_t)b * D + i] = e[i] + pe[i];
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        ln_row<NV, false>(x, ln1_w, ln1_b, x, nullptr, nullptr, nullptr, nullptr, b, ACT_NONE, threadIdx.x);
+        __syncwarp();
+        ln_row<NV, false>(x, ln2_w, ln2_b, nullptr, xn.hi, xn.lo, nullptr, nullptr, b, ACT_NONE, threadIdx.x);
+    }
+}
+
 static GemmEpilogue aed_epi(int mode, int act, float alpha, const float *bias, float *out, int ldo, H16 h = {nullptr, nullptr}, int ldh = 0) {
     GemmEpilogue e;
     memset(&e, 0, sizeof(e));
@@ -294,10 +363,10 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     float *x = ws.get<float>((size_t)B * D), *qkv = ws.get<float>((size_t)B * 3 * D), *q = ws.get<float>((size_t)B * D);
     float *logits = ws.get<float>((size_t)B * V);
     H16 xn = ws.planes((size_t)B * D), att = ws.planes((size_t)B * D), ff = ws.planes((size_t)B * F);
-    int *st = ws.get<int>(6 * (size_t)B + 4), *best = ws.get<int>(B), *d_prompts = ws.get<int>((size_t)B * max_prompt);
+    int *st = ws.get<int>(7 * (size_t)B + 4), *best = ws.get<int>(B), *d_prompts = ws.get<int>((size_t)B * max_prompt);
     int *d_tokens = ws.get<int>((size_t)B * capn), *d_off = ws.get<int>(2 * (size_t)B);
     if (!sk || !x || !qkv || !q || !logits || !xn.hi || !att.hi || !ff.hi || !st || !best || !d_prompts || !d_tokens || !d_off) return -1;
-    std::vector<int> hst(6 * (size_t)B + 4, 0), hp((size_t)B * max_prompt, 0), ho(2 * (size_t)B);
+    std::vector<int> hst(7 * (size_t)B + 4, 0), hp((size_t)B * max_prompt, 0), ho(2 * (size_t)B);
     for (int b = 0; b < B; b++) {
         hst[b] = prompts[b][0];                              // cur
         hst[3 * B + b] = (int)prompts[b].size();
@@ -329,18 +398,38 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
         if (ln_tail) { e.ln_w = nw; e.ln_b = nb; e.ln_hi = xn.hi; e.ln_lo = xn.lo; e.ln_count = ln_count; }
         return e;
     };
+    // With those widths the turn between positions is one launch too (aed_next_kernel): selection, next embedding and the
+    // two LayerNorms that open a position; it also prepares position 0 (first = 1).
+    auto next = [&](int first) -> int {
+#define AED_NEXT(NV) MB_CUDA(launch_kernel(aed_next_kernel<NV>, dim3(B), dim3(256), 0, stream, true, 1, (const float *)logits, V, eos, capn, B, st, (const int *)d_prompts, \
+                                           max_prompt, d_tokens, aed_emb, aed_pos, aed_max_seq, aed_embln_w, aed_embln_b, aed_layers[0].ln_self_w, aed_layers[0].ln_self_b, x, xn, first))
+        switch (D) {
+            case 128: AED_NEXT(1); break;
+            case 256: AED_NEXT(2); break;
+            case 512: AED_NEXT(4); break;
+            case 640: AED_NEXT(5); break;
+            case 1024: AED_NEXT(8); break;
+            default: AED_NEXT(16); break;            // 2048: the last of gemm_skinny_ln_width's widths
+        }
+#undef AED_NEXT
+        return 0;
+    };
+    const int *pos_b = st + 6 * B + 4;
     auto position = [&]() -> int {
         // every launch of a position is chained: blocks of the next kernel are placed while the one before drains
-        MB_CUDA(launch_kernel(aed_embed_kernel, dim3(B), dim3(128), 0, stream, true, 1, aed_emb, aed_pos, (const int *)st, pd, x, D));
-        if (layer_norm(x, aed_embln_w, aed_embln_b, x, H16{nullptr, nullptr}, B, D, 0, stream, true)) return -1;
-        if (layer_norm(x, aed_layers[0].ln_self_w, aed_layers[0].ln_self_b, nullptr, xn, B, D, 0, stream, true)) return -1;
+        if (!ln_tail) {
+            MB_CUDA(launch_kernel(aed_embed_kernel, dim3(B), dim3(128), 0, stream, true, 1, aed_emb, aed_pos, (const int *)st, pd, x, D));
+            if (layer_norm(x, aed_embln_w, aed_embln_b, x, H16{nullptr, nullptr}, B, D, 0, stream, true)) return -1;
+            if (layer_norm(x, aed_layers[0].ln_self_w, aed_layers[0].ln_self_b, nullptr, xn, B, D, 0, stream, true)) return -1;
+        }
         for (int l = 0; l < L; l++) {
             const AedLayer &A = aed_layers[l];
             float *K = sk + (size_t)(2 * l) * B * max_len * D, *Vc = K + (size_t)B * max_len * D;
             // LayerNorm after the last contraction of this layer: the next layer's first one, or the final one
             const float *nw = l + 1 < L ? aed_layers[l + 1].ln_self_w : aed_fin_w, *nb = l + 1 < L ? aed_layers[l + 1].ln_self_b : aed_fin_b;
             if (gemm(xn, D, A.sqkv, aed_epi(OUT_F32, ACT_NONE, 1.f, A.sqkv_b, qkv, 3 * D), B, true)) return -1;
-            MB_CUDA(launch_kernel(aed_self_attn_kernel, dim3(H, B), dim3(SELF_WARPS * 32), self_smem, stream, true, 1, (const float *)qkv, K, Vc, pd, max_len, D, dk, att));
+            MB_CUDA(launch_kernel(aed_self_attn_kernel, dim3(H, B), dim3(SELF_WARPS * 32), self_smem, stream, true, 1, (const float *)qkv, K, Vc,
+                                  ln_tail ? pos_b : pd, ln_tail ? 1 : 0, max_len, D, dk, att));
             if (gemm(att, D, A.so, resid(A.so_b, A.ln_cross_w, A.ln_cross_b), B, true)) return -1;
             if (!ln_tail && layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream, true)) return -1;
             if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B, true)) return -1;
@@ -354,13 +443,14 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
         }
         // the head is evaluated at prompt positions too (its result is ignored there): one graph for all positions
         if (gemm(xn, D, aed_head, aed_epi(OUT_F32, ACT_NONE, 1.f, aed_head_b, logits, V), B, true)) return -1;
+        if (ln_tail) return next(0);
         if (argmax_rows(logits, V, nullptr, B, V, best, stream, true)) return -1;
         MB_CUDA(launch_kernel(aed_select_kernel, dim3(1), dim3(((B + 31) / 32) * 32), 0, stream, true, 1, (const int *)best, eos, capn, B, st, (const int *)d_prompts,
                               max_prompt, d_tokens));
         return 0;
     };
-    const int lns_per_position = ln_tail ? 2 : 2 + 3 * L;
-    const int launches_per_position = 1 + lns_per_position + L * 8 + 3, gemms_per_position = 6 * L + 1;   // (the contraction wrapper counts its own launches)
+    if (ln_tail && next(1)) return -1;                 // x and xn of position 0
+    const int launches_per_position = ln_tail ? L * 8 + 2 : 1 + (2 + 3 * L) + L * 8 + 3, gemms_per_position = 6 * L + 1;   // (the contraction wrapper counts its own launches)
     (void)min_prompt;
     int n_done = 0;
     cudaGraph_t graph = nullptr;
