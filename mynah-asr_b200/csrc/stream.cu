@@ -70,13 +70,14 @@ __global__ void ss_stream_cache_kernel(const float *__restrict__ x, float *__res
 
 // ---- attention of the chunk's Q rows over [valid cached frames ; chunk], no mask. Grid (H, S), STREAM_ATTN_WARPS warps.
 // score[t][j] = ((q_t + u) . k_j + (q_t + v) . rk[K-1-valid-t+j]) / sqrt(dk); ctx planes [S*Q, d]. dk is a multiple of 4.
-// Scores: a warp takes four keys at a time, a lane four consecutive elements of each k and rk row (8-byte loads, eight in
-// flight per lane). Context: warp w sums the keys j = w, w + warps, ... for the lane's four columns (four keys in flight);
+// Scores: a warp takes STREAM_ATTN_KU keys at a time, a lane four consecutive elements of each k and rk row (8-byte
+// loads). Context: warp w sums the keys j = w, w + warps, ... for the lane's four columns (as many keys in flight);
 // the partial sums are added in warp order.
 // update != 0: afterwards the chunk's k / v rows of this head go to their ring slots (update_kv_cache,
 // src/encoder.c:763-776) — the columns of head h of stream s are read by this block alone, so it may overwrite them
 // once its own reads are done.
 static constexpr int STREAM_ATTN_WARPS = 8;
+static constexpr int STREAM_ATTN_KU = 4;               // keys a warp has in flight (8 measured slower: 19.1 against 17.2 ms per step at 512 streams)
 __device__ __forceinline__ float4 ld_half4(const __half *p) {
     const uint2 a = *reinterpret_cast<const uint2 *>(p);
     const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&a.x)), hi = __half22float2(*reinterpret_cast<const __half2 *>(&a.y));
@@ -111,19 +112,22 @@ stream_attn_kernel(const float *__restrict__ q, const __half *__restrict__ kn, c
         }
         __syncthreads();
         const int base = K - 1 - valid - t;
-        for (int j0 = warp * 4; j0 < K; j0 += 4 * NW) {
-            float a[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int i0 = lane * 4; i0 < dk; i0 += 128) {
-                float4 kk[4], rr[4];
+        constexpr int KU = STREAM_ATTN_KU;
+        for (int j0 = warp * KU; j0 < K; j0 += KU * NW) {
+            float a[KU];
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < KU; u++) a[u] = 0.f;
+            for (int i0 = lane * 4; i0 < dk; i0 += 128) {
+                float4 kk[KU], rr[KU];
+#pragma unroll
+                for (int u = 0; u < KU; u++) {
                     const int j = j0 + u < K ? j0 + u : K - 1;
                     kk[u] = ld_half4(krow(j) + i0);
                     rr[u] = ld_half4(rk + (size_t)(base + j) * d + h * dk + i0);
                 }
                 const float4 u4 = *reinterpret_cast<const float4 *>(qu + i0), v4 = *reinterpret_cast<const float4 *>(qv + i0);
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < KU; u++) {
                     a[u] = fmaf(u4.x, kk[u].x, a[u]); a[u] = fmaf(v4.x, rr[u].x, a[u]);
                     a[u] = fmaf(u4.y, kk[u].y, a[u]); a[u] = fmaf(v4.y, rr[u].y, a[u]);
                     a[u] = fmaf(u4.z, kk[u].z, a[u]); a[u] = fmaf(v4.z, rr[u].z, a[u]);
@@ -131,7 +135,7 @@ stream_attn_kernel(const float *__restrict__ q, const __half *__restrict__ kn, c
                 }
             }
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < KU; u++) {
                 const float r = warp_sum(a[u]);
                 if (lane == 0 && j0 + u < K) sc[j0 + u] = r * scale;
             }
@@ -156,12 +160,12 @@ stream_attn_kernel(const float *__restrict__ q, const __half *__restrict__ kn, c
         for (int c0 = lane * 4; c0 < dk; c0 += 128) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             int j = warp;
-            for (; j + 3 * NW < K; j += 4 * NW) {
-                float4 v[4];
+            for (; j + (KU - 1) * NW < K; j += KU * NW) {
+                float4 v[KU];
 #pragma unroll
-                for (int u = 0; u < 4; u++) v[u] = ld_half4(vrow(j + NW * u) + c0);
+                for (int u = 0; u < KU; u++) v[u] = ld_half4(vrow(j + NW * u) + c0);
 #pragma unroll
-                for (int u = 0; u < 4; u++) {
+                for (int u = 0; u < KU; u++) {
                     const float w = sc[j + NW * u] * inv;
                     o.x = fmaf(w, v[u].x, o.x); o.y = fmaf(w, v[u].y, o.y); o.z = fmaf(w, v[u].z, o.z); o.w = fmaf(w, v[u].w, o.w);
                 }
