@@ -3,8 +3,9 @@
 // mynah_asr_aed_decode (src/decoder_aed.c:139-232) for B utterances in lock step.
 // All utterances sit at the same position p; each row of every kernel depends only on its own
 // utterance, so a batch decodes to the same bits as each utterance alone.
-// The large linears run on the tcgen05 contraction (model.cu); this file holds what sits
-// between them: embedding, the two single-query attentions and the greedy selection.
+// The linears run on the tcgen05 contractions (the cross K/V projections over all frames on the many-row kernel, a
+// position's linears on the few-row kernel, gemm_skinny.cu); this file holds what sits between them: the two
+// single-query attentions and the turn from one position to the next (selection, embedding, opening LayerNorms).
 #include "model.h"
 #include "ln_row.cuh"
 
@@ -462,7 +463,7 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
             note_launch(launches_per_position - gemms_per_position);
         } else {
             if (p == 1) {
-                // positions 1.. replay one captured graph (57 small launches per position are launch-bound otherwise)
+                // positions 1.. replay one captured graph of the chained launches (no host work between the kernels of a position)
                 const bool was_on = prof_on;
                 prof_on = false;                             // no event records inside the capture
                 if (cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {

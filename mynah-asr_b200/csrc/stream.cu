@@ -304,7 +304,7 @@ size_t Model::stream_bytes(const StreamState &st, int n_mel) const {
 }
 
 // In steady state (caches full, full-size chunk, same input / output / workspace addresses as last time, no
-// profiling spans wanted) the ~500 launches of a step are replayed from one captured graph: nothing the host
+// profiling spans wanted) the few hundred launches of a step are replayed from one captured graph: nothing the host
 // passes changes from step to step any more — the ring offset lives in device memory.
 int Model::stream_step(StreamState &st, const float *mel, int n_mel, int is_last, float *out) {
     const bool steady = !st.first && !is_last && st.left > 0 && st.valid == st.left && n_mel == stream_need(st) && !prof_on;
