@@ -114,8 +114,24 @@ aed_self_attn_kernel(const float *__restrict__ qkv, float *__restrict__ ck, floa
     }
 }
 
+// The cross K / V of a layer leave their contraction as planes [sum T, 2D] = (K | V) per frame; a (head, utterance) block
+// of the cross-attention would read 2 dk bytes out of every 4 D. Once per decode they are regrouped so that the T_b rows
+// of one (utterance, head) follow each other: K at ((off_b H + h T_b + j) dk), V the same v_off halves further on.
+// Grid (H, B); 16-byte copies.
+__global__ void aed_kv_by_head_kernel(const __half *__restrict__ src, __half *__restrict__ dst, size_t v_off, const int *__restrict__ enc_off,
+                                      const int *__restrict__ enc_len, int D, int dk) {
+    const int h = blockIdx.x, b = blockIdx.y, T = enc_len[b], c8 = dk >> 3;
+    const size_t r0 = (size_t)enc_off[b], kb = (r0 * gridDim.x + (size_t)h * T) * dk;
+    for (int idx = threadIdx.x; idx < T * c8; idx += blockDim.x) {
+        const int j = idx / c8, c = idx - j * c8;
+        const uint4 *s = reinterpret_cast<const uint4 *>(src + (r0 + j) * 2 * (size_t)D + h * dk) + c;
+        reinterpret_cast<uint4 *>(dst + kb + (size_t)j * dk)[c] = s[0];
+        reinterpret_cast<uint4 *>(dst + kb + v_off + (size_t)j * dk)[c] = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(s) + D);
+    }
+}
+
 // Cross-attention of one query per utterance over its T_b projected encoder frames
-// (src/decoder_aed.c:199-202). Grid (H, B), 512 threads. kv: planes [sum T, 2D] = (K | V) of this layer,
+// (src/decoder_aed.c:199-202). Grid (H, B), 512 threads. kv: the layer's K and V planes grouped by (utterance, head),
 // fp16 hi (+ lo * 2^-11 when present). q [B, D] f32 with bias. dk is a multiple of 4.
 // Scores: a warp takes four key rows at a time, a lane four consecutive elements of each (8-byte loads,
 // eight in flight per lane). Context: a warp owns every sixteenth key, a lane four adjacent columns.
@@ -133,7 +149,7 @@ __device__ __forceinline__ float4 ld_h4(const __half *hi, const __half *lo, size
 static constexpr int CROSS_WARPS = 16;
 static constexpr int CROSS_KU = 8;              // key rows a warp has in flight
 __global__ void __launch_bounds__(CROSS_WARPS * 32)
-aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ kv_hi, const __half *__restrict__ kv_lo,
+aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ kv_hi, const __half *__restrict__ kv_lo, size_t v_off,
                       const int *__restrict__ enc_off, const int *__restrict__ enc_len, int max_T, int D, int dk, H16 out) {
     extern __shared__ float sm[];
     chain_trigger();
@@ -141,7 +157,8 @@ aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ k
     float *sc = sm, *q = sm + ((max_T + 3) & ~3), *red = q + dk, *part = red + 32;     // part: [CROSS_WARPS][dk] partial outputs
     const int h = blockIdx.x, b = blockIdx.y;
     const int T = enc_len[b], lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const size_t r0 = (size_t)enc_off[b], ld = 2 * (size_t)D;
+    // K rows of (utterance b, head h) lie one after the other (aed_kv_by_head_kernel), V rows likewise v_off halves further on
+    const size_t kb = ((size_t)enc_off[b] * gridDim.x + (size_t)h * T) * dk, vb = kb + v_off;
     for (int i = threadIdx.x; i < dk; i += blockDim.x) q[i] = qm[(size_t)b * D + h * dk + i];
     __syncthreads();
     const float scale = 1.0f / sqrtf((float)dk);
@@ -154,7 +171,7 @@ aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ k
 #pragma unroll
             for (int u = 0; u < CROSS_KU; u++) {
                 const int j = j0 + u < T ? j0 + u : T - 1;
-                k[u] = ld_h4(kv_hi, kv_lo, (r0 + j) * ld + h * dk + i0);
+                k[u] = ld_h4(kv_hi, kv_lo, kb + (size_t)j * dk + i0);
             }
             const float4 qq = *reinterpret_cast<const float4 *>(q + i0);
 #pragma unroll
@@ -178,12 +195,11 @@ aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ k
     // CROSS_KU keys in flight); the partial sums are added in warp order
     for (int c0 = lane * 4; c0 < dk; c0 += 128) {
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-        const size_t col = D + h * dk + c0;
         int j = warp;
         for (; j + (CROSS_KU - 1) * CROSS_WARPS < T; j += CROSS_KU * CROSS_WARPS) {
             float4 v[CROSS_KU];
 #pragma unroll
-            for (int u = 0; u < CROSS_KU; u++) v[u] = ld_h4(kv_hi, kv_lo, (r0 + j + CROSS_WARPS * u) * ld + col);
+            for (int u = 0; u < CROSS_KU; u++) v[u] = ld_h4(kv_hi, kv_lo, vb + (size_t)(j + CROSS_WARPS * u) * dk + c0);
 #pragma unroll
             for (int u = 0; u < CROSS_KU; u++) {
                 const float w = sc[j + CROSS_WARPS * u] * inv;
@@ -191,7 +207,7 @@ aed_cross_attn_kernel(const float *__restrict__ qm, const __half *__restrict__ k
             }
         }
         for (; j < T; j += CROSS_WARPS) {
-            const float4 v = ld_h4(kv_hi, kv_lo, (r0 + j) * ld + col);
+            const float4 v = ld_h4(kv_hi, kv_lo, vb + (size_t)j * dk + c0);
             const float w = sc[j] * inv;
             o.x = fmaf(w, v.x, o.x); o.y = fmaf(w, v.y, o.y); o.z = fmaf(w, v.z, o.z); o.w = fmaf(w, v.w, o.w);
         }
@@ -311,7 +327,7 @@ static GemmEpilogue aed_epi(int mode, int act, float alpha, const float *bias, f
 
 size_t Model::aed_bytes(int total_T, int B, int max_len) const {
     const size_t D = aed_d, F = aed_ffn, L = aed_layers.size();
-    return (size_t)total_T * (d_out * 4 + D * 4 + L * 2 * D * 4) + L * 2 * (size_t)B * max_len * D * 4 +
+    return (size_t)total_T * (d_out * 4 + D * 4 + (L + 1) * 2 * D * 4) + L * 2 * (size_t)B * max_len * D * 4 +
            (size_t)B * (D * 24 + 3 * D * 4 + F * 4 + (size_t)aed_vocab * 4) + (size_t)B * (max_len + 64) * 8 + (1 << 20);
 }
 
@@ -353,11 +369,25 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
         if (!encp.hi) return -1;
         if (gemm(enc_h, d_out, aed_proj, aed_epi(OUT_H16, ACT_NONE, 1.f, aed_proj_b, nullptr, 0, encp, D), total_T)) return -1;
     }
+    int *d_off = ws.get<int>(2 * (size_t)B);
+    if (!d_off) return -1;
+    std::vector<int> ho(2 * (size_t)B);
+    for (int b = 0; b < B; b++) { ho[b] = off[b]; ho[B + b] = lens[b]; }
+    MB_CUDA(cudaMemcpyAsync(d_off, ho.data(), ho.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
+    const bool by_head = dk % 8 == 0 && D % 8 == 0;           // 16-byte copies
+    if (!by_head) { set_error("aed_decode: head width %d must be a multiple of 8", dk); return -1; }
+    const size_t v_off = (size_t)total_T * D;
     std::vector<H16> ckv(L);
+    H16 kv_rows = ws.planes((size_t)total_T * 2 * D);          // one layer's (K | V) rows as the contraction writes them
+    if (!kv_rows.hi) return -1;
     for (int l = 0; l < L; l++) {
         ckv[l] = ws.planes((size_t)total_T * 2 * D);
         if (!ckv[l].hi) return -1;
-        if (gemm(encp, D, aed_layers[l].ckv, aed_epi(OUT_H16, ACT_NONE, 1.f, aed_layers[l].ckv_b, nullptr, 0, ckv[l], 2 * D), total_T)) return -1;
+        if (gemm(encp, D, aed_layers[l].ckv, aed_epi(OUT_H16, ACT_NONE, 1.f, aed_layers[l].ckv_b, nullptr, 0, kv_rows, 2 * D), total_T)) return -1;
+        aed_kv_by_head_kernel<<<dim3(H, B), 256, 0, stream>>>(kv_rows.hi, ckv[l].hi, v_off, d_off, d_off + B, D, dk);
+        if (kv_rows.lo) aed_kv_by_head_kernel<<<dim3(H, B), 256, 0, stream>>>(kv_rows.lo, ckv[l].lo, v_off, d_off, d_off + B, D, dk);
+        MB_CUDA(cudaGetLastError());
+        note_launch(kv_rows.lo ? 2 : 1);
     }
     // ---- state
     float *sk = ws.get<float>((size_t)L * 2 * B * max_len * D);
@@ -365,20 +395,18 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
     float *logits = ws.get<float>((size_t)B * V);
     H16 xn = ws.planes((size_t)B * D), att = ws.planes((size_t)B * D), ff = ws.planes((size_t)B * F);
     int *st = ws.get<int>(7 * (size_t)B + 4), *best = ws.get<int>(B), *d_prompts = ws.get<int>((size_t)B * max_prompt);
-    int *d_tokens = ws.get<int>((size_t)B * capn), *d_off = ws.get<int>(2 * (size_t)B);
-    if (!sk || !x || !qkv || !q || !logits || !xn.hi || !att.hi || !ff.hi || !st || !best || !d_prompts || !d_tokens || !d_off) return -1;
-    std::vector<int> hst(7 * (size_t)B + 4, 0), hp((size_t)B * max_prompt, 0), ho(2 * (size_t)B);
+    int *d_tokens = ws.get<int>((size_t)B * capn);
+    if (!sk || !x || !qkv || !q || !logits || !xn.hi || !att.hi || !ff.hi || !st || !best || !d_prompts || !d_tokens) return -1;
+    std::vector<int> hst(7 * (size_t)B + 4, 0), hp((size_t)B * max_prompt, 0);
     for (int b = 0; b < B; b++) {
         hst[b] = prompts[b][0];                              // cur
         hst[3 * B + b] = (int)prompts[b].size();
         hst[4 * B + b] = mlen[b];
         hst[5 * B + b] = caps[b] > 0 ? caps[b] : 0;
         for (size_t i = 0; i < prompts[b].size(); i++) hp[(size_t)b * max_prompt + i] = prompts[b][i];
-        ho[b] = off[b]; ho[B + b] = lens[b];
     }
     MB_CUDA(cudaMemcpyAsync(st, hst.data(), hst.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
     MB_CUDA(cudaMemcpyAsync(d_prompts, hp.data(), hp.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
-    MB_CUDA(cudaMemcpyAsync(d_off, ho.data(), ho.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
     const size_t self_smem = ((size_t)max_len + 4 + (1 + SELF_WARPS) * (size_t)dk + 32) * sizeof(float);
     const int cross_threads = CROSS_WARPS * 32;
     const size_t cross_smem = ((size_t)max_T + 4 + (1 + CROSS_WARPS) * (size_t)dk + 32) * sizeof(float);
@@ -435,7 +463,7 @@ int Model::decode_aed(const float *enc_dev, const std::vector<int> &lens, const 
             if (!ln_tail && layer_norm(x, A.ln_cross_w, A.ln_cross_b, nullptr, xn, B, D, 0, stream, true)) return -1;
             if (gemm(xn, D, A.cq, aed_epi(OUT_F32, ACT_NONE, 1.f, A.cq_b, q, D), B, true)) return -1;
             MB_CUDA(launch_kernel(aed_cross_attn_kernel, dim3(H, B), dim3(cross_threads), cross_smem, stream, true, 1, (const float *)q, (const __half *)ckv[l].hi,
-                                  (const __half *)ckv[l].lo, (const int *)d_off, (const int *)(d_off + B), max_T, D, dk, att));
+                                  (const __half *)ckv[l].lo, v_off, (const int *)d_off, (const int *)(d_off + B), max_T, D, dk, att));
             if (gemm(att, D, A.co, resid(A.co_b, A.ln_ffn_w, A.ln_ffn_b), B, true)) return -1;
             if (!ln_tail && layer_norm(x, A.ln_ffn_w, A.ln_ffn_b, nullptr, xn, B, D, 0, stream, true)) return -1;
             if (gemm(xn, D, A.ff1, aed_epi(OUT_H16, ACT_RELU, 1.f, A.ff1_b, nullptr, 0, ff, F), B, true)) return -1;
