@@ -81,7 +81,7 @@ struct StreamState {
     int mel_cur = 0;
     long long mel_base = 0, mel_total = 0, mel_next = 0;
     float *ss_cache[3] = {nullptr, nullptr, nullptr};   // last input frame of each subsampling stage: [S,F0], [S,F1,C], [S,F2,C]
-    __half *k_cache = nullptr, *v_cache = nullptr;      // [L][S][left][d] fp16
+    __half *k_cache = nullptr, *v_cache = nullptr;      // [L][S][H][left][dk] fp16: the ring of one (stream, head) is contiguous
     float *conv_cache = nullptr;                        // [L][S][k-1][d] GLU rows
     std::vector<int> prompt_ids;                        // prompt-conditioned encoders: one id per stream (empty = 0)
     std::vector<void *> owned;

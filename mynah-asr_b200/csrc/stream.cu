@@ -99,10 +99,11 @@ stream_attn_kernel(const float *__restrict__ q, const __half *__restrict__ kn, c
     float *part = red + 32;                            // [NW][dk]
     const int h = blockIdx.x, s = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float scale = 1.0f / sqrtf((float)dk);
-    const size_t cbase = (size_t)s * left * d + h * dk, nbase = (size_t)s * Q * d + h * dk;
+    // the ring of (stream s, head h) is one contiguous block of left x dk halves: [S][H][left][dk]
+    const size_t cbase = ((size_t)s * gridDim.x + h) * left * dk, nbase = (size_t)s * Q * d + h * dk;
     // row j of the keys / values: a cached frame in its ring slot, or a row of the chunk
-    auto krow = [&](int j) { int x = start + j; if (x >= left) x -= left; return j < valid ? kc + cbase + (size_t)x * d : kn + nbase + (size_t)(j - valid) * d; };
-    auto vrow = [&](int j) { int x = start + j; if (x >= left) x -= left; return j < valid ? vc + cbase + (size_t)x * d : vn + nbase + (size_t)(j - valid) * d; };
+    auto krow = [&](int j) { int x = start + j; if (x >= left) x -= left; return j < valid ? kc + cbase + (size_t)x * dk : kn + nbase + (size_t)(j - valid) * d; };
+    auto vrow = [&](int j) { int x = start + j; if (x >= left) x -= left; return j < valid ? vc + cbase + (size_t)x * dk : vn + nbase + (size_t)(j - valid) * d; };
     for (int t = 0; t < Q; t++) {
         const size_t row = (size_t)s * Q + t;
         for (int i = threadIdx.x; i < dk; i += blockDim.x) {
@@ -193,8 +194,8 @@ stream_attn_kernel(const float *__restrict__ q, const __half *__restrict__ kn, c
             const int t = idx / dk, i = idx - t * dk;
             int x = start + valid + t;
             x %= left;
-            kc[cbase + (size_t)x * d + i] = kn[nbase + (size_t)t * d + i];
-            vc[cbase + (size_t)x * d + i] = vn[nbase + (size_t)t * d + i];
+            kc[cbase + (size_t)x * dk + i] = kn[nbase + (size_t)t * d + i];
+            vc[cbase + (size_t)x * dk + i] = vn[nbase + (size_t)t * d + i];
         }
     }
 }
